@@ -1,0 +1,182 @@
+// Test infrastructure only: a thin extern "C" window onto the UNMODIFIED
+// reference CPU library (compiled by oracle/Makefile into
+// oracle/_ref/libmollm_ref.so).  It exists so that tests, the fixture
+// generator and the bench's CPU-baseline leg can call the reference's own
+// functions through ctypes.  No arithmetic happens here: every function builds
+// the reference's Tensor descriptors and forwards.
+//
+// Reference entry points that are forwarded to:
+//   quantize_a_q8_g128_even_odd   kernels/matmul_quant.cpp:578-641
+//   quantize_a_q8_blocks          kernels/matmul_quant.cpp:280-329
+//   kernel_matmul_fp32            kernels/matmul.cpp:69-97 (x86: W4A32 provider,
+//                                 kernels/cpu_platform_x86.cpp:128-270)
+//   pack_b_q4dot_int4_full / pack_b_q4dot_g128_full
+//                                 kernels/matmul_pack.cpp:641-688
+//   select_moe_routes             kernels/moe_routing.cpp:25-169
+//   kernel_qwen3_moe              kernels/moe.cpp:576-1129
+#include "kernels/matmul.h"
+#include "kernels/matmul_internal.h"
+#include "kernels/moe.h"
+#include "kernels/moe_routing.h"
+#include "kernels/quant_layouts.h"
+#include "kernels/threading.h"
+
+#include <chrono>
+#include <cstdint>
+#include <cstring>
+#include <memory>
+#include <vector>
+
+namespace {
+
+Tensor make_bg128_weight(const void* blocks, int n, int k) {
+    Tensor w = Tensor::create(Precision::INT4, MemoryType::EXTERNAL, n, k, 1, 1,
+                              const_cast<void*>(blocks));
+    w.group_size = 128;
+    w.groups_per_row = static_cast<uint32_t>(k / 128);
+    w.num_groups = static_cast<uint32_t>(n) * w.groups_per_row;
+    w.is_q4_g128_packed = true;
+    w.q4_g128_data = blocks;
+    return w;
+}
+
+ThreadPool* pool_for(int threads) {
+    static std::unique_ptr<ThreadPool> pool;
+    static int pool_threads = 0;
+    if (threads <= 1)
+        return nullptr;
+    if (!pool || pool_threads != threads) {
+        pool.reset(new ThreadPool(threads));
+        pool_threads = threads;
+    }
+    return pool.get();
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* ref_isa_name() { return mollm::cpu::isa_name(); }
+
+// M=1 activation quantiser, one scale per 128 values, even/odd de-interleaved.
+void ref_quantize_a_q8_g128_even_odd(const float* a, int k, int8_t* even,
+                                     int8_t* odd, float* scales) {
+    std::vector<int8_t> e, o;
+    std::vector<float> s;
+    quantize_a_q8_g128_even_odd(a, k, e, o, s);
+    std::memcpy(even, e.data(), e.size());
+    std::memcpy(odd, o.data(), o.size());
+    std::memcpy(scales, s.data(), s.size() * sizeof(float));
+}
+
+// M>1 activation quantiser, one scale per 32 values, natural k order.
+void ref_quantize_a_q8_blocks(const float* a, int m, int k, int lda, int8_t* q,
+                              float* scales) {
+    std::vector<int8_t> qa;
+    std::vector<float> s;
+    quantize_a_q8_blocks(a, m, k, lda, k, qa, s);
+    std::memcpy(q, qa.data(), qa.size());
+    std::memcpy(scales, s.data(), s.size() * sizeof(float));
+}
+
+// Row-major int4 bytes [N, K/2] + fp32 scales [N, K/128] -> BG128 blocks.
+// `out` must hold ((N+7)/8)*(K/128)*544 bytes.  Returns 0 on success.
+int ref_pack_bg128(const uint8_t* rowmajor_q4, const float* scales, int n, int k,
+                   uint8_t* out) {
+    uint8_t* q4dot = pack_b_q4dot_int4_full(rowmajor_q4, n, k, k);
+    if (!q4dot)
+        return -1;
+    uint8_t* bg = pack_b_q4dot_g128_full(q4dot, scales, n, k, k / 128);
+    delete[] q4dot;
+    if (!bg)
+        return -2;
+    std::memcpy(out, bg, pack_b_q4dot_g128_bytes(n, k));
+    delete[] bg;
+    return 0;
+}
+
+// The reference's matmul entry point on a BG128 weight.  On x86 this is the
+// W4A32 provider (fp32 activations), not the W4A8 arithmetic.
+void ref_matmul_bg128(const float* a, int m, int k, int lda, const void* blocks,
+                      int n, float* c, int ldc, int act, int act_n_begin,
+                      int act_n_len, int threads) {
+    Tensor A = Tensor::create(Precision::FP32, MemoryType::EXTERNAL, k, m, 1, 1,
+                              const_cast<float*>(a));
+    A.stride[1] = static_cast<size_t>(lda) * sizeof(float);
+    Tensor B = make_bg128_weight(blocks, n, k);
+    Tensor C = Tensor::create(Precision::FP32, MemoryType::EXTERNAL, n, m, 1, 1, c);
+    C.stride[1] = static_cast<size_t>(ldc) * sizeof(float);
+    kernel_matmul_fp32(A, B, C, pool_for(threads), static_cast<Activation>(act),
+                       act_n_begin, act_n_len);
+}
+
+// Average seconds per call of ref_matmul_bg128 over `repeat` calls, rotating
+// through `copies` weight buffers laid back to back at `blocks` so a hot cache
+// cannot serve the weight stream.
+double ref_time_matmul_bg128(const float* a, int m, int k, const void* blocks,
+                             size_t copy_stride_bytes, int copies, int n,
+                             float* c, int threads, int warmup, int repeat) {
+    ThreadPool* pool = pool_for(threads);
+    Tensor A = Tensor::create(Precision::FP32, MemoryType::EXTERNAL, k, m, 1, 1,
+                              const_cast<float*>(a));
+    Tensor C = Tensor::create(Precision::FP32, MemoryType::EXTERNAL, n, m, 1, 1, c);
+    auto run = [&](int i) {
+        const uint8_t* p = static_cast<const uint8_t*>(blocks) +
+                           static_cast<size_t>(i % copies) * copy_stride_bytes;
+        Tensor B = make_bg128_weight(p, n, k);
+        kernel_matmul_fp32(A, B, C, pool);
+    };
+    for (int i = 0; i < warmup; ++i)
+        run(i);
+    auto t0 = std::chrono::steady_clock::now();
+    for (int i = 0; i < repeat; ++i)
+        run(warmup + i);
+    auto t1 = std::chrono::steady_clock::now();
+    return std::chrono::duration<double>(t1 - t0).count() / repeat;
+}
+
+int ref_select_moe_routes(const float* logits, int tokens, int num_experts,
+                          int top_k, int score_func, int normalize_topk,
+                          int32_t* indices, float* weights) {
+    mollm::detail::MoeRoutingParams p;
+    p.num_experts = num_experts;
+    p.top_k = top_k;
+    p.score_func = score_func;
+    p.normalize_topk = normalize_topk != 0;
+    std::vector<int> idx;
+    std::vector<float> w;
+    if (!mollm::detail::select_moe_routes(logits, tokens, nullptr, p, idx, w))
+        return -1;
+    for (size_t i = 0; i < idx.size(); ++i)
+        indices[i] = idx[i];
+    std::memcpy(weights, w.data(), w.size() * sizeof(float));
+    return 0;
+}
+
+// Routed MoE op with an fp16 router [E, H], BG128 gate_up [E*2I, H] and BG128
+// down [E*H, I] aggregates, softmax top-k routing and no shared expert (the
+// Qwen3-MoE configuration, models/qwen3_moe.py:782-797 of the reference).
+int ref_moe_bg128(const float* hidden, int tokens, int hidden_size,
+                  const uint16_t* router_fp16, int num_experts, int top_k,
+                  int intermediate, const void* gate_up_blocks,
+                  const void* down_blocks, float* out, int threads) {
+    Tensor x = Tensor::create(Precision::FP32, MemoryType::EXTERNAL, hidden_size,
+                              tokens, 1, 1, const_cast<float*>(hidden));
+    Tensor router = Tensor::create(Precision::FP16, MemoryType::EXTERNAL,
+                                   num_experts, hidden_size, 1, 1,
+                                   const_cast<uint16_t*>(router_fp16));
+    Tensor gu = make_bg128_weight(gate_up_blocks, num_experts * 2 * intermediate,
+                                  hidden_size);
+    Tensor dn = make_bg128_weight(down_blocks, num_experts * hidden_size,
+                                  intermediate);
+    Tensor y = Tensor::create(Precision::FP32, MemoryType::EXTERNAL, hidden_size,
+                              tokens, 1, 1, out);
+    std::vector<const Tensor*> inputs = {&x, &router, &gu, &dn};
+    bool ok = kernel_qwen3_moe(inputs, y, pool_for(threads), hidden_size,
+                               num_experts, top_k, intermediate, 0,
+                               /*router_score_func=*/0, /*norm_topk_prob=*/true,
+                               /*has_shared_expert=*/false);
+    return ok ? 0 : -1;
+}
+
+}  // extern "C"

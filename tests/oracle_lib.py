@@ -1,0 +1,222 @@
+"""ctypes bindings of the CPU oracle (oracle/w4a8_oracle.c) and, when it has been
+built, of the unmodified reference library (oracle/_ref).  Test infrastructure only.
+"""
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+ORACLE_DIR = os.path.join(ROOT, "oracle")
+ORACLE_SO = os.path.join(ORACLE_DIR, "liboracle_w4a8.so")
+REF_SO = os.path.join(ORACLE_DIR, "_ref", "libref_shim.so")
+
+ACT_G128, ACT_G32, ACT_F64 = 128, 32, 0
+BLOCK_BYTES = 544
+
+
+def _ptr(a, t=C.c_void_p):
+    return a.ctypes.data_as(t) if a is not None else None
+
+
+def build_oracle():
+    src = os.path.join(ORACLE_DIR, "w4a8_oracle.c")
+    if (not os.path.exists(ORACLE_SO)
+            or os.path.getmtime(ORACLE_SO) < os.path.getmtime(src)):
+        subprocess.check_call(["make", "-s", "-C", ORACLE_DIR, "oracle"])
+
+
+_oracle = None
+
+
+def oracle():
+    global _oracle
+    if _oracle is None:
+        build_oracle()
+        lib = C.CDLL(ORACLE_SO)
+        lib.orc_bg128_bytes.restype = C.c_size_t
+        lib.orc_fp16_to_fp32.restype = C.c_float
+        _oracle = lib
+    return _oracle
+
+
+def have_ref():
+    return os.path.exists(REF_SO)
+
+
+_ref = None
+
+
+def ref():
+    global _ref
+    if _ref is None:
+        lib = C.CDLL(REF_SO)
+        lib.ref_isa_name.restype = C.c_char_p
+        lib.ref_time_matmul_bg128.restype = C.c_double
+        _ref = lib
+    return _ref
+
+
+# ---------------------------------------------------------------- oracle calls
+
+def bg128_bytes(n, k):
+    return ((n + 7) // 8) * (k // 128) * BLOCK_BYTES
+
+
+def bg128_encode(q, scales):
+    """q int8 [N,K] in [-8,7], scales fp32 [N,K/128] -> uint8 blocks."""
+    n, k = q.shape
+    q = np.ascontiguousarray(q, dtype=np.int8)
+    scales = np.ascontiguousarray(scales, dtype=np.float32)
+    out = np.zeros(bg128_bytes(n, k), dtype=np.uint8)
+    oracle().orc_bg128_encode(_ptr(q), _ptr(scales), n, k, _ptr(out))
+    return out
+
+
+def bg128_decode(blocks, n, k):
+    q = np.zeros((n, k), dtype=np.int8)
+    s = np.zeros((n, k // 128), dtype=np.float32)
+    oracle().orc_bg128_decode(_ptr(blocks), n, k, _ptr(q), _ptr(s))
+    return q, s
+
+
+def quantize_g128(x):
+    k = x.shape[-1]
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    q = np.zeros(k, dtype=np.int8)
+    s = np.zeros(k // 128, dtype=np.float32)
+    oracle().orc_quantize_a_g128(_ptr(x), k, _ptr(q), _ptr(s))
+    return q, s
+
+
+def quantize_g128_even_odd(x):
+    k = x.shape[-1]
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    e = np.zeros(k // 2, dtype=np.int8)
+    o = np.zeros(k // 2, dtype=np.int8)
+    s = np.zeros(k // 128, dtype=np.float32)
+    oracle().orc_quantize_a_g128_even_odd(_ptr(x), k, _ptr(e), _ptr(o), _ptr(s))
+    return e, o, s
+
+
+def quantize_g32(x):
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    m, k = x.shape
+    q = np.zeros((m, k), dtype=np.int8)
+    s = np.zeros((m, k // 32), dtype=np.float32)
+    oracle().orc_quantize_a_g32(_ptr(x), m, k, k, _ptr(q), _ptr(s))
+    return q, s
+
+
+def matmul_w4(blocks, n, k, x, rule=ACT_G128, want_sums=False):
+    """x fp32 [M,K] -> y fp32 [M,N] (and int32 group sums when asked)."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    m = x.shape[0]
+    y = np.zeros((m, n), dtype=np.float32)
+    sums = None
+    if want_sums:
+        per = k // 128 if rule == ACT_G128 else k // 32
+        sums = np.zeros((m, n, per), dtype=np.int32)
+    rc = oracle().orc_matmul_w4(_ptr(blocks), n, k, _ptr(x), m, k, _ptr(y), n, rule,
+                                _ptr(sums))
+    assert rc == 0, rc
+    return (y, sums) if want_sums else y
+
+
+def apply_activation(y, act, begin=0, length=-1):
+    y = np.ascontiguousarray(y, dtype=np.float32)
+    m, n = y.shape
+    oracle().orc_apply_activation(_ptr(y), m, n, n, act, begin, length)
+    return y
+
+
+def select_routes(logits, top_k):
+    logits = np.ascontiguousarray(logits, dtype=np.float32)
+    t, e = logits.shape
+    idx = np.zeros((t, top_k), dtype=np.int32)
+    w = np.zeros((t, top_k), dtype=np.float32)
+    rc = oracle().orc_moe_select_routes_softmax(_ptr(logits), t, e, top_k, _ptr(idx),
+                                                _ptr(w))
+    assert rc == 0
+    return idx, w
+
+
+def moe_forward(hidden, router_fp16, top_k, intermediate, gate_up, down, rule=ACT_G128):
+    hidden = np.ascontiguousarray(hidden, dtype=np.float32)
+    t, h = hidden.shape
+    e = router_fp16.shape[0]
+    router_fp16 = np.ascontiguousarray(router_fp16.view(np.uint16))
+    out = np.zeros((t, h), dtype=np.float32)
+    logits = np.zeros((t, e), dtype=np.float32)
+    idx = np.zeros((t, top_k), dtype=np.int32)
+    w = np.zeros((t, top_k), dtype=np.float32)
+    rc = oracle().orc_moe_forward(_ptr(hidden), t, h, h, _ptr(router_fp16), e, top_k,
+                                  intermediate, _ptr(gate_up), _ptr(down), _ptr(out), h,
+                                  rule, _ptr(logits), _ptr(idx), _ptr(w))
+    assert rc == 0, rc
+    return out, logits, idx, w
+
+
+# ------------------------------------------------------------- reference calls
+
+def ref_quantize_g128_even_odd(x):
+    k = x.shape[-1]
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    e = np.zeros(k // 2, dtype=np.int8)
+    o = np.zeros(k // 2, dtype=np.int8)
+    s = np.zeros(k // 128, dtype=np.float32)
+    ref().ref_quantize_a_q8_g128_even_odd(_ptr(x), k, _ptr(e), _ptr(o), _ptr(s))
+    return e, o, s
+
+
+def ref_quantize_g32(x):
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    m, k = x.shape
+    q = np.zeros((m, k), dtype=np.int8)
+    s = np.zeros((m, k // 32), dtype=np.float32)
+    ref().ref_quantize_a_q8_blocks(_ptr(x), m, k, k, _ptr(q), _ptr(s))
+    return q, s
+
+
+def ref_pack_bg128(q, scales):
+    """Through the reference's own packers: row-major nibbles -> q4dot -> BG128."""
+    n, k = q.shape
+    nib = (q.astype(np.int16) & 15).astype(np.uint8)
+    rowmajor = np.ascontiguousarray(nib[:, 0::2] | (nib[:, 1::2] << 4))
+    scales = np.ascontiguousarray(scales, dtype=np.float32)
+    out = np.zeros(bg128_bytes(n, k), dtype=np.uint8)
+    rc = ref().ref_pack_bg128(_ptr(rowmajor), _ptr(scales), n, k, _ptr(out))
+    assert rc == 0, rc
+    return out
+
+
+def ref_matmul(blocks, n, k, x, act=0, begin=0, length=-1, threads=1):
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    m = x.shape[0]
+    y = np.zeros((m, n), dtype=np.float32)
+    ref().ref_matmul_bg128(_ptr(x), m, k, k, _ptr(blocks), n, _ptr(y), n, act, begin,
+                           length, threads)
+    return y
+
+
+def ref_select_routes(logits, top_k):
+    logits = np.ascontiguousarray(logits, dtype=np.float32)
+    t, e = logits.shape
+    idx = np.zeros((t, top_k), dtype=np.int32)
+    w = np.zeros((t, top_k), dtype=np.float32)
+    rc = ref().ref_select_moe_routes(_ptr(logits), t, e, top_k, 0, 1, _ptr(idx), _ptr(w))
+    assert rc == 0
+    return idx, w
+
+
+def ref_moe(hidden, router_fp16, top_k, intermediate, gate_up, down, threads=1):
+    hidden = np.ascontiguousarray(hidden, dtype=np.float32)
+    t, h = hidden.shape
+    e = router_fp16.shape[0]
+    router_fp16 = np.ascontiguousarray(router_fp16.view(np.uint16))
+    out = np.zeros((t, h), dtype=np.float32)
+    rc = ref().ref_moe_bg128(_ptr(hidden), t, h, _ptr(router_fp16), e, top_k,
+                             intermediate, _ptr(gate_up), _ptr(down), _ptr(out), threads)
+    assert rc == 0
+    return out
