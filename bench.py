@@ -1,0 +1,356 @@
+"""Benchmark of the W4G128 / W4A8 matmul path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (benchmark configuration 2's decode GEMV): y[1,9728] = x[1,2560] * W^T with W a
+W4G128 weight, synthetic and seeded.  One step = one GEMV over each of R distinct weight
+copies (R * 12.9 MB > the 126 MB L2, so every launch streams its weight from HBM).
+metric = algorithmic bytes moved per second (weights at 4.125 bit + fp32 x + fp32 y).
+
+ours, N=1      : weights and activations resident in HBM, CUDA-event timing (`value`);
+                 the same step through b2w4_matmul_host with pinned HOST buffers (`e2e`);
+                 M in {4,16,64,256} and a Qwen3-4B-shaped decode matmul walk (`sweep`);
+                 the reference's own CPU kernel on this box's host cores (`cpu_baseline`).
+ours, N>1      : tensor parallel -- every weight is split by output rows across the ranks,
+                 each rank streams its shard, an NCCL all-gather rebuilds y (strong scaling).
+--impl reference: the reference's CPU implementation of the same step (rank 0 only).
+Prints ONE JSON line on rank 0.
+"""
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+from __graft_entry__ import load_package  # noqa: E402
+
+N_OUT, K_IN = 9728, 2560
+COPIES = 32   # distinct weight buffers walked by one pass
+PASSES = 16   # passes per step: one step = PASSES * COPIES GEMVs
+SEED_W, SEED_X = 20261125, 7
+METRIC, UNIT = "w4g128_gemv_hbm_gbs", "GB/s"
+L2_MB = 126
+
+
+def algorithmic_bytes(n, k, m):
+    """int4 weights + one fp16 scale per 128 weights + fp32 x + fp32 y."""
+    return n * k // 2 + n * (k // 128) * 2 + m * k * 4 + m * n * 4
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return float(p["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                 "-lms", "100", "-i", str(self.index)],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc:
+            time.sleep(0.15)
+            self.proc.terminate()
+            self.thread.join(timeout=2)
+
+    def summary(self):
+        sm = [float(r[1]) for r in self.rows if len(r) >= 9 and r[1].replace(".", "").isdigit()]
+        mx = [float(r[2]) for r in self.rows if len(r) >= 9 and r[2].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({names[i] for r in self.rows if len(r) >= 9
+                          for i in range(4) if r[5 + i].lower().startswith("active")})
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None, "reasons": reasons,
+                "samples": len(sm)}
+
+
+def time_steps(torch, fn, steps, warmup, barrier=None):
+    for _ in range(warmup):
+        fn()
+    if barrier:
+        barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    if barrier:
+        barrier()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps  # ms per step
+
+
+# --------------------------------------------------------------------------- reference
+
+def reference_lib():
+    """oracle/_ref (the unmodified reference CPU library) if it was built, else None."""
+    path = os.path.join(ROOT, "oracle", "_ref", "libref_shim.so")
+    if not os.path.exists(path):
+        return None
+    lib = ctypes.CDLL(path)
+    lib.ref_time_matmul_bg128.restype = ctypes.c_double
+    lib.ref_isa_name.restype = ctypes.c_char_p
+    return lib
+
+
+def cpu_gemv_seconds(pkg, m, copies, repeat, warmup=2):
+    """Seconds per GEMV of the reference's CPU kernel (all host threads) on the bench
+    workload, rotating `copies` weight buffers; falls back to the scalar oracle port."""
+    cores = os.cpu_count() or 1
+    x = pkg.synth.activations(SEED_X, 0, m, K_IN)
+    one = pkg.synth.bg128_weight(SEED_W, 1, N_OUT, K_IN)
+    lib = reference_lib()
+    if lib is not None:
+        buf = np.concatenate([np.roll(one, 544 * i) for i in range(copies)])
+        y = np.zeros((m, N_OUT), dtype=np.float32)
+        sec = lib.ref_time_matmul_bg128(
+            x.ctypes.data_as(ctypes.c_void_p), m, K_IN, buf.ctypes.data_as(ctypes.c_void_p),
+            ctypes.c_size_t(one.nbytes), copies, N_OUT, y.ctypes.data_as(ctypes.c_void_p),
+            cores, warmup, repeat)
+        return sec, "reference", cores, lib.ref_isa_name().decode()
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import oracle_lib as ol
+    t0 = time.perf_counter()
+    for _ in range(max(1, repeat // 50)):
+        ol.matmul_w4(one, N_OUT, K_IN, x)
+    return (time.perf_counter() - t0) / max(1, repeat // 50), "port", 1, "scalar C"
+
+
+def run_reference(args):
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    pkg = load_package()
+    copies = 16
+    probe, kind, cores, isa = cpu_gemv_seconds(pkg, 1, copies, 8, warmup=2)
+    per_step = max(copies, min(COPIES * 8, int(2.0 / max(probe, 1e-6))))  # ~2 s per step
+    times = []
+    for i in range(args.warmup + args.steps):
+        sec, kind, cores, isa = cpu_gemv_seconds(pkg, 1, copies, per_step, warmup=0)
+        if i >= args.warmup:
+            times.append(sec)
+    sec = sum(times) / len(times)
+    gbs = algorithmic_bytes(N_OUT, K_IN, 1) / sec / 1e9
+    sample = (f"{per_step} GEMVs per step rotating {copies} weight copies, "
+              f"{cores} host threads, isa {isa} (W4A32 arithmetic)")
+    line = {"impl": "reference", "metric": METRIC, "value": gbs, "unit": UNIT,
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": sec * per_step * 1e3, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"W4G128 GEMV M=1 K={K_IN} N={N_OUT} on host cores",
+                       "copies": copies},
+            "cpu_baseline": {"value": gbs, "unit": UNIT, "cores": cores, "kind": kind,
+                             "sample": sample},
+            "e2e": {"value": gbs, "unit": UNIT, "h2d_bytes_per_step": 0,
+                    "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line))
+
+
+# --------------------------------------------------------------------------------- ours
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    barrier = (lambda: dist.barrier()) if world > 1 else None
+
+    pkg = load_package()
+    ctx = pkg.capi.Context(local)
+    ctx.set_stream(torch.cuda.current_stream().cuda_stream)
+
+    # rank r owns output rows [r*N/P, (r+1)*N/P) of every weight copy (8-row tiles kept whole)
+    n_local = N_OUT // world
+    assert N_OUT % (8 * world) == 0
+    one = pkg.synth.bg128_weight(SEED_W, 1, N_OUT, K_IN)
+    tile_bytes = (K_IN // 128) * 544
+    lo = rank * (n_local // 8) * tile_bytes
+    shard = one[lo:lo + (n_local // 8) * tile_bytes]
+    weights = []
+    for i in range(COPIES):  # distinct device buffers; rolling by whole blocks keeps layout
+        weights.append(ctx.upload_weight(np.roll(shard, 544 * i), n_local, K_IN))
+    stream_bytes = weights[0].stream_bytes
+
+    def make_io(m):
+        x = torch.from_numpy(pkg.synth.activations(SEED_X, 0, m, K_IN)).cuda()
+        y_local = torch.zeros((m, n_local), dtype=torch.float32, device="cuda")
+        y_full = torch.zeros((world, m, n_local), dtype=torch.float32, device="cuda")
+        return x, y_local, y_full
+
+    def make_step(m, rule=pkg.capi.ACT_G128, passes=args.passes, graph=not args.no_graph):
+        """One step = `passes` walks over the weight copies.  The launches are captured in
+        a CUDA graph once (decode loops are launch-bound otherwise) and replayed."""
+        x, y_local, y_full = make_io(m)
+
+        def eager():
+            for _ in range(passes):
+                for w in weights:
+                    ctx.matmul(w, x, y_local, rule=rule)
+                    if world > 1:
+                        dist.all_gather_into_tensor(y_full, y_local)
+        if not graph:
+            return eager
+        eager()  # warm every kernel variant and NCCL before capture
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            ctx.set_stream(side.cuda_stream)
+            with torch.cuda.graph(g, stream=side):
+                eager()
+        ctx.set_stream(torch.cuda.current_stream().cuda_stream)
+        return g.replay
+
+    # ---- headline: M=1, resident inputs -------------------------------------------------
+    l0 = ctx.launches
+    make_step(1, graph=False)()
+    launches_per_step = ctx.launches - l0
+    step = make_step(1)
+    with ClockSampler(local) as clocks:
+        ms = time_steps(torch, step, args.steps, args.warmup, barrier)
+    if world > 1:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    alg = algorithmic_bytes(N_OUT, K_IN, 1)
+    gemvs = COPIES * args.passes
+    value = gemvs * alg / (ms * 1e-3) / 1e9
+    launch_us = ms * 1e3 / gemvs
+    peak, peak_kind = measured_peaks()
+    achieved = algorithmic_bytes(n_local, K_IN, 1) / (launch_us * 1e-6) / 1e9
+
+    line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "s8*s4->s32, f32 scale chain", "data": "synthetic",
+            "config": {"workload": f"W4G128 W4A8 GEMV M=1 K={K_IN} N={N_OUT} "
+                                   f"(benchmark configuration 2, decode)",
+                       "gemvs_per_step": COPIES * args.passes,
+                       "launch": ("eager" if args.no_graph else "CUDA graph replay")
+                       + ", programmatic dependent launch",
+                       "l2": f"rotates {COPIES} distinct weight copies "
+                             f"({COPIES * stream_bytes * world / 1e6:.0f} MB) > {L2_MB} MB L2",
+                       "parallelism": f"tp{world} (output rows split, NCCL all-gather)"
+                       if world > 1 else "single GPU",
+                       "act_rule": "int8 per 128 values"},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak, "traffic": None,
+                         "kernel": "gemv_w4a8_kernel", "peak_kind": peak_kind,
+                         "algorithmic_bytes_per_launch": algorithmic_bytes(n_local, K_IN, 1),
+                         "avg_launch_us": launch_us},
+            "clocks": clocks.summary(),
+            "gpu_launches": launches_per_step * args.steps}
+
+    if rank == 0 and world == 1 and not args.headline_only:
+        # ---- e2e: the same step through the host-buffer entry point ---------------------
+        xh = torch.from_numpy(pkg.synth.activations(SEED_X, 0, 1, K_IN)).pin_memory()
+        yh = torch.zeros((1, N_OUT), dtype=torch.float32).pin_memory()
+        xn, yn = xh.numpy(), yh.numpy()
+
+        def host_step():
+            for _ in range(args.passes):
+                for w in weights:
+                    ctx.matmul_host(w, xn, yn)
+        for _ in range(args.warmup):
+            host_step()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            host_step()
+        e2e_s = (time.perf_counter() - t0) / args.steps
+        line["e2e"] = {"value": gemvs * alg / e2e_s / 1e9, "unit": UNIT,
+                       "h2d_bytes_per_step": gemvs * K_IN * 4,
+                       "d2h_bytes_per_step": gemvs * N_OUT * 4,
+                       "ms_per_step": e2e_s * 1e3,
+                       "api": "b2w4_matmul_host (pinned host x and y, synchronous)"}
+
+        # ---- sweep: batched decode and prefill on the same weight -----------------------
+        sweep = {}
+        for m in (4, 16, 64, 256):
+            s_ms = time_steps(torch, make_step(m, passes=1), max(3, min(args.steps, 25)), 3)
+            per = s_ms * 1e-3 / COPIES
+            sweep[f"m{m}"] = {"us_per_matmul": per * 1e6,
+                              "gbs": algorithmic_bytes(N_OUT, K_IN, m) / per / 1e9,
+                              "tflops": 2.0 * m * N_OUT * K_IN / per / 1e12,
+                              "tokens_per_s": m / per}
+        line["sweep"] = sweep
+
+        # ---- CPU baseline: the reference's own kernel on this box's host cores ----------
+        probe, kind, cores, isa = cpu_gemv_seconds(pkg, 1, 16, 8)
+        repeat = max(32, min(20000, int(12.0 / max(probe, 1e-6))))
+        sec, kind, cores, isa = cpu_gemv_seconds(pkg, 1, 16, repeat)
+        line["cpu_baseline"] = {
+            "value": alg / sec / 1e9, "unit": UNIT, "cores": cores, "kind": kind,
+            "sample": f"{repeat} GEMVs rotating 16 weight copies, isa {isa}, "
+                      f"W4A32 arithmetic ({sec * 1e3:.3f} ms per GEMV)"}
+    elif rank == 0:
+        line["e2e"] = {"value": None, "unit": UNIT, "h2d_bytes_per_step": 0,
+                       "d2h_bytes_per_step": 0, "note": "measured at N=1 only"}
+
+    if rank == 0:
+        print(json.dumps(line))
+    for w in weights:
+        w.free()
+    ctx.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--passes", type=int, default=PASSES,
+                    help="walks over the weight copies per step")
+    ap.add_argument("--no-graph", action="store_true",
+                    help="launch eagerly instead of replaying a CUDA graph (profiling)")
+    ap.add_argument("--headline-only", action="store_true",
+                    help="skip the e2e, sweep and CPU-baseline legs (profiling)")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,140 @@
+/* b200w4 -- C ABI of the B200 (sm_100a) W4G128 / W4A8 matmul path.
+ *
+ * Plain pointers and sizes only.  Every function returns 0 on success or a
+ * negative B2W4_E_* code; b2w4_last_error() gives the text of the last failure
+ * on that context.  Nothing here throws, and nothing falls back to the CPU: if
+ * no sm_100 device is usable, b2w4_ctx_create fails.
+ *
+ * Each entry point names the reference interface (mollm, path:line) it stands
+ * in for.  Weights arrive as the reference's canonical BG128 blocks
+ * (kernels/quant_layouts.h:9-14): block (n8,g) at index n8*(K/128)+g, 8 fp32
+ * row scales then q[4][8][16] nibble bytes; 544 bytes per 8 rows x 128 k.
+ *
+ * Tensors follow the reference's matmul convention (engine/cuda_backend.cu:
+ * 1032-1045): activations x are fp32 [M rows][K], row stride lda elements;
+ * outputs y are fp32 [M rows][N], row stride ldc elements.
+ */
+#ifndef B200W4_H
+#define B200W4_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+    B2W4_OK = 0,
+    B2W4_E_INVALID = -1,   /* bad argument / unsupported shape              */
+    B2W4_E_CUDA = -2,      /* a CUDA call failed                            */
+    B2W4_E_NO_DEVICE = -3, /* no usable sm_100 device                       */
+    B2W4_E_NOMEM = -4,
+    B2W4_E_TIMEOUT = -5    /* a bounded device-side wait gave up            */
+};
+
+/* Activation-quantisation rule (reference kernels/matmul_w4.cpp:1058-1075 for
+ * M==1, :1125-1154 for M>1). */
+enum {
+    B2W4_ACT_G128 = 128, /* one int8 scale per 128 values, applied row by row */
+    B2W4_ACT_G32 = 32    /* one int8 scale per 32 values                      */
+};
+
+/* Post-matmul activation, same numbering as the reference's Activation enum
+ * (kernels/activations.h:28-35). */
+enum { B2W4_NONE = 0, B2W4_SILU = 1, B2W4_GELU = 2, B2W4_RELU = 3, B2W4_RELU_SQUARED = 4 };
+
+typedef struct b2w4_ctx b2w4_ctx;
+typedef struct b2w4_weight b2w4_weight;
+
+/* ---- context -------------------------------------------------------------
+ * Replaces CudaBackend::Impl construction (engine/cuda_backend.cu:394-409):
+ * binds a device, owns scratch for quantised activations.  `stream` is a
+ * cudaStream_t (NULL = the legacy default stream the reference uses). */
+int b2w4_ctx_create(int device, b2w4_ctx** out);
+void b2w4_ctx_destroy(b2w4_ctx* ctx);
+int b2w4_ctx_set_stream(b2w4_ctx* ctx, void* stream);
+int b2w4_sync(b2w4_ctx* ctx); /* end_graph(), engine/cuda_backend.cu:631-639 */
+const char* b2w4_last_error(const b2w4_ctx* ctx);
+const char* b2w4_version(void);
+
+/* ---- weights -------------------------------------------------------------
+ * Replaces CudaBackend::wrap_weight_int4 (engine/cuda_backend.cu:462-487) and
+ * its upload helper (:176-210): validates K%128==0, copies the blocks (the
+ * caller may free or overwrite them afterwards) and repacks them on the device
+ * into the streaming layout the kernels read (nibble plane + scale plane).
+ * `host_blocks` holds ((N+7)/8)*(K/128)*544 bytes. */
+int b2w4_weight_upload(b2w4_ctx* ctx, const void* host_blocks, int n, int k,
+                       b2w4_weight** out);
+/* Same, from blocks already in device memory (weights generated on the GPU). */
+int b2w4_weight_from_device(b2w4_ctx* ctx, const void* device_blocks, int n, int k,
+                            b2w4_weight** out);
+void b2w4_weight_free(b2w4_ctx* ctx, b2w4_weight* w);
+int b2w4_weight_shape(const b2w4_weight* w, int* n, int* k);
+/* 1 if every group scale is exactly representable in fp16 (the device scale
+ * plane is then fp16), 0 if the plane had to stay fp32. */
+int b2w4_weight_scales_fp16(const b2w4_weight* w);
+/* Bytes of device memory one full pass over the weight reads. */
+size_t b2w4_weight_stream_bytes(const b2w4_weight* w);
+
+/* ---- matmul --------------------------------------------------------------
+ * Replaces CudaBackend::Impl::run_matmul_device (engine/cuda_backend.cu:
+ * 212-337): y[M,N] = act(x[M,K] * W^T), device pointers, asynchronous on the
+ * context's stream.  Arithmetic is the reference's W4A8 kernels': int8
+ * activations per `act_rule` group, int32 dot per group, then
+ * y = fma(float(dot), fp32(wscale*ascale), y) in ascending group order
+ * (kernels/matmul_w4.cpp:211-295, :785-901).  `activation` is applied to
+ * columns [act_n_begin, act_n_begin+act_n_len); act_n_len < 0 = all columns
+ * (kernels/matmul_internal.h:73-119). */
+int b2w4_matmul(b2w4_ctx* ctx, const b2w4_weight* w, const float* x_dev, int lda,
+                float* y_dev, int ldc, int m, int act_rule, int activation,
+                int act_n_begin, int act_n_len);
+
+/* Replaces CudaBackend::Impl::run_matmul (host tensors staged through the
+ * device, engine/cuda_backend.cu:339-359) and CudaBackend::lm_head_gemv
+ * (:1404-1424): host x, host y, synchronous. */
+int b2w4_matmul_host(b2w4_ctx* ctx, const b2w4_weight* w, const float* x_host,
+                     int lda, float* y_host, int ldc, int m, int act_rule,
+                     int activation, int act_n_begin, int act_n_len);
+
+/* Parity hook with no reference counterpart in the CUDA backend: writes the
+ * int32 group accumulators of the same kernels, [M][N][K/128] for
+ * B2W4_ACT_G128 or [M][N][K/32] for B2W4_ACT_G32, to device memory. */
+int b2w4_debug_group_sums(b2w4_ctx* ctx, const b2w4_weight* w, const float* x_dev,
+                          int lda, int m, int act_rule, int32_t* sums_dev);
+
+/* Parity hook: the device activation quantiser alone (reference
+ * kernels/matmul_quant.cpp:578-641 and :280-329).  q_dev receives int8 [M][K]
+ * in natural k order, scales_dev fp32 [M][K/act_rule]. */
+int b2w4_quantize_activations(b2w4_ctx* ctx, const float* x_dev, int lda, int m,
+                              int k, int act_rule, int8_t* q_dev, float* scales_dev);
+
+/* ---- routed MoE ----------------------------------------------------------
+ * Replaces kernel_qwen3_moe (kernels/moe.cpp:576-1129) as dispatched for
+ * OpType::MOE (graph/cpu_backend.cpp:169-206) in the Qwen3-MoE configuration:
+ * softmax top-k routing over raw logits with ties to the lower expert id
+ * (kernels/moe_routing.cpp:129-166), fp16 router weight [E,H], expert
+ * aggregates gate_up [E*2I, H] and down [E*H, I] as BG128 weights, no shared
+ * expert.  hidden fp32 [tokens][H] (row stride ldx), out fp32 [tokens][H]
+ * (row stride ldo); all device pointers.  Optional outputs (NULL to skip):
+ * logits [tokens][E], indices int32 / weights fp32 [tokens][top_k]. */
+int b2w4_moe_forward(b2w4_ctx* ctx, const float* hidden_dev, int ldx, int tokens,
+                     int hidden_size, const void* router_fp16_dev, int num_experts,
+                     int top_k, int intermediate, const b2w4_weight* gate_up,
+                     const b2w4_weight* down, float* out_dev, int ldo,
+                     float* logits_dev, int32_t* indices_dev, float* weights_dev);
+
+/* Routing alone: select_moe_routes, score_func 0 (kernels/moe_routing.cpp:
+ * 25-169).  logits fp32 [tokens][E] on the device. */
+int b2w4_moe_select_routes(b2w4_ctx* ctx, const float* logits_dev, int tokens,
+                           int num_experts, int top_k, int32_t* indices_dev,
+                           float* weights_dev);
+
+/* Launch counter: how many of this library's kernels have been launched on the
+ * context since creation (for benchmark bookkeeping). */
+uint64_t b2w4_kernel_launches(const b2w4_ctx* ctx);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200W4_H */

@@ -1,0 +1,12 @@
+"""B200-native W4G128 / W4A8 matmul path behind mollm's accelerator-backend boundary.
+
+  csrc/      hand-written sm_100a kernels and the extern "C" layer (libb200w4.so)
+  capi.py    ctypes binding of that C ABI (tests, bench)
+  synth.py   seeded synthetic weights / activations of the benchmark shapes
+  build.py   in-tree nvcc build
+
+The directory name carries a hyphen, so load it with importlib (see __graft_entry__.py)
+under the module name `palm_infra_b200`.
+"""
+from . import capi, synth  # noqa: F401
+from .build import build as build_library  # noqa: F401

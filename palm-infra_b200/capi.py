@@ -1,0 +1,179 @@
+"""ctypes binding of libb200w4.so, the C-ABI library declared in include/b200w4.h.
+
+This is the only route from Python to the kernels.  There is no CPU fallback: importing
+works anywhere (so the library's exports can be checked without a GPU), but creating a
+Context raises unless an sm_100 device and the built library are present.
+"""
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libb200w4.so")
+
+ACT_G128, ACT_G32 = 128, 32
+NONE, SILU, GELU, RELU, RELU_SQUARED = 0, 1, 2, 3, 4
+
+# every symbol include/b200w4.h declares
+SYMBOLS = [
+    "b2w4_ctx_create", "b2w4_ctx_destroy", "b2w4_ctx_set_stream", "b2w4_sync",
+    "b2w4_last_error", "b2w4_version", "b2w4_weight_upload", "b2w4_weight_from_device",
+    "b2w4_weight_free", "b2w4_weight_shape", "b2w4_weight_scales_fp16",
+    "b2w4_weight_stream_bytes", "b2w4_matmul", "b2w4_matmul_host",
+    "b2w4_debug_group_sums", "b2w4_quantize_activations", "b2w4_moe_forward",
+    "b2w4_moe_select_routes", "b2w4_kernel_launches",
+]
+
+_lib = None
+
+
+class B200W4Error(RuntimeError):
+    pass
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise B200W4Error(
+                f"{LIB_PATH} is missing: build it with `python palm-infra_b200/build.py`; "
+                "there is no fallback path")
+        L = C.CDLL(LIB_PATH)
+        vp, i, f_p = C.c_void_p, C.c_int, C.c_void_p
+        L.b2w4_ctx_create.argtypes = [i, C.POINTER(vp)]
+        L.b2w4_ctx_destroy.argtypes = [vp]
+        L.b2w4_ctx_destroy.restype = None
+        L.b2w4_ctx_set_stream.argtypes = [vp, vp]
+        L.b2w4_sync.argtypes = [vp]
+        L.b2w4_last_error.argtypes = [vp]
+        L.b2w4_last_error.restype = C.c_char_p
+        L.b2w4_version.restype = C.c_char_p
+        L.b2w4_weight_upload.argtypes = [vp, vp, i, i, C.POINTER(vp)]
+        L.b2w4_weight_from_device.argtypes = [vp, vp, i, i, C.POINTER(vp)]
+        L.b2w4_weight_free.argtypes = [vp, vp]
+        L.b2w4_weight_free.restype = None
+        L.b2w4_weight_shape.argtypes = [vp, C.POINTER(i), C.POINTER(i)]
+        L.b2w4_weight_scales_fp16.argtypes = [vp]
+        L.b2w4_weight_stream_bytes.argtypes = [vp]
+        L.b2w4_weight_stream_bytes.restype = C.c_size_t
+        L.b2w4_matmul.argtypes = [vp, vp, f_p, i, f_p, i, i, i, i, i, i]
+        L.b2w4_matmul_host.argtypes = [vp, vp, f_p, i, f_p, i, i, i, i, i, i]
+        L.b2w4_debug_group_sums.argtypes = [vp, vp, f_p, i, i, i, vp]
+        L.b2w4_quantize_activations.argtypes = [vp, f_p, i, i, i, i, vp, vp]
+        L.b2w4_moe_forward.argtypes = [vp, f_p, i, i, i, vp, i, i, i, vp, vp, f_p, i, f_p,
+                                       vp, f_p]
+        L.b2w4_moe_select_routes.argtypes = [vp, f_p, i, i, i, vp, f_p]
+        L.b2w4_kernel_launches.argtypes = [vp]
+        L.b2w4_kernel_launches.restype = C.c_uint64
+        _lib = L
+    return _lib
+
+
+def _dptr(t):
+    """Device pointer of a torch CUDA tensor (or None)."""
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+class Weight:
+    def __init__(self, ctx, handle, n, k):
+        self.ctx, self.handle, self.n, self.k = ctx, handle, n, k
+
+    @property
+    def scales_fp16(self):
+        return bool(lib().b2w4_weight_scales_fp16(self.handle))
+
+    @property
+    def stream_bytes(self):
+        return int(lib().b2w4_weight_stream_bytes(self.handle))
+
+    def free(self):
+        if self.handle:
+            lib().b2w4_weight_free(self.ctx.handle, self.handle)
+            self.handle = None
+
+
+class Context:
+    """One per GPU.  Mirrors what the reference's CudaBackend keeps per device."""
+
+    def __init__(self, device=0):
+        h = C.c_void_p()
+        rc = lib().b2w4_ctx_create(device, C.byref(h))
+        if rc != 0:
+            raise B200W4Error(f"b2w4_ctx_create(device={device}) failed with {rc}: "
+                              "an sm_100 (B200) device is required; there is no CPU path")
+        self.handle = h
+        self.device = device
+
+    def _check(self, rc):
+        if rc != 0:
+            raise B200W4Error(f"b200w4 error {rc}: "
+                              f"{lib().b2w4_last_error(self.handle).decode()}")
+
+    def close(self):
+        if self.handle:
+            lib().b2w4_ctx_destroy(self.handle)
+            self.handle = None
+
+    def set_stream(self, cuda_stream_ptr):
+        self._check(lib().b2w4_ctx_set_stream(self.handle, C.c_void_p(cuda_stream_ptr)))
+
+    def sync(self):
+        self._check(lib().b2w4_sync(self.handle))
+
+    @property
+    def launches(self):
+        return int(lib().b2w4_kernel_launches(self.handle))
+
+    # -- weights
+    def upload_weight(self, host_blocks, n, k):
+        """host_blocks: numpy uint8 array of canonical BG128 blocks."""
+        h = C.c_void_p()
+        self._check(lib().b2w4_weight_upload(self.handle,
+                                             host_blocks.ctypes.data_as(C.c_void_p), n, k,
+                                             C.byref(h)))
+        return Weight(self, h, n, k)
+
+    def weight_from_device(self, dev_blocks, n, k):
+        h = C.c_void_p()
+        self._check(lib().b2w4_weight_from_device(self.handle, _dptr(dev_blocks), n, k,
+                                                  C.byref(h)))
+        return Weight(self, h, n, k)
+
+    # -- matmul on device tensors (torch, fp32, row-major [M,K] / [M,N])
+    def matmul(self, w, x, y, m=None, rule=ACT_G128, act=NONE, act_begin=0, act_len=-1,
+               lda=None, ldc=None):
+        m = x.shape[0] if m is None else m
+        lda = x.stride(0) if lda is None else lda
+        ldc = y.stride(0) if ldc is None else ldc
+        self._check(lib().b2w4_matmul(self.handle, w.handle, _dptr(x), lda, _dptr(y), ldc,
+                                      m, rule, act, act_begin, act_len))
+
+    def matmul_host(self, w, x_np, y_np, rule=ACT_G128, act=NONE, act_begin=0, act_len=-1):
+        m = x_np.shape[0]
+        self._check(lib().b2w4_matmul_host(
+            self.handle, w.handle, x_np.ctypes.data_as(C.c_void_p), x_np.strides[0] // 4,
+            y_np.ctypes.data_as(C.c_void_p), y_np.strides[0] // 4, m, rule, act, act_begin,
+            act_len))
+
+    def group_sums(self, w, x, sums, rule=ACT_G128):
+        self._check(lib().b2w4_debug_group_sums(self.handle, w.handle, _dptr(x),
+                                                x.stride(0), x.shape[0], rule, _dptr(sums)))
+
+    def quantize(self, x, q, scales, rule=ACT_G128):
+        self._check(lib().b2w4_quantize_activations(self.handle, _dptr(x), x.stride(0),
+                                                    x.shape[0], x.shape[1], rule, _dptr(q),
+                                                    _dptr(scales)))
+
+    # -- MoE
+    def moe_forward(self, hidden, router_fp16, top_k, intermediate, gate_up, down, out,
+                    logits=None, indices=None, weights=None):
+        t, h = hidden.shape
+        e = router_fp16.shape[0]
+        self._check(lib().b2w4_moe_forward(
+            self.handle, _dptr(hidden), hidden.stride(0), t, h, _dptr(router_fp16), e, top_k,
+            intermediate, gate_up.handle, down.handle, _dptr(out), out.stride(0),
+            _dptr(logits), _dptr(indices), _dptr(weights)))
+
+    def select_routes(self, logits, top_k, indices, weights):
+        t, e = logits.shape
+        self._check(lib().b2w4_moe_select_routes(self.handle, _dptr(logits), t, e, top_k,
+                                                 _dptr(indices), _dptr(weights)))

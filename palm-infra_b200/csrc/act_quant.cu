@@ -1,0 +1,77 @@
+// Stand-alone activation quantiser: fp32 rows -> int8 codes + one fp32 scale per group.
+// Follows the reference quantisers' rounding points exactly
+// (kernels/matmul_quant.cpp:578-641 per 128 values, :280-329 per 32 values): amax over the
+// group, scale = amax/127 (1 when amax == 0), codes = clamp(rint(x * (127/amax)), +-127).
+#include "b200w4_internal.cuh"
+
+namespace {
+
+// one warp per (row, 128-group); lane holds k = 4*lane .. 4*lane+3 of the group
+template <int RULE, int LAYOUT>
+__global__ void quantize_rows_kernel(const float* __restrict__ x, int lda, int m, int k,
+                                     int8_t* __restrict__ q, float* __restrict__ scales) {
+    const int groups = k >> 7;
+    long long wid = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (wid >= (long long)m * groups)
+        return;
+    const int row = (int)(wid / groups), g = (int)(wid % groups);
+    const float* src = x + (size_t)row * lda + (size_t)g * 128 + lane * 4;
+    float v0 = src[0], v1 = src[1], v2 = src[2], v3 = src[3];
+    float amax = fmaxf(fmaxf(fabsf(v0), fabsf(v1)), fmaxf(fabsf(v2), fabsf(v3)));
+    // max is exact and order-free, so a butterfly gives the sequential loop's value
+    const int span = RULE == 128 ? 32 : 8;
+#pragma unroll
+    for (int off = span / 2; off > 0; off >>= 1)
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+    float scale, inv;
+    b2w4_quant_params(amax, scale, inv);
+    const int c0 = b2w4_quant_code(v0, inv), c1 = b2w4_quant_code(v1, inv);
+    const int c2 = b2w4_quant_code(v2, inv), c3 = b2w4_quant_code(v3, inv);
+    if (RULE == 128) {
+        if (lane == 0)
+            scales[(size_t)row * groups + g] = scale;
+    } else if ((lane & 7) == 0) {
+        scales[(size_t)row * (groups * 4) + g * 4 + (lane >> 3)] = scale;
+    }
+    int8_t* dst = q + (size_t)row * k + (size_t)g * 128;
+    if (LAYOUT == QLAYOUT_NATURAL) {
+        char4 packed = make_char4((signed char)c0, (signed char)c1, (signed char)c2,
+                                  (signed char)c3);
+        *reinterpret_cast<char4*>(dst + lane * 4) = packed;
+    } else {
+        // 32-block `sub` = lane/8 stored as 16 even-k codes then 16 odd-k codes
+        int8_t* blk = dst + (lane >> 3) * 32;
+        const int j = (lane & 7) * 2;
+        *reinterpret_cast<char2*>(blk + j) = make_char2((signed char)c0, (signed char)c2);
+        *reinterpret_cast<char2*>(blk + 16 + j) =
+            make_char2((signed char)c1, (signed char)c3);
+    }
+}
+
+}  // namespace
+
+int b2w4_launch_quantize(b2w4_ctx* ctx, const float* x, int lda, int m, int k,
+                         int act_rule, int8_t* q, float* scales, int layout) {
+    if (k <= 0 || k % 128 != 0 || m <= 0 || lda < k)
+        return b2w4_fail(ctx, B2W4_E_INVALID, "quantize: bad shape m=%d k=%d lda=%d", m,
+                         k, lda);
+    if (act_rule != B2W4_ACT_G128 && act_rule != B2W4_ACT_G32)
+        return b2w4_fail(ctx, B2W4_E_INVALID, "quantize: act_rule must be 128 or 32");
+    long long warps = (long long)m * (k / 128);
+    int grid = (int)((warps * 32 + 255) / 256);
+#define LAUNCH(R, L)                                                              \
+    quantize_rows_kernel<R, L><<<grid, 256, 0, ctx->stream>>>(x, lda, m, k, q, scales)
+    if (act_rule == 128 && layout == QLAYOUT_NATURAL)
+        LAUNCH(128, QLAYOUT_NATURAL);
+    else if (act_rule == 128)
+        LAUNCH(128, QLAYOUT_EVEN_ODD);
+    else if (layout == QLAYOUT_NATURAL)
+        LAUNCH(32, QLAYOUT_NATURAL);
+    else
+        LAUNCH(32, QLAYOUT_EVEN_ODD);
+#undef LAUNCH
+    ctx->launches++;
+    B2W4_CUDA(ctx, cudaGetLastError());
+    return B2W4_OK;
+}

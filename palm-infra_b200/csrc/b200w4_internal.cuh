@@ -1,0 +1,145 @@
+// Internal declarations shared by the b200w4 translation units (sm_100a only).
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+
+#include "b200w4.h"
+
+// ---------------------------------------------------------------------------
+// Device weight: the canonical BG128 stream split into two planes.
+//   nib: [tiles][groups][32] uint4 -- for 8-row tile t and 128-k group g, 32
+//        16-byte chunks in the block's own order: chunk (sub*8 + row) holds
+//        k = g*128 + sub*32 .. +31 of row t*8+row, low nibble = even k.
+//   scl: [tiles][groups][8] fp16 (or fp32 when a scale is not fp16-exact).
+// One 8x128 block is 512 B + 16 B: 4.125 bits per weight.
+// ---------------------------------------------------------------------------
+struct b2w4_weight {
+    int n = 0, k = 0, tiles = 0, groups = 0;
+    int scales_fp16 = 1;
+    uint4* nib = nullptr;
+    void* scl = nullptr;
+    size_t nib_bytes = 0, scl_bytes = 0;
+};
+
+struct b2w4_ctx {
+    int device = 0;
+    int sm_count = 0;
+    cudaStream_t stream = nullptr;
+    uint64_t launches = 0;
+    bool pdl = true;  // programmatic dependent launch between consecutive kernels
+    int gemv_ctas_per_sm = 1;  // a GEMV CTA takes half an SM; the other half hosts the next kernel
+    char err[512] = {0};
+    // grow-only scratch (quantised activations, MoE work lists, staging)
+    void* scratch[8] = {nullptr};
+    size_t scratch_cap[8] = {0};
+    int* flag_dev = nullptr;  // one int for device-side status words
+};
+
+enum ScratchSlot {
+    SCR_QA = 0,      // quantised activations
+    SCR_AS = 1,      // activation scales
+    SCR_STAGE_X = 2, // host-call staging: x
+    SCR_STAGE_Y = 3, // host-call staging: y
+    SCR_MOE_A = 4,
+    SCR_MOE_B = 5,
+    SCR_MOE_C = 6,
+    SCR_MOE_D = 7,
+};
+
+int b2w4_fail(b2w4_ctx* ctx, int code, const char* fmt, ...);
+int b2w4_reserve(b2w4_ctx* ctx, int slot, size_t bytes, void** out);
+
+#define B2W4_CUDA(ctx, call)                                                      \
+    do {                                                                          \
+        cudaError_t e__ = (call);                                                 \
+        if (e__ != cudaSuccess)                                                   \
+            return b2w4_fail((ctx), B2W4_E_CUDA, "%s: %s", #call,                 \
+                             cudaGetErrorString(e__));                            \
+    } while (0)
+
+// kernels' host launchers (defined in the .cu files)
+int b2w4_launch_repack(b2w4_ctx* ctx, const void* dev_blocks, b2w4_weight* w);
+int b2w4_launch_quantize(b2w4_ctx* ctx, const float* x, int lda, int m, int k,
+                         int act_rule, int8_t* q, float* scales, int layout);
+int b2w4_launch_gemv(b2w4_ctx* ctx, const b2w4_weight* w, const float* x, int lda,
+                     float* y, int ldc, int m, int act_rule, int activation,
+                     int act_n_begin, int act_n_len, int32_t* sums);
+
+// activation-quantiser output layouts
+enum {
+    QLAYOUT_NATURAL = 0,  // int8 [M][K], k ascending
+    QLAYOUT_EVEN_ODD = 1, // int8 [M][K], each 32-block stored as even16|odd16
+};
+
+// ---------------------------------------------------------------------------
+// device helpers
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ float b2w4_activation(float v, int act) {
+    // scalar forms of the reference's fused activations
+    // (kernels/activations.h:76-99): SILU = x * 1/(1+exp(-x)), GELU tanh form.
+    switch (act) {
+    case B2W4_SILU: {
+        // exp in fp64 then one rounding: agrees with a correctly rounded expf
+        float e = (float)exp(-(double)v);
+        float s = __fdiv_rn(1.f, __fadd_rn(1.f, e));
+        return __fmul_rn(v, s);
+    }
+    case B2W4_GELU: {
+        const float c = 0.7978845608f;
+        float v3 = __fmul_rn(__fmul_rn(v, v), v);
+        float inner = __fmul_rn(c, __fadd_rn(v, __fmul_rn(0.044715f, v3)));
+        float th = (float)tanh((double)inner);
+        return __fmul_rn(__fmul_rn(0.5f, v), __fadd_rn(1.f, th));
+    }
+    case B2W4_RELU:
+        return v > 0.f ? v : 0.f;
+    case B2W4_RELU_SQUARED: {
+        float r = v > 0.f ? v : 0.f;
+        return __fmul_rn(r, r);
+    }
+    default:
+        return v;
+    }
+}
+
+__device__ __forceinline__ bool b2w4_act_applies(int n, int act, int begin, int len,
+                                                 int n_total) {
+    if (act == B2W4_NONE || len == 0)
+        return false;
+    if (len < 0 || (begin == 0 && len >= n_total))
+        return true;
+    return n >= begin && n < begin + len;
+}
+
+// One activation group: amax -> scale / inverse -> round-to-nearest-even codes.
+// Same rounding points as the reference quantisers
+// (kernels/matmul_quant.cpp:602-603, :628-633).
+__device__ __forceinline__ void b2w4_quant_params(float amax, float& scale, float& inv) {
+    scale = amax > 0.f ? __fdiv_rn(amax, 127.f) : 1.f;
+    inv = amax > 0.f ? __fdiv_rn(127.f, amax) : 0.f;
+}
+
+__device__ __forceinline__ int b2w4_quant_code(float v, float inv) {
+    int q = __float2int_rn(__fmul_rn(v, inv));
+    return max(-127, min(127, q));
+}
+
+__device__ __forceinline__ uint4 b2w4_ldg_stream(const uint4* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+__device__ __forceinline__ void b2w4_pdl_wait() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+__device__ __forceinline__ void b2w4_pdl_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}

@@ -1,0 +1,288 @@
+// extern "C" entry points of libb200w4 (declared in include/b200w4.h): argument checks,
+// context and weight lifetime, and dispatch to the kernels' launchers.  No arithmetic here.
+#include "b200w4_internal.cuh"
+
+#include <cstdlib>
+#include <cstring>
+#include <new>
+
+int b2w4_fail(b2w4_ctx* ctx, int code, const char* fmt, ...) {
+    if (ctx) {
+        va_list ap;
+        va_start(ap, fmt);
+        vsnprintf(ctx->err, sizeof(ctx->err), fmt, ap);
+        va_end(ap);
+    }
+    return code;
+}
+
+int b2w4_reserve(b2w4_ctx* ctx, int slot, size_t bytes, void** out) {
+    if (ctx->scratch_cap[slot] < bytes) {
+        // the old block may still be read by queued kernels
+        B2W4_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        if (ctx->scratch[slot])
+            cudaFree(ctx->scratch[slot]);
+        ctx->scratch[slot] = nullptr;
+        ctx->scratch_cap[slot] = 0;
+        size_t cap = bytes + bytes / 4 + 4096;
+        cudaError_t e = cudaMalloc(&ctx->scratch[slot], cap);
+        if (e != cudaSuccess)
+            return b2w4_fail(ctx, B2W4_E_NOMEM, "cudaMalloc(%zu): %s", cap,
+                             cudaGetErrorString(e));
+        ctx->scratch_cap[slot] = cap;
+    }
+    *out = ctx->scratch[slot];
+    return B2W4_OK;
+}
+
+extern "C" {
+
+const char* b2w4_version(void) { return "b200w4 0.1 (sm_100a)"; }
+
+int b2w4_ctx_create(int device, b2w4_ctx** out) {
+    if (!out)
+        return B2W4_E_INVALID;
+    *out = nullptr;
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || device < 0 || device >= count)
+        return B2W4_E_NO_DEVICE;
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, device) != cudaSuccess)
+        return B2W4_E_NO_DEVICE;
+    if (prop.major != 10)  // the kernels are built for sm_100a only
+        return B2W4_E_NO_DEVICE;
+    if (cudaSetDevice(device) != cudaSuccess)
+        return B2W4_E_CUDA;
+    b2w4_ctx* ctx = new (std::nothrow) b2w4_ctx();
+    if (!ctx)
+        return B2W4_E_NOMEM;
+    ctx->device = device;
+    ctx->sm_count = prop.multiProcessorCount;
+    const char* pdl = getenv("B2W4_PDL");
+    ctx->pdl = !(pdl && pdl[0] == '0');
+    const char* cps = getenv("B2W4_GEMV_CTAS_PER_SM");
+    if (cps && (cps[0] == '1' || cps[0] == '2'))
+        ctx->gemv_ctas_per_sm = cps[0] - '0';
+    if (cudaMalloc(reinterpret_cast<void**>(&ctx->flag_dev), 64) != cudaSuccess ||
+        cudaMemset(ctx->flag_dev, 0, 64) != cudaSuccess) {
+        delete ctx;
+        return B2W4_E_NOMEM;
+    }
+    *out = ctx;
+    return B2W4_OK;
+}
+
+void b2w4_ctx_destroy(b2w4_ctx* ctx) {
+    if (!ctx)
+        return;
+    cudaSetDevice(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    for (int i = 0; i < 8; ++i)
+        if (ctx->scratch[i])
+            cudaFree(ctx->scratch[i]);
+    if (ctx->flag_dev)
+        cudaFree(ctx->flag_dev);
+    delete ctx;
+}
+
+int b2w4_ctx_set_stream(b2w4_ctx* ctx, void* stream) {
+    if (!ctx)
+        return B2W4_E_INVALID;
+    ctx->stream = static_cast<cudaStream_t>(stream);
+    return B2W4_OK;
+}
+
+int b2w4_sync(b2w4_ctx* ctx) {
+    if (!ctx)
+        return B2W4_E_INVALID;
+    B2W4_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    // status word written by a kernel whose bounded wait gave up
+    int status = 0;
+    B2W4_CUDA(ctx, cudaMemcpy(&status, ctx->flag_dev + 1, sizeof(int), cudaMemcpyDeviceToHost));
+    if (status != 0) {
+        cudaMemset(ctx->flag_dev + 1, 0, sizeof(int));
+        return b2w4_fail(ctx, status, "a device-side wait ran out of iterations");
+    }
+    return B2W4_OK;
+}
+
+const char* b2w4_last_error(const b2w4_ctx* ctx) { return ctx ? ctx->err : "no context"; }
+
+uint64_t b2w4_kernel_launches(const b2w4_ctx* ctx) { return ctx ? ctx->launches : 0; }
+
+// ---- weights -----------------------------------------------------------------------
+
+static int weight_create(b2w4_ctx* ctx, const void* dev_blocks, int n, int k,
+                         b2w4_weight** out) {
+    b2w4_weight* w = new (std::nothrow) b2w4_weight();
+    if (!w)
+        return b2w4_fail(ctx, B2W4_E_NOMEM, "out of host memory");
+    w->n = n;
+    w->k = k;
+    w->tiles = (n + 7) / 8;
+    w->groups = k / 128;
+    int rc = b2w4_launch_repack(ctx, dev_blocks, w);
+    if (rc != B2W4_OK) {
+        if (w->nib)
+            cudaFree(w->nib);
+        if (w->scl)
+            cudaFree(w->scl);
+        delete w;
+        return rc;
+    }
+    *out = w;
+    return B2W4_OK;
+}
+
+static int check_weight_shape(b2w4_ctx* ctx, const void* blocks, int n, int k,
+                              b2w4_weight** out) {
+    if (!ctx || !out)
+        return B2W4_E_INVALID;
+    *out = nullptr;
+    if (!blocks || n <= 0 || k <= 0 || k % 128 != 0)
+        return b2w4_fail(ctx, B2W4_E_INVALID,
+                         "weight: need blocks, n>0 and k a positive multiple of 128 "
+                         "(n=%d k=%d)", n, k);
+    return B2W4_OK;
+}
+
+int b2w4_weight_upload(b2w4_ctx* ctx, const void* host_blocks, int n, int k,
+                       b2w4_weight** out) {
+    int rc = check_weight_shape(ctx, host_blocks, n, k, out);
+    if (rc != B2W4_OK)
+        return rc;
+    const size_t bytes = (size_t)((n + 7) / 8) * (k / 128) * 544;
+    void* staging = nullptr;
+    cudaError_t e = cudaMalloc(&staging, bytes);
+    if (e != cudaSuccess)
+        return b2w4_fail(ctx, B2W4_E_NOMEM, "cudaMalloc(%zu): %s", bytes,
+                         cudaGetErrorString(e));
+    e = cudaMemcpyAsync(staging, host_blocks, bytes, cudaMemcpyHostToDevice, ctx->stream);
+    if (e != cudaSuccess) {
+        cudaFree(staging);
+        return b2w4_fail(ctx, B2W4_E_CUDA, "H2D weight copy: %s", cudaGetErrorString(e));
+    }
+    rc = weight_create(ctx, staging, n, k, out);
+    cudaStreamSynchronize(ctx->stream);
+    cudaFree(staging);
+    return rc;
+}
+
+int b2w4_weight_from_device(b2w4_ctx* ctx, const void* device_blocks, int n, int k,
+                            b2w4_weight** out) {
+    int rc = check_weight_shape(ctx, device_blocks, n, k, out);
+    if (rc != B2W4_OK)
+        return rc;
+    return weight_create(ctx, device_blocks, n, k, out);
+}
+
+void b2w4_weight_free(b2w4_ctx* ctx, b2w4_weight* w) {
+    if (!w)
+        return;
+    if (ctx)
+        cudaStreamSynchronize(ctx->stream);
+    if (w->nib)
+        cudaFree(w->nib);
+    if (w->scl)
+        cudaFree(w->scl);
+    delete w;
+}
+
+int b2w4_weight_shape(const b2w4_weight* w, int* n, int* k) {
+    if (!w)
+        return B2W4_E_INVALID;
+    if (n)
+        *n = w->n;
+    if (k)
+        *k = w->k;
+    return B2W4_OK;
+}
+
+int b2w4_weight_scales_fp16(const b2w4_weight* w) { return w ? w->scales_fp16 : 0; }
+
+size_t b2w4_weight_stream_bytes(const b2w4_weight* w) {
+    return w ? w->nib_bytes + w->scl_bytes : 0;
+}
+
+// ---- matmul ------------------------------------------------------------------------
+
+static int check_matmul(b2w4_ctx* ctx, const b2w4_weight* w, const void* x, int lda,
+                        const void* y, int ldc, int m, int act_rule, int activation) {
+    if (!ctx)
+        return B2W4_E_INVALID;
+    if (!w || !x || !y)
+        return b2w4_fail(ctx, B2W4_E_INVALID, "matmul: null weight or tensor");
+    if (m <= 0 || lda < w->k || ldc < w->n)
+        return b2w4_fail(ctx, B2W4_E_INVALID,
+                         "matmul: bad shape m=%d lda=%d (k=%d) ldc=%d (n=%d)", m, lda,
+                         w->k, ldc, w->n);
+    if (act_rule != B2W4_ACT_G128 && act_rule != B2W4_ACT_G32)
+        return b2w4_fail(ctx, B2W4_E_INVALID, "matmul: act_rule must be 128 or 32");
+    if (activation < B2W4_NONE || activation > B2W4_RELU_SQUARED)
+        return b2w4_fail(ctx, B2W4_E_INVALID, "matmul: unknown activation %d", activation);
+    return B2W4_OK;
+}
+
+int b2w4_matmul(b2w4_ctx* ctx, const b2w4_weight* w, const float* x_dev, int lda,
+                float* y_dev, int ldc, int m, int act_rule, int activation,
+                int act_n_begin, int act_n_len) {
+    int rc = check_matmul(ctx, w, x_dev, lda, y_dev, ldc, m, act_rule, activation);
+    if (rc != B2W4_OK)
+        return rc;
+    return b2w4_launch_gemv(ctx, w, x_dev, lda, y_dev, ldc, m, act_rule, activation,
+                            act_n_begin, act_n_len, nullptr);
+}
+
+int b2w4_matmul_host(b2w4_ctx* ctx, const b2w4_weight* w, const float* x_host, int lda,
+                     float* y_host, int ldc, int m, int act_rule, int activation,
+                     int act_n_begin, int act_n_len) {
+    int rc = check_matmul(ctx, w, x_host, lda, y_host, ldc, m, act_rule, activation);
+    if (rc != B2W4_OK)
+        return rc;
+    void *xd = nullptr, *yd = nullptr;
+    const size_t xb = sizeof(float) * (size_t)m * w->k, yb = sizeof(float) * (size_t)m * w->n;
+    if ((rc = b2w4_reserve(ctx, SCR_STAGE_X, xb, &xd)) != B2W4_OK ||
+        (rc = b2w4_reserve(ctx, SCR_STAGE_Y, yb, &yd)) != B2W4_OK)
+        return rc;
+    B2W4_CUDA(ctx, cudaMemcpy2DAsync(xd, sizeof(float) * w->k, x_host, sizeof(float) * lda,
+                                     sizeof(float) * w->k, m, cudaMemcpyHostToDevice,
+                                     ctx->stream));
+    rc = b2w4_launch_gemv(ctx, w, static_cast<const float*>(xd), w->k,
+                          static_cast<float*>(yd), w->n, m, act_rule, activation,
+                          act_n_begin, act_n_len, nullptr);
+    if (rc != B2W4_OK)
+        return rc;
+    B2W4_CUDA(ctx, cudaMemcpy2DAsync(y_host, sizeof(float) * ldc, yd, sizeof(float) * w->n,
+                                     sizeof(float) * w->n, m, cudaMemcpyDeviceToHost,
+                                     ctx->stream));
+    B2W4_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return B2W4_OK;
+}
+
+int b2w4_debug_group_sums(b2w4_ctx* ctx, const b2w4_weight* w, const float* x_dev, int lda,
+                          int m, int act_rule, int32_t* sums_dev) {
+    if (!ctx)
+        return B2W4_E_INVALID;
+    if (!w || !x_dev || !sums_dev || m <= 0 || lda < w->k)
+        return b2w4_fail(ctx, B2W4_E_INVALID, "group_sums: bad argument");
+    if (act_rule != B2W4_ACT_G128 && act_rule != B2W4_ACT_G32)
+        return b2w4_fail(ctx, B2W4_E_INVALID, "group_sums: act_rule must be 128 or 32");
+    void* yd = nullptr;
+    int rc = b2w4_reserve(ctx, SCR_STAGE_Y, sizeof(float) * (size_t)m * w->n, &yd);
+    if (rc != B2W4_OK)
+        return rc;
+    return b2w4_launch_gemv(ctx, w, x_dev, lda, static_cast<float*>(yd), w->n, m, act_rule,
+                            B2W4_NONE, 0, -1, sums_dev);
+}
+
+int b2w4_quantize_activations(b2w4_ctx* ctx, const float* x_dev, int lda, int m, int k,
+                              int act_rule, int8_t* q_dev, float* scales_dev) {
+    if (!ctx)
+        return B2W4_E_INVALID;
+    if (!x_dev || !q_dev || !scales_dev)
+        return b2w4_fail(ctx, B2W4_E_INVALID, "quantize: null pointer");
+    return b2w4_launch_quantize(ctx, x_dev, lda, m, k, act_rule, q_dev, scales_dev,
+                                QLAYOUT_NATURAL);
+}
+
+}  // extern "C"

@@ -1,0 +1,417 @@
+// W4G128 x int8 GEMV for 1..4 activation rows (decode): HBM-bound weight streaming.
+//
+// Arithmetic = the reference's NEON W4A8 GEMV (kernels/matmul_w4.cpp:211-295) applied row
+// by row, with the activation quantiser (kernels/matmul_quant.cpp:578-641) fused in:
+//   per 128-k group g:  D = sum q4*q8 (int32);  y = fma(float(D), fp32(ws*as[g]), y)
+// groups ascending.  The per-32 rule (kernels/matmul_w4.cpp:785-901) is the same loop
+// with one D and one activation scale per 32-k block.
+//
+// Data movement.  A CTA owns `tpc` consecutive 8-row tiles; their nibble stream
+// (tpc * K/128 * 512 bytes, contiguous in the nibble plane) and their scales are brought
+// into shared memory by bulk async copies (cp.async.bulk, one per tile, completion on an
+// mbarrier per tile) that one thread issues as the first thing the kernel does.  Nothing
+// is staged in registers, so the whole weight of a launch is in flight within the first
+// microsecond.  A CTA uses under half of an SM's shared memory, registers and threads: two
+// CTAs are resident per SM, and with programmatic dependent launch the CTAs of the NEXT
+// kernel in the stream become resident and start their copies while this kernel still
+// computes.  Weights never depend on the previous kernel's output; only the activation
+// read waits on the predecessor (griddepcontrol.wait).
+//
+// Math, phase 1.  An item is four consecutive groups of one tile; warp w takes items w,
+// w+W, ... of the CTA in a short, not unrolled loop (the kernel is latency-sensitive and
+// runs a few microseconds: its code has to stay resident in the instruction cache).  In an
+// item, lane (gl = lane/8, row = lane%8) owns group gl for one weight row, reads its four
+// 16-byte chunks (a quarter warp reads 128 contiguous bytes: no bank conflicts) and the
+// even/odd de-interleaved int8 activations (broadcast), and gets the group's int32 sum from
+// 32 dp4a with no cross-lane reduction.  Nibbles stay left-aligned in their bytes
+// ((w<<4)&0xF0F0F0F0 = even k, w&0xF0F0F0F0 = odd k, i.e. 16*q4 as int8); the int32 sum is
+// an exact multiple of 16 and is shifted back before conversion, like the NEON kernel's
+// sdot + fixed-point convert.  The exact integer sums go to shared memory.
+// Phase 2, after one barrier: one thread per (tile, weight row, activation row) runs the
+// order-sensitive fp32 chain over the groups in ascending order.
+#include "b200w4_internal.cuh"
+
+namespace {
+
+// one activation row: 16 warps of <= 64 registers; more rows keep more integer sums in
+// registers: 8 warps of <= 128 registers.  Either way two CTAs share an SM.
+__host__ __device__ constexpr int gemv_warps(int mt) { return mt == 1 ? 16 : 8; }
+constexpr int kMaxTpc = 16;
+constexpr unsigned kSpinLimit = 1u << 22;  // bounded waits: give up, flag, return
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // and never longer than 2 s
+
+struct GemvArgs {
+    const uint4* nib;
+    const void* scl;
+    const float* x;
+    float* y;
+    int32_t* sums;  // optional [m][n][groups or 4*groups]
+    int* status;    // device status word: set when a bounded wait gives up
+    int lda, ldc, m, n, k, groups, tiles;
+    int tpc;       // tiles per CTA
+    int d_stride;  // ints between the integer sums of consecutive tiles (padded)
+    int activation, act_n_begin, act_n_len;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+                 "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// global -> shared bulk copy (the TMA engine, untiled form); both addresses 16-byte
+// aligned, size a multiple of 16
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes,
+                                         uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+        ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar))
+        : "memory");
+}
+
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Waits for phase 0 of an mbarrier; false when the iteration or the time limit runs out.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar) {
+    if (mbar_try_wait(bar, 0))
+        return true;
+    const unsigned long long t0 = global_ns();
+    for (unsigned spins = 0; spins < kSpinLimit; ++spins) {
+        if (mbar_try_wait(bar, 0))
+            return true;
+        if ((spins & 63) == 63 && global_ns() - t0 > kWaitLimitNs)
+            return false;
+    }
+    return false;
+}
+
+// the fused activations carry fp64 exp / tanh code: keep one out-of-line copy
+__device__ __noinline__ float gemv_activation(float v, int act) {
+    return b2w4_activation(v, act);
+}
+
+template <int MT, bool SCL16, bool A32, bool SUMS>
+__global__ void __launch_bounds__(gemv_warps(MT) * 32, 2)
+gemv_w4a8_kernel(const GemvArgs a) {
+    constexpr int kWarps = gemv_warps(MT);
+    constexpr int kThreads = kWarps * 32;
+    extern __shared__ __align__(128) uint8_t smem[];
+    constexpr int SPG = A32 ? 4 : 1;  // integer sums per group
+    const int G = a.groups, K = a.k;
+    const int tile_bytes = G * 512;
+    const int scl_tile_bytes = G * 8 * (SCL16 ? 2 : 4);
+    // shared-memory carve-up (every region a multiple of 16 bytes)
+    uint8_t* s_w = smem;                                   // [tpc][G][512]
+    uint8_t* s_scl = s_w + (size_t)a.tpc * tile_bytes;     // [tpc][G][8] fp16|fp32
+    uint4* s_qa = reinterpret_cast<uint4*>(s_scl + (size_t)a.tpc * scl_tile_bytes);  // [MT][K]
+    float* s_as = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(s_qa) + (size_t)MT * K);
+    int32_t* s_d = reinterpret_cast<int32_t*>(s_as + MT * G * SPG);  // [tpc][G][SPG][MT][8]+pad
+    uint64_t* s_bar = reinterpret_cast<uint64_t*>(
+        (reinterpret_cast<uintptr_t>(s_d + (size_t)a.tpc * a.d_stride) + 7) & ~uintptr_t(7));
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int gl = lane >> 3, row = lane & 7;
+    const int tile0 = blockIdx.x * a.tpc;
+    const int ntile = min(a.tpc, a.tiles - tile0);
+
+    // Let the next kernel in the stream become resident and start its own weight copies.
+    b2w4_pdl_launch_dependents();
+
+    // ---- weight stream: issued before anything else, independent of the predecessor ----
+    if (warp == 0) {
+        // lane t arms and fills tile t's barrier; lane ntile does the scales
+        if (lane <= ntile)
+            mbar_init(&s_bar[lane], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        __syncwarp();
+        if (lane < ntile) {
+            mbar_expect_tx(&s_bar[lane], (uint32_t)tile_bytes);
+            bulk_g2s(s_w + (size_t)lane * tile_bytes,
+                     reinterpret_cast<const uint8_t*>(a.nib) +
+                         (size_t)(tile0 + lane) * tile_bytes,
+                     (uint32_t)tile_bytes, &s_bar[lane]);
+        } else if (lane == ntile) {
+            mbar_expect_tx(&s_bar[ntile], (uint32_t)(ntile * scl_tile_bytes));
+            bulk_g2s(s_scl,
+                     reinterpret_cast<const uint8_t*>(a.scl) + (size_t)tile0 * scl_tile_bytes,
+                     (uint32_t)(ntile * scl_tile_bytes), &s_bar[ntile]);
+        }
+    }
+
+    b2w4_pdl_wait();  // activations come from the previous kernel
+
+    // ---- fused activation quantiser: one half-warp per (activation row, group) ----------
+    // lane h of the half-warp holds k = 8h .. 8h+7 of the group (a quarter of a 32-block)
+    {
+        const int half = lane >> 4, h = lane & 15;
+        const int n_q = a.m * G;
+        // the trip count is the same for both halves of the warp (the shuffles below name
+        // all 32 lanes); a half without an item works on zeros and stores nothing
+#pragma unroll 1
+        for (int base = warp * 2; base < n_q; base += kWarps * 2) {
+            const int item = base + half;
+            const bool live = item < n_q;
+            const int mi = live ? item / G : 0, g = live ? item % G : 0;
+            const float* src = a.x + (size_t)mi * a.lda + (size_t)g * 128 + h * 8;
+            float v[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                v[i] = live ? src[i] : 0.f;
+            float amax = 0.f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                amax = fmaxf(amax, fabsf(v[i]));
+            // max is exact and order-free: the butterfly gives the sequential loop's value
+#pragma unroll
+            for (int off = (A32 ? 2 : 8); off > 0; off >>= 1)
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+            float scale, inv;
+            b2w4_quant_params(amax, scale, inv);
+            int c[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                c[i] = b2w4_quant_code(v[i], inv);
+            if (!live)
+                continue;
+            if (A32) {
+                if ((h & 3) == 0)
+                    s_as[mi * G * 4 + g * 4 + (h >> 2)] = scale;
+            } else if (h == 0) {
+                s_as[mi * G + g] = scale;
+            }
+            // 32-block h/4 is stored as 16 even-k codes then 16 odd-k codes
+            uint8_t* blk = reinterpret_cast<uint8_t*>(s_qa) + (size_t)mi * K + (size_t)g * 128 +
+                           (h >> 2) * 32;
+            const int j = (h & 3) * 4;
+            *reinterpret_cast<char4*>(blk + j) = make_char4(
+                (signed char)c[0], (signed char)c[2], (signed char)c[4], (signed char)c[6]);
+            *reinterpret_cast<char4*>(blk + 16 + j) = make_char4(
+                (signed char)c[1], (signed char)c[3], (signed char)c[5], (signed char)c[7]);
+        }
+    }
+    __syncthreads();  // quantised activations and barrier inits visible to all
+
+    // ---- phase 1: integer group sums ---------------------------------------------------
+    const int ipt = (G + 3) >> 2;
+    const int n_items = ntile * ipt;
+    bool timed_out = false;
+#pragma unroll 1
+    for (int it = warp; it < n_items; it += kWarps) {
+        const int tl = it / ipt;
+        const int g = (it - tl * ipt) * 4 + gl;
+        if (!mbar_wait_bounded(&s_bar[tl])) {
+            timed_out = true;
+            break;
+        }
+        if (g < G) {
+            const uint4* wt =
+                reinterpret_cast<const uint4*>(s_w + (size_t)tl * tile_bytes) + g * 32 + row;
+            uint32_t we[16], wo[16];
+#pragma unroll
+            for (int s = 0; s < 4; ++s) {
+                const uint4 w = wt[s * 8];
+                we[s * 4 + 0] = (w.x << 4) & 0xF0F0F0F0u;
+                wo[s * 4 + 0] = w.x & 0xF0F0F0F0u;
+                we[s * 4 + 1] = (w.y << 4) & 0xF0F0F0F0u;
+                wo[s * 4 + 1] = w.y & 0xF0F0F0F0u;
+                we[s * 4 + 2] = (w.z << 4) & 0xF0F0F0F0u;
+                wo[s * 4 + 2] = w.z & 0xF0F0F0F0u;
+                we[s * 4 + 3] = (w.w << 4) & 0xF0F0F0F0u;
+                wo[s * 4 + 3] = w.w & 0xF0F0F0F0u;
+            }
+            int32_t* dst = s_d + (size_t)tl * a.d_stride + (size_t)g * SPG * MT * 8 + row;
+#pragma unroll
+            for (int mi = 0; mi < MT; ++mi) {
+                if (mi < a.m) {
+                    const uint4* qa = s_qa + ((size_t)mi * K + (size_t)g * 128) / 16;
+                    int total = 0;
+#pragma unroll
+                    for (int s = 0; s < 4; ++s) {
+                        const uint4 ae = qa[s * 2], ao = qa[s * 2 + 1];
+                        // two independent chains per sub-block hide dp4a latency
+                        int p = __dp4a((int)we[s * 4 + 0], (int)ae.x, 0);
+                        int q = __dp4a((int)wo[s * 4 + 0], (int)ao.x, 0);
+                        p = __dp4a((int)we[s * 4 + 1], (int)ae.y, p);
+                        q = __dp4a((int)wo[s * 4 + 1], (int)ao.y, q);
+                        p = __dp4a((int)we[s * 4 + 2], (int)ae.z, p);
+                        q = __dp4a((int)wo[s * 4 + 2], (int)ao.z, q);
+                        p = __dp4a((int)we[s * 4 + 3], (int)ae.w, p);
+                        q = __dp4a((int)wo[s * 4 + 3], (int)ao.w, q);
+                        if (A32)
+                            dst[(s * MT + mi) * 8] = (p + q) >> 4;  // exact: multiple of 16
+                        else
+                            total += p + q;
+                    }
+                    if (!A32)
+                        dst[mi * 8] = total >> 4;
+                }
+            }
+        }
+    }
+    if (timed_out && lane == 0)
+        atomicExch(a.status, B2W4_E_TIMEOUT);
+    __syncthreads();
+    if (!mbar_wait_bounded(&s_bar[ntile])) {  // weight scales
+        if (lane == 0)
+            atomicExch(a.status, B2W4_E_TIMEOUT);
+        return;
+    }
+
+    // ---- phase 2: fp32 chain, one thread per (tile, activation row, weight row) ---------
+#pragma unroll 1
+    for (int t = threadIdx.x; t < ntile * MT * 8; t += kThreads) {
+        const int rr = t & 7, mi = (t >> 3) % MT, tl = t / (8 * MT);
+        if (mi >= a.m)
+            continue;
+        const int n = (tile0 + tl) * 8 + rr;
+        const int32_t* dsrc = s_d + (size_t)tl * a.d_stride + mi * 8 + rr;
+        const float* as = s_as + mi * G * SPG;
+        float acc = 0.f;
+#pragma unroll 4
+        for (int g = 0; g < G; ++g) {
+            const float ws =
+                SCL16 ? __half2float(reinterpret_cast<const __half*>(s_scl)[(tl * G + g) * 8 + rr])
+                      : reinterpret_cast<const float*>(s_scl)[(tl * G + g) * 8 + rr];
+#pragma unroll
+            for (int s = 0; s < SPG; ++s) {
+                const int dv = dsrc[(g * SPG + s) * MT * 8];
+                acc = __fmaf_rn((float)dv, __fmul_rn(ws, as[g * SPG + s]), acc);
+                if (SUMS && n < a.n)
+                    a.sums[((size_t)mi * a.n + n) * (G * SPG) + g * SPG + s] = dv;
+            }
+        }
+        if (n < a.n) {
+            if (b2w4_act_applies(n, a.activation, a.act_n_begin, a.act_n_len, a.n))
+                acc = gemv_activation(acc, a.activation);
+            a.y[(size_t)mi * a.ldc + n] = acc;
+        }
+    }
+}
+
+int gemv_d_stride(int mt, int groups, bool a32) {
+    // +8 ints: consecutive tiles start 8 banks apart, so phase 2's warps read without
+    // bank conflicts
+    return groups * (a32 ? 4 : 1) * mt * 8 + 8;
+}
+
+size_t gemv_smem_bytes(int mt, int k, int groups, int tpc, bool scl16, bool a32) {
+    const int spg = a32 ? 4 : 1;
+    return (size_t)tpc * groups * 512 + (size_t)tpc * groups * 8 * (scl16 ? 2 : 4) +
+           (size_t)mt * k + sizeof(float) * mt * groups * spg +
+           sizeof(int32_t) * (size_t)tpc * gemv_d_stride(mt, groups, a32) + 8 +
+           sizeof(uint64_t) * (tpc + 1);
+}
+
+template <int MT, bool SCL16, bool A32, bool SUMS>
+int launch_one(b2w4_ctx* ctx, const GemvArgs& a, size_t smem) {
+    auto kern = gemv_w4a8_kernel<MT, SCL16, A32, SUMS>;
+    static size_t configured = 48 * 1024;  // per instantiation; one device per process
+    if (smem > configured) {
+        B2W4_CUDA(ctx, cudaFuncSetAttribute(
+                           kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured = smem;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((a.tiles + a.tpc - 1) / a.tpc);
+    cfg.blockDim = dim3(gemv_warps(MT) * 32);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = ctx->pdl ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    B2W4_CUDA(ctx, cudaLaunchKernelEx(&cfg, kern, a));
+    ctx->launches++;
+    return B2W4_OK;
+}
+
+template <int MT>
+int launch_mt(b2w4_ctx* ctx, const GemvArgs& a, bool scl16, bool a32, size_t smem) {
+    const bool sums = a.sums != nullptr;
+    if (scl16) {
+        if (a32)
+            return sums ? launch_one<MT, true, true, true>(ctx, a, smem)
+                        : launch_one<MT, true, true, false>(ctx, a, smem);
+        return sums ? launch_one<MT, true, false, true>(ctx, a, smem)
+                    : launch_one<MT, true, false, false>(ctx, a, smem);
+    }
+    if (a32)
+        return sums ? launch_one<MT, false, true, true>(ctx, a, smem)
+                    : launch_one<MT, false, true, false>(ctx, a, smem);
+    return sums ? launch_one<MT, false, false, true>(ctx, a, smem)
+                : launch_one<MT, false, false, false>(ctx, a, smem);
+}
+
+}  // namespace
+
+// Rows are processed four at a time; each pass streams the weight once.
+int b2w4_launch_gemv(b2w4_ctx* ctx, const b2w4_weight* w, const float* x, int lda,
+                     float* y, int ldc, int m, int act_rule, int activation,
+                     int act_n_begin, int act_n_len, int32_t* sums) {
+    const bool a32 = act_rule == B2W4_ACT_G32;
+    const int spg = a32 ? 4 : 1;
+    const bool scl16 = w->scales_fp16 != 0;
+    for (int m0 = 0; m0 < m; m0 += 4) {
+        const int mc = min(4, m - m0);
+        const int mt = mc == 1 ? 1 : (mc == 2 ? 2 : 4);
+        GemvArgs a;
+        a.nib = w->nib;
+        a.scl = w->scl;
+        a.x = x + (size_t)m0 * lda;
+        a.y = y ? y + (size_t)m0 * ldc : nullptr;
+        a.sums = sums ? sums + (size_t)m0 * w->n * w->groups * spg : nullptr;
+        a.status = ctx->flag_dev + 1;
+        a.lda = lda;
+        a.ldc = ldc;
+        a.m = mc;
+        a.n = w->n;
+        a.k = w->k;
+        a.groups = w->groups;
+        a.tiles = w->tiles;
+        a.activation = activation;
+        a.act_n_begin = act_n_begin;
+        a.act_n_len = act_n_len;
+        // Tiles per CTA: a CTA's shared memory stays under ~100 KB so that two CTAs (this
+        // launch's and the next one's) share an SM; when one wave of CTAs (tiles / SMs,
+        // rounded up) fits that, use it, so that no SM runs the math of two CTAs of one
+        // launch.
+        const int per_tile = w->groups * (512 + (scl16 ? 16 : 32)) +
+                             4 * gemv_d_stride(mt, w->groups, a32);
+        const int budget = 100 * 1024 - mt * w->k - 4 * mt * w->groups * spg - 1024;
+        int tpc = max(1, min(budget / per_tile, kMaxTpc));
+        const int one_wave = (w->tiles + ctx->sm_count - 1) / ctx->sm_count;
+        tpc = min(tpc, max(1, one_wave));
+        a.tpc = tpc;
+        a.d_stride = gemv_d_stride(mt, w->groups, a32);
+        const size_t smem = gemv_smem_bytes(mt, w->k, w->groups, tpc, scl16, a32);
+        if (smem > 220 * 1024)
+            return b2w4_fail(ctx, B2W4_E_INVALID, "gemv: K=%d needs %zu B shared memory",
+                             w->k, smem);
+        int rc = mt == 1 ? launch_mt<1>(ctx, a, scl16, a32, smem)
+                 : mt == 2 ? launch_mt<2>(ctx, a, scl16, a32, smem)
+                           : launch_mt<4>(ctx, a, scl16, a32, smem);
+        if (rc != B2W4_OK)
+            return rc;
+    }
+    return B2W4_OK;
+}
