@@ -49,7 +49,51 @@ __global__ void quantize_rows_kernel(const float* __restrict__ x, int lda, int m
     }
 }
 
+// Same quantiser, output laid out for the tensor-core kernel: per 128-k group a plane of
+// [m_pad tokens][128 bytes]; inside a token's 128 bytes the 32-block `sub` is the 16-byte
+// chunk pair (2*sub: even k, 2*sub+1: odd k), and chunk c is stored at position
+// c ^ (token % 8): the 128-byte swizzle the MMA's shared-memory descriptor expects, so the
+// plane can be bulk-copied into shared memory as is.  Scales: fp32 [groups][m_pad].
+__global__ void quantize_rows_umma_kernel(const float* __restrict__ x, int lda, int m, int k,
+                                          int m_pad, int8_t* __restrict__ q,
+                                          float* __restrict__ scales) {
+    const int groups = k >> 7;
+    long long wid = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (wid >= (long long)m * groups)
+        return;
+    const int row = (int)(wid / groups), g = (int)(wid % groups);
+    const float* src = x + (size_t)row * lda + (size_t)g * 128 + lane * 4;
+    float v0 = src[0], v1 = src[1], v2 = src[2], v3 = src[3];
+    float amax = fmaxf(fmaxf(fabsf(v0), fabsf(v1)), fmaxf(fabsf(v2), fabsf(v3)));
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1)
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+    float scale, inv;
+    b2w4_quant_params(amax, scale, inv);
+    const int c0 = b2w4_quant_code(v0, inv), c1 = b2w4_quant_code(v1, inv);
+    const int c2 = b2w4_quant_code(v2, inv), c3 = b2w4_quant_code(v3, inv);
+    if (lane == 0)
+        scales[(size_t)g * m_pad + row] = scale;
+    int8_t* tokp = q + ((size_t)g * m_pad + row) * 128;
+    const int sub = lane >> 3, j = (lane & 7) * 2, sw = row & 7;
+    *reinterpret_cast<char2*>(tokp + (((2 * sub) ^ sw) << 4) + j) =
+        make_char2((signed char)c0, (signed char)c2);
+    *reinterpret_cast<char2*>(tokp + (((2 * sub + 1) ^ sw) << 4) + j) =
+        make_char2((signed char)c1, (signed char)c3);
+}
+
 }  // namespace
+
+int b2w4_launch_quantize_umma(b2w4_ctx* ctx, const float* x, int lda, int m, int k, int m_pad,
+                              int8_t* q, float* scales) {
+    long long warps = (long long)m * (k / 128);
+    int grid = (int)((warps * 32 + 255) / 256);
+    quantize_rows_umma_kernel<<<grid, 256, 0, ctx->stream>>>(x, lda, m, k, m_pad, q, scales);
+    ctx->launches++;
+    B2W4_CUDA(ctx, cudaGetLastError());
+    return B2W4_OK;
+}
 
 int b2w4_launch_quantize(b2w4_ctx* ctx, const float* x, int lda, int m, int k,
                          int act_rule, int8_t* q, float* scales, int layout) {

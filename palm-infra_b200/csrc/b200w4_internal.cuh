@@ -32,7 +32,7 @@ struct b2w4_ctx {
     cudaStream_t stream = nullptr;
     uint64_t launches = 0;
     bool pdl = true;  // programmatic dependent launch between consecutive kernels
-    int gemv_ctas_per_sm = 1;  // a GEMV CTA takes half an SM; the other half hosts the next kernel
+    int gemv_max_rows = 4;  // activation rows up to which the dp4a GEMV is used
     char err[512] = {0};
     // grow-only scratch (quantised activations, MoE work lists, staging)
     void* scratch[8] = {nullptr};
@@ -69,6 +69,12 @@ int b2w4_launch_quantize(b2w4_ctx* ctx, const float* x, int lda, int m, int k,
 int b2w4_launch_gemv(b2w4_ctx* ctx, const b2w4_weight* w, const float* x, int lda,
                      float* y, int ldc, int m, int act_rule, int activation,
                      int act_n_begin, int act_n_len, int32_t* sums);
+
+int b2w4_launch_quantize_umma(b2w4_ctx* ctx, const float* x, int lda, int m, int k, int m_pad,
+                              int8_t* q, float* scales);
+int b2w4_launch_gemm_tc(b2w4_ctx* ctx, const b2w4_weight* w, const float* x, int lda,
+                        float* y, int ldc, int m, int activation, int act_n_begin,
+                        int act_n_len);
 
 // activation-quantiser output layouts
 enum {

@@ -60,9 +60,9 @@ int b2w4_ctx_create(int device, b2w4_ctx** out) {
     ctx->sm_count = prop.multiProcessorCount;
     const char* pdl = getenv("B2W4_PDL");
     ctx->pdl = !(pdl && pdl[0] == '0');
-    const char* cps = getenv("B2W4_GEMV_CTAS_PER_SM");
-    if (cps && (cps[0] == '1' || cps[0] == '2'))
-        ctx->gemv_ctas_per_sm = cps[0] - '0';
+    const char* gmr = getenv("B2W4_GEMV_MAX_ROWS");  // tuning/debug: rows kept on the GEMV
+    if (gmr && atoi(gmr) > 0)
+        ctx->gemv_max_rows = atoi(gmr);
     if (cudaMalloc(reinterpret_cast<void**>(&ctx->flag_dev), 64) != cudaSuccess ||
         cudaMemset(ctx->flag_dev, 0, 64) != cudaSuccess) {
         delete ctx;
@@ -223,14 +223,27 @@ static int check_matmul(b2w4_ctx* ctx, const b2w4_weight* w, const void* x, int 
     return B2W4_OK;
 }
 
+// Up to four activation rows stream the weight once through the dp4a GEMV; more rows go
+// to the tensor-core kernel (per-128 rule, K <= 10240).  Both produce the same bits.
+static int matmul_dispatch(b2w4_ctx* ctx, const b2w4_weight* w, const float* x, int lda,
+                           float* y, int ldc, int m, int act_rule, int activation,
+                           int act_n_begin, int act_n_len) {
+    const bool tc = m > ctx->gemv_max_rows && act_rule == B2W4_ACT_G128 && w->groups <= 80;
+    if (tc)
+        return b2w4_launch_gemm_tc(ctx, w, x, lda, y, ldc, m, activation, act_n_begin,
+                                   act_n_len);
+    return b2w4_launch_gemv(ctx, w, x, lda, y, ldc, m, act_rule, activation, act_n_begin,
+                            act_n_len, nullptr);
+}
+
 int b2w4_matmul(b2w4_ctx* ctx, const b2w4_weight* w, const float* x_dev, int lda,
                 float* y_dev, int ldc, int m, int act_rule, int activation,
                 int act_n_begin, int act_n_len) {
     int rc = check_matmul(ctx, w, x_dev, lda, y_dev, ldc, m, act_rule, activation);
     if (rc != B2W4_OK)
         return rc;
-    return b2w4_launch_gemv(ctx, w, x_dev, lda, y_dev, ldc, m, act_rule, activation,
-                            act_n_begin, act_n_len, nullptr);
+    return matmul_dispatch(ctx, w, x_dev, lda, y_dev, ldc, m, act_rule, activation,
+                           act_n_begin, act_n_len);
 }
 
 int b2w4_matmul_host(b2w4_ctx* ctx, const b2w4_weight* w, const float* x_host, int lda,
@@ -247,9 +260,9 @@ int b2w4_matmul_host(b2w4_ctx* ctx, const b2w4_weight* w, const float* x_host, i
     B2W4_CUDA(ctx, cudaMemcpy2DAsync(xd, sizeof(float) * w->k, x_host, sizeof(float) * lda,
                                      sizeof(float) * w->k, m, cudaMemcpyHostToDevice,
                                      ctx->stream));
-    rc = b2w4_launch_gemv(ctx, w, static_cast<const float*>(xd), w->k,
-                          static_cast<float*>(yd), w->n, m, act_rule, activation,
-                          act_n_begin, act_n_len, nullptr);
+    rc = matmul_dispatch(ctx, w, static_cast<const float*>(xd), w->k,
+                         static_cast<float*>(yd), w->n, m, act_rule, activation, act_n_begin,
+                         act_n_len);
     if (rc != B2W4_OK)
         return rc;
     B2W4_CUDA(ctx, cudaMemcpy2DAsync(y_host, sizeof(float) * ldc, yd, sizeof(float) * w->n,

@@ -179,3 +179,50 @@ def test_config2_decode_sweep(ctx, m):
     y, _ = run_gpu(ctx, blocks, n, k, x, sums=False)
     y_ref = ol.matmul_w4(blocks, n, k, x)
     assert y.tobytes() == y_ref.tobytes()
+
+
+@pytest.mark.parametrize("m,n,k", [(129, 72, 256), (300, 200, 512), (256, 1000, 1280),
+                                   (37, 2560, 9728)])
+def test_tensor_core_path_shapes_bit_exact(ctx, m, n, k):
+    """More than four activation rows go to the tcgen05 kernel: token blocks of 128, ragged
+    last block, several 256-token CTAs, ragged row tiles, large K."""
+    blocks = pkg.synth.bg128_weight(20261125, n + k + m, n, k)
+    x = pkg.synth.activations(7, m + 1, m, k)
+    x[m // 2, 128:256] = 0.0
+    y, _ = run_gpu(ctx, blocks, n, k, x, sums=False, pad=4)
+    y_ref = ol.matmul_w4(blocks, n, k, x)
+    assert y.tobytes() == y_ref.tobytes()
+
+
+def test_config2_prefill_m256(ctx):
+    """M=256, K=2560, N=9728 (benchmark configuration 2, prefill): bit-exact against the
+    row-by-row W4A8 oracle, and within 1e-2 relative L2 of the exact dequantised product
+    (the W4A8-vs-W4A32 gap itself is ~6e-3 on these distributions)."""
+    n, k, m = 9728, 2560, 256
+    blocks = pkg.synth.bg128_weight(20261125, 1, n, k)
+    x = pkg.synth.activations(7, 256, m, k)
+    y, _ = run_gpu(ctx, blocks, n, k, x, sums=False)
+    y_ref = ol.matmul_w4(blocks, n, k, x)
+    assert y.tobytes() == y_ref.tobytes()
+    rows = [0, 100, 255]
+    exact = ol.matmul_w4(blocks, n, k, x[rows], rule=ol.ACT_F64)
+    assert rel_l2(y[rows], exact) < 1e-2
+
+
+def test_gemv_and_tensor_core_paths_agree(ctx):
+    """The same rows through the dp4a GEMV (one at a time) and through the tensor-core
+    kernel (all at once) give identical bits."""
+    import torch
+    n, k, m = 520, 1024, 24
+    blocks = pkg.synth.bg128_weight(5, 5, n, k)
+    x = pkg.synth.activations(7, 77, m, k)
+    w = ctx.upload_weight(blocks, n, k)
+    xd = torch.from_numpy(x).cuda()
+    y_all = torch.zeros((m, n), device="cuda")
+    y_one = torch.zeros((m, n), device="cuda")
+    ctx.matmul(w, xd, y_all)
+    for r in range(m):
+        ctx.matmul(w, xd[r:r + 1], y_one[r:r + 1])
+    ctx.sync()
+    assert torch.equal(y_all, y_one)
+    w.free()
