@@ -240,9 +240,9 @@ def run_ours(args):
 
     # ---- headline: M=1, resident inputs -------------------------------------------------
     l0 = ctx.launches
-    make_step(1, graph=False)()
+    make_step(args.rows, graph=False)()
     launches_per_step = ctx.launches - l0
-    step = make_step(1)
+    step = make_step(args.rows)
     with ClockSampler(local) as clocks:
         ms = time_steps(torch, step, args.steps, args.warmup, barrier)
     if world > 1:
@@ -342,6 +342,9 @@ def main():
                     help="walks over the weight copies per step")
     ap.add_argument("--no-graph", action="store_true",
                     help="launch eagerly instead of replaying a CUDA graph (profiling)")
+    ap.add_argument("--rows", type=int, default=1,
+                    help="activation rows of the timed matmul (1 = the headline GEMV; other "
+                         "values are for profiling the batched kernels)")
     ap.add_argument("--headline-only", action="store_true",
                     help="skip the e2e, sweep and CPU-baseline legs (profiling)")
     args = ap.parse_args()

@@ -14,29 +14,33 @@
 // block.  R is chosen so that one wave of CTAs covers the weight (N / #SMs rounded up to a
 // tile), which no power-of-two tile would do for N = 9728 on 148 SMs.
 //
-// Pipeline per 128-k group (stage = group, ring of kStages):
-//   producer warp   bulk-copies (TMA engine) the group's nibble chunks of the CTA's row
-//                   tiles and the pre-quantised, pre-swizzled int8 activations
-//   unpack warps    nibbles -> int8 (left-aligned: 16*q4) into the B operand's K-major,
+// Pipeline per 128-k group:
+//   producer warp   bulk-copies (TMA engine) the pre-quantised, pre-swizzled int8
+//                   activations of the group (one copy), and, once per chunk of kGC groups,
+//                   the nibble stream of the CTA's row tiles (one copy per tile: a tile's
+//                   groups are contiguous).  Issuing a bulk copy costs ~60 ns, so the
+//                   number of copies per group, not their size, bounds the producer.
+//   unpack warps    nibbles -> sign-extended int8 into the B operand's K-major,
 //                   128-byte-swizzled layout; a 128-k group is exactly one swizzle row
 //   MMA warp        one thread issues 4 x tcgen05.mma (K = 32 each) per token block into
 //                   the group's TMEM accumulator, then tcgen05.commit
-//   epilogue warps  tcgen05.ld the int32 sums (thread = token, columns = weight rows),
-//                   shift out the factor 16, and run the fp32 chain in registers
-// TMEM holds two group accumulators, so the MMAs of group g+1 overlap the chain of group g.
+//   epilogue warps  tcgen05.ld the int32 sums (thread = token, columns = half of the
+//                   CTA's weight rows) and run the fp32 chain in registers
+// TMEM holds three to six group accumulators, so the MMAs run ahead of the fp32 chain.
 // Every wait is bounded; on a timeout the kernel flags the status word and drains.
 #include "b200w4_internal.cuh"
 
 namespace {
 
-constexpr int kStages = 3;
 constexpr int kProducerWarp = 0;
 constexpr int kMmaWarp = 1;
 constexpr int kUnpackWarp0 = 2, kUnpackWarps = 4;
-constexpr int kEpiWarp0 = 6, kEpiWarps = 8;
-constexpr int kThreads = (kEpiWarp0 + kEpiWarps) * 32;  // 448
+// four epilogue warpgroups: (token block, column half); a warp's TMEM lane quarter is its
+// warp index mod 4
+constexpr int kEpiWarp0 = 6, kEpiWarps = 16;
+constexpr int kThreads = (kEpiWarp0 + kEpiWarps) * 32;  // 704
 constexpr unsigned kSpinLimit = 1u << 24;
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;
+constexpr unsigned long long kWaitLimitCycles = 4000000000ull;  // SM cycles: about 2 s
 
 struct GemmArgs {
     const uint8_t* nib;  // [tiles][G][512]
@@ -53,10 +57,10 @@ struct GemmArgs {
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
-__device__ __forceinline__ unsigned long long global_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
+// SM cycle counter: cheap to read (the global nanosecond timer is not), good enough to
+// bound a wait
+__device__ __forceinline__ unsigned long long wait_clock() {
+    return (unsigned long long)clock64();
 }
 __device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
@@ -84,11 +88,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     if (mbar_try_wait(bar, parity))
         return true;
-    const unsigned long long t0 = global_ns();
+    const unsigned long long t0 = wait_clock();
     for (unsigned spins = 0; spins < kSpinLimit; ++spins) {
         if (mbar_try_wait(bar, parity))
             return true;
-        if ((spins & 255) == 255 && global_ns() - t0 > kWaitLimitNs)
+        if ((spins & 255) == 255 && wait_clock() - t0 > kWaitLimitCycles)
             return false;
     }
     return false;
@@ -133,74 +137,96 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
                  ::"r"(smem_u32(bar))
                  : "memory");
 }
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
     asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
         : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]),
-          "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+          "=r"(r[7])
         : "r"(taddr)
         : "memory");
+}
+// float(d) for |d| < 2^22 without the conversion pipe: 0x4B400000 is 1.5 * 2^23, whose
+// ulp is 1, so adding d to its bit pattern adds d to its value; the subtraction is exact.
+// A group sum is at most 128 * 8 * 127 = 130048 in magnitude.
+__device__ __forceinline__ float int_to_float_exact(int d) {
+    return __fsub_rn(__int_as_float(0x4B400000 + d), 12582912.0f);
 }
 
 __device__ __noinline__ float gemm_activation(float v, int act) {
     return b2w4_activation(v, act);
 }
 
-// shared-memory plan; stage buffers are 1024-byte aligned (swizzle atoms)
-template <int RP>
+constexpr int kGC = 4;      // groups per raw-weight chunk
+constexpr int kBStages = 3; // unpacked-weight (B operand) ring
+
+// shared-memory plan; operand buffers are 1024-byte aligned (swizzle atoms).  NB = token
+// blocks of 128 per CTA: one block leaves room for a deeper activation ring.
+template <int RP, int NB>
 struct Smem {
-    static constexpr int kActStage = 256 * 128;       // two token blocks of 128 x 128 B
-    static constexpr int kBStage = RP * 128;          // int8 weights, swizzled
-    static constexpr int kRawStage = (RP / 8) * 512;  // nibble chunks
+    static constexpr int kAStages = NB == 2 ? 3 : 6;
+    static constexpr int kActStage = NB * 128 * 128;        // NB token blocks of 128 x 128 B
+    static constexpr int kBStage = RP * 128;                // int8 weights, swizzled
+    static constexpr int kRawSlot = (RP / 8) * kGC * 512;   // nibbles: [tile][kGC][512]
     static constexpr int kActOff = 0;
-    static constexpr int kBOff = kActOff + kStages * kActStage;
-    static constexpr int kRawOff = kBOff + kStages * kBStage;
-    static constexpr int kWsOff = kRawOff + kStages * kRawStage;  // fp32 [G][RP], G <= kMaxG
+    static constexpr int kBOff = kActOff + kAStages * kActStage;
+    static constexpr int kRawOff = kBOff + kBStages * kBStage;
+    static constexpr int kWsOff = kRawOff + 2 * kRawSlot;   // fp32 [G][RP], G <= kMaxG
     static constexpr int kMaxG = 80;  // K <= 10240
-    static constexpr int kSclRawOff = kWsOff + kMaxG * RP * 4;    // raw scale chunk
-    static constexpr int kBarOff = kSclRawOff + (RP / 8) * kMaxG * 32;
-    static constexpr int kTotal = kBarOff + 256 + 1024;  // + slack to align the base
+    static constexpr int kBarOff = kWsOff + kMaxG * RP * 4;
+    static constexpr int kTotal = kBarOff + 512 + 1024;  // barriers, + slack to align the base
 };
 
-template <int RP, bool SCL16>
+template <int RP, int NB, bool SCL16>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_w4a8_tc_kernel(const GemmArgs a) {
+    constexpr int kAStages = Smem<RP, NB>::kAStages;
+    constexpr int CH = RP / 2;  // accumulator columns per epilogue thread
+    // TMEM holds kAcc group accumulators of NB*RP columns each (512 columns in all), so
+    // the MMAs run up to kAcc-1 groups ahead of the fp32 chain
+    constexpr int kAcc = 512 / (NB * RP) > 6 ? 6 : 512 / (NB * RP);
+    constexpr int kAccCols = NB * RP;
     extern __shared__ uint8_t smem_raw[];
     // swizzle atoms need a 1024-byte aligned base
     uint8_t* smem = smem_raw + ((1024 - (smem_u32(smem_raw) & 1023)) & 1023);
-    using S = Smem<RP>;
+    using S = Smem<RP, NB>;
     const int G = a.groups;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int R = min(a.rows_per_cta, a.n - blockIdx.x * a.rows_per_cta);  // may be ragged
     const int r_tiles = (R + 7) / 8;
     const int tile0 = blockIdx.x * (a.rows_per_cta / 8);
-    const int tok0 = blockIdx.y * 256;
-    const int m_here = min(256, a.m - tok0);
+    const int tok0 = blockIdx.y * (NB * 128);
+    const int m_here = min(NB * 128, a.m - tok0);
     const int n_blocks = (m_here + 127) / 128;  // token blocks of 128 in this CTA
 
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S::kBarOff);
-    uint64_t* raw_full = bars;                 // [kStages] nibbles + activations landed
-    uint64_t* b_full = bars + kStages;         // [kStages] unpack done
-    uint64_t* stage_free = bars + 2 * kStages; // [kStages] MMAs that read the stage retired
-    uint64_t* acc_full = bars + 3 * kStages;   // [2] group accumulator complete
-    uint64_t* acc_free = acc_full + 2;         // [2] epilogue has read it
-    uint64_t* scl_full = acc_free + 2;         // [1]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(scl_full + 1);
+    uint64_t* act_full = bars;                  // [kAStages] activations of a group landed
+    uint64_t* act_free = act_full + kAStages;   // [kAStages] MMAs that read them retired
+    uint64_t* b_full = act_free + kAStages;     // [kBStages] unpack done
+    uint64_t* b_free = b_full + kBStages;       // [kBStages] MMAs that read it retired
+    uint64_t* raw_full = b_free + kBStages;     // [2] nibble chunk landed
+    uint64_t* raw_free = raw_full + 2;          // [2] unpack warps are done with it
+    uint64_t* acc_full = raw_free + 2;          // [kAcc] group accumulator complete
+    uint64_t* acc_free = acc_full + kAcc;       // [kAcc] epilogue has read it
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_free + kAcc);
     volatile int* s_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; ++s) {
-            mbar_init(&raw_full[s], 1);
+        for (int s = 0; s < kAStages; ++s) {
+            mbar_init(&act_full[s], 1);
+            mbar_init(&act_free[s], 1);
+        }
+        for (int s = 0; s < kBStages; ++s) {
             mbar_init(&b_full[s], kUnpackWarps);
-            mbar_init(&stage_free[s], 1);
+            mbar_init(&b_free[s], 1);
         }
         for (int b = 0; b < 2; ++b) {
-            mbar_init(&acc_full[b], 1);
-            mbar_init(&acc_free[b], kEpiWarps);
+            mbar_init(&raw_full[b], 1);
+            mbar_init(&raw_free[b], kUnpackWarps);
         }
-        mbar_init(scl_full, 1);
+        for (int b = 0; b < kAcc; ++b) {
+            mbar_init(&acc_full[b], 1);
+            mbar_init(&acc_free[b], kEpiWarps);  // every epilogue warp arrives, busy or not
+        }
         *s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -222,82 +248,111 @@ gemm_w4a8_tc_kernel(const GemmArgs a) {
 
     if (warp == kProducerWarp) {
         // =============================== producer ===================================
-        if (lane == 0) {
-            // weight scales of the CTA's row tiles: [r_tiles][G][8], one contiguous run
-            const uint32_t scl_bytes = (uint32_t)r_tiles * G * 8 * (SCL16 ? 2 : 4);
-            mbar_expect_tx(scl_full, scl_bytes);
-            bulk_g2s(smem + S::kSclRawOff,
-                     reinterpret_cast<const uint8_t*>(a.scl) +
-                         (size_t)tile0 * G * 8 * (SCL16 ? 2 : 4),
-                     scl_bytes, scl_full);
-            for (int g = 0; g < G; ++g) {
-                const int s = g % kStages, round = g / kStages;
-                if (round > 0 && !mbar_wait(&stage_free[s], (round - 1) & 1)) {
-                    fail();
+        // lane t copies row tile t's share of a nibble chunk, lane 31 a group's activations
+        bool ok = true;
+        for (int g = 0; g < G; ++g) {
+            if (g % kGC == 0) {
+                const int chunk = g / kGC, slot = chunk & 1, use = chunk >> 1;
+                const int gc = min(kGC, G - g);
+                if (use > 0 && !mbar_wait(&raw_free[slot], (use - 1) & 1))
+                    ok = false;
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok)
                     break;
-                }
-                const uint32_t act_bytes = (uint32_t)n_blocks * 128 * 128;
-                mbar_expect_tx(&raw_full[s], (uint32_t)r_tiles * 512 + act_bytes);
-                for (int t = 0; t < r_tiles; ++t)
-                    bulk_g2s(smem + S::kRawOff + s * S::kRawStage + t * 512,
-                             a.nib + ((size_t)(tile0 + t) * G + g) * 512, 512, &raw_full[s]);
+                if (lane == 0)
+                    mbar_expect_tx(&raw_full[slot], (uint32_t)r_tiles * gc * 512);
+                __syncwarp();
+                if (lane < r_tiles)
+                    bulk_g2s(smem + S::kRawOff + slot * S::kRawSlot + lane * (kGC * 512),
+                             a.nib + ((size_t)(tile0 + lane) * G + g) * 512, (uint32_t)gc * 512,
+                             &raw_full[slot]);
+            }
+            const int s = g % kAStages, round = g / kAStages;
+            if (round > 0 && !mbar_wait(&act_free[s], (round - 1) & 1))
+                ok = false;
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok)
+                break;
+            if (lane == 31) {
+                // only the 8-token atoms that hold real tokens are copied; the MMA reads
+                // whatever the rest of the 128-token block holds and the epilogue ignores
+                // those accumulator rows
+                const uint32_t act_bytes = (uint32_t)((m_here + 7) / 8) * 1024;
+                mbar_expect_tx(&act_full[s], act_bytes);
                 bulk_g2s(smem + S::kActOff + s * S::kActStage,
-                         a.qa + ((size_t)g * a.m_pad + tok0) * 128, act_bytes, &raw_full[s]);
+                         a.qa + ((size_t)g * a.m_pad + tok0) * 128, act_bytes, &act_full[s]);
             }
         }
+        if (!ok && lane == 0)
+            fail();
     } else if (warp == kMmaWarp) {
         // =============================== MMA issue ===================================
         if (lane == 0) {
             const uint32_t idesc = umma_idesc_i8(RP);
             for (int g = 0; g < G; ++g) {
-                const int s = g % kStages, round = g / kStages;
-                const int b = g & 1, use = g >> 1;
-                if (!mbar_wait(&b_full[s], round & 1) ||
+                const int sa = g % kAStages, ra = g / kAStages;
+                const int sb = g % kBStages, rb = g / kBStages;
+                const int b = g % kAcc, use = g / kAcc;
+                if (!mbar_wait(&b_full[sb], rb & 1) || !mbar_wait(&act_full[sa], ra & 1) ||
                     (use > 0 && !mbar_wait(&acc_free[b], (use - 1) & 1))) {
                     fail();
                     break;
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t b_addr = smem_u32(smem + S::kBOff + s * S::kBStage);
+                const uint32_t b_addr = smem_u32(smem + S::kBOff + sb * S::kBStage);
                 for (int mb = 0; mb < n_blocks; ++mb) {
                     const uint32_t a_addr =
-                        smem_u32(smem + S::kActOff + s * S::kActStage + mb * 128 * 128);
-                    const uint32_t d = tmem_base + (uint32_t)(b * 256 + mb * RP);
+                        smem_u32(smem + S::kActOff + sa * S::kActStage + mb * 128 * 128);
+                    const uint32_t d = tmem_base + (uint32_t)(b * kAccCols + mb * RP);
 #pragma unroll
                     for (int j = 0; j < 4; ++j)  // four K = 32 steps inside the swizzle row
                         umma_i8(d, umma_desc_k_sw128(a_addr + j * 32),
                                 umma_desc_k_sw128(b_addr + j * 32), idesc, j > 0 ? 1u : 0u);
                 }
-                umma_commit(&stage_free[s]);  // the stage's operands may be overwritten
-                umma_commit(&acc_full[b]);    // the group's sums are complete
+                // a commit fires when every MMA issued so far has retired
+                umma_commit(&act_free[sa]);  // the activation stage may be refilled
+                umma_commit(&b_free[sb]);    // the unpacked weights may be overwritten
+                umma_commit(&acc_full[b]);   // the group's sums are complete
             }
         }
     } else if (warp < kEpiWarp0) {
         // =============================== unpack ======================================
         const int ut = (warp - kUnpackWarp0) * 32 + lane;  // 0..127
         for (int g = 0; g < G; ++g) {
-            const int s = g % kStages, round = g / kStages;
-            // raw_full also orders us after stage_free: the producer waited for it
-            if (*s_abort || !mbar_wait(&raw_full[s], round & 1)) {
+            const int chunk = g / kGC, slot = chunk & 1, cuse = chunk >> 1, gi = g % kGC;
+            const int sb = g % kBStages, rb = g / kBStages;
+            bool ok = !*s_abort;
+            if (ok && gi == 0)
+                ok = mbar_wait(&raw_full[slot], cuse & 1);   // the chunk's nibbles landed
+            if (ok && rb > 0)
+                ok = mbar_wait(&b_free[sb], (rb - 1) & 1);   // MMAs left this B stage
+            if (!ok) {
                 if (lane == 0)
                     fail();
                 break;
             }
-            const uint4* raw = reinterpret_cast<const uint4*>(smem + S::kRawOff + s * S::kRawStage);
-            uint8_t* bst = smem + S::kBOff + s * S::kBStage;
+            // raw slot: [tile][kGC groups][32 chunks of 16 B]
+            const uint4* raw =
+                reinterpret_cast<const uint4*>(smem + S::kRawOff + slot * S::kRawSlot) + gi * 32;
+            uint8_t* bst = smem + S::kBOff + sb * S::kBStage;
             // chunk c of tile t: sub = c/8, row = c%8 -> 32 k of weight row t*8+row
             for (int c = ut; c < r_tiles * 32; c += kUnpackWarps * 32) {
-                const uint4 w = raw[c];
                 const int t = c >> 5, sub = (c >> 3) & 3, row = c & 7;
+                const uint4 w = raw[t * (kGC * 32) + (c & 31)];
+                // low nibbles = even k, high nibbles = odd k; a nibble with bit 3 set is
+                // negative: OR in 0xF0 (0x08 * 30 = 0xF0, no carry between bytes)
                 uint4 ev, od;
-                ev.x = (w.x << 4) & 0xF0F0F0F0u;
-                od.x = w.x & 0xF0F0F0F0u;
-                ev.y = (w.y << 4) & 0xF0F0F0F0u;
-                od.y = w.y & 0xF0F0F0F0u;
-                ev.z = (w.z << 4) & 0xF0F0F0F0u;
-                od.z = w.z & 0xF0F0F0F0u;
-                ev.w = (w.w << 4) & 0xF0F0F0F0u;
-                od.w = w.w & 0xF0F0F0F0u;
+                {
+                    uint32_t t;
+                    t = w.x & 0x0F0F0F0Fu; ev.x = t | ((t & 0x08080808u) * 30u);
+                    t = (w.x >> 4) & 0x0F0F0F0Fu; od.x = t | ((t & 0x08080808u) * 30u);
+                    t = w.y & 0x0F0F0F0Fu; ev.y = t | ((t & 0x08080808u) * 30u);
+                    t = (w.y >> 4) & 0x0F0F0F0Fu; od.y = t | ((t & 0x08080808u) * 30u);
+                    t = w.z & 0x0F0F0F0Fu; ev.z = t | ((t & 0x08080808u) * 30u);
+                    t = (w.z >> 4) & 0x0F0F0F0Fu; od.z = t | ((t & 0x08080808u) * 30u);
+                    t = w.w & 0x0F0F0F0Fu; ev.w = t | ((t & 0x08080808u) * 30u);
+                    t = (w.w >> 4) & 0x0F0F0F0Fu; od.w = t | ((t & 0x08080808u) * 30u);
+                }
                 // weight row r = t*8+row: atom t (1024 B), row `row` (128 B), 16-byte
                 // chunks 2*sub (even k) and 2*sub+1 (odd k), XOR-swizzled with the row
                 uint8_t* rowp = bst + t * 1024 + row * 128;
@@ -307,46 +362,47 @@ gemm_w4a8_tc_kernel(const GemmArgs a) {
             // make the generic-proxy writes visible to the tensor core's async proxy
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
-            if (lane == 0)
-                mbar_arrive(&b_full[s]);
+            if (lane == 0) {
+                mbar_arrive(&b_full[sb]);
+                if (gi == kGC - 1 || g == G - 1)
+                    mbar_arrive(&raw_free[slot]);  // this warp is done with the chunk
+            }
         }
     } else {
         // =============================== epilogue ====================================
-        const int ew = warp - kEpiWarp0;   // 0..7
-        const int mb = ew >> 2;            // token block of this warpgroup
-        const int lq = warp & 3;           // TMEM lane quarter this warp may read
+        const int ew = warp - kEpiWarp0;       // 0..15
+        const int eg = ew >> 2;                // warpgroup
+        const int mb = eg % NB;                // its token block
+        const int ch = eg / NB;                // its column half
+        const int lq = warp & 3;               // TMEM lane quarter this warp may read
         const int tok = tok0 + mb * 128 + lq * 32 + lane;
-        const bool active = mb < n_blocks;
-        float acc[RP];
+        const bool active = ch < 2 && mb < n_blocks;
+        float acc[CH];
 #pragma unroll
-        for (int c = 0; c < RP; ++c)
+        for (int c = 0; c < CH; ++c)
             acc[c] = 0.f;
         // weight scales -> fp32 [G][RP] (column = row of the CTA), shared by all tokens
-        if (!mbar_wait(scl_full, 0)) {
-            if (lane == 0)
-                fail();
-        } else {
+        {
             float* wsf = reinterpret_cast<float*>(smem + S::kWsOff);
             const int et = ew * 32 + lane;
             for (int i = et; i < G * RP; i += kEpiWarps * 32) {
                 const int g = i / RP, c = i - g * RP;
                 float v = 0.f;
                 if (c < r_tiles * 8) {
-                    const int idx = ((c >> 3) * G + g) * 8 + (c & 7);
-                    v = SCL16 ? __half2float(reinterpret_cast<const __half*>(
-                                    smem + S::kSclRawOff)[idx])
-                              : reinterpret_cast<const float*>(smem + S::kSclRawOff)[idx];
+                    const size_t idx = ((size_t)(tile0 + (c >> 3)) * G + g) * 8 + (c & 7);
+                    v = SCL16 ? __half2float(reinterpret_cast<const __half*>(a.scl)[idx])
+                              : reinterpret_cast<const float*>(a.scl)[idx];
                 }
                 wsf[i] = v;
             }
         }
-        // named barrier among the 8 epilogue warps only
+        // named barrier among the epilogue warps only
         asm volatile("bar.sync 1, %0;" ::"n"(kEpiWarps * 32) : "memory");
-        const float* wsf = reinterpret_cast<const float*>(smem + S::kWsOff);
+        const float* wsf = reinterpret_cast<const float*>(smem + S::kWsOff) + ch * CH;
         const bool has_tok = active && tok < a.m;
         float a_next = has_tok ? a.as[tok] : 0.f;  // group 0; later groups one ahead
         for (int g = 0; g < G; ++g) {
-            const int b = g & 1, use = g >> 1;
+            const int b = g % kAcc, use = g / kAcc;
             const float a_s = a_next;
             if (g + 1 < G && has_tok)
                 a_next = a.as[(size_t)(g + 1) * a.m_pad + tok];
@@ -357,25 +413,23 @@ gemm_w4a8_tc_kernel(const GemmArgs a) {
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             if (active) {
-                const uint32_t taddr =
-                    tmem_base + ((uint32_t)(lq * 32) << 16) + (uint32_t)(b * 256 + mb * RP);
+                const uint32_t taddr = tmem_base + ((uint32_t)(lq * 32) << 16) +
+                                       (uint32_t)(b * kAccCols + mb * RP + ch * CH);
 #pragma unroll
-                for (int c0 = 0; c0 < RP; c0 += 16) {
-                    uint32_t r[16];
-                    tmem_ld16(taddr + c0, r);
+                for (int c0 = 0; c0 < CH; c0 += 8) {
+                    uint32_t r[8];
+                    tmem_ld8(taddr + c0, r);
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-                    for (int i = 0; i < 16; i += 4) {
+                    for (int i = 0; i < 8; i += 4) {
                         const float4 w4 = *reinterpret_cast<const float4*>(wsf + g * RP + c0 + i);
-                        // the nibbles were left-aligned (16*q4): the sum is an exact
-                        // multiple of 16
-                        acc[c0 + i + 0] = __fmaf_rn((float)((int)r[i + 0] >> 4),
+                        acc[c0 + i + 0] = __fmaf_rn(int_to_float_exact((int)r[i + 0]),
                                                     __fmul_rn(w4.x, a_s), acc[c0 + i + 0]);
-                        acc[c0 + i + 1] = __fmaf_rn((float)((int)r[i + 1] >> 4),
+                        acc[c0 + i + 1] = __fmaf_rn(int_to_float_exact((int)r[i + 1]),
                                                     __fmul_rn(w4.y, a_s), acc[c0 + i + 1]);
-                        acc[c0 + i + 2] = __fmaf_rn((float)((int)r[i + 2] >> 4),
+                        acc[c0 + i + 2] = __fmaf_rn(int_to_float_exact((int)r[i + 2]),
                                                     __fmul_rn(w4.z, a_s), acc[c0 + i + 2]);
-                        acc[c0 + i + 3] = __fmaf_rn((float)((int)r[i + 3] >> 4),
+                        acc[c0 + i + 3] = __fmaf_rn(int_to_float_exact((int)r[i + 3]),
                                                     __fmul_rn(w4.w, a_s), acc[c0 + i + 3]);
                     }
                 }
@@ -385,16 +439,45 @@ gemm_w4a8_tc_kernel(const GemmArgs a) {
             if (lane == 0)
                 mbar_arrive(&acc_free[b]);
         }
-        if (active && tok < a.m && !*s_abort) {
-            const int n0 = blockIdx.x * a.rows_per_cta;
-            float* dst = a.y + (size_t)tok * a.ldc + n0;
+        // Output: a thread holds one token's CH columns, which lie CH*4 bytes apart from the
+        // next token's in y.  Stage the warp's 32 x CH block in shared memory (the operand
+        // ring is idle: the last accumulator was complete, so every MMA and copy has
+        // retired) and store token rows with the lanes running along the columns.
+        if (active && !*s_abort) {
+            constexpr int SP = CH + 4;  // row pitch: 16-byte aligned, conflict-free float4s
+            float* stage = reinterpret_cast<float*>(smem + S::kActOff) + ew * (32 * SP);
+            const int n0 = blockIdx.x * a.rows_per_cta + ch * CH;
 #pragma unroll
-            for (int c = 0; c < RP; ++c) {
-                if (c < R) {
-                    float v = acc[c];
-                    if (b2w4_act_applies(n0 + c, a.activation, a.act_n_begin, a.act_n_len, a.n))
-                        v = gemm_activation(v, a.activation);
-                    dst[c] = v;
+            for (int c = 0; c < CH; c += 4) {
+                float4 v = make_float4(acc[c], acc[c + 1], acc[c + 2], acc[c + 3]);
+                if (a.activation != B2W4_NONE) {
+                    float* e = &v.x;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        if (b2w4_act_applies(n0 + c + i, a.activation, a.act_n_begin,
+                                             a.act_n_len, a.n))
+                            e[i] = gemm_activation(e[i], a.activation);
+                }
+                *reinterpret_cast<float4*>(stage + lane * SP + c) = v;
+            }
+            __syncwarp();
+            const int tok_w = tok0 + mb * 128 + lq * 32;  // first token of this warp
+            const int rows_w = min(32, a.m - tok_w);
+            const bool vec_ok = (a.ldc & 3) == 0 && (reinterpret_cast<uintptr_t>(a.y) & 15) == 0;
+            constexpr int V = CH / 4;  // float4s per token row
+#pragma unroll 4
+            for (int i = lane; i < rows_w * V; i += 32) {
+                const int r = i / V, c = (i - r * V) * 4;
+                const float4 v = *reinterpret_cast<const float4*>(stage + r * SP + c);
+                float* dst = a.y + (size_t)(tok_w + r) * a.ldc + n0 + c;
+                const int left = R - (ch * CH + c);  // valid columns from here on
+                if (left >= 4 && vec_ok) {
+                    *reinterpret_cast<float4*>(dst) = v;
+                } else {
+                    if (left > 0) dst[0] = v.x;
+                    if (left > 1) dst[1] = v.y;
+                    if (left > 2) dst[2] = v.z;
+                    if (left > 3) dst[3] = v.w;
                 }
             }
         }
@@ -410,11 +493,11 @@ gemm_w4a8_tc_kernel(const GemmArgs a) {
     }
 }
 
-template <int RP>
+template <int RP, int NB>
 int launch_rp(b2w4_ctx* ctx, const GemmArgs& a, bool scl16, dim3 grid) {
-    using S = Smem<RP>;
-    auto kern = scl16 ? gemm_w4a8_tc_kernel<RP, true> : gemm_w4a8_tc_kernel<RP, false>;
-    static bool configured[2] = {false, false};
+    using S = Smem<RP, NB>;
+    auto kern = scl16 ? gemm_w4a8_tc_kernel<RP, NB, true> : gemm_w4a8_tc_kernel<RP, NB, false>;
+    static bool configured[2] = {false, false};  // per instantiation; one device per process
     if (!configured[scl16]) {
         B2W4_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                             S::kTotal));
@@ -424,6 +507,15 @@ int launch_rp(b2w4_ctx* ctx, const GemmArgs& a, bool scl16, dim3 grid) {
     ctx->launches++;
     B2W4_CUDA(ctx, cudaGetLastError());
     return B2W4_OK;
+}
+
+template <int NB>
+int launch_nb(b2w4_ctx* ctx, const GemmArgs& a, bool scl16, dim3 grid, int rows) {
+    if (rows <= 32)
+        return launch_rp<32, NB>(ctx, a, scl16, grid);
+    if (rows <= 64)
+        return launch_rp<64, NB>(ctx, a, scl16, grid);
+    return launch_rp<80, NB>(ctx, a, scl16, grid);
 }
 
 }  // namespace
@@ -446,7 +538,8 @@ int b2w4_launch_gemm_tc(b2w4_ctx* ctx, const b2w4_weight* w, const float* x, int
                                         static_cast<float*>(as))) != B2W4_OK)
         return rc;
     // rows per CTA: one wave of CTAs over the SMs when the token extent is one block
-    const int token_blocks = (m + 255) / 256;
+    const int nb = m > 128 ? 2 : 1;  // token blocks of 128 per CTA
+    const int token_blocks = (m + nb * 128 - 1) / (nb * 128);
     int per_sm = (w->tiles * token_blocks + ctx->sm_count - 1) / ctx->sm_count;
     int r_tiles = (per_sm + token_blocks - 1) / token_blocks;
     r_tiles = max(1, min(r_tiles, 10));  // at most 80 accumulator columns per thread
@@ -470,9 +563,5 @@ int b2w4_launch_gemm_tc(b2w4_ctx* ctx, const b2w4_weight* w, const float* x, int
     a.act_n_len = act_n_len;
     dim3 grid((w->tiles + r_tiles - 1) / r_tiles, token_blocks);
     const bool scl16 = w->scales_fp16 != 0;
-    if (R <= 32)
-        return launch_rp<32>(ctx, a, scl16, grid);
-    if (R <= 64)
-        return launch_rp<64>(ctx, a, scl16, grid);
-    return launch_rp<80>(ctx, a, scl16, grid);
+    return nb == 2 ? launch_nb<2>(ctx, a, scl16, grid, R) : launch_nb<1>(ctx, a, scl16, grid, R);
 }

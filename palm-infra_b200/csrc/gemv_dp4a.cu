@@ -38,7 +38,7 @@ namespace {
 __host__ __device__ constexpr int gemv_warps(int mt) { return mt == 1 ? 16 : 8; }
 constexpr int kMaxTpc = 16;
 constexpr unsigned kSpinLimit = 1u << 22;  // bounded waits: give up, flag, return
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // and never longer than 2 s
+constexpr unsigned long long kWaitLimitCycles = 4000000000ull;  // SM cycles: about 2 s
 
 struct GemvArgs {
     const uint4* nib;
@@ -85,20 +85,20 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
         : "memory");
 }
 
-__device__ __forceinline__ unsigned long long global_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
+// SM cycle counter: cheap to read (the global nanosecond timer is not), good enough to
+// bound a wait
+__device__ __forceinline__ unsigned long long wait_clock() {
+    return (unsigned long long)clock64();
 }
 // Waits for phase 0 of an mbarrier; false when the iteration or the time limit runs out.
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar) {
     if (mbar_try_wait(bar, 0))
         return true;
-    const unsigned long long t0 = global_ns();
+    const unsigned long long t0 = wait_clock();
     for (unsigned spins = 0; spins < kSpinLimit; ++spins) {
         if (mbar_try_wait(bar, 0))
             return true;
-        if ((spins & 63) == 63 && global_ns() - t0 > kWaitLimitNs)
+        if ((spins & 63) == 63 && wait_clock() - t0 > kWaitLimitCycles)
             return false;
     }
     return false;

@@ -1,11 +1,589 @@
+// Routed mixture-of-experts op on the GPU, Qwen3-MoE configuration (softmax top-k routing,
+// no shared expert).  Stands in for kernel_qwen3_moe (reference kernels/moe.cpp:576-1129)
+// and select_moe_routes (kernels/moe_routing.cpp:25-169):
+//   1 router logits          hidden[T,H] x router[E,H]^T, fp16 router, fp64 accumulation
+//   2 route selection        top-k by raw logit, ties to the lower expert id, softmax over
+//                            the k selected logits
+//   3 compaction             counting sort of the T*k routes by expert, tokens ascending
+//   4 activation quantiser   int8 per 128 values, once per token (shared by its routes)
+//   5 grouped gate_up GEMV   per expert, over its ragged route list  -> [routes][2I]
+//   6 SwiGLU + quantiser     silu(gate) * up, int8 per 128 values    -> [routes][I]
+//   7 grouped down GEMV                                              -> [routes][H]
+//   8 combine                out[t] = sum_e w * y, experts in ascending id, sequential fma
+// Expert matmuls use the same W4A8 arithmetic as the dense path (per-128 rule, int32 group
+// sums, fp32 chain in group order), so a route's result equals a one-row GEMV of that
+// expert's weight slice.  Nothing is atomically accumulated: every output is written by one
+// thread in a fixed order.
 #include "b200w4_internal.cuh"
+
+namespace {
+
+constexpr unsigned kSpinLimit = 1u << 22;
+constexpr unsigned long long kWaitLimitCycles = 4000000000ull;  // SM cycles: about 2 s
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+// SM cycle counter: cheap to read (the global nanosecond timer is not), good enough to
+// bound a wait
+__device__ __forceinline__ unsigned long long wait_clock() {
+    return (unsigned long long)clock64();
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+                 "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar) {
+    if (mbar_try_wait(bar, 0))
+        return true;
+    const unsigned long long t0 = wait_clock();
+    for (unsigned spins = 0; spins < kSpinLimit; ++spins) {
+        if (mbar_try_wait(bar, 0))
+            return true;
+        if ((spins & 63) == 63 && wait_clock() - t0 > kWaitLimitCycles)
+            return false;
+    }
+    return false;
+}
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes,
+                                         uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+        ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar))
+        : "memory");
+}
+
+// ---- 1. router logits: one warp per (token, expert) -----------------------------------
+// fp32 activation times fp16 weight is exact in fp64 and a few thousand such terms of
+// similar magnitude add without rounding, so the fp64 sum does not depend on its order;
+// one rounding to fp32 at the end (the oracle accumulates the same way).
+__global__ void moe_router_logits_kernel(const float* __restrict__ hidden, int ldx, int tokens,
+                                         int hidden_size, const __half* __restrict__ router,
+                                         int num_experts, float* __restrict__ logits) {
+    const long long wid = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (wid >= (long long)tokens * num_experts)
+        return;
+    const int t = (int)(wid / num_experts), e = (int)(wid % num_experts);
+    const float* x = hidden + (size_t)t * ldx;
+    const __half* r = router + (size_t)e * hidden_size;
+    double acc = 0.0;
+    for (int d = lane; d < hidden_size; d += 32)
+        acc += (double)x[d] * (double)__half2float(r[d]);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1)
+        acc += __shfl_xor_sync(0xffffffffu, acc, off);
+    if (lane == 0)
+        logits[(size_t)t * num_experts + e] = (float)acc;
+}
+
+// ---- 2. route selection: one thread per token ------------------------------------------
+// insertion top-k with strict '>' (equal logits keep the lower expert id first), then
+// softmax over the selected logits: exp(l - l_max), sequential fp32 sum, times 1/sum
+// (kernels/moe_routing.cpp:129-142, :157-166).
+constexpr int kMaxTopK = 16;
+__global__ void moe_select_routes_kernel(const float* __restrict__ logits, int tokens,
+                                         int num_experts, int top_k, int32_t* __restrict__ idx,
+                                         float* __restrict__ weights) {
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= tokens)
+        return;
+    const float* row = logits + (size_t)t * num_experts;
+    int bi[kMaxTopK];
+    float bw[kMaxTopK];
+    for (int j = 0; j < top_k; ++j) {
+        bi[j] = 0;
+        bw[j] = -INFINITY;
+    }
+    for (int e = 0; e < num_experts; ++e) {
+        const float v = row[e];
+        for (int j = 0; j < top_k; ++j) {
+            if (v > bw[j]) {
+                for (int s = top_k - 1; s > j; --s) {
+                    bw[s] = bw[s - 1];
+                    bi[s] = bi[s - 1];
+                }
+                bw[j] = v;
+                bi[j] = e;
+                break;
+            }
+        }
+    }
+    const float maximum = bw[0];
+    float sum = 0.f;
+    for (int j = 0; j < top_k; ++j) {
+        // exp in fp64 and one rounding: agrees with a correctly rounded expf
+        bw[j] = (float)exp((double)__fsub_rn(bw[j], maximum));
+        sum = __fadd_rn(sum, bw[j]);
+    }
+    const float inverse = sum > 0.f ? __fdiv_rn(1.f, sum) : 0.f;
+    for (int j = 0; j < top_k; ++j) {
+        idx[(size_t)t * top_k + j] = bi[j];
+        weights[(size_t)t * top_k + j] = __fmul_rn(bw[j], inverse);
+    }
+}
+
+// ---- 3. compaction: one block, thread e owns expert e ----------------------------------
+// counts, exclusive offsets, and per expert its routes in ascending token order
+// (kernels/moe.cpp:759-776).  pos[t][j] = the compact position of token t's j-th route.
+__global__ void moe_compact_kernel(const int32_t* __restrict__ idx, int tokens, int top_k,
+                                   int num_experts, int32_t* __restrict__ offsets,
+                                   int32_t* __restrict__ route_token,
+                                   int32_t* __restrict__ pos) {
+    extern __shared__ int s_cnt[];  // [E+1]
+    const int routes = tokens * top_k;
+    for (int e = threadIdx.x; e <= num_experts; e += blockDim.x)
+        s_cnt[e] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < routes; i += blockDim.x)
+        atomicAdd(&s_cnt[idx[i]], 1);  // integer counts: order-free
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int run = 0;
+        for (int e = 0; e < num_experts; ++e) {
+            const int c = s_cnt[e];
+            s_cnt[e] = run;
+            run += c;
+        }
+        s_cnt[num_experts] = run;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e <= num_experts; e += blockDim.x)
+        offsets[e] = s_cnt[e];
+    for (int e = threadIdx.x; e < num_experts; e += blockDim.x) {
+        int cursor = s_cnt[e];
+        const int end = s_cnt[e + 1];
+        for (int i = 0; i < routes && cursor < end; ++i) {
+            if (idx[i] == e) {
+                route_token[cursor] = i / top_k;
+                pos[i] = cursor;
+                ++cursor;
+            }
+        }
+    }
+}
+
+// ---- 6. SwiGLU + quantiser: one warp per (route, 128-wide group of I) ------------------
+// inter = (g * 1/(1+exp(-g))) * u with gate = columns [0,I), up = [I,2I)
+// (kernels/moe.cpp:160-183), then the per-128 quantiser; codes in even/odd order.
+__global__ void moe_swiglu_quant_kernel(const float* __restrict__ gu, int routes,
+                                        int intermediate, int8_t* __restrict__ q,
+                                        float* __restrict__ scales) {
+    const int groups = intermediate >> 7;
+    const long long wid = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (wid >= (long long)routes * groups)
+        return;
+    const int r = (int)(wid / groups), g = (int)(wid % groups);
+    const float* gp = gu + (size_t)r * 2 * intermediate + (size_t)g * 128 + lane * 4;
+    const float* up = gp + intermediate;
+    float v[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float gate = gp[i];
+        const float e = (float)exp(-(double)gate);
+        const float s = __fdiv_rn(1.f, __fadd_rn(1.f, e));
+        v[i] = __fmul_rn(__fmul_rn(gate, s), up[i]);
+    }
+    float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1)
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+    float scale, inv;
+    b2w4_quant_params(amax, scale, inv);
+    const int c0 = b2w4_quant_code(v[0], inv), c1 = b2w4_quant_code(v[1], inv);
+    const int c2 = b2w4_quant_code(v[2], inv), c3 = b2w4_quant_code(v[3], inv);
+    if (lane == 0)
+        scales[(size_t)r * groups + g] = scale;
+    int8_t* blk = q + (size_t)r * intermediate + (size_t)g * 128 + (lane >> 3) * 32;
+    const int j = (lane & 7) * 2;
+    *reinterpret_cast<char2*>(blk + j) = make_char2((signed char)c0, (signed char)c2);
+    *reinterpret_cast<char2*>(blk + 16 + j) = make_char2((signed char)c1, (signed char)c3);
+}
+
+// ---- 8. combine: one thread per (token, hidden column) ---------------------------------
+// out[t] starts at 0 and takes fma(w, y, out) for the token's experts in ascending id
+// (kernels/moe.cpp:642-645, :966, :1100-1110).
+__global__ void moe_combine_kernel(const float* __restrict__ dn, const int32_t* __restrict__ idx,
+                                   const float* __restrict__ weights,
+                                   const int32_t* __restrict__ pos, int tokens, int top_k,
+                                   int hidden_size, float* __restrict__ out, int ldo) {
+    const int t = blockIdx.y;
+    const int d = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= tokens || d >= hidden_size)
+        return;
+    int order[kMaxTopK];
+    for (int j = 0; j < top_k; ++j)
+        order[j] = j;
+    for (int a = 1; a < top_k; ++a) {  // insertion sort of the k routes by expert id
+        const int cur = order[a];
+        const int key = idx[(size_t)t * top_k + cur];
+        int b = a - 1;
+        while (b >= 0 && idx[(size_t)t * top_k + order[b]] > key) {
+            order[b + 1] = order[b];
+            --b;
+        }
+        order[b + 1] = cur;
+    }
+    float acc = 0.f;
+    for (int j = 0; j < top_k; ++j) {
+        const int r = order[j];
+        const float w = weights[(size_t)t * top_k + r];
+        acc = __fmaf_rn(w, dn[(size_t)pos[(size_t)t * top_k + r] * hidden_size + d], acc);
+    }
+    out[(size_t)t * ldo + d] = acc;
+}
+
+// ---- 5 / 7. grouped expert GEMV over ragged route lists --------------------------------
+// grid = (CTAs per expert, experts).  CTA (c, e) owns `tpc` 8-row tiles of expert e's slice
+// of the aggregate weight and every route of that expert; an expert without routes costs
+// one read of two offsets.  The slice's nibble stream is bulk-copied into shared memory
+// once and reused for all of the expert's routes, four at a time.  The math is the dense
+// GEMV's: phase 1 integer group sums by dp4a (lane = (group, weight row)), phase 2 the fp32
+// chain per (tile, route, weight row) in ascending group order.
+constexpr int kGW = 8;          // warps
+constexpr int kGT = kGW * 32;
+constexpr int kGR = 4;          // routes per pass
+
+struct GroupedArgs {
+    const uint8_t* nib;
+    const void* scl;
+    const int8_t* qa;         // [rows][K] int8, even/odd order inside each 32-block
+    const float* as;          // [rows][G]
+    const int32_t* offsets;   // [E+1] route ranges
+    const int32_t* row_map;   // route -> activation row, or null for identity
+    float* out;               // [routes][n_e]
+    int* status;
+    int k, groups, n_e, tiles_e, tpc, d_stride;
+};
+
+template <bool SCL16>
+__global__ void __launch_bounds__(kGT, 2)
+moe_grouped_gemv_kernel(const GroupedArgs a) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int e = blockIdx.y;
+    const int r0 = a.offsets[e], r1 = a.offsets[e + 1];
+    const int tl0 = blockIdx.x * a.tpc;
+    const int ntile = min(a.tpc, a.tiles_e - tl0);
+    if (r0 >= r1 || ntile <= 0)
+        return;
+    const int G = a.groups, K = a.k;
+    const int tile_bytes = G * 512;
+    const int scl_tile_bytes = G * 8 * (SCL16 ? 2 : 4);
+    uint8_t* s_w = smem;
+    uint8_t* s_scl = s_w + (size_t)a.tpc * tile_bytes;
+    uint4* s_qa = reinterpret_cast<uint4*>(s_scl + (size_t)a.tpc * scl_tile_bytes);  // [kGR][K]
+    float* s_as = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(s_qa) + (size_t)kGR * K);
+    int32_t* s_d = reinterpret_cast<int32_t*>(s_as + kGR * G);  // [tpc][G][kGR][8] + pad
+    uint64_t* s_bar = reinterpret_cast<uint64_t*>(
+        (reinterpret_cast<uintptr_t>(s_d + (size_t)a.tpc * a.d_stride) + 7) & ~uintptr_t(7));
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int gl = lane >> 3, row = lane & 7;
+    const size_t gtile0 = (size_t)e * a.tiles_e + tl0;  // tile index in the aggregate
+
+    if (warp == 0) {
+        if (lane == 0)
+            mbar_init(&s_bar[0], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) {
+            const uint32_t wb = (uint32_t)ntile * tile_bytes, sb = (uint32_t)ntile * scl_tile_bytes;
+            mbar_expect_tx(&s_bar[0], wb + sb);
+            bulk_g2s(s_w, a.nib + gtile0 * tile_bytes, wb, &s_bar[0]);
+            bulk_g2s(s_scl, reinterpret_cast<const uint8_t*>(a.scl) + gtile0 * scl_tile_bytes, sb,
+                     &s_bar[0]);
+        }
+    }
+    const int ipt = (G + 3) >> 2;
+    const int n_items = ntile * ipt;
+    bool weights_ready = false;
+
+    for (int base = r0; base < r1; base += kGR) {
+        const int mc = min(kGR, r1 - base);
+        // quantised activations of this pass's routes
+        for (int i = threadIdx.x; i < mc * (K / 16); i += kGT) {
+            const int mi = i / (K / 16), c = i - mi * (K / 16);
+            const int src_row = a.row_map ? a.row_map[base + mi] : base + mi;
+            s_qa[mi * (K / 16) + c] =
+                reinterpret_cast<const uint4*>(a.qa + (size_t)src_row * K)[c];
+        }
+        for (int i = threadIdx.x; i < mc * G; i += kGT) {
+            const int mi = i / G, g = i - mi * G;
+            const int src_row = a.row_map ? a.row_map[base + mi] : base + mi;
+            s_as[mi * G + g] = a.as[(size_t)src_row * G + g];
+        }
+        __syncthreads();
+        if (!weights_ready) {
+            if (!mbar_wait_bounded(&s_bar[0])) {
+                if (lane == 0)
+                    atomicExch(a.status, B2W4_E_TIMEOUT);
+                return;  // every thread sees the same barrier: the exit is CTA-uniform
+            }
+            weights_ready = true;
+        }
+        // phase 1
+#pragma unroll 1
+        for (int it = warp; it < n_items; it += kGW) {
+            const int tl = it / ipt;
+            const int g = (it - tl * ipt) * 4 + gl;
+            if (g < G) {
+                const uint4* wt =
+                    reinterpret_cast<const uint4*>(s_w + (size_t)tl * tile_bytes) + g * 32 + row;
+                uint32_t we[16], wo[16];
+#pragma unroll
+                for (int s = 0; s < 4; ++s) {
+                    const uint4 w = wt[s * 8];
+                    we[s * 4 + 0] = (w.x << 4) & 0xF0F0F0F0u;
+                    wo[s * 4 + 0] = w.x & 0xF0F0F0F0u;
+                    we[s * 4 + 1] = (w.y << 4) & 0xF0F0F0F0u;
+                    wo[s * 4 + 1] = w.y & 0xF0F0F0F0u;
+                    we[s * 4 + 2] = (w.z << 4) & 0xF0F0F0F0u;
+                    wo[s * 4 + 2] = w.z & 0xF0F0F0F0u;
+                    we[s * 4 + 3] = (w.w << 4) & 0xF0F0F0F0u;
+                    wo[s * 4 + 3] = w.w & 0xF0F0F0F0u;
+                }
+                int32_t* dst = s_d + (size_t)tl * a.d_stride + (size_t)g * kGR * 8 + row;
+#pragma unroll
+                for (int mi = 0; mi < kGR; ++mi) {
+                    if (mi < mc) {
+                        const uint4* qa = s_qa + ((size_t)mi * K + (size_t)g * 128) / 16;
+                        int total = 0;
+#pragma unroll
+                        for (int s = 0; s < 4; ++s) {
+                            const uint4 ae = qa[s * 2], ao = qa[s * 2 + 1];
+                            int p = __dp4a((int)we[s * 4 + 0], (int)ae.x, 0);
+                            int q = __dp4a((int)wo[s * 4 + 0], (int)ao.x, 0);
+                            p = __dp4a((int)we[s * 4 + 1], (int)ae.y, p);
+                            q = __dp4a((int)wo[s * 4 + 1], (int)ao.y, q);
+                            p = __dp4a((int)we[s * 4 + 2], (int)ae.z, p);
+                            q = __dp4a((int)wo[s * 4 + 2], (int)ao.z, q);
+                            p = __dp4a((int)we[s * 4 + 3], (int)ae.w, p);
+                            q = __dp4a((int)wo[s * 4 + 3], (int)ao.w, q);
+                            total += p + q;
+                        }
+                        dst[mi * 8] = total >> 4;  // nibbles were left-aligned: exact
+                    }
+                }
+            }
+        }
+        __syncthreads();
+        // phase 2
+#pragma unroll 1
+        for (int t = threadIdx.x; t < ntile * kGR * 8; t += kGT) {
+            const int rr = t & 7, mi = (t >> 3) % kGR, tl = t / (8 * kGR);
+            if (mi >= mc)
+                continue;
+            const int32_t* dsrc = s_d + (size_t)tl * a.d_stride + mi * 8 + rr;
+            const float* as = s_as + mi * G;
+            float acc = 0.f;
+#pragma unroll 4
+            for (int g = 0; g < G; ++g) {
+                const float ws =
+                    SCL16 ? __half2float(
+                                reinterpret_cast<const __half*>(s_scl)[(tl * G + g) * 8 + rr])
+                          : reinterpret_cast<const float*>(s_scl)[(tl * G + g) * 8 + rr];
+                acc = __fmaf_rn((float)dsrc[g * kGR * 8], __fmul_rn(ws, as[g]), acc);
+            }
+            const int n = (tl0 + tl) * 8 + rr;
+            if (n < a.n_e)
+                a.out[(size_t)(base + mi) * a.n_e + n] = acc;
+        }
+        __syncthreads();
+    }
+}
+
+int grouped_d_stride(int groups) { return groups * kGR * 8 + 8; }
+
+size_t grouped_smem(int k, int groups, int tpc, bool scl16) {
+    return (size_t)tpc * groups * 512 + (size_t)tpc * groups * 8 * (scl16 ? 2 : 4) +
+           (size_t)kGR * k + sizeof(float) * kGR * groups +
+           sizeof(int32_t) * (size_t)tpc * grouped_d_stride(groups) + 8 + 16;
+}
+
+int launch_grouped(b2w4_ctx* ctx, const b2w4_weight* w, int num_experts, const int8_t* qa,
+                   const float* as, const int32_t* offsets, const int32_t* row_map,
+                   float* out) {
+    const int n_e = w->n / num_experts;
+    const bool scl16 = w->scales_fp16 != 0;
+    GroupedArgs a;
+    a.nib = reinterpret_cast<const uint8_t*>(w->nib);
+    a.scl = w->scl;
+    a.qa = qa;
+    a.as = as;
+    a.offsets = offsets;
+    a.row_map = row_map;
+    a.out = out;
+    a.status = ctx->flag_dev + 1;
+    a.k = w->k;
+    a.groups = w->groups;
+    a.n_e = n_e;
+    a.tiles_e = n_e / 8;
+    int tpc = 16;
+    while (tpc > 1 && grouped_smem(w->k, w->groups, tpc, scl16) > 100 * 1024)
+        tpc >>= 1;
+    a.tpc = tpc;
+    a.d_stride = grouped_d_stride(w->groups);
+    const size_t smem = grouped_smem(w->k, w->groups, tpc, scl16);
+    if (smem > 220 * 1024)
+        return b2w4_fail(ctx, B2W4_E_INVALID, "moe: K=%d needs %zu B shared memory", w->k, smem);
+    auto kern = scl16 ? moe_grouped_gemv_kernel<true> : moe_grouped_gemv_kernel<false>;
+    static size_t configured[2] = {48 * 1024, 48 * 1024};
+    if (smem > configured[scl16]) {
+        B2W4_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            (int)smem));
+        configured[scl16] = smem;
+    }
+    dim3 grid((a.tiles_e + tpc - 1) / tpc, num_experts);
+    kern<<<grid, kGT, smem, ctx->stream>>>(a);
+    ctx->launches++;
+    B2W4_CUDA(ctx, cudaGetLastError());
+    return B2W4_OK;
+}
+
+}  // namespace
+
+static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
 extern "C" {
-int b2w4_moe_forward(b2w4_ctx* ctx, const float*, int, int, int, const void*, int, int, int,
-                     const b2w4_weight*, const b2w4_weight*, float*, int, float*, int32_t*,
-                     float*) {
-    return b2w4_fail(ctx, B2W4_E_INVALID, "moe: not built yet");
+
+int b2w4_moe_select_routes(b2w4_ctx* ctx, const float* logits_dev, int tokens,
+                           int num_experts, int top_k, int32_t* indices_dev,
+                           float* weights_dev) {
+    if (!ctx)
+        return B2W4_E_INVALID;
+    if (!logits_dev || !indices_dev || !weights_dev || tokens <= 0 || num_experts <= 0 ||
+        top_k <= 0 || top_k > num_experts || top_k > kMaxTopK)
+        return b2w4_fail(ctx, B2W4_E_INVALID,
+                         "select_routes: need 0 < top_k <= min(experts, %d) (tokens=%d "
+                         "experts=%d top_k=%d)", kMaxTopK, tokens, num_experts, top_k);
+    moe_select_routes_kernel<<<(tokens + 127) / 128, 128, 0, ctx->stream>>>(
+        logits_dev, tokens, num_experts, top_k, indices_dev, weights_dev);
+    ctx->launches++;
+    B2W4_CUDA(ctx, cudaGetLastError());
+    return B2W4_OK;
 }
-int b2w4_moe_select_routes(b2w4_ctx* ctx, const float*, int, int, int, int32_t*, float*) {
-    return b2w4_fail(ctx, B2W4_E_INVALID, "moe: not built yet");
+
+int b2w4_moe_forward(b2w4_ctx* ctx, const float* hidden_dev, int ldx, int tokens,
+                     int hidden_size, const void* router_fp16_dev, int num_experts, int top_k,
+                     int intermediate, const b2w4_weight* gate_up, const b2w4_weight* down,
+                     float* out_dev, int ldo, float* logits_dev, int32_t* indices_dev,
+                     float* weights_dev) {
+    if (!ctx)
+        return B2W4_E_INVALID;
+    if (!hidden_dev || !router_fp16_dev || !gate_up || !down || !out_dev)
+        return b2w4_fail(ctx, B2W4_E_INVALID, "moe: null argument");
+    if (tokens <= 0 || num_experts <= 0 || top_k <= 0 || top_k > num_experts ||
+        top_k > kMaxTopK || hidden_size % 128 || intermediate % 128 || ldx < hidden_size ||
+        ldo < hidden_size)
+        return b2w4_fail(ctx, B2W4_E_INVALID,
+                         "moe: bad shape tokens=%d hidden=%d experts=%d top_k=%d inter=%d",
+                         tokens, hidden_size, num_experts, top_k, intermediate);
+    if (gate_up->k != hidden_size || gate_up->n != num_experts * 2 * intermediate ||
+        down->k != intermediate || down->n != num_experts * hidden_size)
+        return b2w4_fail(ctx, B2W4_E_INVALID,
+                         "moe: expert aggregates must be gate_up [E*2I, H] and down [E*H, I]");
+    const int routes = tokens * top_k;
+    const int gh = hidden_size / 128, gi = intermediate / 128;
+    // small routing state in one block
+    const size_t o_logits = 0;
+    const size_t o_idx = align_up(o_logits + sizeof(float) * tokens * num_experts, 256);
+    const size_t o_w = align_up(o_idx + sizeof(int32_t) * routes, 256);
+    const size_t o_off = align_up(o_w + sizeof(float) * routes, 256);
+    const size_t o_rt = align_up(o_off + sizeof(int32_t) * (num_experts + 1), 256);
+    const size_t o_pos = align_up(o_rt + sizeof(int32_t) * routes, 256);
+    const size_t small_bytes = align_up(o_pos + sizeof(int32_t) * routes, 256);
+    // quantised hidden (per token) and quantised SwiGLU output (per route)
+    const size_t o_qh = 0;
+    const size_t o_ash = align_up(o_qh + (size_t)tokens * hidden_size, 256);
+    const size_t o_qi = align_up(o_ash + sizeof(float) * tokens * gh, 256);
+    const size_t o_asi = align_up(o_qi + (size_t)routes * intermediate, 256);
+    const size_t quant_bytes = align_up(o_asi + sizeof(float) * routes * gi, 256);
+    void *sm = nullptr, *qb = nullptr, *gu = nullptr, *dn = nullptr;
+    int rc;
+    if ((rc = b2w4_reserve(ctx, SCR_MOE_A, small_bytes, &sm)) != B2W4_OK ||
+        (rc = b2w4_reserve(ctx, SCR_MOE_B, quant_bytes, &qb)) != B2W4_OK ||
+        (rc = b2w4_reserve(ctx, SCR_MOE_C, sizeof(float) * (size_t)routes * 2 * intermediate,
+                           &gu)) != B2W4_OK ||
+        (rc = b2w4_reserve(ctx, SCR_MOE_D, sizeof(float) * (size_t)routes * hidden_size,
+                           &dn)) != B2W4_OK)
+        return rc;
+    uint8_t* smb = static_cast<uint8_t*>(sm);
+    uint8_t* qbb = static_cast<uint8_t*>(qb);
+    float* logits = reinterpret_cast<float*>(smb + o_logits);
+    int32_t* idx = reinterpret_cast<int32_t*>(smb + o_idx);
+    float* wts = reinterpret_cast<float*>(smb + o_w);
+    int32_t* offsets = reinterpret_cast<int32_t*>(smb + o_off);
+    int32_t* route_token = reinterpret_cast<int32_t*>(smb + o_rt);
+    int32_t* pos = reinterpret_cast<int32_t*>(smb + o_pos);
+    int8_t* q_hidden = reinterpret_cast<int8_t*>(qbb + o_qh);
+    float* as_hidden = reinterpret_cast<float*>(qbb + o_ash);
+    int8_t* q_inter = reinterpret_cast<int8_t*>(qbb + o_qi);
+    float* as_inter = reinterpret_cast<float*>(qbb + o_asi);
+    cudaStream_t st = ctx->stream;
+
+    {
+        const long long threads = (long long)tokens * num_experts * 32;
+        moe_router_logits_kernel<<<(int)((threads + 255) / 256), 256, 0, st>>>(
+            hidden_dev, ldx, tokens, hidden_size, static_cast<const __half*>(router_fp16_dev),
+            num_experts, logits);
+        ctx->launches++;
+    }
+    moe_select_routes_kernel<<<(tokens + 127) / 128, 128, 0, st>>>(logits, tokens, num_experts,
+                                                                   top_k, idx, wts);
+    ctx->launches++;
+    moe_compact_kernel<<<1, 256, sizeof(int) * (num_experts + 1), st>>>(
+        idx, tokens, top_k, num_experts, offsets, route_token, pos);
+    ctx->launches++;
+    B2W4_CUDA(ctx, cudaGetLastError());
+    if ((rc = b2w4_launch_quantize(ctx, hidden_dev, ldx, tokens, hidden_size, B2W4_ACT_G128,
+                                   q_hidden, as_hidden, QLAYOUT_EVEN_ODD)) != B2W4_OK)
+        return rc;
+    if ((rc = launch_grouped(ctx, gate_up, num_experts, q_hidden, as_hidden, offsets,
+                             route_token, static_cast<float*>(gu))) != B2W4_OK)
+        return rc;
+    {
+        const long long threads = (long long)routes * gi * 32;
+        moe_swiglu_quant_kernel<<<(int)((threads + 255) / 256), 256, 0, st>>>(
+            static_cast<const float*>(gu), routes, intermediate, q_inter, as_inter);
+        ctx->launches++;
+    }
+    if ((rc = launch_grouped(ctx, down, num_experts, q_inter, as_inter, offsets, nullptr,
+                             static_cast<float*>(dn))) != B2W4_OK)
+        return rc;
+    {
+        dim3 grid((hidden_size + 255) / 256, tokens);
+        moe_combine_kernel<<<grid, 256, 0, st>>>(static_cast<const float*>(dn), idx, wts, pos,
+                                                 tokens, top_k, hidden_size, out_dev, ldo);
+        ctx->launches++;
+    }
+    B2W4_CUDA(ctx, cudaGetLastError());
+    if (logits_dev)
+        B2W4_CUDA(ctx, cudaMemcpyAsync(logits_dev, logits,
+                                       sizeof(float) * (size_t)tokens * num_experts,
+                                       cudaMemcpyDeviceToDevice, st));
+    if (indices_dev)
+        B2W4_CUDA(ctx, cudaMemcpyAsync(indices_dev, idx, sizeof(int32_t) * (size_t)routes,
+                                       cudaMemcpyDeviceToDevice, st));
+    if (weights_dev)
+        B2W4_CUDA(ctx, cudaMemcpyAsync(weights_dev, wts, sizeof(float) * (size_t)routes,
+                                       cudaMemcpyDeviceToDevice, st));
+    return B2W4_OK;
 }
-}
+
+}  // extern "C"
