@@ -97,6 +97,26 @@ int b2w4_matmul_host(b2w4_ctx* ctx, const b2w4_weight* w, const float* x_host,
                      int lda, float* y_host, int ldc, int m, int act_rule,
                      int activation, int act_n_begin, int act_n_len);
 
+/* No counterpart in the reference.  Some callers of this library cannot allocate
+ * device memory at the time they run a matmul: code inside a real-time or
+ * latency-critical serving loop that forbids cudaMalloc (it synchronises the
+ * device), code running while a stream capture is open, or a host runtime whose
+ * memory budget was fixed at start-up.  b2w4_matmul quantises the activations
+ * into a pool that grows with cudaMalloc on demand; this variant runs the same
+ * tensor-core kernel with that buffer in a fixed 2.6 MiB array inside the
+ * library image, and calls no cudaMalloc, cudaFree or other allocating routine.
+ * Limits: 5 <= m <= 256 rows, K <= 10240; anything else is B2W4_E_INVALID.
+ * Same arithmetic and bits as b2w4_matmul (per-128 rule only).
+ * The first call on a device looks up the array's device address
+ * (cudaGetSymbolAddress) with that device current: make that first call before
+ * any stream capture.  All calls share the array, which keeps the previous
+ * call's contents (nothing in it needs to start at zero); calls that overlap on
+ * the GPU race on it.  Every GPU that uses the library holds the array until
+ * the process exits. */
+int b2w4_matmul_static_scratch(b2w4_ctx* ctx, const b2w4_weight* w, const float* x_dev,
+                               int lda, float* y_dev, int ldc, int m, int activation,
+                               int act_n_begin, int act_n_len);
+
 /* Parity hook with no reference counterpart in the CUDA backend: writes the
  * int32 group accumulators of the same kernels, [M][N][K/128] for
  * B2W4_ACT_G128 or [M][N][K/32] for B2W4_ACT_G32, to device memory. */

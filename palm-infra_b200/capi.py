@@ -19,6 +19,7 @@ SYMBOLS = [
     "b2w4_last_error", "b2w4_version", "b2w4_weight_upload", "b2w4_weight_from_device",
     "b2w4_weight_free", "b2w4_weight_shape", "b2w4_weight_scales_fp16",
     "b2w4_weight_stream_bytes", "b2w4_matmul", "b2w4_matmul_host",
+    "b2w4_matmul_static_scratch",
     "b2w4_debug_group_sums", "b2w4_quantize_activations", "b2w4_moe_forward",
     "b2w4_moe_select_routes", "b2w4_kernel_launches",
 ]
@@ -57,6 +58,7 @@ def lib():
         L.b2w4_weight_stream_bytes.restype = C.c_size_t
         L.b2w4_matmul.argtypes = [vp, vp, f_p, i, f_p, i, i, i, i, i, i]
         L.b2w4_matmul_host.argtypes = [vp, vp, f_p, i, f_p, i, i, i, i, i, i]
+        L.b2w4_matmul_static_scratch.argtypes = [vp, vp, f_p, i, f_p, i, i, i, i, i]
         L.b2w4_debug_group_sums.argtypes = [vp, vp, f_p, i, i, i, vp]
         L.b2w4_quantize_activations.argtypes = [vp, f_p, i, i, i, i, vp, vp]
         L.b2w4_moe_forward.argtypes = [vp, f_p, i, i, i, vp, i, i, i, vp, vp, f_p, i, f_p,
@@ -146,6 +148,16 @@ class Context:
         ldc = y.stride(0) if ldc is None else ldc
         self._check(lib().b2w4_matmul(self.handle, w.handle, _dptr(x), lda, _dptr(y), ldc,
                                       m, rule, act, act_begin, act_len))
+
+    def matmul_static_scratch(self, w, x, y, m=None, act=NONE, act_begin=0, act_len=-1):
+        """The tensor-core matmul with its scratch in the library's fixed device array
+        (5 <= M <= 256, K <= 10240): allocates nothing.  The first call on a device does a
+        one-time address look-up, so make it before any stream capture; overlapping calls
+        race on the shared array."""
+        m = x.shape[0] if m is None else m
+        self._check(lib().b2w4_matmul_static_scratch(self.handle, w.handle, _dptr(x),
+                                                     x.stride(0), _dptr(y), y.stride(0), m,
+                                                     act, act_begin, act_len))
 
     def matmul_host(self, w, x_np, y_np, rule=ACT_G128, act=NONE, act_begin=0, act_len=-1):
         m = x_np.shape[0]

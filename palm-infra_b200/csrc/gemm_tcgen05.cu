@@ -565,3 +565,107 @@ int b2w4_launch_gemm_tc(b2w4_ctx* ctx, const b2w4_weight* w, const float* x, int
     const bool scl16 = w->scales_fp16 != 0;
     return nb == 2 ? launch_nb<2>(ctx, a, scl16, grid, R) : launch_nb<1>(ctx, a, scl16, grid, R);
 }
+
+// ---------------------------------------------------------------------------------------
+// b2w4_matmul_static_scratch: the tensor-core matmul for callers that may not allocate.
+//
+// The tensor-core kernel reads activations that a first kernel has quantised into device
+// memory.  b2w4_matmul takes that buffer from a grow-on-demand cudaMalloc pool; this variant
+// takes it from the fixed array below, so the call issues no cudaMalloc / cudaFree and no
+// other allocating routine.  The array is part of the library image: every GPU on which the
+// library is used holds these 2.6 MiB until the process exits.
+//
+// Limits: 5 <= M <= 256 activation rows and K <= 10240 (80 groups of 128).
+// The array is shared by every call and keeps the last call's contents.  Nothing in it has
+// to start at zero: the quantiser rewrites every (group, row < M) entry each call, and rows
+// M..M_pad only feed accumulator lanes that are never read.  Two calls that overlap on the
+// GPU (different streams, or different contexts on one device) race on it.
+namespace {
+
+constexpr int kStaticMaxRows = 256;
+constexpr int kStaticMaxGroups = 80;
+constexpr size_t kStaticCodeBytes = (size_t)kStaticMaxGroups * kStaticMaxRows * 128;
+constexpr size_t kStaticScaleBytes = sizeof(float) * kStaticMaxGroups * kStaticMaxRows;
+constexpr int kStaticMaxDevices = 64;
+
+static __device__ __align__(256) uint8_t g_static_scratch[kStaticCodeBytes + kStaticScaleBytes];
+
+// In host code `g_static_scratch` is only a handle for the symbol, not a device address;
+// the address a kernel can use comes from cudaGetSymbolAddress, per device.
+void* g_static_scratch_addr[kStaticMaxDevices] = {nullptr};
+
+}  // namespace
+
+extern "C" int b2w4_matmul_static_scratch(b2w4_ctx* ctx, const b2w4_weight* w,
+                                          const float* x_dev, int lda, float* y_dev, int ldc,
+                                          int m, int activation, int act_n_begin,
+                                          int act_n_len) {
+    if (!ctx)
+        return B2W4_E_INVALID;
+    if (!w || !x_dev || !y_dev)
+        return b2w4_fail(ctx, B2W4_E_INVALID, "matmul_static_scratch: null weight or tensor");
+    if (m < 5 || m > kStaticMaxRows)
+        return b2w4_fail(ctx, B2W4_E_INVALID,
+                         "matmul_static_scratch: M=%d is outside 5..%d (the fixed scratch "
+                         "holds %d rows; use b2w4_matmul for other sizes)",
+                         m, kStaticMaxRows, kStaticMaxRows);
+    if (w->groups > kStaticMaxGroups)
+        return b2w4_fail(ctx, B2W4_E_INVALID,
+                         "matmul_static_scratch: K=%d exceeds %d (the fixed scratch holds %d "
+                         "groups of 128)", w->k, kStaticMaxGroups * 128, kStaticMaxGroups);
+    if (lda < w->k || ldc < w->n)
+        return b2w4_fail(ctx, B2W4_E_INVALID, "matmul_static_scratch: lda=%d (k=%d) ldc=%d (n=%d)",
+                         lda, w->k, ldc, w->n);
+    if (activation < B2W4_NONE || activation > B2W4_RELU_SQUARED)
+        return b2w4_fail(ctx, B2W4_E_INVALID, "matmul_static_scratch: unknown activation %d",
+                         activation);
+    if (ctx->device < 0 || ctx->device >= kStaticMaxDevices)
+        return b2w4_fail(ctx, B2W4_E_INVALID, "matmul_static_scratch: device index %d",
+                         ctx->device);
+    // one-time set-up per device, done by the first call on that device (so that first call
+    // should be made before any stream capture begins)
+    if (!g_static_scratch_addr[ctx->device]) {
+        int current = -1;
+        B2W4_CUDA(ctx, cudaGetDevice(&current));
+        if (current != ctx->device)
+            return b2w4_fail(ctx, B2W4_E_INVALID,
+                             "matmul_static_scratch: device %d must be current (it is %d)",
+                             ctx->device, current);
+        void* addr = nullptr;
+        B2W4_CUDA(ctx, cudaGetSymbolAddress(&addr, g_static_scratch));
+        g_static_scratch_addr[ctx->device] = addr;
+    }
+    uint8_t* base = static_cast<uint8_t*>(g_static_scratch_addr[ctx->device]);
+    int8_t* qa = reinterpret_cast<int8_t*>(base);
+    float* as = reinterpret_cast<float*>(base + kStaticCodeBytes);
+    const int G = w->groups;
+    const int m_pad = (m + 127) / 128 * 128;
+    int rc = b2w4_launch_quantize_umma(ctx, x_dev, lda, m, w->k, m_pad, qa, as);
+    if (rc != B2W4_OK)
+        return rc;
+    const int nb = m > 128 ? 2 : 1;
+    const int token_blocks = 1;  // M <= 256: one CTA row of token blocks
+    int r_tiles = (w->tiles + ctx->sm_count - 1) / ctx->sm_count;
+    r_tiles = max(1, min(r_tiles, 10));
+    GemmArgs a;
+    a.nib = reinterpret_cast<const uint8_t*>(w->nib);
+    a.scl = w->scl;
+    a.qa = qa;
+    a.as = as;
+    a.y = y_dev;
+    a.status = ctx->flag_dev + 1;
+    a.ldc = ldc;
+    a.m = m;
+    a.m_pad = m_pad;
+    a.n = w->n;
+    a.groups = G;
+    a.tiles = w->tiles;
+    a.rows_per_cta = r_tiles * 8;
+    a.activation = activation;
+    a.act_n_begin = act_n_begin;
+    a.act_n_len = act_n_len;
+    dim3 grid((w->tiles + r_tiles - 1) / r_tiles, token_blocks);
+    const bool scl16 = w->scales_fp16 != 0;
+    return nb == 2 ? launch_nb<2>(ctx, a, scl16, grid, r_tiles * 8)
+                   : launch_nb<1>(ctx, a, scl16, grid, r_tiles * 8);
+}
