@@ -40,6 +40,24 @@ METRIC, UNIT = "w4g128_gemv_hbm_gbs", "GB/s"
 L2_MB = 126
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of ONE gemv_w4a8_kernel launch on this workload,
+# from the ncu capture summarised in profiles/gemv_w4a8_m1_k2560_n9728.md
+NCU_DRAM_BYTES_PER_LAUNCH = None
+
+
+def workload_config(world=1, passes=PASSES, graph=True):
+    return {"workload": f"W4G128 W4A8 GEMV M=1 K={K_IN} N={N_OUT} "
+                        f"(benchmark configuration 2, decode)",
+            "gemvs_per_step": COPIES * passes,
+            "l2": f"rotates {COPIES} distinct weight copies "
+                  f"({COPIES * 12.84:.0f} MB) > {L2_MB} MB L2",
+            "parallelism": (f"tp{world}: output rows split over the ranks, NCCL all-gather "
+                            f"of y after every GEMV") if world > 1 else "single GPU",
+            "act_rule": "int8 per 128 values",
+            "launch": ("CUDA graph replay" if graph else "eager")
+                      + ", programmatic dependent launch"}
+
+
 def algorithmic_bytes(n, k, m):
     """int4 weights + one fp16 scale per 128 weights + fp32 x + fp32 y."""
     return n * k // 2 + n * (k // 128) * 2 + m * k * 4 + m * n * 4
@@ -168,8 +186,10 @@ def run_reference(args):
             "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": sec * per_step * 1e3, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": f"W4G128 GEMV M=1 K={K_IN} N={N_OUT} on host cores",
-                       "copies": copies},
+            "config": dict(workload_config(1, 1, False), gemvs_per_step=per_step,
+                           l2=f"rotates {copies} weight copies ({copies * 13.2:.0f} MB)",
+                           launch=f"{cores} host threads, {isa}",
+                           reference="the reference's own CPU kernel (W4A32) on the host cores"),
             "cpu_baseline": {"value": gbs, "unit": UNIT, "cores": cores, "kind": kind,
                              "sample": sample},
             "e2e": {"value": gbs, "unit": UNIT, "h2d_bytes_per_step": 0,
@@ -179,6 +199,45 @@ def run_reference(args):
 
 
 # --------------------------------------------------------------------------------- ours
+
+def decode_walk(torch, pkg, ctx, args):
+    """The W4 matmuls of one decode token of a Qwen3-4B-shaped dense decoder (benchmark
+    configuration 3): 36 layers of qkv [6144,2560], o [2560,4096], gate_up [19456,2560],
+    down [2560,9728], then lm_head [151936,2560]; 2.07 GB of weights per token, every layer
+    its own device buffers.  Matmul path only (no attention, norms or sampling)."""
+    shapes = [(6144, 2560), (2560, 4096), (19456, 2560), (2560, 9728)]
+    layers, vocab = 36, 151936
+    host = [pkg.synth.bg128_weight(SEED_W, 50 + i, n, k) for i, (n, k) in enumerate(shapes)]
+    ws = []
+    for layer in range(layers):
+        for (n, k), blk in zip(shapes, host):
+            ws.append(ctx.upload_weight(np.roll(blk, 544 * layer), n, k))
+    ws.append(ctx.upload_weight(pkg.synth.bg128_weight(SEED_W, 60, vocab, 2560), vocab, 2560))
+    xs = {k: torch.from_numpy(pkg.synth.activations(SEED_X, k, 1, k)).cuda()
+          for k in (2560, 4096, 9728)}
+    ys = {n: torch.zeros((1, n), dtype=torch.float32, device="cuda")
+          for n in (6144, 2560, 19456, vocab)}
+
+    def eager():
+        for w in ws:
+            ctx.matmul(w, xs[w.k], ys[w.n])
+    eager()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        ctx.set_stream(side.cuda_stream)
+        with torch.cuda.graph(g, stream=side):
+            eager()
+    ctx.set_stream(torch.cuda.current_stream().cuda_stream)
+    ms = time_steps(torch, g.replay, max(5, min(args.steps, 30)), 3)
+    total = sum(algorithmic_bytes(w.n, w.k, 1) for w in ws)
+    out = {"matmuls_per_token": len(ws), "weight_gb_per_token": total / 1e9,
+           "ms_per_token": ms, "tokens_per_s": 1e3 / ms, "gbs": total / (ms * 1e-3) / 1e9}
+    for w in ws:
+        w.free()
+    return out
+
 
 def run_ours(args):
     import torch
@@ -197,12 +256,8 @@ def run_ours(args):
     ctx.set_stream(torch.cuda.current_stream().cuda_stream)
 
     # rank r owns output rows [r*N/P, (r+1)*N/P) of every weight copy (8-row tiles kept whole)
-    n_local = N_OUT // world
-    assert N_OUT % (8 * world) == 0
     one = pkg.synth.bg128_weight(SEED_W, 1, N_OUT, K_IN)
-    tile_bytes = (K_IN // 128) * 544
-    lo = rank * (n_local // 8) * tile_bytes
-    shard = one[lo:lo + (n_local // 8) * tile_bytes]
+    shard, n_local, _ = pkg.shard.shard_blocks(one, N_OUT, K_IN, rank, world)
     weights = []
     for i in range(COPIES):  # distinct device buffers; rolling by whole blocks keeps layout
         weights.append(ctx.upload_weight(np.roll(shard, 544 * i), n_local, K_IN))
@@ -238,6 +293,13 @@ def run_ours(args):
         ctx.set_stream(torch.cuda.current_stream().cuda_stream)
         return g.replay
 
+    def max_over_ranks(v):
+        if world == 1:
+            return v
+        t = torch.tensor([v], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
     # ---- headline: M=1, resident inputs -------------------------------------------------
     l0 = ctx.launches
     make_step(args.rows, graph=False)()
@@ -245,10 +307,7 @@ def run_ours(args):
     step = make_step(args.rows)
     with ClockSampler(local) as clocks:
         ms = time_steps(torch, step, args.steps, args.warmup, barrier)
-    if world > 1:
-        t = torch.tensor([ms], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
+    ms = max_over_ranks(ms)
     alg = algorithmic_bytes(N_OUT, K_IN, 1)
     gemvs = COPIES * args.passes
     value = gemvs * alg / (ms * 1e-3) / 1e9
@@ -260,28 +319,20 @@ def run_ours(args):
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "s8*s4->s32, f32 scale chain", "data": "synthetic",
-            "config": {"workload": f"W4G128 W4A8 GEMV M=1 K={K_IN} N={N_OUT} "
-                                   f"(benchmark configuration 2, decode)",
-                       "gemvs_per_step": COPIES * args.passes,
-                       "launch": ("eager" if args.no_graph else "CUDA graph replay")
-                       + ", programmatic dependent launch",
-                       "l2": f"rotates {COPIES} distinct weight copies "
-                             f"({COPIES * stream_bytes * world / 1e6:.0f} MB) > {L2_MB} MB L2",
-                       "parallelism": f"tp{world} (output rows split, NCCL all-gather)"
-                       if world > 1 else "single GPU",
-                       "act_rule": "int8 per 128 values"},
+            "config": workload_config(world, args.passes, not args.no_graph),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "traffic": None,
+                         "frac": achieved / peak, "traffic": NCU_DRAM_BYTES_PER_LAUNCH if world == 1 else None,
                          "kernel": "gemv_w4a8_kernel", "peak_kind": peak_kind,
                          "algorithmic_bytes_per_launch": algorithmic_bytes(n_local, K_IN, 1),
                          "avg_launch_us": launch_us},
             "clocks": clocks.summary(),
             "gpu_launches": launches_per_step * args.steps}
 
-    if rank == 0 and world == 1 and not args.headline_only:
-        # ---- e2e: the same step through the host-buffer entry point ---------------------
+    if not args.headline_only:
+        # ---- e2e: the same step through the host-buffer entry point (every rank streams its
+        # shard from pinned host x to pinned host y; the slowest rank counts) ---------------
         xh = torch.from_numpy(pkg.synth.activations(SEED_X, 0, 1, K_IN)).pin_memory()
-        yh = torch.zeros((1, N_OUT), dtype=torch.float32).pin_memory()
+        yh = torch.zeros((1, n_local), dtype=torch.float32).pin_memory()
         xn, yn = xh.numpy(), yh.numpy()
 
         def host_step():
@@ -290,16 +341,19 @@ def run_ours(args):
                     ctx.matmul_host(w, xn, yn)
         for _ in range(args.warmup):
             host_step()
+        if barrier:
+            barrier()
         t0 = time.perf_counter()
         for _ in range(args.steps):
             host_step()
-        e2e_s = (time.perf_counter() - t0) / args.steps
+        e2e_s = max_over_ranks((time.perf_counter() - t0) / args.steps)
         line["e2e"] = {"value": gemvs * alg / e2e_s / 1e9, "unit": UNIT,
-                       "h2d_bytes_per_step": gemvs * K_IN * 4,
+                       "h2d_bytes_per_step": gemvs * K_IN * 4 * world,
                        "d2h_bytes_per_step": gemvs * N_OUT * 4,
                        "ms_per_step": e2e_s * 1e3,
                        "api": "b2w4_matmul_host (pinned host x and y, synchronous)"}
 
+    if rank == 0 and world == 1 and not args.headline_only:
         # ---- sweep: batched decode and prefill on the same weight -----------------------
         sweep = {}
         for m in (4, 16, 64, 256):
@@ -309,6 +363,7 @@ def run_ours(args):
                               "gbs": algorithmic_bytes(N_OUT, K_IN, m) / per / 1e9,
                               "tflops": 2.0 * m * N_OUT * K_IN / per / 1e12,
                               "tokens_per_s": m / per}
+        sweep["dense4b_decode_matmul_walk"] = decode_walk(torch, pkg, ctx, args)
         line["sweep"] = sweep
 
         # ---- CPU baseline: the reference's own kernel on this box's host cores ----------
@@ -319,9 +374,6 @@ def run_ours(args):
             "value": alg / sec / 1e9, "unit": UNIT, "cores": cores, "kind": kind,
             "sample": f"{repeat} GEMVs rotating 16 weight copies, isa {isa}, "
                       f"W4A32 arithmetic ({sec * 1e3:.3f} ms per GEMV)"}
-    elif rank == 0:
-        line["e2e"] = {"value": None, "unit": UNIT, "h2d_bytes_per_step": 0,
-                       "d2h_bytes_per_step": 0, "note": "measured at N=1 only"}
 
     if rank == 0:
         print(json.dumps(line))

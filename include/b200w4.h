@@ -60,7 +60,7 @@ const char* b2w4_version(void);
 
 /* ---- weights -------------------------------------------------------------
  * Replaces CudaBackend::wrap_weight_int4 (engine/cuda_backend.cu:462-487) and
- * its upload helper (:176-210): validates K%128==0, copies the blocks (the
+ * its upload helper (:147-175): validates K%128==0, copies the blocks (the
  * caller may free or overwrite them afterwards) and repacks them on the device
  * into the streaming layout the kernels read (nibble plane + scale plane).
  * `host_blocks` holds ((N+7)/8)*(K/128)*544 bytes. */
@@ -92,7 +92,7 @@ int b2w4_matmul(b2w4_ctx* ctx, const b2w4_weight* w, const float* x_dev, int lda
 
 /* Replaces CudaBackend::Impl::run_matmul (host tensors staged through the
  * device, engine/cuda_backend.cu:339-359) and CudaBackend::lm_head_gemv
- * (:1404-1424): host x, host y, synchronous. */
+ * (:1393-1400): host x, host y, synchronous. */
 int b2w4_matmul_host(b2w4_ctx* ctx, const b2w4_weight* w, const float* x_host,
                      int lda, float* y_host, int ldc, int m, int act_rule,
                      int activation, int act_n_begin, int act_n_len);
