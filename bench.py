@@ -42,7 +42,7 @@ L2_MB = 126
 
 # dram__bytes_read.sum + dram__bytes_write.sum of ONE gemv_w4a8_kernel launch on this workload,
 # from the ncu capture summarised in profiles/gemv_w4a8_m1_k2560_n9728.md
-NCU_DRAM_BYTES_PER_LAUNCH = None
+NCU_DRAM_BYTES_PER_LAUNCH = 12874240
 
 
 def workload_config(world=1, passes=PASSES, graph=True):
@@ -240,6 +240,9 @@ def decode_walk(torch, pkg, ctx, args):
 
 
 def run_ours(args):
+    # NCCL prints its version banner on stdout at some debug levels; stdout carries the JSON line
+    if os.environ.get("NCCL_DEBUG", "").upper() in ("VERSION", "INFO"):
+        os.environ["NCCL_DEBUG"] = "WARN"
     import torch
     import torch.distributed as dist
 
@@ -376,12 +379,19 @@ def run_ours(args):
                       f"W4A32 arithmetic ({sec * 1e3:.3f} ms per GEMV)"}
 
     if rank == 0:
-        print(json.dumps(line))
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        # Tear-down order matters with NCCL work captured in CUDA graphs: drain the device,
+        # meet the other ranks, then leave without running NCCL's destructors (they can wait
+        # for ever on a communicator a captured graph still references).
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        os._exit(0)
     for w in weights:
         w.free()
     ctx.close()
-    if world > 1:
-        dist.destroy_process_group()
 
 
 def main():
