@@ -33,6 +33,7 @@ struct b2w4_ctx {
     uint64_t launches = 0;
     bool pdl = true;  // programmatic dependent launch between consecutive kernels
     int gemv_max_rows = 4;  // activation rows up to which the dp4a GEMV is used
+    int gemv_tpc_override = 0;  // tuning: cap on 8-row tiles per GEMV CTA (0 = heuristic)
     char err[512] = {0};
     // grow-only scratch (quantised activations, MoE work lists, staging)
     void* scratch[8] = {nullptr};

@@ -60,6 +60,9 @@ int b2w4_ctx_create(int device, b2w4_ctx** out) {
     ctx->sm_count = prop.multiProcessorCount;
     const char* pdl = getenv("B2W4_PDL");
     ctx->pdl = !(pdl && pdl[0] == '0');
+    const char* tpc = getenv("B2W4_GEMV_TPC");  // tuning: cap on tiles per GEMV CTA
+    if (tpc && atoi(tpc) > 0)
+        ctx->gemv_tpc_override = atoi(tpc);
     const char* gmr = getenv("B2W4_GEMV_MAX_ROWS");  // tuning/debug: rows kept on the GEMV
     if (gmr && atoi(gmr) > 0)
         ctx->gemv_max_rows = atoi(gmr);

@@ -391,16 +391,18 @@ int b2w4_launch_gemv(b2w4_ctx* ctx, const b2w4_weight* w, const float* x, int ld
         a.activation = activation;
         a.act_n_begin = act_n_begin;
         a.act_n_len = act_n_len;
-        // Tiles per CTA: a CTA's shared memory stays under ~108 KB so that two CTAs (this
+        // Tiles per CTA: a CTA's shared memory stays under ~100 KB so that two CTAs (this
         // launch's and the next one's) share an SM; when one wave of CTAs (tiles / SMs,
         // rounded up) fits that, use it, so that no SM runs the math of two CTAs of one
         // launch.
         const int per_tile = w->groups * (512 + (scl16 ? 16 : 32)) +
                              4 * gemv_d_stride(mt, w->groups, a32);
-        const int budget = 108 * 1024 - mt * w->k - 4 * mt * w->groups * spg - 1024;
+        const int budget = 100 * 1024 - mt * w->k - 4 * mt * w->groups * spg - 1024;
         int tpc = max(1, min(budget / per_tile, kMaxTpc));
         const int one_wave = (w->tiles + ctx->sm_count - 1) / ctx->sm_count;
         tpc = min(tpc, max(1, one_wave));
+        if (ctx->gemv_tpc_override > 0)
+            tpc = min(tpc, ctx->gemv_tpc_override);
         a.tpc = tpc;
         a.d_stride = gemv_d_stride(mt, w->groups, a32);
         const size_t smem = gemv_smem_bytes(mt, w->k, w->groups, tpc, scl16, a32);
