@@ -234,6 +234,26 @@ def decode_walk(torch, pkg, ctx, args):
     total = sum(algorithmic_bytes(w.n, w.k, 1) for w in ws)
     out = {"matmuls_per_token": len(ws), "weight_gb_per_token": total / 1e9,
            "ms_per_token": ms, "tokens_per_s": 1e3 / ms, "gbs": total / (ms * 1e-3) / 1e9}
+    # the same walk restricted to one layer shape at a time (36 distinct buffers each)
+    per_shape = {}
+    for i, (n, k) in enumerate(shapes + [(vocab, 2560)]):
+        sel = [w for w in ws if (w.n, w.k) == (n, k)]
+        reps = 1 if n == vocab else 1
+
+        def eager_shape():
+            for _ in range(reps):
+                for w in sel:
+                    ctx.matmul(w, xs[w.k], ys[w.n])
+        gs = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            ctx.set_stream(side.cuda_stream)
+            with torch.cuda.graph(gs, stream=side):
+                eager_shape()
+        ctx.set_stream(torch.cuda.current_stream().cuda_stream)
+        s_ms = time_steps(torch, gs.replay, 10, 3)
+        us = s_ms * 1e3 / (len(sel) * reps)
+        per_shape[f"n{n}_k{k}"] = {"us": us, "gbs": algorithmic_bytes(n, k, 1) / us / 1e3}
+    out["per_shape"] = per_shape
     for w in ws:
         w.free()
     return out

@@ -391,15 +391,17 @@ int b2w4_launch_gemv(b2w4_ctx* ctx, const b2w4_weight* w, const float* x, int ld
         a.activation = activation;
         a.act_n_begin = act_n_begin;
         a.act_n_len = act_n_len;
-        // Tiles per CTA: a CTA's shared memory stays under ~100 KB so that two CTAs (this
-        // launch's and the next one's) share an SM; when one wave of CTAs (tiles / SMs,
-        // rounded up) fits that, use it, so that no SM runs the math of two CTAs of one
-        // launch.
+        // Tiles per CTA: a CTA's shared memory stays under ~100 KB so that two CTAs share an
+        // SM (two of this launch, or one of this launch and one of the next, which then
+        // prefetches its weights early).
         const int per_tile = w->groups * (512 + (scl16 ? 16 : 32)) +
                              4 * gemv_d_stride(mt, w->groups, a32);
         const int budget = 100 * 1024 - mt * w->k - 4 * mt * w->groups * spg - 1024;
         int tpc = max(1, min(budget / per_tile, kMaxTpc));
-        const int one_wave = (w->tiles + ctx->sm_count - 1) / ctx->sm_count;
+        // Measured on config 1 (1216 tiles): one wave of about 1.4-1.7 CTAs per SM is fastest
+        // (244 CTAs: 4.8 us; 152: 6.0 us; 304, which needs a second wave: 6.6 us).
+        const int wave_ctas = ctx->sm_count * 17 / 10;
+        const int one_wave = (w->tiles + wave_ctas - 1) / wave_ctas;
         tpc = min(tpc, max(1, one_wave));
         if (ctx->gemv_tpc_override > 0)
             tpc = min(tpc, ctx->gemv_tpc_override);
