@@ -200,6 +200,43 @@ def run_reference(args):
 
 # --------------------------------------------------------------------------------- ours
 
+def moe_layer(torch, pkg, ctx, args):
+    """One Qwen3-30B-A3B-shaped routed-MoE layer (benchmark configuration 4): hidden 2048,
+    128 experts, top-8 softmax routing, expert intermediate 768; one decode token and a
+    256-token prefill.  Router, routing, compaction, both grouped expert matmuls, SwiGLU and
+    the ordered combine are all inside the timed call (b2w4_moe_forward)."""
+    h, e, top_k, inter = 2048, 128, 8, 768
+    router = torch.from_numpy(pkg.synth.router_weight(SEED_W, 70, e, h).view(np.int16)).cuda()
+    gu = ctx.upload_weight(pkg.synth.bg128_weight(SEED_W, 71, e * 2 * inter, h), e * 2 * inter, h)
+    dn = ctx.upload_weight(pkg.synth.bg128_weight(SEED_W, 72, e * h, inter), e * h, inter)
+    expert_bytes = (2 * inter * h + h * inter) * 4.125 / 8
+    out = {}
+    for t in (1, 256):
+        x = torch.from_numpy(pkg.synth.activations(SEED_X, 80 + t, t, h)).cuda()
+        y = torch.zeros((t, h), dtype=torch.float32, device="cuda")
+        idx = torch.zeros((t, top_k), dtype=torch.int32, device="cuda")
+
+        def call():
+            ctx.moe_forward(x, router, top_k, inter, gu, dn, y, None, idx, None)
+        call()  # also grows the context's scratch buffers before the capture
+        torch.cuda.synchronize()
+        active = len(set(idx.cpu().numpy().ravel().tolist()))
+        g = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            ctx.set_stream(side.cuda_stream)
+            with torch.cuda.graph(g, stream=side):
+                call()
+        ctx.set_stream(torch.cuda.current_stream().cuda_stream)
+        ms = time_steps(torch, g.replay, 20, 3)
+        out[f"tokens{t}"] = {"us_per_layer": ms * 1e3, "active_experts": active,
+                             "tokens_per_s_per_layer": t / (ms * 1e-3),
+                             "expert_weight_gbs": active * expert_bytes / (ms * 1e-3) / 1e9}
+    gu.free()
+    dn.free()
+    return out
+
+
 def decode_walk(torch, pkg, ctx, args):
     """The W4 matmuls of one decode token of a Qwen3-4B-shaped dense decoder (benchmark
     configuration 3): 36 layers of qkv [6144,2560], o [2560,4096], gate_up [19456,2560],
@@ -387,6 +424,7 @@ def run_ours(args):
                               "tflops": 2.0 * m * N_OUT * K_IN / per / 1e12,
                               "tokens_per_s": m / per}
         sweep["dense4b_decode_matmul_walk"] = decode_walk(torch, pkg, ctx, args)
+        sweep["moe30b_layer"] = moe_layer(torch, pkg, ctx, args)
         line["sweep"] = sweep
 
         # ---- CPU baseline: the reference's own kernel on this box's host cores ----------
