@@ -163,14 +163,15 @@ constexpr int kBStages = 3; // unpacked-weight (B operand) ring
 // blocks of 128 per CTA: one block leaves room for a deeper activation ring.
 template <int RP, int NB>
 struct Smem {
-    static constexpr int kAStages = NB == 2 ? 3 : 6;
+    static constexpr int kAStages = NB == 2 ? 3 : 4;
+    static constexpr int kRawSlots = NB == 2 ? 2 : 4;    // nibble chunks in flight
     static constexpr int kActStage = NB * 128 * 128;        // NB token blocks of 128 x 128 B
     static constexpr int kBStage = RP * 128;                // int8 weights, swizzled
     static constexpr int kRawSlot = (RP / 8) * kGC * 512;   // nibbles: [tile][kGC][512]
     static constexpr int kActOff = 0;
     static constexpr int kBOff = kActOff + kAStages * kActStage;
     static constexpr int kRawOff = kBOff + kBStages * kBStage;
-    static constexpr int kWsOff = kRawOff + 2 * kRawSlot;   // fp32 [G][RP], G <= kMaxG
+    static constexpr int kWsOff = kRawOff + kRawSlots * kRawSlot;  // fp32 [G][RP], G <= kMaxG
     static constexpr int kMaxG = 80;  // K <= 10240
     static constexpr int kBarOff = kWsOff + kMaxG * RP * 4;
     static constexpr int kTotal = kBarOff + 512 + 1024;  // barriers, + slack to align the base
@@ -180,11 +181,16 @@ template <int RP, int NB, bool SCL16>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_w4a8_tc_kernel(const GemmArgs a) {
     constexpr int kAStages = Smem<RP, NB>::kAStages;
+    constexpr int kRawSlots = Smem<RP, NB>::kRawSlots;
     constexpr int CH = RP / 2;  // accumulator columns per epilogue thread
     // TMEM holds kAcc group accumulators of NB*RP columns each (512 columns in all), so
     // the MMAs run up to kAcc-1 groups ahead of the fp32 chain
     constexpr int kAcc = 512 / (NB * RP) > 6 ? 6 : 512 / (NB * RP);
     constexpr int kAccCols = NB * RP;
+    // With one token block only two of the four epilogue warpgroups have accumulator rows;
+    // the other two unpack weights instead (the unpack stage bounds the pipeline there).
+    constexpr int kEpiActive = NB == 2 ? kEpiWarps : kEpiWarps / 2;
+    constexpr int kUnpackAll = kUnpackWarps + (kEpiWarps - kEpiActive);
     extern __shared__ uint8_t smem_raw[];
     // swizzle atoms need a 1024-byte aligned base
     uint8_t* smem = smem_raw + ((1024 - (smem_u32(smem_raw) & 1023)) & 1023);
@@ -203,9 +209,9 @@ gemm_w4a8_tc_kernel(const GemmArgs a) {
     uint64_t* act_free = act_full + kAStages;   // [kAStages] MMAs that read them retired
     uint64_t* b_full = act_free + kAStages;     // [kBStages] unpack done
     uint64_t* b_free = b_full + kBStages;       // [kBStages] MMAs that read it retired
-    uint64_t* raw_full = b_free + kBStages;     // [2] nibble chunk landed
-    uint64_t* raw_free = raw_full + 2;          // [2] unpack warps are done with it
-    uint64_t* acc_full = raw_free + 2;          // [kAcc] group accumulator complete
+    uint64_t* raw_full = b_free + kBStages;     // [kRawSlots] nibble chunk landed
+    uint64_t* raw_free = raw_full + kRawSlots;  // [kRawSlots] unpack warps are done with it
+    uint64_t* acc_full = raw_free + kRawSlots;          // [kAcc] group accumulator complete
     uint64_t* acc_free = acc_full + kAcc;       // [kAcc] epilogue has read it
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_free + kAcc);
     volatile int* s_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -216,16 +222,16 @@ gemm_w4a8_tc_kernel(const GemmArgs a) {
             mbar_init(&act_free[s], 1);
         }
         for (int s = 0; s < kBStages; ++s) {
-            mbar_init(&b_full[s], kUnpackWarps);
+            mbar_init(&b_full[s], kUnpackAll);
             mbar_init(&b_free[s], 1);
         }
-        for (int b = 0; b < 2; ++b) {
+        for (int b = 0; b < kRawSlots; ++b) {
             mbar_init(&raw_full[b], 1);
-            mbar_init(&raw_free[b], kUnpackWarps);
+            mbar_init(&raw_free[b], kUnpackAll);
         }
         for (int b = 0; b < kAcc; ++b) {
             mbar_init(&acc_full[b], 1);
-            mbar_init(&acc_free[b], kEpiWarps);  // every epilogue warp arrives, busy or not
+            mbar_init(&acc_free[b], kEpiActive);
         }
         *s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -252,7 +258,7 @@ gemm_w4a8_tc_kernel(const GemmArgs a) {
         bool ok = true;
         for (int g = 0; g < G; ++g) {
             if (g % kGC == 0) {
-                const int chunk = g / kGC, slot = chunk & 1, use = chunk >> 1;
+                const int chunk = g / kGC, slot = chunk % kRawSlots, use = chunk / kRawSlots;
                 const int gc = min(kGC, G - g);
                 if (use > 0 && !mbar_wait(&raw_free[slot], (use - 1) & 1))
                     ok = false;
@@ -315,11 +321,14 @@ gemm_w4a8_tc_kernel(const GemmArgs a) {
                 umma_commit(&acc_full[b]);   // the group's sums are complete
             }
         }
-    } else if (warp < kEpiWarp0) {
+    } else if (warp < kEpiWarp0 || warp >= kEpiWarp0 + kEpiActive) {
         // =============================== unpack ======================================
-        const int ut = (warp - kUnpackWarp0) * 32 + lane;  // 0..127
+        const int uw = warp < kEpiWarp0 ? warp - kUnpackWarp0
+                                        : kUnpackWarps + (warp - kEpiWarp0 - kEpiActive);
+        const int ut = uw * 32 + lane;
         for (int g = 0; g < G; ++g) {
-            const int chunk = g / kGC, slot = chunk & 1, cuse = chunk >> 1, gi = g % kGC;
+            const int chunk = g / kGC, slot = chunk % kRawSlots, cuse = chunk / kRawSlots;
+            const int gi = g % kGC;
             const int sb = g % kBStages, rb = g / kBStages;
             bool ok = !*s_abort;
             if (ok && gi == 0)
@@ -336,7 +345,7 @@ gemm_w4a8_tc_kernel(const GemmArgs a) {
                 reinterpret_cast<const uint4*>(smem + S::kRawOff + slot * S::kRawSlot) + gi * 32;
             uint8_t* bst = smem + S::kBOff + sb * S::kBStage;
             // chunk c of tile t: sub = c/8, row = c%8 -> 32 k of weight row t*8+row
-            for (int c = ut; c < r_tiles * 32; c += kUnpackWarps * 32) {
+            for (int c = ut; c < r_tiles * 32; c += kUnpackAll * 32) {
                 const int t = c >> 5, sub = (c >> 3) & 3, row = c & 7;
                 const uint4 w = raw[t * (kGC * 32) + (c & 31)];
                 // low nibbles = even k, high nibbles = odd k; a nibble with bit 3 set is
@@ -385,7 +394,7 @@ gemm_w4a8_tc_kernel(const GemmArgs a) {
         {
             float* wsf = reinterpret_cast<float*>(smem + S::kWsOff);
             const int et = ew * 32 + lane;
-            for (int i = et; i < G * RP; i += kEpiWarps * 32) {
+            for (int i = et; i < G * RP; i += kEpiActive * 32) {
                 const int g = i / RP, c = i - g * RP;
                 float v = 0.f;
                 if (c < r_tiles * 8) {
@@ -397,15 +406,22 @@ gemm_w4a8_tc_kernel(const GemmArgs a) {
             }
         }
         // named barrier among the epilogue warps only
-        asm volatile("bar.sync 1, %0;" ::"n"(kEpiWarps * 32) : "memory");
+        asm volatile("bar.sync 1, %0;" ::"n"(kEpiActive * 32) : "memory");
         const float* wsf = reinterpret_cast<const float*>(smem + S::kWsOff) + ch * CH;
         const bool has_tok = active && tok < a.m;
-        float a_next = has_tok ? a.as[tok] : 0.f;  // group 0; later groups one ahead
+        // the token's activation scales are fetched four groups ahead: a global load takes
+        // about as long as a whole group, so a shorter distance would pace the loop
+        auto load_as = [&](int g) {
+            return (has_tok && g < G) ? a.as[(size_t)g * a.m_pad + tok] : 0.f;
+        };
+        float a0 = load_as(0), a1 = load_as(1), a2 = load_as(2), a3 = load_as(3);
         for (int g = 0; g < G; ++g) {
             const int b = g % kAcc, use = g / kAcc;
-            const float a_s = a_next;
-            if (g + 1 < G && has_tok)
-                a_next = a.as[(size_t)(g + 1) * a.m_pad + tok];
+            const float a_s = a0;
+            a0 = a1;
+            a1 = a2;
+            a2 = a3;
+            a3 = load_as(g + 4);
             if (*s_abort || !mbar_wait(&acc_full[b], use & 1)) {
                 if (lane == 0)
                     fail();
@@ -415,22 +431,32 @@ gemm_w4a8_tc_kernel(const GemmArgs a) {
             if (active) {
                 const uint32_t taddr = tmem_base + ((uint32_t)(lq * 32) << 16) +
                                        (uint32_t)(b * kAccCols + mb * RP + ch * CH);
+                // columns are requested in batches of up to 24 before one wait: the TMEM read
+                // latency is paid once or twice per group, not once per 8 columns
+                constexpr int kBatch = 24;
 #pragma unroll
-                for (int c0 = 0; c0 < CH; c0 += 8) {
-                    uint32_t r[8];
-                    tmem_ld8(taddr + c0, r);
+                for (int b0 = 0; b0 < CH; b0 += kBatch) {
+                    constexpr int kMaxB = kBatch;
+                    uint32_t r[kMaxB];
+#pragma unroll
+                    for (int c0 = 0; c0 < kMaxB; c0 += 8)
+                        if (b0 + c0 < CH)
+                            tmem_ld8(taddr + b0 + c0, *reinterpret_cast<uint32_t(*)[8]>(&r[c0]));
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-                    for (int i = 0; i < 8; i += 4) {
-                        const float4 w4 = *reinterpret_cast<const float4*>(wsf + g * RP + c0 + i);
-                        acc[c0 + i + 0] = __fmaf_rn(int_to_float_exact((int)r[i + 0]),
-                                                    __fmul_rn(w4.x, a_s), acc[c0 + i + 0]);
-                        acc[c0 + i + 1] = __fmaf_rn(int_to_float_exact((int)r[i + 1]),
-                                                    __fmul_rn(w4.y, a_s), acc[c0 + i + 1]);
-                        acc[c0 + i + 2] = __fmaf_rn(int_to_float_exact((int)r[i + 2]),
-                                                    __fmul_rn(w4.z, a_s), acc[c0 + i + 2]);
-                        acc[c0 + i + 3] = __fmaf_rn(int_to_float_exact((int)r[i + 3]),
-                                                    __fmul_rn(w4.w, a_s), acc[c0 + i + 3]);
+                    for (int c = 0; c < kMaxB; c += 4) {
+                        if (b0 + c < CH) {
+                            const float4 w4 =
+                                *reinterpret_cast<const float4*>(wsf + g * RP + b0 + c);
+                            acc[b0 + c + 0] = __fmaf_rn(int_to_float_exact((int)r[c + 0]),
+                                                        __fmul_rn(w4.x, a_s), acc[b0 + c + 0]);
+                            acc[b0 + c + 1] = __fmaf_rn(int_to_float_exact((int)r[c + 1]),
+                                                        __fmul_rn(w4.y, a_s), acc[b0 + c + 1]);
+                            acc[b0 + c + 2] = __fmaf_rn(int_to_float_exact((int)r[c + 2]),
+                                                        __fmul_rn(w4.z, a_s), acc[b0 + c + 2]);
+                            acc[b0 + c + 3] = __fmaf_rn(int_to_float_exact((int)r[c + 3]),
+                                                        __fmul_rn(w4.w, a_s), acc[b0 + c + 3]);
+                        }
                     }
                 }
             }
