@@ -26,9 +26,10 @@
 // 32 dp4a with no cross-lane reduction.  Nibbles stay left-aligned in their bytes
 // ((w<<4)&0xF0F0F0F0 = even k, w&0xF0F0F0F0 = odd k, i.e. 16*q4 as int8); the int32 sum is
 // an exact multiple of 16 and is shifted back before conversion, like the NEON kernel's
-// sdot + fixed-point convert.  The exact integer sums go to shared memory.
+// sdot + fixed-point convert.  The integer sum (as a float: exact) and the scale product
+// fp32(ws*as) go to shared memory.
 // Phase 2, after one barrier: one thread per (tile, weight row, activation row) runs the
-// order-sensitive fp32 chain over the groups in ascending order.
+// order-sensitive chain of fused multiply-adds over the groups in ascending order.
 #include "b200w4_internal.cuh"
 
 namespace {
@@ -124,9 +125,12 @@ gemv_w4a8_kernel(const GemvArgs a) {
     uint8_t* s_scl = s_w + (size_t)a.tpc * tile_bytes;     // [tpc][G][8] fp16|fp32
     uint4* s_qa = reinterpret_cast<uint4*>(s_scl + (size_t)a.tpc * scl_tile_bytes);  // [MT][K]
     float* s_as = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(s_qa) + (size_t)MT * K);
-    int32_t* s_d = reinterpret_cast<int32_t*>(s_as + MT * G * SPG);  // [tpc][G][SPG][MT][8]+pad
+    // per (tile, group, [32-block], activation row, weight row): the integer sum as a float
+    // (exact: |sum| < 2^24) and the scale product it is multiplied with
+    float* s_d = s_as + MT * G * SPG;                      // [tpc][G][SPG][MT][8] + pad
+    float* s_sc = s_d + (size_t)a.tpc * a.d_stride;        // same shape
     uint64_t* s_bar = reinterpret_cast<uint64_t*>(
-        (reinterpret_cast<uintptr_t>(s_d + (size_t)a.tpc * a.d_stride) + 7) & ~uintptr_t(7));
+        (reinterpret_cast<uintptr_t>(s_sc + (size_t)a.tpc * a.d_stride) + 7) & ~uintptr_t(7));
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int gl = lane >> 3, row = lane & 7;
@@ -213,9 +217,9 @@ gemv_w4a8_kernel(const GemvArgs a) {
     // ---- phase 1: integer group sums ---------------------------------------------------
     const int ipt = (G + 3) >> 2;
     const int n_items = ntile * ipt;
-    bool timed_out = false;
+    bool timed_out = !mbar_wait_bounded(&s_bar[ntile]);  // weight scales
 #pragma unroll 1
-    for (int it = warp; it < n_items; it += kWarps) {
+    for (int it = warp; it < n_items && !timed_out; it += kWarps) {
         const int tl = it / ipt;
         const int g = (it - tl * ipt) * 4 + gl;
         if (!mbar_wait_bounded(&s_bar[tl])) {
@@ -238,7 +242,12 @@ gemv_w4a8_kernel(const GemvArgs a) {
                 we[s * 4 + 3] = (w.w << 4) & 0xF0F0F0F0u;
                 wo[s * 4 + 3] = w.w & 0xF0F0F0F0u;
             }
-            int32_t* dst = s_d + (size_t)tl * a.d_stride + (size_t)g * SPG * MT * 8 + row;
+            const size_t slot = (size_t)tl * a.d_stride + (size_t)g * SPG * MT * 8 + row;
+            float* dst = s_d + slot;
+            float* dsc = s_sc + slot;
+            const float ws =
+                SCL16 ? __half2float(reinterpret_cast<const __half*>(s_scl)[(tl * G + g) * 8 + row])
+                      : reinterpret_cast<const float*>(s_scl)[(tl * G + g) * 8 + row];
 #pragma unroll
             for (int mi = 0; mi < MT; ++mi) {
                 if (mi < a.m) {
@@ -256,13 +265,18 @@ gemv_w4a8_kernel(const GemvArgs a) {
                         q = __dp4a((int)wo[s * 4 + 2], (int)ao.z, q);
                         p = __dp4a((int)we[s * 4 + 3], (int)ae.w, p);
                         q = __dp4a((int)wo[s * 4 + 3], (int)ao.w, q);
-                        if (A32)
-                            dst[(s * MT + mi) * 8] = (p + q) >> 4;  // exact: multiple of 16
-                        else
+                        if (A32) {
+                            dst[(s * MT + mi) * 8] = (float)((p + q) >> 4);  // multiple of 16
+                            dsc[(s * MT + mi) * 8] =
+                                __fmul_rn(ws, s_as[mi * G * 4 + g * 4 + s]);
+                        } else {
                             total += p + q;
+                        }
                     }
-                    if (!A32)
-                        dst[mi * 8] = total >> 4;
+                    if (!A32) {
+                        dst[mi * 8] = (float)(total >> 4);
+                        dsc[mi * 8] = __fmul_rn(ws, s_as[mi * G + g]);
+                    }
                 }
             }
         }
@@ -270,11 +284,6 @@ gemv_w4a8_kernel(const GemvArgs a) {
     if (timed_out && lane == 0)
         atomicExch(a.status, B2W4_E_TIMEOUT);
     __syncthreads();
-    if (!mbar_wait_bounded(&s_bar[ntile])) {  // weight scales
-        if (lane == 0)
-            atomicExch(a.status, B2W4_E_TIMEOUT);
-        return;
-    }
 
     // ---- phase 2: fp32 chain, one thread per (tile, activation row, weight row) ---------
 #pragma unroll 1
@@ -283,21 +292,16 @@ gemv_w4a8_kernel(const GemvArgs a) {
         if (mi >= a.m)
             continue;
         const int n = (tile0 + tl) * 8 + rr;
-        const int32_t* dsrc = s_d + (size_t)tl * a.d_stride + mi * 8 + rr;
-        const float* as = s_as + mi * G * SPG;
+        const float* dsrc = s_d + (size_t)tl * a.d_stride + mi * 8 + rr;
+        const float* csrc = s_sc + (size_t)tl * a.d_stride + mi * 8 + rr;
         float acc = 0.f;
+        // only the fused multiply-add depends on the previous step; the loads do not
 #pragma unroll 4
-        for (int g = 0; g < G; ++g) {
-            const float ws =
-                SCL16 ? __half2float(reinterpret_cast<const __half*>(s_scl)[(tl * G + g) * 8 + rr])
-                      : reinterpret_cast<const float*>(s_scl)[(tl * G + g) * 8 + rr];
-#pragma unroll
-            for (int s = 0; s < SPG; ++s) {
-                const int dv = dsrc[(g * SPG + s) * MT * 8];
-                acc = __fmaf_rn((float)dv, __fmul_rn(ws, as[g * SPG + s]), acc);
-                if (SUMS && n < a.n)
-                    a.sums[((size_t)mi * a.n + n) * (G * SPG) + g * SPG + s] = dv;
-            }
+        for (int j = 0; j < G * SPG; ++j) {
+            const float dv = dsrc[j * MT * 8];
+            acc = __fmaf_rn(dv, csrc[j * MT * 8], acc);
+            if (SUMS && n < a.n)
+                a.sums[((size_t)mi * a.n + n) * (G * SPG) + j] = (int)dv;
         }
         if (n < a.n) {
             if (b2w4_act_applies(n, a.activation, a.act_n_begin, a.act_n_len, a.n))
@@ -317,7 +321,7 @@ size_t gemv_smem_bytes(int mt, int k, int groups, int tpc, bool scl16, bool a32)
     const int spg = a32 ? 4 : 1;
     return (size_t)tpc * groups * 512 + (size_t)tpc * groups * 8 * (scl16 ? 2 : 4) +
            (size_t)mt * k + sizeof(float) * mt * groups * spg +
-           sizeof(int32_t) * (size_t)tpc * gemv_d_stride(mt, groups, a32) + 8 +
+           2 * sizeof(float) * (size_t)tpc * gemv_d_stride(mt, groups, a32) + 8 +
            sizeof(uint64_t) * (tpc + 1);
 }
 
@@ -395,7 +399,7 @@ int b2w4_launch_gemv(b2w4_ctx* ctx, const b2w4_weight* w, const float* x, int ld
         // SM (two of this launch, or one of this launch and one of the next, which then
         // prefetches its weights early).
         const int per_tile = w->groups * (512 + (scl16 ? 16 : 32)) +
-                             4 * gemv_d_stride(mt, w->groups, a32);
+                             8 * gemv_d_stride(mt, w->groups, a32);
         const int budget = 100 * 1024 - mt * w->k - 4 * mt * w->groups * spg - 1024;
         int tpc = max(1, min(budget / per_tile, kMaxTpc));
         // Measured on config 1 (1216 tiles): one wave of about 1.4-1.7 CTAs per SM is fastest
