@@ -150,6 +150,31 @@ int b2w4_moe_select_routes(b2w4_ctx* ctx, const float* logits_dev, int tokens,
                            int num_experts, int top_k, int32_t* indices_dev,
                            float* weights_dev);
 
+/* ---- expert-parallel MoE ---------------------------------------------------
+ * No counterpart in the reference, which runs one process on one device; the op
+ * is kernel_qwen3_moe (kernels/moe.cpp:576-1129) split at the point where the
+ * experts' outputs meet.  Rank r of P holds the aggregates of experts
+ * [expert_begin, expert_begin+expert_count) only (gate_up_local
+ * [expert_count*2I, H], down_local [expert_count*H, I]); hidden and the router
+ * weight are replicated, so every rank derives the same routes without an
+ * exchange.  b2w4_moe_expert_outputs writes route_out fp32 [tokens*top_k][H]:
+ * row t*top_k+j is the down-projection output of token t's j-th route when its
+ * expert is held here, zeros otherwise, and indices / weights [tokens][top_k]
+ * as b2w4_moe_forward does.  The caller sums route_out over the ranks (an
+ * all-reduce: each row has one owner, the sum adds only zeros and changes no
+ * bit) and calls b2w4_moe_combine, which applies out[t] = fma(w, y, out[t])
+ * over the token's routes in ascending expert id (kernels/moe.cpp:1100-1110):
+ * the result equals b2w4_moe_forward's bit for bit. */
+int b2w4_moe_expert_outputs(b2w4_ctx* ctx, const float* hidden_dev, int ldx, int tokens,
+                            int hidden_size, const void* router_fp16_dev, int num_experts,
+                            int top_k, int intermediate, const b2w4_weight* gate_up_local,
+                            const b2w4_weight* down_local, int expert_begin,
+                            int expert_count, float* route_out_dev, int32_t* indices_dev,
+                            float* weights_dev);
+int b2w4_moe_combine(b2w4_ctx* ctx, const float* route_out_dev, int tokens, int hidden_size,
+                     int top_k, const int32_t* indices_dev, const float* weights_dev,
+                     float* out_dev, int ldo);
+
 /* Launch counter: how many of this library's kernels have been launched on the
  * context since creation (for benchmark bookkeeping). */
 uint64_t b2w4_kernel_launches(const b2w4_ctx* ctx);

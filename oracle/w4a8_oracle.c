@@ -475,3 +475,27 @@ int orc_moe_forward(const float* hidden, int tokens, int hidden_size, int ldx,
     free(route_weights);
     return rc;
 }
+
+void orc_moe_combine(const float* route_out, int tokens, int hidden_size, int top_k,
+                     const int32_t* indices, const float* weights, float* out, int ldo) {
+    for (int t = 0; t < tokens; ++t) {
+        float* dst = out + (size_t)t * ldo;
+        const int32_t* idx = indices + (size_t)t * top_k;
+        memset(dst, 0, sizeof(float) * (size_t)hidden_size);
+        /* visit the routes by ascending expert id; a token's experts are distinct */
+        int last = -1;
+        for (int step = 0; step < top_k; ++step) {
+            int best = -1;
+            for (int j = 0; j < top_k; ++j)
+                if (idx[j] > last && (best < 0 || idx[j] < idx[best]))
+                    best = j;
+            if (best < 0)
+                break;
+            last = idx[best];
+            const float* src = route_out + ((size_t)t * top_k + best) * hidden_size;
+            float w = weights[(size_t)t * top_k + best];
+            for (int d = 0; d < hidden_size; ++d)
+                dst[d] = fmaf(w, src[d], dst[d]);
+        }
+    }
+}

@@ -80,6 +80,14 @@ int orc_moe_forward(const float* hidden, int tokens, int hidden_size, int ldx,
                     int expert_rule, float* logits_out, int32_t* indices_out,
                     float* weights_out);
 
+/* The combine step of kernel_qwen3_moe alone (kernels/moe.cpp:642-645, :966,
+ * :1100-1110): out[t] starts at 0 and takes fmaf(w, y, out[t]) for the token's
+ * routes in ascending expert id (the order the expert loop visits them).
+ * route_out fp32 [tokens*top_k][H], row t*top_k+j = the j-th route's expert
+ * output.  Used to check the expert-parallel split of the op. */
+void orc_moe_combine(const float* route_out, int tokens, int hidden_size, int top_k,
+                     const int32_t* indices, const float* weights, float* out, int ldo);
+
 float orc_fp16_to_fp32(uint16_t h);
 
 #ifdef __cplusplus

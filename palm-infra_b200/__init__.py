@@ -4,10 +4,11 @@
   capi.py    ctypes binding of that C ABI (tests, bench)
   synth.py   seeded synthetic weights / activations of the benchmark shapes
   shard.py   tensor-parallel (row) and expert-parallel sharding of weights across ranks
+  expert_parallel.py  routed MoE over ranks: local expert outputs, all-reduce, ordered combine
   build.py   in-tree nvcc build
 
 The directory name carries a hyphen, so load it with importlib (see __graft_entry__.py)
 under the module name `palm_infra_b200`.
 """
-from . import capi, shard, synth  # noqa: F401
+from . import capi, expert_parallel, shard, synth  # noqa: F401
 from .build import build as build_library  # noqa: F401

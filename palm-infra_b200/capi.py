@@ -21,7 +21,8 @@ SYMBOLS = [
     "b2w4_weight_stream_bytes", "b2w4_matmul", "b2w4_matmul_host",
     "b2w4_matmul_static_scratch",
     "b2w4_debug_group_sums", "b2w4_quantize_activations", "b2w4_moe_forward",
-    "b2w4_moe_select_routes", "b2w4_kernel_launches",
+    "b2w4_moe_select_routes", "b2w4_moe_expert_outputs", "b2w4_moe_combine",
+    "b2w4_kernel_launches",
 ]
 
 _lib = None
@@ -64,6 +65,9 @@ def lib():
         L.b2w4_moe_forward.argtypes = [vp, f_p, i, i, i, vp, i, i, i, vp, vp, f_p, i, f_p,
                                        vp, f_p]
         L.b2w4_moe_select_routes.argtypes = [vp, f_p, i, i, i, vp, f_p]
+        L.b2w4_moe_expert_outputs.argtypes = [vp, f_p, i, i, i, vp, i, i, i, vp, vp, i, i, f_p,
+                                              vp, f_p]
+        L.b2w4_moe_combine.argtypes = [vp, f_p, i, i, i, vp, f_p, f_p, i]
         L.b2w4_kernel_launches.argtypes = [vp]
         L.b2w4_kernel_launches.restype = C.c_uint64
         _lib = L
@@ -184,6 +188,22 @@ class Context:
             self.handle, _dptr(hidden), hidden.stride(0), t, h, _dptr(router_fp16), e, top_k,
             intermediate, gate_up.handle, down.handle, _dptr(out), out.stride(0),
             _dptr(logits), _dptr(indices), _dptr(weights)))
+
+    def moe_expert_outputs(self, hidden, router_fp16, top_k, intermediate, gate_up_local,
+                           down_local, expert_begin, expert_count, route_out, indices, weights):
+        """One rank's half of the expert-parallel MoE op: route_out [tokens*top_k, H]."""
+        t, h = hidden.shape
+        e = router_fp16.shape[0]
+        self._check(lib().b2w4_moe_expert_outputs(
+            self.handle, _dptr(hidden), hidden.stride(0), t, h, _dptr(router_fp16), e, top_k,
+            intermediate, gate_up_local.handle, down_local.handle, expert_begin, expert_count,
+            _dptr(route_out), _dptr(indices), _dptr(weights)))
+
+    def moe_combine(self, route_out, top_k, indices, weights, out):
+        t, h = out.shape
+        self._check(lib().b2w4_moe_combine(self.handle, _dptr(route_out), t, h, top_k,
+                                           _dptr(indices), _dptr(weights), _dptr(out),
+                                           out.stride(0)))
 
     def select_routes(self, logits, top_k, indices, weights):
         t, e = logits.shape

@@ -183,13 +183,18 @@ __global__ void moe_compact_kernel(const int32_t* __restrict__ idx, int tokens, 
 // (kernels/moe.cpp:160-183), then the per-128 quantiser; codes in even/odd order.
 __global__ void moe_swiglu_quant_kernel(const float* __restrict__ gu, int routes,
                                         int intermediate, int8_t* __restrict__ q,
-                                        float* __restrict__ scales) {
+                                        float* __restrict__ scales,
+                                        const int32_t* __restrict__ route_lo,
+                                        const int32_t* __restrict__ route_hi) {
     const int groups = intermediate >> 7;
     const long long wid = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
     if (wid >= (long long)routes * groups)
         return;
     const int r = (int)(wid / groups), g = (int)(wid % groups);
+    // expert-parallel runs only own the compact positions of their experts
+    if (route_lo && (r < *route_lo || r >= *route_hi))
+        return;
     const float* gp = gu + (size_t)r * 2 * intermediate + (size_t)g * 128 + lane * 4;
     const float* up = gp + intermediate;
     float v[4];
@@ -244,9 +249,30 @@ __global__ void moe_combine_kernel(const float* __restrict__ dn, const int32_t* 
     for (int j = 0; j < top_k; ++j) {
         const int r = order[j];
         const float w = weights[(size_t)t * top_k + r];
-        acc = __fmaf_rn(w, dn[(size_t)pos[(size_t)t * top_k + r] * hidden_size + d], acc);
+        const size_t row = pos ? (size_t)pos[(size_t)t * top_k + r] : (size_t)t * top_k + r;
+        acc = __fmaf_rn(w, dn[row * hidden_size + d], acc);
     }
     out[(size_t)t * ldo + d] = acc;
+}
+
+// ---- expert-parallel hand-over: route outputs in (token, route) order -------------------
+// Row t*top_k+j takes the down-projection output of token t's j-th route when that route's
+// expert is one of this rank's, zeros otherwise; summed over the ranks (each row has exactly
+// one owner, so the sum only adds zeros) the buffer holds every route's output.
+__global__ void moe_scatter_routes_kernel(const float* __restrict__ dn,
+                                          const int32_t* __restrict__ idx,
+                                          const int32_t* __restrict__ pos, int routes,
+                                          int hidden_size, int expert_begin, int expert_count,
+                                          float* __restrict__ route_out) {
+    const int r = blockIdx.y;
+    const int d = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (r >= routes || d >= hidden_size)
+        return;
+    const int e = idx[r] - expert_begin;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (e >= 0 && e < expert_count)
+        v = *reinterpret_cast<const float4*>(dn + (size_t)pos[r] * hidden_size + d);
+    *reinterpret_cast<float4*>(route_out + (size_t)r * hidden_size + d) = v;
 }
 
 // ---- 5 / 7. grouped expert GEMV over ragged route lists --------------------------------
@@ -479,25 +505,35 @@ int b2w4_moe_select_routes(b2w4_ctx* ctx, const float* logits_dev, int tokens,
     return B2W4_OK;
 }
 
-int b2w4_moe_forward(b2w4_ctx* ctx, const float* hidden_dev, int ldx, int tokens,
-                     int hidden_size, const void* router_fp16_dev, int num_experts, int top_k,
-                     int intermediate, const b2w4_weight* gate_up, const b2w4_weight* down,
-                     float* out_dev, int ldo, float* logits_dev, int32_t* indices_dev,
-                     float* weights_dev) {
+}  // extern "C"
+
+// The whole MoE op.  With route_out == nullptr it computes every expert and combines into
+// out_dev.  With route_out set it is one rank of an expert-parallel group: routing runs over
+// all num_experts (replicated), the aggregates hold experts [expert_begin, expert_begin +
+// expert_count) only, and the rank's route outputs go to route_out in (token, route) order.
+static int moe_run(b2w4_ctx* ctx, const float* hidden_dev, int ldx, int tokens, int hidden_size,
+                   const void* router_fp16_dev, int num_experts, int top_k, int intermediate,
+                   const b2w4_weight* gate_up, const b2w4_weight* down, int expert_begin,
+                   int expert_count, float* out_dev, int ldo, float* route_out,
+                   float* logits_dev, int32_t* indices_dev, float* weights_dev) {
     if (!ctx)
         return B2W4_E_INVALID;
-    if (!hidden_dev || !router_fp16_dev || !gate_up || !down || !out_dev)
+    if (!hidden_dev || !router_fp16_dev || !gate_up || !down || (!out_dev && !route_out))
         return b2w4_fail(ctx, B2W4_E_INVALID, "moe: null argument");
     if (tokens <= 0 || num_experts <= 0 || top_k <= 0 || top_k > num_experts ||
         top_k > kMaxTopK || hidden_size % 128 || intermediate % 128 || ldx < hidden_size ||
-        ldo < hidden_size)
+        (out_dev && ldo < hidden_size))
         return b2w4_fail(ctx, B2W4_E_INVALID,
                          "moe: bad shape tokens=%d hidden=%d experts=%d top_k=%d inter=%d",
                          tokens, hidden_size, num_experts, top_k, intermediate);
-    if (gate_up->k != hidden_size || gate_up->n != num_experts * 2 * intermediate ||
-        down->k != intermediate || down->n != num_experts * hidden_size)
+    if (expert_begin < 0 || expert_count <= 0 || expert_begin + expert_count > num_experts)
+        return b2w4_fail(ctx, B2W4_E_INVALID, "moe: experts [%d, %d) outside [0, %d)",
+                         expert_begin, expert_begin + expert_count, num_experts);
+    if (gate_up->k != hidden_size || gate_up->n != expert_count * 2 * intermediate ||
+        down->k != intermediate || down->n != expert_count * hidden_size)
         return b2w4_fail(ctx, B2W4_E_INVALID,
-                         "moe: expert aggregates must be gate_up [E*2I, H] and down [E*H, I]");
+                         "moe: expert aggregates must be gate_up [E*2I, H] and down [E*H, I] "
+                         "for the %d experts held", expert_count);
     const int routes = tokens * top_k;
     const int gh = hidden_size / 128, gi = intermediate / 128;
     // small routing state in one block
@@ -554,19 +590,30 @@ int b2w4_moe_forward(b2w4_ctx* ctx, const float* hidden_dev, int ldx, int tokens
     if ((rc = b2w4_launch_quantize(ctx, hidden_dev, ldx, tokens, hidden_size, B2W4_ACT_G128,
                                    q_hidden, as_hidden, QLAYOUT_EVEN_ODD)) != B2W4_OK)
         return rc;
-    if ((rc = launch_grouped(ctx, gate_up, num_experts, q_hidden, as_hidden, offsets,
+    // the grouped kernels index experts from the first one held; compact positions stay global
+    const int32_t* local_offsets = offsets + expert_begin;
+    const bool partial = expert_count != num_experts;
+    if ((rc = launch_grouped(ctx, gate_up, expert_count, q_hidden, as_hidden, local_offsets,
                              route_token, static_cast<float*>(gu))) != B2W4_OK)
         return rc;
     {
         const long long threads = (long long)routes * gi * 32;
         moe_swiglu_quant_kernel<<<(int)((threads + 255) / 256), 256, 0, st>>>(
-            static_cast<const float*>(gu), routes, intermediate, q_inter, as_inter);
+            static_cast<const float*>(gu), routes, intermediate, q_inter, as_inter,
+            partial ? local_offsets : nullptr, partial ? local_offsets + expert_count : nullptr);
         ctx->launches++;
     }
-    if ((rc = launch_grouped(ctx, down, num_experts, q_inter, as_inter, offsets, nullptr,
+    if ((rc = launch_grouped(ctx, down, expert_count, q_inter, as_inter, local_offsets, nullptr,
                              static_cast<float*>(dn))) != B2W4_OK)
         return rc;
-    {
+    if (route_out) {
+        dim3 grid((hidden_size / 4 + 255) / 256, routes);
+        moe_scatter_routes_kernel<<<grid, 256, 0, st>>>(static_cast<const float*>(dn), idx, pos,
+                                                        routes, hidden_size, expert_begin,
+                                                        expert_count, route_out);
+        ctx->launches++;
+    }
+    if (out_dev) {
         dim3 grid((hidden_size + 255) / 256, tokens);
         moe_combine_kernel<<<grid, 256, 0, st>>>(static_cast<const float*>(dn), idx, wts, pos,
                                                  tokens, top_k, hidden_size, out_dev, ldo);
@@ -583,6 +630,49 @@ int b2w4_moe_forward(b2w4_ctx* ctx, const float* hidden_dev, int ldx, int tokens
     if (weights_dev)
         B2W4_CUDA(ctx, cudaMemcpyAsync(weights_dev, wts, sizeof(float) * (size_t)routes,
                                        cudaMemcpyDeviceToDevice, st));
+    return B2W4_OK;
+}
+
+extern "C" {
+
+int b2w4_moe_forward(b2w4_ctx* ctx, const float* hidden_dev, int ldx, int tokens,
+                     int hidden_size, const void* router_fp16_dev, int num_experts, int top_k,
+                     int intermediate, const b2w4_weight* gate_up, const b2w4_weight* down,
+                     float* out_dev, int ldo, float* logits_dev, int32_t* indices_dev,
+                     float* weights_dev) {
+    if (ctx && !out_dev)
+        return b2w4_fail(ctx, B2W4_E_INVALID, "moe: null argument");
+    return moe_run(ctx, hidden_dev, ldx, tokens, hidden_size, router_fp16_dev, num_experts,
+                   top_k, intermediate, gate_up, down, 0, num_experts, out_dev, ldo, nullptr,
+                   logits_dev, indices_dev, weights_dev);
+}
+
+int b2w4_moe_expert_outputs(b2w4_ctx* ctx, const float* hidden_dev, int ldx, int tokens,
+                            int hidden_size, const void* router_fp16_dev, int num_experts,
+                            int top_k, int intermediate, const b2w4_weight* gate_up_local,
+                            const b2w4_weight* down_local, int expert_begin, int expert_count,
+                            float* route_out_dev, int32_t* indices_dev, float* weights_dev) {
+    if (ctx && (!route_out_dev || !indices_dev || !weights_dev))
+        return b2w4_fail(ctx, B2W4_E_INVALID, "moe: null argument");
+    return moe_run(ctx, hidden_dev, ldx, tokens, hidden_size, router_fp16_dev, num_experts,
+                   top_k, intermediate, gate_up_local, down_local, expert_begin, expert_count,
+                   nullptr, 0, route_out_dev, nullptr, indices_dev, weights_dev);
+}
+
+int b2w4_moe_combine(b2w4_ctx* ctx, const float* route_out_dev, int tokens, int hidden_size,
+                     int top_k, const int32_t* indices_dev, const float* weights_dev,
+                     float* out_dev, int ldo) {
+    if (!ctx)
+        return B2W4_E_INVALID;
+    if (!route_out_dev || !indices_dev || !weights_dev || !out_dev || tokens <= 0 ||
+        hidden_size <= 0 || top_k <= 0 || top_k > kMaxTopK || ldo < hidden_size)
+        return b2w4_fail(ctx, B2W4_E_INVALID, "moe_combine: bad argument");
+    dim3 grid((hidden_size + 255) / 256, tokens);
+    moe_combine_kernel<<<grid, 256, 0, ctx->stream>>>(route_out_dev, indices_dev, weights_dev,
+                                                      nullptr, tokens, top_k, hidden_size,
+                                                      out_dev, ldo);
+    ctx->launches++;
+    B2W4_CUDA(ctx, cudaGetLastError());
     return B2W4_OK;
 }
 

@@ -1,0 +1,93 @@
+"""Expert-parallel routed MoE: one process per GPU, experts split in contiguous blocks.
+
+The reference runs one process on one device (kernels/moe.cpp:576-1129); this is the same op
+cut where the experts' outputs meet.  Hidden states and the fp16 router weight are replicated,
+so every rank derives the same routes with no dispatch exchange.  Rank r computes the routes
+whose expert lies in [r*E/P, (r+1)*E/P) and writes their down-projection outputs into a
+[tokens*top_k, H] buffer that is zero everywhere else; one all-reduce (sum) completes the
+buffer on every rank -- each row has exactly one owner, so the sum adds only zeros and changes
+no bit -- and the ordered combine (fma in ascending expert id, kernels/moe.cpp:1100-1110) then
+gives the single-device result bit for bit.
+
+The exchange moves tokens*top_k*H fp32 per layer: 64 KiB for a Qwen3-30B decode token, 16 MiB
+for a 256-token prefill.
+"""
+import numpy as np
+
+from .shard import BLOCK_BYTES, expert_range
+
+
+def shard_expert_blocks(blocks, num_experts, rows_per_expert, k, rank, world):
+    """blocks: flat uint8 BG128 array of an expert aggregate [E*rows_per_expert, K] (expert e
+    owns rows e*rows_per_expert..., kernels/moe.cpp:1022-1027) -> (rank's blocks, first
+    expert, expert count).  Experts are whole multiples of 8 rows, so the rank's experts are
+    one contiguous byte range."""
+    if rows_per_expert % 8:
+        raise ValueError(f"rows per expert ({rows_per_expert}) must be a multiple of 8")
+    lo, hi = expert_range(num_experts, rank, world)
+    expert_bytes = (rows_per_expert // 8) * (k // 128) * BLOCK_BYTES
+    return blocks[lo * expert_bytes:hi * expert_bytes], lo, hi - lo
+
+
+class DeviceEngine:
+    """The two halves of the op on this rank's GPU, through the C ABI
+    (b2w4_moe_expert_outputs / b2w4_moe_combine)."""
+
+    def __init__(self, ctx, router_fp16, gate_up_local, down_local, top_k, intermediate,
+                 expert_begin, expert_count):
+        self.ctx, self.router = ctx, router_fp16
+        self.gate_up, self.down = gate_up_local, down_local
+        self.top_k, self.intermediate = top_k, intermediate
+        self.expert_begin, self.expert_count = expert_begin, expert_count
+        self._buf = {}
+
+    def _buffers(self, hidden):
+        import torch
+        t, h = hidden.shape
+        if t not in self._buf:
+            self._buf[t] = (
+                torch.empty((t * self.top_k, h), dtype=torch.float32, device=hidden.device),
+                torch.empty((t, self.top_k), dtype=torch.int32, device=hidden.device),
+                torch.empty((t, self.top_k), dtype=torch.float32, device=hidden.device))
+        return self._buf[t]
+
+    def expert_outputs(self, hidden):
+        route_out, idx, wts = self._buffers(hidden)
+        self.ctx.moe_expert_outputs(hidden, self.router, self.top_k, self.intermediate,
+                                    self.gate_up, self.down, self.expert_begin,
+                                    self.expert_count, route_out, idx, wts)
+        return route_out, idx, wts
+
+    def combine(self, route_out, idx, wts, out):
+        self.ctx.moe_combine(route_out, self.top_k, idx, wts, out)
+
+
+class ExpertParallelMoE:
+    """forward(hidden, out): expert outputs on this rank -> all-reduce -> ordered combine.
+
+    `engine` supplies the two compute halves (DeviceEngine on a GPU); `all_reduce` is the
+    collective on the route buffer (torch.distributed.all_reduce of the process group, issued
+    on the stream the engine's context runs on so the three steps stay stream-ordered)."""
+
+    def __init__(self, engine, all_reduce):
+        self.engine = engine
+        self.all_reduce = all_reduce
+
+    def forward(self, hidden, out):
+        route_out, idx, wts = self.engine.expert_outputs(hidden)
+        self.all_reduce(route_out)
+        self.engine.combine(route_out, idx, wts, out)
+        return out
+
+
+def build_device_moe(ctx, router_fp16, gate_up_blocks, down_blocks, num_experts, top_k,
+                     hidden_size, intermediate, rank, world, all_reduce):
+    """Shard the two expert aggregates for `rank`, upload them and return the op."""
+    gu, lo, cnt = shard_expert_blocks(gate_up_blocks, num_experts, 2 * intermediate,
+                                      hidden_size, rank, world)
+    dn, _, _ = shard_expert_blocks(down_blocks, num_experts, hidden_size, intermediate,
+                                   rank, world)
+    gate_up = ctx.upload_weight(np.ascontiguousarray(gu), cnt * 2 * intermediate, hidden_size)
+    down = ctx.upload_weight(np.ascontiguousarray(dn), cnt * hidden_size, intermediate)
+    engine = DeviceEngine(ctx, router_fp16, gate_up, down, top_k, intermediate, lo, cnt)
+    return ExpertParallelMoE(engine, all_reduce)

@@ -158,6 +158,51 @@ def moe_forward(hidden, router_fp16, top_k, intermediate, gate_up, down, rule=AC
     return out, logits, idx, w
 
 
+def router_logits(hidden, router_fp16):
+    hidden = np.ascontiguousarray(hidden, dtype=np.float32)
+    t, h = hidden.shape
+    e = router_fp16.shape[0]
+    router_fp16 = np.ascontiguousarray(router_fp16.view(np.uint16))
+    logits = np.zeros((t, e), dtype=np.float32)
+    oracle().orc_router_logits(_ptr(hidden), t, h, h, _ptr(router_fp16), e, _ptr(logits))
+    return logits
+
+
+def moe_combine(route_out, idx, w):
+    t, top_k = idx.shape
+    route_out = np.ascontiguousarray(route_out, dtype=np.float32)
+    h = route_out.shape[1]
+    idx = np.ascontiguousarray(idx, dtype=np.int32)
+    w = np.ascontiguousarray(w, dtype=np.float32)
+    out = np.zeros((t, h), dtype=np.float32)
+    oracle().orc_moe_combine(_ptr(route_out), t, h, top_k, _ptr(idx), _ptr(w), _ptr(out), h)
+    return out
+
+
+def expert_route_outputs(hidden, idx, intermediate, gate_up, down, experts, lo=0, hi=None):
+    """Per-route expert outputs [tokens*top_k, H] from the oracle's pieces, for the routes
+    whose expert lies in [lo, hi); zeros elsewhere.  gate_up / down hold all `experts`."""
+    hidden = np.ascontiguousarray(hidden, dtype=np.float32)
+    t, h = hidden.shape
+    top_k = idx.shape[1]
+    hi = experts if hi is None else hi
+    gu_bytes = bg128_bytes(2 * intermediate, h)
+    dn_bytes = bg128_bytes(h, intermediate)
+    out = np.zeros((t * top_k, h), dtype=np.float32)
+    for tok in range(t):
+        for j in range(top_k):
+            e = int(idx[tok, j])
+            if not lo <= e < hi:
+                continue
+            gu = matmul_w4(gate_up[e * gu_bytes:(e + 1) * gu_bytes], 2 * intermediate, h,
+                           hidden[tok:tok + 1])
+            gate = apply_activation(gu[:, :intermediate].copy(), 1)  # g * 1/(1+expf(-g))
+            inter = (gate * gu[:, intermediate:]).astype(np.float32)
+            out[tok * top_k + j] = matmul_w4(down[e * dn_bytes:(e + 1) * dn_bytes], h,
+                                             intermediate, inter)[0]
+    return out
+
+
 # ------------------------------------------------------------- reference calls
 
 def ref_quantize_g128_even_odd(x):

@@ -129,3 +129,71 @@ def test_bad_shapes_are_errors(ctx):
     assert (out.cpu().numpy() == 0).all()               # zero input -> zero output
     gu.free()
     dn.free()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("t,h,e,top_k,inter", [(1, 256, 16, 4, 128), (33, 512, 32, 8, 128),
+                                               (16, 2048, 128, 8, 768)])
+def test_expert_parallel_split_is_bit_identical(ctx, world, t, h, e, top_k, inter):
+    """The expert-parallel halves of the op (b2w4_moe_expert_outputs per rank, sum of the
+    route buffers, b2w4_moe_combine) against the one-device op and the oracle's route
+    outputs.  The ranks of the group are run one after another on this GPU and their buffers
+    summed with a plain add, which is what the all-reduce computes."""
+    import torch
+    ep = pkg.expert_parallel
+    hidden = pkg.synth.activations(7, 300 + t, t, h)
+    router = pkg.synth.router_weight(20261125, 50 + e, e, h, std=0.3)
+    gu = pkg.synth.bg128_weight(20261125, 300 + e, e * 2 * inter, h)
+    dn = pkg.synth.bg128_weight(20261125, 400 + e, e * h, inter)
+    one_dev = run_moe(ctx, hidden, router, top_k, inter, gu, dn)
+    xd = torch.from_numpy(hidden).cuda()
+    rd = torch.from_numpy(router.view(np.int16)).cuda()
+    total = torch.zeros((t * top_k, h), dtype=torch.float32, device="cuda")
+    owners = np.zeros(t * top_k, dtype=np.int32)
+    for rank in range(world):
+        gu_l, lo, cnt = ep.shard_expert_blocks(gu, e, 2 * inter, h, rank, world)
+        dn_l, _, _ = ep.shard_expert_blocks(dn, e, h, inter, rank, world)
+        wg = ctx.upload_weight(np.ascontiguousarray(gu_l), cnt * 2 * inter, h)
+        wd = ctx.upload_weight(np.ascontiguousarray(dn_l), cnt * h, inter)
+        eng = ep.DeviceEngine(ctx, rd, wg, wd, top_k, inter, lo, cnt)
+        routes, idx, w = eng.expert_outputs(xd)
+        ctx.sync()
+        assert (idx.cpu().numpy() == one_dev[2]).all()
+        assert w.cpu().numpy().tobytes() == one_dev[3].tobytes()
+        local = (one_dev[2].ravel() >= lo) & (one_dev[2].ravel() < lo + cnt)
+        rows = routes.cpu().numpy()
+        assert (rows[~local] == 0).all()                   # rows of other ranks stay zero
+        owners += local
+        total += routes
+        wg.free()
+        wd.free()
+    assert (owners == 1).all()
+    want_routes = ol.expert_route_outputs(hidden, one_dev[2], inter, gu, dn, e) \
+        if t * top_k <= 64 else None
+    if want_routes is not None:
+        assert total.cpu().numpy().tobytes() == want_routes.tobytes()
+    out = torch.full((t, h), 5.0, dtype=torch.float32, device="cuda")
+    eng.combine(total, idx, w, out)
+    ctx.sync()
+    assert out.cpu().numpy().tobytes() == one_dev[0].tobytes()
+    assert out.cpu().numpy().tobytes() == ol.moe_combine(total.cpu().numpy(), one_dev[2],
+                                                         one_dev[3]).tobytes()
+
+
+def test_expert_parallel_bad_range_is_error(ctx):
+    import torch
+    x = torch.zeros((2, 128), device="cuda")
+    r = torch.zeros((4, 128), dtype=torch.int16, device="cuda")
+    gu = ctx.upload_weight(pkg.synth.bg128_weight(1, 1, 2 * 2 * 128, 128), 2 * 2 * 128, 128)
+    dn = ctx.upload_weight(pkg.synth.bg128_weight(1, 2, 2 * 128, 128), 2 * 128, 128)
+    routes = torch.zeros((4, 128), device="cuda")
+    idx = torch.zeros((2, 2), dtype=torch.int32, device="cuda")
+    w = torch.zeros((2, 2), device="cuda")
+    with pytest.raises(pkg.capi.B200W4Error):
+        ctx.moe_expert_outputs(x, r, 2, 128, gu, dn, 3, 2, routes, idx, w)   # experts 3..4 of 4
+    with pytest.raises(pkg.capi.B200W4Error):
+        ctx.moe_expert_outputs(x, r, 2, 128, gu, dn, 0, 4, routes, idx, w)   # aggregates hold 2
+    ctx.moe_expert_outputs(x, r, 2, 128, gu, dn, 2, 2, routes, idx, w)
+    ctx.sync()
+    gu.free()
+    dn.free()

@@ -52,3 +52,74 @@ def test_shard_ranges():
     assert pkg.shard.expert_range(128, 7, 8) == (112, 128)
     with pytest.raises(ValueError):
         pkg.shard.expert_range(128, 0, 3)
+
+
+# ---- expert-parallel MoE: split at the route outputs, all-reduce, ordered combine --------
+E, TOPK, H, I, T = 8, 2, 128, 128, 5
+
+
+def _moe_inputs():
+    router = pkg.synth.router_weight(9, 1, E, H)
+    gu = pkg.synth.bg128_weight(9, 2, E * 2 * I, H)
+    dn = pkg.synth.bg128_weight(9, 3, E * H, I)
+    x = pkg.synth.activations(9, 4, T, H)
+    return router, gu, dn, x
+
+
+class _OracleEngine:
+    """The CPU oracle standing in for the device halves of the op."""
+
+    def __init__(self, router, gu_local, dn_local, lo, cnt):
+        self.router, self.gu, self.dn, self.lo, self.cnt = router, gu_local, dn_local, lo, cnt
+
+    def expert_outputs(self, hidden):
+        logits = ol.router_logits(hidden, self.router)
+        idx, w = ol.select_routes(logits, TOPK)
+        # local aggregates are indexed from the first expert held
+        routes = ol.expert_route_outputs(hidden, idx - self.lo, I, self.gu, self.dn, self.cnt)
+        return torch.from_numpy(routes), idx, w
+
+    def combine(self, route_out, idx, w, out):
+        out[:] = ol.moe_combine(route_out.numpy(), idx, w)
+
+
+def _ep_worker(rank, world, port, out_dir):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    router, gu, dn, x = _moe_inputs()
+    ep = pkg.expert_parallel
+    gu_l, lo, cnt = ep.shard_expert_blocks(gu, E, 2 * I, H, rank, world)
+    dn_l, _, _ = ep.shard_expert_blocks(dn, E, H, I, rank, world)
+    op = ep.ExpertParallelMoE(_OracleEngine(router, gu_l, dn_l, lo, cnt), dist.all_reduce)
+    out = np.zeros((T, H), dtype=np.float32)
+    op.forward(x, out)
+    np.save(os.path.join(out_dir, f"moe{rank}.npy"), out)
+    dist.destroy_process_group()
+
+
+def test_moe_split_equals_monolithic_oracle():
+    router, gu, dn, x = _moe_inputs()
+    want, logits, idx, w = ol.moe_forward(x, router, TOPK, I, gu, dn)
+    assert ol.router_logits(x, router).tobytes() == logits.tobytes()
+    routes = ol.expert_route_outputs(x, idx, I, gu, dn, E)
+    assert ol.moe_combine(routes, idx, w).tobytes() == want.tobytes()
+
+
+def test_expert_parallel_moe_world2(tmp_path):
+    port = 31500 + os.getpid() % 2000
+    mp.spawn(_ep_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    router, gu, dn, x = _moe_inputs()
+    want = ol.moe_forward(x, router, TOPK, I, gu, dn)[0]
+    for r in range(2):
+        assert np.load(tmp_path / f"moe{r}.npy").tobytes() == want.tobytes()
+
+
+def test_expert_shard_ranges():
+    ep = pkg.expert_parallel
+    blocks = pkg.synth.bg128_weight(5, 3, 4 * 16, 128)
+    parts = [ep.shard_expert_blocks(blocks, 4, 16, 128, r, 2) for r in range(2)]
+    assert np.concatenate([p[0] for p in parts]).tobytes() == blocks.tobytes()
+    assert [(p[1], p[2]) for p in parts] == [(0, 2), (2, 2)]
+    with pytest.raises(ValueError):
+        ep.shard_expert_blocks(blocks, 4, 12, 128, 0, 2)
