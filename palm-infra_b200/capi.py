@@ -170,6 +170,22 @@ class Context:
             y_np.ctypes.data_as(C.c_void_p), y_np.strides[0] // 4, m, rule, act, act_begin,
             act_len))
 
+    def bind_matmul_host(self, w, x_np, y_np, rule=ACT_G128, act=NONE, act_begin=0, act_len=-1):
+        """The same call with its arguments resolved once: returns a function of no arguments
+        for loops that repeat it (pointer extraction from numpy costs as much as the call)."""
+        fn = lib().b2w4_matmul_host
+        args = (self.handle, w.handle, x_np.ctypes.data, x_np.strides[0] // 4,
+                y_np.ctypes.data, y_np.strides[0] // 4, x_np.shape[0], rule, act, act_begin,
+                act_len)
+        keep = (w, x_np, y_np)
+
+        def call():
+            rc = fn(*args)
+            if rc != 0:
+                self._check(rc)
+            return keep[2]
+        return call
+
     def group_sums(self, w, x, sums, rule=ACT_G128):
         self._check(lib().b2w4_debug_group_sums(self.handle, w.handle, _dptr(x),
                                                 x.stride(0), x.shape[0], rule, _dptr(sums)))

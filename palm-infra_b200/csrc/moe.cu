@@ -68,13 +68,77 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
         : "memory");
 }
 
-// ---- 1. router logits: one warp per (token, expert) -----------------------------------
+// ---- 1. router logits: one warp per (4 tokens, EPW experts) -----------------------------
 // fp32 activation times fp16 weight is exact in fp64 and a few thousand such terms of
 // similar magnitude add without rounding, so the fp64 sum does not depend on its order;
-// one rounding to fp32 at the end (the oracle accumulates the same way).
+// one rounding to fp32 at the end (the oracle accumulates the same way).  A lane takes 8
+// consecutive columns per step (one 16-byte load of router halves, two of each token's
+// activations); the warp's router rows are reused for its 4 tokens.
+constexpr int kRouterTok = 4;
+template <int EPW>
 __global__ void moe_router_logits_kernel(const float* __restrict__ hidden, int ldx, int tokens,
                                          int hidden_size, const __half* __restrict__ router,
                                          int num_experts, float* __restrict__ logits) {
+    const int eblocks = (num_experts + EPW - 1) / EPW;
+    const long long wid = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    const int tblocks = (tokens + kRouterTok - 1) / kRouterTok;
+    if (wid >= (long long)tblocks * eblocks)
+        return;
+    const int t0 = (int)(wid / eblocks) * kRouterTok, e0 = (int)(wid % eblocks) * EPW;
+    double acc[kRouterTok][EPW];
+#pragma unroll
+    for (int i = 0; i < kRouterTok; ++i)
+#pragma unroll
+        for (int j = 0; j < EPW; ++j)
+            acc[i][j] = 0.0;
+#pragma unroll 2
+    for (int d = lane * 8; d < hidden_size; d += 256) {
+        float xv[kRouterTok][8];
+#pragma unroll
+        for (int i = 0; i < kRouterTok; ++i) {
+            // rows past the last token repeat it: loaded, never stored
+            const float* x = hidden + (size_t)min(t0 + i, tokens - 1) * ldx + d;
+            const float4 lo = *reinterpret_cast<const float4*>(x);
+            const float4 hi = *reinterpret_cast<const float4*>(x + 4);
+            xv[i][0] = lo.x, xv[i][1] = lo.y, xv[i][2] = lo.z, xv[i][3] = lo.w;
+            xv[i][4] = hi.x, xv[i][5] = hi.y, xv[i][6] = hi.z, xv[i][7] = hi.w;
+        }
+#pragma unroll
+        for (int j = 0; j < EPW; ++j) {
+            const int e = min(e0 + j, num_experts - 1);
+            const uint4 raw = *reinterpret_cast<const uint4*>(router + (size_t)e * hidden_size + d);
+            const __half2* h2 = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const float2 r = __half22float2(h2[c]);
+#pragma unroll
+                for (int i = 0; i < kRouterTok; ++i) {
+                    acc[i][j] += (double)xv[i][2 * c] * (double)r.x;
+                    acc[i][j] += (double)xv[i][2 * c + 1] * (double)r.y;
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < kRouterTok; ++i)
+#pragma unroll
+        for (int j = 0; j < EPW; ++j) {
+            double v = acc[i][j];
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1)
+                v += __shfl_xor_sync(0xffffffffu, v, off);
+            if (lane == 0 && t0 + i < tokens && e0 + j < num_experts)
+                logits[(size_t)(t0 + i) * num_experts + e0 + j] = (float)v;
+        }
+}
+
+// Fallback for activations whose rows are not 16-byte aligned: one warp per (token, expert),
+// scalar loads.
+__global__ void moe_router_logits_scalar_kernel(const float* __restrict__ hidden, int ldx,
+                                                int tokens, int hidden_size,
+                                                const __half* __restrict__ router,
+                                                int num_experts, float* __restrict__ logits) {
     const long long wid = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
     if (wid >= (long long)tokens * num_experts)
@@ -92,90 +156,155 @@ __global__ void moe_router_logits_kernel(const float* __restrict__ hidden, int l
         logits[(size_t)t * num_experts + e] = (float)acc;
 }
 
-// ---- 2. route selection: one thread per token ------------------------------------------
-// insertion top-k with strict '>' (equal logits keep the lower expert id first), then
-// softmax over the selected logits: exp(l - l_max), sequential fp32 sum, times 1/sum
-// (kernels/moe_routing.cpp:129-142, :157-166).
+// ---- 2. route selection: one warp per token ---------------------------------------------
+// The reference selects by insertion with strict '>' (kernels/moe_routing.cpp:129-142): the
+// result is the k largest logits in descending order, equal logits in ascending expert id,
+// and a logit that is -inf or NaN never displaces the initial (expert 0, -inf) slot.  Here
+// that is k rounds of a warp-wide arg-max over (logit descending, expert id ascending) with
+// taken experts masked out.  Then the softmax over the selected logits: exp(l - l_max),
+// sequential fp32 sum, times 1/sum (:157-166).
 constexpr int kMaxTopK = 16;
+constexpr int kSelectMaxExperts = 1024;  // 32 lanes x 32 mask bits
 __global__ void moe_select_routes_kernel(const float* __restrict__ logits, int tokens,
                                          int num_experts, int top_k, int32_t* __restrict__ idx,
                                          float* __restrict__ weights) {
-    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    const int t = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
     if (t >= tokens)
         return;
     const float* row = logits + (size_t)t * num_experts;
-    int bi[kMaxTopK];
-    float bw[kMaxTopK];
+    uint32_t taken = 0;       // bit s: expert lane + 32*s already selected
+    float my_v = -INFINITY;   // lane j keeps the j-th selected logit
+    int my_e = 0;
     for (int j = 0; j < top_k; ++j) {
-        bi[j] = 0;
-        bw[j] = -INFINITY;
-    }
-    for (int e = 0; e < num_experts; ++e) {
-        const float v = row[e];
-        for (int j = 0; j < top_k; ++j) {
-            if (v > bw[j]) {
-                for (int s = top_k - 1; s > j; --s) {
-                    bw[s] = bw[s - 1];
-                    bi[s] = bi[s - 1];
-                }
-                bw[j] = v;
-                bi[j] = e;
-                break;
+        float bv = -INFINITY;
+        int be = INT_MAX;
+        for (int e = lane, s = 0; e < num_experts; e += 32, ++s) {
+            const float v = row[e];
+            if (!((taken >> s) & 1u) && v > bv) {
+                bv = v;
+                be = e;
             }
         }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, off);
+            const int oe = __shfl_xor_sync(0xffffffffu, be, off);
+            if (oe != INT_MAX && (be == INT_MAX || ov > bv || (ov == bv && oe < be))) {
+                bv = ov;
+                be = oe;
+            }
+        }
+        if (be != INT_MAX && (be & 31) == lane)
+            taken |= 1u << (be >> 5);
+        if (lane == j) {
+            my_v = be == INT_MAX ? -INFINITY : bv;
+            my_e = be == INT_MAX ? 0 : be;
+        }
     }
-    const float maximum = bw[0];
+    const float maximum = __shfl_sync(0xffffffffu, my_v, 0);
+    // exp in fp64 and one rounding: agrees with a correctly rounded expf
+    const float ex = lane < top_k ? (float)exp((double)__fsub_rn(my_v, maximum)) : 0.f;
     float sum = 0.f;
-    for (int j = 0; j < top_k; ++j) {
-        // exp in fp64 and one rounding: agrees with a correctly rounded expf
-        bw[j] = (float)exp((double)__fsub_rn(bw[j], maximum));
-        sum = __fadd_rn(sum, bw[j]);
-    }
+    for (int j = 0; j < top_k; ++j)
+        sum = __fadd_rn(sum, __shfl_sync(0xffffffffu, ex, j));
     const float inverse = sum > 0.f ? __fdiv_rn(1.f, sum) : 0.f;
-    for (int j = 0; j < top_k; ++j) {
-        idx[(size_t)t * top_k + j] = bi[j];
-        weights[(size_t)t * top_k + j] = __fmul_rn(bw[j], inverse);
+    if (lane < top_k) {
+        idx[(size_t)t * top_k + lane] = my_e;
+        weights[(size_t)t * top_k + lane] = __fmul_rn(ex, inverse);
     }
 }
 
-// ---- 3. compaction: one block, thread e owns expert e ----------------------------------
+// ---- 3. compaction: one block ------------------------------------------------------------
 // counts, exclusive offsets, and per expert its routes in ascending token order
-// (kernels/moe.cpp:759-776).  pos[t][j] = the compact position of token t's j-th route.
-__global__ void moe_compact_kernel(const int32_t* __restrict__ idx, int tokens, int top_k,
-                                   int num_experts, int32_t* __restrict__ offsets,
-                                   int32_t* __restrict__ route_token,
-                                   int32_t* __restrict__ pos) {
-    extern __shared__ int s_cnt[];  // [E+1]
+// (kernels/moe.cpp:759-776).  pos[t][j] = the compact position of token t's j-th route;
+// active[] lists the experts that have routes, ascending, active[E] their number.
+// Stable placement, a chunk of routes at a time (one route per thread): lanes of a warp that
+// hold the same expert find each other with match.any, the lowest of them records the warp's
+// count for that expert, a scan over the warps turns the counts into first slots, and every
+// route lands at its warp's first slot plus its rank among the matching lanes.
+constexpr int kCompactThreads = 1024;
+constexpr int kCompactTableInts = 8192;  // warps x experts count table
+__global__ void __launch_bounds__(kCompactThreads)
+moe_compact_kernel(const int32_t* __restrict__ idx, int tokens, int top_k, int num_experts,
+                   int32_t* __restrict__ offsets, int32_t* __restrict__ route_token,
+                   int32_t* __restrict__ pos, int32_t* __restrict__ active) {
+    extern __shared__ int s_int[];
+    const int E = num_experts;
+    const int nw = min(kCompactThreads / 32, max(1, kCompactTableInts / E));  // warps placing
+    int* s_cnt = s_int;             // [E+1] counts
+    int* s_cursor = s_cnt + E + 1;  // [E] next free slot per expert
+    int* s_wc = s_cursor + E;       // [nw][E]
     const int routes = tokens * top_k;
-    for (int e = threadIdx.x; e <= num_experts; e += blockDim.x)
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const unsigned lt = (1u << lane) - 1u;
+    for (int e = threadIdx.x; e <= E; e += blockDim.x)
         s_cnt[e] = 0;
     __syncthreads();
-    for (int i = threadIdx.x; i < routes; i += blockDim.x)
-        atomicAdd(&s_cnt[idx[i]], 1);  // integer counts: order-free
+    for (int i0 = 0; i0 < routes; i0 += blockDim.x) {
+        const int i = i0 + threadIdx.x;
+        const int e = i < routes ? idx[i] : -1;
+        const unsigned peers = __match_any_sync(0xffffffffu, e);
+        if (e >= 0 && (peers & lt) == 0)
+            atomicAdd(&s_cnt[e], __popc(peers));  // integer counts: order-free
+    }
     __syncthreads();
-    if (threadIdx.x == 0) {
-        int run = 0;
-        for (int e = 0; e < num_experts; ++e) {
-            const int c = s_cnt[e];
-            s_cnt[e] = run;
+    // exclusive offsets and the list of experts with routes: entry e sums the counts below it
+    for (int e = threadIdx.x; e <= E; e += blockDim.x) {
+        int run = 0, rank = 0;
+        for (int q = 0; q < e; ++q) {
+            const int c = s_cnt[q];
             run += c;
+            rank += c > 0;
         }
-        s_cnt[num_experts] = run;
+        offsets[e] = run;
+        if (e < E) {
+            s_cursor[e] = run;
+            if (s_cnt[e] > 0)
+                active[rank] = e;
+        } else {
+            active[E] = rank;
+        }
     }
     __syncthreads();
-    for (int e = threadIdx.x; e <= num_experts; e += blockDim.x)
-        offsets[e] = s_cnt[e];
-    for (int e = threadIdx.x; e < num_experts; e += blockDim.x) {
-        int cursor = s_cnt[e];
-        const int end = s_cnt[e + 1];
-        for (int i = 0; i < routes && cursor < end; ++i) {
-            if (idx[i] == e) {
-                route_token[cursor] = i / top_k;
-                pos[i] = cursor;
-                ++cursor;
-            }
+    const int chunk = nw * 32;
+    for (int c0 = 0; c0 < routes; c0 += chunk) {
+        for (int w = threadIdx.x; w < nw * E; w += blockDim.x)
+            s_wc[w] = 0;
+        __syncthreads();
+        const int i = c0 + threadIdx.x;
+        int e = -1;
+        unsigned peers = 0;
+        if (warp < nw) {  // warp-uniform
+            e = i < routes ? idx[i] : -1;
+            peers = __match_any_sync(0xffffffffu, e);
+            if (e >= 0 && (peers & lt) == 0)
+                s_wc[warp * E + e] = __popc(peers);
         }
+        __syncthreads();
+        for (int x = threadIdx.x; x < E; x += blockDim.x) {
+            int run = s_cursor[x];
+            for (int w = 0; w < nw; ++w) {
+                const int c = s_wc[w * E + x];
+                s_wc[w * E + x] = run;
+                run += c;
+            }
+            s_cursor[x] = run;
+        }
+        __syncthreads();
+        if (e >= 0) {
+            const int slot = s_wc[warp * E + e] + __popc(peers & lt);
+            route_token[slot] = i / top_k;
+            pos[i] = slot;
+        }
+        __syncthreads();
     }
+}
+
+size_t compact_smem(int num_experts) {
+    int nw = kCompactTableInts / num_experts;
+    nw = nw < 1 ? 1 : (nw > kCompactThreads / 32 ? kCompactThreads / 32 : nw);
+    return sizeof(int) * ((size_t)2 * num_experts + 1 + (size_t)nw * num_experts);
 }
 
 // ---- 6. SwiGLU + quantiser: one warp per (route, 128-wide group of I) ------------------
@@ -221,38 +350,46 @@ __global__ void moe_swiglu_quant_kernel(const float* __restrict__ gu, int routes
     *reinterpret_cast<char2*>(blk + 16 + j) = make_char2((signed char)c1, (signed char)c3);
 }
 
-// ---- 8. combine: one thread per (token, hidden column) ---------------------------------
+// ---- 8. combine: one block per (token, 512 hidden columns) -------------------------------
 // out[t] starts at 0 and takes fma(w, y, out) for the token's experts in ascending id
-// (kernels/moe.cpp:642-645, :966, :1100-1110).
-__global__ void moe_combine_kernel(const float* __restrict__ dn, const int32_t* __restrict__ idx,
-                                   const float* __restrict__ weights,
-                                   const int32_t* __restrict__ pos, int tokens, int top_k,
-                                   int hidden_size, float* __restrict__ out, int ldo) {
+// (kernels/moe.cpp:642-645, :966, :1100-1110).  The token's k routes are put in that order
+// once per block; pos == nullptr reads route rows in (token, route) order.
+constexpr int kCombineThreads = 128;
+__global__ void __launch_bounds__(kCombineThreads)
+moe_combine_kernel(const float* __restrict__ dn, const int32_t* __restrict__ idx,
+                   const float* __restrict__ weights, const int32_t* __restrict__ pos,
+                   int tokens, int top_k, int hidden_size, float* __restrict__ out, int ldo) {
+    __shared__ int s_row[kMaxTopK];
+    __shared__ float s_w[kMaxTopK];
     const int t = blockIdx.y;
-    const int d = blockIdx.x * blockDim.x + threadIdx.x;
-    if (t >= tokens || d >= hidden_size)
-        return;
-    int order[kMaxTopK];
-    for (int j = 0; j < top_k; ++j)
-        order[j] = j;
-    for (int a = 1; a < top_k; ++a) {  // insertion sort of the k routes by expert id
-        const int cur = order[a];
-        const int key = idx[(size_t)t * top_k + cur];
-        int b = a - 1;
-        while (b >= 0 && idx[(size_t)t * top_k + order[b]] > key) {
-            order[b + 1] = order[b];
-            --b;
+    if (threadIdx.x < top_k) {
+        // rank of this route among the token's routes by expert id (ids are distinct, except
+        // for the repeated placeholder slots of a degenerate row: ties go to the lower slot)
+        const int j = threadIdx.x;
+        const int key = idx[(size_t)t * top_k + j];
+        int rank = 0;
+        for (int o = 0; o < top_k; ++o) {
+            const int other = idx[(size_t)t * top_k + o];
+            rank += other < key || (other == key && o < j);
         }
-        order[b + 1] = cur;
+        s_row[rank] = pos ? pos[(size_t)t * top_k + j] : t * top_k + j;
+        s_w[rank] = weights[(size_t)t * top_k + j];
     }
-    float acc = 0.f;
+    __syncthreads();
+    const int d = (blockIdx.x * kCombineThreads + threadIdx.x) * 4;
+    if (d >= hidden_size)
+        return;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int j = 0; j < top_k; ++j) {
-        const int r = order[j];
-        const float w = weights[(size_t)t * top_k + r];
-        const size_t row = pos ? (size_t)pos[(size_t)t * top_k + r] : (size_t)t * top_k + r;
-        acc = __fmaf_rn(w, dn[row * hidden_size + d], acc);
+        const float w = s_w[j];
+        const float4 y = *reinterpret_cast<const float4*>(dn + (size_t)s_row[j] * hidden_size + d);
+        acc.x = __fmaf_rn(w, y.x, acc.x);
+        acc.y = __fmaf_rn(w, y.y, acc.y);
+        acc.z = __fmaf_rn(w, y.z, acc.z);
+        acc.w = __fmaf_rn(w, y.w, acc.w);
     }
-    out[(size_t)t * ldo + d] = acc;
+    float* o = out + (size_t)t * ldo + d;
+    o[0] = acc.x, o[1] = acc.y, o[2] = acc.z, o[3] = acc.w;  // ldo need not be a multiple of 4
 }
 
 // ---- expert-parallel hand-over: route outputs in (token, route) order -------------------
@@ -291,7 +428,11 @@ struct GroupedArgs {
     const void* scl;
     const int8_t* qa;         // [rows][K] int8, even/odd order inside each 32-block
     const float* as;          // [rows][G]
-    const int32_t* offsets;   // [E+1] route ranges
+    const int32_t* offsets;   // [E+1] route ranges of all experts
+    const int32_t* active;    // experts that have routes, ascending; active[E_all] = how many
+    int num_experts_all;      // experts routed over
+    int expert_begin;         // first expert whose weights this aggregate holds
+    int expert_count;         // experts held
     const int32_t* row_map;   // route -> activation row, or null for identity
     float* out;               // [routes][n_e]
     int* status;
@@ -302,8 +443,15 @@ template <bool SCL16>
 __global__ void __launch_bounds__(kGT, 2)
 moe_grouped_gemv_kernel(const GroupedArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
-    const int e = blockIdx.y;
-    const int r0 = a.offsets[e], r1 = a.offsets[e + 1];
+    // blockIdx.y walks the experts that have routes, not all experts: a decode token
+    // touches top_k of them
+    if ((int)blockIdx.y >= a.active[a.num_experts_all])
+        return;
+    const int e_all = a.active[blockIdx.y];
+    const int e = e_all - a.expert_begin;  // index inside the aggregate held here
+    if (e < 0 || e >= a.expert_count)
+        return;
+    const int r0 = a.offsets[e_all], r1 = a.offsets[e_all + 1];
     const int tl0 = blockIdx.x * a.tpc;
     const int ntile = min(a.tpc, a.tiles_e - tl0);
     if (r0 >= r1 || ntile <= 0)
@@ -442,10 +590,11 @@ size_t grouped_smem(int k, int groups, int tpc, bool scl16) {
            sizeof(int32_t) * (size_t)tpc * grouped_d_stride(groups) + 8 + 16;
 }
 
-int launch_grouped(b2w4_ctx* ctx, const b2w4_weight* w, int num_experts, const int8_t* qa,
-                   const float* as, const int32_t* offsets, const int32_t* row_map,
+int launch_grouped(b2w4_ctx* ctx, const b2w4_weight* w, int num_experts_all, int expert_begin,
+                   int expert_count, int routes, const int8_t* qa, const float* as,
+                   const int32_t* offsets, const int32_t* active, const int32_t* row_map,
                    float* out) {
-    const int n_e = w->n / num_experts;
+    const int n_e = w->n / expert_count;
     const bool scl16 = w->scales_fp16 != 0;
     GroupedArgs a;
     a.nib = reinterpret_cast<const uint8_t*>(w->nib);
@@ -453,6 +602,10 @@ int launch_grouped(b2w4_ctx* ctx, const b2w4_weight* w, int num_experts, const i
     a.qa = qa;
     a.as = as;
     a.offsets = offsets;
+    a.active = active;
+    a.num_experts_all = num_experts_all;
+    a.expert_begin = expert_begin;
+    a.expert_count = expert_count;
     a.row_map = row_map;
     a.out = out;
     a.status = ctx->flag_dev + 1;
@@ -475,7 +628,7 @@ int launch_grouped(b2w4_ctx* ctx, const b2w4_weight* w, int num_experts, const i
                                             (int)smem));
         configured[scl16] = smem;
     }
-    dim3 grid((a.tiles_e + tpc - 1) / tpc, num_experts);
+    dim3 grid((a.tiles_e + tpc - 1) / tpc, routes < num_experts_all ? routes : num_experts_all);
     kern<<<grid, kGT, smem, ctx->stream>>>(a);
     ctx->launches++;
     B2W4_CUDA(ctx, cudaGetLastError());
@@ -494,11 +647,13 @@ int b2w4_moe_select_routes(b2w4_ctx* ctx, const float* logits_dev, int tokens,
     if (!ctx)
         return B2W4_E_INVALID;
     if (!logits_dev || !indices_dev || !weights_dev || tokens <= 0 || num_experts <= 0 ||
-        top_k <= 0 || top_k > num_experts || top_k > kMaxTopK)
+        top_k <= 0 || top_k > num_experts || top_k > kMaxTopK ||
+        num_experts > kSelectMaxExperts)
         return b2w4_fail(ctx, B2W4_E_INVALID,
-                         "select_routes: need 0 < top_k <= min(experts, %d) (tokens=%d "
-                         "experts=%d top_k=%d)", kMaxTopK, tokens, num_experts, top_k);
-    moe_select_routes_kernel<<<(tokens + 127) / 128, 128, 0, ctx->stream>>>(
+                         "select_routes: need 0 < top_k <= min(experts, %d), experts <= %d "
+                         "(tokens=%d experts=%d top_k=%d)", kMaxTopK, kSelectMaxExperts, tokens,
+                         num_experts, top_k);
+    moe_select_routes_kernel<<<(tokens + 3) / 4, 128, 0, ctx->stream>>>(
         logits_dev, tokens, num_experts, top_k, indices_dev, weights_dev);
     ctx->launches++;
     B2W4_CUDA(ctx, cudaGetLastError());
@@ -520,8 +675,8 @@ static int moe_run(b2w4_ctx* ctx, const float* hidden_dev, int ldx, int tokens, 
         return B2W4_E_INVALID;
     if (!hidden_dev || !router_fp16_dev || !gate_up || !down || (!out_dev && !route_out))
         return b2w4_fail(ctx, B2W4_E_INVALID, "moe: null argument");
-    if (tokens <= 0 || num_experts <= 0 || top_k <= 0 || top_k > num_experts ||
-        top_k > kMaxTopK || hidden_size % 128 || intermediate % 128 || ldx < hidden_size ||
+    if (tokens <= 0 || num_experts <= 0 || num_experts > kSelectMaxExperts || top_k <= 0 ||
+        top_k > num_experts || top_k > kMaxTopK || hidden_size % 128 || intermediate % 128 || ldx < hidden_size ||
         (out_dev && ldo < hidden_size))
         return b2w4_fail(ctx, B2W4_E_INVALID,
                          "moe: bad shape tokens=%d hidden=%d experts=%d top_k=%d inter=%d",
@@ -543,7 +698,8 @@ static int moe_run(b2w4_ctx* ctx, const float* hidden_dev, int ldx, int tokens, 
     const size_t o_off = align_up(o_w + sizeof(float) * routes, 256);
     const size_t o_rt = align_up(o_off + sizeof(int32_t) * (num_experts + 1), 256);
     const size_t o_pos = align_up(o_rt + sizeof(int32_t) * routes, 256);
-    const size_t small_bytes = align_up(o_pos + sizeof(int32_t) * routes, 256);
+    const size_t o_act = align_up(o_pos + sizeof(int32_t) * routes, 256);
+    const size_t small_bytes = align_up(o_act + sizeof(int32_t) * (num_experts + 1), 256);
     // quantised hidden (per token) and quantised SwiGLU output (per route)
     const size_t o_qh = 0;
     const size_t o_ash = align_up(o_qh + (size_t)tokens * hidden_size, 256);
@@ -567,34 +723,46 @@ static int moe_run(b2w4_ctx* ctx, const float* hidden_dev, int ldx, int tokens, 
     int32_t* offsets = reinterpret_cast<int32_t*>(smb + o_off);
     int32_t* route_token = reinterpret_cast<int32_t*>(smb + o_rt);
     int32_t* pos = reinterpret_cast<int32_t*>(smb + o_pos);
+    int32_t* active = reinterpret_cast<int32_t*>(smb + o_act);
     int8_t* q_hidden = reinterpret_cast<int8_t*>(qbb + o_qh);
     float* as_hidden = reinterpret_cast<float*>(qbb + o_ash);
     int8_t* q_inter = reinterpret_cast<int8_t*>(qbb + o_qi);
     float* as_inter = reinterpret_cast<float*>(qbb + o_asi);
     cudaStream_t st = ctx->stream;
 
-    {
+    const __half* router = static_cast<const __half*>(router_fp16_dev);
+    if ((reinterpret_cast<uintptr_t>(hidden_dev) | reinterpret_cast<uintptr_t>(router)) % 16 ||
+        ldx % 4) {
         const long long threads = (long long)tokens * num_experts * 32;
-        moe_router_logits_kernel<<<(int)((threads + 255) / 256), 256, 0, st>>>(
-            hidden_dev, ldx, tokens, hidden_size, static_cast<const __half*>(router_fp16_dev),
-            num_experts, logits);
-        ctx->launches++;
+        moe_router_logits_scalar_kernel<<<(int)((threads + 255) / 256), 256, 0, st>>>(
+            hidden_dev, ldx, tokens, hidden_size, router, num_experts, logits);
+    } else if (tokens <= 8) {  // decode: one expert per warp keeps every SM busy
+        const long long warps = (long long)((tokens + kRouterTok - 1) / kRouterTok) * num_experts;
+        moe_router_logits_kernel<1><<<(int)((warps * 32 + 127) / 128), 128, 0, st>>>(
+            hidden_dev, ldx, tokens, hidden_size, router, num_experts, logits);
+    } else {
+        const long long warps =
+            (long long)((tokens + kRouterTok - 1) / kRouterTok) * ((num_experts + 3) / 4);
+        moe_router_logits_kernel<4><<<(int)((warps * 32 + 127) / 128), 128, 0, st>>>(
+            hidden_dev, ldx, tokens, hidden_size, router, num_experts, logits);
     }
-    moe_select_routes_kernel<<<(tokens + 127) / 128, 128, 0, st>>>(logits, tokens, num_experts,
-                                                                   top_k, idx, wts);
     ctx->launches++;
-    moe_compact_kernel<<<1, 256, sizeof(int) * (num_experts + 1), st>>>(
-        idx, tokens, top_k, num_experts, offsets, route_token, pos);
+    moe_select_routes_kernel<<<(tokens + 3) / 4, 128, 0, st>>>(logits, tokens, num_experts,
+                                                               top_k, idx, wts);
+    ctx->launches++;
+    moe_compact_kernel<<<1, kCompactThreads, compact_smem(num_experts), st>>>(
+        idx, tokens, top_k, num_experts, offsets, route_token, pos, active);
     ctx->launches++;
     B2W4_CUDA(ctx, cudaGetLastError());
     if ((rc = b2w4_launch_quantize(ctx, hidden_dev, ldx, tokens, hidden_size, B2W4_ACT_G128,
                                    q_hidden, as_hidden, QLAYOUT_EVEN_ODD)) != B2W4_OK)
         return rc;
-    // the grouped kernels index experts from the first one held; compact positions stay global
+    // compact positions stay global; the grouped kernels skip experts held elsewhere
     const int32_t* local_offsets = offsets + expert_begin;
     const bool partial = expert_count != num_experts;
-    if ((rc = launch_grouped(ctx, gate_up, expert_count, q_hidden, as_hidden, local_offsets,
-                             route_token, static_cast<float*>(gu))) != B2W4_OK)
+    if ((rc = launch_grouped(ctx, gate_up, num_experts, expert_begin, expert_count, routes,
+                             q_hidden, as_hidden, offsets, active, route_token,
+                             static_cast<float*>(gu))) != B2W4_OK)
         return rc;
     {
         const long long threads = (long long)routes * gi * 32;
@@ -603,7 +771,8 @@ static int moe_run(b2w4_ctx* ctx, const float* hidden_dev, int ldx, int tokens, 
             partial ? local_offsets : nullptr, partial ? local_offsets + expert_count : nullptr);
         ctx->launches++;
     }
-    if ((rc = launch_grouped(ctx, down, expert_count, q_inter, as_inter, local_offsets, nullptr,
+    if ((rc = launch_grouped(ctx, down, num_experts, expert_begin, expert_count, routes, q_inter,
+                             as_inter, offsets, active, nullptr,
                              static_cast<float*>(dn))) != B2W4_OK)
         return rc;
     if (route_out) {
@@ -614,9 +783,10 @@ static int moe_run(b2w4_ctx* ctx, const float* hidden_dev, int ldx, int tokens, 
         ctx->launches++;
     }
     if (out_dev) {
-        dim3 grid((hidden_size + 255) / 256, tokens);
-        moe_combine_kernel<<<grid, 256, 0, st>>>(static_cast<const float*>(dn), idx, wts, pos,
-                                                 tokens, top_k, hidden_size, out_dev, ldo);
+        dim3 grid((hidden_size / 4 + kCombineThreads - 1) / kCombineThreads, tokens);
+        moe_combine_kernel<<<grid, kCombineThreads, 0, st>>>(static_cast<const float*>(dn), idx,
+                                                             wts, pos, tokens, top_k,
+                                                             hidden_size, out_dev, ldo);
         ctx->launches++;
     }
     B2W4_CUDA(ctx, cudaGetLastError());
@@ -665,12 +835,15 @@ int b2w4_moe_combine(b2w4_ctx* ctx, const float* route_out_dev, int tokens, int 
     if (!ctx)
         return B2W4_E_INVALID;
     if (!route_out_dev || !indices_dev || !weights_dev || !out_dev || tokens <= 0 ||
-        hidden_size <= 0 || top_k <= 0 || top_k > kMaxTopK || ldo < hidden_size)
-        return b2w4_fail(ctx, B2W4_E_INVALID, "moe_combine: bad argument");
-    dim3 grid((hidden_size + 255) / 256, tokens);
-    moe_combine_kernel<<<grid, 256, 0, ctx->stream>>>(route_out_dev, indices_dev, weights_dev,
-                                                      nullptr, tokens, top_k, hidden_size,
-                                                      out_dev, ldo);
+        hidden_size <= 0 || hidden_size % 4 || top_k <= 0 || top_k > kMaxTopK ||
+        ldo < hidden_size || reinterpret_cast<uintptr_t>(route_out_dev) % 16)
+        return b2w4_fail(ctx, B2W4_E_INVALID,
+                         "moe_combine: bad argument (hidden a multiple of 4, route rows "
+                         "16-byte aligned)");
+    dim3 grid((hidden_size / 4 + kCombineThreads - 1) / kCombineThreads, tokens);
+    moe_combine_kernel<<<grid, kCombineThreads, 0, ctx->stream>>>(
+        route_out_dev, indices_dev, weights_dev, nullptr, tokens, top_k, hidden_size, out_dev,
+        ldo);
     ctx->launches++;
     B2W4_CUDA(ctx, cudaGetLastError());
     return B2W4_OK;

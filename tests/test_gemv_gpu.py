@@ -135,6 +135,42 @@ def test_host_entry_point_and_weight_copy_ownership(ctx):
     w.free()
 
 
+@pytest.mark.parametrize("m", [1, 24])
+def test_repeated_pinned_host_calls(ctx, m):
+    """A host call repeated through a bound closure on the same pinned buffers: the buffers'
+    current contents are used every time, also after a larger call in between has moved the
+    context's staging buffers, and after the weight was freed and another one uploaded."""
+    import torch
+    n, k = 328, 640
+    blocks = pkg.synth.bg128_weight(11, 9, n, k)
+    w = ctx.upload_weight(blocks, n, k)
+    xh = torch.zeros((m, k), dtype=torch.float32).pin_memory()
+    yh = torch.zeros((m, n), dtype=torch.float32).pin_memory()
+    call = ctx.bind_matmul_host(w, xh.numpy(), yh.numpy())
+    for step in range(5):
+        x = pkg.synth.activations(7, 500 + step, m, k)
+        xh.numpy()[:] = x
+        yh.zero_()
+        call()
+        assert yh.numpy().tobytes() == ol.matmul_w4(blocks, n, k, x).tobytes(), step
+        if step == 2:  # a larger host call in between moves the staging buffers
+            big_n, big_m = 2048, 64
+            wb = ctx.upload_weight(pkg.synth.bg128_weight(11, 10, big_n, k), big_n, k)
+            xb = pkg.synth.activations(7, 600, big_m, k)
+            yb = np.zeros((big_m, big_n), dtype=np.float32)
+            ctx.matmul_host(wb, xb, yb)
+            wb.free()
+    w.free()
+    # the same buffers with another weight
+    blocks2 = pkg.synth.bg128_weight(11, 11, n, k)
+    w2 = ctx.upload_weight(blocks2, n, k)
+    call2 = ctx.bind_matmul_host(w2, xh.numpy(), yh.numpy())
+    for _ in range(3):
+        call2()
+        assert yh.numpy().tobytes() == ol.matmul_w4(blocks2, n, k, xh.numpy()).tobytes()
+    w2.free()
+
+
 def test_bad_arguments_are_errors(ctx):
     import torch
     blocks = pkg.synth.bg128_weight(1, 1, 8, 128)
