@@ -418,7 +418,7 @@ def run_ours(args):
     if rank == 0 and world == 1 and not args.headline_only:
         # ---- sweep: batched decode and prefill on the same weight -----------------------
         sweep = {}
-        for m in (4, 16, 64, 256):
+        for m in (4, 8, 16, 64, 256):
             s_ms = time_steps(torch, make_step(m, passes=1), max(3, min(args.steps, 25)), 3)
             per = s_ms * 1e-3 / COPIES
             sweep[f"m{m}"] = {"us_per_matmul": per * 1e6,

@@ -32,7 +32,7 @@ struct b2w4_ctx {
     cudaStream_t stream = nullptr;
     uint64_t launches = 0;
     bool pdl = true;  // programmatic dependent launch between consecutive kernels
-    int gemv_max_rows = 4;  // activation rows up to which the dp4a GEMV is used
+    int gemv_max_rows = 8;  // activation rows up to which the GEMV kernels are used
     int gemv_tpc_override = 0;  // tuning: cap on 8-row tiles per GEMV CTA (0 = heuristic)
     char err[512] = {0};
     // grow-only scratch (quantised activations, MoE work lists, staging)
@@ -68,6 +68,10 @@ int b2w4_launch_repack(b2w4_ctx* ctx, const void* dev_blocks, b2w4_weight* w);
 int b2w4_launch_quantize(b2w4_ctx* ctx, const float* x, int lda, int m, int k,
                          int act_rule, int8_t* q, float* scales, int layout);
 int b2w4_launch_gemv(b2w4_ctx* ctx, const b2w4_weight* w, const float* x, int lda,
+                     float* y, int ldc, int m, int act_rule, int activation,
+                     int act_n_begin, int act_n_len, int32_t* sums);
+// 2..8 activation rows per pass on the int8 tensor instruction (gemv_mma.cu)
+int b2w4_launch_gemv_mma(b2w4_ctx* ctx, const b2w4_weight* w, const float* x, int lda,
                      float* y, int ldc, int m, int act_rule, int activation,
                      int act_n_begin, int act_n_len, int32_t* sums);
 

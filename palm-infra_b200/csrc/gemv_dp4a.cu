@@ -1,4 +1,6 @@
-// W4G128 x int8 GEMV for 1..4 activation rows (decode): HBM-bound weight streaming.
+// W4G128 x int8 GEMV for one activation row (decode): HBM-bound weight streaming.
+// (Two and more rows go to the tensor-instruction kernel in gemv_mma.cu; the row-count
+// template parameter below is kept at 1.)
 //
 // Arithmetic = the reference's NEON W4A8 GEMV (kernels/matmul_w4.cpp:211-295) applied row
 // by row, with the activation quantiser (kernels/matmul_quant.cpp:578-641) fused in:
@@ -380,6 +382,9 @@ int launch_mt(b2w4_ctx* ctx, const GemvArgs& a, bool scl16, bool a32, size_t sme
 int b2w4_launch_gemv(b2w4_ctx* ctx, const b2w4_weight* w, const float* x, int lda,
                      float* y, int ldc, int m, int act_rule, int activation,
                      int act_n_begin, int act_n_len, int32_t* sums) {
+    if (m > 1)  // several rows share one pass over the weight on the tensor instruction
+        return b2w4_launch_gemv_mma(ctx, w, x, lda, y, ldc, m, act_rule, activation, act_n_begin,
+                                    act_n_len, sums);
     const bool a32 = act_rule == B2W4_ACT_G32;
     const int spg = a32 ? 4 : 1;
     const bool scl16 = w->scales_fp16 != 0;
@@ -423,9 +428,7 @@ int b2w4_launch_gemv(b2w4_ctx* ctx, const b2w4_weight* w, const float* x, int ld
         if (smem > 220 * 1024)
             return b2w4_fail(ctx, B2W4_E_INVALID, "gemv: K=%d needs %zu B shared memory",
                              w->k, smem);
-        int rc = mt == 1 ? launch_mt<1>(ctx, a, scl16, a32, smem)
-                 : mt == 2 ? launch_mt<2>(ctx, a, scl16, a32, smem)
-                           : launch_mt<4>(ctx, a, scl16, a32, smem);
+        int rc = launch_mt<1>(ctx, a, scl16, a32, smem);  // mt == 1: see the top
         if (rc != B2W4_OK)
             return rc;
     }

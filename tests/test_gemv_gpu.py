@@ -78,7 +78,8 @@ def test_quantiser_bit_exact(ctx):
 
 @pytest.mark.parametrize("m,n,k", [(1, 8, 128), (1, 7, 128), (2, 13, 256), (3, 264, 512),
                                    (4, 1000, 768), (5, 72, 512), (9, 40, 1280),
-                                   (1, 2560, 9728), (4, 520, 4096)])
+                                   (1, 2560, 9728), (4, 520, 4096), (6, 328, 640),
+                                   (7, 8, 128), (8, 1304, 2560), (8, 2560, 9728)])
 @pytest.mark.parametrize("rule", [ol.ACT_G128, ol.ACT_G32])
 def test_synthetic_shapes_bit_exact(ctx, m, n, k, rule):
     if rule == ol.ACT_G32 and k > 4096:
@@ -207,7 +208,7 @@ def test_config1_full_size_properties(ctx):
     assert y_top.tobytes() == y[:, :n // 2].tobytes()
 
 
-@pytest.mark.parametrize("m", [4, 16, 64])
+@pytest.mark.parametrize("m", [4, 8, 16, 64])
 def test_config2_decode_sweep(ctx, m):
     n, k = 9728, 2560
     blocks = pkg.synth.bg128_weight(20261125, 1, n, k)
@@ -220,7 +221,7 @@ def test_config2_decode_sweep(ctx, m):
 @pytest.mark.parametrize("m,n,k", [(129, 72, 256), (300, 200, 512), (256, 1000, 1280),
                                    (37, 2560, 9728)])
 def test_tensor_core_path_shapes_bit_exact(ctx, m, n, k):
-    """More than four activation rows go to the tcgen05 kernel: token blocks of 128, ragged
+    """More than eight activation rows go to the tcgen05 kernel: token blocks of 128, ragged
     last block, several 256-token CTAs, ragged row tiles, large K."""
     blocks = pkg.synth.bg128_weight(20261125, n + k + m, n, k)
     x = pkg.synth.activations(7, m + 1, m, k)
