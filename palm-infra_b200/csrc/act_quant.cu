@@ -39,6 +39,11 @@ __global__ void quantize_rows_kernel(const float* __restrict__ x, int lda, int m
         char4 packed = make_char4((signed char)c0, (signed char)c1, (signed char)c2,
                                   (signed char)c3);
         *reinterpret_cast<char4*>(dst + lane * 4) = packed;
+    } else if (LAYOUT == QLAYOUT_MMA) {
+        // the lane holds k = 4*lane..+3: 32-block lane/8, even-k indices 2*(lane%8) and +1
+        int8_t* blk = dst + ((lane & 7) >> 1) * 32 + (lane >> 3) * 4 + (lane & 1) * 2;
+        *reinterpret_cast<char2*>(blk) = make_char2((signed char)c0, (signed char)c2);
+        *reinterpret_cast<char2*>(blk + 16) = make_char2((signed char)c1, (signed char)c3);
     } else {
         // 32-block `sub` = lane/8 stored as 16 even-k codes then 16 odd-k codes
         int8_t* blk = dst + (lane >> 3) * 32;
@@ -108,6 +113,8 @@ int b2w4_launch_quantize(b2w4_ctx* ctx, const float* x, int lda, int m, int k,
     quantize_rows_kernel<R, L><<<grid, 256, 0, ctx->stream>>>(x, lda, m, k, q, scales)
     if (act_rule == 128 && layout == QLAYOUT_NATURAL)
         LAUNCH(128, QLAYOUT_NATURAL);
+    else if (act_rule == 128 && layout == QLAYOUT_MMA)
+        LAUNCH(128, QLAYOUT_MMA);
     else if (act_rule == 128)
         LAUNCH(128, QLAYOUT_EVEN_ODD);
     else if (layout == QLAYOUT_NATURAL)

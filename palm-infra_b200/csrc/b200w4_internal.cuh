@@ -85,6 +85,10 @@ int b2w4_launch_gemm_tc(b2w4_ctx* ctx, const b2w4_weight* w, const float* x, int
 enum {
     QLAYOUT_NATURAL = 0,  // int8 [M][K], k ascending
     QLAYOUT_EVEN_ODD = 1, // int8 [M][K], each 32-block stored as even16|odd16
+    // int8 [M][K]; inside each 128-group: [word position p 0..3][32 bytes], the 32 bytes
+    // being the even-k codes 4p..4p+3 of the four 32-blocks (16 bytes) then the odd-k ones:
+    // the B-operand words of one lane of the m16n8k32 tensor instruction, contiguous
+    QLAYOUT_MMA = 2,
 };
 
 // ---------------------------------------------------------------------------

@@ -309,7 +309,7 @@ size_t compact_smem(int num_experts) {
 
 // ---- 6. SwiGLU + quantiser: one warp per (route, 128-wide group of I) ------------------
 // inter = (g * 1/(1+exp(-g))) * u with gate = columns [0,I), up = [I,2I)
-// (kernels/moe.cpp:160-183), then the per-128 quantiser; codes in even/odd order.
+// (kernels/moe.cpp:160-183), then the per-128 quantiser; codes in tensor-operand order.
 __global__ void moe_swiglu_quant_kernel(const float* __restrict__ gu, int routes,
                                         int intermediate, int8_t* __restrict__ q,
                                         float* __restrict__ scales,
@@ -344,10 +344,13 @@ __global__ void moe_swiglu_quant_kernel(const float* __restrict__ gu, int routes
     const int c2 = b2w4_quant_code(v[2], inv), c3 = b2w4_quant_code(v[3], inv);
     if (lane == 0)
         scales[(size_t)r * groups + g] = scale;
-    int8_t* blk = q + (size_t)r * intermediate + (size_t)g * 128 + (lane >> 3) * 32;
-    const int j = (lane & 7) * 2;
-    *reinterpret_cast<char2*>(blk + j) = make_char2((signed char)c0, (signed char)c2);
-    *reinterpret_cast<char2*>(blk + 16 + j) = make_char2((signed char)c1, (signed char)c3);
+    // tensor-operand order inside the group: [word position][even words of the four
+    // 32-blocks, then the odd words]; the lane holds k = 4*lane..+3: 32-block lane/8, even
+    // codes at even index 2*(lane%8), 2*(lane%8)+1
+    int8_t* blk = q + (size_t)r * intermediate + (size_t)g * 128 + ((lane & 7) >> 1) * 32 +
+                  (lane >> 3) * 4 + (lane & 1) * 2;
+    *reinterpret_cast<char2*>(blk) = make_char2((signed char)c0, (signed char)c2);
+    *reinterpret_cast<char2*>(blk + 16) = make_char2((signed char)c1, (signed char)c3);
 }
 
 // ---- 8. combine: one block per (token, 512 hidden columns) -------------------------------
@@ -412,21 +415,24 @@ __global__ void moe_scatter_routes_kernel(const float* __restrict__ dn,
     *reinterpret_cast<float4*>(route_out + (size_t)r * hidden_size + d) = v;
 }
 
-// ---- 5 / 7. grouped expert GEMV over ragged route lists --------------------------------
-// grid = (CTAs per expert, experts).  CTA (c, e) owns `tpc` 8-row tiles of expert e's slice
-// of the aggregate weight and every route of that expert; an expert without routes costs
-// one read of two offsets.  The slice's nibble stream is bulk-copied into shared memory
-// once and reused for all of the expert's routes, four at a time.  The math is the dense
-// GEMV's: phase 1 integer group sums by dp4a (lane = (group, weight row)), phase 2 the fp32
-// chain per (tile, route, weight row) in ascending group order.
+// ---- 5 / 7. grouped expert matmul over ragged route lists ------------------------------
+// grid = (CTAs per expert, experts that have routes).  CTA (c, y) owns `tpc` 8-row tiles of
+// one expert's slice of the aggregate weight and every route of that expert.  The slice's
+// nibble stream is bulk-copied into shared memory once and reused for all of the expert's
+// routes, eight at a time: the routes are the eight columns of the warp-level int8 tensor
+// instruction (mma.sync m16n8k32), the 16 weight rows of a tile pair its rows.  The math is
+// the dense small-batch kernel's: phase 1 integer group sums (a weight word w of 8 nibbles
+// splits into hi = w & 0xF0F0F0F0, odd k as 16*q, and lo = (w ^ 0x08080808) & 0x0F0F0F0F,
+// even k as q+8; sum = mma(lo, a_even) - 8*sum(a_even) + mma(hi, a_odd)/16), phase 2 the
+// fp32 chain per (tile, route, weight row) in ascending group order.
 constexpr int kGW = 8;          // warps
 constexpr int kGT = kGW * 32;
-constexpr int kGR = 4;          // routes per pass
+constexpr int kGR = 8;          // routes per pass
 
 struct GroupedArgs {
     const uint8_t* nib;
     const void* scl;
-    const int8_t* qa;         // [rows][K] int8, even/odd order inside each 32-block
+    const int8_t* qa;         // [rows][K] int8, tensor-operand order inside each group
     const float* as;          // [rows][G]
     const int32_t* offsets;   // [E+1] route ranges of all experts
     const int32_t* active;    // experts that have routes, ascending; active[E_all] = how many
@@ -438,6 +444,25 @@ struct GroupedArgs {
     int* status;
     int k, groups, n_e, tiles_e, tpc, d_stride;
 };
+
+template <bool U>
+__device__ __forceinline__ void moe_mma_16x8x32(int (&d)[4], uint32_t a0, uint32_t a1,
+                                                uint32_t a2, uint32_t a3, uint32_t b0,
+                                                uint32_t b1) {
+    // lane (gid = lane/4, tid = lane%4): a0 row gid, k 4*tid..+3; a1 row gid+8; a2/a3 k+16;
+    // b0 k 4*tid..+3 of column gid, b1 k+16; d0/d1 row gid, columns 2*tid, 2*tid+1; d2/d3 row
+    // gid+8
+    if (U)
+        asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+            "{%8,%9}, {%0,%1,%2,%3};"
+            : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+            : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    else
+        asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+            "{%8,%9}, {%0,%1,%2,%3};"
+            : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+            : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
 
 template <bool SCL16>
 __global__ void __launch_bounds__(kGT, 2)
@@ -463,12 +488,13 @@ moe_grouped_gemv_kernel(const GroupedArgs a) {
     uint8_t* s_scl = s_w + (size_t)a.tpc * tile_bytes;
     uint4* s_qa = reinterpret_cast<uint4*>(s_scl + (size_t)a.tpc * scl_tile_bytes);  // [kGR][K]
     float* s_as = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(s_qa) + (size_t)kGR * K);
-    int32_t* s_d = reinterpret_cast<int32_t*>(s_as + kGR * G);  // [tpc][G][kGR][8] + pad
+    int* s_es = reinterpret_cast<int*>(s_as + kGR * G);  // -8 * sum of the even-k codes
+    float* s_d = reinterpret_cast<float*>(s_es + kGR * G);  // [tpc][G][kGR][8] + pad
     uint64_t* s_bar = reinterpret_cast<uint64_t*>(
         (reinterpret_cast<uintptr_t>(s_d + (size_t)a.tpc * a.d_stride) + 7) & ~uintptr_t(7));
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int gl = lane >> 3, row = lane & 7;
+    const int gid = lane >> 2, tid = lane & 3;
     const size_t gtile0 = (size_t)e * a.tiles_e + tl0;  // tile index in the aggregate
 
     if (warp == 0) {
@@ -484,8 +510,10 @@ moe_grouped_gemv_kernel(const GroupedArgs a) {
                      &s_bar[0]);
         }
     }
-    const int ipt = (G + 3) >> 2;
-    const int n_items = ntile * ipt;
+    const int npair = (ntile + 1) >> 1;
+    const int n_items = npair * G;
+    const uint32_t* s_w32 = reinterpret_cast<const uint32_t*>(s_w);
+    const int tile_words = tile_bytes >> 2;
     bool weights_ready = false;
 
     for (int base = r0; base < r1; base += kGR) {
@@ -503,6 +531,21 @@ moe_grouped_gemv_kernel(const GroupedArgs a) {
             s_as[mi * G + g] = a.as[(size_t)src_row * G + g];
         }
         __syncthreads();
+        // -8 * (sum of the even-k codes) per (route, group): the even words of a group are
+        // uint4 0, 2, 4, 6 of its 8
+        for (int i = threadIdx.x; i < mc * G; i += kGT) {
+            const uint4* q = s_qa + (size_t)i * 8;
+            int sum = 0;
+#pragma unroll
+            for (int c = 0; c < 8; c += 2) {
+                const uint4 v = q[c];
+                sum = __dp4a(0x01010101, (int)v.x, sum);
+                sum = __dp4a(0x01010101, (int)v.y, sum);
+                sum = __dp4a(0x01010101, (int)v.z, sum);
+                sum = __dp4a(0x01010101, (int)v.w, sum);
+            }
+            s_es[i] = -8 * sum;
+        }
         if (!weights_ready) {
             if (!mbar_wait_bounded(&s_bar[0])) {
                 if (lane == 0)
@@ -511,48 +554,45 @@ moe_grouped_gemv_kernel(const GroupedArgs a) {
             }
             weights_ready = true;
         }
-        // phase 1
-#pragma unroll 1
+        __syncthreads();
+        // phase 1: item = (pair of tiles = 16 weight rows, group); columns = routes
+        const int bcol = gid < mc ? gid : 0;  // unused columns repeat route 0, never read back
+        const int qa_base = bcol * (K >> 4) + tid * 2;
+#pragma unroll 2
         for (int it = warp; it < n_items; it += kGW) {
-            const int tl = it / ipt;
-            const int g = (it - tl * ipt) * 4 + gl;
-            if (g < G) {
-                const uint4* wt =
-                    reinterpret_cast<const uint4*>(s_w + (size_t)tl * tile_bytes) + g * 32 + row;
-                uint32_t we[16], wo[16];
+            const int tp = it / G;
+            const int g = it - tp * G;
+            const int t0 = tp * 2;
+            const bool two = t0 + 1 < ntile;
+            // word `lane` of the 128 bytes of (tile, group, 32-block s): row gid, k 8*tid..+7
+            const int wbase = t0 * tile_words + g * 128 + lane;
+            uint32_t lo0[4], hi0[4], lo1[4], hi1[4];
 #pragma unroll
-                for (int s = 0; s < 4; ++s) {
-                    const uint4 w = wt[s * 8];
-                    we[s * 4 + 0] = (w.x << 4) & 0xF0F0F0F0u;
-                    wo[s * 4 + 0] = w.x & 0xF0F0F0F0u;
-                    we[s * 4 + 1] = (w.y << 4) & 0xF0F0F0F0u;
-                    wo[s * 4 + 1] = w.y & 0xF0F0F0F0u;
-                    we[s * 4 + 2] = (w.z << 4) & 0xF0F0F0F0u;
-                    wo[s * 4 + 2] = w.z & 0xF0F0F0F0u;
-                    we[s * 4 + 3] = (w.w << 4) & 0xF0F0F0F0u;
-                    wo[s * 4 + 3] = w.w & 0xF0F0F0F0u;
-                }
-                int32_t* dst = s_d + (size_t)tl * a.d_stride + (size_t)g * kGR * 8 + row;
+            for (int s = 0; s < 4; ++s) {
+                const uint32_t u = s_w32[wbase + s * 32];
+                const uint32_t v = two ? s_w32[wbase + tile_words + s * 32] : 0u;  // q = 0
+                lo0[s] = (u ^ 0x08080808u) & 0x0F0F0F0Fu;
+                hi0[s] = u & 0xF0F0F0F0u;
+                lo1[s] = (v ^ 0x08080808u) & 0x0F0F0F0Fu;
+                hi1[s] = v & 0xF0F0F0F0u;
+            }
+            const uint4 be = s_qa[qa_base + g * 8], bo = s_qa[qa_base + g * 8 + 1];
+            int cl[4] = {0, 0, 0, 0}, ch[4] = {0, 0, 0, 0};
+            moe_mma_16x8x32<true>(cl, lo0[0], lo1[0], lo0[1], lo1[1], be.x, be.y);
+            moe_mma_16x8x32<false>(ch, hi0[0], hi1[0], hi0[1], hi1[1], bo.x, bo.y);
+            moe_mma_16x8x32<true>(cl, lo0[2], lo1[2], lo0[3], lo1[3], be.z, be.w);
+            moe_mma_16x8x32<false>(ch, hi0[2], hi1[2], hi0[3], hi1[3], bo.z, bo.w);
+            const int dbase = t0 * a.d_stride + g * (kGR * 8) + gid;
 #pragma unroll
-                for (int mi = 0; mi < kGR; ++mi) {
-                    if (mi < mc) {
-                        const uint4* qa = s_qa + ((size_t)mi * K + (size_t)g * 128) / 16;
-                        int total = 0;
-#pragma unroll
-                        for (int s = 0; s < 4; ++s) {
-                            const uint4 ae = qa[s * 2], ao = qa[s * 2 + 1];
-                            int p = __dp4a((int)we[s * 4 + 0], (int)ae.x, 0);
-                            int q = __dp4a((int)wo[s * 4 + 0], (int)ao.x, 0);
-                            p = __dp4a((int)we[s * 4 + 1], (int)ae.y, p);
-                            q = __dp4a((int)wo[s * 4 + 1], (int)ao.y, q);
-                            p = __dp4a((int)we[s * 4 + 2], (int)ae.z, p);
-                            q = __dp4a((int)wo[s * 4 + 2], (int)ao.z, q);
-                            p = __dp4a((int)we[s * 4 + 3], (int)ae.w, p);
-                            q = __dp4a((int)wo[s * 4 + 3], (int)ao.w, q);
-                            total += p + q;
-                        }
-                        dst[mi * 8] = total >> 4;  // nibbles were left-aligned: exact
-                    }
+            for (int c = 0; c < 2; ++c) {
+                const int mi = tid * 2 + c;
+                if (mi < mc) {
+                    const int e8 = s_es[mi * G + g];
+                    // ch sums 16*q4*a: an exact multiple of 16
+                    s_d[dbase + mi * 8] = (float)(cl[c] + e8 + (ch[c] >> 4));
+                    if (two)
+                        s_d[dbase + a.d_stride + mi * 8] =
+                            (float)(cl[2 + c] + e8 + (ch[2 + c] >> 4));
                 }
             }
         }
@@ -563,7 +603,7 @@ moe_grouped_gemv_kernel(const GroupedArgs a) {
             const int rr = t & 7, mi = (t >> 3) % kGR, tl = t / (8 * kGR);
             if (mi >= mc)
                 continue;
-            const int32_t* dsrc = s_d + (size_t)tl * a.d_stride + mi * 8 + rr;
+            const float* dsrc = s_d + tl * a.d_stride + mi * 8 + rr;
             const float* as = s_as + mi * G;
             float acc = 0.f;
 #pragma unroll 4
@@ -572,7 +612,7 @@ moe_grouped_gemv_kernel(const GroupedArgs a) {
                     SCL16 ? __half2float(
                                 reinterpret_cast<const __half*>(s_scl)[(tl * G + g) * 8 + rr])
                           : reinterpret_cast<const float*>(s_scl)[(tl * G + g) * 8 + rr];
-                acc = __fmaf_rn((float)dsrc[g * kGR * 8], __fmul_rn(ws, as[g]), acc);
+                acc = __fmaf_rn(dsrc[g * kGR * 8], __fmul_rn(ws, as[g]), acc);
             }
             const int n = (tl0 + tl) * 8 + rr;
             if (n < a.n_e)
@@ -586,8 +626,8 @@ int grouped_d_stride(int groups) { return groups * kGR * 8 + 8; }
 
 size_t grouped_smem(int k, int groups, int tpc, bool scl16) {
     return (size_t)tpc * groups * 512 + (size_t)tpc * groups * 8 * (scl16 ? 2 : 4) +
-           (size_t)kGR * k + sizeof(float) * kGR * groups +
-           sizeof(int32_t) * (size_t)tpc * grouped_d_stride(groups) + 8 + 16;
+           (size_t)kGR * k + 2 * sizeof(float) * kGR * groups +
+           sizeof(float) * (size_t)tpc * grouped_d_stride(groups) + 8 + 16;
 }
 
 int launch_grouped(b2w4_ctx* ctx, const b2w4_weight* w, int num_experts_all, int expert_begin,
@@ -614,8 +654,8 @@ int launch_grouped(b2w4_ctx* ctx, const b2w4_weight* w, int num_experts_all, int
     a.n_e = n_e;
     a.tiles_e = n_e / 8;
     int tpc = 16;
-    while (tpc > 1 && grouped_smem(w->k, w->groups, tpc, scl16) > 100 * 1024)
-        tpc >>= 1;
+    while (tpc > 2 && grouped_smem(w->k, w->groups, tpc, scl16) > 113 * 1024)
+        tpc -= 2;  // even: tiles are taken in pairs
     a.tpc = tpc;
     a.d_stride = grouped_d_stride(w->groups);
     const size_t smem = grouped_smem(w->k, w->groups, tpc, scl16);
@@ -755,7 +795,7 @@ static int moe_run(b2w4_ctx* ctx, const float* hidden_dev, int ldx, int tokens, 
     ctx->launches++;
     B2W4_CUDA(ctx, cudaGetLastError());
     if ((rc = b2w4_launch_quantize(ctx, hidden_dev, ldx, tokens, hidden_size, B2W4_ACT_G128,
-                                   q_hidden, as_hidden, QLAYOUT_EVEN_ODD)) != B2W4_OK)
+                                   q_hidden, as_hidden, QLAYOUT_MMA)) != B2W4_OK)
         return rc;
     // compact positions stay global; the grouped kernels skip experts held elsewhere
     const int32_t* local_offsets = offsets + expert_begin;
