@@ -88,7 +88,61 @@ __global__ void quantize_rows_umma_kernel(const float* __restrict__ x, int lda, 
         make_char2((signed char)c1, (signed char)c3);
 }
 
+// Same quantiser for the mma.sync GEMM: codes int8 [m][K] in tensor-operand order
+// (QLAYOUT_MMA), scales and the accumulator bias 0x4B400000 - 8 * (sum of the group's codes)
+// transposed to [groups][m_pad] so that one group of all tokens is contiguous.  (The kernel
+// multiplies unsigned nibbles q+8; starting its int32 accumulator at the bias makes it end as
+// 0x4B400000 + D, the bit pattern of the float 12582912 + D.)
+__global__ void quantize_rows_mma_kernel(const float* __restrict__ x, int lda, int m, int k,
+                                         int m_pad, int8_t* __restrict__ q,
+                                         float* __restrict__ scales_t,
+                                         int32_t* __restrict__ es_t) {
+    b2w4_pdl_launch_dependents();  // the GEMM behind may start fetching its weights
+    const int groups = k >> 7;
+    long long wid = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (wid >= (long long)m * groups)
+        return;
+    const int row = (int)(wid / groups), g = (int)(wid % groups);
+    const float4 v = *reinterpret_cast<const float4*>(x + (size_t)row * lda + (size_t)g * 128 +
+                                                      lane * 4);
+    float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1)
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+    float scale, inv;
+    b2w4_quant_params(amax, scale, inv);
+    const int c0 = b2w4_quant_code(v.x, inv), c1 = b2w4_quant_code(v.y, inv);
+    const int c2 = b2w4_quant_code(v.z, inv), c3 = b2w4_quant_code(v.w, inv);
+    int esum = c0 + c1 + c2 + c3;  // integer: order-free
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1)
+        esum += __shfl_xor_sync(0xffffffffu, esum, off);
+    if (lane == 0) {
+        scales_t[(size_t)g * m_pad + row] = scale;
+        es_t[(size_t)g * m_pad + row] = 0x4B400000 - 8 * esum;
+    }
+    // the lane holds k = 4*lane..+3: 32-block lane/8, even-k indices 2*(lane%8) and +1
+    int8_t* blk = q + (size_t)row * k + (size_t)g * 128 + ((lane & 7) >> 1) * 32 +
+                  (lane >> 3) * 4 + (lane & 1) * 2;
+    *reinterpret_cast<char2*>(blk) = make_char2((signed char)c0, (signed char)c2);
+    *reinterpret_cast<char2*>(blk + 16) = make_char2((signed char)c1, (signed char)c3);
+}
+
 }  // namespace
+
+int b2w4_launch_quantize_mma(b2w4_ctx* ctx, const float* x, int lda, int m, int k, int m_pad,
+                             int8_t* q, float* scales_t, int32_t* es_t) {
+    if ((reinterpret_cast<uintptr_t>(x) & 15) || (lda & 3))
+        return b2w4_fail(ctx, B2W4_E_INVALID, "quantize: rows must be 16-byte aligned");
+    long long warps = (long long)m * (k / 128);
+    int grid = (int)((warps * 32 + 255) / 256);
+    quantize_rows_mma_kernel<<<grid, 256, 0, ctx->stream>>>(x, lda, m, k, m_pad, q, scales_t,
+                                                            es_t);
+    ctx->launches++;
+    B2W4_CUDA(ctx, cudaGetLastError());
+    return B2W4_OK;
+}
 
 int b2w4_launch_quantize_umma(b2w4_ctx* ctx, const float* x, int lda, int m, int k, int m_pad,
                               int8_t* q, float* scales) {

@@ -33,6 +33,9 @@ struct b2w4_ctx {
     uint64_t launches = 0;
     bool pdl = true;  // programmatic dependent launch between consecutive kernels
     int gemv_max_rows = 8;  // activation rows up to which the GEMV kernels are used
+    // 0 = mma.sync GEMM when its resident mode fits (few tokens), else the tcgen05 GEMM;
+    // tuning: 1 = always the tcgen05 GEMM, 2 = the mma.sync GEMM whenever the shape fits it
+    int gemm_kind = 0;
     int gemv_tpc_override = 0;  // tuning: cap on 8-row tiles per GEMV CTA (0 = heuristic)
     char err[512] = {0};
     // grow-only scratch (quantised activations, MoE work lists, staging)
@@ -67,6 +70,14 @@ int b2w4_reserve(b2w4_ctx* ctx, int slot, size_t bytes, void** out);
 int b2w4_launch_repack(b2w4_ctx* ctx, const void* dev_blocks, b2w4_weight* w);
 int b2w4_launch_quantize(b2w4_ctx* ctx, const float* x, int lda, int m, int k,
                          int act_rule, int8_t* q, float* scales, int layout);
+// 9..256 rows per launch on mma.sync with register accumulators (gemm_mma.cu)
+bool b2w4_gemm_mma_fits(const b2w4_weight* w, int m);
+bool b2w4_gemm_mma_resident(const b2w4_weight* w, int m, int sm_count);
+int b2w4_launch_gemm_mma(b2w4_ctx* ctx, const b2w4_weight* w, const float* x, int lda,
+                         float* y, int ldc, int m, int activation, int act_n_begin,
+                         int act_n_len);
+int b2w4_launch_quantize_mma(b2w4_ctx* ctx, const float* x, int lda, int m, int k, int m_pad,
+                             int8_t* q, float* scales_t, int32_t* es_t);
 int b2w4_launch_gemv(b2w4_ctx* ctx, const b2w4_weight* w, const float* x, int lda,
                      float* y, int ldc, int m, int act_rule, int activation,
                      int act_n_begin, int act_n_len, int32_t* sums);

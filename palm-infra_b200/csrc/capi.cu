@@ -63,6 +63,11 @@ int b2w4_ctx_create(int device, b2w4_ctx** out) {
     const char* tpc = getenv("B2W4_GEMV_TPC");  // tuning: cap on tiles per GEMV CTA
     if (tpc && atoi(tpc) > 0)
         ctx->gemv_tpc_override = atoi(tpc);
+    const char* gk = getenv("B2W4_GEMM");  // tuning: "tc" / "mma" force one many-row kernel
+    if (gk && gk[0] == 't')
+        ctx->gemm_kind = 1;
+    if (gk && gk[0] == 'm')
+        ctx->gemm_kind = 2;
     const char* gmr = getenv("B2W4_GEMV_MAX_ROWS");  // tuning/debug: rows kept on the GEMV
     if (gmr && atoi(gmr) > 0)
         ctx->gemv_max_rows = atoi(gmr);
@@ -226,12 +231,22 @@ static int check_matmul(b2w4_ctx* ctx, const b2w4_weight* w, const void* x, int 
     return B2W4_OK;
 }
 
-// Up to four activation rows stream the weight once through the dp4a GEMV; more rows go
-// to the tensor-core kernel (per-128 rule, K <= 10240).  Both produce the same bits.
+// Up to eight activation rows stream the weight once through the GEMV kernels (one row:
+// dp4a; two to eight: the warp-level int8 tensor instruction); more rows go to the tcgen05
+// kernel (per-128 rule, K <= 10240).  All produce the same bits.
 static int matmul_dispatch(b2w4_ctx* ctx, const b2w4_weight* w, const float* x, int lda,
                            float* y, int ldc, int m, int act_rule, int activation,
                            int act_n_begin, int act_n_len) {
-    const bool tc = m > ctx->gemv_max_rows && act_rule == B2W4_ACT_G128 && w->groups <= 80;
+    const bool rows = m > ctx->gemv_max_rows && act_rule == B2W4_ACT_G128;
+    // unaligned activation rows: the tcgen05 path's quantiser reads scalars
+    const bool vec = (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (lda & 3) == 0;
+    const bool tc = rows && w->groups <= 80;
+    const bool mma = rows && vec && b2w4_gemm_mma_fits(w, m) &&
+                     (ctx->gemm_kind == 2 || (ctx->gemm_kind == 0 &&
+                      (!tc || b2w4_gemm_mma_resident(w, m, ctx->sm_count))));
+    if (mma)
+        return b2w4_launch_gemm_mma(ctx, w, x, lda, y, ldc, m, activation, act_n_begin,
+                                    act_n_len);
     if (tc)
         return b2w4_launch_gemm_tc(ctx, w, x, lda, y, ldc, m, activation, act_n_begin,
                                    act_n_len);

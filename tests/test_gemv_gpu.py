@@ -12,6 +12,31 @@ pkg = load_package()
 pytestmark = pytest.mark.gpu
 
 
+def _forced_ctx(kind):
+    import os
+    os.environ["B2W4_GEMM"] = kind
+    try:
+        return pkg.capi.Context(0)
+    finally:
+        del os.environ["B2W4_GEMM"]
+
+
+@pytest.fixture(scope="module")
+def ctx_tc():
+    """A context that sends every many-row matmul to the tcgen05 kernel."""
+    c = _forced_ctx("tc")
+    yield c
+    c.close()
+
+
+@pytest.fixture(scope="module")
+def ctx_mma():
+    """A context that sends every many-row matmul that fits to the mma.sync kernel."""
+    c = _forced_ctx("mma")
+    yield c
+    c.close()
+
+
 @pytest.fixture(scope="module")
 def ctx():
     c = pkg.capi.Context(0)
@@ -208,7 +233,7 @@ def test_config1_full_size_properties(ctx):
     assert y_top.tobytes() == y[:, :n // 2].tobytes()
 
 
-@pytest.mark.parametrize("m", [4, 8, 16, 64])
+@pytest.mark.parametrize("m", [4, 8, 16, 33, 64])
 def test_config2_decode_sweep(ctx, m):
     n, k = 9728, 2560
     blocks = pkg.synth.bg128_weight(20261125, 1, n, k)
@@ -220,9 +245,12 @@ def test_config2_decode_sweep(ctx, m):
 
 @pytest.mark.parametrize("m,n,k", [(129, 72, 256), (300, 200, 512), (256, 1000, 1280),
                                    (37, 2560, 9728)])
-def test_tensor_core_path_shapes_bit_exact(ctx, m, n, k):
-    """More than eight activation rows go to the tcgen05 kernel: token blocks of 128, ragged
-    last block, several 256-token CTAs, ragged row tiles, large K."""
+@pytest.mark.parametrize("kind", ["mma", "tc"])
+def test_many_row_paths_shapes_bit_exact(ctx_mma, ctx_tc, kind, m, n, k):
+    """More than eight activation rows go to the mma.sync GEMM (register accumulators) or,
+    when forced or when the shape does not fit it, to the tcgen05 GEMM: ragged token counts,
+    several launches of 256 tokens, ragged row tiles, large K."""
+    ctx = ctx_tc if kind == "tc" else ctx_mma
     blocks = pkg.synth.bg128_weight(20261125, n + k + m, n, k)
     x = pkg.synth.activations(7, m + 1, m, k)
     x[m // 2, 128:256] = 0.0
