@@ -237,6 +237,41 @@ def moe_layer(torch, pkg, ctx, args):
     return out
 
 
+def moe_layer_ep(torch, dist, pkg, ctx, rank, world):
+    """The same Qwen3-30B-A3B-shaped MoE layer expert-parallel over `world` ranks: each rank
+    holds 128/world experts, computes the routes of its experts, one NCCL all-reduce of the
+    [tokens*top_k, H] route buffer, ordered combine on every rank.  Device time, max over
+    ranks."""
+    h, e, top_k, inter = 2048, 128, 8, 768
+    router = torch.from_numpy(pkg.synth.router_weight(SEED_W, 70, e, h).view(np.int16)).cuda()
+    gu_blocks = pkg.synth.bg128_weight(SEED_W, 71, e * 2 * inter, h)
+    dn_blocks = pkg.synth.bg128_weight(SEED_W, 72, e * h, inter)
+    op = pkg.expert_parallel.build_device_moe(ctx, router, gu_blocks, dn_blocks, e, top_k, h,
+                                              inter, rank, world,
+                                              lambda t: dist.all_reduce(t))
+    out = {}
+    for t in (1, 256):
+        x = torch.from_numpy(pkg.synth.activations(SEED_X, 80 + t, t, h)).cuda()
+        y = torch.zeros((t, h), dtype=torch.float32, device="cuda")
+        op.forward(x, y)  # grows scratch, warms NCCL
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            ctx.set_stream(side.cuda_stream)
+            with torch.cuda.graph(g, stream=side):
+                op.forward(x, y)
+        ctx.set_stream(torch.cuda.current_stream().cuda_stream)
+        ms = time_steps(torch, g.replay, 20, 3, lambda: dist.barrier())
+        tm = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(tm, op=dist.ReduceOp.MAX)
+        ms = float(tm.item())
+        out[f"tokens{t}"] = {"us_per_layer": ms * 1e3,
+                             "tokens_per_s_per_layer": t / (ms * 1e-3),
+                             "exchange_bytes": t * top_k * h * 4}
+    return out
+
+
 def decode_walk(torch, pkg, ctx, args):
     """The W4 matmuls of one decode token of a Qwen3-4B-shaped dense decoder (benchmark
     configuration 3): 36 layers of qkv [6144,2560], o [2560,4096], gate_up [19456,2560],
@@ -360,6 +395,12 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    if args.moe_only:  # one leg alone (profiling commands)
+        if rank == 0:
+            print(json.dumps({"moe30b_layer": moe_layer(torch, pkg, ctx, args)}), flush=True)
+        ctx.close()
+        return
+
     # ---- headline: M=1, resident inputs -------------------------------------------------
     l0 = ctx.launches
     make_step(args.rows, graph=False)()
@@ -438,6 +479,10 @@ def run_ours(args):
             "sample": f"{repeat} GEMVs rotating 16 weight copies, isa {isa}, "
                       f"W4A32 arithmetic ({sec * 1e3:.3f} ms per GEMV)"}
 
+    if world > 1 and not args.headline_only and 128 % world == 0:
+        ep = moe_layer_ep(torch, dist, pkg, ctx, rank, world)  # every rank takes part
+        line["moe30b_layer_ep"] = ep
+
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -467,6 +512,8 @@ def main():
     ap.add_argument("--rows", type=int, default=1,
                     help="activation rows of the timed matmul (1 = the headline GEMV; other "
                          "values are for profiling the batched kernels)")
+    ap.add_argument("--moe-only", action="store_true",
+                    help="run only the MoE layer leg of the sweep (single GPU)")
     ap.add_argument("--headline-only", action="store_true",
                     help="skip the e2e, sweep and CPU-baseline legs (profiling)")
     args = ap.parse_args()
