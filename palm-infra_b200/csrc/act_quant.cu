@@ -10,6 +10,7 @@ namespace {
 template <int RULE, int LAYOUT>
 __global__ void quantize_rows_kernel(const float* __restrict__ x, int lda, int m, int k,
                                      int8_t* __restrict__ q, float* __restrict__ scales) {
+    b2w4_pdl_chain_entry();
     const int groups = k >> 7;
     long long wid = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
@@ -163,8 +164,9 @@ int b2w4_launch_quantize(b2w4_ctx* ctx, const float* x, int lda, int m, int k,
         return b2w4_fail(ctx, B2W4_E_INVALID, "quantize: act_rule must be 128 or 32");
     long long warps = (long long)m * (k / 128);
     int grid = (int)((warps * 32 + 255) / 256);
-#define LAUNCH(R, L)                                                              \
-    quantize_rows_kernel<R, L><<<grid, 256, 0, ctx->stream>>>(x, lda, m, k, q, scales)
+#define LAUNCH(R, L)                                                                         \
+    B2W4_CUDA(ctx, b2w4_launch_chained(ctx->pdl, quantize_rows_kernel<R, L>, dim3(grid),        \
+                                       dim3(256), 0, ctx->stream, x, lda, m, k, q, scales))
     if (act_rule == 128 && layout == QLAYOUT_NATURAL)
         LAUNCH(128, QLAYOUT_NATURAL);
     else if (act_rule == 128 && layout == QLAYOUT_MMA)

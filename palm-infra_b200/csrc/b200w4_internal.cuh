@@ -169,3 +169,29 @@ __device__ __forceinline__ void b2w4_pdl_wait() {
 __device__ __forceinline__ void b2w4_pdl_launch_dependents() {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
+// First statements of a small kernel in a chain of dependent launches: let the next kernel's
+// CTAs be scheduled now, then wait until everything the previous kernel wrote is visible.
+// Nothing may touch memory before this.  (Without the launch attribute both are no-ops.)
+__device__ __forceinline__ void b2w4_pdl_chain_entry() {
+    b2w4_pdl_launch_dependents();
+    b2w4_pdl_wait();
+}
+
+// Launch with programmatic stream serialisation: the kernel may become resident while its
+// predecessor in the stream still runs (it must call b2w4_pdl_wait / b2w4_pdl_chain_entry
+// before touching memory).  Shortens the gap between short dependent kernels.
+template <typename... KArgs, typename... Args>
+inline cudaError_t b2w4_launch_chained(bool pdl, void (*kernel)(KArgs...), dim3 grid, dim3 block,
+                                       size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = pdl ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}

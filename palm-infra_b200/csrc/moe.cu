@@ -75,17 +75,13 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
 // consecutive columns per step (one 16-byte load of router halves, two of each token's
 // activations); the warp's router rows are reused for its 4 tokens.
 constexpr int kRouterTok = 4;
+// logits of tokens t0..t0+3 against experts e0..e0+EPW-1, computed by one warp
 template <int EPW>
-__global__ void moe_router_logits_kernel(const float* __restrict__ hidden, int ldx, int tokens,
-                                         int hidden_size, const __half* __restrict__ router,
-                                         int num_experts, float* __restrict__ logits) {
-    const int eblocks = (num_experts + EPW - 1) / EPW;
-    const long long wid = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-    const int lane = threadIdx.x & 31;
-    const int tblocks = (tokens + kRouterTok - 1) / kRouterTok;
-    if (wid >= (long long)tblocks * eblocks)
-        return;
-    const int t0 = (int)(wid / eblocks) * kRouterTok, e0 = (int)(wid % eblocks) * EPW;
+__device__ __forceinline__ void router_logits_warp(const float* __restrict__ hidden, int ldx,
+                                                   int tokens, int hidden_size,
+                                                   const __half* __restrict__ router,
+                                                   int num_experts, float* __restrict__ logits,
+                                                   int t0, int e0, int lane) {
     double acc[kRouterTok][EPW];
 #pragma unroll
     for (int i = 0; i < kRouterTok; ++i)
@@ -133,12 +129,29 @@ __global__ void moe_router_logits_kernel(const float* __restrict__ hidden, int l
         }
 }
 
+template <int EPW>
+__global__ void moe_router_logits_kernel(const float* __restrict__ hidden, int ldx, int tokens,
+                                         int hidden_size, const __half* __restrict__ router,
+                                         int num_experts, float* __restrict__ logits) {
+    b2w4_pdl_chain_entry();
+    const int eblocks = (num_experts + EPW - 1) / EPW;
+    const long long wid = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    const int tblocks = (tokens + kRouterTok - 1) / kRouterTok;
+    if (wid >= (long long)tblocks * eblocks)
+        return;
+    const int t0 = (int)(wid / eblocks) * kRouterTok, e0 = (int)(wid % eblocks) * EPW;
+    router_logits_warp<EPW>(hidden, ldx, tokens, hidden_size, router, num_experts, logits, t0, e0,
+                            lane);
+}
+
 // Fallback for activations whose rows are not 16-byte aligned: one warp per (token, expert),
 // scalar loads.
 __global__ void moe_router_logits_scalar_kernel(const float* __restrict__ hidden, int ldx,
                                                 int tokens, int hidden_size,
                                                 const __half* __restrict__ router,
                                                 int num_experts, float* __restrict__ logits) {
+    b2w4_pdl_chain_entry();
     const long long wid = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
     if (wid >= (long long)tokens * num_experts)
@@ -165,13 +178,11 @@ __global__ void moe_router_logits_scalar_kernel(const float* __restrict__ hidden
 // sequential fp32 sum, times 1/sum (:157-166).
 constexpr int kMaxTopK = 16;
 constexpr int kSelectMaxExperts = 1024;  // 32 lanes x 32 mask bits
-__global__ void moe_select_routes_kernel(const float* __restrict__ logits, int tokens,
-                                         int num_experts, int top_k, int32_t* __restrict__ idx,
-                                         float* __restrict__ weights) {
-    const int t = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-    const int lane = threadIdx.x & 31;
-    if (t >= tokens)
-        return;
+// routes of token t, by one warp; also returns lane j's expert (lanes >= top_k: undefined)
+__device__ __forceinline__ int select_routes_warp(const float* logits, int t,
+                                                  int num_experts, int top_k,
+                                                  int32_t* __restrict__ idx,
+                                                  float* __restrict__ weights, int lane) {
     const float* row = logits + (size_t)t * num_experts;
     uint32_t taken = 0;       // bit s: expert lane + 32*s already selected
     float my_v = -INFINITY;   // lane j keeps the j-th selected logit
@@ -213,6 +224,18 @@ __global__ void moe_select_routes_kernel(const float* __restrict__ logits, int t
         idx[(size_t)t * top_k + lane] = my_e;
         weights[(size_t)t * top_k + lane] = __fmul_rn(ex, inverse);
     }
+    return my_e;
+}
+
+__global__ void moe_select_routes_kernel(const float* __restrict__ logits, int tokens,
+                                         int num_experts, int top_k, int32_t* __restrict__ idx,
+                                         float* __restrict__ weights) {
+    b2w4_pdl_chain_entry();
+    const int t = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (t >= tokens)
+        return;
+    select_routes_warp(logits, t, num_experts, top_k, idx, weights, lane);
 }
 
 // ---- 3. compaction: one block ------------------------------------------------------------
@@ -229,6 +252,7 @@ __global__ void __launch_bounds__(kCompactThreads)
 moe_compact_kernel(const int32_t* __restrict__ idx, int tokens, int top_k, int num_experts,
                    int32_t* __restrict__ offsets, int32_t* __restrict__ route_token,
                    int32_t* __restrict__ pos, int32_t* __restrict__ active) {
+    b2w4_pdl_chain_entry();
     extern __shared__ int s_int[];
     const int E = num_experts;
     const int nw = min(kCompactThreads / 32, max(1, kCompactTableInts / E));  // warps placing
@@ -307,6 +331,102 @@ size_t compact_smem(int num_experts) {
     return sizeof(int) * ((size_t)2 * num_experts + 1 + (size_t)nw * num_experts);
 }
 
+// ---- 1-4 fused for a few tokens (decode) ---------------------------------------------------
+// One launch instead of four: every warp of the grid quantises its share of the hidden rows
+// and computes its share of the router logits; the block that arrives last at a counter (no
+// block waits for another) selects the routes, one warp per token, and compacts them.  Same
+// device functions, same bits as the separate kernels.
+constexpr int kFusedTokens = 8;
+constexpr int kFusedRoutes = 128;
+constexpr int kFusedThreads = 128;
+__global__ void __launch_bounds__(kFusedThreads)
+moe_route_fused_kernel(const float* __restrict__ hidden, int ldx, int tokens, int hidden_size,
+                       const __half* __restrict__ router, int num_experts, int top_k,
+                       float* logits, int32_t* __restrict__ idx, float* __restrict__ weights,
+                       int32_t* __restrict__ offsets, int32_t* __restrict__ route_token,
+                       int32_t* __restrict__ pos, int32_t* __restrict__ active,
+                       int8_t* __restrict__ q_hidden, float* __restrict__ as_hidden,
+                       int* __restrict__ arrivals) {
+    b2w4_pdl_chain_entry();
+    __shared__ int s_last;
+    __shared__ int s_route[kFusedRoutes];  // expert of route i = (token, j)
+    extern __shared__ int s_cnt[];         // [E+1]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int gwarp = blockIdx.x * (kFusedThreads / 32) + warp;
+    const int nwarps = gridDim.x * (kFusedThreads / 32);
+    // hidden rows -> int8, one warp per (token, 128-group), codes in tensor-operand order
+    const int G = hidden_size >> 7;
+    for (int task = gwarp; task < tokens * G; task += nwarps) {
+        const int row = task / G, g = task - row * G;
+        const float4 v = *reinterpret_cast<const float4*>(hidden + (size_t)row * ldx +
+                                                          (size_t)g * 128 + lane * 4);
+        float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1)
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+        float scale, inv;
+        b2w4_quant_params(amax, scale, inv);
+        const int c0 = b2w4_quant_code(v.x, inv), c1 = b2w4_quant_code(v.y, inv);
+        const int c2 = b2w4_quant_code(v.z, inv), c3 = b2w4_quant_code(v.w, inv);
+        if (lane == 0)
+            as_hidden[(size_t)row * G + g] = scale;
+        int8_t* blk = q_hidden + (size_t)row * hidden_size + (size_t)g * 128 +
+                      ((lane & 7) >> 1) * 32 + (lane >> 3) * 4 + (lane & 1) * 2;
+        *reinterpret_cast<char2*>(blk) = make_char2((signed char)c0, (signed char)c2);
+        *reinterpret_cast<char2*>(blk + 16) = make_char2((signed char)c1, (signed char)c3);
+    }
+    // router logits, one warp per expert and block of four tokens
+    for (int e = gwarp; e < num_experts; e += nwarps)
+        for (int t0 = 0; t0 < tokens; t0 += kRouterTok)
+            router_logits_warp<1>(hidden, ldx, tokens, hidden_size, router, num_experts, logits,
+                                  t0, e, lane);
+    // arrival: the last block to get here sees every block's logits
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        s_last = atomicAdd(arrivals, 1) == (int)gridDim.x - 1;
+    }
+    __syncthreads();
+    if (!s_last)
+        return;
+    __threadfence();
+    for (int t = warp; t < tokens; t += kFusedThreads / 32) {
+        const int e = select_routes_warp(logits, t, num_experts, top_k, idx, weights, lane);
+        if (lane < top_k)
+            s_route[t * top_k + lane] = e;
+    }
+    for (int e = threadIdx.x; e <= num_experts; e += kFusedThreads)
+        s_cnt[e] = 0;
+    __syncthreads();
+    const int routes = tokens * top_k;
+    if (threadIdx.x < routes)
+        atomicAdd(&s_cnt[s_route[threadIdx.x]], 1);  // integer counts: order-free
+    __syncthreads();
+    // thread e: offset = routes of lower experts, its routes placed in token order
+    for (int e = threadIdx.x; e <= num_experts; e += kFusedThreads) {
+        int run = 0, rank = 0;
+        for (int q = 0; q < e; ++q) {
+            const int c = s_cnt[q];
+            run += c;
+            rank += c > 0;
+        }
+        offsets[e] = run;
+        if (e == num_experts) {
+            active[num_experts] = rank;
+        } else if (s_cnt[e] > 0) {
+            active[rank] = e;
+            for (int i = 0; i < routes; ++i)
+                if (s_route[i] == e) {
+                    route_token[run] = i / top_k;
+                    pos[i] = run;
+                    ++run;
+                }
+        }
+    }
+    if (threadIdx.x == 0)
+        *arrivals = 0;  // ready for the next launch
+}
+
 // ---- 6. SwiGLU + quantiser: one warp per (route, 128-wide group of I) ------------------
 // inter = (g * 1/(1+exp(-g))) * u with gate = columns [0,I), up = [I,2I)
 // (kernels/moe.cpp:160-183), then the per-128 quantiser; codes in tensor-operand order.
@@ -315,6 +435,7 @@ __global__ void moe_swiglu_quant_kernel(const float* __restrict__ gu, int routes
                                         float* __restrict__ scales,
                                         const int32_t* __restrict__ route_lo,
                                         const int32_t* __restrict__ route_hi) {
+    b2w4_pdl_chain_entry();
     const int groups = intermediate >> 7;
     const long long wid = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
@@ -362,6 +483,7 @@ __global__ void __launch_bounds__(kCombineThreads)
 moe_combine_kernel(const float* __restrict__ dn, const int32_t* __restrict__ idx,
                    const float* __restrict__ weights, const int32_t* __restrict__ pos,
                    int tokens, int top_k, int hidden_size, float* __restrict__ out, int ldo) {
+    b2w4_pdl_chain_entry();
     __shared__ int s_row[kMaxTopK];
     __shared__ float s_w[kMaxTopK];
     const int t = blockIdx.y;
@@ -404,6 +526,7 @@ __global__ void moe_scatter_routes_kernel(const float* __restrict__ dn,
                                           const int32_t* __restrict__ pos, int routes,
                                           int hidden_size, int expert_begin, int expert_count,
                                           float* __restrict__ route_out) {
+    b2w4_pdl_chain_entry();
     const int r = blockIdx.y;
     const int d = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
     if (r >= routes || d >= hidden_size)
@@ -467,6 +590,7 @@ __device__ __forceinline__ void moe_mma_16x8x32(int (&d)[4], uint32_t a0, uint32
 template <bool SCL16>
 __global__ void __launch_bounds__(kGT, 2)
 moe_grouped_gemv_kernel(const GroupedArgs a) {
+    b2w4_pdl_chain_entry();
     extern __shared__ __align__(128) uint8_t smem[];
     // blockIdx.y walks the experts that have routes, not all experts: a decode token
     // touches top_k of them
@@ -669,7 +793,7 @@ int launch_grouped(b2w4_ctx* ctx, const b2w4_weight* w, int num_experts_all, int
         configured[scl16] = smem;
     }
     dim3 grid((a.tiles_e + tpc - 1) / tpc, routes < num_experts_all ? routes : num_experts_all);
-    kern<<<grid, kGT, smem, ctx->stream>>>(a);
+    B2W4_CUDA(ctx, b2w4_launch_chained(ctx->pdl, kern, grid, dim3(kGT), smem, ctx->stream, a));
     ctx->launches++;
     B2W4_CUDA(ctx, cudaGetLastError());
     return B2W4_OK;
@@ -693,8 +817,9 @@ int b2w4_moe_select_routes(b2w4_ctx* ctx, const float* logits_dev, int tokens,
                          "select_routes: need 0 < top_k <= min(experts, %d), experts <= %d "
                          "(tokens=%d experts=%d top_k=%d)", kMaxTopK, kSelectMaxExperts, tokens,
                          num_experts, top_k);
-    moe_select_routes_kernel<<<(tokens + 3) / 4, 128, 0, ctx->stream>>>(
-        logits_dev, tokens, num_experts, top_k, indices_dev, weights_dev);
+    B2W4_CUDA(ctx, b2w4_launch_chained(ctx->pdl, moe_select_routes_kernel, dim3((tokens + 3) / 4),
+                                       dim3(128), 0, ctx->stream, logits_dev, tokens,
+                                       num_experts, top_k, indices_dev, weights_dev));
     ctx->launches++;
     B2W4_CUDA(ctx, cudaGetLastError());
     return B2W4_OK;
@@ -771,32 +896,55 @@ static int moe_run(b2w4_ctx* ctx, const float* hidden_dev, int ldx, int tokens, 
     cudaStream_t st = ctx->stream;
 
     const __half* router = static_cast<const __half*>(router_fp16_dev);
-    if ((reinterpret_cast<uintptr_t>(hidden_dev) | reinterpret_cast<uintptr_t>(router)) % 16 ||
-        ldx % 4) {
-        const long long threads = (long long)tokens * num_experts * 32;
-        moe_router_logits_scalar_kernel<<<(int)((threads + 255) / 256), 256, 0, st>>>(
-            hidden_dev, ldx, tokens, hidden_size, router, num_experts, logits);
-    } else if (tokens <= 8) {  // decode: one expert per warp keeps every SM busy
-        const long long warps = (long long)((tokens + kRouterTok - 1) / kRouterTok) * num_experts;
-        moe_router_logits_kernel<1><<<(int)((warps * 32 + 127) / 128), 128, 0, st>>>(
-            hidden_dev, ldx, tokens, hidden_size, router, num_experts, logits);
+    const bool aligned =
+        (reinterpret_cast<uintptr_t>(hidden_dev) | reinterpret_cast<uintptr_t>(router)) % 16 == 0 &&
+        ldx % 4 == 0;
+    const bool fused = aligned && tokens <= kFusedTokens && routes <= kFusedRoutes;
+    if (fused) {
+        // enough blocks to spread the router rows over the SMs, one warp per expert
+        const int blocks = (num_experts + kFusedThreads / 32 - 1) / (kFusedThreads / 32);
+        B2W4_CUDA(ctx, b2w4_launch_chained(
+                           ctx->pdl, moe_route_fused_kernel, dim3(blocks), dim3(kFusedThreads),
+                           sizeof(int) * (num_experts + 1), st, hidden_dev, ldx, tokens,
+                           hidden_size, router, num_experts, top_k, logits, idx, wts, offsets,
+                           route_token, pos, active, q_hidden, as_hidden, ctx->flag_dev + 4));
+        ctx->launches++;
     } else {
-        const long long warps =
-            (long long)((tokens + kRouterTok - 1) / kRouterTok) * ((num_experts + 3) / 4);
-        moe_router_logits_kernel<4><<<(int)((warps * 32 + 127) / 128), 128, 0, st>>>(
-            hidden_dev, ldx, tokens, hidden_size, router, num_experts, logits);
+        if (!aligned) {
+            const long long threads = (long long)tokens * num_experts * 32;
+            B2W4_CUDA(ctx, b2w4_launch_chained(ctx->pdl, moe_router_logits_scalar_kernel,
+                                               dim3((int)((threads + 255) / 256)), dim3(256), 0, st,
+                                               hidden_dev, ldx, tokens, hidden_size, router,
+                                               num_experts, logits));
+        } else if (tokens <= 8) {  // decode: one expert per warp keeps every SM busy
+            const long long warps = (long long)((tokens + kRouterTok - 1) / kRouterTok) * num_experts;
+            B2W4_CUDA(ctx, b2w4_launch_chained(ctx->pdl, moe_router_logits_kernel<1>,
+                                               dim3((int)((warps * 32 + 127) / 128)), dim3(128), 0, st,
+                                               hidden_dev, ldx, tokens, hidden_size, router,
+                                               num_experts, logits));
+        } else {
+            const long long warps =
+                (long long)((tokens + kRouterTok - 1) / kRouterTok) * ((num_experts + 3) / 4);
+            B2W4_CUDA(ctx, b2w4_launch_chained(ctx->pdl, moe_router_logits_kernel<4>,
+                                               dim3((int)((warps * 32 + 127) / 128)), dim3(128), 0, st,
+                                               hidden_dev, ldx, tokens, hidden_size, router,
+                                               num_experts, logits));
+        }
+        ctx->launches++;
+        B2W4_CUDA(ctx, b2w4_launch_chained(ctx->pdl, moe_select_routes_kernel, dim3((tokens + 3) / 4),
+                                           dim3(128), 0, st, logits, tokens, num_experts, top_k, idx,
+                                           wts));
+        ctx->launches++;
+        B2W4_CUDA(ctx, b2w4_launch_chained(ctx->pdl, moe_compact_kernel, dim3(1),
+                                           dim3(kCompactThreads), compact_smem(num_experts), st, idx,
+                                           tokens, top_k, num_experts, offsets, route_token, pos,
+                                           active));
+        ctx->launches++;
+        B2W4_CUDA(ctx, cudaGetLastError());
+        if ((rc = b2w4_launch_quantize(ctx, hidden_dev, ldx, tokens, hidden_size, B2W4_ACT_G128,
+                                       q_hidden, as_hidden, QLAYOUT_MMA)) != B2W4_OK)
+            return rc;
     }
-    ctx->launches++;
-    moe_select_routes_kernel<<<(tokens + 3) / 4, 128, 0, st>>>(logits, tokens, num_experts,
-                                                               top_k, idx, wts);
-    ctx->launches++;
-    moe_compact_kernel<<<1, kCompactThreads, compact_smem(num_experts), st>>>(
-        idx, tokens, top_k, num_experts, offsets, route_token, pos, active);
-    ctx->launches++;
-    B2W4_CUDA(ctx, cudaGetLastError());
-    if ((rc = b2w4_launch_quantize(ctx, hidden_dev, ldx, tokens, hidden_size, B2W4_ACT_G128,
-                                   q_hidden, as_hidden, QLAYOUT_MMA)) != B2W4_OK)
-        return rc;
     // compact positions stay global; the grouped kernels skip experts held elsewhere
     const int32_t* local_offsets = offsets + expert_begin;
     const bool partial = expert_count != num_experts;
@@ -806,9 +954,11 @@ static int moe_run(b2w4_ctx* ctx, const float* hidden_dev, int ldx, int tokens, 
         return rc;
     {
         const long long threads = (long long)routes * gi * 32;
-        moe_swiglu_quant_kernel<<<(int)((threads + 255) / 256), 256, 0, st>>>(
-            static_cast<const float*>(gu), routes, intermediate, q_inter, as_inter,
-            partial ? local_offsets : nullptr, partial ? local_offsets + expert_count : nullptr);
+        B2W4_CUDA(ctx, b2w4_launch_chained(
+                           ctx->pdl, moe_swiglu_quant_kernel, dim3((int)((threads + 255) / 256)),
+                           dim3(256), 0, st, static_cast<const float*>(gu), routes, intermediate,
+                           q_inter, as_inter, partial ? local_offsets : nullptr,
+                           partial ? local_offsets + expert_count : nullptr));
         ctx->launches++;
     }
     if ((rc = launch_grouped(ctx, down, num_experts, expert_begin, expert_count, routes, q_inter,
@@ -817,16 +967,17 @@ static int moe_run(b2w4_ctx* ctx, const float* hidden_dev, int ldx, int tokens, 
         return rc;
     if (route_out) {
         dim3 grid((hidden_size / 4 + 255) / 256, routes);
-        moe_scatter_routes_kernel<<<grid, 256, 0, st>>>(static_cast<const float*>(dn), idx, pos,
-                                                        routes, hidden_size, expert_begin,
-                                                        expert_count, route_out);
+        B2W4_CUDA(ctx, b2w4_launch_chained(ctx->pdl, moe_scatter_routes_kernel, grid, dim3(256), 0,
+                                           st, static_cast<const float*>(dn), idx, pos, routes,
+                                           hidden_size, expert_begin, expert_count, route_out));
         ctx->launches++;
     }
     if (out_dev) {
         dim3 grid((hidden_size / 4 + kCombineThreads - 1) / kCombineThreads, tokens);
-        moe_combine_kernel<<<grid, kCombineThreads, 0, st>>>(static_cast<const float*>(dn), idx,
-                                                             wts, pos, tokens, top_k,
-                                                             hidden_size, out_dev, ldo);
+        B2W4_CUDA(ctx, b2w4_launch_chained(ctx->pdl, moe_combine_kernel, grid,
+                                           dim3(kCombineThreads), 0, st,
+                                           static_cast<const float*>(dn), idx, wts, pos, tokens,
+                                           top_k, hidden_size, out_dev, ldo));
         ctx->launches++;
     }
     B2W4_CUDA(ctx, cudaGetLastError());
@@ -881,9 +1032,10 @@ int b2w4_moe_combine(b2w4_ctx* ctx, const float* route_out_dev, int tokens, int 
                          "moe_combine: bad argument (hidden a multiple of 4, route rows "
                          "16-byte aligned)");
     dim3 grid((hidden_size / 4 + kCombineThreads - 1) / kCombineThreads, tokens);
-    moe_combine_kernel<<<grid, kCombineThreads, 0, ctx->stream>>>(
-        route_out_dev, indices_dev, weights_dev, nullptr, tokens, top_k, hidden_size, out_dev,
-        ldo);
+    B2W4_CUDA(ctx, b2w4_launch_chained(ctx->pdl, moe_combine_kernel, grid, dim3(kCombineThreads),
+                                       0, ctx->stream, route_out_dev, indices_dev, weights_dev,
+                                       static_cast<const int32_t*>(nullptr), tokens, top_k,
+                                       hidden_size, out_dev, ldo));
     ctx->launches++;
     B2W4_CUDA(ctx, cudaGetLastError());
     return B2W4_OK;
