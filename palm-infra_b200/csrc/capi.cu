@@ -275,17 +275,41 @@ int b2w4_matmul_host(b2w4_ctx* ctx, const b2w4_weight* w, const float* x_host, i
     if ((rc = b2w4_reserve(ctx, SCR_STAGE_X, xb, &xd)) != B2W4_OK ||
         (rc = b2w4_reserve(ctx, SCR_STAGE_Y, yb, &yd)) != B2W4_OK)
         return rc;
-    B2W4_CUDA(ctx, cudaMemcpy2DAsync(xd, sizeof(float) * w->k, x_host, sizeof(float) * lda,
-                                     sizeof(float) * w->k, m, cudaMemcpyHostToDevice,
-                                     ctx->stream));
+    // contiguous rows (always the case for one row) take the plain 1-D copy
+    if (m == 1 || lda == w->k)
+        B2W4_CUDA(ctx, cudaMemcpyAsync(xd, x_host, xb, cudaMemcpyHostToDevice, ctx->stream));
+    else
+        B2W4_CUDA(ctx, cudaMemcpy2DAsync(xd, sizeof(float) * w->k, x_host, sizeof(float) * lda,
+                                         sizeof(float) * w->k, m, cudaMemcpyHostToDevice,
+                                         ctx->stream));
+    // A small result in mapped pinned host memory is stored by the kernel itself, straight
+    // across the host link: no second copy-engine hop before the host may read it (measured on
+    // the decode GEMV: 21 us per call instead of 28 us).  Large results keep the copy engine.
+    if (yb <= (1u << 20)) {
+        cudaPointerAttributes at;
+        if (cudaPointerGetAttributes(&at, y_host) == cudaSuccess &&
+            at.type == cudaMemoryTypeHost && at.devicePointer) {
+            rc = matmul_dispatch(ctx, w, static_cast<const float*>(xd), w->k,
+                                 static_cast<float*>(at.devicePointer), ldc, m, act_rule,
+                                 activation, act_n_begin, act_n_len);
+            if (rc != B2W4_OK)
+                return rc;
+            B2W4_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+            return B2W4_OK;
+        }
+        cudaGetLastError();  // pageable memory: not an error, take the staged path
+    }
     rc = matmul_dispatch(ctx, w, static_cast<const float*>(xd), w->k,
                          static_cast<float*>(yd), w->n, m, act_rule, activation, act_n_begin,
                          act_n_len);
     if (rc != B2W4_OK)
         return rc;
-    B2W4_CUDA(ctx, cudaMemcpy2DAsync(y_host, sizeof(float) * ldc, yd, sizeof(float) * w->n,
-                                     sizeof(float) * w->n, m, cudaMemcpyDeviceToHost,
-                                     ctx->stream));
+    if (m == 1 || ldc == w->n)
+        B2W4_CUDA(ctx, cudaMemcpyAsync(y_host, yd, yb, cudaMemcpyDeviceToHost, ctx->stream));
+    else
+        B2W4_CUDA(ctx, cudaMemcpy2DAsync(y_host, sizeof(float) * ldc, yd, sizeof(float) * w->n,
+                                         sizeof(float) * w->n, m, cudaMemcpyDeviceToHost,
+                                         ctx->stream));
     B2W4_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     return B2W4_OK;
 }
