@@ -408,16 +408,17 @@ int b2w4_launch_gemv(b2w4_ctx* ctx, const b2w4_weight* w, const float* x, int ld
         a.activation = activation;
         a.act_n_begin = act_n_begin;
         a.act_n_len = act_n_len;
-        // Tiles per CTA: a CTA's shared memory stays under ~100 KB so that two CTAs share an
-        // SM (two of this launch, or one of this launch and one of the next, which then
-        // prefetches its weights early).
+        // Tiles per CTA: a CTA's shared memory stays under half an SM's so that two CTAs share
+        // an SM, and the launch is one wave of at most 1.75 CTAs per SM.  Measured on the
+        // decode shapes of a 4B dense model (148 SMs): N=9728 K=2560 (1216 tiles) 244 CTAs
+        // 4.26 us (152 CTAs 6.0, 304 CTAs needing a second wave 6.6); N=6144 (768 tiles) 256
+        // CTAs 3.55 us against 192 CTAs 4.08; N=19456 (2432 tiles) 271 CTAs 7.0 us against 304
+        // CTAs 8.65.
         const int per_tile = w->groups * (512 + (scl16 ? 16 : 32)) +
                              8 * gemv_d_stride(mt, w->groups, a32);
-        const int budget = 100 * 1024 - mt * w->k - 4 * mt * w->groups * spg - 1024;
+        const int budget = 113 * 1024 - mt * w->k - 4 * mt * w->groups * spg - 1024;
         int tpc = max(1, min(budget / per_tile, kMaxTpc));
-        // Measured on config 1 (1216 tiles): one wave of about 1.4-1.7 CTAs per SM is fastest
-        // (244 CTAs: 4.8 us; 152: 6.0 us; 304, which needs a second wave: 6.6 us).
-        const int wave_ctas = ctx->sm_count * 17 / 10;
+        const int wave_ctas = ctx->sm_count * 7 / 4;
         const int one_wave = (w->tiles + wave_ctas - 1) / wave_ctas;
         tpc = min(tpc, max(1, one_wave));
         if (ctx->gemv_tpc_override > 0)
