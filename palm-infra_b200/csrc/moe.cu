@@ -75,24 +75,26 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
 // consecutive columns per step (one 16-byte load of router halves, two of each token's
 // activations); the warp's router rows are reused for its 4 tokens.
 constexpr int kRouterTok = 4;
-// logits of tokens t0..t0+3 against experts e0..e0+EPW-1, computed by one warp
-template <int EPW>
+// logits of tokens t0..t0+NT-1 against experts e0..e0+EPW-1, computed by one warp.  The K loop
+// is unrolled so that several steps' loads are in flight at once: with one token and one
+// expert per warp (decode) the warp is a pure latency chain otherwise.
+template <int EPW, int NT>
 __device__ __forceinline__ void router_logits_warp(const float* __restrict__ hidden, int ldx,
                                                    int tokens, int hidden_size,
                                                    const __half* __restrict__ router,
                                                    int num_experts, float* __restrict__ logits,
                                                    int t0, int e0, int lane) {
-    double acc[kRouterTok][EPW];
+    double acc[NT][EPW];
 #pragma unroll
-    for (int i = 0; i < kRouterTok; ++i)
+    for (int i = 0; i < NT; ++i)
 #pragma unroll
         for (int j = 0; j < EPW; ++j)
             acc[i][j] = 0.0;
-#pragma unroll 2
+#pragma unroll (NT == 1 ? 8 : 2)
     for (int d = lane * 8; d < hidden_size; d += 256) {
-        float xv[kRouterTok][8];
+        float xv[NT][8];
 #pragma unroll
-        for (int i = 0; i < kRouterTok; ++i) {
+        for (int i = 0; i < NT; ++i) {
             // rows past the last token repeat it: loaded, never stored
             const float* x = hidden + (size_t)min(t0 + i, tokens - 1) * ldx + d;
             const float4 lo = *reinterpret_cast<const float4*>(x);
@@ -109,7 +111,7 @@ __device__ __forceinline__ void router_logits_warp(const float* __restrict__ hid
             for (int c = 0; c < 4; ++c) {
                 const float2 r = __half22float2(h2[c]);
 #pragma unroll
-                for (int i = 0; i < kRouterTok; ++i) {
+                for (int i = 0; i < NT; ++i) {
                     acc[i][j] += (double)xv[i][2 * c] * (double)r.x;
                     acc[i][j] += (double)xv[i][2 * c + 1] * (double)r.y;
                 }
@@ -117,7 +119,7 @@ __device__ __forceinline__ void router_logits_warp(const float* __restrict__ hid
         }
     }
 #pragma unroll
-    for (int i = 0; i < kRouterTok; ++i)
+    for (int i = 0; i < NT; ++i)
 #pragma unroll
         for (int j = 0; j < EPW; ++j) {
             double v = acc[i][j];
@@ -141,8 +143,8 @@ __global__ void moe_router_logits_kernel(const float* __restrict__ hidden, int l
     if (wid >= (long long)tblocks * eblocks)
         return;
     const int t0 = (int)(wid / eblocks) * kRouterTok, e0 = (int)(wid % eblocks) * EPW;
-    router_logits_warp<EPW>(hidden, ldx, tokens, hidden_size, router, num_experts, logits, t0, e0,
-                            lane);
+    router_logits_warp<EPW, kRouterTok>(hidden, ldx, tokens, hidden_size, router, num_experts,
+                                        logits, t0, e0, lane);
 }
 
 // Fallback for activations whose rows are not 16-byte aligned: one warp per (token, expert),
@@ -177,24 +179,32 @@ __global__ void moe_router_logits_scalar_kernel(const float* __restrict__ hidden
 // taken experts masked out.  Then the softmax over the selected logits: exp(l - l_max),
 // sequential fp32 sum, times 1/sum (:157-166).
 constexpr int kMaxTopK = 16;
-constexpr int kSelectMaxExperts = 1024;  // 32 lanes x 32 mask bits
-// routes of token t, by one warp; also returns lane j's expert (lanes >= top_k: undefined)
+constexpr int kSelectMaxExperts = 1024;  // 32 lanes x 32 logits in registers
+
+// routes of token t, by one warp; also returns lane j's expert (lanes >= top_k: undefined).
+// NS = logits per lane (32 * NS >= experts).
+template <int NS>
 __device__ __forceinline__ int select_routes_warp(const float* logits, int t,
                                                   int num_experts, int top_k,
                                                   int32_t* __restrict__ idx,
                                                   float* __restrict__ weights, int lane) {
     const float* row = logits + (size_t)t * num_experts;
-    uint32_t taken = 0;       // bit s: expert lane + 32*s already selected
+    // the lane's logits (experts lane, lane+32, ...) stay in registers for all k rounds; a
+    // selected or absent expert becomes NaN, which no '>' ever accepts
+    float mine[NS];
+#pragma unroll
+    for (int s = 0; s < NS; ++s)
+        mine[s] = lane + 32 * s < num_experts ? row[lane + 32 * s] : NAN;
     float my_v = -INFINITY;   // lane j keeps the j-th selected logit
     int my_e = 0;
     for (int j = 0; j < top_k; ++j) {
         float bv = -INFINITY;
         int be = INT_MAX;
-        for (int e = lane, s = 0; e < num_experts; e += 32, ++s) {
-            const float v = row[e];
-            if (!((taken >> s) & 1u) && v > bv) {
-                bv = v;
-                be = e;
+#pragma unroll
+        for (int s = 0; s < NS; ++s) {
+            if (mine[s] > bv) {
+                bv = mine[s];
+                be = lane + 32 * s;
             }
         }
 #pragma unroll
@@ -206,8 +216,12 @@ __device__ __forceinline__ int select_routes_warp(const float* logits, int t,
                 be = oe;
             }
         }
-        if (be != INT_MAX && (be & 31) == lane)
-            taken |= 1u << (be >> 5);
+        if (be != INT_MAX && (be & 31) == lane) {
+#pragma unroll
+            for (int s = 0; s < NS; ++s)
+                if (s == (be >> 5))
+                    mine[s] = NAN;
+        }
         if (lane == j) {
             my_v = be == INT_MAX ? -INFINITY : bv;
             my_e = be == INT_MAX ? 0 : be;
@@ -227,6 +241,20 @@ __device__ __forceinline__ int select_routes_warp(const float* logits, int t,
     return my_e;
 }
 
+// dispatch on the number of experts
+__device__ __forceinline__ int select_routes_any(const float* logits, int t, int num_experts,
+                                                 int top_k, int32_t* __restrict__ idx,
+                                                 float* __restrict__ weights, int lane) {
+    if (num_experts <= 128)
+        return select_routes_warp<4>(logits, t, num_experts, top_k, idx, weights, lane);
+    if (num_experts <= 256)
+        return select_routes_warp<8>(logits, t, num_experts, top_k, idx, weights, lane);
+    if (num_experts <= 512)
+        return select_routes_warp<16>(logits, t, num_experts, top_k, idx, weights, lane);
+    return select_routes_warp<kSelectMaxExperts / 32>(logits, t, num_experts, top_k, idx, weights,
+                                                      lane);
+}
+
 __global__ void moe_select_routes_kernel(const float* __restrict__ logits, int tokens,
                                          int num_experts, int top_k, int32_t* __restrict__ idx,
                                          float* __restrict__ weights) {
@@ -235,7 +263,7 @@ __global__ void moe_select_routes_kernel(const float* __restrict__ logits, int t
     const int lane = threadIdx.x & 31;
     if (t >= tokens)
         return;
-    select_routes_warp(logits, t, num_experts, top_k, idx, weights, lane);
+    select_routes_any(logits, t, num_experts, top_k, idx, weights, lane);
 }
 
 // ---- 3. compaction: one block ------------------------------------------------------------
@@ -376,10 +404,15 @@ moe_route_fused_kernel(const float* __restrict__ hidden, int ldx, int tokens, in
         *reinterpret_cast<char2*>(blk + 16) = make_char2((signed char)c1, (signed char)c3);
     }
     // router logits, one warp per expert and block of four tokens
-    for (int e = gwarp; e < num_experts; e += nwarps)
-        for (int t0 = 0; t0 < tokens; t0 += kRouterTok)
-            router_logits_warp<1>(hidden, ldx, tokens, hidden_size, router, num_experts, logits,
-                                  t0, e, lane);
+    for (int e = gwarp; e < num_experts; e += nwarps) {
+        if (tokens == 1)
+            router_logits_warp<1, 1>(hidden, ldx, tokens, hidden_size, router, num_experts, logits,
+                                     0, e, lane);
+        else
+            for (int t0 = 0; t0 < tokens; t0 += kRouterTok)
+                router_logits_warp<1, kRouterTok>(hidden, ldx, tokens, hidden_size, router,
+                                                  num_experts, logits, t0, e, lane);
+    }
     // arrival: the last block to get here sees every block's logits
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -391,7 +424,7 @@ moe_route_fused_kernel(const float* __restrict__ hidden, int ldx, int tokens, in
         return;
     __threadfence();
     for (int t = warp; t < tokens; t += kFusedThreads / 32) {
-        const int e = select_routes_warp(logits, t, num_experts, top_k, idx, weights, lane);
+        const int e = select_routes_any(logits, t, num_experts, top_k, idx, weights, lane);
         if (lane < top_k)
             s_route[t * top_k + lane] = e;
     }
@@ -402,26 +435,57 @@ moe_route_fused_kernel(const float* __restrict__ hidden, int ldx, int tokens, in
     if (threadIdx.x < routes)
         atomicAdd(&s_cnt[s_route[threadIdx.x]], 1);  // integer counts: order-free
     __syncthreads();
-    // thread e: offset = routes of lower experts, its routes placed in token order
-    for (int e = threadIdx.x; e <= num_experts; e += kFusedThreads) {
-        int run = 0, rank = 0;
-        for (int q = 0; q < e; ++q) {
-            const int c = s_cnt[q];
-            run += c;
-            rank += c > 0;
+    // exclusive scan of the counts (and of "has routes") over the experts, a block-wide chunk
+    // of experts at a time; then thread e places its routes in token order
+    __shared__ int s_wsum[kFusedThreads / 32][2];
+    int carry_run = 0, carry_rank = 0;
+    for (int base = 0; base <= num_experts; base += kFusedThreads) {
+        const int e = base + threadIdx.x;
+        const int c = e < num_experts ? s_cnt[e] : 0;
+        int run = c, rank = c > 0;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {  // inclusive scan inside the warp
+            const int r = __shfl_up_sync(0xffffffffu, run, off);
+            const int k = __shfl_up_sync(0xffffffffu, rank, off);
+            if (lane >= off) {
+                run += r;
+                rank += k;
+            }
         }
-        offsets[e] = run;
-        if (e == num_experts) {
-            active[num_experts] = rank;
-        } else if (s_cnt[e] > 0) {
-            active[rank] = e;
-            for (int i = 0; i < routes; ++i)
-                if (s_route[i] == e) {
-                    route_token[run] = i / top_k;
-                    pos[i] = run;
-                    ++run;
-                }
+        if (lane == 31) {
+            s_wsum[warp][0] = run;
+            s_wsum[warp][1] = rank;
         }
+        __syncthreads();
+        int wrun = carry_run, wrank = carry_rank, trun = 0, trank = 0;
+#pragma unroll
+        for (int w = 0; w < kFusedThreads / 32; ++w) {
+            if (w < warp) {
+                wrun += s_wsum[w][0];
+                wrank += s_wsum[w][1];
+            }
+            trun += s_wsum[w][0];
+            trank += s_wsum[w][1];
+        }
+        run += wrun - c;          // exclusive
+        rank += wrank - (c > 0);
+        if (e <= num_experts) {
+            offsets[e] = run;
+            if (e == num_experts) {
+                active[num_experts] = rank;
+            } else if (c > 0) {
+                active[rank] = e;
+                for (int i = 0; i < routes; ++i)
+                    if (s_route[i] == e) {
+                        route_token[run] = i / top_k;
+                        pos[i] = run;
+                        ++run;
+                    }
+            }
+        }
+        carry_run += trun;
+        carry_rank += trank;
+        __syncthreads();
     }
     if (threadIdx.x == 0)
         *arrivals = 0;  // ready for the next launch
