@@ -269,7 +269,9 @@ __global__ void moe_select_routes_kernel(const float* __restrict__ logits, int t
 // ---- 3. compaction: one block ------------------------------------------------------------
 // counts, exclusive offsets, and per expert its routes in ascending token order
 // (kernels/moe.cpp:759-776).  pos[t][j] = the compact position of token t's j-th route;
-// active[] lists the experts that have routes, ascending, active[E] their number.
+// slots[y] = (expert, first route, one past its last route) of the y-th expert that has routes,
+// ascending; empty (0, 0, 0) from the number of such experts on: what a grouped-matmul CTA
+// needs to start, in one 16-byte load.
 // Stable placement, a chunk of routes at a time (one route per thread): lanes of a warp that
 // hold the same expert find each other with match.any, the lowest of them records the warp's
 // count for that expert, a scan over the warps turns the counts into first slots, and every
@@ -279,7 +281,7 @@ constexpr int kCompactTableInts = 8192;  // warps x experts count table
 __global__ void __launch_bounds__(kCompactThreads)
 moe_compact_kernel(const int32_t* __restrict__ idx, int tokens, int top_k, int num_experts,
                    int32_t* __restrict__ offsets, int32_t* __restrict__ route_token,
-                   int32_t* __restrict__ pos, int32_t* __restrict__ active) {
+                   int32_t* __restrict__ pos, int4* __restrict__ slots) {
     b2w4_pdl_chain_entry();
     extern __shared__ int s_int[];
     const int E = num_experts;
@@ -313,9 +315,10 @@ moe_compact_kernel(const int32_t* __restrict__ idx, int tokens, int top_k, int n
         if (e < E) {
             s_cursor[e] = run;
             if (s_cnt[e] > 0)
-                active[rank] = e;
+                slots[rank] = make_int4(e, run, run + s_cnt[e], 0);
         } else {
-            active[E] = rank;
+            for (int y = rank; y < E; ++y)  // slots past the last expert with routes: empty
+                slots[y] = make_int4(0, 0, 0, 0);
         }
     }
     __syncthreads();
@@ -364,6 +367,7 @@ size_t compact_smem(int num_experts) {
 // and computes its share of the router logits; the block that arrives last at a counter (no
 // block waits for another) selects the routes, one warp per token, and compacts them.  Same
 // device functions, same bits as the separate kernels.
+constexpr int kFusedSwigluTokens = 4;
 constexpr int kFusedTokens = 8;
 constexpr int kFusedRoutes = 128;
 constexpr int kFusedThreads = 128;
@@ -372,7 +376,7 @@ moe_route_fused_kernel(const float* __restrict__ hidden, int ldx, int tokens, in
                        const __half* __restrict__ router, int num_experts, int top_k,
                        float* logits, int32_t* __restrict__ idx, float* __restrict__ weights,
                        int32_t* __restrict__ offsets, int32_t* __restrict__ route_token,
-                       int32_t* __restrict__ pos, int32_t* __restrict__ active,
+                       int32_t* __restrict__ pos, int4* __restrict__ slots,
                        int8_t* __restrict__ q_hidden, float* __restrict__ as_hidden,
                        int* __restrict__ arrivals) {
     b2w4_pdl_chain_entry();
@@ -472,9 +476,10 @@ moe_route_fused_kernel(const float* __restrict__ hidden, int ldx, int tokens, in
         if (e <= num_experts) {
             offsets[e] = run;
             if (e == num_experts) {
-                active[num_experts] = rank;
+                for (int y = rank; y < num_experts; ++y)  // the remaining slots: empty
+                    slots[y] = make_int4(0, 0, 0, 0);
             } else if (c > 0) {
-                active[rank] = e;
+                slots[rank] = make_int4(e, run, run + c, 0);
                 for (int i = 0; i < routes; ++i)
                     if (s_route[i] == e) {
                         route_token[run] = i / top_k;
@@ -494,23 +499,13 @@ moe_route_fused_kernel(const float* __restrict__ hidden, int ldx, int tokens, in
 // ---- 6. SwiGLU + quantiser: one warp per (route, 128-wide group of I) ------------------
 // inter = (g * 1/(1+exp(-g))) * u with gate = columns [0,I), up = [I,2I)
 // (kernels/moe.cpp:160-183), then the per-128 quantiser; codes in tensor-operand order.
-__global__ void moe_swiglu_quant_kernel(const float* __restrict__ gu, int routes,
-                                        int intermediate, int8_t* __restrict__ q,
-                                        float* __restrict__ scales,
-                                        const int32_t* __restrict__ route_lo,
-                                        const int32_t* __restrict__ route_hi) {
-    b2w4_pdl_chain_entry();
-    const int groups = intermediate >> 7;
-    const long long wid = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-    const int lane = threadIdx.x & 31;
-    if (wid >= (long long)routes * groups)
-        return;
-    const int r = (int)(wid / groups), g = (int)(wid % groups);
-    // expert-parallel runs only own the compact positions of their experts
-    if (route_lo && (r < *route_lo || r >= *route_hi))
-        return;
-    const float* gp = gu + (size_t)r * 2 * intermediate + (size_t)g * 128 + lane * 4;
-    const float* up = gp + intermediate;
+// one warp: 128 values of one route, written to `group_dst` (the 128 code bytes of the group)
+// and `scale_dst`
+__device__ __forceinline__ void swiglu_quant_warp(const float* __restrict__ gate_row,
+                                                  const float* __restrict__ up_row, int lane,
+                                                  int8_t* group_dst, float* scale_dst) {
+    const float* gp = gate_row + lane * 4;
+    const float* up = up_row + lane * 4;
     float v[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -528,14 +523,34 @@ __global__ void moe_swiglu_quant_kernel(const float* __restrict__ gu, int routes
     const int c0 = b2w4_quant_code(v[0], inv), c1 = b2w4_quant_code(v[1], inv);
     const int c2 = b2w4_quant_code(v[2], inv), c3 = b2w4_quant_code(v[3], inv);
     if (lane == 0)
-        scales[(size_t)r * groups + g] = scale;
+        *scale_dst = scale;
     // tensor-operand order inside the group: [word position][even words of the four
     // 32-blocks, then the odd words]; the lane holds k = 4*lane..+3: 32-block lane/8, even
     // codes at even index 2*(lane%8), 2*(lane%8)+1
-    int8_t* blk = q + (size_t)r * intermediate + (size_t)g * 128 + ((lane & 7) >> 1) * 32 +
-                  (lane >> 3) * 4 + (lane & 1) * 2;
+    int8_t* blk = group_dst + ((lane & 7) >> 1) * 32 + (lane >> 3) * 4 + (lane & 1) * 2;
     *reinterpret_cast<char2*>(blk) = make_char2((signed char)c0, (signed char)c2);
     *reinterpret_cast<char2*>(blk + 16) = make_char2((signed char)c1, (signed char)c3);
+}
+
+__global__ void moe_swiglu_quant_kernel(const float* __restrict__ gu, int routes,
+                                        int intermediate, int8_t* __restrict__ q,
+                                        float* __restrict__ scales,
+                                        const int32_t* __restrict__ route_lo,
+                                        const int32_t* __restrict__ route_hi) {
+    b2w4_pdl_chain_entry();
+    const int groups = intermediate >> 7;
+    const long long wid = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (wid >= (long long)routes * groups)
+        return;
+    const int r = (int)(wid / groups), g = (int)(wid % groups);
+    // expert-parallel runs only own the compact positions of their experts
+    if (route_lo && (r < *route_lo || r >= *route_hi))
+        return;
+    const float* gp = gu + (size_t)r * 2 * intermediate + (size_t)g * 128;
+    swiglu_quant_warp(gp, gp + intermediate, lane,
+                      q + (size_t)r * intermediate + (size_t)g * 128,
+                      scales + (size_t)r * groups + g);
 }
 
 // ---- 8. combine: one block per (token, 512 hidden columns) -------------------------------
@@ -621,8 +636,9 @@ struct GroupedArgs {
     const void* scl;
     const int8_t* qa;         // [rows][K] int8, tensor-operand order inside each group
     const float* as;          // [rows][G]
-    const int32_t* offsets;   // [E+1] route ranges of all experts
-    const int32_t* active;    // experts that have routes, ascending; active[E_all] = how many
+    const float* gate_up;     // if set (few routes): the activations are silu(gate)*up of these
+                              // fp32 [routes][2K] rows, quantised here instead of read from qa
+    const int4* slots;        // y-th expert with routes: (expert, first route, end), else empty
     int num_experts_all;      // experts routed over
     int expert_begin;         // first expert whose weights this aggregate holds
     int expert_count;         // experts held
@@ -658,13 +674,11 @@ moe_grouped_gemv_kernel(const GroupedArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
     // blockIdx.y walks the experts that have routes, not all experts: a decode token
     // touches top_k of them
-    if ((int)blockIdx.y >= a.active[a.num_experts_all])
-        return;
-    const int e_all = a.active[blockIdx.y];
+    const int4 slot = a.slots[blockIdx.y];
+    const int e_all = slot.x, r0 = slot.y, r1 = slot.z;
     const int e = e_all - a.expert_begin;  // index inside the aggregate held here
     if (e < 0 || e >= a.expert_count)
         return;
-    const int r0 = a.offsets[e_all], r1 = a.offsets[e_all + 1];
     const int tl0 = blockIdx.x * a.tpc;
     const int ntile = min(a.tpc, a.tiles_e - tl0);
     if (r0 >= r1 || ntile <= 0)
@@ -707,16 +721,28 @@ moe_grouped_gemv_kernel(const GroupedArgs a) {
     for (int base = r0; base < r1; base += kGR) {
         const int mc = min(kGR, r1 - base);
         // quantised activations of this pass's routes
-        for (int i = threadIdx.x; i < mc * (K / 16); i += kGT) {
-            const int mi = i / (K / 16), c = i - mi * (K / 16);
-            const int src_row = a.row_map ? a.row_map[base + mi] : base + mi;
-            s_qa[mi * (K / 16) + c] =
-                reinterpret_cast<const uint4*>(a.qa + (size_t)src_row * K)[c];
-        }
-        for (int i = threadIdx.x; i < mc * G; i += kGT) {
-            const int mi = i / G, g = i - mi * G;
-            const int src_row = a.row_map ? a.row_map[base + mi] : base + mi;
-            s_as[mi * G + g] = a.as[(size_t)src_row * G + g];
+        if (a.gate_up) {
+            // every CTA of the expert repeats this for the expert's routes: cheap for the few
+            // routes of a decode step, and it saves a launch
+            for (int task = warp; task < mc * G; task += kGW) {
+                const int mi = task / G, g = task - mi * G;
+                const float* gp = a.gate_up + (size_t)(base + mi) * 2 * K + (size_t)g * 128;
+                swiglu_quant_warp(gp, gp + K, lane,
+                                  reinterpret_cast<int8_t*>(s_qa) + (size_t)mi * K + (size_t)g * 128,
+                                  s_as + mi * G + g);
+            }
+        } else {
+            for (int i = threadIdx.x; i < mc * (K / 16); i += kGT) {
+                const int mi = i / (K / 16), c = i - mi * (K / 16);
+                const int src_row = a.row_map ? a.row_map[base + mi] : base + mi;
+                s_qa[mi * (K / 16) + c] =
+                    reinterpret_cast<const uint4*>(a.qa + (size_t)src_row * K)[c];
+            }
+            for (int i = threadIdx.x; i < mc * G; i += kGT) {
+                const int mi = i / G, g = i - mi * G;
+                const int src_row = a.row_map ? a.row_map[base + mi] : base + mi;
+                s_as[mi * G + g] = a.as[(size_t)src_row * G + g];
+            }
         }
         __syncthreads();
         // -8 * (sum of the even-k codes) per (route, group): the even words of a group are
@@ -820,8 +846,8 @@ size_t grouped_smem(int k, int groups, int tpc, bool scl16) {
 
 int launch_grouped(b2w4_ctx* ctx, const b2w4_weight* w, int num_experts_all, int expert_begin,
                    int expert_count, int routes, const int8_t* qa, const float* as,
-                   const int32_t* offsets, const int32_t* active, const int32_t* row_map,
-                   float* out) {
+                   const int4* slots, const int32_t* row_map, float* out,
+                   const float* fused_gate_up = nullptr) {
     const int n_e = w->n / expert_count;
     const bool scl16 = w->scales_fp16 != 0;
     GroupedArgs a;
@@ -829,8 +855,8 @@ int launch_grouped(b2w4_ctx* ctx, const b2w4_weight* w, int num_experts_all, int
     a.scl = w->scl;
     a.qa = qa;
     a.as = as;
-    a.offsets = offsets;
-    a.active = active;
+    a.slots = slots;
+    a.gate_up = fused_gate_up;
     a.num_experts_all = num_experts_all;
     a.expert_begin = expert_begin;
     a.expert_count = expert_count;
@@ -928,7 +954,7 @@ static int moe_run(b2w4_ctx* ctx, const float* hidden_dev, int ldx, int tokens, 
     const size_t o_rt = align_up(o_off + sizeof(int32_t) * (num_experts + 1), 256);
     const size_t o_pos = align_up(o_rt + sizeof(int32_t) * routes, 256);
     const size_t o_act = align_up(o_pos + sizeof(int32_t) * routes, 256);
-    const size_t small_bytes = align_up(o_act + sizeof(int32_t) * (num_experts + 1), 256);
+    const size_t small_bytes = align_up(o_act + sizeof(int4) * num_experts, 256);
     // quantised hidden (per token) and quantised SwiGLU output (per route)
     const size_t o_qh = 0;
     const size_t o_ash = align_up(o_qh + (size_t)tokens * hidden_size, 256);
@@ -952,7 +978,7 @@ static int moe_run(b2w4_ctx* ctx, const float* hidden_dev, int ldx, int tokens, 
     int32_t* offsets = reinterpret_cast<int32_t*>(smb + o_off);
     int32_t* route_token = reinterpret_cast<int32_t*>(smb + o_rt);
     int32_t* pos = reinterpret_cast<int32_t*>(smb + o_pos);
-    int32_t* active = reinterpret_cast<int32_t*>(smb + o_act);
+    int4* slots = reinterpret_cast<int4*>(smb + o_act);
     int8_t* q_hidden = reinterpret_cast<int8_t*>(qbb + o_qh);
     float* as_hidden = reinterpret_cast<float*>(qbb + o_ash);
     int8_t* q_inter = reinterpret_cast<int8_t*>(qbb + o_qi);
@@ -971,7 +997,7 @@ static int moe_run(b2w4_ctx* ctx, const float* hidden_dev, int ldx, int tokens, 
                            ctx->pdl, moe_route_fused_kernel, dim3(blocks), dim3(kFusedThreads),
                            sizeof(int) * (num_experts + 1), st, hidden_dev, ldx, tokens,
                            hidden_size, router, num_experts, top_k, logits, idx, wts, offsets,
-                           route_token, pos, active, q_hidden, as_hidden, ctx->flag_dev + 4));
+                           route_token, pos, slots, q_hidden, as_hidden, ctx->flag_dev + 4));
         ctx->launches++;
     } else {
         if (!aligned) {
@@ -1002,7 +1028,7 @@ static int moe_run(b2w4_ctx* ctx, const float* hidden_dev, int ldx, int tokens, 
         B2W4_CUDA(ctx, b2w4_launch_chained(ctx->pdl, moe_compact_kernel, dim3(1),
                                            dim3(kCompactThreads), compact_smem(num_experts), st, idx,
                                            tokens, top_k, num_experts, offsets, route_token, pos,
-                                           active));
+                                           slots));
         ctx->launches++;
         B2W4_CUDA(ctx, cudaGetLastError());
         if ((rc = b2w4_launch_quantize(ctx, hidden_dev, ldx, tokens, hidden_size, B2W4_ACT_G128,
@@ -1013,10 +1039,12 @@ static int moe_run(b2w4_ctx* ctx, const float* hidden_dev, int ldx, int tokens, 
     const int32_t* local_offsets = offsets + expert_begin;
     const bool partial = expert_count != num_experts;
     if ((rc = launch_grouped(ctx, gate_up, num_experts, expert_begin, expert_count, routes,
-                             q_hidden, as_hidden, offsets, active, route_token,
+                             q_hidden, as_hidden, slots, route_token,
                              static_cast<float*>(gu))) != B2W4_OK)
         return rc;
-    {
+    // few routes: SwiGLU and its quantiser run inside the down-projection's CTAs
+    const bool fuse_swiglu = tokens <= kFusedSwigluTokens;
+    if (!fuse_swiglu) {
         const long long threads = (long long)routes * gi * 32;
         B2W4_CUDA(ctx, b2w4_launch_chained(
                            ctx->pdl, moe_swiglu_quant_kernel, dim3((int)((threads + 255) / 256)),
@@ -1026,8 +1054,8 @@ static int moe_run(b2w4_ctx* ctx, const float* hidden_dev, int ldx, int tokens, 
         ctx->launches++;
     }
     if ((rc = launch_grouped(ctx, down, num_experts, expert_begin, expert_count, routes, q_inter,
-                             as_inter, offsets, active, nullptr,
-                             static_cast<float*>(dn))) != B2W4_OK)
+                             as_inter, slots, nullptr, static_cast<float*>(dn),
+                             fuse_swiglu ? static_cast<const float*>(gu) : nullptr)) != B2W4_OK)
         return rc;
     if (route_out) {
         dim3 grid((hidden_size / 4 + 255) / 256, routes);
