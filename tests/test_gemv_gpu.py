@@ -259,6 +259,17 @@ def test_many_row_paths_shapes_bit_exact(ctx_mma, ctx_tc, kind, m, n, k):
     assert y.tobytes() == y_ref.tobytes()
 
 
+@pytest.mark.parametrize("m,n,k", [(24, 72, 10368), (260, 40, 10368), (12, 264, 16384)])
+def test_many_rows_beyond_the_tcgen05_kernels_k_limit(ctx, m, n, k):
+    """K above 10240 (more than 80 groups) cannot go to the tcgen05 kernel: the mma.sync
+    kernel takes it, resident or through its activation ring, 256 rows per launch."""
+    blocks = pkg.synth.bg128_weight(20261125, n + k + m, n, k)
+    x = pkg.synth.activations(7, m + 3, m, k)
+    y, _ = run_gpu(ctx, blocks, n, k, x, sums=False)
+    y_ref = ol.matmul_w4(blocks, n, k, x)
+    assert y.tobytes() == y_ref.tobytes()
+
+
 def test_config2_prefill_m256(ctx):
     """M=256, K=2560, N=9728 (benchmark configuration 2, prefill): bit-exact against the
     row-by-row W4A8 oracle, and within 1e-2 relative L2 of the exact dequantised product

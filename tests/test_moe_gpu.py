@@ -99,6 +99,23 @@ def test_ragged_expert_groups(ctx, t, h, e, top_k, inter):
     check_against_oracle(got, want)
 
 
+@pytest.mark.parametrize("t,h,e,top_k,inter", [(8, 256, 256, 8, 128), (9, 256, 64, 2, 128),
+                                               (3, 128, 512, 16, 128), (5, 128, 1024, 4, 128),
+                                               (4, 256, 8, 1, 256), (40, 128, 4, 4, 128)])
+def test_routing_path_boundaries(ctx, t, h, e, top_k, inter):
+    """Both sides of every switch in the op: 8 tokens (fused decode routing) and 9 (separate
+    kernels), 4 tokens (decode grouped kernel, SwiGLU fused) and 5 (prefill kernel), expert
+    counts of every logits-per-lane variant (128, 256, 512, 1024), top_k of 1 and of 16, and
+    experts with more routes than one pass holds (40 tokens all on 4 experts)."""
+    hidden = pkg.synth.activations(7, 900 + t + e, t, h)
+    router = pkg.synth.router_weight(20261125, 700 + e, e, h, std=0.3)
+    gu = pkg.synth.bg128_weight(20261125, 800 + e, e * 2 * inter, h)
+    dn = pkg.synth.bg128_weight(20261125, 900 + e, e * h, inter)
+    got = run_moe(ctx, hidden, router, top_k, inter, gu, dn)
+    want = ol.moe_forward(hidden, router, top_k, inter, gu, dn)
+    check_against_oracle(got, want)
+
+
 def test_qwen3_30b_shaped_layer(ctx):
     """One Qwen3-30B-A3B-shaped MoE layer: hidden 2048, 128 experts, top-8, expert
     intermediate 768; 16 prompt tokens and 1 decode token."""
