@@ -466,6 +466,13 @@ def run_ours(args):
                               "gbs": algorithmic_bytes(N_OUT, K_IN, m) / per / 1e9,
                               "tflops": 2.0 * m * N_OUT * K_IN / per / 1e12,
                               "tokens_per_s": m / per}
+        # the reference's M > 1 rule (one activation scale per 32 values) on the prefill shape
+        s_ms = time_steps(torch, make_step(256, rule=pkg.capi.ACT_G32, passes=1),
+                          max(3, min(args.steps, 25)), 3)
+        per = s_ms * 1e-3 / COPIES
+        sweep["m256_per32_rule"] = {"us_per_matmul": per * 1e6,
+                                    "tflops": 2.0 * 256 * N_OUT * K_IN / per / 1e12,
+                                    "tokens_per_s": 256 / per}
         sweep["dense4b_decode_matmul_walk"] = decode_walk(torch, pkg, ctx, args)
         sweep["moe30b_layer"] = moe_layer(torch, pkg, ctx, args)
         line["sweep"] = sweep

@@ -91,9 +91,11 @@ __global__ void quantize_rows_umma_kernel(const float* __restrict__ x, int lda, 
 
 // Same quantiser for the mma.sync GEMM: codes int8 [m][K] in tensor-operand order
 // (QLAYOUT_MMA), scales and the accumulator bias 0x4B400000 - 8 * (sum of the group's codes)
-// transposed to [groups][m_pad] so that one group of all tokens is contiguous.  (The kernel
+// transposed to [groups][m_pad] (per-32 rule: [groups*4][m_pad], one entry per 32-block) so
+// that one group of all tokens is contiguous.  (The kernel
 // multiplies unsigned nibbles q+8; starting its int32 accumulator at the bias makes it end as
 // 0x4B400000 + D, the bit pattern of the float 12582912 + D.)
+template <bool A32>
 __global__ void quantize_rows_mma_kernel(const float* __restrict__ x, int lda, int m, int k,
                                          int m_pad, int8_t* __restrict__ q,
                                          float* __restrict__ scales_t,
@@ -108,8 +110,9 @@ __global__ void quantize_rows_mma_kernel(const float* __restrict__ x, int lda, i
     const float4 v = *reinterpret_cast<const float4*>(x + (size_t)row * lda + (size_t)g * 128 +
                                                       lane * 4);
     float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+    // per 128 values: all 32 lanes; per 32 values: the 8 lanes of a 32-block
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1)
+    for (int off = A32 ? 4 : 16; off > 0; off >>= 1)
         amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
     float scale, inv;
     b2w4_quant_params(amax, scale, inv);
@@ -117,9 +120,15 @@ __global__ void quantize_rows_mma_kernel(const float* __restrict__ x, int lda, i
     const int c2 = b2w4_quant_code(v.z, inv), c3 = b2w4_quant_code(v.w, inv);
     int esum = c0 + c1 + c2 + c3;  // integer: order-free
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1)
+    for (int off = A32 ? 4 : 16; off > 0; off >>= 1)
         esum += __shfl_xor_sync(0xffffffffu, esum, off);
-    if (lane == 0) {
+    if (A32) {
+        if ((lane & 7) == 0) {
+            const size_t at = (size_t)(g * 4 + (lane >> 3)) * m_pad + row;
+            scales_t[at] = scale;
+            es_t[at] = 0x4B400000 - 8 * esum;
+        }
+    } else if (lane == 0) {
         scales_t[(size_t)g * m_pad + row] = scale;
         es_t[(size_t)g * m_pad + row] = 0x4B400000 - 8 * esum;
     }
@@ -133,13 +142,17 @@ __global__ void quantize_rows_mma_kernel(const float* __restrict__ x, int lda, i
 }  // namespace
 
 int b2w4_launch_quantize_mma(b2w4_ctx* ctx, const float* x, int lda, int m, int k, int m_pad,
-                             int8_t* q, float* scales_t, int32_t* es_t) {
+                             int act_rule, int8_t* q, float* scales_t, int32_t* es_t) {
     if ((reinterpret_cast<uintptr_t>(x) & 15) || (lda & 3))
         return b2w4_fail(ctx, B2W4_E_INVALID, "quantize: rows must be 16-byte aligned");
     long long warps = (long long)m * (k / 128);
     int grid = (int)((warps * 32 + 255) / 256);
-    quantize_rows_mma_kernel<<<grid, 256, 0, ctx->stream>>>(x, lda, m, k, m_pad, q, scales_t,
-                                                            es_t);
+    if (act_rule == B2W4_ACT_G32)
+        quantize_rows_mma_kernel<true><<<grid, 256, 0, ctx->stream>>>(x, lda, m, k, m_pad, q,
+                                                                      scales_t, es_t);
+    else
+        quantize_rows_mma_kernel<false><<<grid, 256, 0, ctx->stream>>>(x, lda, m, k, m_pad, q,
+                                                                       scales_t, es_t);
     ctx->launches++;
     B2W4_CUDA(ctx, cudaGetLastError());
     return B2W4_OK;

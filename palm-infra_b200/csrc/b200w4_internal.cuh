@@ -71,13 +71,13 @@ int b2w4_launch_repack(b2w4_ctx* ctx, const void* dev_blocks, b2w4_weight* w);
 int b2w4_launch_quantize(b2w4_ctx* ctx, const float* x, int lda, int m, int k,
                          int act_rule, int8_t* q, float* scales, int layout);
 // 9..256 rows per launch on mma.sync with register accumulators (gemm_mma.cu)
-bool b2w4_gemm_mma_fits(const b2w4_weight* w, int m);
-bool b2w4_gemm_mma_resident(const b2w4_weight* w, int m, int sm_count);
+bool b2w4_gemm_mma_fits(const b2w4_weight* w, int m, int act_rule);
+bool b2w4_gemm_mma_resident(const b2w4_weight* w, int m, int act_rule, int sm_count);
 int b2w4_launch_gemm_mma(b2w4_ctx* ctx, const b2w4_weight* w, const float* x, int lda,
-                         float* y, int ldc, int m, int activation, int act_n_begin,
-                         int act_n_len);
+                         float* y, int ldc, int m, int act_rule, int activation,
+                         int act_n_begin, int act_n_len);
 int b2w4_launch_quantize_mma(b2w4_ctx* ctx, const float* x, int lda, int m, int k, int m_pad,
-                             int8_t* q, float* scales_t, int32_t* es_t);
+                             int act_rule, int8_t* q, float* scales_t, int32_t* es_t);
 int b2w4_launch_gemv(b2w4_ctx* ctx, const b2w4_weight* w, const float* x, int lda,
                      float* y, int ldc, int m, int act_rule, int activation,
                      int act_n_begin, int act_n_len, int32_t* sums);

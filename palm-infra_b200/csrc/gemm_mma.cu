@@ -1,10 +1,12 @@
 // W4G128 x int8 GEMM for 9..256 activation rows per launch (batched decode, prefill) on the
 // warp-level int8 tensor instruction (mma.sync m16n8k32) with register accumulators.
 //
-// Arithmetic = the reference's NEON W4A8 GEMV applied row by row (kernels/matmul_w4.cpp:
-// 211-295 with the per-128 quantiser, kernels/matmul_quant.cpp:578-641):
+// Arithmetic = the reference's NEON W4A8 kernels: the GEMV applied row by row
+// (kernels/matmul_w4.cpp:211-295 with the per-128 quantiser, kernels/matmul_quant.cpp:578-641)
 //   per 128-k group g:  D = sum q4*q8 (int32);  y = fma(float(D), fp32(ws*as[g]), y)
-// groups ascending.  The contract needs every group's exact int32 sum before the next fp32
+// groups ascending, or the M > 1 rule (kernels/matmul_w4.cpp:785-901 with the per-32 quantiser,
+// kernels/matmul_quant.cpp:280-329): the same step per 32-k block with one activation scale
+// per block, blocks ascending.  The contract needs every group's exact int32 sum before the next fp32
 // step, so an accumulator cannot run across K: each group's sums are produced, converted and
 // folded into the fp32 chain, and the chain value of every (token, weight row) stays in one
 // register of one thread for the whole K loop.  With mma.sync the int32 sums come back in
@@ -39,8 +41,9 @@ struct GemmMmaArgs {
     const uint8_t* nib;
     const void* scl;
     const int8_t* qa;    // [m][K] int8, tensor-operand order inside each group
-    const float* as_t;   // [G][m_pad] activation scales
-    const int32_t* es_t; // [G][m_pad] 0x4B400000 - 8 * sum of the group's codes
+    const float* as_t;   // [G*spg][m_pad] activation scales (spg = 1: per 128, 4: per 32-block)
+    const int32_t* es_t; // [G*spg][m_pad] 0x4B400000 - 8 * sum of the group's (block's) codes
+    int spg;
     float* y;
     int ldc, m, m_pad, n, k, groups, tiles;
     int tiles_base, tiles_rem, tile_cap;
@@ -95,13 +98,15 @@ __device__ __forceinline__ void load_stage(const GemmMmaArgs& a, int g, uint8_t*
         gm_cp_async16(s_b + t * kRowBytes + c * 16,
                       a.qa + (size_t)t * a.k + (size_t)g * 128 + c * 16);
     }
-    for (int t = threadIdx.x; t < a.m; t += kGemmThreads) {
-        gm_cp_async4(s_as + t, a.as_t + (size_t)g * a.m_pad + t);
-        gm_cp_async4(s_es + t, a.es_t + (size_t)g * a.m_pad + t);
+    const int m8 = (a.m + 7) & ~7;
+    for (int i = threadIdx.x; i < a.m * a.spg; i += kGemmThreads) {
+        const int sb = i / a.m, t = i - sb * a.m;
+        gm_cp_async4(s_as + sb * m8 + t, a.as_t + (size_t)(g * a.spg + sb) * a.m_pad + t);
+        gm_cp_async4(s_es + sb * m8 + t, a.es_t + (size_t)(g * a.spg + sb) * a.m_pad + t);
     }
 }
 
-template <int CB, bool SCL16>
+template <int CB, bool SCL16, bool A32>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_w4a8_mma_kernel(const GemmMmaArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
@@ -113,8 +118,9 @@ gemm_w4a8_mma_kernel(const GemmMmaArgs a) {
     uint8_t* s_scl = s_w + (size_t)a.tile_cap * tile_bytes;   // [cap][G][8]
     const int S = a.stages;
     uint8_t* s_b = s_scl + (size_t)a.tile_cap * scl_tile_bytes;  // [S][m8][kRowBytes]
-    float* s_as = reinterpret_cast<float*>(s_b + S * (size_t)m8 * kRowBytes);  // [S][m8]
-    int* s_es = reinterpret_cast<int*>(s_as + S * m8);                          // [S][m8]
+    constexpr int SPG = A32 ? 4 : 1;  // scales / biases per group
+    float* s_as = reinterpret_cast<float*>(s_b + S * (size_t)m8 * kRowBytes);  // [S][SPG][m8]
+    int* s_es = reinterpret_cast<int*>(s_as + S * SPG * m8);                    // [S][SPG][m8]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int gid = lane >> 2, tid = lane & 3;
@@ -143,7 +149,8 @@ gemm_w4a8_mma_kernel(const GemmMmaArgs a) {
     const int pre = resident ? G : S - 1;
     for (int g = 0; g < pre; ++g) {
         if (g < G)
-            load_stage(a, g, s_b + (size_t)g * m8 * kRowBytes, s_as + g * m8, s_es + g * m8);
+            load_stage(a, g, s_b + (size_t)g * m8 * kRowBytes, s_as + g * SPG * m8,
+                       s_es + g * SPG * m8);
         asm volatile("cp.async.commit_group;" ::: "memory");
     }
     if (resident) {
@@ -175,16 +182,16 @@ gemm_w4a8_mma_kernel(const GemmMmaArgs a) {
             __syncthreads();  // stage g visible to all; everyone is done with stage g-1
             if (g + S - 1 < G) {
                 const int sn = (g + S - 1) % S;  // the slot stage g-1 used
-                load_stage(a, g + S - 1, s_b + (size_t)sn * m8 * kRowBytes, s_as + sn * m8,
-                           s_es + sn * m8);
+                load_stage(a, g + S - 1, s_b + (size_t)sn * m8 * kRowBytes, s_as + sn * SPG * m8,
+                           s_es + sn * SPG * m8);
             }
             asm volatile("cp.async.commit_group;" ::: "memory");
         }
         const int st = resident ? g : g % S;
         if (cb0 < cb1) {
             const uint8_t* b = s_b + (size_t)st * m8 * kRowBytes;
-            const float* as = s_as + st * m8;
-            const int* es = s_es + st * m8;
+            const float* as = s_as + st * SPG * m8;
+            const int* es = s_es + st * SPG * m8;
             // word `lane` of the 128 bytes of (tile, group, 32-block s): row gid, k 8*tid..+7
             const int wbase = t0 * tile_words + g * 128 + lane;
             uint32_t lo0[4], hi0[4], lo1[4], hi1[4];
@@ -212,26 +219,48 @@ gemm_w4a8_mma_kernel(const GemmMmaArgs a) {
                     const uint4* bp = reinterpret_cast<const uint4*>(bl + cb * (8 * kRowBytes));
                     const uint4 be = bp[0], bo = bp[1];
                     const int tk = cb * 8 + tid * 2;  // tokens of this lane's accumulators
-                    const int2 bias = *reinterpret_cast<const int2*>(es + tk);
-                    const float2 asv = *reinterpret_cast<const float2*>(as + tk);
-                    // two chains of two instructions (latency), joined by one add
-                    int c[4] = {bias.x, bias.y, bias.x, bias.y}, c2[4] = {0, 0, 0, 0};
-                    gm_mma(c, lo0[0], lo1[0], lo0[1], lo1[1], be.x, be.y);
-                    gm_mma(c2, hi0[0], hi1[0], hi0[1], hi1[1], bo.x, bo.y);
-                    gm_mma(c, lo0[2], lo1[2], lo0[3], lo1[3], be.z, be.w);
-                    gm_mma(c2, hi0[2], hi1[2], hi0[3], hi1[3], bo.z, bo.w);
+                    if (A32) {
+                        // per 32-block: one instruction (even k | odd k), its own bias and
+                        // activation scale; blocks folded into the chain in ascending order
+                        const uint32_t bev[4] = {be.x, be.y, be.z, be.w};
+                        const uint32_t bov[4] = {bo.x, bo.y, bo.z, bo.w};
 #pragma unroll
-                    for (int i = 0; i < 4; ++i)
-                        c[i] += c2[i];
-                    // c = 0x4B400000 + D: as a float 12582912 + D, exactly
-                    acc[j][0] = __fmaf_rn(__fsub_rn(__int_as_float(c[0]), 12582912.f),
-                                          __fmul_rn(ws0, asv.x), acc[j][0]);
-                    acc[j][1] = __fmaf_rn(__fsub_rn(__int_as_float(c[1]), 12582912.f),
-                                          __fmul_rn(ws0, asv.y), acc[j][1]);
-                    acc[j][2] = __fmaf_rn(__fsub_rn(__int_as_float(c[2]), 12582912.f),
-                                          __fmul_rn(ws1, asv.x), acc[j][2]);
-                    acc[j][3] = __fmaf_rn(__fsub_rn(__int_as_float(c[3]), 12582912.f),
-                                          __fmul_rn(ws1, asv.y), acc[j][3]);
+                        for (int sb = 0; sb < 4; ++sb) {
+                            const int2 bias = *reinterpret_cast<const int2*>(es + sb * m8 + tk);
+                            const float2 asv = *reinterpret_cast<const float2*>(as + sb * m8 + tk);
+                            int c[4] = {bias.x, bias.y, bias.x, bias.y};
+                            gm_mma(c, lo0[sb], lo1[sb], hi0[sb], hi1[sb], bev[sb], bov[sb]);
+                            acc[j][0] = __fmaf_rn(__fsub_rn(__int_as_float(c[0]), 12582912.f),
+                                                  __fmul_rn(ws0, asv.x), acc[j][0]);
+                            acc[j][1] = __fmaf_rn(__fsub_rn(__int_as_float(c[1]), 12582912.f),
+                                                  __fmul_rn(ws0, asv.y), acc[j][1]);
+                            acc[j][2] = __fmaf_rn(__fsub_rn(__int_as_float(c[2]), 12582912.f),
+                                                  __fmul_rn(ws1, asv.x), acc[j][2]);
+                            acc[j][3] = __fmaf_rn(__fsub_rn(__int_as_float(c[3]), 12582912.f),
+                                                  __fmul_rn(ws1, asv.y), acc[j][3]);
+                        }
+                    } else {
+                        const int2 bias = *reinterpret_cast<const int2*>(es + tk);
+                        const float2 asv = *reinterpret_cast<const float2*>(as + tk);
+                        // two chains of two instructions (latency), joined by one add
+                        int c[4] = {bias.x, bias.y, bias.x, bias.y}, c2[4] = {0, 0, 0, 0};
+                        gm_mma(c, lo0[0], lo1[0], lo0[1], lo1[1], be.x, be.y);
+                        gm_mma(c2, hi0[0], hi1[0], hi0[1], hi1[1], bo.x, bo.y);
+                        gm_mma(c, lo0[2], lo1[2], lo0[3], lo1[3], be.z, be.w);
+                        gm_mma(c2, hi0[2], hi1[2], hi0[3], hi1[3], bo.z, bo.w);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i)
+                            c[i] += c2[i];
+                        // c = 0x4B400000 + D: as a float 12582912 + D, exactly
+                        acc[j][0] = __fmaf_rn(__fsub_rn(__int_as_float(c[0]), 12582912.f),
+                                              __fmul_rn(ws0, asv.x), acc[j][0]);
+                        acc[j][1] = __fmaf_rn(__fsub_rn(__int_as_float(c[1]), 12582912.f),
+                                              __fmul_rn(ws0, asv.y), acc[j][1]);
+                        acc[j][2] = __fmaf_rn(__fsub_rn(__int_as_float(c[2]), 12582912.f),
+                                              __fmul_rn(ws1, asv.x), acc[j][2]);
+                        acc[j][3] = __fmaf_rn(__fsub_rn(__int_as_float(c[3]), 12582912.f),
+                                              __fmul_rn(ws1, asv.y), acc[j][3]);
+                    }
                 }
             }
         }
@@ -269,14 +298,14 @@ gemm_w4a8_mma_kernel(const GemmMmaArgs a) {
     }
 }
 
-size_t gemm_mma_smem(int groups, int cap, int m8, bool scl16, int stages = kMinStages) {
+size_t gemm_mma_smem(int groups, int cap, int m8, bool scl16, int spg, int stages = kMinStages) {
     return (size_t)cap * groups * 512 + (size_t)cap * groups * 8 * (scl16 ? 2 : 4) +
-           stages * ((size_t)m8 * kRowBytes + 2 * sizeof(float) * (size_t)m8) + 16;
+           stages * ((size_t)m8 * kRowBytes + 2 * sizeof(float) * (size_t)m8 * spg) + 16;
 }
 
-template <int CB, bool SCL16>
+template <int CB, bool SCL16, bool A32>
 int gemm_mma_launch(b2w4_ctx* ctx, const GemmMmaArgs& a, size_t smem, int ctas) {
-    auto kern = gemm_w4a8_mma_kernel<CB, SCL16>;
+    auto kern = gemm_w4a8_mma_kernel<CB, SCL16, A32>;
     static size_t configured = 48 * 1024;  // per instantiation; one device per process
     if (smem > configured) {
         B2W4_CUDA(ctx, cudaFuncSetAttribute(
@@ -300,34 +329,40 @@ int gemm_mma_launch(b2w4_ctx* ctx, const GemmMmaArgs& a, size_t smem, int ctas) 
 
 template <int CB>
 int gemm_mma_launch_cb(b2w4_ctx* ctx, const GemmMmaArgs& a, bool scl16, size_t smem, int ctas) {
-    return scl16 ? gemm_mma_launch<CB, true>(ctx, a, smem, ctas)
-                 : gemm_mma_launch<CB, false>(ctx, a, smem, ctas);
+    if (a.spg == 4)
+        return scl16 ? gemm_mma_launch<CB, true, true>(ctx, a, smem, ctas)
+                     : gemm_mma_launch<CB, false, true>(ctx, a, smem, ctas);
+    return scl16 ? gemm_mma_launch<CB, true, false>(ctx, a, smem, ctas)
+                 : gemm_mma_launch<CB, false, false>(ctx, a, smem, ctas);
 }
 
 }  // namespace
 
 // True when the shape fits this kernel: a tile (8 rows x K) plus the activation ring must fit
 // one SM's shared memory.
-bool b2w4_gemm_mma_fits(const b2w4_weight* w, int m) {
+bool b2w4_gemm_mma_fits(const b2w4_weight* w, int m, int act_rule) {
     const int m8 = (std::min(m, kMaxRows) + 7) & ~7;
-    return gemm_mma_smem(w->groups, 2, m8, w->scales_fp16 != 0) <= 220 * 1024;
+    const int spg = act_rule == B2W4_ACT_G32 ? 4 : 1;
+    return gemm_mma_smem(w->groups, 2, m8, w->scales_fp16 != 0, spg) <= 220 * 1024;
 }
 
 // True when, with one CTA per SM, the CTA's weights and ALL groups of the activations fit in
 // shared memory together: the regime this kernel is the fastest in (measured on config 2:
 // 16 rows 14 us against 19 us on the tcgen05 kernel; from 64 rows on the tcgen05 kernel wins).
-bool b2w4_gemm_mma_resident(const b2w4_weight* w, int m, int sm_count) {
+bool b2w4_gemm_mma_resident(const b2w4_weight* w, int m, int act_rule, int sm_count) {
     if (m > kMaxRows)
         return false;
     const int m8 = (m + 7) & ~7;
     const int cap = (w->tiles + sm_count - 1) / sm_count;
-    return gemm_mma_smem(w->groups, cap, m8, w->scales_fp16 != 0, w->groups) <= 220 * 1024;
+    const int spg = act_rule == B2W4_ACT_G32 ? 4 : 1;
+    return gemm_mma_smem(w->groups, cap, m8, w->scales_fp16 != 0, spg, w->groups) <= 220 * 1024;
 }
 
 int b2w4_launch_gemm_mma(b2w4_ctx* ctx, const b2w4_weight* w, const float* x, int lda,
-                         float* y, int ldc, int m, int activation, int act_n_begin,
-                         int act_n_len) {
+                         float* y, int ldc, int m, int act_rule, int activation,
+                         int act_n_begin, int act_n_len) {
     const int G = w->groups;
+    const int spg = act_rule == B2W4_ACT_G32 ? 4 : 1;
     const bool scl16 = w->scales_fp16 != 0;
     for (int m0 = 0; m0 < m; m0 += kMaxRows) {
         const int mc = std::min(kMaxRows, m - m0);
@@ -335,11 +370,12 @@ int b2w4_launch_gemm_mma(b2w4_ctx* ctx, const b2w4_weight* w, const float* x, in
         void *qa = nullptr, *sc = nullptr;
         int rc;
         if ((rc = b2w4_reserve(ctx, SCR_QA, (size_t)mc * w->k, &qa)) != B2W4_OK ||
-            (rc = b2w4_reserve(ctx, SCR_AS, 2 * sizeof(float) * (size_t)G * m8, &sc)) != B2W4_OK)
+            (rc = b2w4_reserve(ctx, SCR_AS, 2 * sizeof(float) * (size_t)G * spg * m8, &sc)) !=
+                B2W4_OK)
             return rc;
         float* as_t = static_cast<float*>(sc);
-        int32_t* es_t = reinterpret_cast<int32_t*>(as_t + (size_t)G * m8);
-        if ((rc = b2w4_launch_quantize_mma(ctx, x + (size_t)m0 * lda, lda, mc, w->k, m8,
+        int32_t* es_t = reinterpret_cast<int32_t*>(as_t + (size_t)G * spg * m8);
+        if ((rc = b2w4_launch_quantize_mma(ctx, x + (size_t)m0 * lda, lda, mc, w->k, m8, act_rule,
                                            static_cast<int8_t*>(qa), as_t, es_t)) != B2W4_OK)
             return rc;
         // tiles per CTA: what fits beside the activation ring, one CTA per SM when possible
@@ -347,9 +383,9 @@ int b2w4_launch_gemm_mma(b2w4_ctx* ctx, const b2w4_weight* w, const float* x, in
         const int ncb = m8 / 8;
         const int min_wpp = (ncb + 11) / 12;
         int cap = std::min(16, 2 * (kGemmWarps / min_wpp));
-        while (cap > 1 && gemm_mma_smem(G, cap, m8, scl16) > 220 * 1024)
+        while (cap > 1 && gemm_mma_smem(G, cap, m8, scl16, spg) > 220 * 1024)
             --cap;
-        if (gemm_mma_smem(G, cap, m8, scl16) > 220 * 1024)
+        if (gemm_mma_smem(G, cap, m8, scl16, spg) > 220 * 1024)
             return b2w4_fail(ctx, B2W4_E_INVALID, "gemm: K=%d needs too much shared memory", w->k);
         const int sms = ctx->sm_count;
         int ctas = (w->tiles + sms - 1) / sms <= cap ? std::min(w->tiles, sms)
@@ -364,6 +400,7 @@ int b2w4_launch_gemm_mma(b2w4_ctx* ctx, const b2w4_weight* w, const float* x, in
         a.ldc = ldc;
         a.m = mc;
         a.m_pad = m8;
+        a.spg = spg;
         a.n = w->n;
         a.k = w->k;
         a.groups = G;
@@ -375,13 +412,13 @@ int b2w4_launch_gemm_mma(b2w4_ctx* ctx, const b2w4_weight* w, const float* x, in
         a.act_n_begin = act_n_begin;
         a.act_n_len = act_n_len;
         a.stages = kMinStages;
-        if (gemm_mma_smem(G, a.tile_cap, m8, scl16, G) <= 220 * 1024)
+        if (gemm_mma_smem(G, a.tile_cap, m8, scl16, spg, G) <= 220 * 1024)
             a.stages = G;  // few tokens: all groups resident, no per-group barrier
         else
             while (a.stages < kMaxStages &&
-                   gemm_mma_smem(G, a.tile_cap, m8, scl16, a.stages + 1) <= 220 * 1024)
+                   gemm_mma_smem(G, a.tile_cap, m8, scl16, spg, a.stages + 1) <= 220 * 1024)
                 ++a.stages;
-        const size_t smem = gemm_mma_smem(G, a.tile_cap, m8, scl16, a.stages);
+        const size_t smem = gemm_mma_smem(G, a.tile_cap, m8, scl16, spg, a.stages);
         // column blocks per warp: 16 warps over the CTA's tile pairs
         const int wpp = kGemmWarps / ((a.tile_cap + 1) / 2);
         const int need = (ncb + wpp - 1) / wpp;
