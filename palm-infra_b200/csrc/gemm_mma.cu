@@ -90,6 +90,7 @@ __device__ __forceinline__ void gm_wait_groups(int n) {
 }
 
 // one stage = one 128-k group of every token: codes, scales, accumulator biases
+template <int SPG>
 __device__ __forceinline__ void load_stage(const GemmMmaArgs& a, int g, uint8_t* s_b, float* s_as,
                                            int* s_es) {
     const int chunks = a.m * 8;  // 16-byte chunks
@@ -99,11 +100,12 @@ __device__ __forceinline__ void load_stage(const GemmMmaArgs& a, int g, uint8_t*
                       a.qa + (size_t)t * a.k + (size_t)g * 128 + c * 16);
     }
     const int m8 = (a.m + 7) & ~7;
-    for (int i = threadIdx.x; i < a.m * a.spg; i += kGemmThreads) {
-        const int sb = i / a.m, t = i - sb * a.m;
-        gm_cp_async4(s_as + sb * m8 + t, a.as_t + (size_t)(g * a.spg + sb) * a.m_pad + t);
-        gm_cp_async4(s_es + sb * m8 + t, a.es_t + (size_t)(g * a.spg + sb) * a.m_pad + t);
-    }
+#pragma unroll
+    for (int sb = 0; sb < SPG; ++sb)
+        for (int t = threadIdx.x; t < a.m; t += kGemmThreads) {
+            gm_cp_async4(s_as + sb * m8 + t, a.as_t + (size_t)(g * SPG + sb) * a.m_pad + t);
+            gm_cp_async4(s_es + sb * m8 + t, a.es_t + (size_t)(g * SPG + sb) * a.m_pad + t);
+        }
 }
 
 template <int CB, bool SCL16, bool A32>
@@ -149,7 +151,7 @@ gemm_w4a8_mma_kernel(const GemmMmaArgs a) {
     const int pre = resident ? G : S - 1;
     for (int g = 0; g < pre; ++g) {
         if (g < G)
-            load_stage(a, g, s_b + (size_t)g * m8 * kRowBytes, s_as + g * SPG * m8,
+            load_stage<SPG>(a, g, s_b + (size_t)g * m8 * kRowBytes, s_as + g * SPG * m8,
                        s_es + g * SPG * m8);
         asm volatile("cp.async.commit_group;" ::: "memory");
     }
@@ -182,7 +184,7 @@ gemm_w4a8_mma_kernel(const GemmMmaArgs a) {
             __syncthreads();  // stage g visible to all; everyone is done with stage g-1
             if (g + S - 1 < G) {
                 const int sn = (g + S - 1) % S;  // the slot stage g-1 used
-                load_stage(a, g + S - 1, s_b + (size_t)sn * m8 * kRowBytes, s_as + sn * SPG * m8,
+                load_stage<SPG>(a, g + S - 1, s_b + (size_t)sn * m8 * kRowBytes, s_as + sn * SPG * m8,
                            s_es + sn * SPG * m8);
             }
             asm volatile("cp.async.commit_group;" ::: "memory");
