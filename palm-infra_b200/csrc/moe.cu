@@ -176,7 +176,7 @@ __global__ void moe_router_logits_scalar_kernel(const float* __restrict__ hidden
 // result is the k largest logits in descending order, equal logits in ascending expert id,
 // and a logit that is -inf or NaN never displaces the initial (expert 0, -inf) slot.  Here
 // that is k rounds of a warp-wide arg-max over (logit descending, expert id ascending) with
-// taken experts masked out.  Then the softmax over the selected logits: exp(l - l_max),
+// taken experts masked out; a round is two warp reductions (redux.sync) on integer keys.  Then the softmax over the selected logits: exp(l - l_max),
 // sequential fp32 sum, times 1/sum (:157-166).
 constexpr int kMaxTopK = 16;
 constexpr int kSelectMaxExperts = 1024;  // 32 lanes x 32 logits in registers
@@ -189,42 +189,45 @@ __device__ __forceinline__ int select_routes_warp(const float* logits, int t,
                                                   int32_t* __restrict__ idx,
                                                   float* __restrict__ weights, int lane) {
     const float* row = logits + (size_t)t * num_experts;
-    // the lane's logits (experts lane, lane+32, ...) stay in registers for all k rounds; a
-    // selected or absent expert becomes NaN, which no '>' ever accepts
+    // the lane's logits (experts lane, lane+32, ...) stay in registers for all k rounds
     float mine[NS];
 #pragma unroll
     for (int s = 0; s < NS; ++s)
         mine[s] = lane + 32 * s < num_experts ? row[lane + 32 * s] : NAN;
     float my_v = -INFINITY;   // lane j keeps the j-th selected logit
     int my_e = 0;
+    // Order-preserving integer key of a logit: larger float <=> larger key, -0 counted as +0
+    // like the float comparison does; NaN and -inf get key 0, which never qualifies (the
+    // insertion's strict '>' against its initial -inf).
+    uint32_t key[NS];
+#pragma unroll
+    for (int s = 0; s < NS; ++s) {
+        const float v = __fadd_rn(mine[s], 0.f);
+        const uint32_t u = __float_as_uint(v);
+        key[s] = !(v > -INFINITY) ? 0u : ((u & 0x80000000u) ? ~u : (u | 0x80000000u));
+    }
     for (int j = 0; j < top_k; ++j) {
-        float bv = -INFINITY;
-        int be = INT_MAX;
+        uint32_t bk = 0u;
+        int bs = 0;
 #pragma unroll
-        for (int s = 0; s < NS; ++s) {
-            if (mine[s] > bv) {
-                bv = mine[s];
-                be = lane + 32 * s;
+        for (int s = 0; s < NS; ++s)
+            if (key[s] > bk) {  // strict: of equal logits the lower expert id stays
+                bk = key[s];
+                bs = s;
             }
-        }
-#pragma unroll
-        for (int off = 16; off > 0; off >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, bv, off);
-            const int oe = __shfl_xor_sync(0xffffffffu, be, off);
-            if (oe != INT_MAX && (be == INT_MAX || ov > bv || (ov == bv && oe < be))) {
-                bv = ov;
-                be = oe;
-            }
-        }
-        if (be != INT_MAX && (be & 31) == lane) {
+        // two warp reductions: the largest key, then the lowest expert id that holds it
+        const uint32_t wk = __reduce_max_sync(0xffffffffu, bk);
+        const uint32_t we = __reduce_min_sync(
+            0xffffffffu, (wk != 0u && bk == wk) ? (uint32_t)(lane + 32 * bs) : 0xffffffffu);
+        if (wk != 0u && (int)(we & 31u) == lane) {
 #pragma unroll
             for (int s = 0; s < NS; ++s)
-                if (s == (be >> 5))
-                    mine[s] = NAN;
+                if (s == (int)(we >> 5))
+                    key[s] = 0u;  // taken
         }
-        if (lane == j) {
-            my_v = be == INT_MAX ? -INFINITY : bv;
-            my_e = be == INT_MAX ? 0 : be;
+        if (lane == j && wk != 0u) {  // the key gives the logit back, bit for bit
+            my_v = __uint_as_float((wk & 0x80000000u) ? (wk ^ 0x80000000u) : ~wk);
+            my_e = (int)we;
         }
     }
     const float maximum = __shfl_sync(0xffffffffu, my_v, 0);
@@ -294,6 +297,8 @@ moe_compact_kernel(const int32_t* __restrict__ idx, int tokens, int top_k, int n
     const unsigned lt = (1u << lane) - 1u;
     for (int e = threadIdx.x; e <= E; e += blockDim.x)
         s_cnt[e] = 0;
+    for (int y = threadIdx.x; y < E; y += blockDim.x)
+        slots[y] = make_int4(0, 0, 0, 0);  // experts with routes overwrite theirs below
     __syncthreads();
     for (int i0 = 0; i0 < routes; i0 += blockDim.x) {
         const int i = i0 + threadIdx.x;
@@ -316,9 +321,6 @@ moe_compact_kernel(const int32_t* __restrict__ idx, int tokens, int top_k, int n
             s_cursor[e] = run;
             if (s_cnt[e] > 0)
                 slots[rank] = make_int4(e, run, run + s_cnt[e], 0);
-        } else {
-            for (int y = rank; y < E; ++y)  // slots past the last expert with routes: empty
-                slots[y] = make_int4(0, 0, 0, 0);
         }
     }
     __syncthreads();
@@ -434,6 +436,8 @@ moe_route_fused_kernel(const float* __restrict__ hidden, int ldx, int tokens, in
     }
     for (int e = threadIdx.x; e <= num_experts; e += kFusedThreads)
         s_cnt[e] = 0;
+    for (int y = threadIdx.x; y < num_experts; y += kFusedThreads)
+        slots[y] = make_int4(0, 0, 0, 0);  // experts with routes overwrite theirs below
     __syncthreads();
     const int routes = tokens * top_k;
     if (threadIdx.x < routes)
@@ -475,10 +479,7 @@ moe_route_fused_kernel(const float* __restrict__ hidden, int ldx, int tokens, in
         rank += wrank - (c > 0);
         if (e <= num_experts) {
             offsets[e] = run;
-            if (e == num_experts) {
-                for (int y = rank; y < num_experts; ++y)  // the remaining slots: empty
-                    slots[y] = make_int4(0, 0, 0, 0);
-            } else if (c > 0) {
+            if (e < num_experts && c > 0) {
                 slots[rank] = make_int4(e, run, run + c, 0);
                 for (int i = 0; i < routes; ++i)
                     if (s_route[i] == e) {
