@@ -572,13 +572,16 @@ moe_combine_kernel(const float* __restrict__ dn, const int32_t* __restrict__ idx
         // for the repeated placeholder slots of a degenerate row: ties go to the lower slot)
         const int j = threadIdx.x;
         const int key = idx[(size_t)t * top_k + j];
+        // loaded before the rank is known: one memory round trip instead of two
+        const int row = pos ? pos[(size_t)t * top_k + j] : t * top_k + j;
+        const float w = weights[(size_t)t * top_k + j];
         int rank = 0;
         for (int o = 0; o < top_k; ++o) {
             const int other = idx[(size_t)t * top_k + o];
             rank += other < key || (other == key && o < j);
         }
-        s_row[rank] = pos ? pos[(size_t)t * top_k + j] : t * top_k + j;
-        s_w[rank] = weights[(size_t)t * top_k + j];
+        s_row[rank] = row;
+        s_w[rank] = w;
     }
     __syncthreads();
     const int d = (blockIdx.x * kCombineThreads + threadIdx.x) * 4;
