@@ -1009,7 +1009,7 @@ moe_grouped_gemv_kernel(const GroupedArgs a) {
                 continue;
             const bool two = !split_tiles && t0 + 1 < ntile;
             float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-#pragma unroll 2
+#pragma unroll 4
             for (int g = 0; g < G; ++g) {
                 // word `lane` of the 128 bytes of (tile, group, 32-block s): row gid, k 8*tid..+7
                 const int wbase = t0 * tile_words + g * 128 + lane;
