@@ -71,6 +71,15 @@ def measured_peaks():
     return 6650.0, "fallback"
 
 
+def measured_tensor_peak():
+    """Dense bf16 TFLOP/s of a cuBLAS GEMM timed alone on this pool (the tensor roofline the
+    many-row matmuls are held against; the int8 path's own peak is twice that)."""
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        return float(json.load(open(path))["bf16_tflops"]), "measured"
+    return 1590.0, "fallback"
+
+
 class ClockSampler:
     """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
@@ -462,10 +471,18 @@ def run_ours(args):
         for m in (4, 8, 16, 64, 256):
             s_ms = time_steps(torch, make_step(m, passes=1), max(3, min(args.steps, 25)), 3)
             per = s_ms * 1e-3 / COPIES
-            sweep[f"m{m}"] = {"us_per_matmul": per * 1e6,
-                              "gbs": algorithmic_bytes(N_OUT, K_IN, m) / per / 1e9,
-                              "tflops": 2.0 * m * N_OUT * K_IN / per / 1e12,
-                              "tokens_per_s": m / per}
+            tflops = 2.0 * m * N_OUT * K_IN / per / 1e12
+            gbs = algorithmic_bytes(N_OUT, K_IN, m) / per / 1e9
+            t_peak, t_kind = measured_tensor_peak()
+            sweep[f"m{m}"] = {"us_per_matmul": per * 1e6, "gbs": gbs, "tflops": tflops,
+                              "tokens_per_s": m / per,
+                              # the binding roofline of the shape: weight streaming up to 64
+                              # rows, the tensor pipe at 256
+                              "roofline": ({"bound": "tensor", "frac": tflops / t_peak,
+                                            "peak": t_peak, "unit": "TFLOP/s", "peak_kind": t_kind}
+                                           if m >= 256 else
+                                           {"bound": "hbm", "frac": gbs / peak, "peak": peak,
+                                            "unit": "GB/s", "peak_kind": peak_kind})}
         # the reference's M > 1 rule (one activation scale per 32 values) on the prefill shape
         s_ms = time_steps(torch, make_step(256, rule=pkg.capi.ACT_G32, passes=1),
                           max(3, min(args.steps, 25)), 3)
