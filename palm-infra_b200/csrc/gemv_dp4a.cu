@@ -306,7 +306,7 @@ gemv_w4a8_kernel(const GemvArgs a) {
         const float* csrc = s_sc + (size_t)tl * a.d_stride + mi * 8 + rr;
         float acc = 0.f;
         // only the fused multiply-add depends on the previous step; the loads do not
-#pragma unroll 4
+#pragma unroll 10
         for (int j = 0; j < G * SPG; ++j) {
             const float dv = dsrc[j * MT * 8];
             acc = __fmaf_rn(dv, csrc[j * MT * 8], acc);
