@@ -25,11 +25,14 @@
 // item, lane (gl = lane/8, row = lane%8) owns group gl for one weight row, reads its four
 // 16-byte chunks (a quarter warp reads 128 contiguous bytes: no bank conflicts) and the
 // even/odd de-interleaved int8 activations (broadcast), and gets the group's int32 sum from
-// 32 dp4a with no cross-lane reduction.  Nibbles stay left-aligned in their bytes
-// ((w<<4)&0xF0F0F0F0 = even k, w&0xF0F0F0F0 = odd k, i.e. 16*q4 as int8); the int32 sum is
-// an exact multiple of 16 and is shifted back before conversion, like the NEON kernel's
-// sdot + fixed-point convert.  The integer sum (as a float: exact) and the scale product
-// fp32(ws*as) go to shared memory.
+// 32 dp4a with no cross-lane reduction.  A weight word w holds 8 nibbles; two logic
+// instructions split it without shifts:
+//   hi = w & 0xF0F0F0F0                  odd k, bytes = 16*q as int8
+//   lo = (w ^ 0x08080808) & 0x0F0F0F0F   even k, bytes = q+8 as uint8
+// sum(q*a) = dp4a.u8.s8(lo, a_even) - 8*sum(a_even) + dp4a.s8.s8(hi, a_odd)/16: the last
+// term is an exact multiple of 16 (like the NEON kernel's sdot on left-aligned nibbles and
+// its fixed-point convert) and sum(a_even) comes from the quantiser, one per group.  The
+// integer sum (as a float: exact) and the scale product fp32(ws*as) go to shared memory.
 // Phase 2, after one barrier: one thread per (tile, weight row, activation row) runs the
 // order-sensitive chain of fused multiply-adds over the groups in ascending order.
 #include "b200w4_internal.cuh"
@@ -52,6 +55,7 @@ struct GemvArgs {
     int* status;    // device status word: set when a bounded wait gives up
     int lda, ldc, m, n, k, groups, tiles;
     int tpc;       // tiles per CTA
+    int ipt_magic; // item / items-per-tile == (item * ipt_magic) >> 16, or 0: divide
     int d_stride;  // ints between the integer sums of consecutive tiles (padded)
     int activation, act_n_begin, act_n_len;
 };
@@ -107,6 +111,13 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar) {
     return false;
 }
 
+// uint8 x int8 dot of four byte pairs
+__device__ __forceinline__ int dp4a_us(uint32_t a, uint32_t b, int c) {
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
 // the fused activations carry fp64 exp / tanh code: keep one out-of-line copy
 __device__ __noinline__ float gemv_activation(float v, int act) {
     return b2w4_activation(v, act);
@@ -129,7 +140,8 @@ gemv_w4a8_kernel(const GemvArgs a) {
     float* s_as = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(s_qa) + (size_t)MT * K);
     // per (tile, group, [32-block], activation row, weight row): the integer sum as a float
     // (exact: |sum| < 2^24) and the scale product it is multiplied with
-    float* s_d = s_as + MT * G * SPG;                      // [tpc][G][SPG][MT][8] + pad
+    int* s_es = reinterpret_cast<int*>(s_as + MT * G * SPG);  // -8 * sum of the even-k codes
+    float* s_d = reinterpret_cast<float*>(s_es + MT * G * SPG);  // [tpc][G][SPG][MT][8] + pad
     float* s_sc = s_d + (size_t)a.tpc * a.d_stride;        // same shape
     uint64_t* s_bar = reinterpret_cast<uint64_t*>(
         (reinterpret_cast<uintptr_t>(s_sc + (size_t)a.tpc * a.d_stride) + 7) & ~uintptr_t(7));
@@ -204,13 +216,20 @@ gemv_w4a8_kernel(const GemvArgs a) {
 #pragma unroll
             for (int i = 0; i < 8; ++i)
                 c[i] = b2w4_quant_code(v[i], inv);
+            int esum = c[0] + c[2] + c[4] + c[6];  // integer: order-free
+#pragma unroll
+            for (int off = (A32 ? 2 : 8); off > 0; off >>= 1)
+                esum += __shfl_xor_sync(0xffffffffu, esum, off);
             if (!live)
                 continue;
             if (A32) {
-                if ((h & 3) == 0)
+                if ((h & 3) == 0) {
                     s_as[mi * G * 4 + g * 4 + (h >> 2)] = scale;
+                    s_es[mi * G * 4 + g * 4 + (h >> 2)] = -8 * esum;
+                }
             } else if (h == 0) {
                 s_as[mi * G + g] = scale;
+                s_es[mi * G + g] = -8 * esum;
             }
             // 32-block h/4 is stored as 16 even-k codes then 16 odd-k codes
             uint8_t* blk = reinterpret_cast<uint8_t*>(s_qa) + (size_t)mi * K + (size_t)g * 128 +
@@ -230,7 +249,7 @@ gemv_w4a8_kernel(const GemvArgs a) {
     bool timed_out = !mbar_wait_bounded(&s_bar[ntile]);  // weight scales
 #pragma unroll 1
     for (int it = warp; it < n_items && !timed_out; it += kWarps) {
-        const int tl = it / ipt;
+        const int tl = a.ipt_magic ? (it * a.ipt_magic) >> 16 : it / ipt;
         const int g = (it - tl * ipt) * 4 + gl;
         if (!mbar_wait_bounded(&s_bar[tl])) {
             timed_out = true;
@@ -238,21 +257,23 @@ gemv_w4a8_kernel(const GemvArgs a) {
         }
         if (g < G) {
             const uint4* wt =
-                reinterpret_cast<const uint4*>(s_w + (size_t)tl * tile_bytes) + g * 32 + row;
-            uint32_t we[16], wo[16];
+                reinterpret_cast<const uint4*>(s_w) + (tl * tile_bytes >> 4) + g * 32 + row;
+            // a weight word holds 8 nibbles; two logic instructions split it without shifts:
+            // odd k as 16*q (int8), even k as q+8 (uint8)
+            uint32_t wl[16], wh[16];
 #pragma unroll
             for (int s = 0; s < 4; ++s) {
                 const uint4 w = wt[s * 8];
-                we[s * 4 + 0] = (w.x << 4) & 0xF0F0F0F0u;
-                wo[s * 4 + 0] = w.x & 0xF0F0F0F0u;
-                we[s * 4 + 1] = (w.y << 4) & 0xF0F0F0F0u;
-                wo[s * 4 + 1] = w.y & 0xF0F0F0F0u;
-                we[s * 4 + 2] = (w.z << 4) & 0xF0F0F0F0u;
-                wo[s * 4 + 2] = w.z & 0xF0F0F0F0u;
-                we[s * 4 + 3] = (w.w << 4) & 0xF0F0F0F0u;
-                wo[s * 4 + 3] = w.w & 0xF0F0F0F0u;
+                wl[s * 4 + 0] = (w.x ^ 0x08080808u) & 0x0F0F0F0Fu;
+                wh[s * 4 + 0] = w.x & 0xF0F0F0F0u;
+                wl[s * 4 + 1] = (w.y ^ 0x08080808u) & 0x0F0F0F0Fu;
+                wh[s * 4 + 1] = w.y & 0xF0F0F0F0u;
+                wl[s * 4 + 2] = (w.z ^ 0x08080808u) & 0x0F0F0F0Fu;
+                wh[s * 4 + 2] = w.z & 0xF0F0F0F0u;
+                wl[s * 4 + 3] = (w.w ^ 0x08080808u) & 0x0F0F0F0Fu;
+                wh[s * 4 + 3] = w.w & 0xF0F0F0F0u;
             }
-            const size_t slot = (size_t)tl * a.d_stride + (size_t)g * SPG * MT * 8 + row;
+            const int slot = tl * a.d_stride + g * SPG * MT * 8 + row;
             float* dst = s_d + slot;
             float* dsc = s_sc + slot;
             const float ws =
@@ -261,30 +282,33 @@ gemv_w4a8_kernel(const GemvArgs a) {
 #pragma unroll
             for (int mi = 0; mi < MT; ++mi) {
                 if (mi < a.m) {
-                    const uint4* qa = s_qa + ((size_t)mi * K + (size_t)g * 128) / 16;
-                    int total = 0;
+                    const uint4* qa = s_qa + ((mi * K + g * 128) >> 4);
+                    int pt = 0, qt = 0;
 #pragma unroll
                     for (int s = 0; s < 4; ++s) {
                         const uint4 ae = qa[s * 2], ao = qa[s * 2 + 1];
                         // two independent chains per sub-block hide dp4a latency
-                        int p = __dp4a((int)we[s * 4 + 0], (int)ae.x, 0);
-                        int q = __dp4a((int)wo[s * 4 + 0], (int)ao.x, 0);
-                        p = __dp4a((int)we[s * 4 + 1], (int)ae.y, p);
-                        q = __dp4a((int)wo[s * 4 + 1], (int)ao.y, q);
-                        p = __dp4a((int)we[s * 4 + 2], (int)ae.z, p);
-                        q = __dp4a((int)wo[s * 4 + 2], (int)ao.z, q);
-                        p = __dp4a((int)we[s * 4 + 3], (int)ae.w, p);
-                        q = __dp4a((int)wo[s * 4 + 3], (int)ao.w, q);
+                        int p = dp4a_us(wl[s * 4 + 0], ae.x, 0);
+                        int q = __dp4a((int)wh[s * 4 + 0], (int)ao.x, 0);
+                        p = dp4a_us(wl[s * 4 + 1], ae.y, p);
+                        q = __dp4a((int)wh[s * 4 + 1], (int)ao.y, q);
+                        p = dp4a_us(wl[s * 4 + 2], ae.z, p);
+                        q = __dp4a((int)wh[s * 4 + 2], (int)ao.z, q);
+                        p = dp4a_us(wl[s * 4 + 3], ae.w, p);
+                        q = __dp4a((int)wh[s * 4 + 3], (int)ao.w, q);
                         if (A32) {
-                            dst[(s * MT + mi) * 8] = (float)((p + q) >> 4);  // multiple of 16
+                            // q sums 16*q4*a: an exact multiple of 16
+                            dst[(s * MT + mi) * 8] =
+                                (float)(p + s_es[mi * G * 4 + g * 4 + s] + (q >> 4));
                             dsc[(s * MT + mi) * 8] =
                                 __fmul_rn(ws, s_as[mi * G * 4 + g * 4 + s]);
                         } else {
-                            total += p + q;
+                            pt += p;
+                            qt += q;
                         }
                     }
                     if (!A32) {
-                        dst[mi * 8] = (float)(total >> 4);
+                        dst[mi * 8] = (float)(pt + s_es[mi * G + g] + (qt >> 4));
                         dsc[mi * 8] = __fmul_rn(ws, s_as[mi * G + g]);
                     }
                 }
@@ -330,7 +354,7 @@ int gemv_d_stride(int mt, int groups, bool a32) {
 size_t gemv_smem_bytes(int mt, int k, int groups, int tpc, bool scl16, bool a32) {
     const int spg = a32 ? 4 : 1;
     return (size_t)tpc * groups * 512 + (size_t)tpc * groups * 8 * (scl16 ? 2 : 4) +
-           (size_t)mt * k + sizeof(float) * mt * groups * spg +
+           (size_t)mt * k + 2 * sizeof(float) * mt * groups * spg +
            2 * sizeof(float) * (size_t)tpc * gemv_d_stride(mt, groups, a32) + 8 +
            sizeof(uint64_t) * (tpc + 1);
 }
@@ -416,7 +440,7 @@ int b2w4_launch_gemv(b2w4_ctx* ctx, const b2w4_weight* w, const float* x, int ld
         // CTAs 8.65.
         const int per_tile = w->groups * (512 + (scl16 ? 16 : 32)) +
                              8 * gemv_d_stride(mt, w->groups, a32);
-        const int budget = 113 * 1024 - mt * w->k - 4 * mt * w->groups * spg - 1024;
+        const int budget = 113 * 1024 - mt * w->k - 8 * mt * w->groups * spg - 1024;
         int tpc = max(1, min(budget / per_tile, kMaxTpc));
         const int wave_ctas = ctx->sm_count * 7 / 4;
         const int one_wave = (w->tiles + wave_ctas - 1) / wave_ctas;
@@ -424,6 +448,13 @@ int b2w4_launch_gemv(b2w4_ctx* ctx, const b2w4_weight* w, const float* x, int ld
         if (ctx->gemv_tpc_override > 0)
             tpc = min(tpc, ctx->gemv_tpc_override);
         a.tpc = tpc;
+        {
+            const int ipt = (w->groups + 3) / 4;
+            a.ipt_magic = 65536 / ipt + 1;
+            for (int it = 0; it < tpc * ipt; ++it)  // exact for every item of a CTA?
+                if (((it * a.ipt_magic) >> 16) != it / ipt)
+                    a.ipt_magic = 0;
+        }
         a.d_stride = gemv_d_stride(mt, w->groups, a32);
         const size_t smem = gemv_smem_bytes(mt, w->k, w->groups, tpc, scl16, a32);
         if (smem > 220 * 1024)
