@@ -42,7 +42,7 @@ L2_MB = 126
 
 # dram__bytes_read.sum + dram__bytes_write.sum of ONE gemv_w4a8_kernel launch on this workload,
 # from the ncu capture summarised in profiles/gemv_w4a8_m1_k2560_n9728.md
-NCU_DRAM_BYTES_PER_LAUNCH = 12873984
+NCU_DRAM_BYTES_PER_LAUNCH = 12876800
 
 
 def workload_config(world=1, passes=PASSES, graph=True):
