@@ -397,6 +397,66 @@ def run_ours(args):
         ctx.set_stream(torch.cuda.current_stream().cuda_stream)
         return g.replay
 
+    def make_peer_step(passes=args.passes):
+        """The same walk with the exchange inside the kernel: the GEMV's epilogue stores this
+        rank's rows into every rank's output over peer mappings (symmetric memory) and a
+        bounded wait kernel holds the stream until every rank's rows have landed.  Returns
+        None when symmetric memory is not available."""
+        try:
+            import torch.distributed._symmetric_memory as symm
+            y_sym = symm.empty((1, N_OUT), dtype=torch.float32, device=f"cuda:{local}")
+            arrive = symm.empty((64,), dtype=torch.int32, device=f"cuda:{local}")
+            arrive.zero_()
+            y_sym.zero_()
+            torch.cuda.synchronize()
+            hy = symm.rendezvous(y_sym, dist.group.WORLD.group_name)
+            ha = symm.rendezvous(arrive, dist.group.WORLD.group_name)
+        except Exception as exc:  # no peer mappings on this box: the NCCL walk stands
+            print(f"in-kernel exchange unavailable: {exc}", file=sys.stderr)
+            return None
+        group = pkg.capi.TpGroup()
+        group.rank, group.world = rank, world
+        for p_ in range(world):
+            group.y_peers[p_] = hy.buffer_ptrs[p_]
+            group.arrive_peers[p_] = ha.buffer_ptrs[p_]
+        x, y_local, y_full = make_io(1)
+        dist.barrier()
+        # once, eagerly: the gathered row must equal the NCCL all-gather of the shards, bit for bit
+        ctx.matmul(weights[0], x, y_local)
+        dist.all_gather_into_tensor(y_full, y_local)
+        ctx.matmul_tp(weights[0], x, N_OUT, rank * n_local, group)
+        ctx.tp_wait(group)
+        ctx.sync()
+        torch.cuda.synchronize()
+        want = y_full.permute(1, 0, 2).reshape(1, N_OUT)
+        if not torch.equal(want, y_sym):
+            raise RuntimeError("in-kernel exchange and all-gather disagree")
+        dist.barrier()
+
+        group.wait_previous = 1  # each GEMV first waits for the exchange before it
+
+        def eager():
+            for _ in range(passes):
+                for w in weights:
+                    ctx.matmul_tp(w, x, N_OUT, rank * n_local, group)
+            ctx.tp_wait(group)  # the step ends with every rank's rows here
+        eager()
+        torch.cuda.synchronize()
+        dist.barrier()
+        g = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            ctx.set_stream(side.cuda_stream)
+            with torch.cuda.graph(g, stream=side):
+                eager()
+        ctx.set_stream(torch.cuda.current_stream().cuda_stream)
+        keep = (y_sym, arrive, hy, ha, group)  # peer mappings live as long as the step
+
+        def replay():
+            g.replay()
+            return keep
+        return replay
+
     def max_over_ranks(v):
         if world == 1:
             return v
@@ -418,6 +478,17 @@ def run_ours(args):
     with ClockSampler(local) as clocks:
         ms = time_steps(torch, step, args.steps, args.warmup, barrier)
     ms = max_over_ranks(ms)
+    exchange = "none (one GPU)" if world == 1 else "NCCL all-gather after every GEMV"
+    nccl_ms = None
+    if world > 1 and args.rows == 1 and not args.no_graph and world <= 8:
+        peer_step = make_peer_step()
+        if peer_step is not None:
+            nccl_ms = ms
+            with ClockSampler(local) as clocks:
+                ms = time_steps(torch, peer_step, args.steps, args.warmup, barrier)
+            ms = max_over_ranks(ms)
+            exchange = ("in the GEMV kernel: peer stores into every rank's output + arrival "
+                        "counters; each GEMV waits (bounded) for the exchange before it")
     alg = algorithmic_bytes(N_OUT, K_IN, 1)
     gemvs = COPIES * args.passes
     value = gemvs * alg / (ms * 1e-3) / 1e9
@@ -437,6 +508,11 @@ def run_ours(args):
                          "avg_launch_us": launch_us},
             "clocks": clocks.summary(),
             "gpu_launches": launches_per_step * args.steps}
+    line["config"]["exchange"] = exchange
+    if nccl_ms is not None:
+        line["nccl_allgather_variant"] = {"value": gemvs * alg / (nccl_ms * 1e-3) / 1e9,
+                                          "unit": UNIT, "ms_per_step": nccl_ms}
+        line["gpu_launches"] = (launches_per_step + 1) * args.steps  # + one wait kernel
 
     if not args.headline_only:
         # ---- e2e: the same step through the host-buffer entry point (every rank streams its

@@ -175,6 +175,35 @@ int b2w4_moe_combine(b2w4_ctx* ctx, const float* route_out_dev, int tokens, int 
                      int top_k, const int32_t* indices_dev, const float* weights_dev,
                      float* out_dev, int ldo);
 
+/* ---- tensor-parallel decode matmul with the exchange inside the kernel -------
+ * No counterpart in the reference (one process, one device).  Rank r of `world`
+ * holds the rows [n_offset, n_offset + N_shard) of a weight (8-row tiles whole)
+ * and every rank needs the full output.  Instead of a matmul followed by an
+ * all-gather call, the kernel's epilogue stores its rows straight into every
+ * rank's copy of the output through peer mappings (y_peers[p] = rank p's
+ * [1][ldc] buffer as mapped into this process, e.g. the buffer_ptrs of a
+ * symmetric-memory rendezvous), and the launch's last CTA adds one to this
+ * rank's slot of every rank's arrival counters (arrive_peers[p] = rank p's
+ * uint32[world], zero before first use).  b2w4_tp_wait enqueues a bounded wait
+ * (about 50 ms, then B2W4_E_TIMEOUT through b2w4_sync) until every rank's rows of
+ * the latest matmul have landed here; work queued after it may read the output.
+ * With wait_previous != 0 the matmul itself does that wait for the previous
+ * exchange of the group before it reads x_dev (a chain of tensor-parallel
+ * matmuls then needs no kernel between them).  A rank may run one exchange
+ * ahead of its peers, so a caller that reuses an output buffer alternates two.
+ * One activation row per call; same arithmetic and bits as b2w4_matmul.  Every
+ * rank must issue the same sequence of calls. */
+typedef struct b2w4_tp_group {
+    int rank, world;       /* world <= 8 */
+    void* y_peers[8];
+    void* arrive_peers[8];
+    int wait_previous;
+} b2w4_tp_group;
+int b2w4_matmul_tp(b2w4_ctx* ctx, const b2w4_weight* w_shard, const float* x_dev, int ldc,
+                   int n_offset, const b2w4_tp_group* group, int activation, int act_n_begin,
+                   int act_n_len);
+int b2w4_tp_wait(b2w4_ctx* ctx, const b2w4_tp_group* group);
+
 /* Launch counter: how many of this library's kernels have been launched on the
  * context since creation (for benchmark bookkeeping). */
 uint64_t b2w4_kernel_launches(const b2w4_ctx* ctx);

@@ -22,10 +22,18 @@ SYMBOLS = [
     "b2w4_matmul_static_scratch",
     "b2w4_debug_group_sums", "b2w4_quantize_activations", "b2w4_moe_forward",
     "b2w4_moe_select_routes", "b2w4_moe_expert_outputs", "b2w4_moe_combine",
+    "b2w4_matmul_tp", "b2w4_tp_wait",
     "b2w4_kernel_launches",
 ]
 
 _lib = None
+
+
+class TpGroup(C.Structure):
+    """b2w4_tp_group: this rank, the world size, and every rank's output buffer and arrival
+    counters as mapped into this process (peer pointers)."""
+    _fields_ = [("rank", C.c_int), ("world", C.c_int), ("y_peers", C.c_void_p * 8),
+                ("arrive_peers", C.c_void_p * 8), ("wait_previous", C.c_int)]
 
 
 class B200W4Error(RuntimeError):
@@ -68,6 +76,8 @@ def lib():
         L.b2w4_moe_expert_outputs.argtypes = [vp, f_p, i, i, i, vp, i, i, i, vp, vp, i, i, f_p,
                                               vp, f_p]
         L.b2w4_moe_combine.argtypes = [vp, f_p, i, i, i, vp, f_p, f_p, i]
+        L.b2w4_matmul_tp.argtypes = [vp, vp, f_p, i, i, C.POINTER(TpGroup), i, i, i]
+        L.b2w4_tp_wait.argtypes = [vp, C.POINTER(TpGroup)]
         L.b2w4_kernel_launches.argtypes = [vp]
         L.b2w4_kernel_launches.restype = C.c_uint64
         _lib = L
@@ -185,6 +195,14 @@ class Context:
                 self._check(rc)
             return keep[2]
         return call
+
+    def matmul_tp(self, w_shard, x, ldc, n_offset, group, act=NONE, act_begin=0, act_len=-1):
+        """One-row matmul whose epilogue stores this rank's rows into every rank's output."""
+        self._check(lib().b2w4_matmul_tp(self.handle, w_shard.handle, _dptr(x), ldc, n_offset,
+                                         C.byref(group), act, act_begin, act_len))
+
+    def tp_wait(self, group):
+        self._check(lib().b2w4_tp_wait(self.handle, C.byref(group)))
 
     def group_sums(self, w, x, sums, rule=ACT_G128):
         self._check(lib().b2w4_debug_group_sums(self.handle, w.handle, _dptr(x),

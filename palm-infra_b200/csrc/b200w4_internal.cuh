@@ -78,9 +78,23 @@ int b2w4_launch_gemm_mma(b2w4_ctx* ctx, const b2w4_weight* w, const float* x, in
                          int act_n_begin, int act_n_len);
 int b2w4_launch_quantize_mma(b2w4_ctx* ctx, const float* x, int lda, int m, int k, int m_pad,
                              int act_rule, int8_t* q, float* scales_t, int32_t* es_t);
+// Tensor-parallel epilogue of the one-row GEMV: the kernel stores its rows into every rank's
+// copy of the output and the launch's last CTA bumps this rank's arrival counter on every
+// rank.  world == 0: off.
+constexpr int kTpMaxWorld = 8;
+struct b2w4_tp_args {
+    float* y_peer[kTpMaxWorld];          // rank p's output buffer, as mapped on this GPU
+    unsigned* arrive_peer[kTpMaxWorld];  // rank p's arrival counters [world]
+    unsigned* done;                      // this GPU's CTA counter (last-CTA detection)
+    int world, rank, n_offset;           // n_offset: first output column of this rank's rows
+    int wait_previous;                   // wait for the previous exchange before reading x
+};
+
 int b2w4_launch_gemv(b2w4_ctx* ctx, const b2w4_weight* w, const float* x, int lda,
                      float* y, int ldc, int m, int act_rule, int activation,
-                     int act_n_begin, int act_n_len, int32_t* sums);
+                     int act_n_begin, int act_n_len, int32_t* sums,
+                     const b2w4_tp_args* tp = nullptr);
+int b2w4_launch_tp_wait(b2w4_ctx* ctx, unsigned* arrive_local, int world, int rank);
 // 2..8 activation rows per pass on the int8 tensor instruction (gemv_mma.cu)
 int b2w4_launch_gemv_mma(b2w4_ctx* ctx, const b2w4_weight* w, const float* x, int lda,
                      float* y, int ldc, int m, int act_rule, int activation,

@@ -316,6 +316,43 @@ int b2w4_matmul_host(b2w4_ctx* ctx, const b2w4_weight* w, const float* x_host, i
     return B2W4_OK;
 }
 
+int b2w4_matmul_tp(b2w4_ctx* ctx, const b2w4_weight* w, const float* x_dev, int ldc,
+                   int n_offset, const b2w4_tp_group* group, int activation, int act_n_begin,
+                   int act_n_len) {
+    if (!ctx)
+        return B2W4_E_INVALID;
+    if (!w || !x_dev || !group || group->world < 1 || group->world > kTpMaxWorld ||
+        group->rank < 0 || group->rank >= group->world || n_offset < 0 ||
+        ldc < n_offset + w->n)
+        return b2w4_fail(ctx, B2W4_E_INVALID, "matmul_tp: bad argument");
+    if (activation < B2W4_NONE || activation > B2W4_RELU_SQUARED)
+        return b2w4_fail(ctx, B2W4_E_INVALID, "matmul_tp: unknown activation %d", activation);
+    b2w4_tp_args tp = {};
+    for (int p = 0; p < group->world; ++p) {
+        if (!group->y_peers[p] || !group->arrive_peers[p])
+            return b2w4_fail(ctx, B2W4_E_INVALID, "matmul_tp: null peer pointer");
+        tp.y_peer[p] = static_cast<float*>(group->y_peers[p]);
+        tp.arrive_peer[p] = static_cast<unsigned*>(group->arrive_peers[p]);
+    }
+    tp.done = reinterpret_cast<unsigned*>(ctx->flag_dev + 6);
+    tp.world = group->world;
+    tp.rank = group->rank;
+    tp.n_offset = n_offset;
+    tp.wait_previous = group->wait_previous;
+    return b2w4_launch_gemv(ctx, w, x_dev, w->k, nullptr, ldc, 1, B2W4_ACT_G128, activation,
+                            act_n_begin, act_n_len, nullptr, &tp);
+}
+
+int b2w4_tp_wait(b2w4_ctx* ctx, const b2w4_tp_group* group) {
+    if (!ctx)
+        return B2W4_E_INVALID;
+    if (!group || group->world < 1 || group->world > kTpMaxWorld || group->rank < 0 ||
+        group->rank >= group->world || !group->arrive_peers[group->rank])
+        return b2w4_fail(ctx, B2W4_E_INVALID, "tp_wait: bad argument");
+    return b2w4_launch_tp_wait(ctx, static_cast<unsigned*>(group->arrive_peers[group->rank]),
+                               group->world, group->rank);
+}
+
 int b2w4_debug_group_sums(b2w4_ctx* ctx, const b2w4_weight* w, const float* x_dev, int lda,
                           int m, int act_rule, int32_t* sums_dev) {
     if (!ctx)

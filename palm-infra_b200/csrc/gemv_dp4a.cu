@@ -45,6 +45,7 @@ __host__ __device__ constexpr int gemv_warps(int mt) { return mt == 1 ? 16 : 8; 
 constexpr int kMaxTpc = 16;
 constexpr unsigned kSpinLimit = 1u << 22;  // bounded waits: give up, flag, return
 constexpr unsigned long long kWaitLimitCycles = 4000000000ull;  // SM cycles: about 2 s
+constexpr unsigned long long kTpWaitLimitCycles = 100000000ull;  // about 50 ms
 
 struct GemvArgs {
     const uint4* nib;
@@ -58,6 +59,7 @@ struct GemvArgs {
     int ipt_magic; // item / items-per-tile == (item * ipt_magic) >> 16, or 0: divide
     int d_stride;  // ints between the integer sums of consecutive tiles (padded)
     int activation, act_n_begin, act_n_len;
+    b2w4_tp_args tp;  // tensor-parallel epilogue (world == 0: off)
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -176,6 +178,25 @@ gemv_w4a8_kernel(const GemvArgs a) {
     }
 
     b2w4_pdl_wait();  // activations come from the previous kernel
+
+    // Tensor-parallel chain: the activations may be the gathered output of the previous
+    // exchange, so every rank's rows of it must have landed here first.  This rank's own
+    // counter is final (its previous kernel has completed); thread r waits, bounded, for
+    // rank r's counter to reach it.
+    if (a.tp.world != 0 && a.tp.wait_previous) {
+        if ((int)threadIdx.x < a.tp.world) {
+            const volatile unsigned* arrive = a.tp.arrive_peer[a.tp.rank];
+            const unsigned target = arrive[a.tp.rank];
+            const unsigned long long t0 = wait_clock();
+            while ((int)(arrive[threadIdx.x] - target) < 0) {
+                if (wait_clock() - t0 > kTpWaitLimitCycles) {
+                    atomicExch(a.status, B2W4_E_TIMEOUT);
+                    break;
+                }
+            }
+        }
+        __syncthreads();
+    }
 
     // ---- fused activation quantiser: one half-warp per (activation row, group) ----------
     // lane h of the half-warp holds k = 8h .. 8h+7 of the group (a quarter of a 32-block)
@@ -340,7 +361,47 @@ gemv_w4a8_kernel(const GemvArgs a) {
         if (n < a.n) {
             if (b2w4_act_applies(n, a.activation, a.act_n_begin, a.act_n_len, a.n))
                 acc = gemv_activation(acc, a.activation);
-            a.y[(size_t)mi * a.ldc + n] = acc;
+            if (a.tp.world == 0) {
+                a.y[(size_t)mi * a.ldc + n] = acc;
+            } else {
+                // the all-gather is this store: every rank's copy of the output, this GPU's
+                // own included, gets the value over peer mappings
+                const size_t at = (size_t)mi * a.ldc + a.tp.n_offset + n;
+#pragma unroll
+                for (int p = 0; p < kTpMaxWorld; ++p)
+                    if (p < a.tp.world)
+                        a.tp.y_peer[p][at] = acc;
+            }
+        }
+    }
+    if (a.tp.world == 0)
+        return;
+    // Arrival: after the barrier one thread's system-wide fence covers the whole CTA's peer
+    // stores; the CTA that comes last (nobody waits for it) then tells every rank that this
+    // rank's rows have landed.
+    __syncthreads();
+    if (threadIdx.x != 0)
+        return;
+    __threadfence_system();
+    if (atomicAdd(a.tp.done, 1u) != gridDim.x - 1)
+        return;
+    *a.tp.done = 0;  // ready for the next launch
+    __threadfence_system();
+    for (int p = 0; p < a.tp.world; ++p)
+        atomicAdd_system(a.tp.arrive_peer[p] + a.tp.rank, 1u);
+}
+
+// Waits (bounded) until every rank's rows of the latest tensor-parallel matmul have landed on
+// this GPU: rank r's counter has caught up with this rank's own.  One thread per rank.
+__global__ void tp_wait_kernel(volatile unsigned* arrive, int world, int rank, int* status) {
+    if ((int)threadIdx.x >= world)
+        return;
+    const unsigned target = arrive[rank];
+    const unsigned long long t0 = wait_clock();
+    while ((int)(arrive[threadIdx.x] - target) < 0) {
+        if (wait_clock() - t0 > kTpWaitLimitCycles) {
+            atomicExch(status, B2W4_E_TIMEOUT);
+            return;
         }
     }
 }
@@ -405,7 +466,9 @@ int launch_mt(b2w4_ctx* ctx, const GemvArgs& a, bool scl16, bool a32, size_t sme
 // Rows are processed four at a time; each pass streams the weight once.
 int b2w4_launch_gemv(b2w4_ctx* ctx, const b2w4_weight* w, const float* x, int lda,
                      float* y, int ldc, int m, int act_rule, int activation,
-                     int act_n_begin, int act_n_len, int32_t* sums) {
+                     int act_n_begin, int act_n_len, int32_t* sums, const b2w4_tp_args* tp) {
+    if (tp && m > 1)
+        return b2w4_fail(ctx, B2W4_E_INVALID, "tensor-parallel epilogue: one row per call");
     if (m > 1)  // several rows share one pass over the weight on the tensor instruction
         return b2w4_launch_gemv_mma(ctx, w, x, lda, y, ldc, m, act_rule, activation, act_n_begin,
                                     act_n_len, sums);
@@ -432,6 +495,11 @@ int b2w4_launch_gemv(b2w4_ctx* ctx, const b2w4_weight* w, const float* x, int ld
         a.activation = activation;
         a.act_n_begin = act_n_begin;
         a.act_n_len = act_n_len;
+        a.tp = b2w4_tp_args();
+        if (tp)
+            a.tp = *tp;
+        else
+            a.tp.world = 0;
         // Tiles per CTA: a CTA's shared memory stays under half an SM's so that two CTAs share
         // an SM, and the launch is one wave of at most 1.75 CTAs per SM.  Measured on the
         // decode shapes of a 4B dense model (148 SMs): N=9728 K=2560 (1216 tiles) 244 CTAs
@@ -464,5 +532,12 @@ int b2w4_launch_gemv(b2w4_ctx* ctx, const b2w4_weight* w, const float* x, int ld
         if (rc != B2W4_OK)
             return rc;
     }
+    return B2W4_OK;
+}
+
+int b2w4_launch_tp_wait(b2w4_ctx* ctx, unsigned* arrive_local, int world, int rank) {
+    tp_wait_kernel<<<1, 32, 0, ctx->stream>>>(arrive_local, world, rank, ctx->flag_dev + 1);
+    ctx->launches++;
+    B2W4_CUDA(ctx, cudaGetLastError());
     return B2W4_OK;
 }
