@@ -398,48 +398,44 @@ def run_ours(args):
         return g.replay
 
     def make_peer_step(passes=args.passes):
-        """The same walk with the exchange inside the kernel: the GEMV's epilogue stores this
-        rank's rows into every rank's output over peer mappings (symmetric memory) and a
-        bounded wait kernel holds the stream until every rank's rows have landed.  Returns
-        None when symmetric memory is not available."""
+        """The same walk with the exchange inside the kernels: the GEMV's epilogue stores
+        (value, exchange number) words into every rank's staging buffer over peer mappings
+        (symmetric memory) and a small gather kernel waits, bounded, for all of them and
+        unpacks the row.  Returns None when symmetric memory is not available."""
         try:
             import torch.distributed._symmetric_memory as symm
-            y_sym = symm.empty((1, N_OUT), dtype=torch.float32, device=f"cuda:{local}")
-            arrive = symm.empty((64,), dtype=torch.int32, device=f"cuda:{local}")
-            arrive.zero_()
-            y_sym.zero_()
+            stage = symm.empty((2 * N_OUT + 1,), dtype=torch.int64, device=f"cuda:{local}")
+            stage.zero_()
             torch.cuda.synchronize()
-            hy = symm.rendezvous(y_sym, dist.group.WORLD.group_name)
-            ha = symm.rendezvous(arrive, dist.group.WORLD.group_name)
+            hs = symm.rendezvous(stage, dist.group.WORLD.group_name)
         except Exception as exc:  # no peer mappings on this box: the NCCL walk stands
             print(f"in-kernel exchange unavailable: {exc}", file=sys.stderr)
             return None
         group = pkg.capi.TpGroup()
         group.rank, group.world = rank, world
         for p_ in range(world):
-            group.y_peers[p_] = hy.buffer_ptrs[p_]
-            group.arrive_peers[p_] = ha.buffer_ptrs[p_]
+            group.stage_peers[p_] = hs.buffer_ptrs[p_]
         x, y_local, y_full = make_io(1)
+        y_row = torch.zeros((1, N_OUT), dtype=torch.float32, device="cuda")
         dist.barrier()
-        # once, eagerly: the gathered row must equal the NCCL all-gather of the shards, bit for bit
-        ctx.matmul(weights[0], x, y_local)
-        dist.all_gather_into_tensor(y_full, y_local)
-        ctx.matmul_tp(weights[0], x, N_OUT, rank * n_local, group)
-        ctx.tp_wait(group)
-        ctx.sync()
-        torch.cuda.synchronize()
-        want = y_full.permute(1, 0, 2).reshape(1, N_OUT)
-        if not torch.equal(want, y_sym):
-            raise RuntimeError("in-kernel exchange and all-gather disagree")
+        # eagerly, twice (both halves of the staging buffer): the gathered row must equal the
+        # NCCL all-gather of the shards, bit for bit
+        for w in weights[:2]:
+            ctx.matmul(w, x, y_local)
+            dist.all_gather_into_tensor(y_full, y_local)
+            ctx.matmul_tp(w, x, N_OUT, rank * n_local, group)
+            ctx.tp_gather(group, y_row, N_OUT)
+            ctx.sync()
+            torch.cuda.synchronize()
+            if not torch.equal(y_full.permute(1, 0, 2).reshape(1, N_OUT), y_row):
+                raise RuntimeError("in-kernel exchange and all-gather disagree")
         dist.barrier()
-
-        group.wait_previous = 1  # each GEMV first waits for the exchange before it
 
         def eager():
             for _ in range(passes):
                 for w in weights:
                     ctx.matmul_tp(w, x, N_OUT, rank * n_local, group)
-            ctx.tp_wait(group)  # the step ends with every rank's rows here
+                    ctx.tp_gather(group, y_row, N_OUT)
         eager()
         torch.cuda.synchronize()
         dist.barrier()
@@ -450,7 +446,7 @@ def run_ours(args):
             with torch.cuda.graph(g, stream=side):
                 eager()
         ctx.set_stream(torch.cuda.current_stream().cuda_stream)
-        keep = (y_sym, arrive, hy, ha, group)  # peer mappings live as long as the step
+        keep = (stage, hs, group, y_row)  # peer mappings live as long as the step
 
         def replay():
             g.replay()
@@ -487,8 +483,8 @@ def run_ours(args):
             with ClockSampler(local) as clocks:
                 ms = time_steps(torch, peer_step, args.steps, args.warmup, barrier)
             ms = max_over_ranks(ms)
-            exchange = ("in the GEMV kernel: peer stores into every rank's output + arrival "
-                        "counters; each GEMV waits (bounded) for the exchange before it")
+            exchange = ("in the GEMV kernel: flagged 8-byte peer stores into every rank's "
+                        "staging buffer, gather kernel with a bounded wait")
     alg = algorithmic_bytes(N_OUT, K_IN, 1)
     gemvs = COPIES * args.passes
     value = gemvs * alg / (ms * 1e-3) / 1e9
@@ -512,7 +508,7 @@ def run_ours(args):
     if nccl_ms is not None:
         line["nccl_allgather_variant"] = {"value": gemvs * alg / (nccl_ms * 1e-3) / 1e9,
                                           "unit": UNIT, "ms_per_step": nccl_ms}
-        line["gpu_launches"] = (launches_per_step + 1) * args.steps  # + one wait kernel
+        line["gpu_launches"] = 2 * launches_per_step * args.steps  # GEMV + gather kernel
 
     if not args.headline_only:
         # ---- e2e: the same step through the host-buffer entry point (every rank streams its

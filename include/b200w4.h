@@ -178,31 +178,30 @@ int b2w4_moe_combine(b2w4_ctx* ctx, const float* route_out_dev, int tokens, int 
 /* ---- tensor-parallel decode matmul with the exchange inside the kernel -------
  * No counterpart in the reference (one process, one device).  Rank r of `world`
  * holds the rows [n_offset, n_offset + N_shard) of a weight (8-row tiles whole)
- * and every rank needs the full output.  Instead of a matmul followed by an
- * all-gather call, the kernel's epilogue stores its rows straight into every
- * rank's copy of the output through peer mappings (y_peers[p] = rank p's
- * [1][ldc] buffer as mapped into this process, e.g. the buffer_ptrs of a
- * symmetric-memory rendezvous), and the launch's last CTA adds one to this
- * rank's slot of every rank's arrival counters (arrive_peers[p] = rank p's
- * uint32[world], zero before first use).  b2w4_tp_wait enqueues a bounded wait
- * (about 50 ms, then B2W4_E_TIMEOUT through b2w4_sync) until every rank's rows of
- * the latest matmul have landed here; work queued after it may read the output.
- * With wait_previous != 0 the matmul itself does that wait for the previous
- * exchange of the group before it reads x_dev (a chain of tensor-parallel
- * matmuls then needs no kernel between them).  A rank may run one exchange
- * ahead of its peers, so a caller that reuses an output buffer alternates two.
- * One activation row per call; same arithmetic and bits as b2w4_matmul.  Every
- * rank must issue the same sequence of calls. */
+ * and every rank needs the full output row.  Instead of a matmul followed by an
+ * all-gather call, the matmul's epilogue stores each of its values, paired with
+ * the number of the exchange in one 8-byte word, straight into every rank's
+ * staging buffer through peer mappings (stage_peers[p] = rank p's
+ * uint64[2 * ldc + 1] buffer as mapped into this process, e.g. the buffer_ptrs
+ * of a symmetric-memory rendezvous; all zero before first use; the two halves
+ * alternate between exchanges and the last word counts completed exchanges).
+ * b2w4_tp_gather enqueues the other half: it waits until every entry of the
+ * current half carries the exchange number (bounded, about 50 ms, then
+ * B2W4_E_TIMEOUT through b2w4_sync), unpacks the values into the plain row
+ * y_dev[ldc] of this rank, and advances the count.  No fence or flag write
+ * follows the data, so the exchange costs one trip over the link.
+ * Every rank issues the same sequence matmul_tp, tp_gather, matmul_tp, ... with
+ * the same ldc; columns of the row that no rank owns are not supported (the
+ * shards cover [0, ldc)).  One activation row per call; same arithmetic and bits
+ * as b2w4_matmul on the unsharded weight. */
 typedef struct b2w4_tp_group {
     int rank, world;       /* world <= 8 */
-    void* y_peers[8];
-    void* arrive_peers[8];
-    int wait_previous;
+    void* stage_peers[8];
 } b2w4_tp_group;
 int b2w4_matmul_tp(b2w4_ctx* ctx, const b2w4_weight* w_shard, const float* x_dev, int ldc,
                    int n_offset, const b2w4_tp_group* group, int activation, int act_n_begin,
                    int act_n_len);
-int b2w4_tp_wait(b2w4_ctx* ctx, const b2w4_tp_group* group);
+int b2w4_tp_gather(b2w4_ctx* ctx, const b2w4_tp_group* group, float* y_dev, int ldc);
 
 /* Launch counter: how many of this library's kernels have been launched on the
  * context since creation (for benchmark bookkeeping). */

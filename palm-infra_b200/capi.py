@@ -22,7 +22,7 @@ SYMBOLS = [
     "b2w4_matmul_static_scratch",
     "b2w4_debug_group_sums", "b2w4_quantize_activations", "b2w4_moe_forward",
     "b2w4_moe_select_routes", "b2w4_moe_expert_outputs", "b2w4_moe_combine",
-    "b2w4_matmul_tp", "b2w4_tp_wait",
+    "b2w4_matmul_tp", "b2w4_tp_gather",
     "b2w4_kernel_launches",
 ]
 
@@ -30,10 +30,9 @@ _lib = None
 
 
 class TpGroup(C.Structure):
-    """b2w4_tp_group: this rank, the world size, and every rank's output buffer and arrival
-    counters as mapped into this process (peer pointers)."""
-    _fields_ = [("rank", C.c_int), ("world", C.c_int), ("y_peers", C.c_void_p * 8),
-                ("arrive_peers", C.c_void_p * 8), ("wait_previous", C.c_int)]
+    """b2w4_tp_group: this rank, the world size, and every rank's staging buffer
+    (uint64[2 * ldc + 1], zeroed) as mapped into this process (peer pointers)."""
+    _fields_ = [("rank", C.c_int), ("world", C.c_int), ("stage_peers", C.c_void_p * 8)]
 
 
 class B200W4Error(RuntimeError):
@@ -77,7 +76,7 @@ def lib():
                                               vp, f_p]
         L.b2w4_moe_combine.argtypes = [vp, f_p, i, i, i, vp, f_p, f_p, i]
         L.b2w4_matmul_tp.argtypes = [vp, vp, f_p, i, i, C.POINTER(TpGroup), i, i, i]
-        L.b2w4_tp_wait.argtypes = [vp, C.POINTER(TpGroup)]
+        L.b2w4_tp_gather.argtypes = [vp, C.POINTER(TpGroup), f_p, i]
         L.b2w4_kernel_launches.argtypes = [vp]
         L.b2w4_kernel_launches.restype = C.c_uint64
         _lib = L
@@ -201,8 +200,9 @@ class Context:
         self._check(lib().b2w4_matmul_tp(self.handle, w_shard.handle, _dptr(x), ldc, n_offset,
                                          C.byref(group), act, act_begin, act_len))
 
-    def tp_wait(self, group):
-        self._check(lib().b2w4_tp_wait(self.handle, C.byref(group)))
+    def tp_gather(self, group, y, ldc):
+        """Wait for every rank's values of the latest matmul_tp and unpack them into y."""
+        self._check(lib().b2w4_tp_gather(self.handle, C.byref(group), _dptr(y), ldc))
 
     def group_sums(self, w, x, sums, rule=ACT_G128):
         self._check(lib().b2w4_debug_group_sums(self.handle, w.handle, _dptr(x),

@@ -83,18 +83,15 @@ int b2w4_launch_quantize_mma(b2w4_ctx* ctx, const float* x, int lda, int m, int 
 // rank.  world == 0: off.
 constexpr int kTpMaxWorld = 8;
 struct b2w4_tp_args {
-    float* y_peer[kTpMaxWorld];          // rank p's output buffer, as mapped on this GPU
-    unsigned* arrive_peer[kTpMaxWorld];  // rank p's arrival counters [world]
-    unsigned* done;                      // this GPU's CTA counter (last-CTA detection)
-    int world, rank, n_offset;           // n_offset: first output column of this rank's rows
-    int wait_previous;                   // wait for the previous exchange before reading x
+    unsigned long long* stage_peer[kTpMaxWorld];  // rank p's staging buffer, mapped on this GPU
+    int world, rank, n_offset;  // n_offset: first output column of this rank's rows
 };
 
 int b2w4_launch_gemv(b2w4_ctx* ctx, const b2w4_weight* w, const float* x, int lda,
                      float* y, int ldc, int m, int act_rule, int activation,
                      int act_n_begin, int act_n_len, int32_t* sums,
                      const b2w4_tp_args* tp = nullptr);
-int b2w4_launch_tp_wait(b2w4_ctx* ctx, unsigned* arrive_local, int world, int rank);
+int b2w4_launch_tp_gather(b2w4_ctx* ctx, unsigned long long* stage_local, float* y, int ldc);
 // 2..8 activation rows per pass on the int8 tensor instruction (gemv_mma.cu)
 int b2w4_launch_gemv_mma(b2w4_ctx* ctx, const b2w4_weight* w, const float* x, int lda,
                      float* y, int ldc, int m, int act_rule, int activation,

@@ -329,28 +329,25 @@ int b2w4_matmul_tp(b2w4_ctx* ctx, const b2w4_weight* w, const float* x_dev, int 
         return b2w4_fail(ctx, B2W4_E_INVALID, "matmul_tp: unknown activation %d", activation);
     b2w4_tp_args tp = {};
     for (int p = 0; p < group->world; ++p) {
-        if (!group->y_peers[p] || !group->arrive_peers[p])
-            return b2w4_fail(ctx, B2W4_E_INVALID, "matmul_tp: null peer pointer");
-        tp.y_peer[p] = static_cast<float*>(group->y_peers[p]);
-        tp.arrive_peer[p] = static_cast<unsigned*>(group->arrive_peers[p]);
+        if (!group->stage_peers[p] || (reinterpret_cast<uintptr_t>(group->stage_peers[p]) & 7))
+            return b2w4_fail(ctx, B2W4_E_INVALID, "matmul_tp: null or unaligned peer pointer");
+        tp.stage_peer[p] = static_cast<unsigned long long*>(group->stage_peers[p]);
     }
-    tp.done = reinterpret_cast<unsigned*>(ctx->flag_dev + 6);
     tp.world = group->world;
     tp.rank = group->rank;
     tp.n_offset = n_offset;
-    tp.wait_previous = group->wait_previous;
     return b2w4_launch_gemv(ctx, w, x_dev, w->k, nullptr, ldc, 1, B2W4_ACT_G128, activation,
                             act_n_begin, act_n_len, nullptr, &tp);
 }
 
-int b2w4_tp_wait(b2w4_ctx* ctx, const b2w4_tp_group* group) {
+int b2w4_tp_gather(b2w4_ctx* ctx, const b2w4_tp_group* group, float* y_dev, int ldc) {
     if (!ctx)
         return B2W4_E_INVALID;
-    if (!group || group->world < 1 || group->world > kTpMaxWorld || group->rank < 0 ||
-        group->rank >= group->world || !group->arrive_peers[group->rank])
-        return b2w4_fail(ctx, B2W4_E_INVALID, "tp_wait: bad argument");
-    return b2w4_launch_tp_wait(ctx, static_cast<unsigned*>(group->arrive_peers[group->rank]),
-                               group->world, group->rank);
+    if (!group || !y_dev || ldc <= 0 || group->world < 1 || group->world > kTpMaxWorld ||
+        group->rank < 0 || group->rank >= group->world || !group->stage_peers[group->rank])
+        return b2w4_fail(ctx, B2W4_E_INVALID, "tp_gather: bad argument");
+    return b2w4_launch_tp_gather(
+        ctx, static_cast<unsigned long long*>(group->stage_peers[group->rank]), y_dev, ldc);
 }
 
 int b2w4_debug_group_sums(b2w4_ctx* ctx, const b2w4_weight* w, const float* x_dev, int lda,

@@ -46,6 +46,7 @@ constexpr int kMaxTpc = 16;
 constexpr unsigned kSpinLimit = 1u << 22;  // bounded waits: give up, flag, return
 constexpr unsigned long long kWaitLimitCycles = 4000000000ull;  // SM cycles: about 2 s
 constexpr unsigned long long kTpWaitLimitCycles = 100000000ull;  // about 50 ms
+constexpr int kTpGatherThreads = 256;
 
 struct GemvArgs {
     const uint4* nib;
@@ -179,24 +180,12 @@ gemv_w4a8_kernel(const GemvArgs a) {
 
     b2w4_pdl_wait();  // activations come from the previous kernel
 
-    // Tensor-parallel chain: the activations may be the gathered output of the previous
-    // exchange, so every rank's rows of it must have landed here first.  This rank's own
-    // counter is final (its previous kernel has completed); thread r waits, bounded, for
-    // rank r's counter to reach it.
-    if (a.tp.world != 0 && a.tp.wait_previous) {
-        if ((int)threadIdx.x < a.tp.world) {
-            const volatile unsigned* arrive = a.tp.arrive_peer[a.tp.rank];
-            const unsigned target = arrive[a.tp.rank];
-            const unsigned long long t0 = wait_clock();
-            while ((int)(arrive[threadIdx.x] - target) < 0) {
-                if (wait_clock() - t0 > kTpWaitLimitCycles) {
-                    atomicExch(a.status, B2W4_E_TIMEOUT);
-                    break;
-                }
-            }
-        }
-        __syncthreads();
-    }
+    // Tensor-parallel exchange number: one more than the count of completed gathers, kept in
+    // the word behind this rank's staging buffer (written by the gather kernel).
+    unsigned tp_exchange = 0;
+    if (a.tp.world != 0)
+        tp_exchange = *reinterpret_cast<const volatile unsigned*>(
+                          a.tp.stage_peer[a.tp.rank] + 2 * (size_t)a.ldc) + 1u;
 
     // ---- fused activation quantiser: one half-warp per (activation row, group) ----------
     // lane h of the half-warp holds k = 8h .. 8h+7 of the group (a quarter of a 32-block)
@@ -364,45 +353,49 @@ gemv_w4a8_kernel(const GemvArgs a) {
             if (a.tp.world == 0) {
                 a.y[(size_t)mi * a.ldc + n] = acc;
             } else {
-                // the all-gather is this store: every rank's copy of the output, this GPU's
-                // own included, gets the value over peer mappings
-                const size_t at = (size_t)mi * a.ldc + a.tp.n_offset + n;
+                // The all-gather is this store: every rank's staging buffer, this GPU's own
+                // included, gets (value, exchange number) as one 8-byte word over peer
+                // mappings.  The word is written whole, so the reader needs no fence: an
+                // entry that carries the current exchange number carries its value.
+                const unsigned long long word =
+                    ((unsigned long long)tp_exchange << 32) | __float_as_uint(acc);
+                const size_t at = (size_t)(tp_exchange & 1) * a.ldc + a.tp.n_offset + n;
 #pragma unroll
                 for (int p = 0; p < kTpMaxWorld; ++p)
                     if (p < a.tp.world)
-                        a.tp.y_peer[p][at] = acc;
+                        a.tp.stage_peer[p][at] = word;
             }
         }
     }
-    if (a.tp.world == 0)
-        return;
-    // Arrival: after the barrier one thread's system-wide fence covers the whole CTA's peer
-    // stores; the CTA that comes last (nobody waits for it) then tells every rank that this
-    // rank's rows have landed.
-    __syncthreads();
-    if (threadIdx.x != 0)
-        return;
-    __threadfence_system();
-    if (atomicAdd(a.tp.done, 1u) != gridDim.x - 1)
-        return;
-    *a.tp.done = 0;  // ready for the next launch
-    __threadfence_system();
-    for (int p = 0; p < a.tp.world; ++p)
-        atomicAdd_system(a.tp.arrive_peer[p] + a.tp.rank, 1u);
 }
 
-// Waits (bounded) until every rank's rows of the latest tensor-parallel matmul have landed on
-// this GPU: rank r's counter has caught up with this rank's own.  One thread per rank.
-__global__ void tp_wait_kernel(volatile unsigned* arrive, int world, int rank, int* status) {
-    if ((int)threadIdx.x >= world)
-        return;
-    const unsigned target = arrive[rank];
+// Second half of the tensor-parallel exchange: waits (bounded) until every entry of the
+// current exchange's half of the staging buffer carries the exchange number -- written by this
+// GPU's own matmul (complete: this kernel is ordered after it) and by the peers' -- and unpacks
+// the values into the plain output row.  The last block then advances the exchange count.
+__global__ void __launch_bounds__(kTpGatherThreads)
+tp_gather_kernel(unsigned long long* stage, float* y, int ldc, unsigned* done, int* status) {
+    b2w4_pdl_chain_entry();
+    unsigned* count = reinterpret_cast<unsigned*>(stage + 2 * (size_t)ldc);
+    const unsigned exchange = *reinterpret_cast<volatile unsigned*>(count) + 1u;
+    const volatile unsigned long long* src = stage + (size_t)(exchange & 1) * ldc;
     const unsigned long long t0 = wait_clock();
-    while ((int)(arrive[threadIdx.x] - target) < 0) {
-        if (wait_clock() - t0 > kTpWaitLimitCycles) {
-            atomicExch(status, B2W4_E_TIMEOUT);
-            return;
+    bool gave_up = false;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < ldc; i += gridDim.x * blockDim.x) {
+        unsigned long long word = src[i];
+        while ((unsigned)(word >> 32) != exchange && !gave_up) {
+            if (wait_clock() - t0 > kTpWaitLimitCycles) {
+                atomicExch(status, B2W4_E_TIMEOUT);
+                gave_up = true;
+            }
+            word = src[i];
         }
+        y[i] = __uint_as_float((unsigned)word);
+    }
+    __syncthreads();  // every thread of the block has read the count
+    if (threadIdx.x == 0 && atomicAdd(done, 1u) == gridDim.x - 1) {
+        *done = 0;  // ready for the next launch
+        *count = exchange;
     }
 }
 
@@ -535,9 +528,13 @@ int b2w4_launch_gemv(b2w4_ctx* ctx, const b2w4_weight* w, const float* x, int ld
     return B2W4_OK;
 }
 
-int b2w4_launch_tp_wait(b2w4_ctx* ctx, unsigned* arrive_local, int world, int rank) {
-    tp_wait_kernel<<<1, 32, 0, ctx->stream>>>(arrive_local, world, rank, ctx->flag_dev + 1);
+int b2w4_launch_tp_gather(b2w4_ctx* ctx, unsigned long long* stage_local, float* y, int ldc) {
+    const int blocks = max(1, min((ldc + kTpGatherThreads - 1) / kTpGatherThreads,
+                                  ctx->sm_count));
+    B2W4_CUDA(ctx, b2w4_launch_chained(ctx->pdl, tp_gather_kernel, dim3(blocks),
+                                       dim3(kTpGatherThreads), 0, ctx->stream, stage_local, y,
+                                       ldc, reinterpret_cast<unsigned*>(ctx->flag_dev + 6),
+                                       ctx->flag_dev + 1));
     ctx->launches++;
-    B2W4_CUDA(ctx, cudaGetLastError());
     return B2W4_OK;
 }
