@@ -1,0 +1,137 @@
+"""GPU parity of the tensor-parallel one-row matmul whose all-gather is done by the kernels
+(b2w4_matmul_tp + b2w4_tp_gather): the gathered row equals the unsharded b2w4_matmul and the
+CPU oracle bit for bit.  The ranks of a group are emulated on one GPU as contexts that share
+one stream (every matmul of an exchange is queued before the gathers, so no kernel ever waits
+for another); peer pointers are then plain device pointers."""
+import numpy as np
+import pytest
+
+import oracle_lib as ol
+from __graft_entry__ import load_package
+
+pkg = load_package()
+pytestmark = pytest.mark.gpu
+
+
+def _group(rank, world, stages):
+    g = pkg.capi.TpGroup()
+    g.rank, g.world = rank, world
+    for p in range(world):
+        g.stage_peers[p] = stages[p].data_ptr()
+    return g
+
+
+def _ranks(world, n):
+    import torch
+    ctxs = [pkg.capi.Context(0) for _ in range(world)]
+    stream = torch.cuda.current_stream().cuda_stream
+    for c in ctxs:
+        c.set_stream(stream)
+    stages = [torch.zeros(2 * n + 1, dtype=torch.int64, device="cuda") for _ in range(world)]
+    groups = [_group(r, world, stages) for r in range(world)]
+    return ctxs, stages, groups
+
+
+@pytest.mark.parametrize("world,n,k", [(1, 64, 256), (2, 96, 384), (2, 9728, 2560),
+                                        (4, 1024, 1024), (3, 72, 128), (8, 512, 640)])
+def test_gathered_row_equals_unsharded_matmul(world, n, k):
+    import torch
+    blocks = pkg.synth.bg128_weight(11, 1, n, k)
+    ctxs, stages, groups = _ranks(world, n)
+    shards = []
+    for r in range(world):
+        sh, n_local, lo = pkg.shard.shard_blocks(blocks, n, k, r, world)
+        shards.append((ctxs[r].upload_weight(sh, n_local, k), lo))
+    whole = ctxs[0].upload_weight(blocks, n, k)
+    rows = [torch.full((1, n), -3.0, dtype=torch.float32, device="cuda") for _ in range(world)]
+    want = torch.zeros((1, n), dtype=torch.float32, device="cuda")
+    # several exchanges in a row: both halves of the staging buffer, and their reuse
+    for it in range(5):
+        x = pkg.synth.activations(20 + it, 0, 1, k)
+        xd = torch.from_numpy(x).cuda()
+        ctxs[0].matmul(whole, xd, want)
+        for r in range(world):
+            ctxs[r].matmul_tp(shards[r][0], xd, n, shards[r][1], groups[r])
+        for r in range(world):
+            ctxs[r].tp_gather(groups[r], rows[r], n)
+        for c in ctxs:
+            c.sync()
+        ref = ol.matmul_w4(blocks, n, k, x, rule=ol.ACT_G128)
+        for r in range(world):
+            assert torch.equal(rows[r], want), (it, r)
+            assert np.array_equal(rows[r].cpu().numpy().view(np.uint32), ref.view(np.uint32))
+            assert int(stages[r][2 * n].item()) == it + 1  # completed exchanges
+    for c in ctxs:
+        c.close()
+
+
+def test_activation_range_in_the_exchange():
+    import torch
+    world, n, k = 2, 256, 512
+    blocks = pkg.synth.bg128_weight(12, 1, n, k)
+    ctxs, stages, groups = _ranks(world, n)
+    x = pkg.synth.activations(31, 0, 1, k)
+    xd = torch.from_numpy(x).cuda()
+    whole = ctxs[0].upload_weight(blocks, n, k)
+    want = torch.zeros((1, n), dtype=torch.float32, device="cuda")
+    ctxs[0].matmul(whole, xd, want, act=pkg.capi.SILU)
+    rows = [torch.zeros((1, n), dtype=torch.float32, device="cuda") for _ in range(world)]
+    for r in range(world):
+        sh, n_local, lo = pkg.shard.shard_blocks(blocks, n, k, r, world)
+        w = ctxs[r].upload_weight(sh, n_local, k)
+        ctxs[r].matmul_tp(w, xd, n, lo, groups[r], act=pkg.capi.SILU)
+    for r in range(world):
+        ctxs[r].tp_gather(groups[r], rows[r], n)
+        ctxs[r].sync()
+        assert torch.equal(rows[r], want)
+    for c in ctxs:
+        c.close()
+
+
+def test_gather_without_a_peer_times_out_and_context_stays_usable():
+    """A rank whose peer never stores (here: rank 1 of 2 is silent) gets B2W4_E_TIMEOUT from
+    the bounded wait at the next sync, not a hang; the context then works again."""
+    import torch
+    n, k = 64, 256
+    blocks = pkg.synth.bg128_weight(13, 1, n, k)
+    ctxs, stages, groups = _ranks(2, n)
+    sh, n_local, lo = pkg.shard.shard_blocks(blocks, n, k, 0, 2)
+    w = ctxs[0].upload_weight(sh, n_local, k)
+    xd = torch.from_numpy(pkg.synth.activations(5, 0, 1, k)).cuda()
+    row = torch.zeros((1, n), dtype=torch.float32, device="cuda")
+    ctxs[0].matmul_tp(w, xd, n, lo, groups[0])
+    ctxs[0].tp_gather(groups[0], row, n)
+    with pytest.raises(pkg.capi.B200W4Error):
+        ctxs[0].sync()
+    whole = ctxs[0].upload_weight(blocks, n, k)
+    y = torch.zeros((1, n), dtype=torch.float32, device="cuda")
+    ctxs[0].matmul(whole, xd, y)
+    ctxs[0].sync()
+    ref = ol.matmul_w4(blocks, n, k, pkg.synth.activations(5, 0, 1, k), rule=ol.ACT_G128)
+    assert np.array_equal(y.cpu().numpy().view(np.uint32), ref.view(np.uint32))
+    for c in ctxs:
+        c.close()
+
+
+def test_bad_arguments_are_refused():
+    import torch
+    n, k = 64, 256
+    blocks = pkg.synth.bg128_weight(14, 1, n, k)
+    ctxs, stages, groups = _ranks(1, n)
+    ctx = ctxs[0]
+    w = ctx.upload_weight(blocks, n, k)
+    xd = torch.zeros((1, k), dtype=torch.float32, device="cuda")
+    row = torch.zeros((1, n), dtype=torch.float32, device="cuda")
+    with pytest.raises(pkg.capi.B200W4Error):
+        ctx.matmul_tp(w, xd, n - 8, 0, groups[0])  # the row is shorter than the shard
+    bad = _group(0, 1, stages)
+    bad.world = 9
+    with pytest.raises(pkg.capi.B200W4Error):
+        ctx.matmul_tp(w, xd, n, 0, bad)
+    empty = pkg.capi.TpGroup()
+    empty.rank, empty.world = 0, 1
+    with pytest.raises(pkg.capi.B200W4Error):
+        ctx.matmul_tp(w, xd, n, 0, empty)
+    with pytest.raises(pkg.capi.B200W4Error):
+        ctx.tp_gather(empty, row, n)
+    ctx.close()
