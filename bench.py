@@ -277,7 +277,53 @@ def moe_layer_ep(torch, dist, pkg, ctx, rank, world):
         ms = float(tm.item())
         out[f"tokens{t}"] = {"us_per_layer": ms * 1e3,
                              "tokens_per_s_per_layer": t / (ms * 1e-3),
+                             "exchange": "NCCL all-reduce of the route buffer",
                              "exchange_bytes": t * top_k * h * 4}
+    # decode step with the hand-over inside the kernels (peer stores into staging buffers)
+    try:
+        import torch.distributed._symmetric_memory as symm
+        rows = top_k
+        words = pkg.expert_parallel.PeerExchangeMoE.stage_words(rows, h)
+        stage = symm.empty((words,), dtype=torch.int64, device=f"cuda:{torch.cuda.current_device()}")
+        stage.zero_()
+        torch.cuda.synchronize()
+        hs = symm.rendezvous(stage, dist.group.WORLD.group_name)
+    except Exception as exc:
+        print(f"in-kernel MoE hand-over unavailable: {exc}", file=sys.stderr)
+        return out
+    group = pkg.capi.TpGroup()
+    group.rank, group.world = rank, world
+    for p_ in range(world):
+        group.stage_peers[p_] = hs.buffer_ptrs[p_]
+    peer = pkg.expert_parallel.PeerExchangeMoE(op.engine, group, rows)
+    x = torch.from_numpy(pkg.synth.activations(SEED_X, 81, 1, h)).cuda()
+    y = torch.zeros((1, h), dtype=torch.float32, device="cuda")
+    y2 = torch.zeros((1, h), dtype=torch.float32, device="cuda")
+    dist.barrier()
+    for _ in range(3):  # both halves of the staging buffer; bit for bit the all-reduce result
+        op.forward(x, y)
+        peer.forward(x, y2)
+        ctx.sync()
+        torch.cuda.synchronize()
+        if not torch.equal(y, y2):
+            raise RuntimeError("in-kernel MoE hand-over and all-reduce disagree")
+    dist.barrier()
+    g = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        ctx.set_stream(side.cuda_stream)
+        with torch.cuda.graph(g, stream=side):
+            peer.forward(x, y2)
+    ctx.set_stream(torch.cuda.current_stream().cuda_stream)
+    ms = time_steps(torch, g.replay, 20, 3, lambda: dist.barrier())
+    tm = torch.tensor([ms], device="cuda", dtype=torch.float64)
+    dist.all_reduce(tm, op=dist.ReduceOp.MAX)
+    ms = float(tm.item())
+    out["tokens1_peer_exchange"] = {
+        "us_per_layer": ms * 1e3, "tokens_per_s_per_layer": 1 / (ms * 1e-3),
+        "exchange": "in the kernels: tagged 8-byte peer stores into every rank's staging buffer",
+        "exchange_bytes": top_k * h * 8}
+    moe_layer_ep.keep = (stage, hs, group)  # peer mappings outlive the graph replays
     return out
 
 
@@ -404,7 +450,7 @@ def run_ours(args):
         unpacks the row.  Returns None when symmetric memory is not available."""
         try:
             import torch.distributed._symmetric_memory as symm
-            stage = symm.empty((2 * N_OUT + 1,), dtype=torch.int64, device=f"cuda:{local}")
+            stage = symm.empty((2 + 2 * N_OUT,), dtype=torch.int64, device=f"cuda:{local}")
             stage.zero_()
             torch.cuda.synchronize()
             hs = symm.rendezvous(stage, dist.group.WORLD.group_name)

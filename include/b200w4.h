@@ -175,33 +175,49 @@ int b2w4_moe_combine(b2w4_ctx* ctx, const float* route_out_dev, int tokens, int 
                      int top_k, const int32_t* indices_dev, const float* weights_dev,
                      float* out_dev, int ldo);
 
-/* ---- tensor-parallel decode matmul with the exchange inside the kernel -------
- * No counterpart in the reference (one process, one device).  Rank r of `world`
- * holds the rows [n_offset, n_offset + N_shard) of a weight (8-row tiles whole)
- * and every rank needs the full output row.  Instead of a matmul followed by an
- * all-gather call, the matmul's epilogue stores each of its values, paired with
- * the number of the exchange in one 8-byte word, straight into every rank's
- * staging buffer through peer mappings (stage_peers[p] = rank p's
- * uint64[2 * ldc + 1] buffer as mapped into this process, e.g. the buffer_ptrs
- * of a symmetric-memory rendezvous; all zero before first use; the two halves
- * alternate between exchanges and the last word counts completed exchanges).
- * b2w4_tp_gather enqueues the other half: it waits until every entry of the
- * current half carries the exchange number (bounded, about 50 ms, then
- * B2W4_E_TIMEOUT through b2w4_sync), unpacks the values into the plain row
- * y_dev[ldc] of this rank, and advances the count.  No fence or flag write
- * follows the data, so the exchange costs one trip over the link.
- * Every rank issues the same sequence matmul_tp, tp_gather, matmul_tp, ... with
- * the same ldc; columns of the row that no rank owns are not supported (the
- * shards cover [0, ldc)).  One activation row per call; same arithmetic and bits
- * as b2w4_matmul on the unsharded weight. */
+/* ---- exchanges inside the kernels: tensor-parallel matmul, expert-parallel MoE --
+ * No counterpart in the reference (one process, one device).  Instead of a
+ * kernel followed by a collective call, the producing kernel stores each value,
+ * paired with the number of the exchange in one 8-byte word, straight into every
+ * rank's staging buffer through peer mappings, and the consuming kernel takes an
+ * entry once it carries the current exchange number (bounded wait, about 50 ms,
+ * then B2W4_E_TIMEOUT through b2w4_sync).  A word is written whole, so no fence or
+ * flag write follows the data and the exchange costs one trip over the link.
+ * stage_peers[p] = rank p's staging buffer as mapped into this process (e.g. the
+ * buffer_ptrs of a symmetric-memory rendezvous), 16-byte aligned, all zero before
+ * first use: uint64[2 + 2 * half] with word 0 the count of completed exchanges
+ * and two halves that alternate, so that a rank may run one exchange ahead of
+ * its peers.  Every rank issues the same sequence of calls on a group, and a
+ * staging buffer serves one kind of call with one half size. */
 typedef struct b2w4_tp_group {
     int rank, world;       /* world <= 8 */
     void* stage_peers[8];
 } b2w4_tp_group;
+
+/* Tensor-parallel decode matmul with the all-gather inside: rank r holds the rows
+ * [n_offset, n_offset + N_shard) of a weight (8-row tiles whole), the shards cover
+ * [0, ldc), and every rank needs the full row.  b2w4_matmul_tp is b2w4_matmul for
+ * one activation row whose epilogue stores into every rank's staging buffer
+ * (half = ldc); b2w4_tp_gather waits for every entry of the current half,
+ * unpacks the row into y_dev[ldc] and advances the count.  Same arithmetic and
+ * bits as b2w4_matmul on the unsharded weight. */
 int b2w4_matmul_tp(b2w4_ctx* ctx, const b2w4_weight* w_shard, const float* x_dev, int ldc,
                    int n_offset, const b2w4_tp_group* group, int activation, int act_n_begin,
                    int act_n_len);
 int b2w4_tp_gather(b2w4_ctx* ctx, const b2w4_tp_group* group, float* y_dev, int ldc);
+
+/* Expert-parallel MoE with the hand-over inside: b2w4_moe_expert_outputs, the sum
+ * over the ranks and b2w4_moe_combine as one call.  The owner of a route stores
+ * its down-projection row into every rank's staging buffer (half = stage_rows *
+ * H words, stage_rows >= tokens * top_k and the same on every call of the group)
+ * and the combine takes the rows from there.  out equals b2w4_moe_forward's bit
+ * for bit.  Meant for decode steps: it moves 8 bytes per value to every peer. */
+int b2w4_moe_forward_ep(b2w4_ctx* ctx, const float* hidden_dev, int ldx, int tokens,
+                        int hidden_size, const void* router_fp16_dev, int num_experts,
+                        int top_k, int intermediate, const b2w4_weight* gate_up_local,
+                        const b2w4_weight* down_local, int expert_begin, int expert_count,
+                        const b2w4_tp_group* group, int stage_rows, float* out_dev, int ldo,
+                        int32_t* indices_dev, float* weights_dev);
 
 /* Launch counter: how many of this library's kernels have been launched on the
  * context since creation (for benchmark bookkeeping). */

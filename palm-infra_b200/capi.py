@@ -22,7 +22,7 @@ SYMBOLS = [
     "b2w4_matmul_static_scratch",
     "b2w4_debug_group_sums", "b2w4_quantize_activations", "b2w4_moe_forward",
     "b2w4_moe_select_routes", "b2w4_moe_expert_outputs", "b2w4_moe_combine",
-    "b2w4_matmul_tp", "b2w4_tp_gather",
+    "b2w4_matmul_tp", "b2w4_tp_gather", "b2w4_moe_forward_ep",
     "b2w4_kernel_launches",
 ]
 
@@ -31,7 +31,7 @@ _lib = None
 
 class TpGroup(C.Structure):
     """b2w4_tp_group: this rank, the world size, and every rank's staging buffer
-    (uint64[2 * ldc + 1], zeroed) as mapped into this process (peer pointers)."""
+    (uint64[2 + 2 * half], zeroed, 16-byte aligned) as mapped into this process (peer pointers)."""
     _fields_ = [("rank", C.c_int), ("world", C.c_int), ("stage_peers", C.c_void_p * 8)]
 
 
@@ -77,6 +77,8 @@ def lib():
         L.b2w4_moe_combine.argtypes = [vp, f_p, i, i, i, vp, f_p, f_p, i]
         L.b2w4_matmul_tp.argtypes = [vp, vp, f_p, i, i, C.POINTER(TpGroup), i, i, i]
         L.b2w4_tp_gather.argtypes = [vp, C.POINTER(TpGroup), f_p, i]
+        L.b2w4_moe_forward_ep.argtypes = [vp, f_p, i, i, i, vp, i, i, i, vp, vp, i, i,
+                                          C.POINTER(TpGroup), i, f_p, i, vp, f_p]
         L.b2w4_kernel_launches.argtypes = [vp]
         L.b2w4_kernel_launches.restype = C.c_uint64
         _lib = L
@@ -232,6 +234,20 @@ class Context:
             self.handle, _dptr(hidden), hidden.stride(0), t, h, _dptr(router_fp16), e, top_k,
             intermediate, gate_up_local.handle, down_local.handle, expert_begin, expert_count,
             _dptr(route_out), _dptr(indices), _dptr(weights)))
+
+    def moe_forward_ep(self, hidden, router_fp16, top_k, intermediate, gate_up_local, down_local,
+                       expert_begin, expert_count, group, stage_rows, out, indices=None,
+                       weights=None):
+        """The expert-parallel MoE op as one call: route rows go to every rank's staging
+        buffer over peer mappings and the combine reads them there."""
+        t, h = hidden.shape
+        e = router_fp16.shape[0]
+        self._check(lib().b2w4_moe_forward_ep(
+            self.handle, _dptr(hidden), hidden.stride(0), t, h, _dptr(router_fp16), e, top_k,
+            intermediate, gate_up_local.handle, down_local.handle, expert_begin, expert_count,
+            C.byref(group), stage_rows, _dptr(out), out.stride(0),
+            _dptr(indices) if indices is not None else None,
+            _dptr(weights) if weights is not None else None))
 
     def moe_combine(self, route_out, top_k, indices, weights, out):
         t, h = out.shape

@@ -82,6 +82,11 @@ int b2w4_launch_quantize_mma(b2w4_ctx* ctx, const float* x, int lda, int m, int 
 // copy of the output and the launch's last CTA bumps this rank's arrival counter on every
 // rank.  world == 0: off.
 constexpr int kTpMaxWorld = 8;
+// Staging buffer of a peer exchange (uint64 words): word 0 counts completed exchanges, word 1
+// is unused, then two halves that alternate between exchanges.  Every data word is
+// (exchange number << 32 | fp32 bits), written whole, so a reader needs no fence.
+constexpr int kTpStageHeader = 2;
+constexpr unsigned long long kTpWaitLimitCycles = 100000000ull;  // about 50 ms
 struct b2w4_tp_args {
     unsigned long long* stage_peer[kTpMaxWorld];  // rank p's staging buffer, mapped on this GPU
     int world, rank, n_offset;  // n_offset: first output column of this rank's rows

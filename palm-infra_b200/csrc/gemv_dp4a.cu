@@ -45,7 +45,6 @@ __host__ __device__ constexpr int gemv_warps(int mt) { return mt == 1 ? 16 : 8; 
 constexpr int kMaxTpc = 16;
 constexpr unsigned kSpinLimit = 1u << 22;  // bounded waits: give up, flag, return
 constexpr unsigned long long kWaitLimitCycles = 4000000000ull;  // SM cycles: about 2 s
-constexpr unsigned long long kTpWaitLimitCycles = 100000000ull;  // about 50 ms
 constexpr int kTpGatherThreads = 256;
 
 struct GemvArgs {
@@ -181,11 +180,11 @@ gemv_w4a8_kernel(const GemvArgs a) {
     b2w4_pdl_wait();  // activations come from the previous kernel
 
     // Tensor-parallel exchange number: one more than the count of completed gathers, kept in
-    // the word behind this rank's staging buffer (written by the gather kernel).
+    // the first word of this rank's staging buffer (written by the gather kernel).
     unsigned tp_exchange = 0;
     if (a.tp.world != 0)
-        tp_exchange = *reinterpret_cast<const volatile unsigned*>(
-                          a.tp.stage_peer[a.tp.rank] + 2 * (size_t)a.ldc) + 1u;
+        tp_exchange =
+            *reinterpret_cast<const volatile unsigned*>(a.tp.stage_peer[a.tp.rank]) + 1u;
 
     // ---- fused activation quantiser: one half-warp per (activation row, group) ----------
     // lane h of the half-warp holds k = 8h .. 8h+7 of the group (a quarter of a 32-block)
@@ -359,7 +358,8 @@ gemv_w4a8_kernel(const GemvArgs a) {
                 // entry that carries the current exchange number carries its value.
                 const unsigned long long word =
                     ((unsigned long long)tp_exchange << 32) | __float_as_uint(acc);
-                const size_t at = (size_t)(tp_exchange & 1) * a.ldc + a.tp.n_offset + n;
+                const size_t at = kTpStageHeader + (size_t)(tp_exchange & 1) * a.ldc +
+                                  a.tp.n_offset + n;
 #pragma unroll
                 for (int p = 0; p < kTpMaxWorld; ++p)
                     if (p < a.tp.world)
@@ -376,9 +376,10 @@ gemv_w4a8_kernel(const GemvArgs a) {
 __global__ void __launch_bounds__(kTpGatherThreads)
 tp_gather_kernel(unsigned long long* stage, float* y, int ldc, unsigned* done, int* status) {
     b2w4_pdl_chain_entry();
-    unsigned* count = reinterpret_cast<unsigned*>(stage + 2 * (size_t)ldc);
+    unsigned* count = reinterpret_cast<unsigned*>(stage);
     const unsigned exchange = *reinterpret_cast<volatile unsigned*>(count) + 1u;
-    const volatile unsigned long long* src = stage + (size_t)(exchange & 1) * ldc;
+    const volatile unsigned long long* src =
+        stage + kTpStageHeader + (size_t)(exchange & 1) * ldc;
     const unsigned long long t0 = wait_clock();
     bool gave_up = false;
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < ldc; i += gridDim.x * blockDim.x) {

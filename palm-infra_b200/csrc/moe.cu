@@ -621,6 +621,106 @@ __global__ void moe_scatter_routes_kernel(const float* __restrict__ dn,
     *reinterpret_cast<float4*>(route_out + (size_t)r * hidden_size + d) = v;
 }
 
+// ---- expert-parallel hand-over inside the kernels ---------------------------------------
+// Instead of a zero-padded buffer summed by an all-reduce call, the owner of a route stores its
+// output row into every rank's staging buffer over peer mappings, each value paired with the
+// exchange number in one 8-byte word (the same protocol as the tensor-parallel matmul's
+// all-gather); rows of other ranks' experts are left to their owners.
+__global__ void moe_scatter_routes_peers_kernel(const float* __restrict__ dn,
+                                                const int32_t* __restrict__ idx,
+                                                const int32_t* __restrict__ pos, int routes,
+                                                int hidden_size, int expert_begin,
+                                                int expert_count, int stage_rows,
+                                                const b2w4_tp_args peers) {
+    b2w4_pdl_chain_entry();
+    const int r = blockIdx.y;
+    const int d = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (r >= routes || d >= hidden_size)
+        return;
+    const int e = idx[r] - expert_begin;
+    if (e < 0 || e >= expert_count)
+        return;
+    const unsigned exchange =
+        *reinterpret_cast<const volatile unsigned*>(peers.stage_peer[peers.rank]) + 1u;
+    const float4 v = *reinterpret_cast<const float4*>(dn + (size_t)pos[r] * hidden_size + d);
+    const unsigned long long tag = (unsigned long long)exchange << 32;
+    const ulonglong2 w01 = make_ulonglong2(tag | __float_as_uint(v.x), tag | __float_as_uint(v.y));
+    const ulonglong2 w23 = make_ulonglong2(tag | __float_as_uint(v.z), tag | __float_as_uint(v.w));
+    const size_t at = kTpStageHeader + (size_t)(exchange & 1) * stage_rows * hidden_size +
+                      (size_t)r * hidden_size + d;
+#pragma unroll
+    for (int p = 0; p < kTpMaxWorld; ++p)
+        if (p < peers.world) {
+            ulonglong2* dst = reinterpret_cast<ulonglong2*>(peers.stage_peer[p] + at);
+            dst[0] = w01;
+            dst[1] = w23;
+        }
+}
+
+// Combine over the staging buffer: as moe_combine_kernel, but every value is taken from the
+// current exchange's half once it carries the exchange number (bounded wait).  The last block
+// advances the count of completed exchanges.
+__global__ void __launch_bounds__(kCombineThreads)
+moe_combine_staged_kernel(unsigned long long* stage, int stage_rows,
+                          const int32_t* __restrict__ idx, const float* __restrict__ weights,
+                          int tokens, int top_k, int hidden_size, float* __restrict__ out, int ldo,
+                          unsigned* done, int* status) {
+    b2w4_pdl_chain_entry();
+    __shared__ int s_row[kMaxTopK];
+    __shared__ float s_w[kMaxTopK];
+    const int t = blockIdx.y;
+    unsigned* count = reinterpret_cast<unsigned*>(stage);
+    const unsigned exchange = *reinterpret_cast<volatile unsigned*>(count) + 1u;
+    if (threadIdx.x < top_k) {
+        const int j = threadIdx.x;
+        const int key = idx[(size_t)t * top_k + j];
+        const float w = weights[(size_t)t * top_k + j];
+        int rank = 0;
+        for (int o = 0; o < top_k; ++o) {
+            const int other = idx[(size_t)t * top_k + o];
+            rank += other < key || (other == key && o < j);
+        }
+        s_row[rank] = t * top_k + j;
+        s_w[rank] = w;
+    }
+    __syncthreads();
+    const int d = (blockIdx.x * kCombineThreads + threadIdx.x) * 4;
+    if (d < hidden_size) {
+        const unsigned long long* half =
+            stage + kTpStageHeader + (size_t)(exchange & 1) * stage_rows * hidden_size;
+        const long long t0 = clock64();
+        bool gave_up = false;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int j = 0; j < top_k; ++j) {
+            const volatile unsigned long long* src = half + (size_t)s_row[j] * hidden_size + d;
+            unsigned long long w0, w1, w2, w3;
+            for (;;) {
+                w0 = src[0], w1 = src[1], w2 = src[2], w3 = src[3];
+                if (((unsigned)(w0 >> 32) == exchange && (unsigned)(w1 >> 32) == exchange &&
+                     (unsigned)(w2 >> 32) == exchange && (unsigned)(w3 >> 32) == exchange) ||
+                    gave_up)
+                    break;
+                if ((unsigned long long)(clock64() - t0) > kTpWaitLimitCycles) {
+                    atomicExch(status, B2W4_E_TIMEOUT);
+                    gave_up = true;
+                }
+            }
+            const float w = s_w[j];
+            acc.x = __fmaf_rn(w, __uint_as_float((unsigned)w0), acc.x);
+            acc.y = __fmaf_rn(w, __uint_as_float((unsigned)w1), acc.y);
+            acc.z = __fmaf_rn(w, __uint_as_float((unsigned)w2), acc.z);
+            acc.w = __fmaf_rn(w, __uint_as_float((unsigned)w3), acc.w);
+        }
+        float* o = out + (size_t)t * ldo + d;
+        o[0] = acc.x, o[1] = acc.y, o[2] = acc.z, o[3] = acc.w;
+    }
+    __syncthreads();  // every thread of the block has read the count
+    if (threadIdx.x == 0 && atomicAdd(done, 1u) == gridDim.x * gridDim.y - 1) {
+        *done = 0;  // ready for the next launch
+        *count = exchange;
+    }
+}
+
 // ---- 5 / 7 (few tokens). grouped expert matmul, decode variant -------------------------
 // Used for up to kFusedSwigluTokens tokens, where an expert has one or two routes: items
 // (tile pair, group) are spread over all warps, the integer sums go through shared memory and
@@ -1213,7 +1313,8 @@ static int moe_run(b2w4_ctx* ctx, const float* hidden_dev, int ldx, int tokens, 
                    const void* router_fp16_dev, int num_experts, int top_k, int intermediate,
                    const b2w4_weight* gate_up, const b2w4_weight* down, int expert_begin,
                    int expert_count, float* out_dev, int ldo, float* route_out,
-                   float* logits_dev, int32_t* indices_dev, float* weights_dev) {
+                   float* logits_dev, int32_t* indices_dev, float* weights_dev,
+                   const b2w4_tp_args* peers = nullptr, int stage_rows = 0) {
     if (!ctx)
         return B2W4_E_INVALID;
     if (!hidden_dev || !router_fp16_dev || !gate_up || !down || (!out_dev && !route_out))
@@ -1353,7 +1454,21 @@ static int moe_run(b2w4_ctx* ctx, const float* hidden_dev, int ldx, int tokens, 
                                            hidden_size, expert_begin, expert_count, route_out));
         ctx->launches++;
     }
-    if (out_dev) {
+    if (peers) {
+        dim3 sgrid((hidden_size / 4 + 255) / 256, routes);
+        B2W4_CUDA(ctx, b2w4_launch_chained(ctx->pdl, moe_scatter_routes_peers_kernel, sgrid,
+                                           dim3(256), 0, st, static_cast<const float*>(dn), idx,
+                                           pos, routes, hidden_size, expert_begin, expert_count,
+                                           stage_rows, *peers));
+        dim3 cgrid((hidden_size / 4 + kCombineThreads - 1) / kCombineThreads, tokens);
+        B2W4_CUDA(ctx, b2w4_launch_chained(ctx->pdl, moe_combine_staged_kernel, cgrid,
+                                           dim3(kCombineThreads), 0, st,
+                                           peers->stage_peer[peers->rank], stage_rows, idx, wts,
+                                           tokens, top_k, hidden_size, out_dev, ldo,
+                                           reinterpret_cast<unsigned*>(ctx->flag_dev + 6),
+                                           ctx->flag_dev + 1));
+        ctx->launches += 2;
+    } else if (out_dev) {
         dim3 grid((hidden_size / 4 + kCombineThreads - 1) / kCombineThreads, tokens);
         B2W4_CUDA(ctx, b2w4_launch_chained(ctx->pdl, moe_combine_kernel, grid,
                                            dim3(kCombineThreads), 0, st,
@@ -1399,6 +1514,33 @@ int b2w4_moe_expert_outputs(b2w4_ctx* ctx, const float* hidden_dev, int ldx, int
     return moe_run(ctx, hidden_dev, ldx, tokens, hidden_size, router_fp16_dev, num_experts,
                    top_k, intermediate, gate_up_local, down_local, expert_begin, expert_count,
                    nullptr, 0, route_out_dev, nullptr, indices_dev, weights_dev);
+}
+
+int b2w4_moe_forward_ep(b2w4_ctx* ctx, const float* hidden_dev, int ldx, int tokens,
+                        int hidden_size, const void* router_fp16_dev, int num_experts, int top_k,
+                        int intermediate, const b2w4_weight* gate_up_local,
+                        const b2w4_weight* down_local, int expert_begin, int expert_count,
+                        const b2w4_tp_group* group, int stage_rows, float* out_dev, int ldo,
+                        int32_t* indices_dev, float* weights_dev) {
+    if (!ctx)
+        return B2W4_E_INVALID;
+    if (!out_dev || !group || group->world < 1 || group->world > kTpMaxWorld ||
+        group->rank < 0 || group->rank >= group->world || tokens <= 0 || top_k <= 0 ||
+        stage_rows < tokens * top_k)
+        return b2w4_fail(ctx, B2W4_E_INVALID,
+                         "moe_forward_ep: bad group, or fewer staging rows than routes");
+    b2w4_tp_args peers = {};
+    for (int p = 0; p < group->world; ++p) {
+        if (!group->stage_peers[p] || (reinterpret_cast<uintptr_t>(group->stage_peers[p]) & 15))
+            return b2w4_fail(ctx, B2W4_E_INVALID,
+                             "moe_forward_ep: null peer pointer, or not 16-byte aligned");
+        peers.stage_peer[p] = static_cast<unsigned long long*>(group->stage_peers[p]);
+    }
+    peers.world = group->world;
+    peers.rank = group->rank;
+    return moe_run(ctx, hidden_dev, ldx, tokens, hidden_size, router_fp16_dev, num_experts,
+                   top_k, intermediate, gate_up_local, down_local, expert_begin, expert_count,
+                   out_dev, ldo, nullptr, nullptr, indices_dev, weights_dev, &peers, stage_rows);
 }
 
 int b2w4_moe_combine(b2w4_ctx* ctx, const float* route_out_dev, int tokens, int hidden_size,

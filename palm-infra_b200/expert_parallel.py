@@ -91,3 +91,28 @@ def build_device_moe(ctx, router_fp16, gate_up_blocks, down_blocks, num_experts,
     down = ctx.upload_weight(np.ascontiguousarray(dn), cnt * hidden_size, intermediate)
     engine = DeviceEngine(ctx, router_fp16, gate_up, down, top_k, intermediate, lo, cnt)
     return ExpertParallelMoE(engine, all_reduce)
+
+
+class PeerExchangeMoE:
+    """forward(hidden, out) with the hand-over inside the kernels (b2w4_moe_forward_ep): the
+    owner of a route stores its row, each value tagged with the exchange number, into every
+    rank's staging buffer over peer mappings and the combine reads the rows there -- no
+    collective call.  Moves 8 bytes per value to every peer, so it is the decode-step variant;
+    `stage_rows` (>= tokens*top_k of the largest step) fixes the staging layout for the life
+    of the group.  Same bits as ExpertParallelMoE and the single-device op."""
+
+    def __init__(self, engine, group, stage_rows):
+        self.engine, self.group, self.stage_rows = engine, group, stage_rows
+
+    @staticmethod
+    def stage_words(stage_rows, hidden_size):
+        """uint64 words a rank's staging buffer needs (zeroed, 16-byte aligned)."""
+        return 2 + 2 * stage_rows * hidden_size
+
+    def forward(self, hidden, out):
+        e = self.engine
+        if hidden.shape[0] * e.top_k > self.stage_rows:
+            raise ValueError("more routes than staging rows")
+        e.ctx.moe_forward_ep(hidden, e.router, e.top_k, e.intermediate, e.gate_up, e.down,
+                             e.expert_begin, e.expert_count, self.group, self.stage_rows, out)
+        return out

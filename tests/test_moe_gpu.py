@@ -214,3 +214,77 @@ def test_expert_parallel_bad_range_is_error(ctx):
     ctx.sync()
     gu.free()
     dn.free()
+
+
+def _peer_group(rank, world, stages):
+    g = pkg.capi.TpGroup()
+    g.rank, g.world = rank, world
+    for p in range(world):
+        g.stage_peers[p] = stages[p].data_ptr()
+    return g
+
+
+@pytest.mark.parametrize("t,h,e,top_k,inter", [(1, 256, 8, 2, 128), (3, 128, 16, 4, 256),
+                                                 (1, 2048, 128, 8, 768)])
+def test_hand_over_inside_the_kernels_one_rank(ctx, t, h, e, top_k, inter):
+    """b2w4_moe_forward_ep with a group of one (this rank owns every expert): the staged
+    scatter + combine give b2w4_moe_forward's output bit for bit, over both halves of the
+    staging buffer and their reuse.  (More ranks need more GPUs: one call both stores and
+    waits, so ranks cannot be queued one after another on one device.)"""
+    import torch
+    ep = pkg.expert_parallel
+    hidden = pkg.synth.activations(7, 500 + t, t, h)
+    router = pkg.synth.router_weight(20261125, 60 + e, e, h, std=0.3)
+    gu = pkg.synth.bg128_weight(20261125, 500 + e, e * 2 * inter, h)
+    dn = pkg.synth.bg128_weight(20261125, 600 + e, e * h, inter)
+    want = run_moe(ctx, hidden, router, top_k, inter, gu, dn)
+    rows = t * top_k + 3  # more staging rows than routes is allowed
+    stage = torch.zeros(ep.PeerExchangeMoE.stage_words(rows, h), dtype=torch.int64, device="cuda")
+    group = _peer_group(0, 1, [stage])
+    wg = ctx.upload_weight(gu, e * 2 * inter, h)
+    wd = ctx.upload_weight(dn, e * h, inter)
+    xd = torch.from_numpy(hidden).cuda()
+    rd = torch.from_numpy(router.view(np.int16)).cuda()
+    op = ep.PeerExchangeMoE(ep.DeviceEngine(ctx, rd, wg, wd, top_k, inter, 0, e), group, rows)
+    for it in range(4):
+        out = torch.full((t, h), 9.0, dtype=torch.float32, device="cuda")
+        op.forward(xd, out)
+        ctx.sync()
+        assert out.cpu().numpy().tobytes() == want[0].tobytes(), it
+        assert int(stage[0].item()) == it + 1
+    with pytest.raises(ValueError):
+        ep.PeerExchangeMoE(op.engine, group, t * top_k - 1).forward(xd, out)
+    with pytest.raises(pkg.capi.B200W4Error):
+        ctx.moe_forward_ep(xd, rd, top_k, inter, wg, wd, 0, e, group, t * top_k - 1, out)
+    wg.free()
+    wd.free()
+
+
+def test_hand_over_with_a_silent_peer_times_out(ctx):
+    """Rank 0 of 2 holds half the experts and its peer never stores: the combine's bounded
+    wait runs out, the next sync reports the error, and the context works afterwards."""
+    import torch
+    ep = pkg.expert_parallel
+    t, h, e, top_k, inter = 2, 128, 8, 4, 128
+    hidden = pkg.synth.activations(7, 700, t, h)
+    router = pkg.synth.router_weight(20261125, 70, e, h, std=0.3)
+    gu = pkg.synth.bg128_weight(20261125, 700, e * 2 * inter, h)
+    dn = pkg.synth.bg128_weight(20261125, 701, e * h, inter)
+    gu_l, lo, cnt = ep.shard_expert_blocks(gu, e, 2 * inter, h, 0, 2)
+    dn_l, _, _ = ep.shard_expert_blocks(dn, e, h, inter, 0, 2)
+    wg = ctx.upload_weight(np.ascontiguousarray(gu_l), cnt * 2 * inter, h)
+    wd = ctx.upload_weight(np.ascontiguousarray(dn_l), cnt * h, inter)
+    rows = t * top_k
+    stages = [torch.zeros(ep.PeerExchangeMoE.stage_words(rows, h), dtype=torch.int64,
+                          device="cuda") for _ in range(2)]
+    xd = torch.from_numpy(hidden).cuda()
+    rd = torch.from_numpy(router.view(np.int16)).cuda()
+    out = torch.zeros((t, h), dtype=torch.float32, device="cuda")
+    ctx.moe_forward_ep(xd, rd, top_k, inter, wg, wd, lo, cnt, _peer_group(0, 2, stages), rows,
+                       out)
+    with pytest.raises(pkg.capi.B200W4Error):
+        ctx.sync()
+    wg.free()
+    wd.free()
+    want = run_moe(ctx, hidden, router, top_k, inter, gu, dn)  # the context still works
+    assert np.isfinite(want[0]).all()
