@@ -196,15 +196,16 @@ typedef struct b2w4_tp_group {
 
 /* Tensor-parallel decode matmul with the all-gather inside: rank r holds the rows
  * [n_offset, n_offset + N_shard) of a weight (8-row tiles whole), the shards cover
- * [0, ldc), and every rank needs the full row.  b2w4_matmul_tp is b2w4_matmul for
- * one activation row whose epilogue stores into every rank's staging buffer
- * (half = ldc); b2w4_tp_gather waits for every entry of the current half,
- * unpacks the row into y_dev[ldc] and advances the count.  Same arithmetic and
- * bits as b2w4_matmul on the unsharded weight. */
-int b2w4_matmul_tp(b2w4_ctx* ctx, const b2w4_weight* w_shard, const float* x_dev, int ldc,
-                   int n_offset, const b2w4_tp_group* group, int activation, int act_n_begin,
-                   int act_n_len);
-int b2w4_tp_gather(b2w4_ctx* ctx, const b2w4_tp_group* group, float* y_dev, int ldc);
+ * [0, ldc), and every rank needs the full rows.  b2w4_matmul_tp is b2w4_matmul
+ * (per-128 activation rule) for m <= 8 activation rows x_dev [m][lda] whose
+ * epilogue stores into every rank's staging buffer (half = 8 * ldc whatever m
+ * is); b2w4_tp_gather, with the same m, waits for every entry of the current
+ * half, unpacks the rows into y_dev [m][ldc] and advances the count.  Same
+ * arithmetic and bits as b2w4_matmul on the unsharded weight. */
+int b2w4_matmul_tp(b2w4_ctx* ctx, const b2w4_weight* w_shard, const float* x_dev, int lda,
+                   int m, int ldc, int n_offset, const b2w4_tp_group* group, int activation,
+                   int act_n_begin, int act_n_len);
+int b2w4_tp_gather(b2w4_ctx* ctx, const b2w4_tp_group* group, float* y_dev, int m, int ldc);
 
 /* Expert-parallel MoE with the hand-over inside: b2w4_moe_expert_outputs, the sum
  * over the ranks and b2w4_moe_combine as one call.  The owner of a route stores

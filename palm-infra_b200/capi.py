@@ -31,7 +31,7 @@ _lib = None
 
 class TpGroup(C.Structure):
     """b2w4_tp_group: this rank, the world size, and every rank's staging buffer
-    (uint64[2 + 2 * half], zeroed, 16-byte aligned) as mapped into this process (peer pointers)."""
+    (uint64[2 + 2 * half], zeroed, 16-byte aligned; half = 8 * ldc for matmul_tp) as mapped into this process (peer pointers)."""
     _fields_ = [("rank", C.c_int), ("world", C.c_int), ("stage_peers", C.c_void_p * 8)]
 
 
@@ -75,8 +75,8 @@ def lib():
         L.b2w4_moe_expert_outputs.argtypes = [vp, f_p, i, i, i, vp, i, i, i, vp, vp, i, i, f_p,
                                               vp, f_p]
         L.b2w4_moe_combine.argtypes = [vp, f_p, i, i, i, vp, f_p, f_p, i]
-        L.b2w4_matmul_tp.argtypes = [vp, vp, f_p, i, i, C.POINTER(TpGroup), i, i, i]
-        L.b2w4_tp_gather.argtypes = [vp, C.POINTER(TpGroup), f_p, i]
+        L.b2w4_matmul_tp.argtypes = [vp, vp, f_p, i, i, i, i, C.POINTER(TpGroup), i, i, i]
+        L.b2w4_tp_gather.argtypes = [vp, C.POINTER(TpGroup), f_p, i, i]
         L.b2w4_moe_forward_ep.argtypes = [vp, f_p, i, i, i, vp, i, i, i, vp, vp, i, i,
                                           C.POINTER(TpGroup), i, f_p, i, vp, f_p]
         L.b2w4_kernel_launches.argtypes = [vp]
@@ -198,13 +198,16 @@ class Context:
         return call
 
     def matmul_tp(self, w_shard, x, ldc, n_offset, group, act=NONE, act_begin=0, act_len=-1):
-        """One-row matmul whose epilogue stores this rank's rows into every rank's output."""
-        self._check(lib().b2w4_matmul_tp(self.handle, w_shard.handle, _dptr(x), ldc, n_offset,
-                                         C.byref(group), act, act_begin, act_len))
+        """Matmul of up to 8 rows x [m, K] whose epilogue stores this rank's output columns
+        into every rank's staging buffer."""
+        self._check(lib().b2w4_matmul_tp(self.handle, w_shard.handle, _dptr(x), x.stride(0),
+                                         x.shape[0], ldc, n_offset, C.byref(group), act,
+                                         act_begin, act_len))
 
     def tp_gather(self, group, y, ldc):
         """Wait for every rank's values of the latest matmul_tp and unpack them into y."""
-        self._check(lib().b2w4_tp_gather(self.handle, C.byref(group), _dptr(y), ldc))
+        self._check(lib().b2w4_tp_gather(self.handle, C.byref(group), _dptr(y), y.shape[0],
+                                         ldc))
 
     def group_sums(self, w, x, sums, rule=ACT_G128):
         self._check(lib().b2w4_debug_group_sums(self.handle, w.handle, _dptr(x),

@@ -86,6 +86,7 @@ constexpr int kTpMaxWorld = 8;
 // is unused, then two halves that alternate between exchanges.  Every data word is
 // (exchange number << 32 | fp32 bits), written whole, so a reader needs no fence.
 constexpr int kTpStageHeader = 2;
+constexpr int kTpMaxRows = 8;  // activation rows per tensor-parallel matmul; half = 8 * ldc words
 constexpr unsigned long long kTpWaitLimitCycles = 100000000ull;  // about 50 ms
 struct b2w4_tp_args {
     unsigned long long* stage_peer[kTpMaxWorld];  // rank p's staging buffer, mapped on this GPU
@@ -96,11 +97,13 @@ int b2w4_launch_gemv(b2w4_ctx* ctx, const b2w4_weight* w, const float* x, int ld
                      float* y, int ldc, int m, int act_rule, int activation,
                      int act_n_begin, int act_n_len, int32_t* sums,
                      const b2w4_tp_args* tp = nullptr);
-int b2w4_launch_tp_gather(b2w4_ctx* ctx, unsigned long long* stage_local, float* y, int ldc);
+int b2w4_launch_tp_gather(b2w4_ctx* ctx, unsigned long long* stage_local, float* y, int m,
+                          int ldc);
 // 2..8 activation rows per pass on the int8 tensor instruction (gemv_mma.cu)
 int b2w4_launch_gemv_mma(b2w4_ctx* ctx, const b2w4_weight* w, const float* x, int lda,
                      float* y, int ldc, int m, int act_rule, int activation,
-                     int act_n_begin, int act_n_len, int32_t* sums);
+                     int act_n_begin, int act_n_len, int32_t* sums,
+                     const b2w4_tp_args* tp = nullptr);
 
 int b2w4_launch_quantize_umma(b2w4_ctx* ctx, const float* x, int lda, int m, int k, int m_pad,
                               int8_t* q, float* scales);

@@ -316,14 +316,14 @@ int b2w4_matmul_host(b2w4_ctx* ctx, const b2w4_weight* w, const float* x_host, i
     return B2W4_OK;
 }
 
-int b2w4_matmul_tp(b2w4_ctx* ctx, const b2w4_weight* w, const float* x_dev, int ldc,
-                   int n_offset, const b2w4_tp_group* group, int activation, int act_n_begin,
-                   int act_n_len) {
+int b2w4_matmul_tp(b2w4_ctx* ctx, const b2w4_weight* w, const float* x_dev, int lda, int m,
+                   int ldc, int n_offset, const b2w4_tp_group* group, int activation,
+                   int act_n_begin, int act_n_len) {
     if (!ctx)
         return B2W4_E_INVALID;
     if (!w || !x_dev || !group || group->world < 1 || group->world > kTpMaxWorld ||
         group->rank < 0 || group->rank >= group->world || n_offset < 0 ||
-        ldc < n_offset + w->n)
+        ldc < n_offset + w->n || m < 1 || m > kTpMaxRows || lda < w->k)
         return b2w4_fail(ctx, B2W4_E_INVALID, "matmul_tp: bad argument");
     if (activation < B2W4_NONE || activation > B2W4_RELU_SQUARED)
         return b2w4_fail(ctx, B2W4_E_INVALID, "matmul_tp: unknown activation %d", activation);
@@ -336,18 +336,18 @@ int b2w4_matmul_tp(b2w4_ctx* ctx, const b2w4_weight* w, const float* x_dev, int 
     tp.world = group->world;
     tp.rank = group->rank;
     tp.n_offset = n_offset;
-    return b2w4_launch_gemv(ctx, w, x_dev, w->k, nullptr, ldc, 1, B2W4_ACT_G128, activation,
+    return b2w4_launch_gemv(ctx, w, x_dev, lda, nullptr, ldc, m, B2W4_ACT_G128, activation,
                             act_n_begin, act_n_len, nullptr, &tp);
 }
 
-int b2w4_tp_gather(b2w4_ctx* ctx, const b2w4_tp_group* group, float* y_dev, int ldc) {
+int b2w4_tp_gather(b2w4_ctx* ctx, const b2w4_tp_group* group, float* y_dev, int m, int ldc) {
     if (!ctx)
         return B2W4_E_INVALID;
-    if (!group || !y_dev || ldc <= 0 || group->world < 1 || group->world > kTpMaxWorld ||
+    if (!group || !y_dev || ldc <= 0 || m < 1 || m > kTpMaxRows || group->world < 1 || group->world > kTpMaxWorld ||
         group->rank < 0 || group->rank >= group->world || !group->stage_peers[group->rank])
         return b2w4_fail(ctx, B2W4_E_INVALID, "tp_gather: bad argument");
     return b2w4_launch_tp_gather(
-        ctx, static_cast<unsigned long long*>(group->stage_peers[group->rank]), y_dev, ldc);
+        ctx, static_cast<unsigned long long*>(group->stage_peers[group->rank]), y_dev, m, ldc);
 }
 
 int b2w4_debug_group_sums(b2w4_ctx* ctx, const b2w4_weight* w, const float* x_dev, int lda,

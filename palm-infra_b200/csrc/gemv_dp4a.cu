@@ -358,8 +358,9 @@ gemv_w4a8_kernel(const GemvArgs a) {
                 // entry that carries the current exchange number carries its value.
                 const unsigned long long word =
                     ((unsigned long long)tp_exchange << 32) | __float_as_uint(acc);
-                const size_t at = kTpStageHeader + (size_t)(tp_exchange & 1) * a.ldc +
-                                  a.tp.n_offset + n;
+                const size_t at = kTpStageHeader +
+                                  (size_t)(tp_exchange & 1) * kTpMaxRows * a.ldc +
+                                  (size_t)mi * a.ldc + a.tp.n_offset + n;
 #pragma unroll
                 for (int p = 0; p < kTpMaxWorld; ++p)
                     if (p < a.tp.world)
@@ -374,15 +375,18 @@ gemv_w4a8_kernel(const GemvArgs a) {
 // GPU's own matmul (complete: this kernel is ordered after it) and by the peers' -- and unpacks
 // the values into the plain output row.  The last block then advances the exchange count.
 __global__ void __launch_bounds__(kTpGatherThreads)
-tp_gather_kernel(unsigned long long* stage, float* y, int ldc, unsigned* done, int* status) {
+tp_gather_kernel(unsigned long long* stage, float* y, int m, int ldc, unsigned* done,
+                 int* status) {
     b2w4_pdl_chain_entry();
     unsigned* count = reinterpret_cast<unsigned*>(stage);
     const unsigned exchange = *reinterpret_cast<volatile unsigned*>(count) + 1u;
     const volatile unsigned long long* src =
-        stage + kTpStageHeader + (size_t)(exchange & 1) * ldc;
+        stage + kTpStageHeader + (size_t)(exchange & 1) * kTpMaxRows * ldc;
     const unsigned long long t0 = wait_clock();
     bool gave_up = false;
-    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < ldc; i += gridDim.x * blockDim.x) {
+    // the m rows of the exchange are contiguous in the half and in y
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < m * ldc;
+         i += gridDim.x * blockDim.x) {
         unsigned long long word = src[i];
         while ((unsigned)(word >> 32) != exchange && !gave_up) {
             if (wait_clock() - t0 > kTpWaitLimitCycles) {
@@ -461,11 +465,12 @@ int launch_mt(b2w4_ctx* ctx, const GemvArgs& a, bool scl16, bool a32, size_t sme
 int b2w4_launch_gemv(b2w4_ctx* ctx, const b2w4_weight* w, const float* x, int lda,
                      float* y, int ldc, int m, int act_rule, int activation,
                      int act_n_begin, int act_n_len, int32_t* sums, const b2w4_tp_args* tp) {
-    if (tp && m > 1)
-        return b2w4_fail(ctx, B2W4_E_INVALID, "tensor-parallel epilogue: one row per call");
+    if (tp && m > kTpMaxRows)
+        return b2w4_fail(ctx, B2W4_E_INVALID, "tensor-parallel epilogue: at most %d rows",
+                         kTpMaxRows);
     if (m > 1)  // several rows share one pass over the weight on the tensor instruction
         return b2w4_launch_gemv_mma(ctx, w, x, lda, y, ldc, m, act_rule, activation, act_n_begin,
-                                    act_n_len, sums);
+                                    act_n_len, sums, tp);
     const bool a32 = act_rule == B2W4_ACT_G32;
     const int spg = a32 ? 4 : 1;
     const bool scl16 = w->scales_fp16 != 0;
@@ -529,12 +534,13 @@ int b2w4_launch_gemv(b2w4_ctx* ctx, const b2w4_weight* w, const float* x, int ld
     return B2W4_OK;
 }
 
-int b2w4_launch_tp_gather(b2w4_ctx* ctx, unsigned long long* stage_local, float* y, int ldc) {
-    const int blocks = max(1, min((ldc + kTpGatherThreads - 1) / kTpGatherThreads,
+int b2w4_launch_tp_gather(b2w4_ctx* ctx, unsigned long long* stage_local, float* y, int m,
+                          int ldc) {
+    const int blocks = max(1, min((m * ldc + kTpGatherThreads - 1) / kTpGatherThreads,
                                   ctx->sm_count));
     B2W4_CUDA(ctx, b2w4_launch_chained(ctx->pdl, tp_gather_kernel, dim3(blocks),
                                        dim3(kTpGatherThreads), 0, ctx->stream, stage_local, y,
-                                       ldc, reinterpret_cast<unsigned*>(ctx->flag_dev + 6),
+                                       m, ldc, reinterpret_cast<unsigned*>(ctx->flag_dev + 6),
                                        ctx->flag_dev + 1));
     ctx->launches++;
     return B2W4_OK;

@@ -54,6 +54,7 @@ struct MmaArgs {
     int g_magic;                // item / groups == (item * g_magic) >> 16, or 0: divide
     int d_stride;  // floats between the integer sums of consecutive tiles (padded)
     int activation, act_n_begin, act_n_len;
+    b2w4_tp_args tp;  // world != 0: the rows go to every rank's staging buffer instead of y
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -132,6 +133,13 @@ gemv_w4a8_mma_kernel(const MmaArgs a) {
     }
 
     b2w4_pdl_wait();  // activations come from the previous kernel
+
+    // Tensor-parallel exchange number: one more than the count of completed gathers (first
+    // word of this rank's staging buffer, written by the gather kernel).
+    unsigned tp_exchange = 0;
+    if (a.tp.world != 0)
+        tp_exchange =
+            *reinterpret_cast<const volatile unsigned*>(a.tp.stage_peer[a.tp.rank]) + 1u;
 
     // ---- fused activation quantiser: one half-warp per (activation row, group) ----------
     // lane h of the half-warp holds k = 8h .. 8h+7 of the group (a quarter of a 32-block)
@@ -307,7 +315,20 @@ gemv_w4a8_mma_kernel(const MmaArgs a) {
         if (n < a.n) {
             if (b2w4_act_applies(n, a.activation, a.act_n_begin, a.act_n_len, a.n))
                 acc = mma_gemv_activation(acc, a.activation);
-            a.y[(size_t)mi * a.ldc + n] = acc;
+            if (a.tp.world == 0) {
+                a.y[(size_t)mi * a.ldc + n] = acc;
+            } else {
+                // (value, exchange number) as one 8-byte word into every rank's staging buffer
+                const unsigned long long word =
+                    ((unsigned long long)tp_exchange << 32) | __float_as_uint(acc);
+                const size_t at = kTpStageHeader +
+                                  (size_t)(tp_exchange & 1) * kTpMaxRows * a.ldc +
+                                  (size_t)mi * a.ldc + a.tp.n_offset + n;
+#pragma unroll
+                for (int p = 0; p < kTpMaxWorld; ++p)
+                    if (p < a.tp.world)
+                        a.tp.stage_peer[p][at] = word;
+            }
         }
     }
 }
@@ -371,7 +392,8 @@ int mma_launch_mt(b2w4_ctx* ctx, const MmaArgs& a, bool scl16, bool a32, size_t 
 // streams the weight once.
 int b2w4_launch_gemv_mma(b2w4_ctx* ctx, const b2w4_weight* w, const float* x, int lda,
                          float* y, int ldc, int m, int act_rule, int activation,
-                         int act_n_begin, int act_n_len, int32_t* sums) {
+                         int act_n_begin, int act_n_len, int32_t* sums,
+                         const b2w4_tp_args* tp) {
     const bool a32 = act_rule == B2W4_ACT_G32;
     const int spg = a32 ? 4 : 1;
     const bool scl16 = w->scales_fp16 != 0;
@@ -394,6 +416,9 @@ int b2w4_launch_gemv_mma(b2w4_ctx* ctx, const b2w4_weight* w, const float* x, in
         a.activation = activation;
         a.act_n_begin = act_n_begin;
         a.act_n_len = act_n_len;
+        a.tp = b2w4_tp_args();
+        if (tp)
+            a.tp = *tp;
         // Tiles per CTA.  `cap` tiles fit while two CTAs still share an SM.  A weight small
         // enough gets one CTA per SM (the next launch's CTAs are then resident beside this
         // one's and their weights land early); a larger one gets two per SM in one balanced

@@ -1,4 +1,4 @@
-"""GPU parity of the tensor-parallel one-row matmul whose all-gather is done by the kernels
+"""GPU parity of the tensor-parallel decode matmul (1..8 rows) whose all-gather is done by the kernels
 (b2w4_matmul_tp + b2w4_tp_gather): the gathered row equals the unsharded b2w4_matmul and the
 CPU oracle bit for bit.  The ranks of a group are emulated on one GPU as contexts that share
 one stream (every matmul of an exchange is queued before the gathers, so no kernel ever waits
@@ -27,14 +27,17 @@ def _ranks(world, n):
     stream = torch.cuda.current_stream().cuda_stream
     for c in ctxs:
         c.set_stream(stream)
-    stages = [torch.zeros(2 + 2 * n, dtype=torch.int64, device="cuda") for _ in range(world)]
+    stages = [torch.zeros(2 + 16 * n, dtype=torch.int64, device="cuda") for _ in range(world)]
     groups = [_group(r, world, stages) for r in range(world)]
     return ctxs, stages, groups
 
 
-@pytest.mark.parametrize("world,n,k", [(1, 64, 256), (2, 96, 384), (2, 9728, 2560),
-                                        (4, 1024, 1024), (3, 72, 128), (8, 512, 640)])
-def test_gathered_row_equals_unsharded_matmul(world, n, k):
+@pytest.mark.parametrize("world,n,k,m", [(1, 64, 256, 1), (2, 96, 384, 1), (2, 9728, 2560, 1),
+                                          (4, 1024, 1024, 1), (3, 72, 128, 1),
+                                          (8, 512, 640, 1), (2, 96, 384, 2), (2, 2560, 4096, 3),
+                                          (4, 1024, 1024, 4), (2, 9728, 2560, 8),
+                                          (8, 512, 640, 5)])
+def test_gathered_rows_equal_unsharded_matmul(world, n, k, m):
     import torch
     blocks = pkg.synth.bg128_weight(11, 1, n, k)
     ctxs, stages, groups = _ranks(world, n)
@@ -43,11 +46,11 @@ def test_gathered_row_equals_unsharded_matmul(world, n, k):
         sh, n_local, lo = pkg.shard.shard_blocks(blocks, n, k, r, world)
         shards.append((ctxs[r].upload_weight(sh, n_local, k), lo))
     whole = ctxs[0].upload_weight(blocks, n, k)
-    rows = [torch.full((1, n), -3.0, dtype=torch.float32, device="cuda") for _ in range(world)]
-    want = torch.zeros((1, n), dtype=torch.float32, device="cuda")
+    rows = [torch.full((m, n), -3.0, dtype=torch.float32, device="cuda") for _ in range(world)]
+    want = torch.zeros((m, n), dtype=torch.float32, device="cuda")
     # several exchanges in a row: both halves of the staging buffer, and their reuse
     for it in range(5):
-        x = pkg.synth.activations(20 + it, 0, 1, k)
+        x = pkg.synth.activations(20 + it, 0, m, k)
         xd = torch.from_numpy(x).cuda()
         ctxs[0].matmul(whole, xd, want)
         for r in range(world):
@@ -124,6 +127,8 @@ def test_bad_arguments_are_refused():
     row = torch.zeros((1, n), dtype=torch.float32, device="cuda")
     with pytest.raises(pkg.capi.B200W4Error):
         ctx.matmul_tp(w, xd, n - 8, 0, groups[0])  # the row is shorter than the shard
+    with pytest.raises(pkg.capi.B200W4Error):  # at most 8 rows per exchange
+        ctx.matmul_tp(w, torch.zeros((9, k), dtype=torch.float32, device="cuda"), n, 0, groups[0])
     bad = _group(0, 1, stages)
     bad.world = 9
     with pytest.raises(pkg.capi.B200W4Error):
