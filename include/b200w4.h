@@ -175,6 +175,18 @@ int b2w4_moe_combine(b2w4_ctx* ctx, const float* route_out_dev, int tokens, int 
                      int top_k, const int32_t* indices_dev, const float* weights_dev,
                      float* out_dev, int ldo);
 
+/* ---- lm_head with the greedy token picked on the device -----------------------
+ * Replaces the pair "lm_head matmul, copy N logits to the host, argmax_token"
+ * (engine/sampler.cpp:31-77) of a greedy decode step, as the reference's Metal
+ * backend does with lm_head_argmax_device_and_end_graph and its small-batch form
+ * (engine/metal_backend.h:159-176; engine/engine.cpp:792-803, :1189): the
+ * matmul's epilogue reduces the logits of each of the m <= 8 activation rows to
+ * token_dev[row] = the first index of the maximum (a NaN never wins, except at
+ * index 0 where nothing beats it -- the scalar loop's behaviour).  y_dev may be
+ * NULL (logits not written at all) or fp32 [m][ldc].  Per-128 activation rule. */
+int b2w4_matmul_argmax(b2w4_ctx* ctx, const b2w4_weight* w, const float* x_dev, int lda, int m,
+                       float* y_dev, int ldc, int32_t* token_dev);
+
 /* ---- exchanges inside the kernels: tensor-parallel matmul, expert-parallel MoE --
  * No counterpart in the reference (one process, one device).  Instead of a
  * kernel followed by a collective call, the producing kernel stores each value,

@@ -14,12 +14,14 @@
 //                                 kernels/matmul_pack.cpp:641-688
 //   select_moe_routes             kernels/moe_routing.cpp:25-169
 //   kernel_qwen3_moe              kernels/moe.cpp:576-1129
+//   sample_token (temperature 0)  engine/sampler.cpp:458-462 -> argmax_token :31-77
 #include "kernels/matmul.h"
 #include "kernels/matmul_internal.h"
 #include "kernels/moe.h"
 #include "kernels/moe_routing.h"
 #include "kernels/quant_layouts.h"
 #include "kernels/threading.h"
+#include "engine/sampler.h"
 
 #include <chrono>
 #include <cstdint>
@@ -177,6 +179,14 @@ int ref_moe_bg128(const float* hidden, int tokens, int hidden_size,
                                /*router_score_func=*/0, /*norm_topk_prob=*/true,
                                /*has_shared_expert=*/false);
     return ok ? 0 : -1;
+}
+
+// Greedy token: the stateless sampling entry at temperature 0 is argmax_token
+// (engine/sampler.cpp:31-77, :166-172, :458-462).
+int ref_greedy_token(const float* logits, int vocab_size) {
+    std::vector<float> copy(logits, logits + (vocab_size > 0 ? vocab_size : 0));
+    unsigned int seed = 1;
+    return sample_token(copy.data(), vocab_size, 0.0f, 1, 0.0f, &seed);
 }
 
 }  // extern "C"

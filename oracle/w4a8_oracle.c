@@ -499,3 +499,12 @@ void orc_moe_combine(const float* route_out, int tokens, int hidden_size, int to
         }
     }
 }
+
+/* engine/sampler.cpp:72-77 (and :169-170 for the empty row) */
+int orc_argmax_token(const float* logits, int vocab_size) {
+    int best = 0;
+    for (int i = 1; i < vocab_size; ++i)
+        if (logits[i] > logits[best])
+            best = i;
+    return best;
+}

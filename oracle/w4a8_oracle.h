@@ -88,6 +88,12 @@ int orc_moe_forward(const float* hidden, int tokens, int hidden_size, int ldx,
 void orc_moe_combine(const float* route_out, int tokens, int hidden_size, int top_k,
                      const int32_t* indices, const float* weights, float* out, int ldo);
 
+/* Greedy token of one row of logits (engine/sampler.cpp:72-77, the scalar form
+ * of argmax_token): best = 0; every i with logits[i] > logits[best] takes over.
+ * The first maximum wins; a NaN never wins, except at index 0 where nothing
+ * beats it.  vocab_size <= 0 gives 0 (engine/sampler.cpp:169-170). */
+int orc_argmax_token(const float* logits, int vocab_size);
+
 float orc_fp16_to_fp32(uint16_t h);
 
 #ifdef __cplusplus

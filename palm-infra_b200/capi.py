@@ -22,7 +22,7 @@ SYMBOLS = [
     "b2w4_matmul_static_scratch",
     "b2w4_debug_group_sums", "b2w4_quantize_activations", "b2w4_moe_forward",
     "b2w4_moe_select_routes", "b2w4_moe_expert_outputs", "b2w4_moe_combine",
-    "b2w4_matmul_tp", "b2w4_tp_gather", "b2w4_moe_forward_ep",
+    "b2w4_matmul_tp", "b2w4_tp_gather", "b2w4_moe_forward_ep", "b2w4_matmul_argmax",
     "b2w4_kernel_launches",
 ]
 
@@ -77,6 +77,7 @@ def lib():
         L.b2w4_moe_combine.argtypes = [vp, f_p, i, i, i, vp, f_p, f_p, i]
         L.b2w4_matmul_tp.argtypes = [vp, vp, f_p, i, i, i, i, C.POINTER(TpGroup), i, i, i]
         L.b2w4_tp_gather.argtypes = [vp, C.POINTER(TpGroup), f_p, i, i]
+        L.b2w4_matmul_argmax.argtypes = [vp, vp, f_p, i, i, f_p, i, vp]
         L.b2w4_moe_forward_ep.argtypes = [vp, f_p, i, i, i, vp, i, i, i, vp, vp, i, i,
                                           C.POINTER(TpGroup), i, f_p, i, vp, f_p]
         L.b2w4_kernel_launches.argtypes = [vp]
@@ -203,6 +204,14 @@ class Context:
         self._check(lib().b2w4_matmul_tp(self.handle, w_shard.handle, _dptr(x), x.stride(0),
                                          x.shape[0], ldc, n_offset, C.byref(group), act,
                                          act_begin, act_len))
+
+    def matmul_argmax(self, w, x, tokens, y=None):
+        """Matmul of up to 8 rows whose epilogue picks each row's greedy token (int32 tokens
+        [m] on the device); the logits are written only when y is given."""
+        self._check(lib().b2w4_matmul_argmax(
+            self.handle, w.handle, _dptr(x), x.stride(0), x.shape[0],
+            _dptr(y) if y is not None else None, y.stride(0) if y is not None else 0,
+            _dptr(tokens)))
 
     def tp_gather(self, group, y, ldc):
         """Wait for every rank's values of the latest matmul_tp and unpack them into y."""

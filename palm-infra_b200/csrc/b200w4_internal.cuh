@@ -82,6 +82,60 @@ int b2w4_launch_quantize_mma(b2w4_ctx* ctx, const float* x, int lda, int m, int 
 // copy of the output and the launch's last CTA bumps this rank's arrival counter on every
 // rank.  world == 0: off.
 constexpr int kTpMaxWorld = 8;
+// Fused greedy-token epilogue of the decode matmul (engine/sampler.cpp:72-77: best = 0, then
+// every i with logits[i] > logits[best] takes over -- the first maximum wins, a NaN never
+// wins unless it sits at index 0, where nothing can beat it).  Each output becomes the 64-bit
+// word (order-preserving key of the value << 32 | ~index); the maximum word over a row is its
+// token.  cells[8]: one word per activation row, zero between launches (the launch's last CTA
+// reads and clears them); done: CTA counter of the launch, zero between launches.
+constexpr int kTop1MaxRows = 8;
+struct b2w4_top1_args {
+    unsigned long long* cells;
+    unsigned* done;
+    int32_t* token;  // [m] result
+};
+#ifdef __CUDACC__
+__device__ __forceinline__ unsigned long long b2w4_top1_word(float v, int n) {
+    unsigned bits = __float_as_uint(v), key;
+    if (v != v) {
+        key = n == 0 ? 0xFFFFFFFFu : 0u;
+    } else {
+        if (bits == 0x80000000u)
+            bits = 0u;  // -0 == +0: the lower index wins
+        key = (bits & 0x80000000u) ? ~bits : bits | 0x80000000u;  // -inf -> 0x007FFFFF > 0
+    }
+    return ((unsigned long long)key << 32) | (0xFFFFFFFFu - (unsigned)n);
+}
+// After the output loop, every thread of the CTA: `best` is the thread's maximum word for
+// activation row mi (the 8 lanes of a group share mi), s_top1[8] was zeroed at kernel start.
+__device__ __forceinline__ void b2w4_top1_finish(const b2w4_top1_args& t, unsigned long long best,
+                                                 int mi, int m, unsigned long long* s_top1) {
+#pragma unroll
+    for (int o = 1; o <= 4; o <<= 1) {
+        const unsigned long long other = __shfl_xor_sync(0xFFFFFFFFu, best, o);
+        best = other > best ? other : best;
+    }
+    if ((threadIdx.x & 7) == 0 && mi < m)
+        atomicMax(&s_top1[mi], best);
+    __syncthreads();
+    if ((int)threadIdx.x < m) {
+        atomicMax(t.cells + threadIdx.x, s_top1[threadIdx.x]);
+        __threadfence();
+    }
+    __syncthreads();
+    if (threadIdx.x != 0)
+        return;
+    if (atomicAdd(t.done, 1u) != gridDim.x - 1)
+        return;
+    __threadfence();  // the last CTA: every CTA's maximum is in the cells
+    for (int r = 0; r < m; ++r) {
+        const unsigned long long w = atomicExch(t.cells + r, 0ull);  // read and clear
+        t.token[r] = (int32_t)(0xFFFFFFFFu - (unsigned)w);
+    }
+    *t.done = 0;
+}
+#endif
+
 // Staging buffer of a peer exchange (uint64 words): word 0 counts completed exchanges, word 1
 // is unused, then two halves that alternate between exchanges.  Every data word is
 // (exchange number << 32 | fp32 bits), written whole, so a reader needs no fence.
@@ -96,14 +150,14 @@ struct b2w4_tp_args {
 int b2w4_launch_gemv(b2w4_ctx* ctx, const b2w4_weight* w, const float* x, int lda,
                      float* y, int ldc, int m, int act_rule, int activation,
                      int act_n_begin, int act_n_len, int32_t* sums,
-                     const b2w4_tp_args* tp = nullptr);
+                     const b2w4_tp_args* tp = nullptr, const b2w4_top1_args* top1 = nullptr);
 int b2w4_launch_tp_gather(b2w4_ctx* ctx, unsigned long long* stage_local, float* y, int m,
                           int ldc);
 // 2..8 activation rows per pass on the int8 tensor instruction (gemv_mma.cu)
 int b2w4_launch_gemv_mma(b2w4_ctx* ctx, const b2w4_weight* w, const float* x, int lda,
                      float* y, int ldc, int m, int act_rule, int activation,
                      int act_n_begin, int act_n_len, int32_t* sums,
-                     const b2w4_tp_args* tp = nullptr);
+                     const b2w4_tp_args* tp = nullptr, const b2w4_top1_args* top1 = nullptr);
 
 int b2w4_launch_quantize_umma(b2w4_ctx* ctx, const float* x, int lda, int m, int k, int m_pad,
                               int8_t* q, float* scales);

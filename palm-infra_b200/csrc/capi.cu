@@ -71,8 +71,8 @@ int b2w4_ctx_create(int device, b2w4_ctx** out) {
     const char* gmr = getenv("B2W4_GEMV_MAX_ROWS");  // tuning/debug: rows kept on the GEMV
     if (gmr && atoi(gmr) > 0)
         ctx->gemv_max_rows = atoi(gmr);
-    if (cudaMalloc(reinterpret_cast<void**>(&ctx->flag_dev), 64) != cudaSuccess ||
-        cudaMemset(ctx->flag_dev, 0, 64) != cudaSuccess) {
+    if (cudaMalloc(reinterpret_cast<void**>(&ctx->flag_dev), 256) != cudaSuccess ||
+        cudaMemset(ctx->flag_dev, 0, 256) != cudaSuccess) {
         delete ctx;
         return B2W4_E_NOMEM;
     }
@@ -338,6 +338,22 @@ int b2w4_matmul_tp(b2w4_ctx* ctx, const b2w4_weight* w, const float* x_dev, int 
     tp.n_offset = n_offset;
     return b2w4_launch_gemv(ctx, w, x_dev, lda, nullptr, ldc, m, B2W4_ACT_G128, activation,
                             act_n_begin, act_n_len, nullptr, &tp);
+}
+
+int b2w4_matmul_argmax(b2w4_ctx* ctx, const b2w4_weight* w, const float* x_dev, int lda, int m,
+                       float* y_dev, int ldc, int32_t* token_dev) {
+    if (!ctx)
+        return B2W4_E_INVALID;
+    if (!w || !x_dev || !token_dev || m < 1 || m > kTop1MaxRows || lda < w->k ||
+        (y_dev && ldc < w->n))
+        return b2w4_fail(ctx, B2W4_E_INVALID, "matmul_argmax: bad argument (1..%d rows)",
+                         kTop1MaxRows);
+    b2w4_top1_args top1;
+    top1.cells = reinterpret_cast<unsigned long long*>(ctx->flag_dev + 16);  // 8 words
+    top1.done = reinterpret_cast<unsigned*>(ctx->flag_dev + 7);
+    top1.token = token_dev;
+    return b2w4_launch_gemv(ctx, w, x_dev, lda, y_dev, ldc, m, B2W4_ACT_G128, B2W4_NONE, 0, -1,
+                            nullptr, nullptr, &top1);
 }
 
 int b2w4_tp_gather(b2w4_ctx* ctx, const b2w4_tp_group* group, float* y_dev, int m, int ldc) {

@@ -60,7 +60,10 @@ struct GemvArgs {
     int d_stride;  // ints between the integer sums of consecutive tiles (padded)
     int activation, act_n_begin, act_n_len;
     b2w4_tp_args tp;  // tensor-parallel epilogue (world == 0: off)
+    b2w4_top1_args top1;  // greedy-token epilogue (MODE 2)
 };
+// Kernel modes: plain, with the int32 group sums written out, with the greedy-token epilogue.
+constexpr int kModePlain = 0, kModeSums = 1, kModeTop1 = 2;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -125,7 +128,7 @@ __device__ __noinline__ float gemv_activation(float v, int act) {
     return b2w4_activation(v, act);
 }
 
-template <int MT, bool SCL16, bool A32, bool SUMS>
+template <int MT, bool SCL16, bool A32, int MODE>
 __global__ void __launch_bounds__(gemv_warps(MT) * 32, 2)
 gemv_w4a8_kernel(const GemvArgs a) {
     constexpr int kWarps = gemv_warps(MT);
@@ -148,6 +151,11 @@ gemv_w4a8_kernel(const GemvArgs a) {
     uint64_t* s_bar = reinterpret_cast<uint64_t*>(
         (reinterpret_cast<uintptr_t>(s_sc + (size_t)a.tpc * a.d_stride) + 7) & ~uintptr_t(7));
 
+    constexpr bool SUMS = MODE == kModeSums;
+    __shared__ unsigned long long s_top1[8];
+    if (MODE == kModeTop1 && threadIdx.x < 8)
+        s_top1[threadIdx.x] = 0ull;  // barriers follow before the epilogue uses it
+    unsigned long long top1_best = 0ull;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int gl = lane >> 3, row = lane & 7;
     const int tile0 = blockIdx.x * a.tpc;
@@ -349,7 +357,12 @@ gemv_w4a8_kernel(const GemvArgs a) {
         if (n < a.n) {
             if (b2w4_act_applies(n, a.activation, a.act_n_begin, a.act_n_len, a.n))
                 acc = gemv_activation(acc, a.activation);
-            if (a.tp.world == 0) {
+            if (MODE == kModeTop1) {
+                const unsigned long long word = b2w4_top1_word(acc, n);
+                top1_best = word > top1_best ? word : top1_best;
+                if (a.y)
+                    a.y[(size_t)mi * a.ldc + n] = acc;
+            } else if (a.tp.world == 0) {
                 a.y[(size_t)mi * a.ldc + n] = acc;
             } else {
                 // The all-gather is this store: every rank's staging buffer, this GPU's own
@@ -368,6 +381,8 @@ gemv_w4a8_kernel(const GemvArgs a) {
             }
         }
     }
+    if (MODE == kModeTop1)
+        b2w4_top1_finish(a.top1, top1_best, (threadIdx.x >> 3) % MT, a.m, s_top1);
 }
 
 // Second half of the tensor-parallel exchange: waits (bounded) until every entry of the
@@ -418,9 +433,9 @@ size_t gemv_smem_bytes(int mt, int k, int groups, int tpc, bool scl16, bool a32)
            sizeof(uint64_t) * (tpc + 1);
 }
 
-template <int MT, bool SCL16, bool A32, bool SUMS>
+template <int MT, bool SCL16, bool A32, int MODE>
 int launch_one(b2w4_ctx* ctx, const GemvArgs& a, size_t smem) {
-    auto kern = gemv_w4a8_kernel<MT, SCL16, A32, SUMS>;
+    auto kern = gemv_w4a8_kernel<MT, SCL16, A32, MODE>;
     static size_t configured = 48 * 1024;  // per instantiation; one device per process
     if (smem > configured) {
         B2W4_CUDA(ctx, cudaFuncSetAttribute(
@@ -444,19 +459,15 @@ int launch_one(b2w4_ctx* ctx, const GemvArgs& a, size_t smem) {
 
 template <int MT>
 int launch_mt(b2w4_ctx* ctx, const GemvArgs& a, bool scl16, bool a32, size_t smem) {
-    const bool sums = a.sums != nullptr;
-    if (scl16) {
-        if (a32)
-            return sums ? launch_one<MT, true, true, true>(ctx, a, smem)
-                        : launch_one<MT, true, true, false>(ctx, a, smem);
-        return sums ? launch_one<MT, true, false, true>(ctx, a, smem)
-                    : launch_one<MT, true, false, false>(ctx, a, smem);
-    }
-    if (a32)
-        return sums ? launch_one<MT, false, true, true>(ctx, a, smem)
-                    : launch_one<MT, false, true, false>(ctx, a, smem);
-    return sums ? launch_one<MT, false, false, true>(ctx, a, smem)
-                : launch_one<MT, false, false, false>(ctx, a, smem);
+    const int mode = a.sums ? kModeSums : (a.top1.cells ? kModeTop1 : kModePlain);
+#define B2W4_GEMV_MODES(S, A)                                              \
+    (mode == kModeSums   ? launch_one<MT, S, A, kModeSums>(ctx, a, smem)   \
+     : mode == kModeTop1 ? launch_one<MT, S, A, kModeTop1>(ctx, a, smem)   \
+                         : launch_one<MT, S, A, kModePlain>(ctx, a, smem))
+    if (scl16)
+        return a32 ? B2W4_GEMV_MODES(true, true) : B2W4_GEMV_MODES(true, false);
+    return a32 ? B2W4_GEMV_MODES(false, true) : B2W4_GEMV_MODES(false, false);
+#undef B2W4_GEMV_MODES
 }
 
 }  // namespace
@@ -464,13 +475,14 @@ int launch_mt(b2w4_ctx* ctx, const GemvArgs& a, bool scl16, bool a32, size_t sme
 // Rows are processed four at a time; each pass streams the weight once.
 int b2w4_launch_gemv(b2w4_ctx* ctx, const b2w4_weight* w, const float* x, int lda,
                      float* y, int ldc, int m, int act_rule, int activation,
-                     int act_n_begin, int act_n_len, int32_t* sums, const b2w4_tp_args* tp) {
+                     int act_n_begin, int act_n_len, int32_t* sums, const b2w4_tp_args* tp,
+                     const b2w4_top1_args* top1) {
     if (tp && m > kTpMaxRows)
         return b2w4_fail(ctx, B2W4_E_INVALID, "tensor-parallel epilogue: at most %d rows",
                          kTpMaxRows);
     if (m > 1)  // several rows share one pass over the weight on the tensor instruction
         return b2w4_launch_gemv_mma(ctx, w, x, lda, y, ldc, m, act_rule, activation, act_n_begin,
-                                    act_n_len, sums, tp);
+                                    act_n_len, sums, tp, top1);
     const bool a32 = act_rule == B2W4_ACT_G32;
     const int spg = a32 ? 4 : 1;
     const bool scl16 = w->scales_fp16 != 0;
@@ -499,6 +511,9 @@ int b2w4_launch_gemv(b2w4_ctx* ctx, const b2w4_weight* w, const float* x, int ld
             a.tp = *tp;
         else
             a.tp.world = 0;
+        a.top1 = b2w4_top1_args();
+        if (top1)
+            a.top1 = *top1;
         // Tiles per CTA: a CTA's shared memory stays under half an SM's so that two CTAs share
         // an SM, and the launch is one wave of at most 1.75 CTAs per SM.  Measured on the
         // decode shapes of a 4B dense model (148 SMs): N=9728 K=2560 (1216 tiles) 244 CTAs

@@ -55,7 +55,10 @@ struct MmaArgs {
     int d_stride;  // floats between the integer sums of consecutive tiles (padded)
     int activation, act_n_begin, act_n_len;
     b2w4_tp_args tp;  // world != 0: the rows go to every rank's staging buffer instead of y
+    b2w4_top1_args top1;  // greedy-token epilogue (MODE 2)
 };
+// Kernel modes: plain, with the int32 group sums written out, with the greedy-token epilogue.
+constexpr int kModePlain = 0, kModeSums = 1, kModeTop1 = 2;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -89,7 +92,7 @@ __device__ __noinline__ float mma_gemv_activation(float v, int act) {
     return b2w4_activation(v, act);
 }
 
-template <int MT, bool SCL16, bool A32, bool SUMS>
+template <int MT, bool SCL16, bool A32, int MODE>
 __global__ void __launch_bounds__(kMmaWarps * 32, 2)
 gemv_w4a8_mma_kernel(const MmaArgs a) {
     constexpr int kWarps = kMmaWarps;
@@ -109,6 +112,11 @@ gemv_w4a8_mma_kernel(const MmaArgs a) {
     // (exact: |sum| < 2^24)
     float* s_d = reinterpret_cast<float*>(s_es + MT * G * SPG);  // [cap][G][SPG][MT][8] + pad
 
+    constexpr bool SUMS = MODE == kModeSums;
+    __shared__ unsigned long long s_top1[8];
+    if (MODE == kModeTop1 && threadIdx.x < 8)
+        s_top1[threadIdx.x] = 0ull;  // barriers follow before the epilogue uses it
+    unsigned long long top1_best = 0ull;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int gl = lane >> 3, row = lane & 7;
     const int cta = blockIdx.x;
@@ -315,7 +323,12 @@ gemv_w4a8_mma_kernel(const MmaArgs a) {
         if (n < a.n) {
             if (b2w4_act_applies(n, a.activation, a.act_n_begin, a.act_n_len, a.n))
                 acc = mma_gemv_activation(acc, a.activation);
-            if (a.tp.world == 0) {
+            if (MODE == kModeTop1) {
+                const unsigned long long word = b2w4_top1_word(acc, n);
+                top1_best = word > top1_best ? word : top1_best;
+                if (a.y)
+                    a.y[(size_t)mi * a.ldc + n] = acc;
+            } else if (a.tp.world == 0) {
                 a.y[(size_t)mi * a.ldc + n] = acc;
             } else {
                 // (value, exchange number) as one 8-byte word into every rank's staging buffer
@@ -331,6 +344,9 @@ gemv_w4a8_mma_kernel(const MmaArgs a) {
             }
         }
     }
+    // kThreads / 8 is a multiple of MT: a thread's activation row is the same in every pass
+    if (MODE == kModeTop1)
+        b2w4_top1_finish(a.top1, top1_best, (threadIdx.x >> 3) % MT, a.m, s_top1);
 }
 
 int mma_d_stride(int mt, int groups, bool a32) {
@@ -345,9 +361,9 @@ size_t mma_smem_bytes(int mt, int k, int groups, int cap, bool scl16, bool a32) 
            sizeof(float) * (size_t)cap * mma_d_stride(mt, groups, a32) + 16;
 }
 
-template <int MT, bool SCL16, bool A32, bool SUMS>
+template <int MT, bool SCL16, bool A32, int MODE>
 int mma_launch_one(b2w4_ctx* ctx, const MmaArgs& a, size_t smem, int ctas) {
-    auto kern = gemv_w4a8_mma_kernel<MT, SCL16, A32, SUMS>;
+    auto kern = gemv_w4a8_mma_kernel<MT, SCL16, A32, MODE>;
     static size_t configured = 48 * 1024;  // per instantiation; one device per process
     if (smem > configured) {
         B2W4_CUDA(ctx, cudaFuncSetAttribute(
@@ -371,19 +387,15 @@ int mma_launch_one(b2w4_ctx* ctx, const MmaArgs& a, size_t smem, int ctas) {
 
 template <int MT>
 int mma_launch_mt(b2w4_ctx* ctx, const MmaArgs& a, bool scl16, bool a32, size_t smem, int ctas) {
-    const bool sums = a.sums != nullptr;
-    if (scl16) {
-        if (a32)
-            return sums ? mma_launch_one<MT, true, true, true>(ctx, a, smem, ctas)
-                        : mma_launch_one<MT, true, true, false>(ctx, a, smem, ctas);
-        return sums ? mma_launch_one<MT, true, false, true>(ctx, a, smem, ctas)
-                    : mma_launch_one<MT, true, false, false>(ctx, a, smem, ctas);
-    }
-    if (a32)
-        return sums ? mma_launch_one<MT, false, true, true>(ctx, a, smem, ctas)
-                    : mma_launch_one<MT, false, true, false>(ctx, a, smem, ctas);
-    return sums ? mma_launch_one<MT, false, false, true>(ctx, a, smem, ctas)
-                : mma_launch_one<MT, false, false, false>(ctx, a, smem, ctas);
+    const int mode = a.sums ? kModeSums : (a.top1.cells ? kModeTop1 : kModePlain);
+#define B2W4_MMA_MODES(S, A)                                                        \
+    (mode == kModeSums   ? mma_launch_one<MT, S, A, kModeSums>(ctx, a, smem, ctas)   \
+     : mode == kModeTop1 ? mma_launch_one<MT, S, A, kModeTop1>(ctx, a, smem, ctas)   \
+                         : mma_launch_one<MT, S, A, kModePlain>(ctx, a, smem, ctas))
+    if (scl16)
+        return a32 ? B2W4_MMA_MODES(true, true) : B2W4_MMA_MODES(true, false);
+    return a32 ? B2W4_MMA_MODES(false, true) : B2W4_MMA_MODES(false, false);
+#undef B2W4_MMA_MODES
 }
 
 }  // namespace
@@ -393,7 +405,7 @@ int mma_launch_mt(b2w4_ctx* ctx, const MmaArgs& a, bool scl16, bool a32, size_t 
 int b2w4_launch_gemv_mma(b2w4_ctx* ctx, const b2w4_weight* w, const float* x, int lda,
                          float* y, int ldc, int m, int act_rule, int activation,
                          int act_n_begin, int act_n_len, int32_t* sums,
-                         const b2w4_tp_args* tp) {
+                         const b2w4_tp_args* tp, const b2w4_top1_args* top1) {
     const bool a32 = act_rule == B2W4_ACT_G32;
     const int spg = a32 ? 4 : 1;
     const bool scl16 = w->scales_fp16 != 0;
@@ -419,6 +431,9 @@ int b2w4_launch_gemv_mma(b2w4_ctx* ctx, const b2w4_weight* w, const float* x, in
         a.tp = b2w4_tp_args();
         if (tp)
             a.tp = *tp;
+        a.top1 = b2w4_top1_args();
+        if (top1)
+            a.top1 = *top1;
         // Tiles per CTA.  `cap` tiles fit while two CTAs still share an SM.  A weight small
         // enough gets one CTA per SM (the next launch's CTAs are then resident beside this
         // one's and their weights land early); a larger one gets two per SM in one balanced

@@ -265,3 +265,13 @@ def ref_moe(hidden, router_fp16, top_k, intermediate, gate_up, down, threads=1):
                              intermediate, _ptr(gate_up), _ptr(down), _ptr(out), threads)
     assert rc == 0
     return out
+
+
+def argmax_token(logits):
+    logits = np.ascontiguousarray(logits, dtype=np.float32)
+    return int(oracle().orc_argmax_token(_ptr(logits), logits.size))
+
+
+def ref_greedy_token(logits):
+    logits = np.ascontiguousarray(logits, dtype=np.float32)
+    return int(ref().ref_greedy_token(_ptr(logits), logits.size))

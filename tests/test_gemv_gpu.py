@@ -316,3 +316,64 @@ def test_gemv_and_tensor_core_paths_agree(ctx):
     ctx.sync()
     assert torch.equal(y_all, y_one)
     w.free()
+
+
+@pytest.mark.parametrize("n,k,m", [(64, 128, 1), (1024, 512, 1), (9728, 2560, 1), (1024, 512, 2),
+                                   (2048, 1024, 4), (9728, 2560, 5), (4096, 640, 8),
+                                   (151936, 2560, 1), (151936, 2560, 3)])
+def test_matmul_argmax_picks_the_oracle_token(ctx, n, k, m):
+    """b2w4_matmul_argmax: the token of every row equals argmax_token over the oracle's
+    logits (which the device logits match bit for bit), with and without the logits written,
+    and again on a second call (the reduction cells are cleared by the launch itself)."""
+    import torch
+    blocks = pkg.synth.bg128_weight(41, 3, n, k)
+    w = ctx.upload_weight(blocks, n, k)
+    for call in range(2):
+        x = pkg.synth.activations(90 + call, 1, m, k)
+        xd = torch.from_numpy(x).cuda()
+        ref = ol.matmul_w4(blocks, n, k, x, rule=ol.ACT_G128)
+        want = [ol.argmax_token(ref[i]) for i in range(m)]
+        tok = torch.full((m,), -1, dtype=torch.int32, device="cuda")
+        y = torch.zeros((m, n), dtype=torch.float32, device="cuda")
+        ctx.matmul_argmax(w, xd, tok, y)
+        ctx.sync()
+        assert tok.cpu().tolist() == want
+        assert np.array_equal(y.cpu().numpy().view(np.uint32), ref.view(np.uint32))
+        tok.fill_(-1)
+        ctx.matmul_argmax(w, xd, tok)        # logits not written at all
+        ctx.sync()
+        assert tok.cpu().tolist() == want
+    w.free()
+
+
+@pytest.mark.parametrize("m", [1, 4])
+def test_matmul_argmax_equal_logits_go_to_the_lowest_index(ctx, m):
+    """Every 8-row tile of the weight is the same tile, so row r and rows r+8, r+16, ... give
+    identical logits in different CTAs: the first of them must win."""
+    import torch
+    k, tiles = 512, 600
+    one = pkg.synth.bg128_weight(42, 1, 8, k)
+    blocks = np.tile(one, tiles)
+    n = 8 * tiles
+    w = ctx.upload_weight(blocks, n, k)
+    x = pkg.synth.activations(95, 2, m, k)
+    ref = ol.matmul_w4(blocks, n, k, x, rule=ol.ACT_G128)
+    want = [ol.argmax_token(ref[i]) for i in range(m)]
+    assert all(t < 8 for t in want)
+    tok = torch.full((m,), -1, dtype=torch.int32, device="cuda")
+    ctx.matmul_argmax(w, torch.from_numpy(x).cuda(), tok)
+    ctx.sync()
+    assert tok.cpu().tolist() == want
+    w.free()
+
+
+def test_matmul_argmax_bad_arguments(ctx):
+    import torch
+    w = ctx.upload_weight(pkg.synth.bg128_weight(43, 1, 64, 128), 64, 128)
+    tok = torch.zeros((9,), dtype=torch.int32, device="cuda")
+    with pytest.raises(pkg.capi.B200W4Error):
+        ctx.matmul_argmax(w, torch.zeros((9, 128), device="cuda"), tok)   # more than 8 rows
+    with pytest.raises(pkg.capi.B200W4Error):
+        ctx.matmul_argmax(w, torch.zeros((1, 128), device="cuda"), tok,
+                          torch.zeros((1, 32), device="cuda"))           # logits row too short
+    w.free()

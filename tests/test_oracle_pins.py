@@ -135,3 +135,37 @@ def test_live_reference_agrees_on_fresh_inputs():
     q32, s32 = ol.quantize_g32(a)
     rq32, rs32 = ol.ref_quantize_g32(a)
     assert (q32 == rq32).all() and (s32 == rs32).all()
+
+
+def _argmax_rows():
+    rng = np.random.default_rng(77)
+    rows = [rng.standard_normal(n).astype(np.float32) for n in (1, 2, 3, 4, 5, 7, 8, 100, 4097)]
+    tie = np.zeros(64, dtype=np.float32)
+    tie[[9, 17, 40]] = 3.5                       # equal maxima: the first wins
+    neg0 = np.full(16, -1.0, dtype=np.float32)
+    neg0[5], neg0[11] = -0.0, 0.0                # -0 == +0: the first wins
+    nan_mid = rng.standard_normal(40).astype(np.float32)
+    nan_mid[[3, 20]] = np.nan                    # a NaN never beats a number
+    nan_first = rng.standard_normal(40).astype(np.float32)
+    nan_first[0] = np.nan                        # ... but nothing beats a NaN at index 0
+    infs = np.array([-np.inf, np.nan, -np.inf, np.inf, np.inf], dtype=np.float32)
+    all_ninf = np.full(9, -np.inf, dtype=np.float32)
+    return rows + [tie, neg0, nan_mid, nan_first, infs, all_ninf]
+
+
+def test_argmax_oracle_cases():
+    """The scalar rule of argmax_token (engine/sampler.cpp:72-77) on its corner cases."""
+    want = [None] * 9 + [9, 5, None, 0, 3, 0]
+    for row, w in zip(_argmax_rows(), want):
+        got = ol.argmax_token(row)
+        if w is None:
+            clean = np.where(np.isnan(row), -np.inf, row)
+            w = int(np.argmax(clean))            # numpy: first maximum
+        assert got == w
+
+
+@pytest.mark.skipif(not ol.have_ref(), reason="oracle/_ref not built")
+def test_argmax_oracle_equals_reference_sampler():
+    """Pinned against the reference's own greedy sampling entry (temperature 0)."""
+    for row in _argmax_rows():
+        assert ol.argmax_token(row) == ol.ref_greedy_token(row)
