@@ -386,6 +386,32 @@ def decode_walk(torch, pkg, ctx, args):
         us = s_ms * 1e3 / (len(sel) * reps)
         per_shape[f"n{n}_k{k}"] = {"us": us, "gbs": algorithmic_bytes(n, k, 1) / us / 1e3}
     out["per_shape"] = per_shape
+    # greedy step at the lm_head: logits written + a library argmax kernel, against the token
+    # picked in the matmul's own epilogue with no logits written (8 graph nodes each so that
+    # the weight, 195 MB, is re-read from HBM every time: it exceeds L2)
+    lm = ws[-1]
+    tok = torch.zeros((1,), dtype=torch.int32, device="cuda")
+    tok64 = torch.zeros((1,), dtype=torch.int64, device="cuda")
+    greedy = {}
+    for name in ("matmul_then_torch_argmax", "matmul_argmax_fused"):
+        def eager_greedy():
+            for _ in range(8):
+                if name == "matmul_argmax_fused":
+                    ctx.matmul_argmax(lm, xs[2560], tok)
+                else:
+                    ctx.matmul(lm, xs[2560], ys[vocab])
+                    torch.argmax(ys[vocab], dim=1, out=tok64)
+        eager_greedy()
+        torch.cuda.synchronize()
+        gg = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            ctx.set_stream(side.cuda_stream)
+            with torch.cuda.graph(gg, stream=side):
+                eager_greedy()
+        ctx.set_stream(torch.cuda.current_stream().cuda_stream)
+        greedy[name] = {"us": time_steps(torch, gg.replay, 10, 3) * 1e3 / 8}
+    greedy["same_token"] = bool(int(tok.item()) == int(tok64.item()))
+    out["lm_head_greedy_token"] = greedy
     for w in ws:
         w.free()
     return out

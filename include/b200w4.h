@@ -219,6 +219,16 @@ int b2w4_matmul_tp(b2w4_ctx* ctx, const b2w4_weight* w_shard, const float* x_dev
                    int act_n_begin, int act_n_len);
 int b2w4_tp_gather(b2w4_ctx* ctx, const b2w4_tp_group* group, float* y_dev, int m, int ldc);
 
+/* Tensor-parallel lm_head with the greedy token picked on the devices: every rank
+ * reduces its rows to one (maximum, index in the unsharded weight) pair per
+ * activation row and hands it to every rank as two tagged words (staging buffer
+ * uint64[2 + 2 * 128]); b2w4_tp_gather_token takes the largest of the world's
+ * pairs -- the token b2w4_matmul_argmax gives on the unsharded weight -- into
+ * token_dev [m] and advances the count.  No logits leave a GPU. */
+int b2w4_matmul_argmax_tp(b2w4_ctx* ctx, const b2w4_weight* w_shard, const float* x_dev, int lda,
+                          int m, int n_offset, const b2w4_tp_group* group);
+int b2w4_tp_gather_token(b2w4_ctx* ctx, const b2w4_tp_group* group, int32_t* token_dev, int m);
+
 /* Expert-parallel MoE with the hand-over inside: b2w4_moe_expert_outputs, the sum
  * over the ranks and b2w4_moe_combine as one call.  The owner of a route stores
  * its down-projection row into every rank's staging buffer (half = stage_rows *

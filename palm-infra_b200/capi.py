@@ -22,7 +22,7 @@ SYMBOLS = [
     "b2w4_matmul_static_scratch",
     "b2w4_debug_group_sums", "b2w4_quantize_activations", "b2w4_moe_forward",
     "b2w4_moe_select_routes", "b2w4_moe_expert_outputs", "b2w4_moe_combine",
-    "b2w4_matmul_tp", "b2w4_tp_gather", "b2w4_moe_forward_ep", "b2w4_matmul_argmax",
+    "b2w4_matmul_tp", "b2w4_tp_gather", "b2w4_moe_forward_ep", "b2w4_matmul_argmax", "b2w4_matmul_argmax_tp", "b2w4_tp_gather_token",
     "b2w4_kernel_launches",
 ]
 
@@ -78,6 +78,8 @@ def lib():
         L.b2w4_matmul_tp.argtypes = [vp, vp, f_p, i, i, i, i, C.POINTER(TpGroup), i, i, i]
         L.b2w4_tp_gather.argtypes = [vp, C.POINTER(TpGroup), f_p, i, i]
         L.b2w4_matmul_argmax.argtypes = [vp, vp, f_p, i, i, f_p, i, vp]
+        L.b2w4_matmul_argmax_tp.argtypes = [vp, vp, f_p, i, i, i, C.POINTER(TpGroup)]
+        L.b2w4_tp_gather_token.argtypes = [vp, C.POINTER(TpGroup), vp, i]
         L.b2w4_moe_forward_ep.argtypes = [vp, f_p, i, i, i, vp, i, i, i, vp, vp, i, i,
                                           C.POINTER(TpGroup), i, f_p, i, vp, f_p]
         L.b2w4_kernel_launches.argtypes = [vp]
@@ -212,6 +214,16 @@ class Context:
             self.handle, w.handle, _dptr(x), x.stride(0), x.shape[0],
             _dptr(y) if y is not None else None, y.stride(0) if y is not None else 0,
             _dptr(tokens)))
+
+    def matmul_argmax_tp(self, w_shard, x, n_offset, group):
+        """This rank's half of the tensor-parallel greedy token (see tp_gather_token)."""
+        self._check(lib().b2w4_matmul_argmax_tp(self.handle, w_shard.handle, _dptr(x),
+                                                x.stride(0), x.shape[0], n_offset,
+                                                C.byref(group)))
+
+    def tp_gather_token(self, group, tokens):
+        self._check(lib().b2w4_tp_gather_token(self.handle, C.byref(group), _dptr(tokens),
+                                               tokens.shape[0]))
 
     def tp_gather(self, group, y, ldc):
         """Wait for every rank's values of the latest matmul_tp and unpack them into y."""

@@ -82,6 +82,17 @@ int b2w4_launch_quantize_mma(b2w4_ctx* ctx, const float* x, int lda, int m, int 
 // copy of the output and the launch's last CTA bumps this rank's arrival counter on every
 // rank.  world == 0: off.
 constexpr int kTpMaxWorld = 8;
+// Staging buffer of a peer exchange (uint64 words): word 0 counts completed exchanges, word 1
+// is unused, then two halves that alternate between exchanges.  Every data word is
+// (exchange number << 32 | fp32 bits), written whole, so a reader needs no fence.
+constexpr int kTpStageHeader = 2;
+constexpr int kTpMaxRows = 8;  // activation rows per tensor-parallel matmul; half = 8 * ldc words
+constexpr unsigned long long kTpWaitLimitCycles = 100000000ull;  // about 50 ms
+struct b2w4_tp_args {
+    unsigned long long* stage_peer[kTpMaxWorld];  // rank p's staging buffer, mapped on this GPU
+    int world, rank, n_offset;  // n_offset: first output column of this rank's rows
+};
+
 // Fused greedy-token epilogue of the decode matmul (engine/sampler.cpp:72-77: best = 0, then
 // every i with logits[i] > logits[best] takes over -- the first maximum wins, a NaN never
 // wins unless it sits at index 0, where nothing can beat it).  Each output becomes the 64-bit
@@ -89,6 +100,9 @@ constexpr int kTpMaxWorld = 8;
 // token.  cells[8]: one word per activation row, zero between launches (the launch's last CTA
 // reads and clears them); done: CTA counter of the launch, zero between launches.
 constexpr int kTop1MaxRows = 8;
+// Tensor-parallel form: every rank's (row, rank) maximum goes to every rank's staging buffer
+// as two tagged words (key, ~global index); half = rows * ranks * 2 words.
+constexpr int kTop1StageHalf = kTop1MaxRows * kTpMaxWorld * 2;
 struct b2w4_top1_args {
     unsigned long long* cells;
     unsigned* done;
@@ -108,8 +122,9 @@ __device__ __forceinline__ unsigned long long b2w4_top1_word(float v, int n) {
 }
 // After the output loop, every thread of the CTA: `best` is the thread's maximum word for
 // activation row mi (the 8 lanes of a group share mi), s_top1[8] was zeroed at kernel start.
-__device__ __forceinline__ void b2w4_top1_finish(const b2w4_top1_args& t, unsigned long long best,
-                                                 int mi, int m, unsigned long long* s_top1) {
+__device__ __forceinline__ void b2w4_top1_finish(const b2w4_top1_args& t, const b2w4_tp_args& tp,
+                                                 unsigned long long best, int mi, int m,
+                                                 unsigned long long* s_top1) {
 #pragma unroll
     for (int o = 1; o <= 4; o <<= 1) {
         const unsigned long long other = __shfl_xor_sync(0xFFFFFFFFu, best, o);
@@ -128,24 +143,31 @@ __device__ __forceinline__ void b2w4_top1_finish(const b2w4_top1_args& t, unsign
     if (atomicAdd(t.done, 1u) != gridDim.x - 1)
         return;
     __threadfence();  // the last CTA: every CTA's maximum is in the cells
+    unsigned long long tag = 0;
+    size_t at = 0;
+    if (tp.world != 0) {
+        const unsigned exchange =
+            *reinterpret_cast<const volatile unsigned*>(tp.stage_peer[tp.rank]) + 1u;
+        tag = (unsigned long long)exchange << 32;
+        at = kTpStageHeader + (size_t)(exchange & 1) * kTop1StageHalf;
+    }
     for (int r = 0; r < m; ++r) {
         const unsigned long long w = atomicExch(t.cells + r, 0ull);  // read and clear
-        t.token[r] = (int32_t)(0xFFFFFFFFu - (unsigned)w);
+        if (tp.world == 0) {
+            t.token[r] = (int32_t)(0xFFFFFFFFu - (unsigned)w);
+        } else {
+            // this rank's maximum of row r, to every rank: two tagged words
+            const size_t slot = at + ((size_t)r * kTpMaxWorld + tp.rank) * 2;
+            for (int p = 0; p < tp.world; ++p) {
+                tp.stage_peer[p][slot] = tag | (w >> 32);
+                tp.stage_peer[p][slot + 1] = tag | (w & 0xFFFFFFFFull);
+            }
+        }
     }
     *t.done = 0;
 }
 #endif
 
-// Staging buffer of a peer exchange (uint64 words): word 0 counts completed exchanges, word 1
-// is unused, then two halves that alternate between exchanges.  Every data word is
-// (exchange number << 32 | fp32 bits), written whole, so a reader needs no fence.
-constexpr int kTpStageHeader = 2;
-constexpr int kTpMaxRows = 8;  // activation rows per tensor-parallel matmul; half = 8 * ldc words
-constexpr unsigned long long kTpWaitLimitCycles = 100000000ull;  // about 50 ms
-struct b2w4_tp_args {
-    unsigned long long* stage_peer[kTpMaxWorld];  // rank p's staging buffer, mapped on this GPU
-    int world, rank, n_offset;  // n_offset: first output column of this rank's rows
-};
 
 int b2w4_launch_gemv(b2w4_ctx* ctx, const b2w4_weight* w, const float* x, int lda,
                      float* y, int ldc, int m, int act_rule, int activation,
@@ -153,6 +175,8 @@ int b2w4_launch_gemv(b2w4_ctx* ctx, const b2w4_weight* w, const float* x, int ld
                      const b2w4_tp_args* tp = nullptr, const b2w4_top1_args* top1 = nullptr);
 int b2w4_launch_tp_gather(b2w4_ctx* ctx, unsigned long long* stage_local, float* y, int m,
                           int ldc);
+int b2w4_launch_tp_gather_token(b2w4_ctx* ctx, unsigned long long* stage_local, int32_t* token,
+                                int m, int world);
 // 2..8 activation rows per pass on the int8 tensor instruction (gemv_mma.cu)
 int b2w4_launch_gemv_mma(b2w4_ctx* ctx, const b2w4_weight* w, const float* x, int lda,
                      float* y, int ldc, int m, int act_rule, int activation,

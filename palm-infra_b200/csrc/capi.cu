@@ -356,6 +356,54 @@ int b2w4_matmul_argmax(b2w4_ctx* ctx, const b2w4_weight* w, const float* x_dev, 
                             nullptr, nullptr, &top1);
 }
 
+static int tp_args_from_group(b2w4_ctx* ctx, const b2w4_tp_group* group, int n_offset,
+                              b2w4_tp_args* tp, const char* who) {
+    if (!group || group->world < 1 || group->world > kTpMaxWorld || group->rank < 0 ||
+        group->rank >= group->world || n_offset < 0)
+        return b2w4_fail(ctx, B2W4_E_INVALID, "%s: bad group", who);
+    *tp = b2w4_tp_args();
+    for (int p = 0; p < group->world; ++p) {
+        if (!group->stage_peers[p] || (reinterpret_cast<uintptr_t>(group->stage_peers[p]) & 7))
+            return b2w4_fail(ctx, B2W4_E_INVALID, "%s: null or unaligned peer pointer", who);
+        tp->stage_peer[p] = static_cast<unsigned long long*>(group->stage_peers[p]);
+    }
+    tp->world = group->world;
+    tp->rank = group->rank;
+    tp->n_offset = n_offset;
+    return B2W4_OK;
+}
+
+int b2w4_matmul_argmax_tp(b2w4_ctx* ctx, const b2w4_weight* w, const float* x_dev, int lda,
+                          int m, int n_offset, const b2w4_tp_group* group) {
+    if (!ctx)
+        return B2W4_E_INVALID;
+    if (!w || !x_dev || m < 1 || m > kTop1MaxRows || lda < w->k)
+        return b2w4_fail(ctx, B2W4_E_INVALID, "matmul_argmax_tp: bad argument (1..%d rows)",
+                         kTop1MaxRows);
+    b2w4_tp_args tp;
+    int rc = tp_args_from_group(ctx, group, n_offset, &tp, "matmul_argmax_tp");
+    if (rc != B2W4_OK)
+        return rc;
+    b2w4_top1_args top1;
+    top1.cells = reinterpret_cast<unsigned long long*>(ctx->flag_dev + 16);
+    top1.done = reinterpret_cast<unsigned*>(ctx->flag_dev + 7);
+    top1.token = nullptr;
+    return b2w4_launch_gemv(ctx, w, x_dev, lda, nullptr, 0, m, B2W4_ACT_G128, B2W4_NONE, 0, -1,
+                            nullptr, &tp, &top1);
+}
+
+int b2w4_tp_gather_token(b2w4_ctx* ctx, const b2w4_tp_group* group, int32_t* token_dev, int m) {
+    if (!ctx)
+        return B2W4_E_INVALID;
+    if (!token_dev || m < 1 || m > kTop1MaxRows)
+        return b2w4_fail(ctx, B2W4_E_INVALID, "tp_gather_token: bad argument");
+    b2w4_tp_args tp;
+    int rc = tp_args_from_group(ctx, group, 0, &tp, "tp_gather_token");
+    if (rc != B2W4_OK)
+        return rc;
+    return b2w4_launch_tp_gather_token(ctx, tp.stage_peer[tp.rank], token_dev, m, tp.world);
+}
+
 int b2w4_tp_gather(b2w4_ctx* ctx, const b2w4_tp_group* group, float* y_dev, int m, int ldc) {
     if (!ctx)
         return B2W4_E_INVALID;

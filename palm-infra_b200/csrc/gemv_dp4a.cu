@@ -358,7 +358,8 @@ gemv_w4a8_kernel(const GemvArgs a) {
             if (b2w4_act_applies(n, a.activation, a.act_n_begin, a.act_n_len, a.n))
                 acc = gemv_activation(acc, a.activation);
             if (MODE == kModeTop1) {
-                const unsigned long long word = b2w4_top1_word(acc, n);
+                // the index is the row of the unsharded weight (n_offset is 0 on one GPU)
+                const unsigned long long word = b2w4_top1_word(acc, a.tp.n_offset + n);
                 top1_best = word > top1_best ? word : top1_best;
                 if (a.y)
                     a.y[(size_t)mi * a.ldc + n] = acc;
@@ -382,7 +383,7 @@ gemv_w4a8_kernel(const GemvArgs a) {
         }
     }
     if (MODE == kModeTop1)
-        b2w4_top1_finish(a.top1, top1_best, (threadIdx.x >> 3) % MT, a.m, s_top1);
+        b2w4_top1_finish(a.top1, a.tp, top1_best, (threadIdx.x >> 3) % MT, a.m, s_top1);
 }
 
 // Second half of the tensor-parallel exchange: waits (bounded) until every entry of the
@@ -417,6 +418,41 @@ tp_gather_kernel(unsigned long long* stage, float* y, int m, int ldc, unsigned* 
         *done = 0;  // ready for the next launch
         *count = exchange;
     }
+}
+
+// Second half of the tensor-parallel greedy token: thread (row r, rank p) waits (bounded) for
+// rank p's maximum word of row r, the block takes the largest per row -- the words carry
+// indices of the unsharded weight, so the order is the one-GPU order -- and advances the count.
+__global__ void __launch_bounds__(kTop1MaxRows* kTpMaxWorld)
+tp_gather_token_kernel(unsigned long long* stage, int32_t* token, int m, int world, int* status) {
+    b2w4_pdl_chain_entry();
+    __shared__ unsigned long long s_best[kTop1MaxRows];
+    unsigned* count = reinterpret_cast<unsigned*>(stage);
+    const unsigned exchange = *reinterpret_cast<volatile unsigned*>(count) + 1u;
+    const int r = threadIdx.x / kTpMaxWorld, p = threadIdx.x % kTpMaxWorld;
+    if (threadIdx.x < kTop1MaxRows)
+        s_best[threadIdx.x] = 0ull;
+    __syncthreads();
+    if (r < m && p < world) {
+        const volatile unsigned long long* src =
+            stage + kTpStageHeader + (size_t)(exchange & 1) * kTop1StageHalf +
+            ((size_t)r * kTpMaxWorld + p) * 2;
+        const unsigned long long t0 = wait_clock();
+        unsigned long long hi = src[0], lo = src[1];
+        while ((unsigned)(hi >> 32) != exchange || (unsigned)(lo >> 32) != exchange) {
+            if (wait_clock() - t0 > kTpWaitLimitCycles) {
+                atomicExch(status, B2W4_E_TIMEOUT);
+                break;
+            }
+            hi = src[0], lo = src[1];
+        }
+        atomicMax(&s_best[r], (hi << 32) | (lo & 0xFFFFFFFFull));
+    }
+    __syncthreads();
+    if ((int)threadIdx.x < m)
+        token[threadIdx.x] = (int32_t)(0xFFFFFFFFu - (unsigned)s_best[threadIdx.x]);
+    if (threadIdx.x == 0)
+        *count = exchange;
 }
 
 int gemv_d_stride(int mt, int groups, bool a32) {
@@ -546,6 +582,15 @@ int b2w4_launch_gemv(b2w4_ctx* ctx, const b2w4_weight* w, const float* x, int ld
         if (rc != B2W4_OK)
             return rc;
     }
+    return B2W4_OK;
+}
+
+int b2w4_launch_tp_gather_token(b2w4_ctx* ctx, unsigned long long* stage_local, int32_t* token,
+                                int m, int world) {
+    B2W4_CUDA(ctx, b2w4_launch_chained(ctx->pdl, tp_gather_token_kernel, dim3(1),
+                                       dim3(kTop1MaxRows * kTpMaxWorld), 0, ctx->stream,
+                                       stage_local, token, m, world, ctx->flag_dev + 1));
+    ctx->launches++;
     return B2W4_OK;
 }
 

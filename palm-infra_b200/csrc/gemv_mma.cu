@@ -324,7 +324,8 @@ gemv_w4a8_mma_kernel(const MmaArgs a) {
             if (b2w4_act_applies(n, a.activation, a.act_n_begin, a.act_n_len, a.n))
                 acc = mma_gemv_activation(acc, a.activation);
             if (MODE == kModeTop1) {
-                const unsigned long long word = b2w4_top1_word(acc, n);
+                // the index is the row of the unsharded weight (n_offset is 0 on one GPU)
+                const unsigned long long word = b2w4_top1_word(acc, a.tp.n_offset + n);
                 top1_best = word > top1_best ? word : top1_best;
                 if (a.y)
                     a.y[(size_t)mi * a.ldc + n] = acc;
@@ -346,7 +347,7 @@ gemv_w4a8_mma_kernel(const MmaArgs a) {
     }
     // kThreads / 8 is a multiple of MT: a thread's activation row is the same in every pass
     if (MODE == kModeTop1)
-        b2w4_top1_finish(a.top1, top1_best, (threadIdx.x >> 3) % MT, a.m, s_top1);
+        b2w4_top1_finish(a.top1, a.tp, top1_best, (threadIdx.x >> 3) % MT, a.m, s_top1);
 }
 
 int mma_d_stride(int mt, int groups, bool a32) {

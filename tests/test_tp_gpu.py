@@ -140,3 +140,60 @@ def test_bad_arguments_are_refused():
     with pytest.raises(pkg.capi.B200W4Error):
         ctx.tp_gather(empty, row, n)
     ctx.close()
+
+
+@pytest.mark.parametrize("world,n,k,m,same_tiles", [(1, 256, 256, 1, False),
+                                                     (2, 1024, 512, 1, False),
+                                                     (4, 2048, 640, 3, False),
+                                                     (8, 151936, 2560, 2, False),
+                                                     (2, 4800, 512, 1, True),
+                                                     (8, 4096, 256, 8, True)])
+def test_tensor_parallel_greedy_token(world, n, k, m, same_tiles):
+    """b2w4_matmul_argmax_tp + b2w4_tp_gather_token: every rank ends with the token that
+    argmax_token picks over the oracle's full logits; with a weight made of one repeated
+    8-row tile the equal maxima sit on different ranks and the lowest index must win."""
+    import torch
+    if same_tiles:
+        blocks = np.tile(pkg.synth.bg128_weight(15, 1, 8, k), n // 8)
+    else:
+        blocks = pkg.synth.bg128_weight(15, 2, n, k)
+    ctxs, stages, groups = _ranks(world, n)
+    shards = []
+    for r in range(world):
+        sh, n_local, lo = pkg.shard.shard_blocks(blocks, n, k, r, world)
+        shards.append((ctxs[r].upload_weight(np.ascontiguousarray(sh), n_local, k), lo))
+    toks = [torch.full((m,), -1, dtype=torch.int32, device="cuda") for _ in range(world)]
+    for it in range(3):
+        x = pkg.synth.activations(60 + it, 0, m, k)
+        xd = torch.from_numpy(x).cuda()
+        ref = ol.matmul_w4(blocks, n, k, x, rule=ol.ACT_G128)
+        want = [ol.argmax_token(ref[i]) for i in range(m)]
+        if same_tiles:
+            assert all(t < 8 for t in want)
+        for r in range(world):
+            ctxs[r].matmul_argmax_tp(shards[r][0], xd, shards[r][1], groups[r])
+        for r in range(world):
+            ctxs[r].tp_gather_token(groups[r], toks[r])
+        for r in range(world):
+            ctxs[r].sync()
+            assert toks[r].cpu().tolist() == want, (it, r)
+            assert int(stages[r][0].item()) == it + 1
+    for c in ctxs:
+        c.close()
+
+
+def test_token_gather_with_a_silent_peer_times_out():
+    import torch
+    n, k = 256, 256
+    blocks = pkg.synth.bg128_weight(16, 1, n, k)
+    ctxs, stages, groups = _ranks(2, n)
+    sh, n_local, lo = pkg.shard.shard_blocks(blocks, n, k, 0, 2)
+    w = ctxs[0].upload_weight(np.ascontiguousarray(sh), n_local, k)
+    tok = torch.zeros((1,), dtype=torch.int32, device="cuda")
+    ctxs[0].matmul_argmax_tp(w, torch.from_numpy(pkg.synth.activations(6, 0, 1, k)).cuda(), lo,
+                             groups[0])
+    ctxs[0].tp_gather_token(groups[0], tok)
+    with pytest.raises(pkg.capi.B200W4Error):
+        ctxs[0].sync()
+    for c in ctxs:
+        c.close()
