@@ -332,6 +332,59 @@ def moe_layer_ep(torch, dist, pkg, ctx, rank, world):
     return out
 
 
+def lm_head_greedy_tp(torch, dist, pkg, ctx, rank, world):
+    """Greedy token at a Qwen3-4B lm_head [151936, 2560] sharded by rows over `world` ranks:
+    every rank streams its shard, keeps one (maximum, index) pair, the pairs cross as tagged
+    words and a small kernel picks the token on every rank.  Device time, max over ranks,
+    8 weight copies per rank so that the weight comes from HBM."""
+    import torch.distributed._symmetric_memory as symm
+    vocab, k, copies = 151936, 2560, 8
+    if vocab % (8 * world):
+        return {"skipped": f"{vocab} rows do not split into 8-row tiles over {world} ranks"}
+    one = pkg.synth.bg128_weight(SEED_W, 60, vocab, k)
+    shard, n_local, lo = pkg.shard.shard_blocks(one, vocab, k, rank, world)
+    ws = [ctx.upload_weight(np.roll(shard, 544 * i), n_local, k) for i in range(copies)]
+    x = torch.from_numpy(pkg.synth.activations(SEED_X, 61, 1, k)).cuda()
+    stage = symm.empty((2 + 256,), dtype=torch.int64, device=f"cuda:{torch.cuda.current_device()}")
+    stage.zero_()
+    torch.cuda.synchronize()
+    hs = symm.rendezvous(stage, dist.group.WORLD.group_name)
+    group = pkg.capi.TpGroup()
+    group.rank, group.world = rank, world
+    for p_ in range(world):
+        group.stage_peers[p_] = hs.buffer_ptrs[p_]
+    tok = torch.full((1,), -1, dtype=torch.int32, device="cuda")
+    dist.barrier()
+
+    def eager():
+        for w in ws:
+            ctx.matmul_argmax_tp(w, x, lo, group)
+            ctx.tp_gather_token(group, tok)
+    eager()
+    ctx.sync()
+    torch.cuda.synchronize()
+    # every rank must hold the same token (the weight copies differ, the last one counts)
+    toks = [torch.zeros_like(tok) for _ in range(world)]
+    dist.all_gather(toks, tok)
+    same = all(int(t.item()) == int(toks[0].item()) for t in toks)
+    g = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        ctx.set_stream(side.cuda_stream)
+        with torch.cuda.graph(g, stream=side):
+            eager()
+    ctx.set_stream(torch.cuda.current_stream().cuda_stream)
+    ms = time_steps(torch, g.replay, 10, 3, lambda: dist.barrier())
+    tm = torch.tensor([ms], device="cuda", dtype=torch.float64)
+    dist.all_reduce(tm, op=dist.ReduceOp.MAX)
+    us = float(tm.item()) * 1e3 / copies
+    lm_head_greedy_tp.keep = (stage, hs, group)
+    for w in ws:
+        w.free()
+    return {"us_per_token": us, "gbs": algorithmic_bytes(vocab, k, 1) / us / 1e3,
+            "ranks_agree": same, "token": int(toks[0].item())}
+
+
 def decode_walk(torch, pkg, ctx, args):
     """The W4 matmuls of one decode token of a Qwen3-4B-shaped dense decoder (benchmark
     configuration 3): 36 layers of qkv [6144,2560], o [2560,4096], gate_up [19456,2560],
@@ -662,6 +715,11 @@ def run_ours(args):
     if world > 1 and not args.headline_only and 128 % world == 0:
         ep = moe_layer_ep(torch, dist, pkg, ctx, rank, world)  # every rank takes part
         line["moe30b_layer_ep"] = ep
+    if world > 1 and not args.headline_only:
+        try:
+            line["lm_head_greedy_token_tp"] = lm_head_greedy_tp(torch, dist, pkg, ctx, rank, world)
+        except Exception as exc:  # no symmetric memory on this box
+            line["lm_head_greedy_token_tp"] = {"skipped": str(exc)[:200]}
 
     if rank == 0:
         print(json.dumps(line), flush=True)

@@ -97,16 +97,16 @@ struct b2w4_tp_args {
 // every i with logits[i] > logits[best] takes over -- the first maximum wins, a NaN never
 // wins unless it sits at index 0, where nothing can beat it).  Each output becomes the 64-bit
 // word (order-preserving key of the value << 32 | ~index); the maximum word over a row is its
-// token.  cells[8]: one word per activation row, zero between launches (the launch's last CTA
-// reads and clears them); done: CTA counter of the launch, zero between launches.
+// token.  cells[8]: one word per activation row, zero between uses: every CTA of the matmul
+// folds its maximum in with one fire-and-forget atomic per row and exits -- no fence, no
+// counter, so the epilogue adds no latency to a CTA -- and the small kernel that follows in
+// the stream reads the cells, clears them and writes the tokens.
 constexpr int kTop1MaxRows = 8;
 // Tensor-parallel form: every rank's (row, rank) maximum goes to every rank's staging buffer
 // as two tagged words (key, ~global index); half = rows * ranks * 2 words.
 constexpr int kTop1StageHalf = kTop1MaxRows * kTpMaxWorld * 2;
 struct b2w4_top1_args {
     unsigned long long* cells;
-    unsigned* done;
-    int32_t* token;  // [m] result
 };
 #ifdef __CUDACC__
 __device__ __forceinline__ unsigned long long b2w4_top1_word(float v, int n) {
@@ -122,9 +122,8 @@ __device__ __forceinline__ unsigned long long b2w4_top1_word(float v, int n) {
 }
 // After the output loop, every thread of the CTA: `best` is the thread's maximum word for
 // activation row mi (the 8 lanes of a group share mi), s_top1[8] was zeroed at kernel start.
-__device__ __forceinline__ void b2w4_top1_finish(const b2w4_top1_args& t, const b2w4_tp_args& tp,
-                                                 unsigned long long best, int mi, int m,
-                                                 unsigned long long* s_top1) {
+__device__ __forceinline__ void b2w4_top1_finish(const b2w4_top1_args& t, unsigned long long best,
+                                                 int mi, int m, unsigned long long* s_top1) {
 #pragma unroll
     for (int o = 1; o <= 4; o <<= 1) {
         const unsigned long long other = __shfl_xor_sync(0xFFFFFFFFu, best, o);
@@ -133,38 +132,8 @@ __device__ __forceinline__ void b2w4_top1_finish(const b2w4_top1_args& t, const 
     if ((threadIdx.x & 7) == 0 && mi < m)
         atomicMax(&s_top1[mi], best);
     __syncthreads();
-    if ((int)threadIdx.x < m) {
+    if ((int)threadIdx.x < m)
         atomicMax(t.cells + threadIdx.x, s_top1[threadIdx.x]);
-        __threadfence();
-    }
-    __syncthreads();
-    if (threadIdx.x != 0)
-        return;
-    if (atomicAdd(t.done, 1u) != gridDim.x - 1)
-        return;
-    __threadfence();  // the last CTA: every CTA's maximum is in the cells
-    unsigned long long tag = 0;
-    size_t at = 0;
-    if (tp.world != 0) {
-        const unsigned exchange =
-            *reinterpret_cast<const volatile unsigned*>(tp.stage_peer[tp.rank]) + 1u;
-        tag = (unsigned long long)exchange << 32;
-        at = kTpStageHeader + (size_t)(exchange & 1) * kTop1StageHalf;
-    }
-    for (int r = 0; r < m; ++r) {
-        const unsigned long long w = atomicExch(t.cells + r, 0ull);  // read and clear
-        if (tp.world == 0) {
-            t.token[r] = (int32_t)(0xFFFFFFFFu - (unsigned)w);
-        } else {
-            // this rank's maximum of row r, to every rank: two tagged words
-            const size_t slot = at + ((size_t)r * kTpMaxWorld + tp.rank) * 2;
-            for (int p = 0; p < tp.world; ++p) {
-                tp.stage_peer[p][slot] = tag | (w >> 32);
-                tp.stage_peer[p][slot + 1] = tag | (w & 0xFFFFFFFFull);
-            }
-        }
-    }
-    *t.done = 0;
 }
 #endif
 
@@ -175,6 +144,9 @@ int b2w4_launch_gemv(b2w4_ctx* ctx, const b2w4_weight* w, const float* x, int ld
                      const b2w4_tp_args* tp = nullptr, const b2w4_top1_args* top1 = nullptr);
 int b2w4_launch_tp_gather(b2w4_ctx* ctx, unsigned long long* stage_local, float* y, int m,
                           int ldc);
+int b2w4_launch_top1_token(b2w4_ctx* ctx, unsigned long long* cells, int32_t* token, int m);
+int b2w4_launch_tp_send_token(b2w4_ctx* ctx, unsigned long long* cells, const b2w4_tp_args& tp,
+                              int m);
 int b2w4_launch_tp_gather_token(b2w4_ctx* ctx, unsigned long long* stage_local, int32_t* token,
                                 int m, int world);
 // 2..8 activation rows per pass on the int8 tensor instruction (gemv_mma.cu)

@@ -340,6 +340,11 @@ int b2w4_matmul_tp(b2w4_ctx* ctx, const b2w4_weight* w, const float* x_dev, int 
                             act_n_begin, act_n_len, nullptr, &tp);
 }
 
+// One word per activation row for the fused greedy token (zero between uses).
+static unsigned long long* top1_cells(b2w4_ctx* ctx) {
+    return reinterpret_cast<unsigned long long*>(ctx->flag_dev + 16);
+}
+
 int b2w4_matmul_argmax(b2w4_ctx* ctx, const b2w4_weight* w, const float* x_dev, int lda, int m,
                        float* y_dev, int ldc, int32_t* token_dev) {
     if (!ctx)
@@ -349,11 +354,12 @@ int b2w4_matmul_argmax(b2w4_ctx* ctx, const b2w4_weight* w, const float* x_dev, 
         return b2w4_fail(ctx, B2W4_E_INVALID, "matmul_argmax: bad argument (1..%d rows)",
                          kTop1MaxRows);
     b2w4_top1_args top1;
-    top1.cells = reinterpret_cast<unsigned long long*>(ctx->flag_dev + 16);  // 8 words
-    top1.done = reinterpret_cast<unsigned*>(ctx->flag_dev + 7);
-    top1.token = token_dev;
-    return b2w4_launch_gemv(ctx, w, x_dev, lda, y_dev, ldc, m, B2W4_ACT_G128, B2W4_NONE, 0, -1,
-                            nullptr, nullptr, &top1);
+    top1.cells = top1_cells(ctx);
+    int rc = b2w4_launch_gemv(ctx, w, x_dev, lda, y_dev, ldc, m, B2W4_ACT_G128, B2W4_NONE, 0, -1,
+                              nullptr, nullptr, &top1);
+    if (rc != B2W4_OK)
+        return rc;
+    return b2w4_launch_top1_token(ctx, top1.cells, token_dev, m);
 }
 
 static int tp_args_from_group(b2w4_ctx* ctx, const b2w4_tp_group* group, int n_offset,
@@ -384,12 +390,15 @@ int b2w4_matmul_argmax_tp(b2w4_ctx* ctx, const b2w4_weight* w, const float* x_de
     int rc = tp_args_from_group(ctx, group, n_offset, &tp, "matmul_argmax_tp");
     if (rc != B2W4_OK)
         return rc;
+    b2w4_tp_args offset_only = b2w4_tp_args();  // the matmul only needs n_offset
+    offset_only.n_offset = n_offset;
     b2w4_top1_args top1;
-    top1.cells = reinterpret_cast<unsigned long long*>(ctx->flag_dev + 16);
-    top1.done = reinterpret_cast<unsigned*>(ctx->flag_dev + 7);
-    top1.token = nullptr;
-    return b2w4_launch_gemv(ctx, w, x_dev, lda, nullptr, 0, m, B2W4_ACT_G128, B2W4_NONE, 0, -1,
-                            nullptr, &tp, &top1);
+    top1.cells = top1_cells(ctx);
+    rc = b2w4_launch_gemv(ctx, w, x_dev, lda, nullptr, 0, m, B2W4_ACT_G128, B2W4_NONE, 0, -1,
+                          nullptr, &offset_only, &top1);
+    if (rc != B2W4_OK)
+        return rc;
+    return b2w4_launch_tp_send_token(ctx, top1.cells, tp, m);
 }
 
 int b2w4_tp_gather_token(b2w4_ctx* ctx, const b2w4_tp_group* group, int32_t* token_dev, int m) {

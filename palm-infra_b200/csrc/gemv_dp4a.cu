@@ -383,7 +383,7 @@ gemv_w4a8_kernel(const GemvArgs a) {
         }
     }
     if (MODE == kModeTop1)
-        b2w4_top1_finish(a.top1, a.tp, top1_best, (threadIdx.x >> 3) % MT, a.m, s_top1);
+        b2w4_top1_finish(a.top1, top1_best, (threadIdx.x >> 3) % MT, a.m, s_top1);
 }
 
 // Second half of the tensor-parallel exchange: waits (bounded) until every entry of the
@@ -420,9 +420,40 @@ tp_gather_kernel(unsigned long long* stage, float* y, int m, int ldc, unsigned* 
     }
 }
 
-// Second half of the tensor-parallel greedy token: thread (row r, rank p) waits (bounded) for
-// rank p's maximum word of row r, the block takes the largest per row -- the words carry
-// indices of the unsharded weight, so the order is the one-GPU order -- and advances the count.
+// Second half of the fused greedy token on one GPU: the matmul before it in the stream left
+// each row's maximum word in the cells; write the tokens and clear the cells.
+__global__ void top1_token_kernel(unsigned long long* cells, int32_t* token, int m) {
+    b2w4_pdl_chain_entry();
+    if ((int)threadIdx.x < m) {
+        const unsigned long long w = atomicExch(cells + threadIdx.x, 0ull);
+        token[threadIdx.x] = (int32_t)(0xFFFFFFFFu - (unsigned)w);
+    }
+}
+
+// Tensor-parallel greedy token, hand-over: this rank's maximum word of every row (left in the
+// cells by the matmul, with indices of the unsharded weight) goes to every rank as two tagged
+// words; the cells are cleared.  Thread (row r, rank q) stores to rank q.
+__global__ void __launch_bounds__(kTop1MaxRows* kTpMaxWorld)
+tp_send_token_kernel(unsigned long long* cells, const b2w4_tp_args tp, int m) {
+    b2w4_pdl_chain_entry();
+    __shared__ unsigned long long s_word[kTop1MaxRows];
+    if ((int)threadIdx.x < m)
+        s_word[threadIdx.x] = atomicExch(cells + threadIdx.x, 0ull);  // read and clear
+    __syncthreads();
+    const unsigned exchange =
+        *reinterpret_cast<const volatile unsigned*>(tp.stage_peer[tp.rank]) + 1u;
+    const unsigned long long tag = (unsigned long long)exchange << 32;
+    const int r = threadIdx.x / kTpMaxWorld, q = threadIdx.x % kTpMaxWorld;
+    if (r < m && q < tp.world) {
+        const size_t slot = kTpStageHeader + (size_t)(exchange & 1) * kTop1StageHalf +
+                            ((size_t)r * kTpMaxWorld + tp.rank) * 2;
+        tp.stage_peer[q][slot] = tag | (s_word[r] >> 32);
+        tp.stage_peer[q][slot + 1] = tag | (s_word[r] & 0xFFFFFFFFull);
+    }
+}
+
+// ... and the pick: thread (row r, rank p) waits (bounded) for rank p's words of row r, the
+// block takes the largest per row -- the one-GPU order -- and advances the count.
 __global__ void __launch_bounds__(kTop1MaxRows* kTpMaxWorld)
 tp_gather_token_kernel(unsigned long long* stage, int32_t* token, int m, int world, int* status) {
     b2w4_pdl_chain_entry();
@@ -582,6 +613,22 @@ int b2w4_launch_gemv(b2w4_ctx* ctx, const b2w4_weight* w, const float* x, int ld
         if (rc != B2W4_OK)
             return rc;
     }
+    return B2W4_OK;
+}
+
+int b2w4_launch_top1_token(b2w4_ctx* ctx, unsigned long long* cells, int32_t* token, int m) {
+    B2W4_CUDA(ctx, b2w4_launch_chained(ctx->pdl, top1_token_kernel, dim3(1), dim3(32), 0,
+                                       ctx->stream, cells, token, m));
+    ctx->launches++;
+    return B2W4_OK;
+}
+
+int b2w4_launch_tp_send_token(b2w4_ctx* ctx, unsigned long long* cells, const b2w4_tp_args& tp,
+                              int m) {
+    B2W4_CUDA(ctx, b2w4_launch_chained(ctx->pdl, tp_send_token_kernel, dim3(1),
+                                       dim3(kTop1MaxRows * kTpMaxWorld), 0, ctx->stream, cells,
+                                       tp, m));
+    ctx->launches++;
     return B2W4_OK;
 }
 

@@ -347,7 +347,7 @@ gemv_w4a8_mma_kernel(const MmaArgs a) {
     }
     // kThreads / 8 is a multiple of MT: a thread's activation row is the same in every pass
     if (MODE == kModeTop1)
-        b2w4_top1_finish(a.top1, a.tp, top1_best, (threadIdx.x >> 3) % MT, a.m, s_top1);
+        b2w4_top1_finish(a.top1, top1_best, (threadIdx.x >> 3) % MT, a.m, s_top1);
 }
 
 int mma_d_stride(int mt, int groups, bool a32) {
