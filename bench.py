@@ -550,8 +550,9 @@ def run_ours(args):
         group.rank, group.world = rank, world
         for p_ in range(world):
             group.stage_peers[p_] = hs.buffer_ptrs[p_]
-        x, y_local, y_full = make_io(1)
-        y_row = torch.zeros((1, N_OUT), dtype=torch.float32, device="cuda")
+        m = args.rows
+        x, y_local, y_full = make_io(m)
+        y_row = torch.zeros((m, N_OUT), dtype=torch.float32, device="cuda")
         dist.barrier()
         # eagerly, twice (both halves of the staging buffer): the gathered row must equal the
         # NCCL all-gather of the shards, bit for bit
@@ -563,7 +564,7 @@ def run_ours(args):
             ctx.tp_gather(group, y_row, N_OUT)
             ctx.sync()
             torch.cuda.synchronize()
-            same = same and torch.equal(y_full.permute(1, 0, 2).reshape(1, N_OUT), y_row)
+            same = same and torch.equal(y_full.permute(1, 0, 2).reshape(m, N_OUT), y_row)
         if not all_ranks_agree(same):  # never time a path whose result differs
             print("in-kernel exchange and all-gather disagree: not used", file=sys.stderr)
             return None
@@ -613,7 +614,7 @@ def run_ours(args):
     ms = max_over_ranks(ms)
     exchange = "none (one GPU)" if world == 1 else "NCCL all-gather after every GEMV"
     nccl_ms = None
-    if world > 1 and args.rows == 1 and not args.no_graph and world <= 8:
+    if world > 1 and args.rows <= 8 and not args.no_graph and world <= 8:
         peer_step = make_peer_step()
         if peer_step is not None:
             nccl_ms = ms
