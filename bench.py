@@ -303,8 +303,12 @@ def moe_layer_ep(torch, dist, pkg, ctx, rank, world):
     same = True
     for _ in range(3):  # both halves of the staging buffer; bit for bit the all-reduce result
         op.forward(x, y)
-        peer.forward(x, y2)
-        ctx.sync()
+        try:
+            peer.forward(x, y2)
+            ctx.sync()
+        except pkg.capi.B200W4Error as exc:  # e.g. the bounded wait ran out
+            print(f"in-kernel MoE hand-over failed: {exc}", file=sys.stderr)
+            same = False
         torch.cuda.synchronize()
         same = same and torch.equal(y, y2)
     agree = torch.tensor([1 if same else 0], device="cuda", dtype=torch.int32)
@@ -360,13 +364,22 @@ def lm_head_greedy_tp(torch, dist, pkg, ctx, rank, world):
         for w in ws:
             ctx.matmul_argmax_tp(w, x, lo, group)
             ctx.tp_gather_token(group, tok)
-    eager()
-    ctx.sync()
+    ok = True
+    try:
+        eager()
+        ctx.sync()
+    except pkg.capi.B200W4Error as exc:  # e.g. the bounded wait ran out
+        print(f"tensor-parallel greedy token failed: {exc}", file=sys.stderr)
+        ok = False
     torch.cuda.synchronize()
     # every rank must hold the same token (the weight copies differ, the last one counts)
     toks = [torch.zeros_like(tok) for _ in range(world)]
-    dist.all_gather(toks, tok)
+    dist.all_gather(toks, tok if ok else torch.full_like(tok, -2 - rank))
     same = all(int(t.item()) == int(toks[0].item()) for t in toks)
+    if not same:  # the same decision on every rank: nothing is timed
+        for w in ws:
+            w.free()
+        return {"error": "ranks disagree or the exchange failed", "ranks_agree": False}
     g = torch.cuda.CUDAGraph()
     side = torch.cuda.Stream()
     with torch.cuda.stream(side):
@@ -560,9 +573,13 @@ def run_ours(args):
         for w in weights[:2]:
             ctx.matmul(w, x, y_local)
             dist.all_gather_into_tensor(y_full, y_local)
-            ctx.matmul_tp(w, x, N_OUT, rank * n_local, group)
-            ctx.tp_gather(group, y_row, N_OUT)
-            ctx.sync()
+            try:
+                ctx.matmul_tp(w, x, N_OUT, rank * n_local, group)
+                ctx.tp_gather(group, y_row, N_OUT)
+                ctx.sync()
+            except pkg.capi.B200W4Error as exc:  # e.g. the bounded wait ran out
+                print(f"in-kernel exchange failed: {exc}", file=sys.stderr)
+                same = False
             torch.cuda.synchronize()
             same = same and torch.equal(y_full.permute(1, 0, 2).reshape(m, N_OUT), y_row)
         if not all_ranks_agree(same):  # never time a path whose result differs
