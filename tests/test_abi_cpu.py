@@ -55,3 +55,19 @@ def test_synth_blocks_follow_the_canonical_layout():
     assert (s[:21] == s[:21].astype(np.float16).astype(np.float32)).all()
     assert q.min() == -8 and q.max() == 7
     assert pkg.synth.bg128_weight(5, 2, n, k).tobytes() == blocks.tobytes()
+
+
+def test_exchange_group_struct_and_null_contexts():
+    """b2w4_tp_group as the header lays it out (two ints, eight pointers), the staging sizes
+    the host helpers promise, and the exchange entry points refusing a null context."""
+    import ctypes as C
+    g = pkg.capi.TpGroup()
+    assert C.sizeof(g) == 8 + 8 * 8
+    assert pkg.capi.TpGroup.stage_peers.offset == 8
+    assert pkg.expert_parallel.PeerExchangeMoE.stage_words(8, 2048) == 2 + 2 * 8 * 2048
+    lib = pkg.capi.lib()
+    assert lib.b2w4_matmul_tp(None, None, None, 0, 1, 0, 0, None, 0, 0, -1) == -1
+    assert lib.b2w4_tp_gather(None, None, None, 1, 0) == -1
+    assert lib.b2w4_matmul_argmax(None, None, None, 0, 1, None, 0, None) == -1
+    assert lib.b2w4_matmul_argmax_tp(None, None, None, 0, 1, 0, None) == -1
+    assert lib.b2w4_tp_gather_token(None, None, None, 1) == -1
