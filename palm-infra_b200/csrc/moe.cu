@@ -663,8 +663,8 @@ __global__ void moe_scatter_routes_peers_kernel(const float* __restrict__ dn,
 __global__ void __launch_bounds__(kCombineThreads)
 moe_combine_staged_kernel(unsigned long long* stage, int stage_rows,
                           const int32_t* __restrict__ idx, const float* __restrict__ weights,
-                          int tokens, int top_k, int hidden_size, float* __restrict__ out, int ldo,
-                          unsigned* done, int* status) {
+                          const int32_t* __restrict__ pos, int tokens, int top_k, int hidden_size,
+                          float* __restrict__ out, int ldo, unsigned* done, int* status) {
     b2w4_pdl_chain_entry();
     __shared__ int s_row[kMaxTopK];
     __shared__ float s_w[kMaxTopK];
@@ -680,7 +680,9 @@ moe_combine_staged_kernel(unsigned long long* stage, int stage_rows,
             const int other = idx[(size_t)t * top_k + o];
             rank += other < key || (other == key && o < j);
         }
-        s_row[rank] = t * top_k + j;
+        // rows in compact order (stored by the down-projection itself) or in (token, route)
+        // order (stored by the scatter kernel)
+        s_row[rank] = pos ? pos[(size_t)t * top_k + j] : t * top_k + j;
         s_w[rank] = w;
     }
     __syncthreads();
@@ -756,6 +758,8 @@ struct GroupedSmallArgs {
     float* out;               // [routes][n_e]
     int* status;
     int k, groups, n_e, tiles_e, tpc, d_stride;
+    b2w4_tp_args peers;       // world != 0: rows go, tagged, to every rank's staging buffer
+    int stage_rows;           // rows per half of that buffer
 };
 
 template <bool U>
@@ -939,8 +943,27 @@ moe_grouped_small_kernel(const GroupedSmallArgs a) {
                 acc = __fmaf_rn(dsrc[g * kSR * 8], __fmul_rn(ws, as[g]), acc);
             }
             const int n = (tl0 + tl) * 8 + rr;
-            if (n < a.n_e)
-                a.out[(size_t)(base + mi) * a.n_e + n] = acc;
+            if (n < a.n_e) {
+                if (a.peers.world == 0) {
+                    a.out[(size_t)(base + mi) * a.n_e + n] = acc;
+                } else {
+                    // expert-parallel hand-over: the row (its compact position is the same
+                    // on every rank) goes to every rank's staging buffer, each value tagged
+                    // with the exchange number in one 8-byte word
+                    const unsigned exchange =
+                        *reinterpret_cast<const volatile unsigned*>(
+                            a.peers.stage_peer[a.peers.rank]) + 1u;
+                    const unsigned long long word =
+                        ((unsigned long long)exchange << 32) | __float_as_uint(acc);
+                    const size_t at = kTpStageHeader +
+                                      (size_t)(exchange & 1) * a.stage_rows * a.n_e +
+                                      (size_t)(base + mi) * a.n_e + n;
+#pragma unroll
+                    for (int p = 0; p < kTpMaxWorld; ++p)
+                        if (p < a.peers.world)
+                            a.peers.stage_peer[p][at] = word;
+                }
+            }
         }
         __syncthreads();
     }
@@ -1198,7 +1221,8 @@ size_t grouped_smem(int k, int groups, int tpc, bool scl16) {
 int launch_grouped(b2w4_ctx* ctx, const b2w4_weight* w, int num_experts_all, int expert_begin,
                    int expert_count, int routes, const int8_t* qa, const float* as,
                    const int4* slots, const int32_t* row_map, float* out, bool decode,
-                   const float* fused_gate_up = nullptr) {
+                   const float* fused_gate_up = nullptr, const b2w4_tp_args* peers = nullptr,
+                   int stage_rows = 0) {
     const int n_e = w->n / expert_count;
     const bool scl16 = w->scales_fp16 != 0;
     const int slots_y = routes < num_experts_all ? routes : num_experts_all;  // grid.y
@@ -1216,6 +1240,10 @@ int launch_grouped(b2w4_ctx* ctx, const b2w4_weight* w, int num_experts_all, int
         a.row_map = row_map;
         a.out = out;
         a.status = ctx->flag_dev + 1;
+        if (peers) {
+            a.peers = *peers;
+            a.stage_rows = stage_rows;
+        }
         a.k = w->k;
         a.groups = w->groups;
         a.n_e = n_e;
@@ -1443,9 +1471,12 @@ static int moe_run(b2w4_ctx* ctx, const float* hidden_dev, int ldx, int tokens, 
                            partial ? local_offsets + expert_count : nullptr));
         ctx->launches++;
     }
+    // decode steps hand the rows over from the down-projection's own epilogue
+    const bool fused_handover = peers != nullptr && decode;
     if ((rc = launch_grouped(ctx, down, num_experts, expert_begin, expert_count, routes, q_inter,
                              as_inter, slots, nullptr, static_cast<float*>(dn), decode,
-                             fuse_swiglu ? static_cast<const float*>(gu) : nullptr)) != B2W4_OK)
+                             fuse_swiglu ? static_cast<const float*>(gu) : nullptr,
+                             fused_handover ? peers : nullptr, stage_rows)) != B2W4_OK)
         return rc;
     if (route_out) {
         dim3 grid((hidden_size / 4 + 255) / 256, routes);
@@ -1455,19 +1486,22 @@ static int moe_run(b2w4_ctx* ctx, const float* hidden_dev, int ldx, int tokens, 
         ctx->launches++;
     }
     if (peers) {
-        dim3 sgrid((hidden_size / 4 + 255) / 256, routes);
-        B2W4_CUDA(ctx, b2w4_launch_chained(ctx->pdl, moe_scatter_routes_peers_kernel, sgrid,
-                                           dim3(256), 0, st, static_cast<const float*>(dn), idx,
-                                           pos, routes, hidden_size, expert_begin, expert_count,
-                                           stage_rows, *peers));
+        if (!fused_handover) {
+            dim3 sgrid((hidden_size / 4 + 255) / 256, routes);
+            B2W4_CUDA(ctx, b2w4_launch_chained(ctx->pdl, moe_scatter_routes_peers_kernel, sgrid,
+                                               dim3(256), 0, st, static_cast<const float*>(dn),
+                                               idx, pos, routes, hidden_size, expert_begin,
+                                               expert_count, stage_rows, *peers));
+            ctx->launches++;
+        }
         dim3 cgrid((hidden_size / 4 + kCombineThreads - 1) / kCombineThreads, tokens);
-        B2W4_CUDA(ctx, b2w4_launch_chained(ctx->pdl, moe_combine_staged_kernel, cgrid,
-                                           dim3(kCombineThreads), 0, st,
-                                           peers->stage_peer[peers->rank], stage_rows, idx, wts,
-                                           tokens, top_k, hidden_size, out_dev, ldo,
-                                           reinterpret_cast<unsigned*>(ctx->flag_dev + 6),
-                                           ctx->flag_dev + 1));
-        ctx->launches += 2;
+        B2W4_CUDA(ctx, b2w4_launch_chained(
+                           ctx->pdl, moe_combine_staged_kernel, cgrid, dim3(kCombineThreads), 0, st,
+                           peers->stage_peer[peers->rank], stage_rows, idx, wts,
+                           fused_handover ? static_cast<const int32_t*>(pos) : nullptr, tokens,
+                           top_k, hidden_size, out_dev, ldo,
+                           reinterpret_cast<unsigned*>(ctx->flag_dev + 6), ctx->flag_dev + 1));
+        ctx->launches++;
     } else if (out_dev) {
         dim3 grid((hidden_size / 4 + kCombineThreads - 1) / kCombineThreads, tokens);
         B2W4_CUDA(ctx, b2w4_launch_chained(ctx->pdl, moe_combine_kernel, grid,

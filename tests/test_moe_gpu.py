@@ -225,12 +225,15 @@ def _peer_group(rank, world, stages):
 
 
 @pytest.mark.parametrize("t,h,e,top_k,inter", [(1, 256, 8, 2, 128), (3, 128, 16, 4, 256),
-                                                 (1, 2048, 128, 8, 768)])
+                                                 (1, 2048, 128, 8, 768), (4, 256, 32, 8, 128),
+                                                 (6, 128, 16, 4, 256), (33, 256, 8, 2, 128)])
 def test_hand_over_inside_the_kernels_one_rank(ctx, t, h, e, top_k, inter):
     """b2w4_moe_forward_ep with a group of one (this rank owns every expert): the staged
     scatter + combine give b2w4_moe_forward's output bit for bit, over both halves of the
-    staging buffer and their reuse.  (More ranks need more GPUs: one call both stores and
-    waits, so ranks cannot be queued one after another on one device.)"""
+    staging buffer and their reuse; up to four tokens the rows are stored by the
+    down-projection's own epilogue, beyond that by a scatter kernel.  (More ranks need more
+    GPUs: one call both stores and waits, so ranks cannot be queued one after another on one
+    device.)"""
     import torch
     ep = pkg.expert_parallel
     hidden = pkg.synth.activations(7, 500 + t, t, h)
