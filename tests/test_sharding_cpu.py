@@ -123,3 +123,64 @@ def test_expert_shard_ranges():
     assert [(p[1], p[2]) for p in parts] == [(0, 2), (2, 2)]
     with pytest.raises(ValueError):
         ep.shard_expert_blocks(blocks, 4, 12, 128, 0, 2)
+
+
+def _token_rows():
+    rng = np.random.default_rng(91)
+    plain = rng.standard_normal(64).astype(np.float32)
+    ties = np.zeros(64, dtype=np.float32)
+    ties[[13, 40, 63]] = 2.5                       # equal maxima on both ranks of a world of 2
+    zeros = np.full(64, -3.0, dtype=np.float32)
+    zeros[50], zeros[20] = 0.0, -0.0               # -0 on rank 0 ties +0 on rank 1
+    nan0 = rng.standard_normal(64).astype(np.float32)
+    nan0[0] = np.nan                               # nothing beats a NaN at index 0
+    nans = rng.standard_normal(64).astype(np.float32)
+    nans[[5, 32, 33]] = np.nan                     # a NaN elsewhere never wins
+    ninf = np.full(64, -np.inf, dtype=np.float32)
+    ninf[32] = np.nan                              # first row of rank 1 is a NaN: not index 0
+    return [plain, ties, zeros, nan0, nans, ninf]
+
+
+def test_top1_words_order_like_argmax_token():
+    """One rank: the largest word of a row is the oracle's argmax_token, corner cases
+    included; shards of any split give the same token through pick_token."""
+    for row in _token_rows():
+        want = ol.argmax_token(row)
+        assert pkg.shard.pick_token([pkg.shard.shard_top1_word(row, 0)]) == want
+        for world in (2, 4, 8):
+            per = len(row) // world
+            words = [pkg.shard.shard_top1_word(row[r * per:(r + 1) * per], r * per)
+                     for r in range(world)]
+            assert pkg.shard.pick_token(words) == want, world
+
+
+def _token_worker(rank, world, port, out_dir):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    blocks = pkg.synth.bg128_weight(8, 1, N, K)
+    x = pkg.synth.activations(9, 1, M, K)
+    mine, rows, lo = pkg.shard.shard_blocks(blocks, N, K, rank, world)
+    y_local = ol.matmul_w4(np.ascontiguousarray(mine), rows, K, x)
+    tokens = []
+    for m in range(M):  # each rank hands over one word per activation row
+        word = pkg.shard.shard_top1_word(y_local[m], lo)
+        mine_t = torch.tensor([word >> 32, word & 0xFFFFFFFF], dtype=torch.int64)
+        parts = [torch.zeros_like(mine_t) for _ in range(world)]
+        dist.all_gather(parts, mine_t)
+        tokens.append(pkg.shard.pick_token([(int(p[0]) << 32) | int(p[1]) for p in parts]))
+    np.save(os.path.join(out_dir, f"tok{rank}.npy"), np.array(tokens))
+    dist.destroy_process_group()
+
+
+def test_row_sharded_greedy_token_world2(tmp_path):
+    """Two gloo ranks, the oracle standing in for the device matmul: every rank ends with the
+    token argmax_token picks over the unsharded logits."""
+    port = 29500 + (os.getpid() + 7) % 2000
+    mp.spawn(_token_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    blocks = pkg.synth.bg128_weight(8, 1, N, K)
+    x = pkg.synth.activations(9, 1, M, K)
+    full = ol.matmul_w4(blocks, N, K, x)
+    want = [ol.argmax_token(full[m]) for m in range(M)]
+    for rank in range(2):
+        assert np.load(tmp_path / f"tok{rank}.npy").tolist() == want
