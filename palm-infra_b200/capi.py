@@ -22,7 +22,8 @@ SYMBOLS = [
     "b2w4_matmul_static_scratch",
     "b2w4_debug_group_sums", "b2w4_quantize_activations", "b2w4_moe_forward",
     "b2w4_moe_select_routes", "b2w4_moe_expert_outputs", "b2w4_moe_combine",
-    "b2w4_matmul_tp", "b2w4_tp_gather", "b2w4_moe_forward_ep", "b2w4_matmul_argmax", "b2w4_matmul_argmax_tp", "b2w4_tp_gather_token",
+    "b2w4_matmul_tp", "b2w4_tp_gather", "b2w4_moe_forward_ep", "b2w4_matmul_argmax",
+    "b2w4_matmul_argmax_tp", "b2w4_tp_gather_token",
     "b2w4_kernel_launches",
 ]
 
