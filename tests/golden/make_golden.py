@@ -144,6 +144,25 @@ def main():
     out["moe_small/out_ref_w4a32"] = ol.ref_moe(hidden, router, top_k, inter, gu, dn)
     out["moe_small/meta"] = np.array([t, h, e_cnt, top_k, inter], dtype=np.int32)
 
+    # greedy token: the reference's own sampling entry at temperature 0 (argmax_token) on
+    # rows with equal maxima, signed zeros, NaNs (first, elsewhere), infinities
+    rng = np.random.default_rng(77)
+    rows = [rng.standard_normal(n).astype(np.float32) for n in (1, 2, 3, 5, 8, 100, 4097)]
+    tie = np.zeros(64, dtype=np.float32)
+    tie[[9, 17, 40]] = 3.5
+    neg0 = np.full(16, -1.0, dtype=np.float32)
+    neg0[5], neg0[11] = -0.0, 0.0
+    nan_mid = rng.standard_normal(40).astype(np.float32)
+    nan_mid[[3, 20]] = np.nan
+    nan_mid[30] = 10.0
+    nan_first = rng.standard_normal(40).astype(np.float32)
+    nan_first[0] = np.nan
+    infs = np.array([-np.inf, np.nan, -np.inf, np.inf, np.inf], dtype=np.float32)
+    rows += [tie, neg0, nan_mid, nan_first, infs, np.full(9, -np.inf, dtype=np.float32)]
+    for i, row in enumerate(rows):
+        out[f"greedy_token/row{i}"] = row
+    out["greedy_token/tokens"] = np.array([ol.ref_greedy_token(r) for r in rows], dtype=np.int32)
+
     path = os.path.join(HERE, "reference_vectors.npz")
     np.savez_compressed(path, **out)
     print("wrote", path, os.path.getsize(path), "bytes,", len(out), "arrays")

@@ -146,6 +146,7 @@ def _argmax_rows():
     neg0[5], neg0[11] = -0.0, 0.0                # -0 == +0: the first wins
     nan_mid = rng.standard_normal(40).astype(np.float32)
     nan_mid[[3, 20]] = np.nan                    # a NaN never beats a number
+    nan_mid[30] = 10.0
     nan_first = rng.standard_normal(40).astype(np.float32)
     nan_first[0] = np.nan                        # ... but nothing beats a NaN at index 0
     infs = np.array([-np.inf, np.nan, -np.inf, np.inf, np.inf], dtype=np.float32)
@@ -169,3 +170,12 @@ def test_argmax_oracle_equals_reference_sampler():
     """Pinned against the reference's own greedy sampling entry (temperature 0)."""
     for row in _argmax_rows():
         assert ol.argmax_token(row) == ol.ref_greedy_token(row)
+
+
+def test_argmax_oracle_matches_golden_tokens():
+    """The committed vectors hold the reference's greedy tokens (sample_token at temperature 0)
+    for rows with ties, signed zeros, NaNs and infinities."""
+    want = case("greedy_token")["tokens"]
+    for i, w in enumerate(want):
+        assert ol.argmax_token(case("greedy_token")[f"row{i}"]) == int(w), i
+    assert int(want[9]) == 30 and int(want[10]) == 0  # a NaN loses, except at index 0
