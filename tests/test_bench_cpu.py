@@ -1,0 +1,26 @@
+"""The benchmark's reference arm needs no GPU: it times the reference's own CPU kernel
+(oracle/_ref, else the oracle port) and must print one JSON line with the agreed keys."""
+import json
+import os
+import subprocess
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_reference_arm_prints_the_contract_line():
+    out = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference",
+                          "--steps", "1", "--warmup", "1"], cwd=ROOT, capture_output=True,
+                         text=True, timeout=600)
+    assert out.returncode == 0, out.stderr[-2000:]
+    line = json.loads(out.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "reference"
+    assert line["metric"] == "w4g128_gemv_hbm_gbs" and line["unit"] == "GB/s"
+    assert line["higher_is_better"] is True and line["n_gpus"] == 1
+    assert line["value"] > 0 and line["ms_per_step"] > 0
+    assert line["config"]["workload"]
+    cpu = line["cpu_baseline"]
+    assert cpu["kind"] in ("reference", "port") and cpu["cores"] >= 1 and cpu["sample"]
+    assert cpu["value"] == line["value"]
+    assert line["e2e"] == {"value": line["value"], "unit": "GB/s", "h2d_bytes_per_step": 0,
+                           "d2h_bytes_per_step": 0}
