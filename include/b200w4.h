@@ -55,6 +55,12 @@ int b2w4_ctx_create(int device, b2w4_ctx** out);
 void b2w4_ctx_destroy(b2w4_ctx* ctx);
 int b2w4_ctx_set_stream(b2w4_ctx* ctx, void* stream);
 int b2w4_sync(b2w4_ctx* ctx); /* end_graph(), engine/cuda_backend.cu:631-639 */
+/* Bound of the device-side waits for ANOTHER GPU's stores (the exchanges inside
+ * the kernels, below), 1..10000 ms, default about 2 s.  It must cover the skew
+ * between the ranks' host threads -- a peer still loading a kernel's code while
+ * this rank's consumer already spins -- not only the flight of the stores.  No
+ * counterpart in the reference (one process, one device). */
+int b2w4_ctx_set_peer_wait_ms(b2w4_ctx* ctx, int milliseconds);
 const char* b2w4_last_error(const b2w4_ctx* ctx);
 const char* b2w4_version(void);
 
@@ -192,9 +198,13 @@ int b2w4_matmul_argmax(b2w4_ctx* ctx, const b2w4_weight* w, const float* x_dev, 
  * kernel followed by a collective call, the producing kernel stores each value,
  * paired with the number of the exchange in one 8-byte word, straight into every
  * rank's staging buffer through peer mappings, and the consuming kernel takes an
- * entry once it carries the current exchange number (bounded wait, about 50 ms,
- * then B2W4_E_TIMEOUT through b2w4_sync).  A word is written whole, so no fence or
- * flag write follows the data and the exchange costs one trip over the link.
+ * entry once it carries the current exchange number (bounded wait, see
+ * b2w4_ctx_set_peer_wait_ms; then B2W4_E_TIMEOUT through b2w4_sync, and every
+ * output value whose entry never arrived is a quiet NaN -- a token: -1 -- never
+ * a stale value of an earlier exchange; the exchange count still advances, so
+ * the group stays in step, and callers must check b2w4_sync before they use the
+ * outputs of a step).  A word is written whole, so no fence or flag write
+ * follows the data and the exchange costs one trip over the link.
  * stage_peers[p] = rank p's staging buffer as mapped into this process (e.g. the
  * buffer_ptrs of a symmetric-memory rendezvous), 16-byte aligned, all zero before
  * first use: uint64[2 + 2 * half] with word 0 the count of completed exchanges

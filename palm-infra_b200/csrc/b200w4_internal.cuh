@@ -37,11 +37,13 @@ struct b2w4_ctx {
     // tuning: 1 = always the tcgen05 GEMM, 2 = the mma.sync GEMM whenever the shape fits it
     int gemm_kind = 0;
     int gemv_tpc_override = 0;  // tuning: cap on 8-row tiles per GEMV CTA (0 = heuristic)
+    unsigned long long peer_wait_cycles = 0;  // bound of waits for a peer's stores (set at create)
     char err[512] = {0};
     // grow-only scratch (quantised activations, MoE work lists, staging)
     void* scratch[8] = {nullptr};
     size_t scratch_cap[8] = {0};
     int* flag_dev = nullptr;  // one int for device-side status words
+    int* status_host = nullptr;  // pinned: the status word lands here behind the queued work
 };
 
 enum ScratchSlot {
@@ -66,6 +68,25 @@ int b2w4_reserve(b2w4_ctx* ctx, int slot, size_t bytes, void** out);
                              cudaGetErrorString(e__));                            \
     } while (0)
 
+// The opt-in to more than 48 KB of dynamic shared memory is an attribute of a kernel PER
+// DEVICE: a cache of what has been configured is indexed by the context's device.
+constexpr int kMaxDevices = 64;
+struct b2w4_smem_optin {
+    size_t bytes[kMaxDevices];  // zero-initialised as a function-local static
+};
+template <typename Kernel>
+inline cudaError_t b2w4_opt_in_smem(b2w4_ctx* ctx, Kernel kern, size_t smem,
+                                    b2w4_smem_optin& cache) {
+    size_t& have = cache.bytes[ctx->device];
+    if (smem <= 48 * 1024 || smem <= have)
+        return cudaSuccess;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)smem);
+    if (e == cudaSuccess)
+        have = smem;
+    return e;
+}
+
 // kernels' host launchers (defined in the .cu files)
 int b2w4_launch_repack(b2w4_ctx* ctx, const void* dev_blocks, b2w4_weight* w);
 int b2w4_launch_quantize(b2w4_ctx* ctx, const float* x, int lda, int m, int k,
@@ -87,7 +108,12 @@ constexpr int kTpMaxWorld = 8;
 // (exchange number << 32 | fp32 bits), written whole, so a reader needs no fence.
 constexpr int kTpStageHeader = 2;
 constexpr int kTpMaxRows = 8;  // activation rows per tensor-parallel matmul; half = 8 * ldc words
-constexpr unsigned long long kTpWaitLimitCycles = 100000000ull;  // about 50 ms
+// Default bound of a wait for another GPU's stores, in SM cycles: about 2 s, the same order
+// as the bound of the waits on this GPU's own copies.  It has to cover the skew between the
+// ranks' host threads (a peer that is still loading a kernel's code, or growing a scratch
+// buffer, when this rank's consumer already spins), not only the flight of the stores.
+// b2w4_ctx_set_peer_wait_ms changes it per context.
+constexpr unsigned long long kTpWaitLimitCycles = 4000000000ull;
 struct b2w4_tp_args {
     unsigned long long* stage_peer[kTpMaxWorld];  // rank p's staging buffer, mapped on this GPU
     int world, rank, n_offset;  // n_offset: first output column of this rank's rows

@@ -44,7 +44,8 @@ int b2w4_ctx_create(int device, b2w4_ctx** out) {
         return B2W4_E_INVALID;
     *out = nullptr;
     int count = 0;
-    if (cudaGetDeviceCount(&count) != cudaSuccess || device < 0 || device >= count)
+    if (cudaGetDeviceCount(&count) != cudaSuccess || device < 0 || device >= count ||
+        device >= kMaxDevices)
         return B2W4_E_NO_DEVICE;
     cudaDeviceProp prop;
     if (cudaGetDeviceProperties(&prop, device) != cudaSuccess)
@@ -58,6 +59,7 @@ int b2w4_ctx_create(int device, b2w4_ctx** out) {
         return B2W4_E_NOMEM;
     ctx->device = device;
     ctx->sm_count = prop.multiProcessorCount;
+    ctx->peer_wait_cycles = kTpWaitLimitCycles;
     const char* pdl = getenv("B2W4_PDL");
     ctx->pdl = !(pdl && pdl[0] == '0');
     const char* tpc = getenv("B2W4_GEMV_TPC");  // tuning: cap on tiles per GEMV CTA
@@ -76,6 +78,11 @@ int b2w4_ctx_create(int device, b2w4_ctx** out) {
         delete ctx;
         return B2W4_E_NOMEM;
     }
+    if (cudaHostAlloc(reinterpret_cast<void**>(&ctx->status_host), 64, cudaHostAllocDefault) !=
+        cudaSuccess) {
+        ctx->status_host = nullptr;  // b2w4_sync then reads the word with a blocking copy
+        cudaGetLastError();
+    }
     *out = ctx;
     return B2W4_OK;
 }
@@ -90,6 +97,8 @@ void b2w4_ctx_destroy(b2w4_ctx* ctx) {
             cudaFree(ctx->scratch[i]);
     if (ctx->flag_dev)
         cudaFree(ctx->flag_dev);
+    if (ctx->status_host)
+        cudaFreeHost(ctx->status_host);
     delete ctx;
 }
 
@@ -100,18 +109,46 @@ int b2w4_ctx_set_stream(b2w4_ctx* ctx, void* stream) {
     return B2W4_OK;
 }
 
-int b2w4_sync(b2w4_ctx* ctx) {
+int b2w4_ctx_set_peer_wait_ms(b2w4_ctx* ctx, int milliseconds) {
     if (!ctx)
         return B2W4_E_INVALID;
-    B2W4_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-    // status word written by a kernel whose bounded wait gave up
+    if (milliseconds < 1 || milliseconds > 10000)
+        return b2w4_fail(ctx, B2W4_E_INVALID, "peer wait: 1..10000 ms (got %d)", milliseconds);
+    int khz = 0;  // SM clock in kHz: the kernels count SM cycles
+    cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, ctx->device);
+    if (khz <= 0)
+        khz = 1965000;
+    ctx->peer_wait_cycles = (unsigned long long)milliseconds * (unsigned long long)khz;
+    return B2W4_OK;
+}
+
+// Drains the stream and reads the status word a kernel sets when one of its bounded waits
+// gave up; clears it so that the context stays usable.
+static int drain_and_check(b2w4_ctx* ctx) {
+    // the status word rides behind the queued work into pinned host memory: one wait, no
+    // second blocking copy
     int status = 0;
-    B2W4_CUDA(ctx, cudaMemcpy(&status, ctx->flag_dev + 1, sizeof(int), cudaMemcpyDeviceToHost));
+    if (ctx->status_host) {
+        B2W4_CUDA(ctx, cudaMemcpyAsync(ctx->status_host, ctx->flag_dev + 1, sizeof(int),
+                                       cudaMemcpyDeviceToHost, ctx->stream));
+        B2W4_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        status = *ctx->status_host;
+    } else {
+        B2W4_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        B2W4_CUDA(ctx,
+                  cudaMemcpy(&status, ctx->flag_dev + 1, sizeof(int), cudaMemcpyDeviceToHost));
+    }
     if (status != 0) {
         cudaMemset(ctx->flag_dev + 1, 0, sizeof(int));
         return b2w4_fail(ctx, status, "a device-side wait ran out of iterations");
     }
     return B2W4_OK;
+}
+
+int b2w4_sync(b2w4_ctx* ctx) {
+    if (!ctx)
+        return B2W4_E_INVALID;
+    return drain_and_check(ctx);
 }
 
 const char* b2w4_last_error(const b2w4_ctx* ctx) { return ctx ? ctx->err : "no context"; }
@@ -296,8 +333,7 @@ int b2w4_matmul_host(b2w4_ctx* ctx, const b2w4_weight* w, const float* x_host, i
                                  activation, act_n_begin, act_n_len);
             if (rc != B2W4_OK)
                 return rc;
-            B2W4_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-            return B2W4_OK;
+            return drain_and_check(ctx);  // a kernel's time-out is this call's return value
         }
         cudaGetLastError();  // pageable memory: not an error, take the staged path
     }
@@ -312,8 +348,7 @@ int b2w4_matmul_host(b2w4_ctx* ctx, const b2w4_weight* w, const float* x_host, i
         B2W4_CUDA(ctx, cudaMemcpy2DAsync(y_host, sizeof(float) * ldc, yd, sizeof(float) * w->n,
                                          sizeof(float) * w->n, m, cudaMemcpyDeviceToHost,
                                          ctx->stream));
-    B2W4_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-    return B2W4_OK;
+    return drain_and_check(ctx);
 }
 
 int b2w4_matmul_tp(b2w4_ctx* ctx, const b2w4_weight* w, const float* x_dev, int lda, int m,

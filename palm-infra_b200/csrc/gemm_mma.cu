@@ -308,12 +308,8 @@ size_t gemm_mma_smem(int groups, int cap, int m8, bool scl16, int spg, int stage
 template <int CB, bool SCL16, bool A32>
 int gemm_mma_launch(b2w4_ctx* ctx, const GemmMmaArgs& a, size_t smem, int ctas) {
     auto kern = gemm_w4a8_mma_kernel<CB, SCL16, A32>;
-    static size_t configured = 48 * 1024;  // per instantiation; one device per process
-    if (smem > configured) {
-        B2W4_CUDA(ctx, cudaFuncSetAttribute(
-                           kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        configured = smem;
-    }
+    static b2w4_smem_optin configured;  // per instantiation and device
+    B2W4_CUDA(ctx, b2w4_opt_in_smem(ctx, kern, smem, configured));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(ctas);
     cfg.blockDim = dim3(kGemmThreads);

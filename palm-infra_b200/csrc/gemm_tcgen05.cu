@@ -523,12 +523,8 @@ template <int RP, int NB>
 int launch_rp(b2w4_ctx* ctx, const GemmArgs& a, bool scl16, dim3 grid) {
     using S = Smem<RP, NB>;
     auto kern = scl16 ? gemm_w4a8_tc_kernel<RP, NB, true> : gemm_w4a8_tc_kernel<RP, NB, false>;
-    static bool configured[2] = {false, false};  // per instantiation; one device per process
-    if (!configured[scl16]) {
-        B2W4_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                            S::kTotal));
-        configured[scl16] = true;
-    }
+    static b2w4_smem_optin configured[2];  // per instantiation and device
+    B2W4_CUDA(ctx, b2w4_opt_in_smem(ctx, kern, S::kTotal, configured[scl16]));
     kern<<<grid, kThreads, S::kTotal, ctx->stream>>>(a);
     ctx->launches++;
     B2W4_CUDA(ctx, cudaGetLastError());

@@ -390,9 +390,11 @@ gemv_w4a8_kernel(const GemvArgs a) {
 // current exchange's half of the staging buffer carries the exchange number -- written by this
 // GPU's own matmul (complete: this kernel is ordered after it) and by the peers' -- and unpacks
 // the values into the plain output row.  The last block then advances the exchange count.
+// An entry that never arrives within `wait_limit` SM cycles becomes a quiet NaN in y (never a
+// stale value of an earlier exchange) and the status word reports the time-out.
 __global__ void __launch_bounds__(kTpGatherThreads)
 tp_gather_kernel(unsigned long long* stage, float* y, int m, int ldc, unsigned* done,
-                 int* status) {
+                 int* status, unsigned long long wait_limit) {
     b2w4_pdl_chain_entry();
     unsigned* count = reinterpret_cast<unsigned*>(stage);
     const unsigned exchange = *reinterpret_cast<volatile unsigned*>(count) + 1u;
@@ -405,13 +407,14 @@ tp_gather_kernel(unsigned long long* stage, float* y, int m, int ldc, unsigned* 
          i += gridDim.x * blockDim.x) {
         unsigned long long word = src[i];
         while ((unsigned)(word >> 32) != exchange && !gave_up) {
-            if (wait_clock() - t0 > kTpWaitLimitCycles) {
+            if (wait_clock() - t0 > wait_limit) {
                 atomicExch(status, B2W4_E_TIMEOUT);
                 gave_up = true;
             }
             word = src[i];
         }
-        y[i] = __uint_as_float((unsigned)word);
+        y[i] = (unsigned)(word >> 32) == exchange ? __uint_as_float((unsigned)word)
+                                                  : __uint_as_float(0x7FC00000u);
     }
     __syncthreads();  // every thread of the block has read the count
     if (threadIdx.x == 0 && atomicAdd(done, 1u) == gridDim.x - 1) {
@@ -455,14 +458,18 @@ tp_send_token_kernel(unsigned long long* cells, const b2w4_tp_args tp, int m) {
 // ... and the pick: thread (row r, rank p) waits (bounded) for rank p's words of row r, the
 // block takes the largest per row -- the one-GPU order -- and advances the count.
 __global__ void __launch_bounds__(kTop1MaxRows* kTpMaxWorld)
-tp_gather_token_kernel(unsigned long long* stage, int32_t* token, int m, int world, int* status) {
+tp_gather_token_kernel(unsigned long long* stage, int32_t* token, int m, int world, int* status,
+                       unsigned long long wait_limit) {
     b2w4_pdl_chain_entry();
     __shared__ unsigned long long s_best[kTop1MaxRows];
+    __shared__ int s_missing[kTop1MaxRows];  // a rank's words of this row never arrived
     unsigned* count = reinterpret_cast<unsigned*>(stage);
     const unsigned exchange = *reinterpret_cast<volatile unsigned*>(count) + 1u;
     const int r = threadIdx.x / kTpMaxWorld, p = threadIdx.x % kTpMaxWorld;
-    if (threadIdx.x < kTop1MaxRows)
+    if (threadIdx.x < kTop1MaxRows) {
         s_best[threadIdx.x] = 0ull;
+        s_missing[threadIdx.x] = 0;
+    }
     __syncthreads();
     if (r < m && p < world) {
         const volatile unsigned long long* src =
@@ -470,18 +477,26 @@ tp_gather_token_kernel(unsigned long long* stage, int32_t* token, int m, int wor
             ((size_t)r * kTpMaxWorld + p) * 2;
         const unsigned long long t0 = wait_clock();
         unsigned long long hi = src[0], lo = src[1];
+        bool arrived = true;
         while ((unsigned)(hi >> 32) != exchange || (unsigned)(lo >> 32) != exchange) {
-            if (wait_clock() - t0 > kTpWaitLimitCycles) {
+            if (wait_clock() - t0 > wait_limit) {
                 atomicExch(status, B2W4_E_TIMEOUT);
+                arrived = false;
                 break;
             }
             hi = src[0], lo = src[1];
         }
-        atomicMax(&s_best[r], (hi << 32) | (lo & 0xFFFFFFFFull));
+        if (arrived)
+            atomicMax(&s_best[r], (hi << 32) | (lo & 0xFFFFFFFFull));
+        else
+            s_missing[r] = 1;
     }
     __syncthreads();
+    // a row that lacks a rank's maximum has no token: -1, never a guess from stale words
     if ((int)threadIdx.x < m)
-        token[threadIdx.x] = (int32_t)(0xFFFFFFFFu - (unsigned)s_best[threadIdx.x]);
+        token[threadIdx.x] = s_missing[threadIdx.x]
+                                 ? -1
+                                 : (int32_t)(0xFFFFFFFFu - (unsigned)s_best[threadIdx.x]);
     if (threadIdx.x == 0)
         *count = exchange;
 }
@@ -503,12 +518,8 @@ size_t gemv_smem_bytes(int mt, int k, int groups, int tpc, bool scl16, bool a32)
 template <int MT, bool SCL16, bool A32, int MODE>
 int launch_one(b2w4_ctx* ctx, const GemvArgs& a, size_t smem) {
     auto kern = gemv_w4a8_kernel<MT, SCL16, A32, MODE>;
-    static size_t configured = 48 * 1024;  // per instantiation; one device per process
-    if (smem > configured) {
-        B2W4_CUDA(ctx, cudaFuncSetAttribute(
-                           kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        configured = smem;
-    }
+    static b2w4_smem_optin configured;  // per instantiation and device
+    B2W4_CUDA(ctx, b2w4_opt_in_smem(ctx, kern, smem, configured));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((a.tiles + a.tpc - 1) / a.tpc);
     cfg.blockDim = dim3(gemv_warps(MT) * 32);
@@ -636,7 +647,8 @@ int b2w4_launch_tp_gather_token(b2w4_ctx* ctx, unsigned long long* stage_local, 
                                 int m, int world) {
     B2W4_CUDA(ctx, b2w4_launch_chained(ctx->pdl, tp_gather_token_kernel, dim3(1),
                                        dim3(kTop1MaxRows * kTpMaxWorld), 0, ctx->stream,
-                                       stage_local, token, m, world, ctx->flag_dev + 1));
+                                       stage_local, token, m, world, ctx->flag_dev + 1,
+                                       ctx->peer_wait_cycles));
     ctx->launches++;
     return B2W4_OK;
 }
@@ -648,7 +660,7 @@ int b2w4_launch_tp_gather(b2w4_ctx* ctx, unsigned long long* stage_local, float*
     B2W4_CUDA(ctx, b2w4_launch_chained(ctx->pdl, tp_gather_kernel, dim3(blocks),
                                        dim3(kTpGatherThreads), 0, ctx->stream, stage_local, y,
                                        m, ldc, reinterpret_cast<unsigned*>(ctx->flag_dev + 6),
-                                       ctx->flag_dev + 1));
+                                       ctx->flag_dev + 1, ctx->peer_wait_cycles));
     ctx->launches++;
     return B2W4_OK;
 }

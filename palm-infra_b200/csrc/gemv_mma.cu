@@ -365,12 +365,8 @@ size_t mma_smem_bytes(int mt, int k, int groups, int cap, bool scl16, bool a32) 
 template <int MT, bool SCL16, bool A32, int MODE>
 int mma_launch_one(b2w4_ctx* ctx, const MmaArgs& a, size_t smem, int ctas) {
     auto kern = gemv_w4a8_mma_kernel<MT, SCL16, A32, MODE>;
-    static size_t configured = 48 * 1024;  // per instantiation; one device per process
-    if (smem > configured) {
-        B2W4_CUDA(ctx, cudaFuncSetAttribute(
-                           kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        configured = smem;
-    }
+    static b2w4_smem_optin configured;  // per instantiation and device
+    B2W4_CUDA(ctx, b2w4_opt_in_smem(ctx, kern, smem, configured));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(ctas);
     cfg.blockDim = dim3(kMmaWarps * 32);

@@ -658,13 +658,15 @@ __global__ void moe_scatter_routes_peers_kernel(const float* __restrict__ dn,
 }
 
 // Combine over the staging buffer: as moe_combine_kernel, but every value is taken from the
-// current exchange's half once it carries the exchange number (bounded wait).  The last block
-// advances the count of completed exchanges.
+// current exchange's half once it carries the exchange number (bounded wait: `wait_limit` SM
+// cycles).  The last block advances the count of completed exchanges.  An output that lacks
+// one of its rows becomes a quiet NaN, never a sum over stale rows.
 __global__ void __launch_bounds__(kCombineThreads)
 moe_combine_staged_kernel(unsigned long long* stage, int stage_rows,
                           const int32_t* __restrict__ idx, const float* __restrict__ weights,
                           const int32_t* __restrict__ pos, int tokens, int top_k, int hidden_size,
-                          float* __restrict__ out, int ldo, unsigned* done, int* status) {
+                          float* __restrict__ out, int ldo, unsigned* done, int* status,
+                          unsigned long long wait_limit) {
     b2w4_pdl_chain_entry();
     __shared__ int s_row[kMaxTopK];
     __shared__ float s_w[kMaxTopK];
@@ -702,10 +704,15 @@ moe_combine_staged_kernel(unsigned long long* stage, int stage_rows,
                      (unsigned)(w2 >> 32) == exchange && (unsigned)(w3 >> 32) == exchange) ||
                     gave_up)
                     break;
-                if ((unsigned long long)(clock64() - t0) > kTpWaitLimitCycles) {
+                if ((unsigned long long)(clock64() - t0) > wait_limit) {
                     atomicExch(status, B2W4_E_TIMEOUT);
                     gave_up = true;
                 }
+            }
+            if (gave_up) {
+                acc = make_float4(__uint_as_float(0x7FC00000u), __uint_as_float(0x7FC00000u),
+                                  __uint_as_float(0x7FC00000u), __uint_as_float(0x7FC00000u));
+                break;
             }
             const float w = s_w[j];
             acc.x = __fmaf_rn(w, __uint_as_float((unsigned)w0), acc.x);
@@ -1258,12 +1265,8 @@ int launch_grouped(b2w4_ctx* ctx, const b2w4_weight* w, int num_experts_all, int
             return b2w4_fail(ctx, B2W4_E_INVALID, "moe: K=%d needs %zu B shared memory", w->k,
                              smem);
         auto kern = scl16 ? moe_grouped_small_kernel<true> : moe_grouped_small_kernel<false>;
-        static size_t configured[2] = {48 * 1024, 48 * 1024};
-        if (smem > configured[scl16]) {
-            B2W4_CUDA(ctx, cudaFuncSetAttribute(
-                               kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            configured[scl16] = smem;
-        }
+        static b2w4_smem_optin configured[2];  // per instantiation and device
+        B2W4_CUDA(ctx, b2w4_opt_in_smem(ctx, kern, smem, configured[scl16]));
         dim3 grid((a.tiles_e + tpc - 1) / tpc, slots_y);
         B2W4_CUDA(ctx, b2w4_launch_chained(ctx->pdl, kern, grid, dim3(kST), smem, ctx->stream, a));
         ctx->launches++;
@@ -1293,12 +1296,8 @@ int launch_grouped(b2w4_ctx* ctx, const b2w4_weight* w, int num_experts_all, int
     if (smem > 220 * 1024)
         return b2w4_fail(ctx, B2W4_E_INVALID, "moe: K=%d needs %zu B shared memory", w->k, smem);
     auto kern = scl16 ? moe_grouped_gemv_kernel<true> : moe_grouped_gemv_kernel<false>;
-    static size_t configured[2] = {48 * 1024, 48 * 1024};
-    if (smem > configured[scl16]) {
-        B2W4_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                            (int)smem));
-        configured[scl16] = smem;
-    }
+    static b2w4_smem_optin configured[2];  // per instantiation and device
+    B2W4_CUDA(ctx, b2w4_opt_in_smem(ctx, kern, smem, configured[scl16]));
     dim3 grid((a.tiles_e + tpc - 1) / tpc, slots_y);
     B2W4_CUDA(ctx, b2w4_launch_chained(ctx->pdl, kern, grid, dim3(kGT), smem, ctx->stream, a));
     ctx->launches++;
@@ -1500,7 +1499,8 @@ static int moe_run(b2w4_ctx* ctx, const float* hidden_dev, int ldx, int tokens, 
                            peers->stage_peer[peers->rank], stage_rows, idx, wts,
                            fused_handover ? static_cast<const int32_t*>(pos) : nullptr, tokens,
                            top_k, hidden_size, out_dev, ldo,
-                           reinterpret_cast<unsigned*>(ctx->flag_dev + 6), ctx->flag_dev + 1));
+                           reinterpret_cast<unsigned*>(ctx->flag_dev + 6), ctx->flag_dev + 1,
+                           ctx->peer_wait_cycles));
         ctx->launches++;
     } else if (out_dev) {
         dim3 grid((hidden_size / 4 + kCombineThreads - 1) / kCombineThreads, tokens);

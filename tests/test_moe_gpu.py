@@ -130,6 +130,48 @@ def test_qwen3_30b_shaped_layer(ctx):
         check_against_oracle(got, want)
 
 
+def _expert_aggregate(tensor_id, experts, rows_per_expert, k, distinct=16):
+    """BG128 aggregate [experts * rows_per_expert, k]: `distinct` experts are generated and
+    the others are those blocks rotated by whole blocks (a different weight per expert, a
+    fraction of the generation time of the full aggregate)."""
+    base = pkg.synth.bg128_weight(20261125, tensor_id, distinct * rows_per_expert, k)
+    per = base.size // distinct
+    parts = []
+    for e in range(experts):
+        src = base[(e % distinct) * per:(e % distinct + 1) * per]
+        parts.append(np.roll(src, 544 * (e // distinct)))
+    return np.concatenate(parts)
+
+
+def test_qwen3_30b_shaped_layer_256_tokens(ctx):
+    """The prefill size the benchmark times: 256 tokens x 8 routes over 128 experts (about
+    16 routes per expert, ragged), Qwen3-30B-A3B layer shape."""
+    h, e, top_k, inter, t = 2048, 128, 8, 768, 256
+    router = pkg.synth.router_weight(20261125, 1, e, h)
+    gu = _expert_aggregate(2, e, 2 * inter, h)
+    dn = _expert_aggregate(3, e, h, inter)
+    hidden = pkg.synth.activations(7, 40 + t, t, h)
+    got = run_moe(ctx, hidden, router, top_k, inter, gu, dn)
+    want = ol.moe_forward(hidden, router, top_k, inter, gu, dn)
+    counts = np.bincount(want[2].ravel(), minlength=e)
+    assert counts.max() > 16 and counts.min() < 16  # ragged groups on both sides of a pass
+    check_against_oracle(got, want)
+
+
+def test_qwen3_235b_shaped_layer(ctx):
+    """One Qwen3-235B-A22B-shaped MoE layer: hidden 4096, 128 experts, top-8, expert
+    intermediate 1536 (1.2 GB of expert weights); 16 prompt tokens and 1 decode token."""
+    h, e, top_k, inter = 4096, 128, 8, 1536
+    router = pkg.synth.router_weight(20261125, 5, e, h)
+    gu = _expert_aggregate(6, e, 2 * inter, h, distinct=8)
+    dn = _expert_aggregate(7, e, h, inter, distinct=8)
+    for t in (16, 1):
+        hidden = pkg.synth.activations(7, 60 + t, t, h)
+        got = run_moe(ctx, hidden, router, top_k, inter, gu, dn)
+        want = ol.moe_forward(hidden, router, top_k, inter, gu, dn)
+        check_against_oracle(got, want)
+
+
 def test_bad_shapes_are_errors(ctx):
     import torch
     x = torch.zeros((2, 128), device="cuda")
@@ -283,10 +325,12 @@ def test_hand_over_with_a_silent_peer_times_out(ctx):
     xd = torch.from_numpy(hidden).cuda()
     rd = torch.from_numpy(router.view(np.int16)).cuda()
     out = torch.zeros((t, h), dtype=torch.float32, device="cuda")
+    ctx.set_peer_wait_ms(20)
     ctx.moe_forward_ep(xd, rd, top_k, inter, wg, wd, lo, cnt, _peer_group(0, 2, stages), rows,
                        out)
     with pytest.raises(pkg.capi.B200W4Error):
         ctx.sync()
+    ctx.set_peer_wait_ms(2000)
     wg.free()
     wd.free()
     want = run_moe(ctx, hidden, router, top_k, inter, gu, dn)  # the context still works

@@ -102,10 +102,19 @@ def test_gather_without_a_peer_times_out_and_context_stays_usable():
     w = ctxs[0].upload_weight(sh, n_local, k)
     xd = torch.from_numpy(pkg.synth.activations(5, 0, 1, k)).cuda()
     row = torch.zeros((1, n), dtype=torch.float32, device="cuda")
+    ctxs[0].set_peer_wait_ms(20)  # the default (about 2 s) covers host skew between ranks
     ctxs[0].matmul_tp(w, xd, n, lo, groups[0])
     ctxs[0].tp_gather(groups[0], row, n)
     with pytest.raises(pkg.capi.B200W4Error):
         ctxs[0].sync()
+    # this rank's own columns arrived; the silent peer's are NaN, never stale values
+    got = row.cpu().numpy()[0]
+    assert np.isfinite(got[lo:lo + n_local]).all()
+    missing = np.ones(n, dtype=bool)
+    missing[lo:lo + n_local] = False
+    assert np.isnan(got[missing]).all()
+    with pytest.raises(pkg.capi.B200W4Error):
+        ctxs[0].set_peer_wait_ms(0)
     whole = ctxs[0].upload_weight(blocks, n, k)
     y = torch.zeros((1, n), dtype=torch.float32, device="cuda")
     ctxs[0].matmul(whole, xd, y)
@@ -190,10 +199,12 @@ def test_token_gather_with_a_silent_peer_times_out():
     sh, n_local, lo = pkg.shard.shard_blocks(blocks, n, k, 0, 2)
     w = ctxs[0].upload_weight(np.ascontiguousarray(sh), n_local, k)
     tok = torch.zeros((1,), dtype=torch.int32, device="cuda")
+    ctxs[0].set_peer_wait_ms(20)
     ctxs[0].matmul_argmax_tp(w, torch.from_numpy(pkg.synth.activations(6, 0, 1, k)).cuda(), lo,
                              groups[0])
     ctxs[0].tp_gather_token(groups[0], tok)
     with pytest.raises(pkg.capi.B200W4Error):
         ctxs[0].sync()
+    assert int(tok.item()) == -1  # no token rather than a guess from one rank's maximum
     for c in ctxs:
         c.close()

@@ -10,6 +10,7 @@ other test."""
 import numpy as np
 import pytest
 
+import oracle_lib as ol
 from __graft_entry__ import load_package
 
 pkg = load_package()
@@ -44,6 +45,49 @@ def test_static_scratch_matches_matmul_on_two_calls_in_a_row():
             ctx.matmul_static_scratch(wide, torch.zeros((8, 10368), device="cuda"),
                                       torch.zeros((8, 8), device="cuda"))
         wide.free()
+    finally:
+        w.free()
+        ctx.close()
+
+
+@pytest.mark.parametrize("fp16_scales", [True, False])
+def test_static_scratch_against_the_oracle_and_allocates_nothing(fp16_scales):
+    """Row counts at the entry point's limits (5, 256) and on both sides of the step where the
+    row padding and the kernel variant change (128 / 129), plus 8, in one sequence of calls on
+    the shared array; every result bit for bit the CPU oracle's per-128 chain.  The device's
+    free memory, read before and after each call, must not move: that is the property the
+    entry point exists for.  (Measured on the second call of each size: the very first launch
+    of a kernel variant lets the CUDA driver load that kernel's code, which is the driver's
+    memory, not this library's.)"""
+    import torch
+    ctx = pkg.capi.Context(0)
+    n, k = 264, 640
+    blocks = pkg.synth.bg128_weight(20261125, 78, n, k).copy()
+    if not fp16_scales:
+        b = blocks.reshape(-1, 544)
+        b[:, :32].view(np.float32)[:] *= np.float32(1.0001)  # scale plane stays fp32
+    w = ctx.upload_weight(blocks, n, k)
+    assert w.scales_fp16 == fp16_scales
+    try:
+        xs = {m: pkg.synth.activations(7, 950 + m, m, k) for m in (5, 8, 128, 129, 256)}
+        xd = {m: torch.from_numpy(x).cuda() for m, x in xs.items()}
+        yd = {m: torch.full((m, n), -1.0, dtype=torch.float32, device="cuda") for m in xs}
+        for m in xs:  # one-time set-up of this device; every kernel variant's code loaded
+            ctx.matmul_static_scratch(w, xd[m], yd[m])
+        ctx.sync()
+        torch.cuda.synchronize()
+        for y in yd.values():
+            y.fill_(-1.0)
+        torch.cuda.synchronize()
+        for m in (256, 5, 129, 128, 8):
+            free_before, _ = torch.cuda.mem_get_info()
+            ctx.matmul_static_scratch(w, xd[m], yd[m])
+            ctx.sync()
+            free_after, _ = torch.cuda.mem_get_info()
+            assert free_after == free_before, f"M={m}: device memory moved by the call"
+            want = ol.matmul_w4(blocks, n, k, xs[m], rule=ol.ACT_G128)
+            got = yd[m].cpu().numpy()
+            assert got.view(np.uint32).tobytes() == want.view(np.uint32).tobytes(), f"M={m}"
     finally:
         w.free()
         ctx.close()
