@@ -76,3 +76,58 @@ def test_one_half_is_not():
         except Violation:
             bad += 1
     assert bad > 0
+
+
+# ---- the wait bound against host skew -------------------------------------------------------
+# A gather kernel spins for at most `wait_limit` after it starts.  The ranks' host threads do
+# not start an exchange at the same instant: one may still be loading a kernel's code (first
+# launch) or growing a buffer when the others already wait for its stores.  The bound must
+# therefore exceed the skew, and a rank that does give up must stay in step with the group.
+
+def run_timed(world, start, exchanges, wait_limit, flight=1.0, kernel=1.0):
+    """Discrete-event model.  Rank r issues exchange e at max(own previous gather's end,
+    start[r] for e == 1): SEND lands on every rank `flight` later; its GATHER begins `kernel`
+    after the send and ends when the last word of the half has landed, or gives up at
+    begin + wait_limit.  Returns (gave_up[r][e], count[r])."""
+    arrive = [[None] * world for _ in range(exchanges + 1)]   # arrive[e][src]: landing time
+    t = list(start)
+    gave_up = [[False] * (exchanges + 1) for _ in range(world)]
+    count = [0] * world
+    for e in range(1, exchanges + 1):
+        begin = [0.0] * world
+        for r in range(world):
+            arrive[e][r] = t[r] + flight
+            begin[r] = t[r] + kernel
+        for r in range(world):
+            last = max(arrive[e])
+            if last - begin[r] > wait_limit:
+                gave_up[r][e] = True
+                t[r] = begin[r] + wait_limit
+            else:
+                t[r] = max(begin[r], last)
+            count[r] = e  # the count advances either way: the group stays in step
+    return gave_up, count
+
+
+def test_eight_ranks_one_starts_late():
+    """Seven ranks start together, the eighth 80 time units later (its first launch of the
+    exchange's kernels loads their code).  A bound of 50 -- the first design -- makes the seven
+    give up on exchange 1; a bound above the skew does not, and in both cases every rank
+    finishes every exchange with the same count, so later exchanges pair up again."""
+    world, exchanges = 8, 5
+    start = [0.0] * 7 + [80.0]
+    gave_up, count = run_timed(world, start, exchanges, wait_limit=50.0)
+    assert all(gave_up[r][1] for r in range(7)) and not gave_up[7][1]
+    assert count == [exchanges] * world
+    assert not any(gave_up[r][e] for r in range(world) for e in range(2, exchanges + 1))
+    gave_up, count = run_timed(world, start, exchanges, wait_limit=2000.0)
+    assert not any(any(g) for g in gave_up)
+    assert count == [exchanges] * world
+
+
+def test_warm_start_removes_the_skew():
+    """With every kernel of the exchange launched once on a private one-rank group before the
+    ranks meet at a barrier, the remaining skew is the barrier's own (a few units): even the
+    short bound holds."""
+    gave_up, _ = run_timed(8, [0.0, 1.5, 0.3, 2.0, 0.1, 0.9, 1.1, 0.4], 5, wait_limit=50.0)
+    assert not any(any(g) for g in gave_up)

@@ -173,14 +173,15 @@ def _token_worker(rank, world, port, out_dir):
     dist.destroy_process_group()
 
 
-def test_row_sharded_greedy_token_world2(tmp_path):
-    """Two gloo ranks, the oracle standing in for the device matmul: every rank ends with the
-    token argmax_token picks over the unsharded logits."""
-    port = 29500 + (os.getpid() + 7) % 2000
-    mp.spawn(_token_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+@pytest.mark.parametrize("world", [2, 8])
+def test_row_sharded_greedy_token(tmp_path, world):
+    """Two and eight gloo ranks, the oracle standing in for the device matmul: every rank ends
+    with the token argmax_token picks over the unsharded logits."""
+    port = 29500 + (os.getpid() + 7 + world) % 2000
+    mp.spawn(_token_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
     blocks = pkg.synth.bg128_weight(8, 1, N, K)
     x = pkg.synth.activations(9, 1, M, K)
     full = ol.matmul_w4(blocks, N, K, x)
     want = [ol.argmax_token(full[m]) for m in range(M)]
-    for rank in range(2):
+    for rank in range(world):
         assert np.load(tmp_path / f"tok{rank}.npy").tolist() == want
