@@ -252,6 +252,60 @@ int b2w4_moe_forward_ep(b2w4_ctx* ctx, const float* hidden_dev, int ldx, int tok
                         const b2w4_tp_group* group, int stage_rows, float* out_dev, int ldo,
                         int32_t* indices_dev, float* weights_dev);
 
+/* ---- a list of decode GEMVs as one persistent kernel ------------------------------
+ * Stands in for the walk over a decode graph's MATMUL nodes with one activation
+ * row (graph/execute.cpp:651-669, one dispatch per weight) and for the batch entry
+ * point that runs several one-row GEMVs in one dispatch
+ * (kernel_matmul_int4_gemv_batch, kernels/matmul_w4.cpp:381-493).  Every op is
+ * b2w4_matmul with m == 1 and the per-128 activation rule -- same arithmetic, same
+ * bits -- but the whole list is ONE cooperative kernel, one CTA per SM: the weights
+ * of later ops stream into shared memory while earlier ops compute, and an op that
+ * consumes an earlier op's output picks it up on the device as soon as it is
+ * written (tagged 8-byte words, no kernel boundary, no barrier).
+ * Op i computes y_i[N_i] = act(W_i * x_i), where x_i[K_i] is
+ *   x_from >= 0 : elements [x_offset, x_offset + K_i) of op x_from's output (an
+ *                 earlier op of the list), or
+ *   x_from == -1: x_dev (fp32 on the device, ready before the run starts), or, when
+ *                 x_dev is NULL, the chain's own input vector (b2w4_chain_input /
+ *                 the x_host of b2w4_chain_run_host).
+ * y_dev (optional) receives the plain fp32 row; the last op's row is also kept in
+ * the chain's own output buffer when it names no y_dev (b2w4_chain_output).
+ * Limits: 1..4096 ops; K such that one 8-row tile of a weight (K/128 * 528 bytes)
+ * plus the quantised activations fit an SM's shared memory (K <= 32768 or so).
+ * All device-side waits are bounded (about 2 s); on expiry b2w4_sync returns
+ * B2W4_E_TIMEOUT and the outputs of that run are undefined. */
+typedef struct b2w4_chain_op {
+    const b2w4_weight* w;
+    int x_from;          /* -1, or the index of an earlier op */
+    int x_offset;        /* first element of that op's output used as input */
+    const float* x_dev;  /* x_from == -1 only; NULL = the chain's input vector */
+    float* y_dev;        /* NULL = not written out */
+    int activation, act_n_begin, act_n_len; /* as b2w4_matmul */
+} b2w4_chain_op;
+typedef struct b2w4_chain b2w4_chain;
+int b2w4_chain_create(b2w4_ctx* ctx, const b2w4_chain_op* ops, int count, b2w4_chain** out);
+void b2w4_chain_destroy(b2w4_ctx* ctx, b2w4_chain* chain);
+/* Asynchronous on the context's stream. */
+int b2w4_chain_run(b2w4_ctx* ctx, b2w4_chain* chain);
+/* One decode step from host memory: x_host[x_len] goes to the chain's input
+ * vector, the list runs, the chain's own output (the last op's row) comes back in
+ * y_host[y_len]; one upload, one kernel, one download, one synchronisation.
+ * Replaces a sequence of CudaBackend::lm_head_gemv-style host calls
+ * (engine/cuda_backend.cu:1393-1400). */
+int b2w4_chain_run_host(b2w4_ctx* ctx, b2w4_chain* chain, const float* x_host, int x_len,
+                        float* y_host, int y_len);
+/* Profiling hook, no reference counterpart: while trace_dev is non-NULL, CTA `cta`
+ * of every run writes 8 int64 time stamps (cycles of that CTA's SM) per op to
+ * trace_dev[op*8 ..]:
+ * 0 op begins, 1 its activations have arrived, 2 quantised, 5 about to wait for
+ * its first tile, 3 that tile's weights are in shared memory, 4 its last tile done
+ * (all compute warp 0); 6 the copy of the op's last tile was issued, 7 cycles
+ * the producer thread waited for ring space during the op's copies. */
+int b2w4_chain_set_trace(b2w4_chain* chain, long long* trace_dev, int cta);
+float* b2w4_chain_input(b2w4_chain* chain);   /* device pointer, may be NULL */
+float* b2w4_chain_output(b2w4_chain* chain);  /* device pointer, may be NULL */
+size_t b2w4_chain_weight_bytes(const b2w4_chain* chain);
+
 /* Launch counter: how many of this library's kernels have been launched on the
  * context since creation (for benchmark bookkeeping). */
 uint64_t b2w4_kernel_launches(const b2w4_ctx* ctx);

@@ -25,6 +25,8 @@ SYMBOLS = [
     "b2w4_moe_select_routes", "b2w4_moe_expert_outputs", "b2w4_moe_combine",
     "b2w4_matmul_tp", "b2w4_tp_gather", "b2w4_moe_forward_ep", "b2w4_matmul_argmax",
     "b2w4_matmul_argmax_tp", "b2w4_tp_gather_token",
+    "b2w4_chain_create", "b2w4_chain_destroy", "b2w4_chain_run", "b2w4_chain_run_host",
+    "b2w4_chain_input", "b2w4_chain_output", "b2w4_chain_weight_bytes", "b2w4_chain_set_trace",
     "b2w4_kernel_launches",
 ]
 
@@ -35,6 +37,13 @@ class TpGroup(C.Structure):
     """b2w4_tp_group: this rank, the world size, and every rank's staging buffer
     (uint64[2 + 2 * half], zeroed, 16-byte aligned; half = 8 * ldc for matmul_tp) as mapped into this process (peer pointers)."""
     _fields_ = [("rank", C.c_int), ("world", C.c_int), ("stage_peers", C.c_void_p * 8)]
+
+
+class ChainOp(C.Structure):
+    """b2w4_chain_op: one GEMV of a list run as one persistent kernel."""
+    _fields_ = [("w", C.c_void_p), ("x_from", C.c_int), ("x_offset", C.c_int),
+                ("x_dev", C.c_void_p), ("y_dev", C.c_void_p), ("activation", C.c_int),
+                ("act_n_begin", C.c_int), ("act_n_len", C.c_int)]
 
 
 class B200W4Error(RuntimeError):
@@ -85,6 +94,18 @@ def lib():
         L.b2w4_tp_gather_token.argtypes = [vp, C.POINTER(TpGroup), vp, i]
         L.b2w4_moe_forward_ep.argtypes = [vp, f_p, i, i, i, vp, i, i, i, vp, vp, i, i,
                                           C.POINTER(TpGroup), i, f_p, i, vp, f_p]
+        L.b2w4_chain_create.argtypes = [vp, C.POINTER(ChainOp), i, C.POINTER(vp)]
+        L.b2w4_chain_destroy.argtypes = [vp, vp]
+        L.b2w4_chain_destroy.restype = None
+        L.b2w4_chain_run.argtypes = [vp, vp]
+        L.b2w4_chain_run_host.argtypes = [vp, vp, f_p, i, f_p, i]
+        L.b2w4_chain_set_trace.argtypes = [vp, vp, i]
+        L.b2w4_chain_input.argtypes = [vp]
+        L.b2w4_chain_input.restype = C.c_void_p
+        L.b2w4_chain_output.argtypes = [vp]
+        L.b2w4_chain_output.restype = C.c_void_p
+        L.b2w4_chain_weight_bytes.argtypes = [vp]
+        L.b2w4_chain_weight_bytes.restype = C.c_size_t
         L.b2w4_kernel_launches.argtypes = [vp]
         L.b2w4_kernel_launches.restype = C.c_uint64
         _lib = L
@@ -111,6 +132,78 @@ class Weight:
     def free(self):
         if self.handle:
             lib().b2w4_weight_free(self.ctx.handle, self.handle)
+            self.handle = None
+
+
+class Chain:
+    """A list of one-row GEMVs compiled into one persistent kernel (b2w4_chain_*).
+    ops: list of dicts with keys w (Weight), and optionally x_from, x_offset, x (torch
+    tensor), y (torch tensor), act, act_begin, act_len."""
+
+    def __init__(self, ctx, ops):
+        self.ctx = ctx
+        arr = (ChainOp * len(ops))()
+        self.keep = []
+        for i, o in enumerate(ops):
+            arr[i].w = o["w"].handle
+            arr[i].x_from = o.get("x_from", -1)
+            arr[i].x_offset = o.get("x_offset", 0)
+            x, y = o.get("x"), o.get("y")
+            arr[i].x_dev = x.data_ptr() if x is not None else None
+            arr[i].y_dev = y.data_ptr() if y is not None else None
+            arr[i].activation = o.get("act", NONE)
+            arr[i].act_n_begin = o.get("act_begin", 0)
+            arr[i].act_n_len = o.get("act_len", -1)
+            self.keep.append((o["w"], x, y))
+        h = C.c_void_p()
+        ctx._check(lib().b2w4_chain_create(ctx.handle, arr, len(ops), C.byref(h)))
+        self.handle = h
+        self.count = len(ops)
+
+    def run(self):
+        self.ctx._check(lib().b2w4_chain_run(self.ctx.handle, self.handle))
+
+    def run_host(self, x_np, y_np):
+        self.ctx._check(lib().b2w4_chain_run_host(
+            self.ctx.handle, self.handle,
+            x_np.ctypes.data_as(C.c_void_p) if x_np is not None else None,
+            x_np.size if x_np is not None else 0,
+            y_np.ctypes.data_as(C.c_void_p) if y_np is not None else None,
+            y_np.size if y_np is not None else 0))
+
+    def bind_run_host(self, x_np, y_np):
+        """run_host with its arguments resolved once (for timing loops)."""
+        fn, ch, h = lib().b2w4_chain_run_host, self.handle, self.ctx.handle
+        args = (h, ch, x_np.ctypes.data, x_np.size, y_np.ctypes.data, y_np.size)
+        keep = (x_np, y_np)
+
+        def call():
+            rc = fn(*args)
+            if rc != 0:
+                self.ctx._check(rc)
+            return keep
+        return call
+
+    def set_trace(self, trace, cta=0):
+        """trace: int64 CUDA tensor [ops, 8] (or None to switch the profiling hook off)."""
+        self.ctx._check(lib().b2w4_chain_set_trace(self.handle, _dptr(trace), cta))
+        self.keep.append(trace)
+
+    @property
+    def input_ptr(self):
+        return lib().b2w4_chain_input(self.handle)
+
+    @property
+    def output_ptr(self):
+        return lib().b2w4_chain_output(self.handle)
+
+    @property
+    def weight_bytes(self):
+        return int(lib().b2w4_chain_weight_bytes(self.handle))
+
+    def free(self):
+        if self.handle:
+            lib().b2w4_chain_destroy(self.ctx.handle, self.handle)
             self.handle = None
 
 

@@ -42,8 +42,12 @@ struct b2w4_ctx {
     // grow-only scratch (quantised activations, MoE work lists, staging)
     void* scratch[8] = {nullptr};
     size_t scratch_cap[8] = {0};
-    int* flag_dev = nullptr;  // one int for device-side status words
-    int* status_host = nullptr;  // pinned: the status word lands here behind the queued work
+    int* flag_dev = nullptr;  // device words: arrival counters, greedy-token cells
+    // The status word a kernel sets when a bounded wait gives up lives in mapped pinned HOST
+    // memory: the host reads it after a stream synchronise with no copy.  status_dev is the
+    // same word's device address.
+    int* status_host = nullptr;
+    int* status_dev = nullptr;
 };
 
 enum ScratchSlot {
@@ -256,6 +260,13 @@ __device__ __forceinline__ uint4 b2w4_ldg_stream(const uint4* p) {
                  : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
                  : "l"(p));
     return v;
+}
+
+// A bounded wait gave up: a plain store (every writer stores the same value) into the
+// host-mapped status word.  The store drains at the latest at the end of the grid, which is
+// before the host's stream synchronise returns.
+__device__ __forceinline__ void b2w4_report_timeout(int* status) {
+    *reinterpret_cast<volatile int*>(status) = B2W4_E_TIMEOUT;
 }
 
 __device__ __forceinline__ void b2w4_pdl_wait() {

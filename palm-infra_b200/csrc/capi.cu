@@ -78,11 +78,17 @@ int b2w4_ctx_create(int device, b2w4_ctx** out) {
         delete ctx;
         return B2W4_E_NOMEM;
     }
-    if (cudaHostAlloc(reinterpret_cast<void**>(&ctx->status_host), 64, cudaHostAllocDefault) !=
-        cudaSuccess) {
-        ctx->status_host = nullptr;  // b2w4_sync then reads the word with a blocking copy
-        cudaGetLastError();
+    if (cudaHostAlloc(reinterpret_cast<void**>(&ctx->status_host), 64, cudaHostAllocMapped) !=
+            cudaSuccess ||
+        cudaHostGetDevicePointer(reinterpret_cast<void**>(&ctx->status_dev), ctx->status_host,
+                                 0) != cudaSuccess) {
+        if (ctx->status_host)
+            cudaFreeHost(ctx->status_host);
+        cudaFree(ctx->flag_dev);
+        delete ctx;
+        return B2W4_E_NOMEM;
     }
+    *ctx->status_host = 0;
     *out = ctx;
     return B2W4_OK;
 }
@@ -125,21 +131,11 @@ int b2w4_ctx_set_peer_wait_ms(b2w4_ctx* ctx, int milliseconds) {
 // Drains the stream and reads the status word a kernel sets when one of its bounded waits
 // gave up; clears it so that the context stays usable.
 static int drain_and_check(b2w4_ctx* ctx) {
-    // the status word rides behind the queued work into pinned host memory: one wait, no
-    // second blocking copy
-    int status = 0;
-    if (ctx->status_host) {
-        B2W4_CUDA(ctx, cudaMemcpyAsync(ctx->status_host, ctx->flag_dev + 1, sizeof(int),
-                                       cudaMemcpyDeviceToHost, ctx->stream));
-        B2W4_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-        status = *ctx->status_host;
-    } else {
-        B2W4_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-        B2W4_CUDA(ctx,
-                  cudaMemcpy(&status, ctx->flag_dev + 1, sizeof(int), cudaMemcpyDeviceToHost));
-    }
+    B2W4_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    const int status = *reinterpret_cast<volatile int*>(ctx->status_host);
     if (status != 0) {
-        cudaMemset(ctx->flag_dev + 1, 0, sizeof(int));
+        *reinterpret_cast<volatile int*>(ctx->status_host) = 0;
+        cudaMemset(ctx->flag_dev + 2, 0, sizeof(int));  // the persistent kernel's abort word
         return b2w4_fail(ctx, status, "a device-side wait ran out of iterations");
     }
     return B2W4_OK;

@@ -249,7 +249,7 @@ gemm_w4a8_tc_kernel(const GemmArgs a) {
     // accumulator b, token block mb: columns [b*256 + mb*RP, +RP)
     auto fail = [&]() {
         *s_abort = 1;
-        atomicExch(a.status, B2W4_E_TIMEOUT);
+        b2w4_report_timeout(a.status);
     };
 
     if (warp == kProducerWarp) {
@@ -572,7 +572,7 @@ int b2w4_launch_gemm_tc(b2w4_ctx* ctx, const b2w4_weight* w, const float* x, int
     a.qa = static_cast<const int8_t*>(qa);
     a.as = static_cast<const float*>(as);
     a.y = y;
-    a.status = ctx->flag_dev + 1;
+    a.status = ctx->status_dev;
     a.ldc = ldc;
     a.m = m;
     a.m_pad = m_pad;
@@ -675,7 +675,7 @@ extern "C" int b2w4_matmul_static_scratch(b2w4_ctx* ctx, const b2w4_weight* w,
     a.qa = qa;
     a.as = as;
     a.y = y_dev;
-    a.status = ctx->flag_dev + 1;
+    a.status = ctx->status_dev;
     a.ldc = ldc;
     a.m = m;
     a.m_pad = m_pad;

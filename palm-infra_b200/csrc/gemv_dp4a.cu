@@ -333,7 +333,7 @@ gemv_w4a8_kernel(const GemvArgs a) {
         }
     }
     if (timed_out && lane == 0)
-        atomicExch(a.status, B2W4_E_TIMEOUT);
+        b2w4_report_timeout(a.status);
     __syncthreads();
 
     // ---- phase 2: fp32 chain, one thread per (tile, activation row, weight row) ---------
@@ -408,7 +408,7 @@ tp_gather_kernel(unsigned long long* stage, float* y, int m, int ldc, unsigned* 
         unsigned long long word = src[i];
         while ((unsigned)(word >> 32) != exchange && !gave_up) {
             if (wait_clock() - t0 > wait_limit) {
-                atomicExch(status, B2W4_E_TIMEOUT);
+                b2w4_report_timeout(status);
                 gave_up = true;
             }
             word = src[i];
@@ -480,7 +480,7 @@ tp_gather_token_kernel(unsigned long long* stage, int32_t* token, int m, int wor
         bool arrived = true;
         while ((unsigned)(hi >> 32) != exchange || (unsigned)(lo >> 32) != exchange) {
             if (wait_clock() - t0 > wait_limit) {
-                atomicExch(status, B2W4_E_TIMEOUT);
+                b2w4_report_timeout(status);
                 arrived = false;
                 break;
             }
@@ -573,7 +573,7 @@ int b2w4_launch_gemv(b2w4_ctx* ctx, const b2w4_weight* w, const float* x, int ld
         a.x = x + (size_t)m0 * lda;
         a.y = y ? y + (size_t)m0 * ldc : nullptr;
         a.sums = sums ? sums + (size_t)m0 * w->n * w->groups * spg : nullptr;
-        a.status = ctx->flag_dev + 1;
+        a.status = ctx->status_dev;
         a.lda = lda;
         a.ldc = ldc;
         a.m = mc;
@@ -647,7 +647,7 @@ int b2w4_launch_tp_gather_token(b2w4_ctx* ctx, unsigned long long* stage_local, 
                                 int m, int world) {
     B2W4_CUDA(ctx, b2w4_launch_chained(ctx->pdl, tp_gather_token_kernel, dim3(1),
                                        dim3(kTop1MaxRows * kTpMaxWorld), 0, ctx->stream,
-                                       stage_local, token, m, world, ctx->flag_dev + 1,
+                                       stage_local, token, m, world, ctx->status_dev,
                                        ctx->peer_wait_cycles));
     ctx->launches++;
     return B2W4_OK;
@@ -660,7 +660,7 @@ int b2w4_launch_tp_gather(b2w4_ctx* ctx, unsigned long long* stage_local, float*
     B2W4_CUDA(ctx, b2w4_launch_chained(ctx->pdl, tp_gather_kernel, dim3(blocks),
                                        dim3(kTpGatherThreads), 0, ctx->stream, stage_local, y,
                                        m, ldc, reinterpret_cast<unsigned*>(ctx->flag_dev + 6),
-                                       ctx->flag_dev + 1, ctx->peer_wait_cycles));
+                                       ctx->status_dev, ctx->peer_wait_cycles));
     ctx->launches++;
     return B2W4_OK;
 }

@@ -705,7 +705,7 @@ moe_combine_staged_kernel(unsigned long long* stage, int stage_rows,
                     gave_up)
                     break;
                 if ((unsigned long long)(clock64() - t0) > wait_limit) {
-                    atomicExch(status, B2W4_E_TIMEOUT);
+                    b2w4_report_timeout(status);
                     gave_up = true;
                 }
             }
@@ -884,7 +884,7 @@ moe_grouped_small_kernel(const GroupedSmallArgs a) {
         if (!weights_ready) {
             if (!mbar_wait_bounded(&s_bar[0])) {
                 if (lane == 0)
-                    atomicExch(a.status, B2W4_E_TIMEOUT);
+                    b2w4_report_timeout(a.status);
                 return;  // every thread sees the same barrier: the exit is CTA-uniform
             }
             weights_ready = true;
@@ -1118,7 +1118,7 @@ moe_grouped_gemv_kernel(const GroupedArgs a) {
         if (!weights_ready) {
             if (!mbar_wait_bounded(&s_bar[0])) {
                 if (lane == 0)
-                    atomicExch(a.status, B2W4_E_TIMEOUT);
+                    b2w4_report_timeout(a.status);
                 return;  // every thread sees the same barrier: the exit is CTA-uniform
             }
             weights_ready = true;
@@ -1246,7 +1246,7 @@ int launch_grouped(b2w4_ctx* ctx, const b2w4_weight* w, int num_experts_all, int
         a.expert_count = expert_count;
         a.row_map = row_map;
         a.out = out;
-        a.status = ctx->flag_dev + 1;
+        a.status = ctx->status_dev;
         if (peers) {
             a.peers = *peers;
             a.stage_rows = stage_rows;
@@ -1283,7 +1283,7 @@ int launch_grouped(b2w4_ctx* ctx, const b2w4_weight* w, int num_experts_all, int
     a.expert_count = expert_count;
     a.row_map = row_map;
     a.out = out;
-    a.status = ctx->flag_dev + 1;
+    a.status = ctx->status_dev;
     a.k = w->k;
     a.groups = w->groups;
     a.n_e = n_e;
@@ -1499,7 +1499,7 @@ static int moe_run(b2w4_ctx* ctx, const float* hidden_dev, int ldx, int tokens, 
                            peers->stage_peer[peers->rank], stage_rows, idx, wts,
                            fused_handover ? static_cast<const int32_t*>(pos) : nullptr, tokens,
                            top_k, hidden_size, out_dev, ldo,
-                           reinterpret_cast<unsigned*>(ctx->flag_dev + 6), ctx->flag_dev + 1,
+                           reinterpret_cast<unsigned*>(ctx->flag_dev + 6), ctx->status_dev,
                            ctx->peer_wait_cycles));
         ctx->launches++;
     } else if (out_dev) {
