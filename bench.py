@@ -2,17 +2,26 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-Workload (benchmark configuration 2's decode GEMV): y[1,9728] = x[1,2560] * W^T with W a
-W4G128 weight, synthetic and seeded.  One step = one GEMV over each of R distinct weight
-copies (R * 12.9 MB > the 126 MB L2, so every launch streams its weight from HBM).
+Workload (benchmark configuration 1, the decode GEMV): y[1,9728] = x[1,2560] * W^T with W a
+W4G128 weight, synthetic and seeded.  One step = GEMVs of one activation vector against R
+distinct weight copies, walked several times (R * 12.9 MB > the 126 MB L2, so every GEMV
+streams its weight from HBM) -- the reference's own microbenchmark does the same on the CPU
+(tests/bench_matmul.cpp rotates weight sets under one input).
 metric = algorithmic bytes moved per second (weights at 4.125 bit + fp32 x + fp32 y).
 
-ours, N=1      : weights and activations resident in HBM, CUDA-event timing (`value`);
-                 the same step through b2w4_matmul_host with pinned HOST buffers (`e2e`);
-                 M in {4,16,64,256} and a Qwen3-4B-shaped decode matmul walk (`sweep`);
-                 the reference's own CPU kernel on this box's host cores (`cpu_baseline`).
+ours, N=1      : the walk as ONE persistent kernel (b2w4_chain_*: a list of GEMVs, weights of
+                 later GEMVs streaming while earlier ones compute), weights and activations
+                 resident in HBM, CUDA-event timing (`value`); the same list through
+                 b2w4_chain_run_host with pinned HOST x and every y stored to pinned host
+                 memory (`e2e`); the list with every GEMV consuming its predecessor's output,
+                 and the one-launch-per-GEMV kernel (`variants`); M in {4,16,64,256} and a
+                 Qwen3-4B-shaped decode matmul walk (`sweep`); the reference's own CUDA
+                 kernels on this GPU (`gpu_reference`) and its CPU kernel on this box's host
+                 cores (`cpu_baseline`).
 ours, N>1      : tensor parallel -- every weight is split by output rows across the ranks,
-                 each rank streams its shard, an NCCL all-gather rebuilds y (strong scaling).
+                 each rank streams its shard and the full row is rebuilt on every rank, by the
+                 exchange inside the kernels (`value`) and by an NCCL all-gather (strong
+                 scaling).
 --impl reference: the reference's CPU implementation of the same step (rank 0 only).
 Prints ONE JSON line on rank 0.
 """
@@ -34,25 +43,27 @@ from __graft_entry__ import load_package  # noqa: E402
 
 N_OUT, K_IN = 9728, 2560
 COPIES = 32   # distinct weight buffers walked by one pass
-PASSES = 16   # passes per step: one step = PASSES * COPIES GEMVs
+PASSES = 16   # passes per list: one persistent-kernel launch = PASSES * COPIES GEMVs
+RUNS_PER_STEP = 20  # launches of the list per step (a step is about 25 ms of device time)
 SEED_W, SEED_X = 20261125, 7
 METRIC, UNIT = "w4g128_gemv_hbm_gbs", "GB/s"
 L2_MB = 126
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of ONE gemv_w4a8_kernel launch on this workload,
-# from the ncu capture summarised in profiles/gemv_w4a8_m1_k2560_n9728.md
+# dram__bytes_read.sum + dram__bytes_write.sum per GEMV of this workload, from ncu captures of
+# the two kernels (persistent list: 410 981 120 B read for 32 GEMVs; one launch per GEMV)
+NCU_DRAM_BYTES_PER_GEMV_CHAIN = 410981120 // 32
 NCU_DRAM_BYTES_PER_LAUNCH = 12876800
 
 
 def workload_config(world=1, passes=PASSES, graph=True):
     return {"workload": f"W4G128 W4A8 GEMV M=1 K={K_IN} N={N_OUT} "
-                        f"(benchmark configuration 2, decode)",
+                        f"(benchmark configuration 1, decode)",
             "gemvs_per_step": COPIES * passes,
             "l2": f"rotates {COPIES} distinct weight copies "
                   f"({COPIES * 12.84:.0f} MB) > {L2_MB} MB L2",
-            "parallelism": (f"tp{world}: output rows split over the ranks, NCCL all-gather "
-                            f"of y after every GEMV") if world > 1 else "single GPU",
+            "parallelism": (f"tp{world}: output rows split over the ranks, the full row rebuilt "
+                            f"on every rank after every GEMV") if world > 1 else "single GPU",
             "act_rule": "int8 per 128 values",
             "launch": ("CUDA graph replay" if graph else "eager")
                       + ", programmatic dependent launch"}
@@ -207,6 +218,56 @@ def run_reference(args):
     print(json.dumps(line))
 
 
+def gpu_reference(torch, pkg, args, our_gemv_gbs, our_m256_us):
+    """The reference's own CUDA matmul kernels (engine/cuda_matmul.cu, compiled unmodified for
+    sm_100 into oracle/_ref/libref_cuda.so) on this GPU and this workload: its one-row GEMV
+    (fp32 activations, W4A32) and its many-row path (dequantise the whole weight to fp16,
+    cast the activations, cuBLAS), the same rotation of weight copies, CUDA events on the
+    legacy default stream the reference launches on.  A comparator, never on the product
+    path."""
+    path = os.path.join(ROOT, "oracle", "_ref", "libref_cuda.so")
+    if not os.path.exists(path):
+        return {"unavailable": "oracle/_ref/libref_cuda.so was not built (make -C oracle refcuda)"}
+    lib = ctypes.CDLL(path)
+    vp = ctypes.c_void_p
+    one = pkg.synth.bg128_weight(SEED_W, 1, N_OUT, K_IN)
+    copies = [torch.from_numpy(np.roll(one, 544 * i)).cuda() for i in range(COPIES)]
+    out = {"kernels": "engine/cuda_matmul.cu of the reference, built for sm_100"}
+    with torch.cuda.stream(torch.cuda.default_stream()):
+        for m, reps in ((1, 8), (256, 1)):
+            x = torch.from_numpy(pkg.synth.activations(SEED_X, 0, m, K_IN)).cuda()
+            y = torch.zeros((m, N_OUT), dtype=torch.float32, device="cuda")
+
+            def walk():
+                for _ in range(reps):
+                    for c in copies:
+                        if m == 1:
+                            rc = lib.refcuda_gemv_g128(vp(x.data_ptr()), vp(c.data_ptr()),
+                                                       vp(y.data_ptr()), N_OUT, K_IN)
+                        else:
+                            rc = lib.refcuda_gemm_g128(vp(x.data_ptr()), K_IN, vp(c.data_ptr()),
+                                                       vp(y.data_ptr()), m, N_OUT, K_IN)
+                        if rc != 0:
+                            raise RuntimeError(f"reference CUDA kernel failed: {rc}")
+            try:
+                ms = time_steps(torch, walk, 5, 3)
+            except RuntimeError as exc:
+                out[f"m{m}"] = {"error": str(exc)[:200]}
+                continue
+            us = ms * 1e3 / (reps * COPIES)
+            if m == 1:
+                gbs = algorithmic_bytes(N_OUT, K_IN, 1) / us / 1e3
+                out["m1_q4_g128_dense_gemv_cuda"] = {
+                    "us_per_gemv": us, "value": gbs, "unit": UNIT,
+                    "ours_over_reference": our_gemv_gbs / gbs}
+            else:
+                out["m256_dequant_then_cublas"] = {
+                    "us_per_matmul": us, "tflops": 2.0 * m * N_OUT * K_IN / us / 1e6,
+                    "ours_over_reference": us / our_m256_us}
+    lib.refcuda_release()
+    return out
+
+
 # --------------------------------------------------------------------------------- ours
 
 def moe_layer(torch, pkg, ctx, args):
@@ -299,6 +360,8 @@ def moe_layer_ep(torch, dist, pkg, ctx, rank, world):
     x = torch.from_numpy(pkg.synth.activations(SEED_X, 81, 1, h)).cuda()
     y = torch.zeros((1, h), dtype=torch.float32, device="cuda")
     y2 = torch.zeros((1, h), dtype=torch.float32, device="cuda")
+    op.forward(x, y)  # the shared kernels' code is loaded before the ranks meet
+    torch.cuda.synchronize()
     dist.barrier()
     same = True
     for _ in range(3):  # both halves of the staging buffer; bit for bit the all-reduce result
@@ -358,6 +421,17 @@ def lm_head_greedy_tp(torch, dist, pkg, ctx, rank, world):
     for p_ in range(world):
         group.stage_peers[p_] = hs.buffer_ptrs[p_]
     tok = torch.full((1,), -1, dtype=torch.int32, device="cuda")
+    # Every kernel of the exchange runs once on a private one-rank group BEFORE the ranks meet:
+    # the first launch of a kernel loads its code, and a rank still loading while its peers'
+    # gathers already spin is host skew the bounded wait would have to absorb.
+    solo_stage = torch.zeros((2 + 256,), dtype=torch.int64, device="cuda")
+    solo = pkg.capi.TpGroup()
+    solo.rank, solo.world = 0, 1
+    solo.stage_peers[0] = solo_stage.data_ptr()
+    ctx.matmul_argmax_tp(ws[0], x, lo, solo)
+    ctx.tp_gather_token(solo, tok)
+    ctx.sync()
+    torch.cuda.synchronize()
     dist.barrier()
 
     def eager():
@@ -483,10 +557,18 @@ def decode_walk(torch, pkg, ctx, args):
     return out
 
 
+def json_only_stdout():
+    """stdout carries the ONE JSON line.  Libraries that log to file descriptor 1 (NCCL with
+    NCCL_DEBUG=INFO does) are sent to stderr instead: fd 1 is re-pointed at fd 2 and the
+    returned file object, a duplicate of the original stdout, is what the line is printed to."""
+    sys.stdout.flush()
+    keep = os.dup(1)
+    os.dup2(2, 1)
+    return os.fdopen(keep, "w")
+
+
 def run_ours(args):
-    # NCCL prints its version banner on stdout at some debug levels; stdout carries the JSON line
-    if os.environ.get("NCCL_DEBUG", "").upper() in ("VERSION", "INFO"):
-        os.environ["NCCL_DEBUG"] = "WARN"
+    out = json_only_stdout()
     import torch
     import torch.distributed as dist
 
@@ -566,6 +648,17 @@ def run_ours(args):
         m = args.rows
         x, y_local, y_full = make_io(m)
         y_row = torch.zeros((m, N_OUT), dtype=torch.float32, device="cuda")
+        # both kernels of the exchange once on a private one-rank group before the ranks meet
+        # (a first launch loads the kernel's code: host skew the bounded wait should not pay)
+        solo_stage = torch.zeros((2 + 16 * n_local,), dtype=torch.int64, device="cuda")
+        solo = pkg.capi.TpGroup()
+        solo.rank, solo.world = 0, 1
+        solo.stage_peers[0] = solo_stage.data_ptr()
+        y_solo = torch.zeros((m, n_local), dtype=torch.float32, device="cuda")
+        ctx.matmul_tp(weights[0], x, n_local, 0, solo)
+        ctx.tp_gather(solo, y_solo, n_local)
+        ctx.sync()
+        torch.cuda.synchronize()
         dist.barrier()
         # eagerly, twice (both halves of the staging buffer): the gathered row must equal the
         # NCCL all-gather of the shards, bit for bit
@@ -617,35 +710,79 @@ def run_ours(args):
 
     if args.moe_only:  # one leg alone (profiling commands)
         if rank == 0:
-            print(json.dumps({"moe30b_layer": moe_layer(torch, pkg, ctx, args)}), flush=True)
+            out.write(json.dumps({"moe30b_layer": moe_layer(torch, pkg, ctx, args)}) + "\n")
+            out.flush()
         ctx.close()
         return
 
     # ---- headline: M=1, resident inputs -------------------------------------------------
-    l0 = ctx.launches
-    make_step(args.rows, graph=False)()
-    launches_per_step = ctx.launches - l0
-    step = make_step(args.rows)
-    with ClockSampler(local) as clocks:
-        ms = time_steps(torch, step, args.steps, args.warmup, barrier)
-    ms = max_over_ranks(ms)
-    exchange = "none (one GPU)" if world == 1 else "NCCL all-gather after every GEMV"
-    nccl_ms = None
-    if world > 1 and args.rows <= 8 and not args.no_graph and world <= 8:
-        peer_step = make_peer_step()
-        if peer_step is not None:
-            nccl_ms = ms
-            with ClockSampler(local) as clocks:
-                ms = time_steps(torch, peer_step, args.steps, args.warmup, barrier)
-            ms = max_over_ranks(ms)
-            exchange = ("in the GEMV kernel: flagged 8-byte peer stores into every rank's "
-                        "staging buffer, gather kernel with a bounded wait")
     alg = algorithmic_bytes(N_OUT, K_IN, 1)
-    gemvs = COPIES * args.passes
-    value = gemvs * alg / (ms * 1e-3) / 1e9
-    launch_us = ms * 1e3 / gemvs
     peak, peak_kind = measured_peaks()
-    achieved = algorithmic_bytes(n_local, K_IN, 1) / (launch_us * 1e-6) / 1e9
+    use_list = world == 1 and args.rows == 1 and not args.per_launch
+    variants = {}
+    if use_list:
+        # One step = RUNS_PER_STEP launches of the persistent kernel, each a list of
+        # passes * COPIES GEMVs of one activation vector (the list shares its quantisation, as
+        # the reference's batch entry point does for identical inputs).
+        x, _, _ = make_io(1)
+        ys = torch.zeros((COPIES, N_OUT), dtype=torch.float32, device="cuda")
+        n_ops = COPIES * args.passes
+        ops = [dict(w=weights[i % COPIES], x=x, y=ys[i % COPIES:i % COPIES + 1])
+               for i in range(n_ops)]
+        chain = pkg.capi.Chain(ctx, ops)
+        runs = RUNS_PER_STEP
+
+        def step():
+            for _ in range(runs):
+                chain.run()
+        l0 = ctx.launches
+        step()
+        launches_per_step = ctx.launches - l0
+        ctx.sync()
+        # the list's rows against the one-launch-per-GEMV kernel's, bit for bit
+        y_one = torch.zeros((1, N_OUT), dtype=torch.float32, device="cuda")
+        for i in (0, COPIES - 1):
+            ctx.matmul(weights[i], x, y_one)
+            ctx.sync()
+            assert torch.equal(ys[i:i + 1], y_one), "list kernel and per-launch kernel differ"
+        with ClockSampler(local) as clocks:
+            ms = time_steps(torch, step, args.steps, args.warmup, barrier)
+        gemvs = n_ops * runs
+        kernel_name, launch_desc = "gemv_chain_kernel", (
+            f"{runs} launches of one persistent cooperative kernel per step, each a list of "
+            f"{n_ops} GEMVs on one activation vector")
+        alg_per_launch = alg * n_ops
+        launch_us = ms * 1e3 / runs
+        traffic = NCU_DRAM_BYTES_PER_GEMV_CHAIN * n_ops
+        exchange = "none (one GPU)"
+        nccl_ms = None
+    else:
+        l0 = ctx.launches
+        make_step(args.rows, graph=False)()
+        launches_per_step = ctx.launches - l0
+        step = make_step(args.rows)
+        with ClockSampler(local) as clocks:
+            ms = time_steps(torch, step, args.steps, args.warmup, barrier)
+        ms = max_over_ranks(ms)
+        exchange = "none (one GPU)" if world == 1 else "NCCL all-gather after every GEMV"
+        nccl_ms = None
+        if world > 1 and args.rows <= 8 and not args.no_graph and world <= 8:
+            peer_step = make_peer_step()
+            if peer_step is not None:
+                nccl_ms = ms
+                with ClockSampler(local) as clocks:
+                    ms = time_steps(torch, peer_step, args.steps, args.warmup, barrier)
+                ms = max_over_ranks(ms)
+                exchange = ("in the GEMV kernel: tagged 8-byte peer stores into every rank's "
+                            "staging buffer, gather kernel with a bounded wait")
+        gemvs = COPIES * args.passes
+        kernel_name = "gemv_w4a8_kernel"
+        launch_desc = None
+        alg_per_launch = algorithmic_bytes(n_local, K_IN, 1)
+        launch_us = ms * 1e3 / gemvs
+        traffic = NCU_DRAM_BYTES_PER_LAUNCH if world == 1 else None
+    value = gemvs * alg / (ms * 1e-3) / 1e9
+    achieved = alg_per_launch / (launch_us * 1e-6) / 1e9
 
     line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
@@ -653,31 +790,76 @@ def run_ours(args):
             "dtype": "s8*s4->s32, f32 scale chain", "data": "synthetic",
             "config": workload_config(world, args.passes, not args.no_graph),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "traffic": NCU_DRAM_BYTES_PER_LAUNCH if world == 1 else None,
-                         "kernel": "gemv_w4a8_kernel", "peak_kind": peak_kind,
-                         "algorithmic_bytes_per_launch": algorithmic_bytes(n_local, K_IN, 1),
+                         "frac": achieved / peak, "traffic": traffic,
+                         "kernel": kernel_name, "peak_kind": peak_kind,
+                         "algorithmic_bytes_per_launch": alg_per_launch,
                          "avg_launch_us": launch_us},
             "clocks": clocks.summary(),
             "gpu_launches": launches_per_step * args.steps}
+    line["config"]["gemvs_per_step"] = gemvs
     line["config"]["exchange"] = exchange
+    if launch_desc:
+        line["config"]["launch"] = launch_desc
+    if world > 1:
+        line["config"]["parallelism"] += f"; timed exchange: {exchange}"
     if nccl_ms is not None:
         line["nccl_allgather_variant"] = {"value": gemvs * alg / (nccl_ms * 1e-3) / 1e9,
                                           "unit": UNIT, "ms_per_step": nccl_ms}
         line["gpu_launches"] = 2 * launches_per_step * args.steps  # GEMV + gather kernel
 
+    if use_list and not args.headline_only:
+        # ---- the same GEMVs two other ways ------------------------------------------------
+        # (a) every GEMV consumes the first K outputs of its predecessor (a decode step's data
+        #     dependency; the chain restarts from x every COPIES GEMVs to stay inside fp32)
+        dep_ops = [dict(w=weights[i % COPIES], x=x) if i % COPIES == 0 else
+                   dict(w=weights[i % COPIES], x_from=i - 1) for i in range(n_ops)]
+        dep = pkg.capi.Chain(ctx, dep_ops)
+        d_ms = time_steps(torch, dep.run, max(3, min(args.steps, 20)), 3)
+        variants["list_with_dependent_gemvs"] = {
+            "value": n_ops * alg / (d_ms * 1e-3) / 1e9, "unit": UNIT,
+            "us_per_gemv": d_ms * 1e3 / n_ops,
+            "what": "each GEMV reads its predecessor's output (tagged words, polled on the device)"}
+        dep.free()
+        # (b) one kernel launch per GEMV, CUDA graph replay with programmatic dependent launch
+        p_ms = time_steps(torch, make_step(1), max(3, min(args.steps, 20)), 3)
+        variants["one_launch_per_gemv"] = {
+            "value": COPIES * args.passes * alg / (p_ms * 1e-3) / 1e9, "unit": UNIT,
+            "us_per_gemv": p_ms * 1e3 / (COPIES * args.passes), "kernel": "gemv_w4a8_kernel"}
+        line["variants"] = variants
+
     if not args.headline_only:
-        # ---- e2e: the same step through the host-buffer entry point (every rank streams its
-        # shard from pinned host x to pinned host y; the slowest rank counts) ---------------
+        # ---- e2e: the same step from HOST buffers ------------------------------------------
         xh = torch.from_numpy(pkg.synth.activations(SEED_X, 0, 1, K_IN)).pin_memory()
-        yh = torch.zeros((1, n_local), dtype=torch.float32).pin_memory()
-        xn, yn = xh.numpy(), yh.numpy()
+        if use_list:
+            # x from pinned host memory every launch; every GEMV's row is stored by the kernel
+            # straight into pinned host memory (its y pointer is the mapped host buffer)
+            yh = torch.zeros((n_ops, N_OUT), dtype=torch.float32).pin_memory()
+            yh_t = [yh[i:i + 1] for i in range(n_ops)]
+            e_ops = [dict(w=weights[i % COPIES], y=yh_t[i]) for i in range(n_ops)]
+            e_chain = pkg.capi.Chain(ctx, e_ops)
+            none_y = np.zeros(0, dtype=np.float32)
+            call = e_chain.bind_run_host(xh.numpy().reshape(-1), none_y)
 
-        calls = [ctx.bind_matmul_host(w, xn, yn) for w in weights]
-
-        def host_step():
-            for _ in range(args.passes):
-                for call in calls:
+            def host_step():
+                for _ in range(runs):
                     call()
+            host_step()
+            assert np.array_equal(yh[COPIES - 1].numpy(), ys[COPIES - 1].cpu().numpy()), \
+                "host-buffer rows differ from the device-resident run"
+            h2d, d2h = runs * K_IN * 4, runs * n_ops * N_OUT * 4
+            api = ("b2w4_chain_run_host: pinned host x uploaded per launch, every GEMV's row "
+                   "stored into pinned host memory by the kernel, one synchronisation per list")
+        else:
+            yh = torch.zeros((1, n_local), dtype=torch.float32).pin_memory()
+            xn, yn = xh.numpy(), yh.numpy()
+            calls = [ctx.bind_matmul_host(w, xn, yn) for w in weights]
+
+            def host_step():
+                for _ in range(args.passes):
+                    for call in calls:
+                        call()
+            h2d, d2h = gemvs * K_IN * 4 * world, gemvs * N_OUT * 4
+            api = "b2w4_matmul_host (pinned host x and y, synchronous)"
         for _ in range(args.warmup):
             host_step()
         if barrier:
@@ -687,10 +869,23 @@ def run_ours(args):
             host_step()
         e2e_s = max_over_ranks((time.perf_counter() - t0) / args.steps)
         line["e2e"] = {"value": gemvs * alg / e2e_s / 1e9, "unit": UNIT,
-                       "h2d_bytes_per_step": gemvs * K_IN * 4 * world,
-                       "d2h_bytes_per_step": gemvs * N_OUT * 4,
-                       "ms_per_step": e2e_s * 1e3,
-                       "api": "b2w4_matmul_host (pinned host x and y, synchronous)"}
+                       "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                       "ms_per_step": e2e_s * 1e3, "api": api}
+        if use_list:
+            # one synchronous host call per GEMV, for comparison
+            yh1 = torch.zeros((1, N_OUT), dtype=torch.float32).pin_memory()
+            calls = [ctx.bind_matmul_host(w, xh.numpy(), yh1.numpy()) for w in weights]
+            for c in calls:
+                c()
+            t0 = time.perf_counter()
+            for _ in range(8):
+                for c in calls:
+                    c()
+            per = (time.perf_counter() - t0) / (8 * COPIES)
+            line["e2e"]["one_host_call_per_gemv"] = {
+                "value": alg / per / 1e9, "unit": UNIT, "us_per_call": per * 1e6,
+                "api": "b2w4_matmul_host"}
+            e_chain.free()
 
     if rank == 0 and world == 1 and not args.headline_only:
         # ---- sweep: batched decode and prefill on the same weight -----------------------
@@ -720,6 +915,8 @@ def run_ours(args):
         sweep["dense4b_decode_matmul_walk"] = decode_walk(torch, pkg, ctx, args)
         sweep["moe30b_layer"] = moe_layer(torch, pkg, ctx, args)
         line["sweep"] = sweep
+        line["gpu_reference"] = gpu_reference(torch, pkg, args, value,
+                                              sweep["m256"]["us_per_matmul"])
 
         # ---- CPU baseline: the reference's own kernel on this box's host cores ----------
         probe, kind, cores, isa = cpu_gemv_seconds(pkg, 1, 16, 8)
@@ -740,7 +937,8 @@ def run_ours(args):
             line["lm_head_greedy_token_tp"] = {"skipped": str(exc)[:200]}
 
     if rank == 0:
-        print(json.dumps(line), flush=True)
+        out.write(json.dumps(line) + "\n")
+        out.flush()
     if world > 1:
         # Tear-down order matters with NCCL work captured in CUDA graphs: drain the device,
         # meet the other ranks, then leave without running NCCL's destructors (they can wait
@@ -770,6 +968,9 @@ def main():
                          "values are for profiling the batched kernels)")
     ap.add_argument("--moe-only", action="store_true",
                     help="run only the MoE layer leg of the sweep (single GPU)")
+    ap.add_argument("--per-launch", action="store_true",
+                    help="time the one-launch-per-GEMV kernel as the headline instead of the "
+                         "persistent list kernel (profiling)")
     ap.add_argument("--headline-only", action="store_true",
                     help="skip the e2e, sweep and CPU-baseline legs (profiling)")
     args = ap.parse_args()
