@@ -285,6 +285,29 @@ typedef struct b2w4_chain_op {
 typedef struct b2w4_chain b2w4_chain;
 int b2w4_chain_create(b2w4_ctx* ctx, const b2w4_chain_op* ops, int count, b2w4_chain** out);
 void b2w4_chain_destroy(b2w4_ctx* ctx, b2w4_chain* chain);
+/* Tensor-parallel form (no counterpart in the reference: one process, one device).
+ * Every rank builds the same list on its row shard of every weight: op i's weight
+ * here holds the rows [n_offset, n_offset + N_shard) of a full row of n_full
+ * values (8-row tiles whole).  The all-gather is inside the kernel: a value is
+ * stored, tagged, into EVERY rank's scratch over the peer mappings, and an op that
+ * consumes an earlier op's output polls its own rank's scratch -- it sees the full
+ * row, exactly as on one GPU, with no collective call and no extra launch; x_offset
+ * and K refer to the full row.  y_peers[p] (optional, all or none) is rank p's
+ * plain fp32 row [n_full] as mapped here: the kernel stores this rank's columns
+ * into every one of them.  y_dev must be NULL.  group->stage_peers[p] is rank p's
+ * scratch: uint64[b2w4_chain_scratch_words(...)], zeroed before the chain is
+ * created, 16-byte aligned, used by this chain only.  Every rank issues the same
+ * sequence of runs.  A rank that runs ahead is held by the bounded waits for its
+ * peers' values; plain y_peers rows of a run are complete on every rank once
+ * every rank has synchronised after that run. */
+typedef struct b2w4_chain_shard {
+    int n_offset, n_full;
+    void* y_peers[8];
+} b2w4_chain_shard;
+int b2w4_chain_create_tp(b2w4_ctx* ctx, const b2w4_chain_op* ops,
+                         const b2w4_chain_shard* shards, int count,
+                         const b2w4_tp_group* group, b2w4_chain** out);
+size_t b2w4_chain_scratch_words(const b2w4_chain_shard* shards, int count);
 /* Asynchronous on the context's stream. */
 int b2w4_chain_run(b2w4_ctx* ctx, b2w4_chain* chain);
 /* One decode step from host memory: x_host[x_len] goes to the chain's input

@@ -25,7 +25,7 @@ SYMBOLS = [
     "b2w4_moe_select_routes", "b2w4_moe_expert_outputs", "b2w4_moe_combine",
     "b2w4_matmul_tp", "b2w4_tp_gather", "b2w4_moe_forward_ep", "b2w4_matmul_argmax",
     "b2w4_matmul_argmax_tp", "b2w4_tp_gather_token",
-    "b2w4_chain_create", "b2w4_chain_destroy", "b2w4_chain_run", "b2w4_chain_run_host",
+    "b2w4_chain_create", "b2w4_chain_create_tp", "b2w4_chain_scratch_words", "b2w4_chain_destroy", "b2w4_chain_run", "b2w4_chain_run_host",
     "b2w4_chain_input", "b2w4_chain_output", "b2w4_chain_weight_bytes", "b2w4_chain_set_trace",
     "b2w4_kernel_launches",
 ]
@@ -44,6 +44,12 @@ class ChainOp(C.Structure):
     _fields_ = [("w", C.c_void_p), ("x_from", C.c_int), ("x_offset", C.c_int),
                 ("x_dev", C.c_void_p), ("y_dev", C.c_void_p), ("activation", C.c_int),
                 ("act_n_begin", C.c_int), ("act_n_len", C.c_int)]
+
+
+class ChainShard(C.Structure):
+    """b2w4_chain_shard: which columns of the full row this rank's shard of an op holds, and
+    (optionally) every rank's plain fp32 row as mapped into this process."""
+    _fields_ = [("n_offset", C.c_int), ("n_full", C.c_int), ("y_peers", C.c_void_p * 8)]
 
 
 class B200W4Error(RuntimeError):
@@ -95,6 +101,10 @@ def lib():
         L.b2w4_moe_forward_ep.argtypes = [vp, f_p, i, i, i, vp, i, i, i, vp, vp, i, i,
                                           C.POINTER(TpGroup), i, f_p, i, vp, f_p]
         L.b2w4_chain_create.argtypes = [vp, C.POINTER(ChainOp), i, C.POINTER(vp)]
+        L.b2w4_chain_create_tp.argtypes = [vp, C.POINTER(ChainOp), C.POINTER(ChainShard), i,
+                                           C.POINTER(TpGroup), C.POINTER(vp)]
+        L.b2w4_chain_scratch_words.argtypes = [C.POINTER(ChainShard), i]
+        L.b2w4_chain_scratch_words.restype = C.c_size_t
         L.b2w4_chain_destroy.argtypes = [vp, vp]
         L.b2w4_chain_destroy.restype = None
         L.b2w4_chain_run.argtypes = [vp, vp]
@@ -140,10 +150,27 @@ class Chain:
     ops: list of dicts with keys w (Weight), and optionally x_from, x_offset, x (torch
     tensor), y (torch tensor), act, act_begin, act_len."""
 
-    def __init__(self, ctx, ops):
+    @staticmethod
+    def shard_table(shards):
+        """shards: list of (n_offset, n_full, [y_peer pointers or None]) -> ChainShard array."""
+        arr = (ChainShard * len(shards))()
+        for i, (off, full, peers) in enumerate(shards):
+            arr[i].n_offset, arr[i].n_full = off, full
+            for p, ptr in enumerate(peers or []):
+                arr[i].y_peers[p] = ptr
+        return arr
+
+    @staticmethod
+    def scratch_words(shard_arr):
+        return int(lib().b2w4_chain_scratch_words(shard_arr, len(shard_arr)))
+
+    def __init__(self, ctx, ops, shards=None, group=None):
+        """shards (a ChainShard array from shard_table) and group (TpGroup whose stage_peers are
+        every rank's zeroed scratch of scratch_words(shards) uint64) select the tensor-parallel
+        form."""
         self.ctx = ctx
         arr = (ChainOp * len(ops))()
-        self.keep = []
+        self.keep = [shards, group]
         for i, o in enumerate(ops):
             arr[i].w = o["w"].handle
             arr[i].x_from = o.get("x_from", -1)
@@ -156,7 +183,11 @@ class Chain:
             arr[i].act_n_len = o.get("act_len", -1)
             self.keep.append((o["w"], x, y))
         h = C.c_void_p()
-        ctx._check(lib().b2w4_chain_create(ctx.handle, arr, len(ops), C.byref(h)))
+        if group is None:
+            ctx._check(lib().b2w4_chain_create(ctx.handle, arr, len(ops), C.byref(h)))
+        else:
+            ctx._check(lib().b2w4_chain_create_tp(ctx.handle, arr, shards, len(ops),
+                                                  C.byref(group), C.byref(h)))
         self.handle = h
         self.count = len(ops)
 

@@ -30,6 +30,7 @@
 #include "b200w4_internal.cuh"
 
 #include <algorithm>
+#include <cstring>
 #include <new>
 #include <vector>
 
@@ -50,8 +51,8 @@ constexpr uint32_t kItemBytesCap = 48 * 1024;
 constexpr int kMaxTeamSize = 8;
 constexpr unsigned long long kChainWaitCycles = 4000000000ull;  // about 2 s
 
-// Device record of one GEMV: one 128-byte line, read into registers once per op and warp.
-// Everything a warp would otherwise have to divide for is precomputed on the host.
+// Device record of one GEMV.  Everything a warp would otherwise have to divide for is
+// precomputed on the host.
 struct __align__(16) ChainOp {
     const uint8_t* nib;
     const uint8_t* scl;
@@ -69,9 +70,16 @@ struct __align__(16) ChainOp {
     int activation, act_n_begin, act_n_len;
     int ipt;                             // iterations (4 groups) per tile
     int reuse_x;                         // same input vector as the op before: already quantised
-    int pad_[3];
+    // Tensor-parallel form (world >= 1; 0 = off): this rank holds the rows [n_offset, n_offset + n) of
+    // the full row; the tagged words go to every rank's scratch at word tag_off + row, the
+    // plain values (optional) to every rank's y at n_offset + row.
+    int world, n_offset;
+    int pad_;
+    unsigned long long tag_off;          // word offset of this op's shard in a rank's scratch
+    float* y_peers[kTpMaxWorld];
 };
-static_assert(sizeof(ChainOp) == 128, "one line per op record");
+static_assert(sizeof(ChainOp) == 208, "op record size");
+constexpr int kOpRecordQuads = sizeof(ChainOp) / 16;
 
 struct ChainArgs {
     const ChainOp* ops;
@@ -88,6 +96,7 @@ struct ChainArgs {
     // op's last copy, 7 cycles the producer waited for ring space during the op.
     long long* trace;
     int trace_cta;
+    unsigned long long* scratch_peers[kTpMaxWorld];  // every rank's tagged scratch (world > 1)
 };
 constexpr int kTraceSlots = 8;
 
@@ -235,15 +244,16 @@ __device__ __forceinline__ void tile_range(const ChainOp& op, int c, int& t0, in
     t0 = c * op.tiles_q + min(c, op.tiles_r);
     t1 = t0 + op.tiles_q + (c < op.tiles_r ? 1 : 0);
 }
-// The op record into registers: eight independent 16-byte loads.
+// The op record into registers: independent 16-byte loads.
 __device__ __forceinline__ ChainOp load_op(const ChainOp* p) {
-    union {
+    union U {
         ChainOp op;
-        uint4 q[8];
+        uint4 q[kOpRecordQuads];
+        __device__ U() {}
     } u;
     const uint4* src = reinterpret_cast<const uint4*>(p);
 #pragma unroll
-    for (int i = 0; i < 8; ++i)
+    for (int i = 0; i < kOpRecordQuads; ++i)
         u.q[i] = __ldg(src + i);
     return u.op;
 }
@@ -565,6 +575,7 @@ __global__ void __launch_bounds__(kChainThreads, 1) gemv_chain_kernel(const Chai
         const int n_out = op.n, act = op.activation, act_b = op.act_n_begin, act_l = op.act_n_len;
         unsigned long long* const y_tag = op.y_tag;
         float* const y_ext = op.y_ext;
+        const int world = op.world;
 
         if (traced)
             ts1 = clock64();
@@ -668,9 +679,25 @@ __global__ void __launch_bounds__(kChainThreads, 1) gemv_chain_kernel(const Chai
                     if (n < n_out) {
                         if (b2w4_act_applies(n, act, act_b, act_l, n_out))
                             acc = chain_activation(acc, act);
-                        y_tag[n] = ((unsigned long long)tag_out << 32) | __float_as_uint(acc);
-                        if (y_ext)
-                            y_ext[n] = acc;
+                        const unsigned long long word =
+                            ((unsigned long long)tag_out << 32) | __float_as_uint(acc);
+                        if (world == 0) {
+                            y_tag[n] = word;
+                            if (y_ext)
+                                y_ext[n] = acc;
+                        } else {
+                            // the all-gather is this store: every rank's scratch (this one's
+                            // included) gets the tagged word over the peer mappings, and a
+                            // consumer op on any rank polls its own scratch as on one GPU
+                            const unsigned long long at = op.tag_off + (unsigned)n;
+#pragma unroll
+                            for (int p = 0; p < kTpMaxWorld; ++p)
+                                if (p < world) {
+                                    a.scratch_peers[p][at] = word;
+                                    if (op.y_peers[p])
+                                        op.y_peers[p][op.n_offset + n] = acc;
+                                }
+                        }
                     }
                 }
             }
@@ -710,6 +737,9 @@ struct b2w4_chain {
     size_t weight_bytes = 0;
     long long* trace = nullptr;  // profiling hook, see ChainArgs
     int trace_cta = 0;
+    // tensor-parallel form: the tagged scratch belongs to the caller (peer-mapped buffers)
+    int world = 1;
+    unsigned long long* scratch_peers[kTpMaxWorld] = {nullptr};
 };
 
 namespace {
@@ -734,20 +764,33 @@ int chain_team_size(int tiles, int groups, int ctas) {
 
 }  // namespace
 
-extern "C" {
+namespace {
 
-int b2w4_chain_create(b2w4_ctx* ctx, const b2w4_chain_op* ops, int count, b2w4_chain** out) {
+// Builds a chain; shards / group are null for one GPU.
+int chain_create(b2w4_ctx* ctx, const b2w4_chain_op* ops, const b2w4_chain_shard* shards,
+                 const b2w4_tp_group* group, int count, b2w4_chain** out) {
     if (!ctx || !out)
         return B2W4_E_INVALID;
     *out = nullptr;
     if (!ops || count < 1 || count > 4096)
         return b2w4_fail(ctx, B2W4_E_INVALID, "chain: 1..4096 ops (got %d)", count);
+    const bool tp = group != nullptr;
+    if (tp) {
+        if (!shards || group->world < 1 || group->world > kTpMaxWorld || group->rank < 0 ||
+            group->rank >= group->world)
+            return b2w4_fail(ctx, B2W4_E_INVALID, "chain_tp: bad group or no shard table");
+        for (int p = 0; p < group->world; ++p)
+            if (!group->stage_peers[p] || (reinterpret_cast<uintptr_t>(group->stage_peers[p]) & 15))
+                return b2w4_fail(ctx, B2W4_E_INVALID, "chain_tp: null or unaligned scratch of rank %d",
+                                 p);
+    }
     std::vector<ChainOp> dev(count);
     std::vector<size_t> y_at(count);
     size_t words = 0;
     int kmax = 0, x_in_len = 0;
     uint32_t max_item = 0;
     size_t weight_bytes = 0;
+    auto full_n = [&](int i) { return tp ? shards[i].n_full : ops[i].w->n; };
     for (int i = 0; i < count; ++i) {
         const b2w4_chain_op& o = ops[i];
         if (!o.w)
@@ -755,16 +798,22 @@ int b2w4_chain_create(b2w4_ctx* ctx, const b2w4_chain_op* ops, int count, b2w4_c
         if (o.activation < B2W4_NONE || o.activation > B2W4_RELU_SQUARED)
             return b2w4_fail(ctx, B2W4_E_INVALID, "chain: op %d: unknown activation %d", i,
                              o.activation);
+        if (tp && (shards[i].n_offset < 0 || shards[i].n_offset + o.w->n > shards[i].n_full ||
+                   o.y_dev))
+            return b2w4_fail(ctx, B2W4_E_INVALID,
+                             "chain_tp: op %d: rows [%d, %d) of %d (and y_dev must be NULL: plain "
+                             "rows go to y_peers)", i, shards[i].n_offset,
+                             shards[i].n_offset + o.w->n, shards[i].n_full);
         if (o.x_from >= i || o.x_from < -1)
             return b2w4_fail(ctx, B2W4_E_INVALID,
                              "chain: op %d takes its input from op %d (must be an earlier op, "
                              "or -1 for x_dev / the chain's input vector)", i, o.x_from);
-        if (o.x_from >= 0 && (o.x_offset < 0 || o.x_offset + o.w->k > ops[o.x_from].w->n))
+        if (o.x_from >= 0 && (o.x_offset < 0 || o.x_offset + o.w->k > full_n(o.x_from)))
             return b2w4_fail(ctx, B2W4_E_INVALID,
                              "chain: op %d reads [%d, %d) of op %d's %d outputs", i, o.x_offset,
-                             o.x_offset + o.w->k, o.x_from, ops[o.x_from].w->n);
+                             o.x_offset + o.w->k, o.x_from, full_n(o.x_from));
         y_at[i] = words;
-        words += (size_t)((o.w->n + 1) & ~1);  // 16-byte aligned rows
+        words += (size_t)((full_n(i) + 1) & ~1);  // 16-byte aligned rows
         kmax = std::max(kmax, o.w->k);
         if (o.x_from < 0 && !o.x_dev)
             x_in_len = std::max(x_in_len, o.w->k);
@@ -791,10 +840,20 @@ int b2w4_chain_create(b2w4_ctx* ctx, const b2w4_chain_op* ops, int count, b2w4_c
     c->weight_bytes = weight_bytes;
     c->x_in_len = x_in_len;
     const b2w4_chain_op& last = ops[count - 1];
-    c->y_out_len = last.y_dev ? 0 : last.w->n;
-    cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&c->tagged), words * 8);
-    if (e == cudaSuccess)
-        e = cudaMemset(c->tagged, 0, words * 8);
+    c->y_out_len = (last.y_dev || tp) ? 0 : last.w->n;
+    cudaError_t e = cudaSuccess;
+    unsigned long long* scratch = nullptr;
+    if (tp) {
+        c->world = group->world;
+        for (int p = 0; p < group->world; ++p)
+            c->scratch_peers[p] = static_cast<unsigned long long*>(group->stage_peers[p]);
+        scratch = c->scratch_peers[group->rank];
+    } else {
+        e = cudaMalloc(reinterpret_cast<void**>(&c->tagged), words * 8);
+        if (e == cudaSuccess)
+            e = cudaMemset(c->tagged, 0, words * 8);
+        scratch = c->tagged;
+    }
     if (e == cudaSuccess)
         e = cudaMalloc(reinterpret_cast<void**>(&c->ops_dev), sizeof(ChainOp) * count);
     if (e == cudaSuccess && c->x_in_len)
@@ -808,18 +867,16 @@ int b2w4_chain_create(b2w4_ctx* ctx, const b2w4_chain_op* ops, int count, b2w4_c
     for (int i = 0; i < count; ++i) {
         const b2w4_chain_op& o = ops[i];
         ChainOp& d = dev[i];
+        memset(&d, 0, sizeof(d));
         d.nib = reinterpret_cast<const uint8_t*>(o.w->nib);
         d.scl = reinterpret_cast<const uint8_t*>(o.w->scl);
-        d.x_ext = nullptr;
-        d.x_tag = nullptr;
-        d.tag_in = 0;
         if (o.x_from >= 0) {
-            d.x_tag = c->tagged + y_at[o.x_from] + o.x_offset;
+            d.x_tag = scratch + y_at[o.x_from] + o.x_offset;
             d.tag_in = (unsigned)o.x_from + 1u;
         } else {
             d.x_ext = o.x_dev ? o.x_dev : c->x_in;
         }
-        d.y_tag = c->tagged + y_at[i];
+        d.y_tag = scratch + y_at[i];
         d.y_ext = o.y_dev ? o.y_dev : (i == count - 1 ? c->y_out : nullptr);
         d.n = o.w->n;
         d.groups = o.w->groups;
@@ -842,7 +899,13 @@ int b2w4_chain_create(b2w4_ctx* ctx, const b2w4_chain_op* ops, int count, b2w4_c
         d.reuse_x = i > 0 && o.x_from < 0 && ops[i - 1].x_from < 0 &&
                     (o.x_dev ? o.x_dev : c->x_in) == (ops[i - 1].x_dev ? ops[i - 1].x_dev : c->x_in) &&
                     o.w->k == ops[i - 1].w->k;
-        d.pad_[0] = d.pad_[1] = d.pad_[2] = 0;
+        d.world = tp ? group->world : 0;  // 0: the one-GPU epilogue
+        if (tp) {
+            d.n_offset = shards[i].n_offset;
+            d.tag_off = y_at[i] + (size_t)shards[i].n_offset;
+            for (int p = 0; p < group->world; ++p)
+                d.y_peers[p] = static_cast<float*>(shards[i].y_peers[p]);
+        }
     }
     e = cudaMemcpy(c->ops_dev, dev.data(), sizeof(ChainOp) * count, cudaMemcpyHostToDevice);
     if (e != cudaSuccess) {
@@ -852,6 +915,28 @@ int b2w4_chain_create(b2w4_ctx* ctx, const b2w4_chain_op* ops, int count, b2w4_c
     }
     *out = c;
     return B2W4_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int b2w4_chain_create(b2w4_ctx* ctx, const b2w4_chain_op* ops, int count, b2w4_chain** out) {
+    return chain_create(ctx, ops, nullptr, nullptr, count, out);
+}
+
+int b2w4_chain_create_tp(b2w4_ctx* ctx, const b2w4_chain_op* ops, const b2w4_chain_shard* shards,
+                         int count, const b2w4_tp_group* group, b2w4_chain** out) {
+    if (!group)
+        return ctx ? b2w4_fail(ctx, B2W4_E_INVALID, "chain_tp: no group") : B2W4_E_INVALID;
+    return chain_create(ctx, ops, shards, group, count, out);
+}
+
+size_t b2w4_chain_scratch_words(const b2w4_chain_shard* shards, int count) {
+    size_t words = 0;
+    for (int i = 0; shards && i < count; ++i)
+        words += (size_t)((shards[i].n_full + 1) & ~1);
+    return words;
 }
 
 void b2w4_chain_destroy(b2w4_ctx* ctx, b2w4_chain* c) {
@@ -877,6 +962,10 @@ int b2w4_chain_run(b2w4_ctx* ctx, b2w4_chain* c) {
         return b2w4_fail(ctx, B2W4_E_INVALID, "chain_run: no chain, or a chain of another device");
     // tags: one per op and run; when the 32-bit space runs out the scratch goes back to zero
     if (c->next_tag > 0xFFFFFFFFu - (unsigned)c->count - 1u) {
+        if (c->world > 1)  // the scratch is the caller's and every rank would have to agree
+            return b2w4_fail(ctx, B2W4_E_INVALID,
+                             "chain_run: tag space of a tensor-parallel chain exhausted; "
+                             "recreate the chain on zeroed scratch buffers");
         B2W4_CUDA(ctx, cudaMemsetAsync(c->tagged, 0, c->tagged_words * 8, ctx->stream));
         c->next_tag = 0;
     }
@@ -890,6 +979,8 @@ int b2w4_chain_run(b2w4_ctx* ctx, b2w4_chain* c) {
     a.kmax = c->kmax;
     a.trace = c->trace;
     a.trace_cta = c->trace_cta;
+    for (int p = 0; p < kTpMaxWorld; ++p)
+        a.scratch_peers[p] = c->scratch_peers[p];
     c->next_tag += (unsigned)c->count;
     static b2w4_smem_optin configured;
     B2W4_CUDA(ctx, b2w4_opt_in_smem(ctx, gemv_chain_kernel, c->smem_bytes, configured));

@@ -175,3 +175,93 @@ def test_bad_lists_are_refused(ctx):
     with pytest.raises(pkg.capi.B200W4Error):
         pkg.capi.Chain(ctx, [])
     w.free()
+
+
+def _tp_rank_chains(world, shapes_full, x, seed):
+    """The ranks of a tensor-parallel group as contexts on this one GPU: per rank its row
+    shards of every weight, its scratch and its plain rows; every rank's chain stores into all
+    ranks' buffers.  Ops all take the device vector x (no rank waits for another)."""
+    import torch
+    ctxs = [pkg.capi.Context(0) for _ in range(world)]
+    blocks = [pkg.synth.bg128_weight(20261125, seed + i, n, k) for i, (n, k) in enumerate(shapes_full)]
+    rows = [[torch.full((1, n), -1.0, dtype=torch.float32, device="cuda") for (n, k) in shapes_full]
+            for _ in range(world)]
+    tables, scratches = [], []
+    for r in range(world):
+        sh = []
+        for i, (n, k) in enumerate(shapes_full):
+            _, n_local, lo = pkg.shard.shard_blocks(blocks[i], n, k, r, world)
+            sh.append((lo, n, [rows[p][i].data_ptr() for p in range(world)]))
+        tables.append(pkg.capi.Chain.shard_table(sh))
+    words = pkg.capi.Chain.scratch_words(tables[0])
+    scratches = [torch.zeros((words,), dtype=torch.int64, device="cuda") for _ in range(world)]
+    chains, keep = [], []
+    for r in range(world):
+        group = pkg.capi.TpGroup()
+        group.rank, group.world = r, world
+        for p in range(world):
+            group.stage_peers[p] = scratches[p].data_ptr()
+        ops = []
+        for i, (n, k) in enumerate(shapes_full):
+            shard, n_local, lo = pkg.shard.shard_blocks(blocks[i], n, k, r, world)
+            w = ctxs[r].upload_weight(np.ascontiguousarray(shard), n_local, k)
+            keep.append(w)
+            ops.append(dict(w=w, x=x))
+        chains.append(pkg.capi.Chain(ctxs[r], ops, tables[r], group))
+    return ctxs, chains, rows, blocks, scratches, keep
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_tensor_parallel_list_rebuilds_full_rows_on_every_rank(world):
+    import torch
+    shapes = [(1024, 512), (2560, 512), (9728, 512)]
+    x_np = pkg.synth.activations(7, 800, 1, 512)
+    x = torch.from_numpy(x_np).cuda()
+    ctxs, chains, rows, blocks, scratches, keep = _tp_rank_chains(world, shapes, x, 800)
+    for run in range(2):
+        for r in range(world):
+            chains[r].run()
+        for r in range(world):
+            ctxs[r].sync()
+        for i, (n, k) in enumerate(shapes):
+            want = ol.matmul_w4(blocks[i], n, k, x_np)
+            for r in range(world):
+                assert np.array_equal(_bits(rows[r][i].cpu().numpy()), _bits(want)), (run, r, i)
+            rows[0][i].fill_(-1.0) if run == 0 else None
+    for c in chains:
+        c.free()
+    for w in keep:
+        w.free()
+    for c in ctxs:
+        c.close()
+
+
+def test_tensor_parallel_form_with_one_rank_and_dependent_ops(ctx):
+    """world == 1 runs the peer-store epilogue and the scratch supplied by the caller with ops
+    that consume earlier ops' rows (several ranks of such a list cannot share one GPU: they
+    wait for one another)."""
+    import torch
+    shapes = [(1024, 512), (512, 1024), (264, 512)]
+    blocks = [pkg.synth.bg128_weight(20261125, 820 + i, n, k) for i, (n, k) in enumerate(shapes)]
+    ws = [ctx.upload_weight(b, n, k) for b, (n, k) in zip(blocks, shapes)]
+    x_np = pkg.synth.activations(7, 820, 1, 512)
+    x = torch.from_numpy(x_np).cuda()
+    rows = [torch.full((1, n), -1.0, dtype=torch.float32, device="cuda") for (n, k) in shapes]
+    table = pkg.capi.Chain.shard_table([(0, n, [rows[i].data_ptr()]) for i, (n, k) in enumerate(shapes)])
+    scratch = torch.zeros((pkg.capi.Chain.scratch_words(table),), dtype=torch.int64, device="cuda")
+    group = pkg.capi.TpGroup()
+    group.rank, group.world = 0, 1
+    group.stage_peers[0] = scratch.data_ptr()
+    ops = [dict(w=ws[0], x=x), dict(w=ws[1], x_from=0), dict(w=ws[2], x_from=1)]
+    chain = pkg.capi.Chain(ctx, ops, table, group)
+    chain.run()
+    ctx.sync()
+    cur = x_np
+    for i, (n, k) in enumerate(shapes):
+        cur = ol.matmul_w4(blocks[i], n, k, cur[:, :k])
+        assert np.array_equal(_bits(rows[i].cpu().numpy()), _bits(cur)), i
+    with pytest.raises(pkg.capi.B200W4Error):  # plain rows of a sharded op go to y_peers
+        pkg.capi.Chain(ctx, [dict(w=ws[0], x=x, y=rows[0])], table, group)
+    chain.free()
+    for w in ws:
+        w.free()
