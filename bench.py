@@ -45,6 +45,8 @@ N_OUT, K_IN = 9728, 2560
 COPIES = 32   # distinct weight buffers walked by one pass
 PASSES = 16   # passes per list: one persistent-kernel launch = PASSES * COPIES GEMVs
 RUNS_PER_STEP = 20  # launches of the list per step (a step is about 25 ms of device time)
+DEP_RESTART = 16    # a dependent list restarts from x every so many GEMVs (the rows grow by a
+                    # factor of up to twenty per GEMV; fp32 carries sixteen of them)
 SEED_W, SEED_X = 20261125, 7
 METRIC, UNIT = "w4g128_gemv_hbm_gbs", "GB/s"
 L2_MB = 126
@@ -701,6 +703,78 @@ def run_ours(args):
             return keep
         return replay
 
+    def make_list_step_tp(passes=args.passes, dependent=False):
+        """The walk as the persistent list kernel on every rank's row shards: each GEMV's
+        values go, tagged and as plain fp32, into EVERY rank's buffers over peer mappings
+        (symmetric memory) from the kernel's epilogue -- the all-gather is those stores -- so
+        every rank ends with the full rows and an op that consumes an earlier op's row polls
+        its own scratch.  No collective call, no extra launch.  Checked bit for bit against
+        the shards' NCCL all-gather before it is timed.  Returns (step, ops per launch) or
+        None."""
+        try:
+            import torch.distributed._symmetric_memory as symm
+            n_ops = COPIES * passes
+            rows = symm.empty((COPIES, N_OUT), dtype=torch.float32, device=f"cuda:{local}")
+            rows.fill_(-1.0)
+            table = pkg.capi.Chain.shard_table(
+                [(rank * n_local, N_OUT, None) for _ in range(n_ops)])
+            words = pkg.capi.Chain.scratch_words(table)
+            scratch = symm.empty((words,), dtype=torch.int64, device=f"cuda:{local}")
+            scratch.zero_()
+            torch.cuda.synchronize()
+            hr = symm.rendezvous(rows, dist.group.WORLD.group_name)
+            hs = symm.rendezvous(scratch, dist.group.WORLD.group_name)
+        except Exception as exc:  # no peer mappings on this box
+            print(f"tensor-parallel list unavailable: {exc}", file=sys.stderr)
+            return None
+        table = pkg.capi.Chain.shard_table(
+            [(rank * n_local, N_OUT,
+              [hr.buffer_ptrs[p] + (i % COPIES) * N_OUT * 4 for p in range(world)])
+             for i in range(n_ops)])
+        group = pkg.capi.TpGroup()
+        group.rank, group.world = rank, world
+        for p_ in range(world):
+            group.stage_peers[p_] = hs.buffer_ptrs[p_]
+        x, y_local, y_full = make_io(1)
+        if dependent:
+            ops = [dict(w=weights[i % COPIES], x=x) if i % DEP_RESTART == 0 else
+                   dict(w=weights[i % COPIES], x_from=i - 1) for i in range(n_ops)]
+        else:
+            ops = [dict(w=weights[i % COPIES], x=x) for i in range(n_ops)]
+        chain = pkg.capi.Chain(ctx, ops, table, group)
+        dist.barrier()
+        ok = True
+        try:
+            chain.run()
+            ctx.sync()
+        except pkg.capi.B200W4Error as exc:
+            print(f"tensor-parallel list failed: {exc}", file=sys.stderr)
+            ok = False
+        torch.cuda.synchronize()
+        dist.barrier()  # every rank's stores of the run have landed
+        if ok:  # full rows on this rank == all-gather of the shards' rows, bit for bit
+            cur = x
+            for i in range(COPIES if dependent else 2):
+                if i % DEP_RESTART == 0:
+                    cur = x
+                ctx.matmul(weights[i], cur[:, :K_IN].contiguous(), y_local)
+                dist.all_gather_into_tensor(y_full, y_local)
+                torch.cuda.synchronize()
+                want = y_full.permute(1, 0, 2).reshape(1, N_OUT).contiguous()
+                ok = ok and torch.equal(rows[i:i + 1].view(torch.int32), want.view(torch.int32))
+                if dependent:
+                    cur = want.clone()
+        if not all_ranks_agree(ok):
+            print("tensor-parallel list and all-gather disagree: not used", file=sys.stderr)
+            return None
+        keep = (rows, scratch, hr, hs, group, table, chain)
+
+        def step():
+            for _ in range(RUNS_PER_STEP):
+                chain.run()
+            return keep
+        return step, n_ops
+
     def max_over_ranks(v):
         if world == 1:
             return v
@@ -766,21 +840,51 @@ def run_ours(args):
         ms = max_over_ranks(ms)
         exchange = "none (one GPU)" if world == 1 else "NCCL all-gather after every GEMV"
         nccl_ms = None
-        if world > 1 and args.rows <= 8 and not args.no_graph and world <= 8:
-            peer_step = make_peer_step()
-            if peer_step is not None:
-                nccl_ms = ms
-                with ClockSampler(local) as clocks:
-                    ms = time_steps(torch, peer_step, args.steps, args.warmup, barrier)
-                ms = max_over_ranks(ms)
-                exchange = ("in the GEMV kernel: tagged 8-byte peer stores into every rank's "
-                            "staging buffer, gather kernel with a bounded wait")
         gemvs = COPIES * args.passes
         kernel_name = "gemv_w4a8_kernel"
         launch_desc = None
         alg_per_launch = algorithmic_bytes(n_local, K_IN, 1)
         launch_us = ms * 1e3 / gemvs
         traffic = NCU_DRAM_BYTES_PER_LAUNCH if world == 1 else None
+        if world > 1 and args.rows <= 8 and not args.no_graph and world <= 8:
+            nccl_ms = ms
+            peer_step = make_peer_step()
+            if peer_step is not None:
+                p_ms = max_over_ranks(time_steps(torch, peer_step, args.steps, args.warmup,
+                                                 barrier))
+                variants["one_launch_per_gemv_exchange_in_kernels"] = {
+                    "value": gemvs * alg / (p_ms * 1e-3) / 1e9, "unit": UNIT,
+                    "us_per_gemv": p_ms * 1e3 / gemvs,
+                    "what": "GEMV kernel stores tagged words to every rank, gather kernel after it"}
+                ms = p_ms
+                launch_us = ms * 1e3 / gemvs
+                exchange = ("in the GEMV kernel: tagged 8-byte peer stores into every rank's "
+                            "staging buffer, gather kernel with a bounded wait")
+            tp_list = make_list_step_tp() if args.rows == 1 else None
+            if tp_list is not None:
+                tp_step, n_ops = tp_list
+                with ClockSampler(local) as clocks:
+                    ms = max_over_ranks(time_steps(torch, tp_step, args.steps, args.warmup,
+                                                   barrier))
+                launches_per_step = RUNS_PER_STEP
+                gemvs = n_ops * RUNS_PER_STEP
+                kernel_name = "gemv_chain_kernel"
+                launch_desc = (f"{RUNS_PER_STEP} launches of one persistent cooperative kernel "
+                               f"per step and rank, each a list of {n_ops} GEMVs on this "
+                               f"rank's row shards")
+                alg_per_launch = algorithmic_bytes(n_local, K_IN, 1) * n_ops
+                launch_us = ms * 1e3 / RUNS_PER_STEP
+                exchange = ("in the list kernel's epilogue: every value stored, tagged and "
+                            "plain, into every rank's buffers over peer mappings")
+                dep = make_list_step_tp(dependent=True)
+                if dep is not None:
+                    d_ms = max_over_ranks(time_steps(torch, dep[0], max(3, min(args.steps, 10)),
+                                                     3, barrier))
+                    variants["list_with_dependent_gemvs"] = {
+                        "value": dep[1] * RUNS_PER_STEP * alg / (d_ms * 1e-3) / 1e9,
+                        "unit": UNIT, "us_per_gemv": d_ms * 1e3 / (dep[1] * RUNS_PER_STEP),
+                        "what": "each GEMV reads the full row of its predecessor, which every "
+                                "rank's epilogue stored into this rank's scratch"}
     value = gemvs * alg / (ms * 1e-3) / 1e9
     achieved = alg_per_launch / (launch_us * 1e-6) / 1e9
 
@@ -803,15 +907,18 @@ def run_ours(args):
     if world > 1:
         line["config"]["parallelism"] += f"; timed exchange: {exchange}"
     if nccl_ms is not None:
-        line["nccl_allgather_variant"] = {"value": gemvs * alg / (nccl_ms * 1e-3) / 1e9,
-                                          "unit": UNIT, "ms_per_step": nccl_ms}
-        line["gpu_launches"] = 2 * launches_per_step * args.steps  # GEMV + gather kernel
+        line["nccl_allgather_variant"] = {
+            "value": COPIES * args.passes * alg / (nccl_ms * 1e-3) / 1e9, "unit": UNIT,
+            "ms_per_step": nccl_ms,
+            "what": "one launch per GEMV, NCCL all-gather of y after every GEMV"}
+    if world > 1 and variants:
+        line["variants"] = variants
 
     if use_list and not args.headline_only:
         # ---- the same GEMVs two other ways ------------------------------------------------
         # (a) every GEMV consumes the first K outputs of its predecessor (a decode step's data
-        #     dependency; the chain restarts from x every COPIES GEMVs to stay inside fp32)
-        dep_ops = [dict(w=weights[i % COPIES], x=x) if i % COPIES == 0 else
+        #     dependency; the chain restarts from x every DEP_RESTART GEMVs to stay inside fp32)
+        dep_ops = [dict(w=weights[i % COPIES], x=x) if i % DEP_RESTART == 0 else
                    dict(w=weights[i % COPIES], x_from=i - 1) for i in range(n_ops)]
         dep = pkg.capi.Chain(ctx, dep_ops)
         d_ms = time_steps(torch, dep.run, max(3, min(args.steps, 20)), 3)
