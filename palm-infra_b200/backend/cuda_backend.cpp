@@ -1,4 +1,4 @@
-// CudaBackend for mollm, rebuilt on libb200w4: a from-scratch implementation of the class
+// CudaBackend for mollm, rebuilt on libb200w4: an implementation of the class
 // the reference declares in engine/cuda_backend.h (which this file includes from the
 // reference tree; the engine constructs the backend by that name, engine/model_loader.cpp:
 // 1085, and the reference's tests drive it directly).
@@ -65,6 +65,46 @@ bool is_moe_qwen3(const GraphNode& node, const std::vector<const Tensor*>& in) {
            hash_in < 0 && in[1]->prec == Precision::FP16 && in[0]->prec == Precision::FP32;
 }
 
+// The three view operators as one descriptor transform.  `out` arrives carrying the shape
+// the executor planned for the node and leaves as a window onto src's storage (same host
+// pointer base, same device allocation); false = not a view this backend can express.
+//   RESHAPE  contiguous source only: src's storage, the planned shape, dense strides
+//   PERMUTE  params i32[0..3]: source dimension d becomes dimension axis[d]
+//   SLICE    params i32 = dim, offset, size: the window starts offset * stride[dim] bytes in
+// (engine/cuda_backend.cu:733-780 is the contract the executor relies on.)
+bool describe_view(const GraphNode& node, const Tensor& src, Tensor* out) {
+    Tensor v = src;
+    switch (node.op_type) {
+    case OpType::RESHAPE:
+        if (!src.is_contiguous())
+            return false;
+        std::copy(out->shape, out->shape + 4, v.shape);
+        v.compute_strides();
+        break;
+    case OpType::PERMUTE:
+        for (int d = 0; d < 4; ++d) {
+            const int to = graph_params::get_i32(node.params, d, d);
+            v.shape[to] = src.shape[d];
+            v.stride[to] = src.stride[d];
+        }
+        break;
+    case OpType::SLICE: {
+        const int dim = graph_params::get_i32(node.params, 0, 0);
+        const size_t skip =
+            static_cast<size_t>(graph_params::get_i32(node.params, 1, 0)) * src.stride[dim];
+        v.shape[dim] = graph_params::get_i32(node.params, 2, static_cast<int>(src.shape[dim]));
+        v.device_offset = src.device_offset + skip;
+        if (src.data)
+            v.data = static_cast<uint8_t*>(src.data) + skip;
+        break;
+    }
+    default:
+        return false;
+    }
+    *out = v;
+    return true;
+}
+
 }  // namespace
 
 struct CudaBackend::Impl {
@@ -97,6 +137,7 @@ struct CudaBackend::Impl {
     void* lm_out = nullptr;
     size_t lm_out_cap = 0;
     std::unordered_map<uint32_t, uint64_t> native_ops, fallback_ops;
+    int multi_row_rule = B2W4_ACT_G32;
 
     bool cuda(cudaError_t e, const char* what) {
         if (e == cudaSuccess)
@@ -127,6 +168,105 @@ struct CudaBackend::Impl {
         auto it = mirrors.find(t.device_data);
         return it == mirrors.end() ? nullptr : &it->second;
     }
+    // The explicit reference bridge for operators with no native kernel: every input that
+    // lives on the device is staged into a host buffer this object owns, the reference's
+    // CPUBackend runs on host descriptors, and then everything that was staged goes back --
+    // the inputs too, because reference kernels update caches and recurrent state in place --
+    // followed by the output.  Weights are never staged: W4G32 descriptors are pointed at the
+    // backend's own copy of the blocks, other weights at the caller's host bytes.
+    class HostBridge {
+      public:
+        HostBridge(CudaBackend& backend, Impl& impl) : be_(backend), im_(impl) {}
+
+        bool bring_in(const std::vector<const Tensor*>& inputs) {
+            host_.resize(inputs.size());
+            slot_.assign(inputs.size(), -1);
+            args_.assign(inputs.size(), nullptr);
+            for (size_t i = 0; i < inputs.size(); ++i) {
+                if (!inputs[i])
+                    continue;
+                Tensor& h = host_[i];
+                h = *inputs[i];
+                if (!host_view_of(*inputs[i], h, static_cast<int>(i)))
+                    return false;
+                h.device_data = nullptr;
+                h.device_offset = 0;
+                args_[i] = &h;
+            }
+            return true;
+        }
+
+        bool run(const GraphNode& node, const Tensor* output, ThreadPool* pool) {
+            out_ = *output;
+            out_on_device_ = output->device_data != nullptr;
+            if (out_on_device_) {  // produced in a host buffer, copied over afterwards
+                out_bytes_ = output->view_span_bytes();
+                out_buf_.assign((out_bytes_ + 7) / 8, 0);
+                out_.data = out_buf_.data();
+                out_.device_data = nullptr;
+                out_.device_offset = 0;
+            }
+            im_.cpu.clear_dispatch_error();
+            im_.cpu.dispatch(node, args_, &out_, pool);
+            if (im_.cpu.dispatch_failed())
+                im_.failed = true;
+            return !im_.failed;
+        }
+
+        bool send_back(const std::vector<const Tensor*>& inputs, Tensor* output) {
+            for (size_t i = 0; i < inputs.size(); ++i)
+                if (slot_[i] >= 0) {
+                    Tensor& dst = *const_cast<Tensor*>(inputs[i]);
+                    if (!be_.copy_from_host(bufs_[static_cast<size_t>(slot_[i])].data(), dst,
+                                            dst.view_span_bytes()))
+                        return false;
+                }
+            if (!out_on_device_)
+                return true;  // a host-resident output was written in place
+            return out_.data == out_buf_.data() &&
+                   be_.copy_from_host(out_.data, *output, out_bytes_);
+        }
+
+      private:
+        // points h.data at host bytes that hold what `dev` holds
+        bool host_view_of(const Tensor& dev, Tensor& h, int index) {
+            if (!im_.is_device_weight(dev)) {
+                if (!dev.device_data)
+                    return true;  // already a host tensor
+                const size_t bytes = dev.view_span_bytes();
+                bufs_.emplace_back((bytes + 7) / 8);
+                slot_[static_cast<size_t>(index)] = static_cast<int>(bufs_.size() - 1);
+                h.data = bufs_.back().data();
+                return be_.copy_to_host(dev, h.data, bytes);
+            }
+            auto g32 = im_.g32_by_handle.find(dev.device_data);
+            if (g32 != im_.g32_by_handle.end()) {
+                uint8_t* blocks = const_cast<uint8_t*>(g32->second->data()) + dev.device_offset;
+                h.data = blocks;
+                h.q4_g32_data = blocks;
+                h.rowmajor_data = blocks;
+                return true;
+            }
+            if (!h.data) {
+                std::fprintf(stderr, "CudaBackend: fallback lacks host weight storage\n");
+                im_.failed = true;
+                return false;
+            }
+            return true;
+        }
+
+        CudaBackend& be_;
+        Impl& im_;
+        std::vector<Tensor> host_;
+        std::vector<const Tensor*> args_;
+        std::vector<std::vector<uint64_t>> bufs_;
+        std::vector<int> slot_;
+        Tensor out_;
+        std::vector<uint64_t> out_buf_;
+        size_t out_bytes_ = 0;
+        bool out_on_device_ = false;
+    };
+
     ~Impl() {
         if (ctx)
             b2w4_sync(ctx);
@@ -158,6 +298,9 @@ CudaBackend::CudaBackend() : impl_(std::make_unique<Impl>()) {
     impl_->ok = b2w4_ctx_create(0, &impl_->ctx) == B2W4_OK;
     if (!impl_->ok)
         impl_->ctx = nullptr;
+    const char* rule = std::getenv("MOLLM_B200_MULTI_ROW_RULE");
+    if (rule && std::atoi(rule) == 128)
+        impl_->multi_row_rule = B2W4_ACT_G128;
 }
 
 CudaBackend::~CudaBackend() = default;
@@ -379,36 +522,39 @@ void CudaBackend::begin_graph() {}
 
 void CudaBackend::end_graph() { synchronize_for_host_read(); }
 
+// Persistent tensors (KV caches, recurrent state), zero-filled.  What the host may touch
+// decides where the bytes live (engine/accelerator_backend.h:61-64; the reference's test pins
+// the three cases, tests/test_cuda_backend.cpp:810-839):
+//   FULL             managed memory, the host pointer IS the device pointer
+//   MIRRORED_PREFIX  device memory plus a host copy of the first `prefix` bytes, which is what
+//                    the host pointer shows and what copy_from_host / zero_tensor keep in step
+//   NONE             device memory; the host pointer is only a handle
 void CudaBackend::alloc_persistent(Tensor& t, size_t nbytes, PersistentHostAccess access,
                                    size_t prefix) {
-    if (!available() || nbytes == 0 ||
-        (access == PersistentHostAccess::MIRRORED_PREFIX && (prefix == 0 || prefix > nbytes))) {
+    const bool mirrored = access == PersistentHostAccess::MIRRORED_PREFIX;
+    if (!available() || nbytes == 0 || (mirrored && (prefix == 0 || prefix > nbytes))) {
         impl_->failed = true;
         return;
     }
-    void* storage = nullptr;
-    if (access == PersistentHostAccess::FULL) {
-        if (!impl_->cuda(cudaMallocManaged(&storage, nbytes), "cudaMallocManaged persistent"))
-            return;
-        impl_->managed.push_back(storage);
-        std::memset(storage, 0, nbytes);
-        t.data = storage;
-    } else {
-        if (!impl_->cuda(cudaMalloc(&storage, nbytes), "cudaMalloc persistent"))
-            return;
-        impl_->owned.push_back(storage);
-        if (!impl_->cuda(cudaMemset(storage, 0, nbytes), "cudaMemset persistent"))
-            return;
-        if (access == PersistentHostAccess::MIRRORED_PREFIX) {
-            Mirror& m = impl_->mirrors[storage];
-            m.bytes = prefix;
-            m.words.assign((prefix + 7) / 8, 0);
-            t.data = m.words.data();  // the host reads only this prefix
-        } else {
-            t.data = storage;  // a handle: PersistentHostAccess::NONE forbids dereferencing it
-        }
+    const bool managed = access == PersistentHostAccess::FULL;
+    void* dev = nullptr;
+    if (!impl_->cuda(managed ? cudaMallocManaged(&dev, nbytes) : cudaMalloc(&dev, nbytes),
+                     "persistent storage"))
+        return;
+    (managed ? impl_->managed : impl_->owned).push_back(dev);
+    if (managed)
+        std::memset(dev, 0, nbytes);
+    else if (!impl_->cuda(cudaMemset(dev, 0, nbytes), "cudaMemset persistent"))
+        return;
+    void* host_view = dev;
+    if (mirrored) {
+        Mirror& m = impl_->mirrors[dev];
+        m.bytes = prefix;
+        m.words.assign((prefix + 7) / 8, 0);
+        host_view = m.words.data();
     }
-    t.device_data = storage;
+    t.data = host_view;
+    t.device_data = dev;
     t.device_offset = 0;
     t.mem_type = MemoryType::EXTERNAL;
 }
@@ -495,39 +641,7 @@ void CudaBackend::dispatch(const GraphNode& node, const std::vector<const Tensor
     const Tensor* in0 = !inputs.empty() ? inputs[0] : nullptr;
 
     // zero-copy views of input 0: the output descriptor is rewritten, no bytes move
-    if (node.op_type == OpType::RESHAPE && in0 && output && in0->is_contiguous()) {
-        int64_t shape[4];
-        for (int d = 0; d < 4; ++d)
-            shape[d] = output->shape[d];
-        *output = *in0;
-        for (int d = 0; d < 4; ++d)
-            output->shape[d] = shape[d];
-        output->compute_strides();
-        native();
-        return;
-    }
-    if (node.op_type == OpType::PERMUTE && in0 && output) {
-        Tensor view = *in0;
-        for (int d = 0; d < 4; ++d) {
-            const int axis = graph_params::get_i32(node.params, d, d);
-            view.shape[axis] = in0->shape[d];
-            view.stride[axis] = in0->stride[d];
-        }
-        *output = view;
-        native();
-        return;
-    }
-    if (node.op_type == OpType::SLICE && in0 && output) {
-        const int dim = graph_params::get_i32(node.params, 0, 0);
-        const int offset = graph_params::get_i32(node.params, 1, 0);
-        const int size =
-            graph_params::get_i32(node.params, 2, static_cast<int>(in0->shape[dim]));
-        *output = *in0;
-        const size_t byte_offset = static_cast<size_t>(offset) * in0->stride[dim];
-        if (in0->data)
-            output->data = static_cast<uint8_t*>(in0->data) + byte_offset;
-        output->device_offset = in0->device_offset + byte_offset;
-        output->shape[dim] = size;
+    if (in0 && output && describe_view(node, *in0, output)) {
         native();
         return;
     }
@@ -548,9 +662,12 @@ void CudaBackend::dispatch(const GraphNode& node, const std::vector<const Tensor
             const int act_len = graph_params::get_i32(node.params, 2, -1);
             const float* a_dev = device_ptr<const float>(*in0);
             float* c_dev = device_ptr<float>(*output);
-            // one int8 activation scale per 128 values, applied row by row: the reference's
-            // single-row rule (kernels/matmul_w4.cpp:1058-1075), used here for every M
-            const int rule = B2W4_ACT_G128;
+            // The reference's W4A8 rule: one int8 activation scale per 128 values for a single
+            // row (kernels/matmul_w4.cpp:1058-1075), one per 32 values once there are several
+            // rows (:1125-1154).  MOLLM_B200_MULTI_ROW_RULE=128 keeps the single-row rule for
+            // every M (faster tensor-core path; results then differ from the reference's
+            // multi-row kernels within the activation-quantisation error).
+            const int rule = m == 1 ? B2W4_ACT_G128 : impl_->multi_row_rule;
             bool ok;
             if (a_dev && c_dev)
                 ok = impl_->b2(b2w4_matmul(impl_->ctx, h, a_dev, lda, c_dev, ldc, m, rule, act,
@@ -603,83 +720,16 @@ void CudaBackend::dispatch(const GraphNode& node, const std::vector<const Tensor
         impl_->failed = true;
         return;
     }
-    synchronize_for_host_read();
-    if (impl_->failed)
-        return;
-    std::vector<Tensor> host_tensors;
-    std::vector<const Tensor*> host_inputs;
-    std::vector<std::vector<uint64_t>> staging;
-    std::vector<int> staged(inputs.size(), -1);
-    host_tensors.reserve(inputs.size());
-    staging.reserve(inputs.size());
-    for (size_t i = 0; i < inputs.size(); ++i) {
-        const Tensor* in = inputs[i];
-        if (!in) {
-            host_inputs.push_back(nullptr);
-            continue;
-        }
-        host_tensors.push_back(*in);
-        Tensor& host = host_tensors.back();
-        const bool weight = impl_->is_device_weight(*in);
-        if (in->device_data && !weight) {
-            // an intermediate or persistent tensor: stage the view from its first byte
-            const size_t bytes = in->view_span_bytes();
-            staging.emplace_back((bytes + 7) / 8);
-            staged[i] = static_cast<int>(staging.size() - 1);
-            if (!copy_to_host(*in, staging.back().data(), bytes))
-                return;
-            host.data = staging.back().data();
-        } else if (weight && impl_->g32_by_handle.count(in->device_data)) {
-            // W4G32: point the host descriptor at the backend's own copy of the blocks
-            uint8_t* copy = const_cast<uint8_t*>(
-                impl_->g32_by_handle[in->device_data]->data());
-            const size_t off = in->device_offset;
-            host.data = copy + off;
-            host.q4_g32_data = copy + off;
-            host.rowmajor_data = copy + off;
-        } else if (weight && !host.data) {
-            std::fprintf(stderr, "CudaBackend: fallback lacks host weight storage\n");
-            impl_->failed = true;
-            return;
-        }
-        host.device_data = nullptr;
-        host.device_offset = 0;
-        host_inputs.push_back(&host);
-    }
     if (!output || (!output->device_data && !output->data)) {
         impl_->failed = true;
         return;
     }
-    // a host-resident output (callers may hand plain host tensors to dispatch) is written in
-    // place; a device-resident one is produced in a host buffer and copied over
-    const bool out_on_device = output->device_data != nullptr;
-    const size_t out_bytes = output->view_span_bytes();
-    std::vector<uint64_t> out_storage(out_on_device ? (out_bytes + 7) / 8 : 0);
-    Tensor host_out = *output;
-    if (out_on_device) {
-        host_out.data = out_storage.data();
-        host_out.device_data = nullptr;
-        host_out.device_offset = 0;
-    }
-    impl_->cpu.clear_dispatch_error();
-    impl_->cpu.dispatch(node, host_inputs, &host_out, thread_pool);
-    if (impl_->cpu.dispatch_failed()) {
-        impl_->failed = true;
+    synchronize_for_host_read();
+    if (impl_->failed)
         return;
-    }
-    // reference kernels may update cache or state inputs in place: copy every staged input back
-    for (size_t i = 0; i < inputs.size(); ++i) {
-        if (staged[i] < 0)
-            continue;
-        Tensor& in = *const_cast<Tensor*>(inputs[i]);
-        if (!copy_from_host(staging[static_cast<size_t>(staged[i])].data(), in,
-                            in.view_span_bytes()))
-            return;
-    }
-    if (out_on_device) {
-        if (host_out.data != out_storage.data() ||
-            !copy_from_host(host_out.data, *output, out_bytes))
-            return;
-    }
+    Impl::HostBridge bridge(*this, *impl_);
+    if (!bridge.bring_in(inputs) || !bridge.run(node, output, thread_pool) ||
+        !bridge.send_back(inputs, output))
+        return;
     ++impl_->fallback_ops[static_cast<uint32_t>(node.op_type)];
 }
