@@ -135,6 +135,14 @@ int b2w4_debug_group_sums(b2w4_ctx* ctx, const b2w4_weight* w, const float* x_de
 int b2w4_quantize_activations(b2w4_ctx* ctx, const float* x_dev, int lda, int m,
                               int k, int act_rule, int8_t* q_dev, float* scales_dev);
 
+/* Activation rule of the routed-MoE expert matmuls.  B2W4_ACT_G32 (default) is the
+ * reference's: an expert that was handed several rows runs the multi-row W4A8
+ * kernel, one activation scale per 32 values (kernels/moe.cpp:1055-1058 ->
+ * kernels/matmul_w4.cpp:1125-1154), an expert with a single row the one-row
+ * kernel, one scale per 128 values (:1058-1075).  B2W4_ACT_G128 applies the
+ * one-row rule to every row (a deviation from the reference, somewhat faster). */
+int b2w4_ctx_set_moe_rule(b2w4_ctx* ctx, int act_rule);
+
 /* ---- routed MoE ----------------------------------------------------------
  * Replaces kernel_qwen3_moe (kernels/moe.cpp:576-1129) as dispatched for
  * OpType::MOE (graph/cpu_backend.cpp:169-206) in the Qwen3-MoE configuration:

@@ -9,6 +9,16 @@
 #include <stdlib.h>
 #include <string.h>
 
+/* exp of a float.  The reference calls std::exp on a float (kernels/activations.h:76-99,
+ * kernels/moe_routing.cpp:157-166, kernels/moe.cpp:160-183), i.e. the platform libm's expf,
+ * which is within one ulp of the correctly rounded value but not always equal to it (glibc:
+ * about 6 in 10000 arguments differ in the last bit).  Mode 0 (default) calls expf, like the
+ * reference built on this host; mode 1 evaluates in double and rounds once, which is what
+ * the GPU kernels do and is independent of the host's libm. */
+static int g_exp_mode = 0;
+void orc_set_exp_mode(int correctly_rounded) { g_exp_mode = correctly_rounded != 0; }
+static float orc_exp(float x) { return g_exp_mode ? (float)exp((double)x) : expf(x); }
+
 /* ---------------------------------------------------------------- fp16 -- */
 
 float orc_fp16_to_fp32(uint16_t h) {
@@ -264,7 +274,7 @@ int orc_matmul_w4(const uint8_t* blocks, int n, int k, const float* x, int m,
 static float activation_scalar(float v, int act) {
     switch (act) {
     case 1: { /* SILU */
-        float s = 1.f / (1.f + expf(-v));
+        float s = 1.f / (1.f + orc_exp(-v));
         return v * s;
     }
     case 2: { /* GELU, tanh form */
@@ -334,7 +344,7 @@ int orc_moe_select_routes_softmax(const float* logits, int tokens,
         float maximum = w[0];
         float sum = 0.f;
         for (int j = 0; j < top_k; ++j) {
-            w[j] = expf(w[j] - maximum);
+            w[j] = orc_exp(w[j] - maximum);
             sum += w[j];
         }
         float inverse = sum > 0.f ? 1.f / sum : 0.f;
@@ -440,7 +450,7 @@ int orc_moe_forward(const float* hidden, int tokens, int hidden_size, int ldx,
                 for (int c = 0; c < intermediate; ++c) {
                     float g = gu[(size_t)i * 2 * intermediate + c];
                     float u = gu[(size_t)i * 2 * intermediate + intermediate + c];
-                    float s = 1.f / (1.f + expf(-g));
+                    float s = 1.f / (1.f + orc_exp(-g));
                     inter[(size_t)i * intermediate + c] = (g * s) * u;
                 }
             rc |= orc_matmul_w4(down_blocks + (size_t)e * dn_expert_bytes,

@@ -37,6 +37,10 @@ enum {
     ORC_ACT_F64 = 0     /* no activation quantisation: exact fp64 product   */
 };
 
+/* 0: exp through the host libm's expf, as the reference built here does (default);
+ * 1: exp evaluated in double and rounded once (what the GPU kernels do). */
+void orc_set_exp_mode(int correctly_rounded);
+
 size_t orc_bg128_bytes(int n, int k);
 void orc_bg128_encode(const int8_t* q, const float* scales, int n, int k,
                       uint8_t* blocks);

@@ -16,7 +16,7 @@ NONE, SILU, GELU, RELU, RELU_SQUARED = 0, 1, 2, 3, 4
 # every symbol include/b200w4.h declares
 SYMBOLS = [
     "b2w4_ctx_create", "b2w4_ctx_destroy", "b2w4_ctx_set_stream", "b2w4_sync",
-    "b2w4_ctx_set_peer_wait_ms",
+    "b2w4_ctx_set_peer_wait_ms", "b2w4_ctx_set_moe_rule",
     "b2w4_last_error", "b2w4_version", "b2w4_weight_upload", "b2w4_weight_from_device",
     "b2w4_weight_free", "b2w4_weight_shape", "b2w4_weight_scales_fp16",
     "b2w4_weight_stream_bytes", "b2w4_matmul", "b2w4_matmul_host",
@@ -71,6 +71,7 @@ def lib():
         L.b2w4_ctx_set_stream.argtypes = [vp, vp]
         L.b2w4_sync.argtypes = [vp]
         L.b2w4_ctx_set_peer_wait_ms.argtypes = [vp, i]
+        L.b2w4_ctx_set_moe_rule.argtypes = [vp, i]
         L.b2w4_last_error.argtypes = [vp]
         L.b2w4_last_error.restype = C.c_char_p
         L.b2w4_version.restype = C.c_char_p
@@ -265,6 +266,11 @@ class Context:
 
     def sync(self):
         self._check(lib().b2w4_sync(self.handle))
+
+    def set_moe_rule(self, rule):
+        """ACT_G32: the reference's rule (per 32 values for an expert that holds several rows,
+        per 128 for a lone row); ACT_G128: per 128 for every row."""
+        self._check(lib().b2w4_ctx_set_moe_rule(self.handle, rule))
 
     def set_peer_wait_ms(self, milliseconds):
         """Bound of the device-side waits for another GPU's stores (default about 2 s)."""

@@ -188,6 +188,8 @@ int b2w4_launch_quantize(b2w4_ctx* ctx, const float* x, int lda, int m, int k,
         LAUNCH(128, QLAYOUT_EVEN_ODD);
     else if (layout == QLAYOUT_NATURAL)
         LAUNCH(32, QLAYOUT_NATURAL);
+    else if (layout == QLAYOUT_MMA)
+        LAUNCH(32, QLAYOUT_MMA);
     else
         LAUNCH(32, QLAYOUT_EVEN_ODD);
 #undef LAUNCH

@@ -37,6 +37,10 @@ struct b2w4_ctx {
     // tuning: 1 = always the tcgen05 GEMM, 2 = the mma.sync GEMM whenever the shape fits it
     int gemm_kind = 0;
     int gemv_tpc_override = 0;  // tuning: cap on 8-row tiles per GEMV CTA (0 = heuristic)
+    // Routed MoE: B2W4_ACT_G32 = the reference's rule (an expert that holds several rows
+    // quantises its activations per 32 values, a lone row per 128); B2W4_ACT_G128 = per 128
+    // for every row.
+    int moe_rule = B2W4_ACT_G32;
     unsigned long long peer_wait_cycles = 0;  // bound of waits for a peer's stores (set at create)
     char err[512] = {0};
     // grow-only scratch (quantised activations, MoE work lists, staging)

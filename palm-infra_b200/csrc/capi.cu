@@ -128,6 +128,15 @@ int b2w4_ctx_set_peer_wait_ms(b2w4_ctx* ctx, int milliseconds) {
     return B2W4_OK;
 }
 
+int b2w4_ctx_set_moe_rule(b2w4_ctx* ctx, int act_rule) {
+    if (!ctx)
+        return B2W4_E_INVALID;
+    if (act_rule != B2W4_ACT_G128 && act_rule != B2W4_ACT_G32)
+        return b2w4_fail(ctx, B2W4_E_INVALID, "moe rule must be 128 or 32");
+    ctx->moe_rule = act_rule;
+    return B2W4_OK;
+}
+
 // Drains the stream and reads the status word a kernel sets when one of its bounded waits
 // gave up; clears it so that the context stays usable.
 static int drain_and_check(b2w4_ctx* ctx) {

@@ -502,9 +502,12 @@ moe_route_fused_kernel(const float* __restrict__ hidden, int ldx, int tokens, in
 // (kernels/moe.cpp:160-183), then the per-128 quantiser; codes in tensor-operand order.
 // one warp: 128 values of one route, written to `group_dst` (the 128 code bytes of the group)
 // and `scale_dst`
+// a32: one scale per 32 values (scale_dst[0..3], the lane's block is lane / 8) instead of one
+// per 128 (scale_dst[0])
 __device__ __forceinline__ void swiglu_quant_warp(const float* __restrict__ gate_row,
                                                   const float* __restrict__ up_row, int lane,
-                                                  int8_t* group_dst, float* scale_dst) {
+                                                  int8_t* group_dst, float* scale_dst,
+                                                  bool a32 = false) {
     const float* gp = gate_row + lane * 4;
     const float* up = up_row + lane * 4;
     float v[4];
@@ -517,14 +520,22 @@ __device__ __forceinline__ void swiglu_quant_warp(const float* __restrict__ gate
     }
     float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1)
+    for (int off = 4; off > 0; off >>= 1)  // the lane's 32-block: eight lanes
         amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+    if (!a32) {
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 8));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 16));
+    }
     float scale, inv;
     b2w4_quant_params(amax, scale, inv);
     const int c0 = b2w4_quant_code(v[0], inv), c1 = b2w4_quant_code(v[1], inv);
     const int c2 = b2w4_quant_code(v[2], inv), c3 = b2w4_quant_code(v[3], inv);
-    if (lane == 0)
+    if (a32) {
+        if ((lane & 7) == 0)
+            scale_dst[lane >> 3] = scale;
+    } else if (lane == 0) {
         *scale_dst = scale;
+    }
     // tensor-operand order inside the group: [word position][even words of the four
     // 32-blocks, then the odd words]; the lane holds k = 4*lane..+3: 32-block lane/8, even
     // codes at even index 2*(lane%8), 2*(lane%8)+1
@@ -533,9 +544,13 @@ __device__ __forceinline__ void swiglu_quant_warp(const float* __restrict__ gate
     *reinterpret_cast<char2*>(blk + 16) = make_char2((signed char)c1, (signed char)c3);
 }
 
+// scales: [routes][scale_stride].  offsets (null = per-128 everywhere): first compact route of
+// every expert, [num_experts + 1]; a route whose expert holds several routes is quantised per
+// 32 values (scales[r][4*g + block]), a lone route per 128 (scales[r][g]).
 __global__ void moe_swiglu_quant_kernel(const float* __restrict__ gu, int routes,
                                         int intermediate, int8_t* __restrict__ q,
-                                        float* __restrict__ scales,
+                                        float* __restrict__ scales, int scale_stride,
+                                        const int32_t* __restrict__ offsets, int num_experts,
                                         const int32_t* __restrict__ route_lo,
                                         const int32_t* __restrict__ route_hi) {
     b2w4_pdl_chain_entry();
@@ -548,10 +563,22 @@ __global__ void moe_swiglu_quant_kernel(const float* __restrict__ gu, int routes
     // expert-parallel runs only own the compact positions of their experts
     if (route_lo && (r < *route_lo || r >= *route_hi))
         return;
+    bool a32 = false;
+    if (offsets) {  // the expert of compact route r: offsets[e] <= r < offsets[e + 1]
+        int lo = 0, hi = num_experts;
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (offsets[mid] <= r)
+                lo = mid;
+            else
+                hi = mid;
+        }
+        a32 = offsets[lo + 1] - offsets[lo] >= 2;
+    }
     const float* gp = gu + (size_t)r * 2 * intermediate + (size_t)g * 128;
     swiglu_quant_warp(gp, gp + intermediate, lane,
                       q + (size_t)r * intermediate + (size_t)g * 128,
-                      scales + (size_t)r * groups + g);
+                      scales + (size_t)r * scale_stride + (a32 ? g * 4 : g), a32);
 }
 
 // ---- 8. combine: one block per (token, 512 hidden columns) -------------------------------
@@ -1007,7 +1034,14 @@ struct GroupedArgs {
     const uint8_t* nib;
     const void* scl;
     const int8_t* qa;         // [rows][K] int8, tensor-operand order inside each group
-    const float* as;          // [rows][G]
+    const float* as;          // [rows][as_stride]: one scale per 128 values at [g]
+    // The reference's rule for an expert that holds SEVERAL rows (kernels/moe.cpp:1055-1058
+    // -> kernels/matmul_w4.cpp:1125-1154): one activation scale per 32 values.  qa32 / as32
+    // are those rows quantised that way (as32[r][4*g + block]); null = per-128 for every
+    // expert.  An expert with a single row keeps the per-128 rule (:1058-1075).
+    const int8_t* qa32;
+    const float* as32;
+    int as_stride, as32_stride;
     const int4* slots;        // y-th expert with routes: (expert, first route, end), else empty
     int num_experts_all;      // experts routed over
     int expert_begin;         // first expert whose weights this aggregate holds
@@ -1053,10 +1087,18 @@ moe_grouped_gemv_kernel(const GroupedArgs a) {
     uint8_t* s_w = smem;
     uint8_t* s_scl = s_w + (size_t)a.tpc * tile_bytes;
     uint8_t* s_qa = s_scl + (size_t)a.tpc * scl_tile_bytes;                         // [kGR][K+pad]
-    float* s_as = reinterpret_cast<float*>(s_qa + (size_t)kGR * row_bytes);         // [G][kGR]
-    int* s_bias = reinterpret_cast<int*>(s_as + kGR * G);                           // [G][kGR]
+    // per (group or 32-block, route): activation scale and accumulator bias; sized for the
+    // per-32 rule (four entries per group)
+    float* s_as = reinterpret_cast<float*>(s_qa + (size_t)kGR * row_bytes);         // [4G][kGR]
+    int* s_bias = reinterpret_cast<int*>(s_as + kGR * G * 4);                       // [4G][kGR]
     uint64_t* s_bar = reinterpret_cast<uint64_t*>(
-        (reinterpret_cast<uintptr_t>(s_bias + kGR * G) + 7) & ~uintptr_t(7));
+        (reinterpret_cast<uintptr_t>(s_bias + kGR * G * 4) + 7) & ~uintptr_t(7));
+    // the expert's rule: per 32 values when it holds several rows
+    const bool a32 = a.qa32 != nullptr && (r1 - r0) >= 2;
+    const int8_t* const qa_src = a32 ? a.qa32 : a.qa;
+    const float* const as_src = a32 ? a.as32 : a.as;
+    const int as_stride = a32 ? a.as32_stride : a.as_stride;
+    const int SPG = a32 ? 4 : 1;  // scales per group
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int gid = lane >> 2, tid = lane & 3;
@@ -1092,28 +1134,36 @@ moe_grouped_gemv_kernel(const GroupedArgs a) {
             const int mi = i / (K / 16), c = i - mi * (K / 16);
             const int src_row = a.row_map ? a.row_map[base + mi] : base + mi;
             *reinterpret_cast<uint4*>(s_qa + (size_t)mi * row_bytes + c * 16) =
-                reinterpret_cast<const uint4*>(a.qa + (size_t)src_row * K)[c];
+                reinterpret_cast<const uint4*>(qa_src + (size_t)src_row * K)[c];
         }
-        for (int i = threadIdx.x; i < mc * G; i += kGT) {
-            const int mi = i / G, g = i - mi * G;
+        for (int i = threadIdx.x; i < mc * G * SPG; i += kGT) {
+            const int mi = i / (G * SPG), gs = i - mi * (G * SPG);
             const int src_row = a.row_map ? a.row_map[base + mi] : base + mi;
-            s_as[g * kGR + mi] = a.as[(size_t)src_row * G + g];
+            s_as[gs * kGR + mi] = as_src[(size_t)src_row * as_stride + gs];
         }
         __syncthreads();
-        // accumulator bias per (route, group): 0x4B400000 - 8 * (sum of the group's codes)
+        // accumulator bias per (route, group): 0x4B400000 - 8 * (sum of the group's codes);
+        // per-32 rule: per (route, 32-block).  In tensor-operand order the codes of 32-block
+        // b are word b of each of the eight 16-byte chunks of the group.
         for (int i = threadIdx.x; i < mc * G; i += kGT) {
             const int mi = i / G, g = i - mi * G;
             const uint4* q = reinterpret_cast<const uint4*>(s_qa + (size_t)mi * row_bytes + g * 128);
-            int sum = 0;
+            int sum[4] = {0, 0, 0, 0};
 #pragma unroll
             for (int c = 0; c < 8; ++c) {
                 const uint4 v = q[c];
-                sum = __dp4a(0x01010101, (int)v.x, sum);
-                sum = __dp4a(0x01010101, (int)v.y, sum);
-                sum = __dp4a(0x01010101, (int)v.z, sum);
-                sum = __dp4a(0x01010101, (int)v.w, sum);
+                sum[0] = __dp4a(0x01010101, (int)v.x, sum[0]);
+                sum[1] = __dp4a(0x01010101, (int)v.y, sum[1]);
+                sum[2] = __dp4a(0x01010101, (int)v.z, sum[2]);
+                sum[3] = __dp4a(0x01010101, (int)v.w, sum[3]);
             }
-            s_bias[g * kGR + mi] = 0x4B400000 - 8 * sum;
+            if (a32) {
+#pragma unroll
+                for (int b = 0; b < 4; ++b)
+                    s_bias[(g * 4 + b) * kGR + mi] = 0x4B400000 - 8 * sum[b];
+            } else {
+                s_bias[g * kGR + mi] = 0x4B400000 - 8 * (sum[0] + sum[1] + sum[2] + sum[3]);
+            }
         }
         if (!weights_ready) {
             if (!mbar_wait_bounded(&s_bar[0])) {
@@ -1169,6 +1219,30 @@ moe_grouped_gemv_kernel(const GroupedArgs a) {
                         const uint4* bp = reinterpret_cast<const uint4*>(
                             s_qa + (size_t)(cb * 8 + gid) * row_bytes + g * 128 + tid * 32);
                         const uint4 be = bp[0], bo = bp[1];
+                        if (a32) {
+                            // one instruction = one 32-block: its own accumulator, bias and
+                            // activation scale, folded into the chain in ascending block order
+                            // (kernels/matmul_w4.cpp:785-901)
+                            const uint32_t bev[4] = {be.x, be.y, be.z, be.w};
+                            const uint32_t bov[4] = {bo.x, bo.y, bo.z, bo.w};
+#pragma unroll
+                            for (int b = 0; b < 4; ++b) {
+                                const int tk = (g * 4 + b) * kGR + cb * 8 + tid * 2;
+                                const int2 bias = *reinterpret_cast<const int2*>(s_bias + tk);
+                                const float2 asv = *reinterpret_cast<const float2*>(s_as + tk);
+                                int c[4] = {bias.x, bias.y, bias.x, bias.y};
+                                moe_mma_16x8x32(c, lo0[b], lo1[b], hi0[b], hi1[b], bev[b], bov[b]);
+                                acc[j][0] = __fmaf_rn(__fsub_rn(__int_as_float(c[0]), 12582912.f),
+                                                      __fmul_rn(ws0, asv.x), acc[j][0]);
+                                acc[j][1] = __fmaf_rn(__fsub_rn(__int_as_float(c[1]), 12582912.f),
+                                                      __fmul_rn(ws0, asv.y), acc[j][1]);
+                                acc[j][2] = __fmaf_rn(__fsub_rn(__int_as_float(c[2]), 12582912.f),
+                                                      __fmul_rn(ws1, asv.x), acc[j][2]);
+                                acc[j][3] = __fmaf_rn(__fsub_rn(__int_as_float(c[3]), 12582912.f),
+                                                      __fmul_rn(ws1, asv.y), acc[j][3]);
+                            }
+                            continue;
+                        }
                         const int tk = g * kGR + cb * 8 + tid * 2;  // routes of this lane's columns
                         const int2 bias = *reinterpret_cast<const int2*>(s_bias + tk);
                         const float2 asv = *reinterpret_cast<const float2*>(s_as + tk);
@@ -1220,13 +1294,16 @@ moe_grouped_gemv_kernel(const GroupedArgs a) {
 
 size_t grouped_smem(int k, int groups, int tpc, bool scl16) {
     return (size_t)tpc * groups * 512 + (size_t)tpc * groups * 8 * (scl16 ? 2 : 4) +
-           (size_t)kGR * (k + kRowPad) + 2 * sizeof(float) * kGR * groups + 8 + 16;
+           (size_t)kGR * (k + kRowPad) + 2 * sizeof(float) * kGR * groups * 4 + 8 + 16;
 }
 
 // `decode` (few tokens): the shared-memory variant, optionally with SwiGLU + quantiser fused
 // into its prologue (fused_gate_up = the gate_up matmul's fp32 output).
+// qa32 / as32: the same rows quantised per 32 values, for experts that hold several routes
+// (null: per-128 for all); as_stride / as32_stride: floats per row of as / as32.
 int launch_grouped(b2w4_ctx* ctx, const b2w4_weight* w, int num_experts_all, int expert_begin,
                    int expert_count, int routes, const int8_t* qa, const float* as,
+                   int as_stride, const int8_t* qa32, const float* as32, int as32_stride,
                    const int4* slots, const int32_t* row_map, float* out, bool decode,
                    const float* fused_gate_up = nullptr, const b2w4_tp_args* peers = nullptr,
                    int stage_rows = 0) {
@@ -1277,6 +1354,10 @@ int launch_grouped(b2w4_ctx* ctx, const b2w4_weight* w, int num_experts_all, int
     a.scl = w->scl;
     a.qa = qa;
     a.as = as;
+    a.as_stride = as_stride;
+    a.qa32 = qa32;
+    a.as32 = as32;
+    a.as32_stride = as32_stride;
     a.slots = slots;
     a.num_experts_all = num_experts_all;
     a.expert_begin = expert_begin;
@@ -1372,11 +1453,18 @@ static int moe_run(b2w4_ctx* ctx, const float* hidden_dev, int ldx, int tokens, 
     const size_t o_act = align_up(o_pos + sizeof(int32_t) * routes, 256);
     const size_t small_bytes = align_up(o_act + sizeof(int4) * num_experts, 256);
     // quantised hidden (per token) and quantised SwiGLU output (per route)
+    // The reference's rule (ctx->moe_rule == B2W4_ACT_G32): an expert that holds several routes
+    // quantises per 32 values, a lone route per 128; with one token every expert holds one
+    // route.  B2W4_ACT_G128: per 128 for every route.
+    const bool rule32 = ctx->moe_rule == B2W4_ACT_G32 && tokens >= 2;
     const size_t o_qh = 0;
     const size_t o_ash = align_up(o_qh + (size_t)tokens * hidden_size, 256);
     const size_t o_qi = align_up(o_ash + sizeof(float) * tokens * gh, 256);
     const size_t o_asi = align_up(o_qi + (size_t)routes * intermediate, 256);
-    const size_t quant_bytes = align_up(o_asi + sizeof(float) * routes * gi, 256);
+    const size_t o_qh32 = align_up(o_asi + sizeof(float) * routes * gi * 4, 256);
+    const size_t o_ash32 = align_up(o_qh32 + (rule32 ? (size_t)tokens * hidden_size : 0), 256);
+    const size_t quant_bytes =
+        align_up(o_ash32 + (rule32 ? sizeof(float) * tokens * gh * 4 : 0), 256);
     void *sm = nullptr, *qb = nullptr, *gu = nullptr, *dn = nullptr;
     int rc;
     if ((rc = b2w4_reserve(ctx, SCR_MOE_A, small_bytes, &sm)) != B2W4_OK ||
@@ -1398,7 +1486,9 @@ static int moe_run(b2w4_ctx* ctx, const float* hidden_dev, int ldx, int tokens, 
     int8_t* q_hidden = reinterpret_cast<int8_t*>(qbb + o_qh);
     float* as_hidden = reinterpret_cast<float*>(qbb + o_ash);
     int8_t* q_inter = reinterpret_cast<int8_t*>(qbb + o_qi);
-    float* as_inter = reinterpret_cast<float*>(qbb + o_asi);
+    float* as_inter = reinterpret_cast<float*>(qbb + o_asi);  // [routes][4 * gi]
+    int8_t* q_hidden32 = rule32 ? reinterpret_cast<int8_t*>(qbb + o_qh32) : nullptr;
+    float* as_hidden32 = rule32 ? reinterpret_cast<float*>(qbb + o_ash32) : nullptr;
     cudaStream_t st = ctx->stream;
 
     const __half* router = static_cast<const __half*>(router_fp16_dev);
@@ -1451,13 +1541,18 @@ static int moe_run(b2w4_ctx* ctx, const float* hidden_dev, int ldx, int tokens, 
                                        q_hidden, as_hidden, QLAYOUT_MMA)) != B2W4_OK)
             return rc;
     }
-    const bool decode = tokens <= kFusedSwigluTokens;  // which grouped-matmul variant
+    if (rule32 && (rc = b2w4_launch_quantize(ctx, hidden_dev, ldx, tokens, hidden_size,
+                                             B2W4_ACT_G32, q_hidden32, as_hidden32,
+                                             QLAYOUT_MMA)) != B2W4_OK)
+        return rc;
+    // which grouped-matmul variant: the few-token one implements the per-128 rule only
+    const bool decode = rule32 ? false : tokens <= kFusedSwigluTokens;
     // compact positions stay global; the grouped kernels skip experts held elsewhere
     const int32_t* local_offsets = offsets + expert_begin;
     const bool partial = expert_count != num_experts;
     if ((rc = launch_grouped(ctx, gate_up, num_experts, expert_begin, expert_count, routes,
-                             q_hidden, as_hidden, slots, route_token,
-                             static_cast<float*>(gu), decode)) != B2W4_OK)
+                             q_hidden, as_hidden, gh, q_hidden32, as_hidden32, gh * 4, slots,
+                             route_token, static_cast<float*>(gu), decode)) != B2W4_OK)
         return rc;
     // few routes: SwiGLU and its quantiser run inside the down-projection's CTAs
     const bool fuse_swiglu = decode;
@@ -1466,14 +1561,19 @@ static int moe_run(b2w4_ctx* ctx, const float* hidden_dev, int ldx, int tokens, 
         B2W4_CUDA(ctx, b2w4_launch_chained(
                            ctx->pdl, moe_swiglu_quant_kernel, dim3((int)((threads + 255) / 256)),
                            dim3(256), 0, st, static_cast<const float*>(gu), routes, intermediate,
-                           q_inter, as_inter, partial ? local_offsets : nullptr,
+                           q_inter, as_inter, gi * 4,
+                           rule32 ? static_cast<const int32_t*>(offsets) : nullptr, num_experts,
+                           partial ? local_offsets : nullptr,
                            partial ? local_offsets + expert_count : nullptr));
         ctx->launches++;
     }
     // decode steps hand the rows over from the down-projection's own epilogue
     const bool fused_handover = peers != nullptr && decode;
+    // a route's SwiGLU row was quantised by its own expert's rule: one code buffer serves both
     if ((rc = launch_grouped(ctx, down, num_experts, expert_begin, expert_count, routes, q_inter,
-                             as_inter, slots, nullptr, static_cast<float*>(dn), decode,
+                             as_inter, gi * 4, rule32 ? q_inter : nullptr,
+                             rule32 ? as_inter : nullptr, gi * 4, slots, nullptr,
+                             static_cast<float*>(dn), decode,
                              fuse_swiglu ? static_cast<const float*>(gu) : nullptr,
                              fused_handover ? peers : nullptr, stage_rows)) != B2W4_OK)
         return rc;

@@ -60,6 +60,14 @@ def ref():
 
 # ---------------------------------------------------------------- oracle calls
 
+def set_exp_mode(correctly_rounded):
+    """How the oracle takes exp of a float: False = the host libm's expf (the reference built
+    on this host; the default, used by the pins against the reference), True = in double,
+    rounded once (what the GPU kernels do; independent of the host's libm).  The two differ in
+    the last bit for about 6 in 10000 arguments."""
+    oracle().orc_set_exp_mode(1 if correctly_rounded else 0)
+
+
 def bg128_bytes(n, k):
     return ((n + 7) // 8) * (k // 128) * BLOCK_BYTES
 
@@ -179,9 +187,12 @@ def moe_combine(route_out, idx, w):
     return out
 
 
-def expert_route_outputs(hidden, idx, intermediate, gate_up, down, experts, lo=0, hi=None):
+def expert_route_outputs(hidden, idx, intermediate, gate_up, down, experts, lo=0, hi=None,
+                         rule=ACT_G128):
     """Per-route expert outputs [tokens*top_k, H] from the oracle's pieces, for the routes
-    whose expert lies in [lo, hi); zeros elsewhere.  gate_up / down hold all `experts`."""
+    whose expert lies in [lo, hi); zeros elsewhere.  gate_up / down hold all `experts`.
+    rule == ACT_G32: the reference's rule -- an expert's rows go through its matmuls together,
+    per-32 activation scales when it holds several, per-128 when it holds one."""
     hidden = np.ascontiguousarray(hidden, dtype=np.float32)
     t, h = hidden.shape
     top_k = idx.shape[1]
@@ -189,17 +200,19 @@ def expert_route_outputs(hidden, idx, intermediate, gate_up, down, experts, lo=0
     gu_bytes = bg128_bytes(2 * intermediate, h)
     dn_bytes = bg128_bytes(h, intermediate)
     out = np.zeros((t * top_k, h), dtype=np.float32)
-    for tok in range(t):
-        for j in range(top_k):
-            e = int(idx[tok, j])
-            if not lo <= e < hi:
-                continue
-            gu = matmul_w4(gate_up[e * gu_bytes:(e + 1) * gu_bytes], 2 * intermediate, h,
-                           hidden[tok:tok + 1])
-            gate = apply_activation(gu[:, :intermediate].copy(), 1)  # g * 1/(1+expf(-g))
-            inter = (gate * gu[:, intermediate:]).astype(np.float32)
-            out[tok * top_k + j] = matmul_w4(down[e * dn_bytes:(e + 1) * dn_bytes], h,
-                                             intermediate, inter)[0]
+    for e in range(lo, hi):
+        where = [(tok, j) for tok in range(t) for j in range(top_k) if int(idx[tok, j]) == e]
+        if not where:
+            continue
+        r = ACT_G32 if rule == ACT_G32 and len(where) >= 2 else ACT_G128
+        rows = np.ascontiguousarray(hidden[[tok for tok, _ in where]])
+        gu = matmul_w4(gate_up[e * gu_bytes:(e + 1) * gu_bytes], 2 * intermediate, h, rows,
+                       rule=r)
+        gate = apply_activation(gu[:, :intermediate].copy(), 1)  # g * 1/(1+expf(-g))
+        inter = (gate * gu[:, intermediate:]).astype(np.float32)
+        y = matmul_w4(down[e * dn_bytes:(e + 1) * dn_bytes], h, intermediate, inter, rule=r)
+        for i, (tok, j) in enumerate(where):
+            out[tok * top_k + j] = y[i]
     return out
 
 

@@ -179,3 +179,21 @@ def test_argmax_oracle_matches_golden_tokens():
     for i, w in enumerate(want):
         assert ol.argmax_token(case("greedy_token")[f"row{i}"]) == int(w), i
     assert int(want[9]) == 30 and int(want[10]) == 0  # a NaN loses, except at index 0
+
+
+def test_exp_modes_differ_by_at_most_one_ulp():
+    """The oracle's two ways of taking exp of a float -- the host libm's expf (default: what the
+    reference built here computes) and double-then-round (what the GPU kernels compute) --
+    agree to one unit in the last place, on SiLU arguments and on softmax differences."""
+    x = np.concatenate([np.linspace(-20, 20, 40001), np.random.default_rng(3).normal(0, 3, 20000)])
+    x = x.astype(np.float32).reshape(1, -1)
+    try:
+        ol.set_exp_mode(False)
+        a = ol.apply_activation(x.copy(), 1)
+        ol.set_exp_mode(True)
+        b = ol.apply_activation(x.copy(), 1)
+    finally:
+        ol.set_exp_mode(False)
+    ulps = np.abs(a.view(np.int32).astype(np.int64) - b.view(np.int32).astype(np.int64))
+    assert ulps.max() <= 2  # one ulp of exp moves the quotient by at most two
+    assert (ulps != 0).mean() < 5e-3
