@@ -337,6 +337,48 @@ float* b2w4_chain_input(b2w4_chain* chain);   /* device pointer, may be NULL */
 float* b2w4_chain_output(b2w4_chain* chain);  /* device pointer, may be NULL */
 size_t b2w4_chain_weight_bytes(const b2w4_chain* chain);
 
+/* ---- the operators between a decoder layer's matmuls ---------------------------------
+ * Device kernels for the operators a dense decoder layer runs between its W4G128
+ * matmuls, so that a decode step needs no host round trip.  All tensors fp32 on the
+ * device, rows = tokens, features contiguous; asynchronous on the context's stream.
+ * Sums over a row are tree reductions (the reference's scalar loops are
+ * sequential): agreement with the reference is to fp32 rounding of a reassociated
+ * sum; the element-wise arithmetic keeps the reference's operation order.
+ *   b2w4_rms_norm      OpType::RMS_NORM, kernel_rms_norm (kernels/norm.cpp:13-31,
+ *                      :95-121): out = (x * 1/sqrt(mean(x^2) + eps)) * weight
+ *   b2w4_add_rms_norm  OpType::ADD_RMS_NORM, kernel_add_rms_norm (:123-190):
+ *                      residual += update (written back), out = rms_norm(residual)
+ *   b2w4_swiglu        OpType::SWIGLU (kernels/elementwise.cpp:529-570): merged row
+ *                      [2I] = gate | up; out[i] = (gate[i] / (1+exp(-gate[i]))) * up[i]
+ *   b2w4_elementwise   OpType::ADD / MUL on equal-shaped contiguous tensors
+ *   b2w4_rope          OpType::ROTARY_EMBED, kernel_rope with interleave == 0
+ *                      (kernels/rope.cpp:11-50, :155-195): x [tokens][heads][dim],
+ *                      cos / sin [tokens][rope_dim/2]; in place when out == x
+ *   b2w4_attention     OpType::SDPA with a KV cache (kernels/attention.cpp:1043-1057
+ *                      for the cache layout [kv_head][capacity][dim], fp32;
+ *                      kernels/attention_x86_avx512.cpp:47-109 for the arithmetic):
+ *                      appends the new tokens' k, v [tokens][kv_heads][dim] at
+ *                      positions past.., then causal attention of q
+ *                      [tokens][heads][dim] over keys 0 .. past + t, full-row softmax,
+ *                      P*V accumulated in ascending key order
+ *   b2w4_embed_rows    rows ids[r] of an fp16 table [vocab][dim] widened to fp32 */
+int b2w4_rms_norm(b2w4_ctx* ctx, const float* x_dev, int ldx, int rows, int dim,
+                  const float* weight_dev, float eps, float* out_dev, int ldo);
+int b2w4_add_rms_norm(b2w4_ctx* ctx, float* residual_dev, int ldr, const float* update_dev,
+                      int ldu, int rows, int dim, const float* weight_dev, float eps,
+                      float* out_dev, int ldo);
+int b2w4_swiglu(b2w4_ctx* ctx, const float* merged_dev, int ldm, int rows, int intermediate,
+                float* out_dev, int ldo);
+int b2w4_elementwise(b2w4_ctx* ctx, const float* a_dev, const float* b_dev, float* out_dev,
+                     size_t count, int multiply);
+int b2w4_rope(b2w4_ctx* ctx, const float* x_dev, float* out_dev, int tokens, int heads, int dim,
+              const float* cos_dev, const float* sin_dev, int rope_dim);
+int b2w4_attention(b2w4_ctx* ctx, const float* q_dev, const float* k_dev, const float* v_dev,
+                   float* k_cache_dev, float* v_cache_dev, float* out_dev, int tokens, int heads,
+                   int kv_heads, int dim, int past, int capacity, float scale);
+int b2w4_embed_rows(b2w4_ctx* ctx, const void* table_fp16_dev, const int32_t* ids_dev, int rows,
+                    int dim, float* out_dev, int ldo);
+
 /* Launch counter: how many of this library's kernels have been launched on the
  * context since creation (for benchmark bookkeeping). */
 uint64_t b2w4_kernel_launches(const b2w4_ctx* ctx);

@@ -15,7 +15,15 @@
 //   select_moe_routes             kernels/moe_routing.cpp:25-169
 //   kernel_qwen3_moe              kernels/moe.cpp:576-1129
 //   sample_token (temperature 0)  engine/sampler.cpp:458-462 -> argmax_token :31-77
+//   kernel_rms_norm / kernel_add_rms_norm   kernels/norm.cpp:95-190
+//   kernel_elementwise (SWIGLU)   kernels/elementwise.cpp:529-...
+//   kernel_rope                   kernels/rope.cpp:155-195
+//   sdpa_x86_avx512_head          kernels/attention_x86_avx512.cpp:47-109
+#include "kernels/attention_x86.h"
+#include "kernels/elementwise.h"
 #include "kernels/matmul.h"
+#include "kernels/norm.h"
+#include "kernels/rope.h"
 #include "kernels/matmul_internal.h"
 #include "kernels/moe.h"
 #include "kernels/moe_routing.h"
@@ -187,6 +195,63 @@ int ref_greedy_token(const float* logits, int vocab_size) {
     std::vector<float> copy(logits, logits + (vocab_size > 0 ? vocab_size : 0));
     unsigned int seed = 1;
     return sample_token(copy.data(), vocab_size, 0.0f, 1, 0.0f, &seed);
+}
+
+// ---- the operators between a decoder layer's matmuls (rows = tokens, features contiguous)
+
+void ref_rms_norm(const float* x, int rows, int dim, const float* weight, float eps,
+                  float* out) {
+    Tensor xt = Tensor::create(Precision::FP32, MemoryType::EXTERNAL, dim, rows, 1, 1,
+                               const_cast<float*>(x));
+    Tensor wt = Tensor::create(Precision::FP32, MemoryType::EXTERNAL, dim, 1, 1, 1,
+                               const_cast<float*>(weight));
+    Tensor ot = Tensor::create(Precision::FP32, MemoryType::EXTERNAL, dim, rows, 1, 1, out);
+    kernel_rms_norm(xt, wt, eps, ot);
+}
+
+void ref_add_rms_norm(float* residual, const float* update, int rows, int dim,
+                      const float* weight, float eps, float* out) {
+    Tensor rt = Tensor::create(Precision::FP32, MemoryType::EXTERNAL, dim, rows, 1, 1, residual);
+    Tensor ut = Tensor::create(Precision::FP32, MemoryType::EXTERNAL, dim, rows, 1, 1,
+                               const_cast<float*>(update));
+    Tensor wt = Tensor::create(Precision::FP32, MemoryType::EXTERNAL, dim, 1, 1, 1,
+                               const_cast<float*>(weight));
+    Tensor ot = Tensor::create(Precision::FP32, MemoryType::EXTERNAL, dim, rows, 1, 1, out);
+    kernel_add_rms_norm(rt, ut, wt, eps, ot, nullptr);
+}
+
+void ref_swiglu(const float* merged, int rows, int intermediate, float* out) {
+    Tensor mt = Tensor::create(Precision::FP32, MemoryType::EXTERNAL, 2 * intermediate, rows, 1, 1,
+                               const_cast<float*>(merged));
+    Tensor ot = Tensor::create(Precision::FP32, MemoryType::EXTERNAL, intermediate, rows, 1, 1,
+                               out);
+    std::vector<const Tensor*> in = {&mt};
+    kernel_elementwise(OpType::SWIGLU, in, &ot, nullptr);
+}
+
+// x, out: [tokens][heads][dim]; cos, sin: [tokens][rope_dim/2]; halves form (interleave off)
+void ref_rope(const float* x, int tokens, int heads, int dim, const float* cosv,
+              const float* sinv, int rope_dim, float* out) {
+    Tensor xt = Tensor::create(Precision::FP32, MemoryType::EXTERNAL, dim, tokens, heads, 1,
+                               const_cast<float*>(x));
+    Tensor ot = Tensor::create(Precision::FP32, MemoryType::EXTERNAL, dim, tokens, heads, 1, out);
+    for (Tensor* t : {&xt, &ot}) {  // token stride = heads * dim, head stride = dim
+        t->stride[1] = sizeof(float) * static_cast<size_t>(heads) * dim;
+        t->stride[2] = sizeof(float) * static_cast<size_t>(dim);
+    }
+    Tensor ct = Tensor::create(Precision::FP32, MemoryType::EXTERNAL, rope_dim / 2, tokens, 1, 1,
+                               const_cast<float*>(cosv));
+    Tensor st = Tensor::create(Precision::FP32, MemoryType::EXTERNAL, rope_dim / 2, tokens, 1, 1,
+                               const_cast<float*>(sinv));
+    kernel_rope(xt, ct, st, rope_dim, false, ot);
+}
+
+// one head: query [q_tokens][dim], key / value [k_tokens][dim], mask [q_tokens][k_tokens] or null
+void ref_sdpa_head(const float* query, const float* key, const float* value, float* output,
+                   int query_tokens, int key_tokens, int key_dim, int value_dim, float scale,
+                   const float* mask) {
+    sdpa_x86_avx512_head(query, key, value, output, query_tokens, key_tokens, key_dim, value_dim,
+                         scale, mask);
 }
 
 }  // extern "C"

@@ -518,3 +518,147 @@ int orc_argmax_token(const float* logits, int vocab_size) {
             best = i;
     return best;
 }
+
+
+/* ---- the operators between a decoder layer's matmuls --------------------------------
+ * Restated from the reference's x86 build (scalar paths unless noted); rows = tokens,
+ * features contiguous. */
+
+/* kernel_rms_norm -> rms_norm_scalar (kernels/norm.cpp:13-31): sequential sum of squares. */
+void orc_rms_norm(const float* x, int rows, int dim, const float* weight, float eps,
+                  float* out) {
+    for (int n = 0; n < rows; ++n) {
+        const float* xr = x + (size_t)n * dim;
+        float* o = out + (size_t)n * dim;
+        float sum_sq = 0.f;
+        for (int d = 0; d < dim; ++d) {
+            float v = xr[d];
+            sum_sq += v * v;
+        }
+        float rms = 1.f / sqrtf(sum_sq / dim + eps);
+        for (int d = 0; d < dim; ++d)
+            o[d] = xr[d] * rms * weight[d];
+    }
+}
+
+/* kernel_add_rms_norm (kernels/norm.cpp:123-190), scalar tail: the sum is written back. */
+void orc_add_rms_norm(float* residual, const float* update, int rows, int dim,
+                      const float* weight, float eps, float* out) {
+    for (int n = 0; n < rows; ++n) {
+        float* r = residual + (size_t)n * dim;
+        const float* u = update + (size_t)n * dim;
+        float* o = out + (size_t)n * dim;
+        float sum_sq = 0.f;
+        for (int d = 0; d < dim; ++d) {
+            float value = r[d] + u[d];
+            r[d] = value;
+            sum_sq += value * value;
+        }
+        float scale = 1.0f / sqrtf(sum_sq / (float)dim + eps);
+        for (int d = 0; d < dim; ++d)
+            o[d] = r[d] * scale * weight[d];
+    }
+}
+
+/* OpType::SWIGLU (kernels/elementwise.cpp:565-569): (g / (1 + exp(-g))) * up. */
+void orc_swiglu(const float* merged, int rows, int intermediate, float* out) {
+    for (int n = 0; n < rows; ++n) {
+        const float* gate = merged + (size_t)n * 2 * intermediate;
+        const float* up = gate + intermediate;
+        for (int i = 0; i < intermediate; ++i) {
+            float g = gate[i];
+            out[(size_t)n * intermediate + i] = (g / (1.f + orc_exp(-g))) * up[i];
+        }
+    }
+}
+
+/* kernel_rope -> rope_scalar, halves form (kernels/rope.cpp:11-50).  x, out:
+ * [tokens][heads][dim]; cos, sin: [tokens][rope_dim/2]. */
+void orc_rope(const float* x, int tokens, int heads, int dim, const float* cosv,
+              const float* sinv, int rope_dim, float* out) {
+    int half = rope_dim / 2;
+    for (int t = 0; t < tokens; ++t)
+        for (int h = 0; h < heads; ++h) {
+            const float* xr = x + ((size_t)t * heads + h) * dim;
+            float* o = out + ((size_t)t * heads + h) * dim;
+            for (int d = rope_dim; d < dim; ++d)
+                o[d] = xr[d];
+            for (int i = 0; i < half; ++i) {
+                float x0 = xr[i], x1 = xr[i + half];
+                float c = cosv[(size_t)t * half + i], s = sinv[(size_t)t * half + i];
+                o[i] = x0 * c - x1 * s;
+                o[i + half] = x0 * s + x1 * c;
+            }
+        }
+}
+
+/* sdpa_x86_avx512_head (kernels/attention_x86_avx512.cpp:12-109).  The dot product keeps two
+ * 16-lane fused accumulators (lanes i and i + 16 of every 32 features), adds them lane-wise
+ * and reduces the 16 lanes the way _mm512_reduce_add_ps expands: halves of 8, of 4, of 2,
+ * of 1.  Softmax: max, exp(v - max), sequential sum, times 1 / sum.  P * V: one fused
+ * multiply-add per key and feature, keys ascending, zero probabilities skipped. */
+static float orc_dot_avx512(const float* a, const float* b, int count) {
+    float first[16] = {0}, second[16] = {0};
+    int i = 0;
+    for (; i + 31 < count; i += 32)
+        for (int l = 0; l < 16; ++l) {
+            first[l] = fmaf(a[i + l], b[i + l], first[l]);
+            second[l] = fmaf(a[i + 16 + l], b[i + 16 + l], second[l]);
+        }
+    for (; i + 15 < count; i += 16)
+        for (int l = 0; l < 16; ++l)
+            first[l] = fmaf(a[i + l], b[i + l], first[l]);
+    float v[16];
+    for (int l = 0; l < 16; ++l)
+        v[l] = first[l] + second[l];
+    for (int width = 8; width >= 1; width >>= 1)
+        for (int l = 0; l < width; ++l)
+            v[l] = v[l] + v[l + width];
+    float result = v[0];
+    for (; i < count; ++i)
+        result += a[i] * b[i];
+    return result;
+}
+
+void orc_sdpa_head(const float* query, const float* key, const float* value, float* output,
+                   int query_tokens, int key_tokens, int key_dim, int value_dim, float scale,
+                   const float* mask) {
+    float* scores = (float*)malloc(sizeof(float) * (size_t)(key_tokens > 0 ? key_tokens : 1));
+    for (int t = 0; t < query_tokens; ++t) {
+        const float* q = query + (size_t)t * key_dim;
+        const float* mrow = mask ? mask + (size_t)t * key_tokens : NULL;
+        int visible = key_tokens;
+        if (mrow)
+            while (visible > 0 && mrow[visible - 1] == -INFINITY)
+                --visible;
+        float* o = output + (size_t)t * value_dim;
+        memset(o, 0, sizeof(float) * (size_t)value_dim);
+        if (visible == 0)
+            continue;
+        for (int j = 0; j < visible; ++j) {
+            scores[j] = orc_dot_avx512(q, key + (size_t)j * key_dim, key_dim) * scale;
+            if (mrow)
+                scores[j] += mrow[j];
+        }
+        float maximum = -INFINITY;
+        for (int j = 0; j < visible; ++j)
+            maximum = scores[j] > maximum ? scores[j] : maximum;
+        float sum = 0.0f;
+        for (int j = 0; j < visible; ++j) {
+            scores[j] = orc_exp(scores[j] - maximum);
+            sum += scores[j];
+        }
+        float inverse = 1.0f / sum;
+        for (int j = 0; j < visible; ++j)
+            scores[j] *= inverse;
+        for (int j = 0; j < visible; ++j) {
+            float p = scores[j];
+            if (p == 0.0f)
+                continue;
+            const float* vr = value + (size_t)j * value_dim;
+            for (int d = 0; d < value_dim; ++d)
+                o[d] = fmaf(vr[d], p, o[d]);
+        }
+    }
+    free(scores);
+}

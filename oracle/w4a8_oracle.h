@@ -103,4 +103,18 @@ float orc_fp16_to_fp32(uint16_t h);
 #ifdef __cplusplus
 }
 #endif
+/* The operators between a decoder layer's matmuls, from the reference's x86 build (rows =
+ * tokens, features contiguous): kernels/norm.cpp:13-31, :123-190; kernels/elementwise.cpp:
+ * 565-569; kernels/rope.cpp:11-50; kernels/attention_x86_avx512.cpp:12-109. */
+void orc_rms_norm(const float* x, int rows, int dim, const float* weight, float eps,
+                  float* out);
+void orc_add_rms_norm(float* residual, const float* update, int rows, int dim,
+                      const float* weight, float eps, float* out);
+void orc_swiglu(const float* merged, int rows, int intermediate, float* out);
+void orc_rope(const float* x, int tokens, int heads, int dim, const float* cosv,
+              const float* sinv, int rope_dim, float* out);
+void orc_sdpa_head(const float* query, const float* key, const float* value, float* output,
+                   int query_tokens, int key_tokens, int key_dim, int value_dim, float scale,
+                   const float* mask);
+
 #endif

@@ -27,6 +27,8 @@ SYMBOLS = [
     "b2w4_matmul_argmax_tp", "b2w4_tp_gather_token",
     "b2w4_chain_create", "b2w4_chain_create_tp", "b2w4_chain_scratch_words", "b2w4_chain_destroy", "b2w4_chain_run", "b2w4_chain_run_host",
     "b2w4_chain_input", "b2w4_chain_output", "b2w4_chain_weight_bytes", "b2w4_chain_set_trace",
+    "b2w4_rms_norm", "b2w4_add_rms_norm", "b2w4_swiglu", "b2w4_elementwise", "b2w4_rope",
+    "b2w4_attention", "b2w4_embed_rows",
     "b2w4_kernel_launches",
 ]
 
@@ -117,6 +119,14 @@ def lib():
         L.b2w4_chain_output.restype = C.c_void_p
         L.b2w4_chain_weight_bytes.argtypes = [vp]
         L.b2w4_chain_weight_bytes.restype = C.c_size_t
+        fl = C.c_float
+        L.b2w4_rms_norm.argtypes = [vp, f_p, i, i, i, f_p, fl, f_p, i]
+        L.b2w4_add_rms_norm.argtypes = [vp, f_p, i, f_p, i, i, i, f_p, fl, f_p, i]
+        L.b2w4_swiglu.argtypes = [vp, f_p, i, i, i, f_p, i]
+        L.b2w4_elementwise.argtypes = [vp, f_p, f_p, f_p, C.c_size_t, i]
+        L.b2w4_rope.argtypes = [vp, f_p, f_p, i, i, i, f_p, f_p, i]
+        L.b2w4_attention.argtypes = [vp, f_p, f_p, f_p, f_p, f_p, f_p, i, i, i, i, i, i, fl]
+        L.b2w4_embed_rows.argtypes = [vp, vp, vp, i, i, f_p, i]
         L.b2w4_kernel_launches.argtypes = [vp]
         L.b2w4_kernel_launches.restype = C.c_uint64
         _lib = L
@@ -375,6 +385,42 @@ class Context:
         self._check(lib().b2w4_quantize_activations(self.handle, _dptr(x), x.stride(0),
                                                     x.shape[0], x.shape[1], rule, _dptr(q),
                                                     _dptr(scales)))
+
+    # -- the operators between a decoder layer's matmuls (torch CUDA tensors, fp32)
+    def rms_norm(self, x, weight, eps, out):
+        rows, dim = x.shape
+        self._check(lib().b2w4_rms_norm(self.handle, _dptr(x), x.stride(0), rows, dim,
+                                        _dptr(weight), eps, _dptr(out), out.stride(0)))
+
+    def add_rms_norm(self, residual, update, weight, eps, out):
+        rows, dim = residual.shape
+        self._check(lib().b2w4_add_rms_norm(self.handle, _dptr(residual), residual.stride(0),
+                                            _dptr(update), update.stride(0), rows, dim,
+                                            _dptr(weight), eps, _dptr(out), out.stride(0)))
+
+    def swiglu(self, merged, out):
+        rows, two_i = merged.shape
+        self._check(lib().b2w4_swiglu(self.handle, _dptr(merged), merged.stride(0), rows,
+                                      two_i // 2, _dptr(out), out.stride(0)))
+
+    def add(self, a, b, out, multiply=False):
+        self._check(lib().b2w4_elementwise(self.handle, _dptr(a), _dptr(b), _dptr(out),
+                                           a.numel(), 1 if multiply else 0))
+
+    def rope(self, x, out, tokens, heads, dim, cos, sin, rope_dim):
+        self._check(lib().b2w4_rope(self.handle, _dptr(x), _dptr(out), tokens, heads, dim,
+                                    _dptr(cos), _dptr(sin), rope_dim))
+
+    def attention(self, q, k, v, k_cache, v_cache, out, tokens, heads, kv_heads, dim, past,
+                  capacity, scale):
+        self._check(lib().b2w4_attention(self.handle, _dptr(q), _dptr(k), _dptr(v),
+                                         _dptr(k_cache), _dptr(v_cache), _dptr(out), tokens,
+                                         heads, kv_heads, dim, past, capacity, scale))
+
+    def embed_rows(self, table_fp16, ids, out):
+        rows, dim = out.shape
+        self._check(lib().b2w4_embed_rows(self.handle, _dptr(table_fp16), _dptr(ids), rows, dim,
+                                          _dptr(out), out.stride(0)))
 
     # -- MoE
     def moe_forward(self, hidden, router_fp16, top_k, intermediate, gate_up, down, out,

@@ -1,0 +1,368 @@
+// The operators that sit between the W4G128 matmuls of a decoder layer, as device kernels, so
+// that a decode step needs no trip to the host between its matmuls: RMSNorm, residual add +
+// RMSNorm, SwiGLU, add / multiply, rotary embedding, KV-cache append, scaled-dot-product
+// attention over the cache, embedding-row lookup.  Semantics follow the reference's CPU
+// operators (the x86 build: its scalar and AVX-512 paths), cited per kernel.  Sums over a row
+// are tree reductions here where the reference's scalar loops are sequential, so these ops
+// agree with the reference to fp32 rounding of a reassociated sum, not bit for bit; everything
+// that is element-wise (rotary embedding, add, multiply, the P*V accumulation in key order)
+// uses the reference's operation order with no contraction.
+// All tensors are fp32, rows = tokens, features contiguous.
+#include "b200w4_internal.cuh"
+
+namespace {
+
+constexpr int kNormThreads = 256;
+
+__device__ __forceinline__ float block_sum(float v, float* s_part) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1)
+        v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, off));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    __syncthreads();  // s_part may still be read from a previous call
+    if (lane == 0)
+        s_part[warp] = v;
+    __syncthreads();
+    float t = 0.f;
+    const int warps = (blockDim.x + 31) >> 5;
+    for (int w = 0; w < warps; ++w)  // every thread adds in the same order
+        t = __fadd_rn(t, s_part[w]);
+    return t;
+}
+
+__device__ __forceinline__ float block_max(float v, float* s_part) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1)
+        v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, off));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    __syncthreads();
+    if (lane == 0)
+        s_part[warp] = v;
+    __syncthreads();
+    float t = s_part[0];
+    const int warps = (blockDim.x + 31) >> 5;
+    for (int w = 1; w < warps; ++w)
+        t = fmaxf(t, s_part[w]);
+    return t;
+}
+
+// kernel_rms_norm (kernels/norm.cpp:13-31, :95-121): r = 1/sqrt(sum(x^2)/D + eps),
+// out = (x * r) * w.  With `update`: kernel_add_rms_norm (:123-190): the sum x + update is
+// written back into x (the residual stream) first.  One block per row.
+__global__ void __launch_bounds__(kNormThreads)
+rms_norm_kernel(float* __restrict__ x, int ldx, const float* __restrict__ update, int ldu,
+                int dim, const float* __restrict__ weight, float eps, float* __restrict__ out,
+                int ldo) {
+    b2w4_pdl_chain_entry();
+    __shared__ float s_part[kNormThreads / 32];
+    float* xr = x + (size_t)blockIdx.x * ldx;
+    const float* ur = update ? update + (size_t)blockIdx.x * ldu : nullptr;
+    float* orow = out + (size_t)blockIdx.x * ldo;
+    float ss = 0.f;
+    for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+        float v = xr[d];
+        if (ur) {
+            v = __fadd_rn(v, ur[d]);
+            xr[d] = v;
+        }
+        ss = __fadd_rn(ss, __fmul_rn(v, v));
+    }
+    ss = block_sum(ss, s_part);
+    const float r = __fdiv_rn(1.f, sqrtf(__fadd_rn(__fdiv_rn(ss, (float)dim), eps)));
+    for (int d = threadIdx.x; d < dim; d += blockDim.x)
+        orow[d] = __fmul_rn(__fmul_rn(xr[d], r), weight[d]);
+}
+
+// Small rows (the per-head Q/K norm: 128 values): one warp per row.
+__global__ void rms_norm_warp_kernel(const float* __restrict__ x, int ldx, int rows, int dim,
+                                     const float* __restrict__ weight, float eps,
+                                     float* __restrict__ out, int ldo) {
+    b2w4_pdl_chain_entry();
+    const int row = (int)(((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5);
+    const int lane = threadIdx.x & 31;
+    if (row >= rows)
+        return;
+    const float* xr = x + (size_t)row * ldx;
+    float ss = 0.f;
+    for (int d = lane; d < dim; d += 32)
+        ss = __fadd_rn(ss, __fmul_rn(xr[d], xr[d]));
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1)
+        ss = __fadd_rn(ss, __shfl_xor_sync(0xffffffffu, ss, off));
+    const float r = __fdiv_rn(1.f, sqrtf(__fadd_rn(__fdiv_rn(ss, (float)dim), eps)));
+    float* orow = out + (size_t)row * ldo;
+    for (int d = lane; d < dim; d += 32)
+        orow[d] = __fmul_rn(__fmul_rn(xr[d], r), weight[d]);
+}
+
+// SWIGLU of kernel_elementwise (kernels/elementwise.cpp:529-570): a merged row [2I] holds gate
+// = [0, I) and up = [I, 2I); out[i] = (g / (1 + exp(-g))) * up[i] -- a division, unlike the
+// MoE op's and the matmul epilogue's g * (1 / (1 + exp(-g))).
+__global__ void swiglu_kernel(const float* __restrict__ merged, int ldm, int rows, int inter,
+                              float* __restrict__ out, int ldo) {
+    b2w4_pdl_chain_entry();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (size_t)rows * inter)
+        return;
+    const int r = (int)(i / inter), c = (int)(i - (size_t)r * inter);
+    const float g = merged[(size_t)r * ldm + c];
+    const float u = merged[(size_t)r * ldm + inter + c];
+    const float e = (float)exp(-(double)g);  // in double, rounded once
+    out[(size_t)r * ldo + c] = __fmul_rn(__fdiv_rn(g, __fadd_rn(1.f, e)), u);
+}
+
+__global__ void binary_kernel(const float* __restrict__ a, const float* __restrict__ b,
+                              float* __restrict__ out, size_t count, int multiply) {
+    b2w4_pdl_chain_entry();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < count)
+        out[i] = multiply ? __fmul_rn(a[i], b[i]) : __fadd_rn(a[i], b[i]);
+}
+
+// kernel_rope, halves form (kernels/rope.cpp:11-50, interleave == false as the Qwen3 graphs
+// use it, models/qwen3.py:332-333): out[i] = x0*c - x1*s, out[i+half] = x0*s + x1*c with
+// x0 = x[i], x1 = x[i+half]; features beyond rope_dim are copied.  x: [tokens][heads][dim],
+// cos / sin: [tokens][rope_dim/2].  In place when out == x.
+__global__ void rope_kernel(const float* __restrict__ x, float* __restrict__ out, int tokens,
+                            int heads, int dim, const float* __restrict__ cosv,
+                            const float* __restrict__ sinv, int rope_dim) {
+    b2w4_pdl_chain_entry();
+    const int half = rope_dim >> 1;
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t per_row = (size_t)half + (size_t)(dim - rope_dim);
+    if (i >= (size_t)tokens * heads * per_row)
+        return;
+    const size_t rowi = i / per_row;
+    const int j = (int)(i - rowi * per_row);
+    const int t = (int)(rowi / heads);
+    const float* xr = x + rowi * dim;
+    float* orow = out + rowi * dim;
+    if (j < half) {
+        const float x0 = xr[j], x1 = xr[j + half];
+        const float c = cosv[(size_t)t * half + j], s = sinv[(size_t)t * half + j];
+        orow[j] = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s));
+        orow[j + half] = __fadd_rn(__fmul_rn(x0, s), __fmul_rn(x1, c));
+    } else {
+        orow[rope_dim + (j - half)] = xr[rope_dim + (j - half)];
+    }
+}
+
+// KV-cache append: the new tokens' keys and values [tokens][kv_heads][dim] go to positions
+// past .. past+tokens-1 of a cache laid out [kv_head][capacity][dim], the layout of the
+// reference's cache after its header (kernels/attention.cpp:1043-1057).
+__global__ void kv_append_kernel(const float* __restrict__ k, const float* __restrict__ v,
+                                 float* __restrict__ k_cache, float* __restrict__ v_cache,
+                                 int tokens, int kv_heads, int dim, int past, int capacity) {
+    b2w4_pdl_chain_entry();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (size_t)tokens * kv_heads * dim)
+        return;
+    const int d = (int)(i % dim);
+    const int h = (int)((i / dim) % kv_heads);
+    const int t = (int)(i / ((size_t)dim * kv_heads));
+    const size_t dst = ((size_t)h * capacity + past + t) * dim + d;
+    k_cache[dst] = k[i];
+    v_cache[dst] = v[i];
+}
+
+// Scaled-dot-product attention of one (query token, head) over the cache, the x86 reference's
+// arithmetic (kernels/attention_x86_avx512.cpp:47-109): scores = dot(q, k_j) * scale for the
+// visible keys (causal: keys 0 .. past + t), full-row softmax (max, exp, sum, times 1/sum),
+// then out = sum_j p_j * v_j accumulated key by key in ascending order with one fused
+// multiply-add per key and feature, as the reference's loop does.  One block per (token,
+// head); thread d owns output feature d.
+constexpr int kAttnThreads = 128;
+__global__ void __launch_bounds__(kAttnThreads)
+attention_kernel(const float* __restrict__ q, const float* __restrict__ k_cache,
+                 const float* __restrict__ v_cache, float* __restrict__ out, int tokens,
+                 int heads, int kv_heads, int dim, int past, int capacity, float scale) {
+    b2w4_pdl_chain_entry();
+    extern __shared__ float s_scores[];  // [visible keys]
+    __shared__ float s_part[kAttnThreads / 32];
+    const int t = blockIdx.x / heads, h = blockIdx.x % heads;
+    const int kvh = h / (heads / kv_heads);
+    const int visible = past + t + 1;
+    const float* qr = q + ((size_t)t * heads + h) * dim;
+    const float* kc = k_cache + (size_t)kvh * capacity * dim;
+    const float* vc = v_cache + (size_t)kvh * capacity * dim;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // a warp per key: lanes split the features, tree-add the partial products
+    for (int j = warp; j < visible; j += kAttnThreads / 32) {
+        float p = 0.f;
+        for (int d = lane; d < dim; d += 32)
+            p = __fmaf_rn(qr[d], kc[(size_t)j * dim + d], p);
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1)
+            p = __fadd_rn(p, __shfl_xor_sync(0xffffffffu, p, off));
+        if (lane == 0)
+            s_scores[j] = __fmul_rn(p, scale);
+    }
+    __syncthreads();
+    float m = -INFINITY;
+    for (int j = threadIdx.x; j < visible; j += blockDim.x)
+        m = fmaxf(m, s_scores[j]);
+    m = block_max(m, s_part);
+    float sum = 0.f;
+    for (int j = threadIdx.x; j < visible; j += blockDim.x) {
+        const float e = (float)exp((double)__fsub_rn(s_scores[j], m));
+        s_scores[j] = e;
+        sum = __fadd_rn(sum, e);
+    }
+    sum = block_sum(sum, s_part);
+    const float inv = __fdiv_rn(1.f, sum);
+    __syncthreads();
+    for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+        float acc = 0.f;
+        for (int j = 0; j < visible; ++j) {
+            const float p = __fmul_rn(s_scores[j], inv);
+            if (p != 0.f)
+                acc = __fmaf_rn(vc[(size_t)j * dim + d], p, acc);
+        }
+        out[((size_t)t * heads + h) * dim + d] = acc;
+    }
+}
+
+// Embedding lookup: rows of an fp16 table widened to fp32 (the reference's EMBEDDING input
+// path widens fp16 rows the same way, engine/engine.cpp:637-672 uploads "hidden").
+__global__ void embed_rows_kernel(const __half* __restrict__ table, const int32_t* __restrict__ ids,
+                                  int rows, int dim, float* __restrict__ out, int ldo) {
+    b2w4_pdl_chain_entry();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (size_t)rows * dim)
+        return;
+    const int r = (int)(i / dim), d = (int)(i - (size_t)r * dim);
+    out[(size_t)r * ldo + d] = __half2float(table[(size_t)ids[r] * dim + d]);
+}
+
+}  // namespace
+
+extern "C" {
+
+int b2w4_rms_norm(b2w4_ctx* ctx, const float* x_dev, int ldx, int rows, int dim,
+                  const float* weight_dev, float eps, float* out_dev, int ldo) {
+    if (!ctx)
+        return B2W4_E_INVALID;
+    if (!x_dev || !weight_dev || !out_dev || rows <= 0 || dim <= 0 || ldx < dim || ldo < dim)
+        return b2w4_fail(ctx, B2W4_E_INVALID, "rms_norm: bad argument");
+    if (dim <= 256) {
+        const size_t threads = (size_t)rows * 32;
+        B2W4_CUDA(ctx, b2w4_launch_chained(ctx->pdl, rms_norm_warp_kernel,
+                                           dim3((unsigned)((threads + 255) / 256)), dim3(256), 0,
+                                           ctx->stream, x_dev, ldx, rows, dim, weight_dev, eps,
+                                           out_dev, ldo));
+    } else {
+        B2W4_CUDA(ctx, b2w4_launch_chained(ctx->pdl, rms_norm_kernel, dim3(rows),
+                                           dim3(kNormThreads), 0, ctx->stream,
+                                           const_cast<float*>(x_dev), ldx,
+                                           static_cast<const float*>(nullptr), 0, dim, weight_dev,
+                                           eps, out_dev, ldo));
+    }
+    ctx->launches++;
+    return B2W4_OK;
+}
+
+int b2w4_add_rms_norm(b2w4_ctx* ctx, float* residual_dev, int ldr, const float* update_dev,
+                      int ldu, int rows, int dim, const float* weight_dev, float eps,
+                      float* out_dev, int ldo) {
+    if (!ctx)
+        return B2W4_E_INVALID;
+    if (!residual_dev || !update_dev || !weight_dev || !out_dev || rows <= 0 || dim <= 0 ||
+        ldr < dim || ldu < dim || ldo < dim)
+        return b2w4_fail(ctx, B2W4_E_INVALID, "add_rms_norm: bad argument");
+    B2W4_CUDA(ctx, b2w4_launch_chained(ctx->pdl, rms_norm_kernel, dim3(rows), dim3(kNormThreads), 0,
+                                       ctx->stream, residual_dev, ldr, update_dev, ldu, dim,
+                                       weight_dev, eps, out_dev, ldo));
+    ctx->launches++;
+    return B2W4_OK;
+}
+
+int b2w4_swiglu(b2w4_ctx* ctx, const float* merged_dev, int ldm, int rows, int intermediate,
+                float* out_dev, int ldo) {
+    if (!ctx)
+        return B2W4_E_INVALID;
+    if (!merged_dev || !out_dev || rows <= 0 || intermediate <= 0 || ldm < 2 * intermediate ||
+        ldo < intermediate)
+        return b2w4_fail(ctx, B2W4_E_INVALID, "swiglu: bad argument");
+    const size_t n = (size_t)rows * intermediate;
+    B2W4_CUDA(ctx, b2w4_launch_chained(ctx->pdl, swiglu_kernel, dim3((unsigned)((n + 255) / 256)),
+                                       dim3(256), 0, ctx->stream, merged_dev, ldm, rows,
+                                       intermediate, out_dev, ldo));
+    ctx->launches++;
+    return B2W4_OK;
+}
+
+int b2w4_elementwise(b2w4_ctx* ctx, const float* a_dev, const float* b_dev, float* out_dev,
+                     size_t count, int multiply) {
+    if (!ctx)
+        return B2W4_E_INVALID;
+    if (!a_dev || !b_dev || !out_dev || count == 0)
+        return b2w4_fail(ctx, B2W4_E_INVALID, "elementwise: bad argument");
+    B2W4_CUDA(ctx, b2w4_launch_chained(ctx->pdl, binary_kernel,
+                                       dim3((unsigned)((count + 255) / 256)), dim3(256), 0,
+                                       ctx->stream, a_dev, b_dev, out_dev, count, multiply));
+    ctx->launches++;
+    return B2W4_OK;
+}
+
+int b2w4_rope(b2w4_ctx* ctx, const float* x_dev, float* out_dev, int tokens, int heads, int dim,
+              const float* cos_dev, const float* sin_dev, int rope_dim) {
+    if (!ctx)
+        return B2W4_E_INVALID;
+    if (!x_dev || !out_dev || !cos_dev || !sin_dev || tokens <= 0 || heads <= 0 || dim <= 0 ||
+        rope_dim <= 0 || rope_dim > dim || (rope_dim & 1))
+        return b2w4_fail(ctx, B2W4_E_INVALID, "rope: bad argument");
+    const size_t n = (size_t)tokens * heads * ((size_t)rope_dim / 2 + (dim - rope_dim));
+    B2W4_CUDA(ctx, b2w4_launch_chained(ctx->pdl, rope_kernel, dim3((unsigned)((n + 255) / 256)),
+                                       dim3(256), 0, ctx->stream, x_dev, out_dev, tokens, heads,
+                                       dim, cos_dev, sin_dev, rope_dim));
+    ctx->launches++;
+    return B2W4_OK;
+}
+
+int b2w4_attention(b2w4_ctx* ctx, const float* q_dev, const float* k_dev, const float* v_dev,
+                   float* k_cache_dev, float* v_cache_dev, float* out_dev, int tokens, int heads,
+                   int kv_heads, int dim, int past, int capacity, float scale) {
+    if (!ctx)
+        return B2W4_E_INVALID;
+    if (!q_dev || !k_dev || !v_dev || !k_cache_dev || !v_cache_dev || !out_dev || tokens <= 0 ||
+        heads <= 0 || kv_heads <= 0 || heads % kv_heads || dim <= 0 || past < 0 ||
+        past + tokens > capacity)
+        return b2w4_fail(ctx, B2W4_E_INVALID,
+                         "attention: bad argument (tokens=%d past=%d capacity=%d heads=%d/%d)",
+                         tokens, past, capacity, heads, kv_heads);
+    const size_t smem = sizeof(float) * (size_t)(past + tokens);
+    if (smem > 200 * 1024)
+        return b2w4_fail(ctx, B2W4_E_INVALID, "attention: %d keys exceed the score buffer",
+                         past + tokens);
+    static b2w4_smem_optin configured;
+    B2W4_CUDA(ctx, b2w4_opt_in_smem(ctx, attention_kernel, smem, configured));
+    const size_t n = (size_t)tokens * kv_heads * dim;
+    B2W4_CUDA(ctx, b2w4_launch_chained(ctx->pdl, kv_append_kernel,
+                                       dim3((unsigned)((n + 255) / 256)), dim3(256), 0,
+                                       ctx->stream, k_dev, v_dev, k_cache_dev, v_cache_dev, tokens,
+                                       kv_heads, dim, past, capacity));
+    B2W4_CUDA(ctx, b2w4_launch_chained(ctx->pdl, attention_kernel, dim3(tokens * heads),
+                                       dim3(kAttnThreads), smem, ctx->stream, q_dev,
+                                       static_cast<const float*>(k_cache_dev),
+                                       static_cast<const float*>(v_cache_dev), out_dev, tokens,
+                                       heads, kv_heads, dim, past, capacity, scale));
+    ctx->launches += 2;
+    return B2W4_OK;
+}
+
+int b2w4_embed_rows(b2w4_ctx* ctx, const void* table_fp16_dev, const int32_t* ids_dev, int rows,
+                    int dim, float* out_dev, int ldo) {
+    if (!ctx)
+        return B2W4_E_INVALID;
+    if (!table_fp16_dev || !ids_dev || !out_dev || rows <= 0 || dim <= 0 || ldo < dim)
+        return b2w4_fail(ctx, B2W4_E_INVALID, "embed_rows: bad argument");
+    const size_t n = (size_t)rows * dim;
+    B2W4_CUDA(ctx, b2w4_launch_chained(ctx->pdl, embed_rows_kernel,
+                                       dim3((unsigned)((n + 255) / 256)), dim3(256), 0,
+                                       ctx->stream, static_cast<const __half*>(table_fp16_dev),
+                                       ids_dev, rows, dim, out_dev, ldo));
+    ctx->launches++;
+    return B2W4_OK;
+}
+
+}  // extern "C"

@@ -288,3 +288,82 @@ def argmax_token(logits):
 def ref_greedy_token(logits):
     logits = np.ascontiguousarray(logits, dtype=np.float32)
     return int(ref().ref_greedy_token(_ptr(logits), logits.size))
+
+
+# ------------------------------------------- operators between a decoder layer's matmuls
+# which = oracle() (the C restatement) or ref() (the reference's own CPU operators); the two
+# libraries export the same signatures under the prefixes orc_ / ref_.
+
+def _dec(which, name):
+    return getattr(which, ("orc_" if which is oracle() else "ref_") + name)
+
+
+def rms_norm(x, weight, eps, which=None):
+    which = which or oracle()
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    w = np.ascontiguousarray(weight, dtype=np.float32)
+    out = np.zeros_like(x)
+    _dec(which, "rms_norm")(_ptr(x), x.shape[0], x.shape[1], _ptr(w), C.c_float(eps), _ptr(out))
+    return out
+
+
+def add_rms_norm(residual, update, weight, eps, which=None):
+    """Returns (new residual, normalised output)."""
+    which = which or oracle()
+    r = np.array(residual, dtype=np.float32, order="C")
+    u = np.ascontiguousarray(update, dtype=np.float32)
+    w = np.ascontiguousarray(weight, dtype=np.float32)
+    out = np.zeros_like(r)
+    _dec(which, "add_rms_norm")(_ptr(r), _ptr(u), r.shape[0], r.shape[1], _ptr(w),
+                                 C.c_float(eps), _ptr(out))
+    return r, out
+
+
+def swiglu(merged, which=None):
+    which = which or oracle()
+    m = np.ascontiguousarray(merged, dtype=np.float32)
+    out = np.zeros((m.shape[0], m.shape[1] // 2), dtype=np.float32)
+    _dec(which, "swiglu")(_ptr(m), m.shape[0], m.shape[1] // 2, _ptr(out))
+    return out
+
+
+def rope(x, cosv, sinv, rope_dim, which=None):
+    """x [tokens, heads, dim]; cos / sin [tokens, rope_dim // 2]."""
+    which = which or oracle()
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    c = np.ascontiguousarray(cosv, dtype=np.float32)
+    s = np.ascontiguousarray(sinv, dtype=np.float32)
+    out = np.zeros_like(x)
+    _dec(which, "rope")(_ptr(x), x.shape[0], x.shape[1], x.shape[2], _ptr(c), _ptr(s), rope_dim,
+                        _ptr(out))
+    return out
+
+
+def sdpa_head(q, k, v, scale, mask=None, which=None):
+    """One head: q [q_tokens, dim], k / v [k_tokens, dim], mask [q_tokens, k_tokens] or None."""
+    which = which or oracle()
+    q = np.ascontiguousarray(q, dtype=np.float32)
+    k = np.ascontiguousarray(k, dtype=np.float32)
+    v = np.ascontiguousarray(v, dtype=np.float32)
+    m = None if mask is None else np.ascontiguousarray(mask, dtype=np.float32)
+    out = np.zeros((q.shape[0], v.shape[1]), dtype=np.float32)
+    _dec(which, "sdpa_head")(_ptr(q), _ptr(k), _ptr(v), _ptr(out), q.shape[0], k.shape[0],
+                             q.shape[1], v.shape[1], C.c_float(scale), _ptr(m))
+    return out
+
+
+def causal_attention(q, k_all, v_all, heads, kv_heads, past, scale, which=None):
+    """q [tokens, heads, dim]; k_all / v_all [past + tokens, kv_heads, dim]: token t sees keys
+    0 .. past + t.  The reference graph expresses that with an additive mask whose invisible
+    tail is -inf (engine/input_prep.cpp:8-16), which its kernel trims
+    (kernels/attention_x86_avx512.cpp:59-66)."""
+    tokens, _, dim = q.shape
+    total = k_all.shape[0]
+    mask = np.zeros((tokens, total), dtype=np.float32)
+    for t in range(tokens):
+        mask[t, past + t + 1:] = -np.inf
+    out = np.zeros((tokens, heads, dim), dtype=np.float32)
+    for h in range(heads):
+        kvh = h // (heads // kv_heads)
+        out[:, h] = sdpa_head(q[:, h], k_all[:, kvh], v_all[:, kvh], scale, mask, which)
+    return out

@@ -197,3 +197,38 @@ def test_exp_modes_differ_by_at_most_one_ulp():
     ulps = np.abs(a.view(np.int32).astype(np.int64) - b.view(np.int32).astype(np.int64))
     assert ulps.max() <= 2  # one ulp of exp moves the quotient by at most two
     assert (ulps != 0).mean() < 5e-3
+
+
+@pytest.mark.skipif(not ol.have_ref(), reason="reference library not built")
+def test_decoder_layer_operators_match_the_reference_bit_for_bit():
+    """The C restatements of RMSNorm, add + RMSNorm, SwiGLU, rotary embedding and the x86
+    attention head against the reference's own CPU operators (live, oracle/_ref), same inputs,
+    identical bits -- including the attention's two-accumulator dot product and the order of
+    its 16-lane reduction."""
+    rng = np.random.default_rng(11)
+    x = rng.normal(0, 1.5, (5, 2560)).astype(np.float32)
+    w = rng.normal(1, 0.1, 2560).astype(np.float32)
+    assert ol.rms_norm(x, w, 1e-6).tobytes() == ol.rms_norm(x, w, 1e-6, ol.ref()).tobytes()
+    u = rng.normal(0, 1, (5, 2560)).astype(np.float32)
+    r0, o0 = ol.add_rms_norm(x, u, w, 1e-6)
+    r1, o1 = ol.add_rms_norm(x, u, w, 1e-6, ol.ref())
+    assert r0.tobytes() == r1.tobytes() and o0.tobytes() == o1.tobytes()
+    m = rng.normal(0, 2, (3, 2 * 1000)).astype(np.float32)
+    assert ol.swiglu(m).tobytes() == ol.swiglu(m, ol.ref()).tobytes()
+    q = rng.normal(0, 1, (4, 6, 128)).astype(np.float32)
+    ang = rng.uniform(0, 6.28, (4, 64)).astype(np.float32)
+    c, s = np.cos(ang).astype(np.float32), np.sin(ang).astype(np.float32)
+    assert ol.rope(q, c, s, 128).tobytes() == ol.rope(q, c, s, 128, ol.ref()).tobytes()
+    part = ol.rope(q[:, :, :96].copy(), c[:, :32], s[:, :32], 64)  # rope_dim < dim
+    assert part.tobytes() == ol.rope(q[:, :, :96].copy(), c[:, :32], s[:, :32], 64,
+                                     ol.ref()).tobytes()
+    for dim in (128, 80):  # 80: a 16-lane step and a scalar tail in the dot product
+        qq = rng.normal(0, 1, (7, dim)).astype(np.float32)
+        kk = rng.normal(0, 1, (19, dim)).astype(np.float32)
+        vv = rng.normal(0, 1, (19, dim)).astype(np.float32)
+        mask = np.zeros((7, 19), dtype=np.float32)
+        for t in range(7):
+            mask[t, 12 + t + 1:] = -np.inf
+        a = ol.sdpa_head(qq, kk, vv, dim ** -0.5, mask)
+        b = ol.sdpa_head(qq, kk, vv, dim ** -0.5, mask, ol.ref())
+        assert a.tobytes() == b.tobytes()
