@@ -569,6 +569,61 @@ def json_only_stdout():
     return os.fdopen(keep, "w")
 
 
+def dense_decoder(torch, pkg, ctx, args):
+    """Benchmark configuration 3 end to end on one GPU: the Qwen3-4B-shaped dense decoder (36
+    layers, hidden 2560, 32 q / 8 kv heads of 128, SwiGLU intermediate 9728, vocabulary
+    151936; synthetic W4G128 weights), a 256-token random prompt and 64 greedy steps, every
+    operator a libb200w4 kernel (palm-infra_b200/decoder.py).  The reference's protocol
+    (examples/cli_common.cpp:418-436): prefill_tps = 256 / prefill seconds, decode_tps = 64 /
+    decode seconds; wall clock around synchronised regions, the greedy token read back every
+    step as a sampler would."""
+    dec = pkg.decoder
+    cfg = dec.DecoderConfig.qwen3_4b()
+    weights = dec.synthetic_weights(cfg, seed=SEED_W, distinct_layers=1)
+    prompt = np.random.default_rng(11).integers(0, cfg.vocab, 256).tolist()
+    out = {"config": "36 layers, hidden 2560, 32/8 heads x 128, intermediate 9728, vocab 151936",
+           "decode_launch": "one captured CUDA graph per step (position and tokens on the "
+                            "device), the token read back by the host after every step"}
+    for name, rule in (("reference_rule", pkg.capi.ACT_G32), ("per128_prefill", pkg.capi.ACT_G128)):
+        model = dec.DenseDecoder(ctx, cfg, weights, capacity=384, multi_row_rule=rule)
+        model.generate(prompt, 3)  # warm every kernel and buffer
+        model.generate(prompt, 3, replay=True)
+        times = []
+        for _ in range(3):
+            model.reset()
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            model.prefill(prompt)
+            ctx.sync()
+            t1 = time.perf_counter()
+            toks = []
+            for _ in range(64):
+                model.replay_decode_step()
+                toks.append(int(model.token.item()))  # synchronises: a host sampler's read
+            t2 = time.perf_counter()
+            for _ in range(64):  # the same steps with no host read in between
+                model.replay_decode_step()
+            torch.cuda.synchronize()
+            t3 = time.perf_counter()
+            model.reset()
+            model.prefill(prompt)
+            ctx.sync()
+            t4 = time.perf_counter()
+            for _ in range(16):  # eager: one host call and one launch per operator
+                model.decode_step()
+            ctx.sync()
+            t5 = time.perf_counter()
+            times.append((t1 - t0, t2 - t1, t3 - t2, (t5 - t4) * 4))
+        pf, dc, dq, de = (statistics.median(t[i] for t in times) for i in range(4))
+        out[name] = {"prefill_tps": 256 / pf, "decode_tps": 64 / dc, "prefill_ms": pf * 1e3,
+                     "decode_ms_per_token": dc * 1e3 / 64,
+                     "decode_tps_no_host_read": 64 / dq, "decode_tps_eager_launches": 64 / de,
+                     "multi_row_rule": "per 32 values (the reference's)" if rule == 32 else
+                                       "per 128 values (tensor-core path)"}
+        model.free()
+    return out
+
+
 def run_ours(args):
     out = json_only_stdout()
     import torch
@@ -1024,6 +1079,7 @@ def run_ours(args):
         line["sweep"] = sweep
         line["gpu_reference"] = gpu_reference(torch, pkg, args, value,
                                               sweep["m256"]["us_per_matmul"])
+        line["dense_decoder_4b"] = dense_decoder(torch, pkg, ctx, args)
 
         # ---- CPU baseline: the reference's own kernel on this box's host cores ----------
         probe, kind, cores, isa = cpu_gemv_seconds(pkg, 1, 16, 8)

@@ -352,15 +352,39 @@ size_t b2w4_chain_weight_bytes(const b2w4_chain* chain);
  *                      [2I] = gate | up; out[i] = (gate[i] / (1+exp(-gate[i]))) * up[i]
  *   b2w4_elementwise   OpType::ADD / MUL on equal-shaped contiguous tensors
  *   b2w4_rope          OpType::ROTARY_EMBED, kernel_rope with interleave == 0
- *                      (kernels/rope.cpp:11-50, :155-195): x [tokens][heads][dim],
- *                      cos / sin [tokens][rope_dim/2]; in place when out == x
+ *                      (kernels/rope.cpp:11-50, :155-195): x [tokens][heads][dim];
+ *                      cos / sin are tables [positions][rope_dim/2] (filled on the
+ *                      host as engine/input_prep.cpp:18-31 does) and token t takes row
+ *                      first_position + t, or *position_dev + t when position_dev is
+ *                      given; in place when out == x
  *   b2w4_attention     OpType::SDPA with a KV cache (kernels/attention.cpp:1043-1057
  *                      for the cache layout [kv_head][capacity][dim], fp32;
  *                      kernels/attention_x86_avx512.cpp:47-109 for the arithmetic):
  *                      appends the new tokens' k, v [tokens][kv_heads][dim] at
  *                      positions past.., then causal attention of q
  *                      [tokens][heads][dim] over keys 0 .. past + t, full-row softmax,
- *                      P*V accumulated in ascending key order
+ *                      P*V accumulated in ascending key order (dim <= 256; the scores
+ *                      of all visible keys are held in shared memory, which bounds
+ *                      them near 45,000); past_dev (optional)
+ *                      gives `past` from device memory instead
+ *                      k_dev and v_dev both NULL: nothing is appended, the cache rows
+ *                      past .. past + tokens - 1 are in place already (b2w4_qkv_prepare)
+ *   b2w4_qkv_prepare   what sits between the fused qkv matmul and attention, in one
+ *                      launch: rows of the merged output [tokens][(heads + 2 kv_heads)
+ *                      * dim] -- Q and K rows get the per-head RMSNorm (weights may be
+ *                      NULL: none) and the rotary embedding over the whole head
+ *                      (engine/cuda_attention.cu:8-55 fuses the two likewise), Q lands
+ *                      in q_out [tokens][heads][dim], K and V in their cache rows
+ *                      past + t.  Bit-identical to b2w4_rms_norm + b2w4_rope +
+ *                      the append of b2w4_attention.  dim a multiple of 64, <= 256
+ *   b2w4_advance       *counter_dev += by, after history_dev[*counter_dev] = *token_dev
+ *                      (both optional).  With the position on the device a decode
+ *                      step is the same sequence of launches for every token and can
+ *                      be captured once in a CUDA graph and replayed (the reference
+ *                      keeps its decode graph static for the same reason,
+ *                      engine/model_loader.cpp:1111) -- no counterpart as an operator
+ *   b2w4_copy_rows     OpType::CONTIGUOUS for a block of rows: a strided window (e.g.
+ *                      the q, k or v columns of a fused qkv output) made contiguous
  *   b2w4_embed_rows    rows ids[r] of an fp16 table [vocab][dim] widened to fp32 */
 int b2w4_rms_norm(b2w4_ctx* ctx, const float* x_dev, int ldx, int rows, int dim,
                   const float* weight_dev, float eps, float* out_dev, int ldo);
@@ -372,10 +396,21 @@ int b2w4_swiglu(b2w4_ctx* ctx, const float* merged_dev, int ldm, int rows, int i
 int b2w4_elementwise(b2w4_ctx* ctx, const float* a_dev, const float* b_dev, float* out_dev,
                      size_t count, int multiply);
 int b2w4_rope(b2w4_ctx* ctx, const float* x_dev, float* out_dev, int tokens, int heads, int dim,
-              const float* cos_dev, const float* sin_dev, int rope_dim);
+              const float* cos_dev, const float* sin_dev, int rope_dim, int first_position,
+              const int* position_dev);
 int b2w4_attention(b2w4_ctx* ctx, const float* q_dev, const float* k_dev, const float* v_dev,
                    float* k_cache_dev, float* v_cache_dev, float* out_dev, int tokens, int heads,
-                   int kv_heads, int dim, int past, int capacity, float scale);
+                   int kv_heads, int dim, int past, const int* past_dev, int capacity,
+                   float scale);
+int b2w4_qkv_prepare(b2w4_ctx* ctx, const float* qkv_dev, int ld, int tokens, int heads,
+                     int kv_heads, int dim, const float* q_weight_dev, const float* k_weight_dev,
+                     float eps, const float* cos_dev, const float* sin_dev, int past,
+                     const int* past_dev, float* q_out_dev, float* k_cache_dev, float* v_cache_dev,
+                     int capacity);
+int b2w4_advance(b2w4_ctx* ctx, int* counter_dev, int by, const int32_t* token_dev,
+                 int32_t* history_dev, int history_len);
+int b2w4_copy_rows(b2w4_ctx* ctx, const float* src_dev, int ld_src, float* dst_dev, int ld_dst,
+                   int rows, int cols);
 int b2w4_embed_rows(b2w4_ctx* ctx, const void* table_fp16_dev, const int32_t* ids_dev, int rows,
                     int dim, float* out_dev, int ldo);
 

@@ -28,7 +28,8 @@ SYMBOLS = [
     "b2w4_chain_create", "b2w4_chain_create_tp", "b2w4_chain_scratch_words", "b2w4_chain_destroy", "b2w4_chain_run", "b2w4_chain_run_host",
     "b2w4_chain_input", "b2w4_chain_output", "b2w4_chain_weight_bytes", "b2w4_chain_set_trace",
     "b2w4_rms_norm", "b2w4_add_rms_norm", "b2w4_swiglu", "b2w4_elementwise", "b2w4_rope",
-    "b2w4_attention", "b2w4_embed_rows",
+    "b2w4_attention", "b2w4_embed_rows", "b2w4_copy_rows", "b2w4_advance",
+    "b2w4_qkv_prepare",
     "b2w4_kernel_launches",
 ]
 
@@ -124,9 +125,13 @@ def lib():
         L.b2w4_add_rms_norm.argtypes = [vp, f_p, i, f_p, i, i, i, f_p, fl, f_p, i]
         L.b2w4_swiglu.argtypes = [vp, f_p, i, i, i, f_p, i]
         L.b2w4_elementwise.argtypes = [vp, f_p, f_p, f_p, C.c_size_t, i]
-        L.b2w4_rope.argtypes = [vp, f_p, f_p, i, i, i, f_p, f_p, i]
-        L.b2w4_attention.argtypes = [vp, f_p, f_p, f_p, f_p, f_p, f_p, i, i, i, i, i, i, fl]
+        L.b2w4_rope.argtypes = [vp, f_p, f_p, i, i, i, f_p, f_p, i, i, vp]
+        L.b2w4_attention.argtypes = [vp, f_p, f_p, f_p, f_p, f_p, f_p, i, i, i, i, i, vp, i, fl]
+        L.b2w4_advance.argtypes = [vp, vp, i, vp, vp, i]
+        L.b2w4_qkv_prepare.argtypes = [vp, f_p, i, i, i, i, i, f_p, f_p, fl, f_p, f_p, i, vp,
+                                       f_p, f_p, f_p, i]
         L.b2w4_embed_rows.argtypes = [vp, vp, vp, i, i, f_p, i]
+        L.b2w4_copy_rows.argtypes = [vp, f_p, i, f_p, i, i, i]
         L.b2w4_kernel_launches.argtypes = [vp]
         L.b2w4_kernel_launches.restype = C.c_uint64
         _lib = L
@@ -407,15 +412,39 @@ class Context:
         self._check(lib().b2w4_elementwise(self.handle, _dptr(a), _dptr(b), _dptr(out),
                                            a.numel(), 1 if multiply else 0))
 
-    def rope(self, x, out, tokens, heads, dim, cos, sin, rope_dim):
+    def rope(self, x, out, tokens, heads, dim, cos, sin, rope_dim, first_position=0,
+             position_dev=None):
+        """cos / sin: tables [positions, rope_dim // 2]; token t takes row first_position + t,
+        or position_dev[0] + t (an int32 CUDA tensor)."""
         self._check(lib().b2w4_rope(self.handle, _dptr(x), _dptr(out), tokens, heads, dim,
-                                    _dptr(cos), _dptr(sin), rope_dim))
+                                    _dptr(cos), _dptr(sin), rope_dim, first_position,
+                                    _dptr(position_dev)))
 
     def attention(self, q, k, v, k_cache, v_cache, out, tokens, heads, kv_heads, dim, past,
-                  capacity, scale):
+                  capacity, scale, past_dev=None):
         self._check(lib().b2w4_attention(self.handle, _dptr(q), _dptr(k), _dptr(v),
                                          _dptr(k_cache), _dptr(v_cache), _dptr(out), tokens,
-                                         heads, kv_heads, dim, past, capacity, scale))
+                                         heads, kv_heads, dim, past, _dptr(past_dev), capacity,
+                                         scale))
+
+    def qkv_prepare(self, qkv, tokens, heads, kv_heads, dim, q_weight, k_weight, eps, cos, sin,
+                    past, q_out, k_cache, v_cache, capacity, past_dev=None):
+        """Merged qkv rows -> normalised + rotated Q in q_out, K and V in their cache rows."""
+        self._check(lib().b2w4_qkv_prepare(
+            self.handle, _dptr(qkv), qkv.stride(0), tokens, heads, kv_heads, dim,
+            _dptr(q_weight), _dptr(k_weight), eps, _dptr(cos), _dptr(sin), past, _dptr(past_dev),
+            _dptr(q_out), _dptr(k_cache), _dptr(v_cache), capacity))
+
+    def advance(self, counter_dev, by=1, token_dev=None, history_dev=None):
+        """counter_dev[0] += by after history_dev[counter_dev[0]] = token_dev[0]."""
+        self._check(lib().b2w4_advance(self.handle, _dptr(counter_dev), by, _dptr(token_dev),
+                                       _dptr(history_dev),
+                                       history_dev.numel() if history_dev is not None else 0))
+
+    def copy_rows(self, src, dst, rows, cols):
+        """dst[r, :cols] = src[r, :cols]; src / dst are 2-D views with their own row strides."""
+        self._check(lib().b2w4_copy_rows(self.handle, _dptr(src), src.stride(0), _dptr(dst),
+                                         dst.stride(0), rows, cols))
 
     def embed_rows(self, table_fp16, ids, out):
         rows, dim = out.shape

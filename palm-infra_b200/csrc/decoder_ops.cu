@@ -13,6 +13,7 @@
 namespace {
 
 constexpr int kNormThreads = 256;
+constexpr int kAttnMaxDim = 256;  // widest attention head
 
 __device__ __forceinline__ float block_sum(float v, float* s_part) {
 #pragma unroll
@@ -58,7 +59,42 @@ rms_norm_kernel(float* __restrict__ x, int ldx, const float* __restrict__ update
     float* xr = x + (size_t)blockIdx.x * ldx;
     const float* ur = update ? update + (size_t)blockIdx.x * ldu : nullptr;
     float* orow = out + (size_t)blockIdx.x * ldo;
+    // up to kNormHeld values per thread stay in registers between the two passes, all their
+    // loads in flight together; longer rows re-read the row
+    constexpr int kNormHeld = 16;
     float ss = 0.f;
+    if (dim <= kNormHeld * kNormThreads) {
+        float v[kNormHeld], w[kNormHeld];
+#pragma unroll
+        for (int u = 0; u < kNormHeld; ++u) {
+            const int d = threadIdx.x + kNormThreads * u;
+            v[u] = d < dim ? xr[d] : 0.f;
+            w[u] = d < dim ? weight[d] : 0.f;
+        }
+        if (ur) {
+#pragma unroll
+            for (int u = 0; u < kNormHeld; ++u) {
+                const int d = threadIdx.x + kNormThreads * u;
+                if (d < dim) {
+                    v[u] = __fadd_rn(v[u], ur[d]);
+                    xr[d] = v[u];
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kNormHeld; ++u)  // the same per-thread order as the strided loop
+            if (threadIdx.x + kNormThreads * u < dim)
+                ss = __fadd_rn(ss, __fmul_rn(v[u], v[u]));
+        ss = block_sum(ss, s_part);
+        const float r = __fdiv_rn(1.f, sqrtf(__fadd_rn(__fdiv_rn(ss, (float)dim), eps)));
+#pragma unroll
+        for (int u = 0; u < kNormHeld; ++u) {
+            const int d = threadIdx.x + kNormThreads * u;
+            if (d < dim)
+                orow[d] = __fmul_rn(__fmul_rn(v[u], r), w[u]);
+        }
+        return;
+    }
     for (int d = threadIdx.x; d < dim; d += blockDim.x) {
         float v = xr[d];
         if (ur) {
@@ -122,19 +158,23 @@ __global__ void binary_kernel(const float* __restrict__ a, const float* __restri
 // kernel_rope, halves form (kernels/rope.cpp:11-50, interleave == false as the Qwen3 graphs
 // use it, models/qwen3.py:332-333): out[i] = x0*c - x1*s, out[i+half] = x0*s + x1*c with
 // x0 = x[i], x1 = x[i+half]; features beyond rope_dim are copied.  x: [tokens][heads][dim],
-// cos / sin: [tokens][rope_dim/2].  In place when out == x.
+// cos / sin: tables [positions][rope_dim/2]; token t uses row pos0 + t, or *pos_dev + t when
+// the position lives on the device (a decode step captured once in a CUDA graph and replayed
+// for every position).  In place when out == x.
 __global__ void rope_kernel(const float* __restrict__ x, float* __restrict__ out, int tokens,
                             int heads, int dim, const float* __restrict__ cosv,
-                            const float* __restrict__ sinv, int rope_dim) {
+                            const float* __restrict__ sinv, int rope_dim, int pos0,
+                            const int* __restrict__ pos_dev) {
     b2w4_pdl_chain_entry();
     const int half = rope_dim >> 1;
+    const int pos = pos_dev ? *pos_dev : pos0;
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t per_row = (size_t)half + (size_t)(dim - rope_dim);
     if (i >= (size_t)tokens * heads * per_row)
         return;
     const size_t rowi = i / per_row;
     const int j = (int)(i - rowi * per_row);
-    const int t = (int)(rowi / heads);
+    const int t = pos + (int)(rowi / heads);
     const float* xr = x + rowi * dim;
     float* orow = out + rowi * dim;
     if (j < half) {
@@ -152,8 +192,10 @@ __global__ void rope_kernel(const float* __restrict__ x, float* __restrict__ out
 // reference's cache after its header (kernels/attention.cpp:1043-1057).
 __global__ void kv_append_kernel(const float* __restrict__ k, const float* __restrict__ v,
                                  float* __restrict__ k_cache, float* __restrict__ v_cache,
-                                 int tokens, int kv_heads, int dim, int past, int capacity) {
+                                 int tokens, int kv_heads, int dim, int past0,
+                                 const int* __restrict__ past_dev, int capacity) {
     b2w4_pdl_chain_entry();
+    const int past = past_dev ? min(*past_dev, capacity - tokens) : past0;
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= (size_t)tokens * kv_heads * dim)
         return;
@@ -165,20 +207,106 @@ __global__ void kv_append_kernel(const float* __restrict__ k, const float* __res
     v_cache[dst] = v[i];
 }
 
+// The step between the fused qkv matmul and attention in one launch (the reference's CUDA
+// backend fuses Q/K norm and rotary embedding the same way, engine/cuda_attention.cu:8-55):
+// per (token, head) row of the merged qkv output -- a warp each -- the Q and K rows get the
+// per-head RMSNorm (weights optional) and the rotary embedding, with exactly the operations of
+// rms_norm_warp_kernel and rope_kernel in their order, Q goes to q_out [tokens][heads][dim],
+// K and V go straight to their cache rows.  Needs rope over the whole head and dim / 2 a
+// multiple of 32, so that both halves of a rotary pair sit in one lane.
+__global__ void qkv_prepare_kernel(const float* __restrict__ qkv, int ld, int tokens, int heads,
+                                   int kv_heads, int dim, const float* __restrict__ q_weight,
+                                   const float* __restrict__ k_weight, float eps,
+                                   const float* __restrict__ cosv, const float* __restrict__ sinv,
+                                   int pos0, const int* __restrict__ pos_dev,
+                                   float* __restrict__ q_out, float* __restrict__ k_cache,
+                                   float* __restrict__ v_cache, int capacity) {
+    b2w4_pdl_chain_entry();
+    const int slots = heads + 2 * kv_heads;
+    const size_t row = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (row >= (size_t)tokens * slots)
+        return;
+    const int pos = pos_dev ? min(*pos_dev, capacity - tokens) : pos0;
+    const int t = (int)(row / slots), slot = (int)(row % slots);
+    const float* xr = qkv + (size_t)t * ld + (size_t)slot * dim;
+    constexpr int kPer = kAttnMaxDim / 32;
+    float v[kPer];
+#pragma unroll
+    for (int i = 0; i < kPer; ++i)
+        v[i] = lane + 32 * i < dim ? xr[lane + 32 * i] : 0.f;
+    if (slot >= heads + kv_heads) {  // a value row: copied to its cache row
+        float* dst = v_cache + ((size_t)(slot - heads - kv_heads) * capacity + pos + t) * dim;
+#pragma unroll
+        for (int i = 0; i < kPer; ++i)
+            if (lane + 32 * i < dim)
+                dst[lane + 32 * i] = v[i];
+        return;
+    }
+    const bool is_q = slot < heads;
+    const float* w = is_q ? q_weight : k_weight;
+    if (w) {
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < kPer; ++i)
+            if (lane + 32 * i < dim)
+                ss = __fadd_rn(ss, __fmul_rn(v[i], v[i]));
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1)
+            ss = __fadd_rn(ss, __shfl_xor_sync(0xffffffffu, ss, off));
+        const float r = __fdiv_rn(1.f, sqrtf(__fadd_rn(__fdiv_rn(ss, (float)dim), eps)));
+#pragma unroll
+        for (int i = 0; i < kPer; ++i)
+            if (lane + 32 * i < dim)
+                v[i] = __fmul_rn(__fmul_rn(v[i], r), w[lane + 32 * i]);
+    }
+    const int half = dim >> 1, hi = half >> 5;  // v[i] pairs with v[i + hi]
+    float* dst = is_q ? q_out + ((size_t)t * heads + slot) * dim
+                      : k_cache + ((size_t)(slot - heads) * capacity + pos + t) * dim;
+#pragma unroll
+    for (int i = 0; i < kPer / 2; ++i) {
+        if (i < hi) {
+            const int j = lane + 32 * i;
+            const float c = cosv[(size_t)(pos + t) * half + j];
+            const float sn = sinv[(size_t)(pos + t) * half + j];
+            float x0 = 0.f, x1 = 0.f;
+#pragma unroll
+            for (int u = 0; u < kPer; ++u) {  // register picks with compile-time indices
+                if (u == i)
+                    x0 = v[u];
+                if (u == i + hi)
+                    x1 = v[u];
+            }
+            dst[j] = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, sn));
+            dst[j + half] = __fadd_rn(__fmul_rn(x0, sn), __fmul_rn(x1, c));
+        }
+    }
+}
+
 // Scaled-dot-product attention of one (query token, head) over the cache, the x86 reference's
 // arithmetic (kernels/attention_x86_avx512.cpp:47-109): scores = dot(q, k_j) * scale for the
 // visible keys (causal: keys 0 .. past + t), full-row softmax (max, exp, sum, times 1/sum),
 // then out = sum_j p_j * v_j accumulated key by key in ascending order with one fused
 // multiply-add per key and feature, as the reference's loop does.  One block per (token,
-// head); thread d owns output feature d.
-constexpr int kAttnThreads = 128;
+// head).  Scores: a warp per key, four keys' loads in flight at a time.  P*V: thread d owns
+// output feature d and walks the keys in order; the value rows come through shared memory in
+// chunks that all threads fetch together, the next chunk's loads in flight while the current
+// one is consumed, so that the ordered sum does not wait on memory once per key.
+constexpr int kAttnThreads = 256;
+constexpr int kAttnWarps = kAttnThreads / 32;
+constexpr int kAttnStage = 4096;                       // floats of V per chunk
+constexpr int kAttnPerThread = kAttnStage / kAttnThreads;
 __global__ void __launch_bounds__(kAttnThreads)
 attention_kernel(const float* __restrict__ q, const float* __restrict__ k_cache,
                  const float* __restrict__ v_cache, float* __restrict__ out, int tokens,
-                 int heads, int kv_heads, int dim, int past, int capacity, float scale) {
+                 int heads, int kv_heads, int dim, int past0, const int* __restrict__ past_dev,
+                 int capacity, float scale, int score_slots) {
     b2w4_pdl_chain_entry();
-    extern __shared__ float s_scores[];  // [visible keys]
-    __shared__ float s_part[kAttnThreads / 32];
+    const int past = past_dev ? min(*past_dev, capacity - tokens) : past0;
+    extern __shared__ float s_dyn[];
+    float* s_scores = s_dyn;                // [score_slots] >= visible keys
+    float* s_stage = s_dyn + score_slots;   // [kAttnStage]
+    __shared__ float s_part[kAttnWarps];
     const int t = blockIdx.x / heads, h = blockIdx.x % heads;
     const int kvh = h / (heads / kv_heads);
     const int visible = past + t + 1;
@@ -186,16 +314,33 @@ attention_kernel(const float* __restrict__ q, const float* __restrict__ k_cache,
     const float* kc = k_cache + (size_t)kvh * capacity * dim;
     const float* vc = v_cache + (size_t)kvh * capacity * dim;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // a warp per key: lanes split the features, tree-add the partial products
-    for (int j = warp; j < visible; j += kAttnThreads / 32) {
-        float p = 0.f;
-        for (int d = lane; d < dim; d += 32)
-            p = __fmaf_rn(qr[d], kc[(size_t)j * dim + d], p);
+
+    constexpr int kQ = kAttnMaxDim / 32, kKeys = 4;
+    float qv[kQ];
 #pragma unroll
-        for (int off = 16; off > 0; off >>= 1)
-            p = __fadd_rn(p, __shfl_xor_sync(0xffffffffu, p, off));
-        if (lane == 0)
-            s_scores[j] = __fmul_rn(p, scale);
+    for (int i = 0; i < kQ; ++i)
+        qv[i] = lane + 32 * i < dim ? qr[lane + 32 * i] : 0.f;
+    for (int j0 = warp * kKeys; j0 < visible; j0 += kAttnWarps * kKeys) {
+        float kv[kKeys][kQ];
+#pragma unroll
+        for (int u = 0; u < kKeys; ++u)
+#pragma unroll
+            for (int i = 0; i < kQ; ++i)
+                kv[u][i] = (j0 + u < visible && lane + 32 * i < dim)
+                               ? kc[(size_t)(j0 + u) * dim + lane + 32 * i] : 0.f;
+#pragma unroll
+        for (int u = 0; u < kKeys; ++u) {
+            float p = 0.f;
+#pragma unroll
+            for (int i = 0; i < kQ; ++i)
+                if (32 * i < dim)  // lanes past the last feature add +0 products
+                    p = __fmaf_rn(qv[i], kv[u][i], p);
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1)
+                p = __fadd_rn(p, __shfl_xor_sync(0xffffffffu, p, off));
+            if (lane == 0 && j0 + u < visible)
+                s_scores[j0 + u] = __fmul_rn(p, scale);
+        }
     }
     __syncthreads();
     float m = -INFINITY;
@@ -210,16 +355,64 @@ attention_kernel(const float* __restrict__ q, const float* __restrict__ k_cache,
     }
     sum = block_sum(sum, s_part);
     const float inv = __fdiv_rn(1.f, sum);
-    __syncthreads();
-    for (int d = threadIdx.x; d < dim; d += blockDim.x) {
-        float acc = 0.f;
-        for (int j = 0; j < visible; ++j) {
-            const float p = __fmul_rn(s_scores[j], inv);
-            if (p != 0.f)
-                acc = __fmaf_rn(vc[(size_t)j * dim + d], p, acc);
+
+    const int chunk = kAttnStage / dim;  // keys per chunk
+    float r[kAttnPerThread];
+    auto fetch = [&](int j0) {
+        const int n = min(chunk, visible - j0) * dim;
+        const float* src = vc + (size_t)j0 * dim;
+#pragma unroll
+        for (int u = 0; u < kAttnPerThread; ++u) {
+            const int i = threadIdx.x + kAttnThreads * u;
+            r[u] = i < n ? src[i] : 0.f;
         }
-        out[((size_t)t * heads + h) * dim + d] = acc;
+    };
+    fetch(0);
+    float acc = 0.f;
+    for (int j0 = 0; j0 < visible; j0 += chunk) {
+        __syncthreads();  // the previous chunk has been consumed (and the scores are final)
+#pragma unroll
+        for (int u = 0; u < kAttnPerThread; ++u)
+            s_stage[threadIdx.x + kAttnThreads * u] = r[u];
+        __syncthreads();
+        if (j0 + chunk < visible)
+            fetch(j0 + chunk);
+        if (threadIdx.x < dim) {
+            const int nk = min(chunk, visible - j0);
+            for (int j = 0; j < nk; ++j) {
+                const float p = __fmul_rn(s_scores[j0 + j], inv);
+                if (p != 0.f)
+                    acc = __fmaf_rn(s_stage[j * dim + threadIdx.x], p, acc);
+            }
+        }
     }
+    if (threadIdx.x < dim)
+        out[((size_t)t * heads + h) * dim + threadIdx.x] = acc;
+}
+
+// A position counter on the device: *counter += by (after a decode step of a replayed graph),
+// and the step's token appended to a history so that the host may read all of them at the end.
+__global__ void advance_kernel(int* counter, int by, const int32_t* token, int32_t* history,
+                               int history_len) {
+    b2w4_pdl_chain_entry();
+    if (threadIdx.x == 0 && blockIdx.x == 0) {
+        const int at = *counter;
+        if (history && token && at >= 0 && at < history_len)
+            history[at] = *token;
+        *counter = at + by;
+    }
+}
+
+// OpType::CONTIGUOUS for a block of rows (kernels/layout.cpp materialises a strided view the
+// same way): dst[r][c] = src[r][c], each side with its own row stride.
+__global__ void copy_rows_kernel(const float* __restrict__ src, int ld_src,
+                                 float* __restrict__ dst, int ld_dst, int rows, int cols) {
+    b2w4_pdl_chain_entry();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (size_t)rows * cols)
+        return;
+    const int r = (int)(i / cols), c = (int)(i - (size_t)r * cols);
+    dst[(size_t)r * ld_dst + c] = src[(size_t)r * ld_src + c];
 }
 
 // Embedding lookup: rows of an fp16 table widened to fp32 (the reference's EMBEDDING input
@@ -305,48 +498,108 @@ int b2w4_elementwise(b2w4_ctx* ctx, const float* a_dev, const float* b_dev, floa
 }
 
 int b2w4_rope(b2w4_ctx* ctx, const float* x_dev, float* out_dev, int tokens, int heads, int dim,
-              const float* cos_dev, const float* sin_dev, int rope_dim) {
+              const float* cos_dev, const float* sin_dev, int rope_dim, int first_position,
+              const int* position_dev) {
     if (!ctx)
         return B2W4_E_INVALID;
     if (!x_dev || !out_dev || !cos_dev || !sin_dev || tokens <= 0 || heads <= 0 || dim <= 0 ||
-        rope_dim <= 0 || rope_dim > dim || (rope_dim & 1))
+        rope_dim <= 0 || rope_dim > dim || (rope_dim & 1) || first_position < 0)
         return b2w4_fail(ctx, B2W4_E_INVALID, "rope: bad argument");
     const size_t n = (size_t)tokens * heads * ((size_t)rope_dim / 2 + (dim - rope_dim));
     B2W4_CUDA(ctx, b2w4_launch_chained(ctx->pdl, rope_kernel, dim3((unsigned)((n + 255) / 256)),
                                        dim3(256), 0, ctx->stream, x_dev, out_dev, tokens, heads,
-                                       dim, cos_dev, sin_dev, rope_dim));
+                                       dim, cos_dev, sin_dev, rope_dim, first_position,
+                                       position_dev));
     ctx->launches++;
     return B2W4_OK;
 }
 
 int b2w4_attention(b2w4_ctx* ctx, const float* q_dev, const float* k_dev, const float* v_dev,
                    float* k_cache_dev, float* v_cache_dev, float* out_dev, int tokens, int heads,
-                   int kv_heads, int dim, int past, int capacity, float scale) {
+                   int kv_heads, int dim, int past, const int* past_dev, int capacity,
+                   float scale) {
     if (!ctx)
         return B2W4_E_INVALID;
-    if (!q_dev || !k_dev || !v_dev || !k_cache_dev || !v_cache_dev || !out_dev || tokens <= 0 ||
-        heads <= 0 || kv_heads <= 0 || heads % kv_heads || dim <= 0 || past < 0 ||
-        past + tokens > capacity)
+    const bool append = k_dev || v_dev;  // neither: the cache rows are in place already
+    if (!q_dev || (append && (!k_dev || !v_dev)) || !k_cache_dev || !v_cache_dev || !out_dev ||
+        tokens <= 0 ||
+        heads <= 0 || kv_heads <= 0 || heads % kv_heads || dim <= 0 || dim > kAttnMaxDim ||
+        past < 0 || past + tokens > capacity)
         return b2w4_fail(ctx, B2W4_E_INVALID,
                          "attention: bad argument (tokens=%d past=%d capacity=%d heads=%d/%d)",
                          tokens, past, capacity, heads, kv_heads);
-    const size_t smem = sizeof(float) * (size_t)(past + tokens);
+    // with the position on the device the score buffer is sized for a full cache
+    const int score_slots = ((past_dev ? capacity : past + tokens) + 3) & ~3;
+    const size_t smem = sizeof(float) * ((size_t)score_slots + kAttnStage);
     if (smem > 200 * 1024)
         return b2w4_fail(ctx, B2W4_E_INVALID, "attention: %d keys exceed the score buffer",
-                         past + tokens);
+                         past_dev ? capacity : past + tokens);
     static b2w4_smem_optin configured;
     B2W4_CUDA(ctx, b2w4_opt_in_smem(ctx, attention_kernel, smem, configured));
     const size_t n = (size_t)tokens * kv_heads * dim;
-    B2W4_CUDA(ctx, b2w4_launch_chained(ctx->pdl, kv_append_kernel,
-                                       dim3((unsigned)((n + 255) / 256)), dim3(256), 0,
-                                       ctx->stream, k_dev, v_dev, k_cache_dev, v_cache_dev, tokens,
-                                       kv_heads, dim, past, capacity));
+    if (append) {
+        B2W4_CUDA(ctx, b2w4_launch_chained(ctx->pdl, kv_append_kernel,
+                                           dim3((unsigned)((n + 255) / 256)), dim3(256), 0,
+                                           ctx->stream, k_dev, v_dev, k_cache_dev, v_cache_dev,
+                                           tokens, kv_heads, dim, past, past_dev, capacity));
+        ctx->launches++;
+    }
     B2W4_CUDA(ctx, b2w4_launch_chained(ctx->pdl, attention_kernel, dim3(tokens * heads),
                                        dim3(kAttnThreads), smem, ctx->stream, q_dev,
                                        static_cast<const float*>(k_cache_dev),
                                        static_cast<const float*>(v_cache_dev), out_dev, tokens,
-                                       heads, kv_heads, dim, past, capacity, scale));
-    ctx->launches += 2;
+                                       heads, kv_heads, dim, past, past_dev, capacity, scale,
+                                       score_slots));
+    ctx->launches++;
+    return B2W4_OK;
+}
+
+int b2w4_qkv_prepare(b2w4_ctx* ctx, const float* qkv_dev, int ld, int tokens, int heads,
+                     int kv_heads, int dim, const float* q_weight_dev, const float* k_weight_dev,
+                     float eps, const float* cos_dev, const float* sin_dev, int past,
+                     const int* past_dev, float* q_out_dev, float* k_cache_dev, float* v_cache_dev,
+                     int capacity) {
+    if (!ctx)
+        return B2W4_E_INVALID;
+    if (!qkv_dev || !cos_dev || !sin_dev || !q_out_dev || !k_cache_dev || !v_cache_dev ||
+        tokens <= 0 || heads <= 0 || kv_heads <= 0 || dim <= 0 || dim > kAttnMaxDim || dim % 64 ||
+        ld < (heads + 2 * kv_heads) * dim || past < 0 || past + tokens > capacity)
+        return b2w4_fail(ctx, B2W4_E_INVALID,
+                         "qkv_prepare: bad argument (tokens=%d past=%d capacity=%d dim=%d)", tokens,
+                         past, capacity, dim);
+    const size_t threads = (size_t)tokens * (heads + 2 * kv_heads) * 32;
+    B2W4_CUDA(ctx, b2w4_launch_chained(ctx->pdl, qkv_prepare_kernel,
+                                       dim3((unsigned)((threads + 255) / 256)), dim3(256), 0,
+                                       ctx->stream, qkv_dev, ld, tokens, heads, kv_heads, dim,
+                                       q_weight_dev, k_weight_dev, eps, cos_dev, sin_dev, past,
+                                       past_dev, q_out_dev, k_cache_dev, v_cache_dev, capacity));
+    ctx->launches++;
+    return B2W4_OK;
+}
+
+int b2w4_advance(b2w4_ctx* ctx, int* counter_dev, int by, const int32_t* token_dev,
+                 int32_t* history_dev, int history_len) {
+    if (!ctx)
+        return B2W4_E_INVALID;
+    if (!counter_dev)
+        return b2w4_fail(ctx, B2W4_E_INVALID, "advance: no counter");
+    B2W4_CUDA(ctx, b2w4_launch_chained(ctx->pdl, advance_kernel, dim3(1), dim3(32), 0, ctx->stream,
+                                       counter_dev, by, token_dev, history_dev, history_len));
+    ctx->launches++;
+    return B2W4_OK;
+}
+
+int b2w4_copy_rows(b2w4_ctx* ctx, const float* src_dev, int ld_src, float* dst_dev, int ld_dst,
+                   int rows, int cols) {
+    if (!ctx)
+        return B2W4_E_INVALID;
+    if (!src_dev || !dst_dev || rows <= 0 || cols <= 0 || ld_src < cols || ld_dst < cols)
+        return b2w4_fail(ctx, B2W4_E_INVALID, "copy_rows: bad argument");
+    const size_t n = (size_t)rows * cols;
+    B2W4_CUDA(ctx, b2w4_launch_chained(ctx->pdl, copy_rows_kernel,
+                                       dim3((unsigned)((n + 255) / 256)), dim3(256), 0,
+                                       ctx->stream, src_dev, ld_src, dst_dev, ld_dst, rows, cols));
+    ctx->launches++;
     return B2W4_OK;
 }
 

@@ -367,3 +367,58 @@ def causal_attention(q, k_all, v_all, heads, kv_heads, past, scale, which=None):
         kvh = h // (heads // kv_heads)
         out[:, h] = sdpa_head(q[:, h], k_all[:, kvh], v_all[:, kvh], scale, mask, which)
     return out
+
+
+def dense_decoder_tokens(cfg, weights, prompt, steps, multi_row_rule=ACT_G32):
+    """Greedy tokens of the Qwen3-shaped dense decoder (the layer structure of the reference's
+    graph builder, models/qwen3.py:171-345) computed entirely from the oracle's pieces on the
+    CPU: the W4A8 matmul (per 128 values for one row, `multi_row_rule` for several), RMSNorm,
+    per-head Q/K norm, rotary embedding with host-computed tables, causal attention over all
+    keys so far, SwiGLU, residual adds.  Returns (tokens, margins): margin = top-1 minus top-2
+    logit of each step, the quantity that says how fragile the token identity is."""
+    from __graft_entry__ import load_package
+    dec = load_package().decoder
+    sh = weights["shapes"]
+    H, D = cfg.hidden, cfg.head_dim
+    embed = weights["embed"].astype(np.float32)
+    k_all = [np.zeros((0, cfg.kv_heads, D), np.float32) for _ in range(cfg.layers)]
+    v_all = [np.zeros((0, cfg.kv_heads, D), np.float32) for _ in range(cfg.layers)]
+    past = 0
+
+    def forward(ids):
+        nonlocal past
+        T = len(ids)
+        rule = ACT_G128 if T == 1 else multi_row_rule
+        cos, sin = dec.rope_tables(range(past, past + T), D, cfg.rope_theta)
+        x = embed[np.asarray(ids)]
+        h = rms_norm(x, weights["layers"][0]["ln1"], cfg.eps)
+        for li, L in enumerate(weights["layers"]):
+            qkv = matmul_w4(L["qkv"], *sh["qkv"], h, rule=rule)
+            q = qkv[:, :cfg.q_dim].reshape(T * cfg.heads, D)
+            k = qkv[:, cfg.q_dim:cfg.q_dim + cfg.kv_dim].reshape(T * cfg.kv_heads, D)
+            v = qkv[:, cfg.q_dim + cfg.kv_dim:].reshape(T, cfg.kv_heads, D)
+            q = rope(rms_norm(q, L["q_norm"], cfg.eps).reshape(T, cfg.heads, D), cos, sin, D)
+            k = rope(rms_norm(k, L["k_norm"], cfg.eps).reshape(T, cfg.kv_heads, D), cos, sin, D)
+            k_all[li] = np.concatenate([k_all[li], k])
+            v_all[li] = np.concatenate([v_all[li], v])
+            attn = causal_attention(q, k_all[li], v_all[li], cfg.heads, cfg.kv_heads, past,
+                                    D ** -0.5).reshape(T, cfg.q_dim)
+            o = matmul_w4(L["o"], *sh["o"], attn, rule=rule)
+            x, h = add_rms_norm(x, o, L["ln2"], cfg.eps)
+            act = swiglu(matmul_w4(L["gate_up"], *sh["gate_up"], h, rule=rule))
+            dn = matmul_w4(L["down"], *sh["down"], act, rule=rule)
+            nxt = weights["layers"][li + 1]["ln1"] if li + 1 < cfg.layers else weights["final_norm"]
+            x, h = add_rms_norm(x, dn, nxt, cfg.eps)
+        past += T
+        logits = matmul_w4(weights["lm_head"], cfg.vocab, H, h[T - 1:T])[0]
+        top = np.sort(logits)[-2:]
+        return argmax_token(logits), float(top[1] - top[0])
+
+    tokens, margins = [], []
+    tok, mg = forward(list(prompt))
+    for _ in range(steps):
+        tokens.append(tok)
+        margins.append(mg)
+        if len(tokens) < steps:
+            tok, mg = forward([tok])
+    return tokens, margins

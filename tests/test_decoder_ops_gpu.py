@@ -128,6 +128,88 @@ def test_attention_over_the_cache(ctx, tokens, past, heads, kv_heads):
         np.ascontiguousarray(v_all.transpose(1, 0, 2)).tobytes()
     want = ol.causal_attention(q, k_all, v_all, heads, kv_heads, past, scale)
     assert rel_l2(out.cpu().numpy(), want) < 1e-5
+    # the same call with the position read from device memory gives the same bits
+    kcd2, vcd2 = _dev(kc), _dev(vc)
+    out2 = torch.zeros_like(out)
+    past_dev = torch.full((1,), past, dtype=torch.int32, device="cuda")
+    ctx.attention(_dev(q), _dev(k), _dev(v), kcd2, vcd2, out2, tokens, heads, kv_heads, dim, 0,
+                  capacity, scale, past_dev)
+    ctx.sync()
+    assert out2.cpu().numpy().tobytes() == out.cpu().numpy().tobytes()
+    assert kcd2.cpu().numpy().tobytes() == kcd.cpu().numpy().tobytes()
     with pytest.raises(pkg.capi.B200W4Error):  # the cache is full
         ctx.attention(_dev(q), _dev(k), _dev(v), kcd, vcd, out, tokens, heads, kv_heads, dim,
                       capacity - tokens + 1, capacity, scale)
+
+
+def test_position_on_the_device(ctx):
+    """Rotary rows taken at first_position + t or at *position_dev + t agree with the oracle
+    on those rows of the table; b2w4_advance records the token and moves the counter."""
+    import torch
+    rng = np.random.default_rng(11)
+    q = rng.normal(0, 1, (3, 4, 64)).astype(np.float32)
+    ang = rng.uniform(0, 6.28, (40, 32)).astype(np.float32)
+    c, s = np.cos(ang).astype(np.float32), np.sin(ang).astype(np.float32)
+    cd, sd, qd = _dev(c), _dev(s), _dev(q)
+    a = torch.zeros_like(qd)
+    b = torch.zeros_like(qd)
+    pos = torch.full((1,), 17, dtype=torch.int32, device="cuda")
+    ctx.rope(qd, a, 3, 4, 64, cd, sd, 64, 17)
+    ctx.rope(qd, b, 3, 4, 64, cd, sd, 64, 0, pos)
+    hist = torch.full((40,), -1, dtype=torch.int32, device="cuda")
+    tok = torch.full((1,), 1234, dtype=torch.int32, device="cuda")
+    ctx.advance(pos, 1, tok, hist)
+    ctx.advance(pos, 2)
+    ctx.sync()
+    want = ol.rope(q, c[17:20], s[17:20], 64)
+    assert a.cpu().numpy().tobytes() == want.tobytes()
+    assert b.cpu().numpy().tobytes() == want.tobytes()
+    assert int(pos.item()) == 20
+    h = hist.cpu().numpy()
+    assert h[17] == 1234 and (np.delete(h, 17) == -1).all()
+
+
+@pytest.mark.parametrize("tokens,past,heads,kv_heads,dim", [(1, 9, 8, 2, 128), (7, 0, 4, 4, 64),
+                                                            (3, 20, 2, 1, 256)])
+def test_fused_qkv_step_equals_the_separate_operators(ctx, tokens, past, heads, kv_heads, dim):
+    """b2w4_qkv_prepare (per-head norm + rotary embedding + cache append in one launch) leaves
+    the same bits in q and in the caches as rms_norm, rope and the append of b2w4_attention
+    run one after the other; attention without an append then gives the same output."""
+    import torch
+    capacity = 64
+    rng = np.random.default_rng(dim + tokens)
+    width = (heads + 2 * kv_heads) * dim
+    qkv = rng.normal(0, 1, (tokens, width)).astype(np.float32)
+    qw = (1 + 0.1 * rng.standard_normal(dim)).astype(np.float32)
+    kw = (1 + 0.1 * rng.standard_normal(dim)).astype(np.float32)
+    ang = rng.uniform(0, 6.28, (capacity, dim // 2)).astype(np.float32)
+    c, s = _dev(np.cos(ang).astype(np.float32)), _dev(np.sin(ang).astype(np.float32))
+    hist = rng.normal(0, 1, (2, kv_heads, capacity, dim)).astype(np.float32)
+    qkv_d, qw_d, kw_d = _dev(qkv), _dev(qw), _dev(kw)
+    scale = dim ** -0.5
+    # operator by operator
+    q = _dev(qkv[:, :heads * dim].reshape(tokens * heads, dim))
+    k = _dev(qkv[:, heads * dim:(heads + kv_heads) * dim].reshape(tokens * kv_heads, dim))
+    v = _dev(qkv[:, (heads + kv_heads) * dim:])
+    kc1, vc1 = _dev(hist[0]), _dev(hist[1])
+    out1 = torch.zeros((tokens, heads, dim), dtype=torch.float32, device="cuda")
+    ctx.rms_norm(q, qw_d, 1e-6, q)
+    ctx.rms_norm(k, kw_d, 1e-6, k)
+    ctx.rope(q, q, tokens, heads, dim, c, s, dim, past)
+    ctx.rope(k, k, tokens, kv_heads, dim, c, s, dim, past)
+    ctx.attention(q, k, v, kc1, vc1, out1, tokens, heads, kv_heads, dim, past, capacity, scale)
+    # fused, once with the position as an argument and once from device memory
+    for past_dev in (None, torch.full((1,), past, dtype=torch.int32, device="cuda")):
+        kc2, vc2 = _dev(hist[0]), _dev(hist[1])
+        q2 = torch.zeros((tokens * heads, dim), dtype=torch.float32, device="cuda")
+        out2 = torch.zeros_like(out1)
+        arg_past = past if past_dev is None else 0
+        ctx.qkv_prepare(qkv_d, tokens, heads, kv_heads, dim, qw_d, kw_d, 1e-6, c, s, arg_past, q2,
+                        kc2, vc2, capacity, past_dev)
+        ctx.attention(q2, None, None, kc2, vc2, out2, tokens, heads, kv_heads, dim, arg_past,
+                      capacity, scale, past_dev)
+        ctx.sync()
+        assert q2.cpu().numpy().tobytes() == q.cpu().numpy().tobytes()
+        assert kc2.cpu().numpy().tobytes() == kc1.cpu().numpy().tobytes()
+        assert vc2.cpu().numpy().tobytes() == vc1.cpu().numpy().tobytes()
+        assert out2.cpu().numpy().tobytes() == out1.cpu().numpy().tobytes()
