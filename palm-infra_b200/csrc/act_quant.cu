@@ -59,7 +59,9 @@ __global__ void quantize_rows_kernel(const float* __restrict__ x, int lda, int m
 // [m_pad tokens][128 bytes]; inside a token's 128 bytes the 32-block `sub` is the 16-byte
 // chunk pair (2*sub: even k, 2*sub+1: odd k), and chunk c is stored at position
 // c ^ (token % 8): the 128-byte swizzle the MMA's shared-memory descriptor expects, so the
-// plane can be bulk-copied into shared memory as is.  Scales: fp32 [groups][m_pad].
+// plane can be bulk-copied into shared memory as is.  Scales: fp32 [groups][m_pad]; with one
+// scale per 32 values (A32) [groups][m_pad][4], a token's four block scales side by side.
+template <bool A32>
 __global__ void quantize_rows_umma_kernel(const float* __restrict__ x, int lda, int m, int k,
                                           int m_pad, int8_t* __restrict__ q,
                                           float* __restrict__ scales) {
@@ -72,15 +74,20 @@ __global__ void quantize_rows_umma_kernel(const float* __restrict__ x, int lda, 
     const float* src = x + (size_t)row * lda + (size_t)g * 128 + lane * 4;
     float v0 = src[0], v1 = src[1], v2 = src[2], v3 = src[3];
     float amax = fmaxf(fmaxf(fabsf(v0), fabsf(v1)), fmaxf(fabsf(v2), fabsf(v3)));
+    // per 128 values: all 32 lanes; per 32 values: the 8 lanes of a 32-block
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1)
+    for (int off = A32 ? 4 : 16; off > 0; off >>= 1)
         amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
     float scale, inv;
     b2w4_quant_params(amax, scale, inv);
     const int c0 = b2w4_quant_code(v0, inv), c1 = b2w4_quant_code(v1, inv);
     const int c2 = b2w4_quant_code(v2, inv), c3 = b2w4_quant_code(v3, inv);
-    if (lane == 0)
+    if (A32) {
+        if ((lane & 7) == 0)
+            scales[((size_t)g * m_pad + row) * 4 + (lane >> 3)] = scale;
+    } else if (lane == 0) {
         scales[(size_t)g * m_pad + row] = scale;
+    }
     int8_t* tokp = q + ((size_t)g * m_pad + row) * 128;
     const int sub = lane >> 3, j = (lane & 7) * 2, sw = row & 7;
     *reinterpret_cast<char2*>(tokp + (((2 * sub) ^ sw) << 4) + j) =
@@ -159,10 +166,15 @@ int b2w4_launch_quantize_mma(b2w4_ctx* ctx, const float* x, int lda, int m, int 
 }
 
 int b2w4_launch_quantize_umma(b2w4_ctx* ctx, const float* x, int lda, int m, int k, int m_pad,
-                              int8_t* q, float* scales) {
+                              int act_rule, int8_t* q, float* scales) {
     long long warps = (long long)m * (k / 128);
     int grid = (int)((warps * 32 + 255) / 256);
-    quantize_rows_umma_kernel<<<grid, 256, 0, ctx->stream>>>(x, lda, m, k, m_pad, q, scales);
+    if (act_rule == B2W4_ACT_G32)
+        quantize_rows_umma_kernel<true><<<grid, 256, 0, ctx->stream>>>(x, lda, m, k, m_pad, q,
+                                                                       scales);
+    else
+        quantize_rows_umma_kernel<false><<<grid, 256, 0, ctx->stream>>>(x, lda, m, k, m_pad, q,
+                                                                        scales);
     ctx->launches++;
     B2W4_CUDA(ctx, cudaGetLastError());
     return B2W4_OK;

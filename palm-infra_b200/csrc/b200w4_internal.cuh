@@ -190,9 +190,9 @@ int b2w4_launch_gemv_mma(b2w4_ctx* ctx, const b2w4_weight* w, const float* x, in
                      const b2w4_tp_args* tp = nullptr, const b2w4_top1_args* top1 = nullptr);
 
 int b2w4_launch_quantize_umma(b2w4_ctx* ctx, const float* x, int lda, int m, int k, int m_pad,
-                              int8_t* q, float* scales);
+                              int act_rule, int8_t* q, float* scales);
 int b2w4_launch_gemm_tc(b2w4_ctx* ctx, const b2w4_weight* w, const float* x, int lda,
-                        float* y, int ldc, int m, int activation, int act_n_begin,
+                        float* y, int ldc, int m, int act_rule, int activation, int act_n_begin,
                         int act_n_len);
 
 // activation-quantiser output layouts

@@ -275,24 +275,26 @@ static int check_matmul(b2w4_ctx* ctx, const b2w4_weight* w, const void* x, int 
 
 // Up to eight activation rows stream the weight once through the GEMV kernels (one row:
 // dp4a; two to eight: the warp-level int8 tensor instruction); more rows go to the tcgen05
-// kernel (per-128 rule, K <= 10240).  All produce the same bits.
+// kernel (K <= 10240).  All produce the same bits for the same activation rule.
 static int matmul_dispatch(b2w4_ctx* ctx, const b2w4_weight* w, const float* x, int lda,
                            float* y, int ldc, int m, int act_rule, int activation,
                            int act_n_begin, int act_n_len) {
     const bool rows = m > ctx->gemv_max_rows;
     // unaligned activation rows: the tcgen05 path's quantiser reads scalars
     const bool vec = (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (lda & 3) == 0;
-    // the tcgen05 kernel implements the per-128 rule only
-    const bool tc = rows && act_rule == B2W4_ACT_G128 && w->groups <= 80;
+    const bool tc = rows && w->groups <= 80;
+    // mma.sync with register accumulators: when asked for, or when the tensor-core kernel
+    // cannot take the call; of itself only under the per-128 rule for weights whose CTAs
+    // are all resident at once
     const bool mma = rows && vec && b2w4_gemm_mma_fits(w, m, act_rule) &&
-                     (ctx->gemm_kind == 2 ||
-                      (ctx->gemm_kind == 0 &&
-                       (!tc || b2w4_gemm_mma_resident(w, m, act_rule, ctx->sm_count))));
+                     (ctx->gemm_kind == 2 || !tc ||
+                      (ctx->gemm_kind == 0 && act_rule == B2W4_ACT_G128 &&
+                       b2w4_gemm_mma_resident(w, m, act_rule, ctx->sm_count)));
     if (mma)
         return b2w4_launch_gemm_mma(ctx, w, x, lda, y, ldc, m, act_rule, activation, act_n_begin,
                                     act_n_len);
     if (tc)
-        return b2w4_launch_gemm_tc(ctx, w, x, lda, y, ldc, m, activation, act_n_begin,
+        return b2w4_launch_gemm_tc(ctx, w, x, lda, y, ldc, m, act_rule, activation, act_n_begin,
                                    act_n_len);
     return b2w4_launch_gemv(ctx, w, x, lda, y, ldc, m, act_rule, activation, act_n_begin,
                             act_n_len, nullptr);

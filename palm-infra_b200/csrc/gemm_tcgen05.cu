@@ -28,6 +28,16 @@
 //                   CTA's weight rows) and run the fp32 chain in registers
 // TMEM holds three to six group accumulators, so the MMAs run ahead of the fp32 chain.
 // Every wait is bounded; on a timeout the kernel flags the status word and drains.
+//
+// The reference's rule for several rows (kernels/matmul_w4.cpp:785-901 with the per-32
+// quantiser, kernels/matmul_quant.cpp:280-329) is the A32 form of the same kernel: one
+// activation scale per 32 values, and per 32-k block b of a group
+//   D_b = sum q4*q8 over the block;  y = fma(float(D_b), fp32(ws*as[g][b]), y)
+// blocks ascending inside groups ascending.  A 32-k block is exactly one K = 32 MMA step, so
+// the four steps of a group go to four accumulators of their own instead of adding up in
+// one; the fp32 chain then has four times the steps per group and becomes the stage that
+// paces the kernel, which is why that form runs one token block per CTA with all sixteen
+// epilogue warps on the chain (four column ranges) and two to four groups of accumulators.
 #include "b200w4_internal.cuh"
 
 namespace {
@@ -46,7 +56,7 @@ struct GemmArgs {
     const uint8_t* nib;  // [tiles][G][512]
     const void* scl;     // [tiles][G][8] fp16|fp32
     const int8_t* qa;    // [G][m_pad][128] int8, 16-byte chunks swizzled by token%8
-    const float* as;     // [G][m_pad]
+    const float* as;     // [G][m_pad]; per-32 rule: [G][m_pad][4], one scale per 32-k block
     float* y;
     int* status;
     int ldc, m, m_pad, n, groups, tiles;
@@ -145,6 +155,12 @@ __device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
         : "r"(taddr)
         : "memory");
 }
+__device__ __forceinline__ void tmem_ld4(uint32_t taddr, uint32_t (&r)[4]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(taddr)
+                 : "memory");
+}
 // float(d) for |d| < 2^22 without the conversion pipe: 0x4B400000 is 1.5 * 2^23, whose
 // ulp is 1, so adding d to its bit pattern adds d to its value; the subtraction is exact.
 // A group sum is at most 128 * 8 * 127 = 130048 in magnitude.
@@ -177,19 +193,24 @@ struct Smem {
     static constexpr int kTotal = kBarOff + 512 + 1024;  // barriers, + slack to align the base
 };
 
-template <int RP, int NB, bool SCL16>
+template <int RP, int NB, bool SCL16, bool A32>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_w4a8_tc_kernel(const GemmArgs a) {
+    static_assert(!A32 || NB == 1, "the per-32 form runs one token block per CTA");
     constexpr int kAStages = Smem<RP, NB>::kAStages;
     constexpr int kRawSlots = Smem<RP, NB>::kRawSlots;
-    constexpr int CH = RP / 2;  // accumulator columns per epilogue thread
-    // TMEM holds kAcc group accumulators of NB*RP columns each (512 columns in all), so
+    constexpr int kSplit = A32 ? 4 : 2;  // column ranges the epilogue warpgroups split
+    constexpr int CH = RP / kSplit;      // accumulator columns per epilogue thread
+    constexpr int kBlk = A32 ? 4 : 1;    // accumulators per group and token block
+    // TMEM holds kAcc group accumulators of kBlk*NB*RP columns each (512 columns in all), so
     // the MMAs run up to kAcc-1 groups ahead of the fp32 chain
-    constexpr int kAcc = 512 / (NB * RP) > 6 ? 6 : 512 / (NB * RP);
-    constexpr int kAccCols = NB * RP;
-    // With one token block only two of the four epilogue warpgroups have accumulator rows;
-    // the other two unpack weights instead (the unpack stage bounds the pipeline there).
-    constexpr int kEpiActive = NB == 2 ? kEpiWarps : kEpiWarps / 2;
+    constexpr int kAccCols = kBlk * NB * RP;
+    constexpr int kAcc = 512 / kAccCols > 6 ? 6 : 512 / kAccCols;
+    static_assert(kAcc >= 2, "no accumulator to run ahead into");
+    // With one token block and the per-128 rule only two of the four epilogue warpgroups
+    // have accumulator rows; the other two unpack weights instead (the unpack stage bounds
+    // the pipeline there).
+    constexpr int kEpiActive = (NB == 2 || A32) ? kEpiWarps : kEpiWarps / 2;
     constexpr int kUnpackAll = kUnpackWarps + (kEpiWarps - kEpiActive);
     extern __shared__ uint8_t smem_raw[];
     // swizzle atoms need a 1024-byte aligned base
@@ -309,11 +330,13 @@ gemm_w4a8_tc_kernel(const GemmArgs a) {
                 for (int mb = 0; mb < n_blocks; ++mb) {
                     const uint32_t a_addr =
                         smem_u32(smem + S::kActOff + sa * S::kActStage + mb * 128 * 128);
-                    const uint32_t d = tmem_base + (uint32_t)(b * kAccCols + mb * RP);
+                    const uint32_t d = tmem_base + (uint32_t)(b * kAccCols + mb * kBlk * RP);
 #pragma unroll
-                    for (int j = 0; j < 4; ++j)  // four K = 32 steps inside the swizzle row
-                        umma_i8(d, umma_desc_k_sw128(a_addr + j * 32),
-                                umma_desc_k_sw128(b_addr + j * 32), idesc, j > 0 ? 1u : 0u);
+                    for (int j = 0; j < 4; ++j)  // four K = 32 steps inside the swizzle row:
+                        // summed into one accumulator, or (A32) one accumulator per step
+                        umma_i8(d + (A32 ? j * RP : 0), umma_desc_k_sw128(a_addr + j * 32),
+                                umma_desc_k_sw128(b_addr + j * 32), idesc,
+                                (!A32 && j > 0) ? 1u : 0u);
                 }
                 // a commit fires when every MMA issued so far has retired
                 umma_commit(&act_free[sa]);  // the activation stage may be refilled
@@ -385,7 +408,8 @@ gemm_w4a8_tc_kernel(const GemmArgs a) {
         const int ch = eg / NB;                // its column half
         const int lq = warp & 3;               // TMEM lane quarter this warp may read
         const int tok = tok0 + mb * 128 + lq * 32 + lane;
-        const bool active = ch < 2 && mb < n_blocks;
+        // a warp whose 32 tokens all lie past the last row has no chain to run
+        const bool active = ch < kSplit && mb < n_blocks && mb * 128 + lq * 32 < m_here;
         float acc[CH];
 #pragma unroll
         for (int c = 0; c < CH; ++c)
@@ -409,61 +433,122 @@ gemm_w4a8_tc_kernel(const GemmArgs a) {
         asm volatile("bar.sync 1, %0;" ::"n"(kEpiActive * 32) : "memory");
         const float* wsf = reinterpret_cast<const float*>(smem + S::kWsOff) + ch * CH;
         const bool has_tok = active && tok < a.m;
-        // the token's activation scales are fetched four groups ahead: a global load takes
-        // about as long as a whole group, so a shorter distance would pace the loop
-        auto load_as = [&](int g) {
-            return (has_tok && g < G) ? a.as[(size_t)g * a.m_pad + tok] : 0.f;
-        };
-        float a0 = load_as(0), a1 = load_as(1), a2 = load_as(2), a3 = load_as(3);
-        for (int g = 0; g < G; ++g) {
-            const int b = g % kAcc, use = g / kAcc;
-            const float a_s = a0;
-            a0 = a1;
-            a1 = a2;
-            a2 = a3;
-            a3 = load_as(g + 4);
-            if (*s_abort || !mbar_wait(&acc_full[b], use & 1)) {
-                if (lane == 0)
-                    fail();
-                break;
-            }
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            if (active) {
-                const uint32_t taddr = tmem_base + ((uint32_t)(lq * 32) << 16) +
-                                       (uint32_t)(b * kAccCols + mb * RP + ch * CH);
-                // columns are requested in batches of up to 24 before one wait: the TMEM read
-                // latency is paid once or twice per group, not once per 8 columns
-                constexpr int kBatch = 24;
+        if constexpr (A32) {
+            // the token's four block scales of a group are one 16-byte load, fetched two
+            // groups ahead (a group's chain is long enough to cover the load)
+            const float4* as4 = reinterpret_cast<const float4*>(a.as);
+            auto load_as = [&](int g) {
+                return (has_tok && g < G) ? as4[(size_t)g * a.m_pad + tok]
+                                          : make_float4(0.f, 0.f, 0.f, 0.f);
+            };
+            float4 a0 = load_as(0), a1 = load_as(1);
+            for (int g = 0; g < G; ++g) {
+                const int b = g % kAcc, use = g / kAcc;
+                const float asv[4] = {a0.x, a0.y, a0.z, a0.w};
+                a0 = a1;
+                a1 = load_as(g + 2);
+                if (*s_abort || !mbar_wait(&acc_full[b], use & 1)) {
+                    if (lane == 0)
+                        fail();
+                    break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                if (active) {
+                    const uint32_t taddr = tmem_base + ((uint32_t)(lq * 32) << 16) +
+                                           (uint32_t)(b * kAccCols + ch * CH);
+                    // two blocks' columns are requested before one wait
+                    constexpr int kJB = 2;
 #pragma unroll
-                for (int b0 = 0; b0 < CH; b0 += kBatch) {
-                    constexpr int kMaxB = kBatch;
-                    uint32_t r[kMaxB];
+                    for (int j0 = 0; j0 < 4; j0 += kJB) {
+                        uint32_t r[kJB][CH];
 #pragma unroll
-                    for (int c0 = 0; c0 < kMaxB; c0 += 8)
-                        if (b0 + c0 < CH)
-                            tmem_ld8(taddr + b0 + c0, *reinterpret_cast<uint32_t(*)[8]>(&r[c0]));
-                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                        for (int j = 0; j < kJB; ++j)
 #pragma unroll
-                    for (int c = 0; c < kMaxB; c += 4) {
-                        if (b0 + c < CH) {
+                            for (int c0 = 0; c0 < CH; c0 += 4)
+                                tmem_ld4(taddr + (j0 + j) * RP + c0,
+                                         *reinterpret_cast<uint32_t(*)[4]>(&r[j][c0]));
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                        for (int c = 0; c < CH; c += 4) {
                             const float4 w4 =
-                                *reinterpret_cast<const float4*>(wsf + g * RP + b0 + c);
-                            acc[b0 + c + 0] = __fmaf_rn(int_to_float_exact((int)r[c + 0]),
-                                                        __fmul_rn(w4.x, a_s), acc[b0 + c + 0]);
-                            acc[b0 + c + 1] = __fmaf_rn(int_to_float_exact((int)r[c + 1]),
-                                                        __fmul_rn(w4.y, a_s), acc[b0 + c + 1]);
-                            acc[b0 + c + 2] = __fmaf_rn(int_to_float_exact((int)r[c + 2]),
-                                                        __fmul_rn(w4.z, a_s), acc[b0 + c + 2]);
-                            acc[b0 + c + 3] = __fmaf_rn(int_to_float_exact((int)r[c + 3]),
-                                                        __fmul_rn(w4.w, a_s), acc[b0 + c + 3]);
+                                *reinterpret_cast<const float4*>(wsf + g * RP + c);
+#pragma unroll
+                            for (int j = 0; j < kJB; ++j) {  // blocks in ascending order
+                                const float s_b = asv[j0 + j];
+                                acc[c + 0] = __fmaf_rn(int_to_float_exact((int)r[j][c + 0]),
+                                                       __fmul_rn(w4.x, s_b), acc[c + 0]);
+                                acc[c + 1] = __fmaf_rn(int_to_float_exact((int)r[j][c + 1]),
+                                                       __fmul_rn(w4.y, s_b), acc[c + 1]);
+                                acc[c + 2] = __fmaf_rn(int_to_float_exact((int)r[j][c + 2]),
+                                                       __fmul_rn(w4.z, s_b), acc[c + 2]);
+                                acc[c + 3] = __fmaf_rn(int_to_float_exact((int)r[j][c + 3]),
+                                                       __fmul_rn(w4.w, s_b), acc[c + 3]);
+                            }
                         }
                     }
                 }
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0)
+                    mbar_arrive(&acc_free[b]);
             }
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            __syncwarp();
-            if (lane == 0)
-                mbar_arrive(&acc_free[b]);
+        } else {
+            // the token's activation scales are fetched four groups ahead: a global load takes
+            // about as long as a whole group, so a shorter distance would pace the loop
+            auto load_as = [&](int g) {
+                return (has_tok && g < G) ? a.as[(size_t)g * a.m_pad + tok] : 0.f;
+            };
+            float a0 = load_as(0), a1 = load_as(1), a2 = load_as(2), a3 = load_as(3);
+            for (int g = 0; g < G; ++g) {
+                const int b = g % kAcc, use = g / kAcc;
+                const float a_s = a0;
+                a0 = a1;
+                a1 = a2;
+                a2 = a3;
+                a3 = load_as(g + 4);
+                if (*s_abort || !mbar_wait(&acc_full[b], use & 1)) {
+                    if (lane == 0)
+                        fail();
+                    break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                if (active) {
+                    const uint32_t taddr = tmem_base + ((uint32_t)(lq * 32) << 16) +
+                                           (uint32_t)(b * kAccCols + mb * RP + ch * CH);
+                    // columns are requested in batches of up to 24 before one wait: the TMEM read
+                    // latency is paid once or twice per group, not once per 8 columns
+                    constexpr int kBatch = 24;
+#pragma unroll
+                    for (int b0 = 0; b0 < CH; b0 += kBatch) {
+                        constexpr int kMaxB = kBatch;
+                        uint32_t r[kMaxB];
+#pragma unroll
+                        for (int c0 = 0; c0 < kMaxB; c0 += 8)
+                            if (b0 + c0 < CH)
+                                tmem_ld8(taddr + b0 + c0, *reinterpret_cast<uint32_t(*)[8]>(&r[c0]));
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                        for (int c = 0; c < kMaxB; c += 4) {
+                            if (b0 + c < CH) {
+                                const float4 w4 =
+                                    *reinterpret_cast<const float4*>(wsf + g * RP + b0 + c);
+                                acc[b0 + c + 0] = __fmaf_rn(int_to_float_exact((int)r[c + 0]),
+                                                            __fmul_rn(w4.x, a_s), acc[b0 + c + 0]);
+                                acc[b0 + c + 1] = __fmaf_rn(int_to_float_exact((int)r[c + 1]),
+                                                            __fmul_rn(w4.y, a_s), acc[b0 + c + 1]);
+                                acc[b0 + c + 2] = __fmaf_rn(int_to_float_exact((int)r[c + 2]),
+                                                            __fmul_rn(w4.z, a_s), acc[b0 + c + 2]);
+                                acc[b0 + c + 3] = __fmaf_rn(int_to_float_exact((int)r[c + 3]),
+                                                            __fmul_rn(w4.w, a_s), acc[b0 + c + 3]);
+                            }
+                        }
+                    }
+                }
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0)
+                    mbar_arrive(&acc_free[b]);
+            }
         }
         // Output: a thread holds one token's CH columns, which lie CH*4 bytes apart from the
         // next token's in y.  Stage the warp's 32 x CH block in shared memory (the operand
@@ -519,10 +604,11 @@ gemm_w4a8_tc_kernel(const GemmArgs a) {
     }
 }
 
-template <int RP, int NB>
+template <int RP, int NB, bool A32 = false>
 int launch_rp(b2w4_ctx* ctx, const GemmArgs& a, bool scl16, dim3 grid) {
     using S = Smem<RP, NB>;
-    auto kern = scl16 ? gemm_w4a8_tc_kernel<RP, NB, true> : gemm_w4a8_tc_kernel<RP, NB, false>;
+    auto kern = scl16 ? gemm_w4a8_tc_kernel<RP, NB, true, A32>
+                      : gemm_w4a8_tc_kernel<RP, NB, false, A32>;
     static b2w4_smem_optin configured[2];  // per instantiation and device
     B2W4_CUDA(ctx, b2w4_opt_in_smem(ctx, kern, S::kTotal, configured[scl16]));
     kern<<<grid, kThreads, S::kTotal, ctx->stream>>>(a);
@@ -540,13 +626,43 @@ int launch_nb(b2w4_ctx* ctx, const GemmArgs& a, bool scl16, dim3 grid, int rows)
     return launch_rp<80, NB>(ctx, a, scl16, grid);
 }
 
+// The per-32 form: one token block per CTA, 32 / 48 / 64 accumulator columns per block.
+int launch_a32(b2w4_ctx* ctx, const GemmArgs& a, bool scl16, dim3 grid, int rows) {
+    if (rows <= 32)
+        return launch_rp<32, 1, true>(ctx, a, scl16, grid);
+    if (rows <= 48)
+        return launch_rp<48, 1, true>(ctx, a, scl16, grid);
+    return launch_rp<64, 1, true>(ctx, a, scl16, grid);
+}
+
+// Rows per CTA for the per-32 form.  The fp32 chain paces a CTA, so its time grows with the
+// accumulator columns of its instantiation (plus a fixed part per group); the launch takes
+// as many rounds as the CTAs need on the SMs.  Pick the tile count with the least product.
+int a32_row_tiles(int tiles, int token_blocks, int sm_count) {
+    int best = 1;
+    long best_cost = -1;
+    for (int r = 1; r <= 8; ++r) {
+        const long ctas = (long)((tiles + r - 1) / r) * token_blocks;
+        const long rounds = (ctas + sm_count - 1) / sm_count;
+        const int cols = r <= 4 ? 32 : r <= 6 ? 48 : 64;
+        const long cost = rounds * (cols + 12);
+        if (best_cost < 0 || cost < best_cost) {
+            best_cost = cost;
+            best = r;
+        }
+    }
+    return best;
+}
+
 }  // namespace
 
 // Quantises the activations (separate launch), then runs the tensor-core kernel.
 int b2w4_launch_gemm_tc(b2w4_ctx* ctx, const b2w4_weight* w, const float* x, int lda,
-                        float* y, int ldc, int m, int activation, int act_n_begin,
+                        float* y, int ldc, int m, int act_rule, int activation, int act_n_begin,
                         int act_n_len) {
     const int G = w->groups;
+    const bool a32 = act_rule == B2W4_ACT_G32;
+    const int spg = a32 ? 4 : 1;  // activation scales per group
     if (G > 80)
         return b2w4_fail(ctx, B2W4_E_INVALID, "gemm: K=%d exceeds the scale staging (K<=10240)",
                          w->k);
@@ -554,17 +670,21 @@ int b2w4_launch_gemm_tc(b2w4_ctx* ctx, const b2w4_weight* w, const float* x, int
     void *qa = nullptr, *as = nullptr;
     int rc;
     if ((rc = b2w4_reserve(ctx, SCR_QA, (size_t)G * m_pad * 128, &qa)) != B2W4_OK ||
-        (rc = b2w4_reserve(ctx, SCR_AS, sizeof(float) * (size_t)G * m_pad, &as)) != B2W4_OK)
+        (rc = b2w4_reserve(ctx, SCR_AS, sizeof(float) * (size_t)G * m_pad * spg, &as)) !=
+            B2W4_OK)
         return rc;
-    if ((rc = b2w4_launch_quantize_umma(ctx, x, lda, m, w->k, m_pad, static_cast<int8_t*>(qa),
-                                        static_cast<float*>(as))) != B2W4_OK)
+    if ((rc = b2w4_launch_quantize_umma(ctx, x, lda, m, w->k, m_pad, act_rule,
+                                        static_cast<int8_t*>(qa), static_cast<float*>(as))) !=
+        B2W4_OK)
         return rc;
     // rows per CTA: one wave of CTAs over the SMs when the token extent is one block
-    const int nb = m > 128 ? 2 : 1;  // token blocks of 128 per CTA
+    const int nb = (m > 128 && !a32) ? 2 : 1;  // token blocks of 128 per CTA
     const int token_blocks = (m + nb * 128 - 1) / (nb * 128);
     int per_sm = (w->tiles * token_blocks + ctx->sm_count - 1) / ctx->sm_count;
     int r_tiles = (per_sm + token_blocks - 1) / token_blocks;
     r_tiles = max(1, min(r_tiles, 10));  // at most 80 accumulator columns per thread
+    if (a32)
+        r_tiles = a32_row_tiles(w->tiles, token_blocks, ctx->sm_count);
     const int R = r_tiles * 8;
     GemmArgs a;
     a.nib = reinterpret_cast<const uint8_t*>(w->nib);
@@ -585,6 +705,8 @@ int b2w4_launch_gemm_tc(b2w4_ctx* ctx, const b2w4_weight* w, const float* x, int
     a.act_n_len = act_n_len;
     dim3 grid((w->tiles + r_tiles - 1) / r_tiles, token_blocks);
     const bool scl16 = w->scales_fp16 != 0;
+    if (a32)
+        return launch_a32(ctx, a, scl16, grid, R);
     return nb == 2 ? launch_nb<2>(ctx, a, scl16, grid, R) : launch_nb<1>(ctx, a, scl16, grid, R);
 }
 
@@ -662,7 +784,7 @@ extern "C" int b2w4_matmul_static_scratch(b2w4_ctx* ctx, const b2w4_weight* w,
     float* as = reinterpret_cast<float*>(base + kStaticCodeBytes);
     const int G = w->groups;
     const int m_pad = (m + 127) / 128 * 128;
-    int rc = b2w4_launch_quantize_umma(ctx, x_dev, lda, m, w->k, m_pad, qa, as);
+    int rc = b2w4_launch_quantize_umma(ctx, x_dev, lda, m, w->k, m_pad, B2W4_ACT_G128, qa, as);
     if (rc != B2W4_OK)
         return rc;
     const int nb = m > 128 ? 2 : 1;

@@ -270,18 +270,38 @@ def test_many_rows_beyond_the_tcgen05_kernels_k_limit(ctx, m, n, k):
     assert y.tobytes() == y_ref.tobytes()
 
 
+@pytest.mark.parametrize("kind", ["tc", "mma"])
 @pytest.mark.parametrize("m,n,k", [(24, 264, 1280), (9, 40, 640), (256, 520, 2560),
-                                   (300, 72, 512), (40, 72, 10368)])
-def test_per32_rule_many_rows_bit_exact(ctx, m, n, k):
+                                   (300, 72, 512), (40, 72, 10368), (129, 2560, 1024),
+                                   (128, 392, 640), (200, 6144, 256)])
+def test_per32_rule_many_rows_bit_exact(ctx_mma, ctx_tc, kind, m, n, k):
     """The reference's M > 1 rule (one int8 scale per 32 values, kernels/matmul_w4.cpp:785-901)
-    for more than eight rows: the mma.sync kernel with one tensor instruction, bias and scale
-    per 32-block, resident and ring mode, several launches of 256 rows."""
+    for more than eight rows, on both many-row kernels: tcgen05 with one tensor-memory
+    accumulator per 32-k block (32 / 48 / 64 weight rows per CTA, one or several token blocks,
+    ragged last tiles), and mma.sync with one tensor instruction, bias and scale per block
+    (resident and ring mode, several launches of 256 rows)."""
     blocks = pkg.synth.bg128_weight(20261125, n + k + m + 1, n, k)
     x = pkg.synth.activations(7, m + 9, m, k)
     x[m // 3, 32:64] = 0.0  # an all-zero 32-block
+    y, _ = run_gpu(ctx_tc if kind == "tc" else ctx_mma, blocks, n, k, x, rule=ol.ACT_G32,
+                   sums=False, pad=4 if n % 16 else 0)
+    y_ref = ol.matmul_w4(blocks, n, k, x, rule=ol.ACT_G32)
+    assert y.tobytes() == y_ref.tobytes()
+
+
+def test_config2_prefill_m256_reference_rule(ctx):
+    """M=256, K=2560, N=9728 (benchmark configuration 2, prefill) under the reference's rule
+    for several rows (per 32 values), the kernel the library picks by itself: bit-exact
+    against the oracle, and within 1e-2 relative L2 of the exact dequantised product."""
+    n, k, m = 9728, 2560, 256
+    blocks = pkg.synth.bg128_weight(20261125, 1, n, k)
+    x = pkg.synth.activations(7, 256, m, k)
     y, _ = run_gpu(ctx, blocks, n, k, x, rule=ol.ACT_G32, sums=False)
     y_ref = ol.matmul_w4(blocks, n, k, x, rule=ol.ACT_G32)
     assert y.tobytes() == y_ref.tobytes()
+    rows = [0, 100, 255]
+    exact = ol.matmul_w4(blocks, n, k, x[rows], rule=ol.ACT_F64)
+    assert rel_l2(y[rows], exact) < 1e-2
 
 
 def test_config2_prefill_m256(ctx):
