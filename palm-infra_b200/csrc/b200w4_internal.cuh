@@ -36,6 +36,7 @@ struct b2w4_ctx {
     // 0 = mma.sync GEMM when its resident mode fits (few tokens), else the tcgen05 GEMM;
     // tuning: 1 = always the tcgen05 GEMM, 2 = the mma.sync GEMM whenever the shape fits it
     int gemm_kind = 0;
+    bool attn_tiles = true;  // a run of tokens takes the tile attention kernel
     int gemv_tpc_override = 0;  // tuning: cap on 8-row tiles per GEMV CTA (0 = heuristic)
     // Routed MoE: B2W4_ACT_G32 = the reference's rule (an expert that holds several rows
     // quantises its activations per 32 values, a lone row per 128); B2W4_ACT_G128 = per 128

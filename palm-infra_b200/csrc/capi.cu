@@ -70,6 +70,9 @@ int b2w4_ctx_create(int device, b2w4_ctx** out) {
         ctx->gemm_kind = 1;
     if (gk && gk[0] == 'm')
         ctx->gemm_kind = 2;
+    const char* at = getenv("B2W4_ATTN");  // debug: "row" keeps the one-row attention kernel
+    if (at && at[0] == 'r')
+        ctx->attn_tiles = false;
     const char* gmr = getenv("B2W4_GEMV_MAX_ROWS");  // tuning/debug: rows kept on the GEMV
     if (gmr && atoi(gmr) > 0)
         ctx->gemv_max_rows = atoi(gmr);
@@ -284,12 +287,15 @@ static int matmul_dispatch(b2w4_ctx* ctx, const b2w4_weight* w, const float* x, 
     const bool vec = (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (lda & 3) == 0;
     const bool tc = rows && w->groups <= 80;
     // mma.sync with register accumulators: when asked for, or when the tensor-core kernel
-    // cannot take the call; of itself only under the per-128 rule for weights whose CTAs
-    // are all resident at once
+    // cannot take the call; of itself under the per-128 rule for weights whose CTAs are all
+    // resident at once, and under the per-32 rule for up to 32 rows (measured: a quarter of
+    // a token block does not pay for the tensor-memory pipeline)
     const bool mma = rows && vec && b2w4_gemm_mma_fits(w, m, act_rule) &&
                      (ctx->gemm_kind == 2 || !tc ||
-                      (ctx->gemm_kind == 0 && act_rule == B2W4_ACT_G128 &&
-                       b2w4_gemm_mma_resident(w, m, act_rule, ctx->sm_count)));
+                      (ctx->gemm_kind == 0 &&
+                       (act_rule == B2W4_ACT_G128
+                            ? b2w4_gemm_mma_resident(w, m, act_rule, ctx->sm_count)
+                            : m <= 32)));
     if (mma)
         return b2w4_launch_gemm_mma(ctx, w, x, lda, y, ldc, m, act_rule, activation, act_n_begin,
                                     act_n_len);

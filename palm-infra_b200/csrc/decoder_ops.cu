@@ -390,6 +390,193 @@ attention_kernel(const float* __restrict__ q, const float* __restrict__ k_cache,
         out[((size_t)t * heads + h) * dim + threadIdx.x] = acc;
 }
 
+// The same attention for a run of new tokens (prefill): one block per (kv head, tile of query
+// tokens) serves every query head of that kv head -- up to kTileRows (token, head) rows --
+// so that a chunk of keys or values is fetched into shared memory once per tile instead of
+// once per row.  Every row's arithmetic is attention_kernel's, operation for operation (the
+// lanes' partial dot products and their xor-tree, the softmax sums per 256 strided partials,
+// the ordered P*V), so both kernels give the same bits.
+//   scores   warp w owns rows 4w .. 4w+3.  For eight keys at a time it forms the 32 partial
+//            products (4 rows x 8 keys) per lane, then a butterfly exchange that halves the
+//            items a lane holds at each of the xor-tree's five levels -- the same sums in the
+//            same order as five shuffles per item, for one shuffle per item
+//   softmax  per row by its warp; probabilities e_j / sum are stored back, zero past the
+//            row's last visible key
+//   P*V      thread (group, d): feature d of DIM/8 rows, keys in ascending order
+constexpr int kTileRows = 32;
+template <int DIM>
+__global__ void __launch_bounds__(kAttnThreads)
+attention_tile_kernel(const float* __restrict__ q, const float* __restrict__ k_cache,
+                      const float* __restrict__ v_cache, float* __restrict__ out, int tokens,
+                      int heads, int kv_heads, int past0, const int* __restrict__ past_dev,
+                      int capacity, float scale, int slots, int tq) {
+    b2w4_pdl_chain_entry();
+    const int past = past_dev ? min(*past_dev, capacity - tokens) : past0;
+    extern __shared__ float s_dyn[];
+    float* s_sc = s_dyn;                           // [kTileRows][slots]
+    float* s_stage = s_dyn + kTileRows * slots;    // [kAttnStage]
+    constexpr int kQ = DIM / 32;                   // features per lane
+    constexpr int kChunk = kAttnStage / DIM;       // keys per staged chunk
+    const int rep = heads / kv_heads;
+    // the last tiles see the most keys: they go first
+    const int kvh = blockIdx.y, t0 = (int)(gridDim.x - 1 - blockIdx.x) * tq;
+    const int t_end = min(t0 + tq, tokens);
+    const int vis_max = past + t_end;              // keys the tile's last token sees
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const float* kc = k_cache + (size_t)kvh * capacity * DIM;
+    const float* vc = v_cache + (size_t)kvh * capacity * DIM;
+    // row r of the tile: token t0 + r / rep, head kvh * rep + r % rep; rows past the tile's
+    // tokens see no key
+    auto row_token = [&](int r) { return t0 + r / rep; };
+    auto row_visible = [&](int r) {
+        return (r < tq * rep && row_token(r) < tokens) ? past + row_token(r) + 1 : 0;
+    };
+
+    float r[kAttnPerThread];
+    auto fetch = [&](const float* base, int j0) {
+        const int n = min(kChunk, vis_max - j0) * DIM;
+        const float* src = base + (size_t)j0 * DIM;
+#pragma unroll
+        for (int u = 0; u < kAttnPerThread; ++u) {
+            const int i = threadIdx.x + kAttnThreads * u;
+            r[u] = i < n ? src[i] : 0.f;
+        }
+    };
+    auto stage = [&]() {
+        __syncthreads();  // the previous chunk has been consumed
+#pragma unroll
+        for (int u = 0; u < kAttnPerThread; ++u)
+            s_stage[threadIdx.x + kAttnThreads * u] = r[u];
+        __syncthreads();
+    };
+
+    // ---- scores ----
+    float qv[4][kQ];
+    int vis[4], vis_warp = 0;
+#pragma unroll
+    for (int rr = 0; rr < 4; ++rr) {
+        const int row = warp * 4 + rr;
+        vis[rr] = row_visible(row);
+        vis_warp = max(vis_warp, vis[rr]);
+        const float* qr = q + ((size_t)row_token(row) * heads + kvh * rep + row % rep) * DIM;
+#pragma unroll
+        for (int i = 0; i < kQ; ++i)
+            qv[rr][i] = vis[rr] ? qr[lane + 32 * i] : 0.f;
+    }
+    fetch(kc, 0);
+    for (int j0 = 0; j0 < vis_max; j0 += kChunk) {
+        stage();
+        if (j0 + kChunk < vis_max)
+            fetch(kc, j0 + kChunk);
+        for (int sub = 0; sub < kChunk / 8 && j0 + sub * 8 < vis_warp; ++sub) {
+            float v[32];  // item rr * 8 + kk: row rr of the warp, key kk of the eight
+#pragma unroll
+            for (int kk = 0; kk < 8; ++kk) {
+                float kr[kQ];
+#pragma unroll
+                for (int i = 0; i < kQ; ++i)
+                    kr[i] = s_stage[(sub * 8 + kk) * DIM + lane + 32 * i];
+#pragma unroll
+                for (int rr = 0; rr < 4; ++rr) {
+                    float p = 0.f;
+#pragma unroll
+                    for (int i = 0; i < kQ; ++i)
+                        p = __fmaf_rn(qv[rr][i], kr[i], p);
+                    v[rr * 8 + kk] = p;
+                }
+            }
+            // xor-tree levels 16, 8, 4, 2, 1; after level `off` a lane keeps the half of its
+            // items selected by that bit of its index, so it ends with item `lane`
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) {
+                const bool up = lane & off;
+#pragma unroll
+                for (int i = 0; i < off; ++i) {
+                    const float send = up ? v[i] : v[i + off];
+                    const float keep = up ? v[i + off] : v[i];
+                    v[i] = __fadd_rn(keep, __shfl_xor_sync(0xffffffffu, send, off));
+                }
+            }
+            const int rr = lane >> 3, key = j0 + sub * 8 + (lane & 7);
+            int my_vis = vis[0];
+            my_vis = rr == 1 ? vis[1] : my_vis;
+            my_vis = rr == 2 ? vis[2] : my_vis;
+            my_vis = rr == 3 ? vis[3] : my_vis;
+            if (key < my_vis)
+                s_sc[(warp * 4 + rr) * slots + key] = __fmul_rn(v[0], scale);
+        }
+    }
+    __syncwarp();
+
+    // ---- softmax, a row at a time by the warp that owns it ----
+#pragma unroll 1
+    for (int rr = 0; rr < 4; ++rr) {
+        float* sc = s_sc + (warp * 4 + rr) * slots;
+        const int n = vis[rr];
+        float m = -INFINITY;
+        for (int j = lane; j < n; j += 32)
+            m = fmaxf(m, sc[j]);
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1)
+            m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
+        // the sum of attention_kernel: 256 partials of stride 256, a tree per 32 of them,
+        // the eight results added in order
+        float sum = 0.f;
+#pragma unroll 1
+        for (int w = 0; w < kAttnWarps; ++w) {
+            float part = 0.f;
+            for (int j = w * 32 + lane; j < n; j += kAttnThreads) {
+                const float e = (float)exp((double)__fsub_rn(sc[j], m));
+                sc[j] = e;
+                part = __fadd_rn(part, e);
+            }
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1)
+                part = __fadd_rn(part, __shfl_xor_sync(0xffffffffu, part, off));
+            sum = __fadd_rn(sum, part);
+        }
+        const float inv = __fdiv_rn(1.f, sum);
+        for (int j = lane; j < ((vis_max + 3) & ~3); j += 32)  // P*V reads four at a time
+            sc[j] = j < n ? __fmul_rn(sc[j], inv) : 0.f;
+    }
+
+    // ---- P*V ----
+    constexpr int kGroups = kAttnThreads / DIM, kRG = kTileRows / kGroups;
+    const int grp = threadIdx.x / DIM, d = threadIdx.x % DIM;
+    float acc[kRG];
+#pragma unroll
+    for (int i = 0; i < kRG; ++i)
+        acc[i] = 0.f;
+    fetch(vc, 0);
+    for (int j0 = 0; j0 < vis_max; j0 += kChunk) {
+        stage();  // its first barrier also orders the probabilities before their use
+        if (j0 + kChunk < vis_max)
+            fetch(vc, j0 + kChunk);
+        const int nk = min(kChunk, vis_max - j0);
+        const float* pr = s_sc + grp * kRG * slots + j0;
+        // four keys at a time; a zero probability leaves the sum as it is (values are
+        // finite), which is what attention_kernel's skip does
+        for (int j = 0; j < nk; j += 4) {
+            const float v0 = s_stage[j * DIM + d], v1 = s_stage[(j + 1) * DIM + d];
+            const float v2 = s_stage[(j + 2) * DIM + d], v3 = s_stage[(j + 3) * DIM + d];
+#pragma unroll
+            for (int i = 0; i < kRG; ++i) {
+                const float4 p = *reinterpret_cast<const float4*>(pr + i * slots + j);
+                acc[i] = __fmaf_rn(v0, p.x, acc[i]);
+                acc[i] = __fmaf_rn(v1, p.y, acc[i]);
+                acc[i] = __fmaf_rn(v2, p.z, acc[i]);
+                acc[i] = __fmaf_rn(v3, p.w, acc[i]);
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < kRG; ++i) {
+        const int row = grp * kRG + i;
+        if (row_visible(row))
+            out[((size_t)row_token(row) * heads + kvh * rep + row % rep) * DIM + d] = acc[i];
+    }
+}
+
 // A position counter on the device: *counter += by (after a decode step of a replayed graph),
 // and the step's token appended to a history so that the host may read all of them at the end.
 __global__ void advance_kernel(int* counter, int by, const int32_t* token, int32_t* history,
@@ -522,34 +709,60 @@ int b2w4_attention(b2w4_ctx* ctx, const float* q_dev, const float* k_dev, const 
         return B2W4_E_INVALID;
     const bool append = k_dev || v_dev;  // neither: the cache rows are in place already
     if (!q_dev || (append && (!k_dev || !v_dev)) || !k_cache_dev || !v_cache_dev || !out_dev ||
-        tokens <= 0 ||
-        heads <= 0 || kv_heads <= 0 || heads % kv_heads || dim <= 0 || dim > kAttnMaxDim ||
-        past < 0 || past + tokens > capacity)
+        tokens <= 0 || heads <= 0 || kv_heads <= 0 || heads % kv_heads || dim <= 0 ||
+        dim > kAttnMaxDim || past < 0 || past + tokens > capacity)
         return b2w4_fail(ctx, B2W4_E_INVALID,
                          "attention: bad argument (tokens=%d past=%d capacity=%d heads=%d/%d)",
                          tokens, past, capacity, heads, kv_heads);
-    // with the position on the device the score buffer is sized for a full cache
-    const int score_slots = ((past_dev ? capacity : past + tokens) + 3) & ~3;
-    const size_t smem = sizeof(float) * ((size_t)score_slots + kAttnStage);
-    if (smem > 200 * 1024)
-        return b2w4_fail(ctx, B2W4_E_INVALID, "attention: %d keys exceed the score buffer",
-                         past_dev ? capacity : past + tokens);
-    static b2w4_smem_optin configured;
-    B2W4_CUDA(ctx, b2w4_opt_in_smem(ctx, attention_kernel, smem, configured));
-    const size_t n = (size_t)tokens * kv_heads * dim;
+    const int keys = past_dev ? capacity : past + tokens;  // position on the device: sized
+                                                           // for a full cache
+    const int rep = heads / kv_heads;
+    // a run of tokens takes the tile kernel while a tile's scores fit in shared memory
+    const int tile_slots = ((keys + 31) & ~31) + 8;  // rows 8 banks apart
+    const size_t tile_smem = sizeof(float) * ((size_t)kTileRows * tile_slots + kAttnStage);
+    const bool tiles = tokens >= 8 && ctx->attn_tiles && rep <= kTileRows &&
+                       (dim == 64 || dim == 128 || dim == 256) && tile_smem <= 200 * 1024;
+    const int score_slots = (keys + 3) & ~3;
+    const size_t row_smem = sizeof(float) * ((size_t)score_slots + kAttnStage);
+    if (!tiles && row_smem > 200 * 1024)
+        return b2w4_fail(ctx, B2W4_E_INVALID, "attention: %d keys exceed the score buffer", keys);
     if (append) {
+        const size_t n = (size_t)tokens * kv_heads * dim;
         B2W4_CUDA(ctx, b2w4_launch_chained(ctx->pdl, kv_append_kernel,
                                            dim3((unsigned)((n + 255) / 256)), dim3(256), 0,
                                            ctx->stream, k_dev, v_dev, k_cache_dev, v_cache_dev,
                                            tokens, kv_heads, dim, past, past_dev, capacity));
         ctx->launches++;
     }
-    B2W4_CUDA(ctx, b2w4_launch_chained(ctx->pdl, attention_kernel, dim3(tokens * heads),
-                                       dim3(kAttnThreads), smem, ctx->stream, q_dev,
-                                       static_cast<const float*>(k_cache_dev),
-                                       static_cast<const float*>(v_cache_dev), out_dev, tokens,
-                                       heads, kv_heads, dim, past, past_dev, capacity, scale,
-                                       score_slots));
+    const float* kc = k_cache_dev;
+    const float* vc = v_cache_dev;
+    if (tiles) {
+        const int tq = kTileRows / rep;
+        const dim3 grid((tokens + tq - 1) / tq, kv_heads);
+#define B2W4_TILE(D)                                                                          \
+    do {                                                                                      \
+        static b2w4_smem_optin cfg;                                                           \
+        B2W4_CUDA(ctx, b2w4_opt_in_smem(ctx, attention_tile_kernel<D>, tile_smem, cfg));      \
+        B2W4_CUDA(ctx, b2w4_launch_chained(ctx->pdl, attention_tile_kernel<D>, grid,          \
+                                           dim3(kAttnThreads), tile_smem, ctx->stream, q_dev, \
+                                           kc, vc, out_dev, tokens, heads, kv_heads, past,    \
+                                           past_dev, capacity, scale, tile_slots, tq));       \
+    } while (0)
+        if (dim == 64)
+            B2W4_TILE(64);
+        else if (dim == 128)
+            B2W4_TILE(128);
+        else
+            B2W4_TILE(256);
+#undef B2W4_TILE
+    } else {
+        static b2w4_smem_optin configured;
+        B2W4_CUDA(ctx, b2w4_opt_in_smem(ctx, attention_kernel, row_smem, configured));
+        B2W4_CUDA(ctx, b2w4_launch_chained(ctx->pdl, attention_kernel, dim3(tokens * heads),
+                                           dim3(kAttnThreads), row_smem, ctx->stream, q_dev, kc,
+                                           vc, out_dev, tokens, heads, kv_heads, dim, past,
+                                           past_dev, capacity, scale, score_slots));
+    }
     ctx->launches++;
     return B2W4_OK;
 }

@@ -37,7 +37,8 @@
 // the four steps of a group go to four accumulators of their own instead of adding up in
 // one; the fp32 chain then has four times the steps per group and becomes the stage that
 // paces the kernel, which is why that form runs one token block per CTA with all sixteen
-// epilogue warps on the chain (four column ranges) and two to four groups of accumulators.
+// epilogue warps on the chain (four column ranges), and hands the accumulators over half a
+// group at a time so that four to eight such halves fit in tensor memory.
 #include "b200w4_internal.cuh"
 
 namespace {
@@ -83,14 +84,16 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// The hint lets the hardware park the thread until the phase completes (or about 20 us pass)
+// instead of having it spin through the issue slots the fp32 chain needs.
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(20000u)
         : "memory");
     return ok != 0;
 }
@@ -155,6 +158,16 @@ __device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
         : "r"(taddr)
         : "memory");
 }
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, "
+        "%11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]),
+          "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
 __device__ __forceinline__ void tmem_ld4(uint32_t taddr, uint32_t (&r)[4]) {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0, %1, %2, %3}, [%4];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
@@ -166,6 +179,38 @@ __device__ __forceinline__ void tmem_ld4(uint32_t taddr, uint32_t (&r)[4]) {
 // A group sum is at most 128 * 8 * 127 = 130048 in magnitude.
 __device__ __forceinline__ float int_to_float_exact(int d) {
     return __fsub_rn(__int_as_float(0x4B400000 + d), 12582912.0f);
+}
+
+// Two fp32 lanes per instruction (sm_100's packed single-precision arithmetic): each lane is
+// the IEEE round-to-nearest operation of its scalar counterpart, so the chain's bits do not
+// change; the fp32 pipes, which pace the per-32 form, see half the instructions.
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ uint64_t sub2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+// float(d0), float(d1) as a pair, by the same route as int_to_float_exact
+__device__ __forceinline__ uint64_t ints_to_float2_exact(uint32_t d0, uint32_t d1) {
+    return sub2(pack2(__int_as_float(0x4B400000 + (int)d0), __int_as_float(0x4B400000 + (int)d1)),
+                pack2(12582912.0f, 12582912.0f));
 }
 
 __device__ __noinline__ float gemm_activation(float v, int act) {
@@ -201,12 +246,15 @@ gemm_w4a8_tc_kernel(const GemmArgs a) {
     constexpr int kRawSlots = Smem<RP, NB>::kRawSlots;
     constexpr int kSplit = A32 ? 4 : 2;  // column ranges the epilogue warpgroups split
     constexpr int CH = RP / kSplit;      // accumulator columns per epilogue thread
-    constexpr int kBlk = A32 ? 4 : 1;    // accumulators per group and token block
-    // TMEM holds kAcc group accumulators of kBlk*NB*RP columns each (512 columns in all), so
-    // the MMAs run up to kAcc-1 groups ahead of the fp32 chain
-    constexpr int kAccCols = kBlk * NB * RP;
-    constexpr int kAcc = 512 / kAccCols > 6 ? 6 : 512 / kAccCols;
+    // The unit that the MMA warp hands to the epilogue: a group's accumulator (NB token
+    // blocks of RP columns), or (A32) half a group -- two 32-k blocks with an accumulator of
+    // RP columns each -- so that the MMAs of a group's second half, and of the next groups,
+    // run while the chain still works on the first.  TMEM holds kAcc units (512 columns).
+    constexpr int kAccCols = A32 ? 2 * RP : NB * RP;
+    constexpr int kAccMax = A32 ? 8 : 6;
+    constexpr int kAcc = 512 / kAccCols > kAccMax ? kAccMax : 512 / kAccCols;
     static_assert(kAcc >= 2, "no accumulator to run ahead into");
+    static_assert(!A32 || CH == 8 || CH == 12 || CH == 16, "epilogue load widths");
     // With one token block and the per-128 rule only two of the four epilogue warpgroups
     // have accumulator rows; the other two unpack weights instead (the unpack stage bounds
     // the pipeline there).
@@ -319,29 +367,58 @@ gemm_w4a8_tc_kernel(const GemmArgs a) {
             for (int g = 0; g < G; ++g) {
                 const int sa = g % kAStages, ra = g / kAStages;
                 const int sb = g % kBStages, rb = g / kBStages;
-                const int b = g % kAcc, use = g / kAcc;
-                if (!mbar_wait(&b_full[sb], rb & 1) || !mbar_wait(&act_full[sa], ra & 1) ||
-                    (use > 0 && !mbar_wait(&acc_free[b], (use - 1) & 1))) {
+                if (!mbar_wait(&b_full[sb], rb & 1) || !mbar_wait(&act_full[sa], ra & 1)) {
                     fail();
                     break;
                 }
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t b_addr = smem_u32(smem + S::kBOff + sb * S::kBStage);
-                for (int mb = 0; mb < n_blocks; ++mb) {
-                    const uint32_t a_addr =
-                        smem_u32(smem + S::kActOff + sa * S::kActStage + mb * 128 * 128);
-                    const uint32_t d = tmem_base + (uint32_t)(b * kAccCols + mb * kBlk * RP);
+                bool ok = true;
+                if constexpr (A32) {
+                    const uint32_t a_addr = smem_u32(smem + S::kActOff + sa * S::kActStage);
 #pragma unroll
-                    for (int j = 0; j < 4; ++j)  // four K = 32 steps inside the swizzle row:
-                        // summed into one accumulator, or (A32) one accumulator per step
-                        umma_i8(d + (A32 ? j * RP : 0), umma_desc_k_sw128(a_addr + j * 32),
-                                umma_desc_k_sw128(b_addr + j * 32), idesc,
-                                (!A32 && j > 0) ? 1u : 0u);
+                    for (int h = 0; h < 2; ++h) {  // blocks 2h and 2h + 1: one unit
+                        const int u = 2 * g + h, b = u % kAcc, use = u / kAcc;
+                        if (use > 0 && !mbar_wait(&acc_free[b], (use - 1) & 1)) {
+                            ok = false;
+                            break;
+                        }
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+                        for (int jj = 0; jj < 2; ++jj) {  // a K = 32 step = a 32-k block
+                            const int j = 2 * h + jj;
+                            umma_i8(tmem_base + (uint32_t)(b * kAccCols + jj * RP),
+                                    umma_desc_k_sw128(a_addr + j * 32),
+                                    umma_desc_k_sw128(b_addr + j * 32), idesc, 0u);
+                        }
+                        umma_commit(&acc_full[b]);  // the two blocks' sums are complete
+                    }
+                } else {
+                    const int b = g % kAcc, use = g / kAcc;
+                    if (use > 0 && !mbar_wait(&acc_free[b], (use - 1) & 1))
+                        ok = false;
+                    if (ok) {
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        for (int mb = 0; mb < n_blocks; ++mb) {
+                            const uint32_t a_addr = smem_u32(smem + S::kActOff +
+                                                             sa * S::kActStage + mb * 128 * 128);
+                            const uint32_t d = tmem_base + (uint32_t)(b * kAccCols + mb * RP);
+#pragma unroll
+                            for (int j = 0; j < 4; ++j)  // four K = 32 steps inside the
+                                                         // swizzle row, summed in one accumulator
+                                umma_i8(d, umma_desc_k_sw128(a_addr + j * 32),
+                                        umma_desc_k_sw128(b_addr + j * 32), idesc,
+                                        j > 0 ? 1u : 0u);
+                        }
+                        umma_commit(&acc_full[b]);  // the group's sums are complete
+                    }
+                }
+                if (!ok) {
+                    fail();
+                    break;
                 }
                 // a commit fires when every MMA issued so far has retired
                 umma_commit(&act_free[sa]);  // the activation stage may be refilled
                 umma_commit(&b_free[sb]);    // the unpacked weights may be overwritten
-                umma_commit(&acc_full[b]);   // the group's sums are complete
             }
         }
     } else if (warp < kEpiWarp0 || warp >= kEpiWarp0 + kEpiActive) {
@@ -442,56 +519,68 @@ gemm_w4a8_tc_kernel(const GemmArgs a) {
                                           : make_float4(0.f, 0.f, 0.f, 0.f);
             };
             float4 a0 = load_as(0), a1 = load_as(1);
-            for (int g = 0; g < G; ++g) {
-                const int b = g % kAcc, use = g / kAcc;
+            uint64_t acc2[CH / 2];  // the chain values, columns (2i, 2i + 1) side by side
+#pragma unroll
+            for (int i = 0; i < CH / 2; ++i)
+                acc2[i] = 0ull;
+            bool live = true;
+            for (int g = 0; g < G && live; ++g) {
                 const float asv[4] = {a0.x, a0.y, a0.z, a0.w};
                 a0 = a1;
                 a1 = load_as(g + 2);
-                if (*s_abort || !mbar_wait(&acc_full[b], use & 1)) {
-                    if (lane == 0)
-                        fail();
-                    break;
-                }
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                if (active) {
-                    const uint32_t taddr = tmem_base + ((uint32_t)(lq * 32) << 16) +
-                                           (uint32_t)(b * kAccCols + ch * CH);
-                    // two blocks' columns are requested before one wait
-                    constexpr int kJB = 2;
 #pragma unroll
-                    for (int j0 = 0; j0 < 4; j0 += kJB) {
-                        uint32_t r[kJB][CH];
+                for (int h = 0; h < 2; ++h) {  // the group's two units: blocks 2h, 2h + 1
+                    const int u = 2 * g + h, b = u % kAcc, use = u / kAcc;
+                    if (*s_abort || !mbar_wait(&acc_full[b], use & 1)) {
+                        if (lane == 0)
+                            fail();
+                        live = false;
+                        break;
+                    }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    if (active) {
+                        const uint32_t taddr = tmem_base + ((uint32_t)(lq * 32) << 16) +
+                                               (uint32_t)(b * kAccCols + ch * CH);
+                        uint32_t r[2][CH];
 #pragma unroll
-                        for (int j = 0; j < kJB; ++j)
-#pragma unroll
-                            for (int c0 = 0; c0 < CH; c0 += 4)
-                                tmem_ld4(taddr + (j0 + j) * RP + c0,
-                                         *reinterpret_cast<uint32_t(*)[4]>(&r[j][c0]));
+                        for (int jj = 0; jj < 2; ++jj) {  // the widest loads that tile CH
+                            const uint32_t tb = taddr + jj * RP;
+                            if constexpr (CH == 16) {
+                                tmem_ld16(tb, *reinterpret_cast<uint32_t(*)[16]>(&r[jj][0]));
+                            } else {
+                                tmem_ld8(tb, *reinterpret_cast<uint32_t(*)[8]>(&r[jj][0]));
+                                if constexpr (CH == 12)
+                                    tmem_ld4(tb + 8,
+                                             *reinterpret_cast<uint32_t(*)[4]>(&r[jj][8]));
+                            }
+                        }
                         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
                         for (int c = 0; c < CH; c += 4) {
                             const float4 w4 =
                                 *reinterpret_cast<const float4*>(wsf + g * RP + c);
+                            const uint64_t w_lo = pack2(w4.x, w4.y), w_hi = pack2(w4.z, w4.w);
 #pragma unroll
-                            for (int j = 0; j < kJB; ++j) {  // blocks in ascending order
-                                const float s_b = asv[j0 + j];
-                                acc[c + 0] = __fmaf_rn(int_to_float_exact((int)r[j][c + 0]),
-                                                       __fmul_rn(w4.x, s_b), acc[c + 0]);
-                                acc[c + 1] = __fmaf_rn(int_to_float_exact((int)r[j][c + 1]),
-                                                       __fmul_rn(w4.y, s_b), acc[c + 1]);
-                                acc[c + 2] = __fmaf_rn(int_to_float_exact((int)r[j][c + 2]),
-                                                       __fmul_rn(w4.z, s_b), acc[c + 2]);
-                                acc[c + 3] = __fmaf_rn(int_to_float_exact((int)r[j][c + 3]),
-                                                       __fmul_rn(w4.w, s_b), acc[c + 3]);
+                            for (int jj = 0; jj < 2; ++jj) {  // blocks in ascending order
+                                const float s_b = asv[2 * h + jj];
+                                const uint64_t s2 = pack2(s_b, s_b);
+                                acc2[c / 2] = fma2(ints_to_float2_exact(r[jj][c], r[jj][c + 1]),
+                                                   mul2(w_lo, s2), acc2[c / 2]);
+                                acc2[c / 2 + 1] =
+                                    fma2(ints_to_float2_exact(r[jj][c + 2], r[jj][c + 3]),
+                                         mul2(w_hi, s2), acc2[c / 2 + 1]);
                             }
                         }
                     }
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0)
+                        mbar_arrive(&acc_free[b]);
                 }
-                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                __syncwarp();
-                if (lane == 0)
-                    mbar_arrive(&acc_free[b]);
             }
+#pragma unroll
+            for (int i = 0; i < CH / 2; ++i)
+                unpack2(acc2[i], acc[2 * i], acc[2 * i + 1]);
         } else {
             // the token's activation scales are fetched four groups ahead: a global load takes
             // about as long as a whole group, so a shorter distance would pace the loop
@@ -499,9 +588,18 @@ gemm_w4a8_tc_kernel(const GemmArgs a) {
                 return (has_tok && g < G) ? a.as[(size_t)g * a.m_pad + tok] : 0.f;
             };
             float a0 = load_as(0), a1 = load_as(1), a2 = load_as(2), a3 = load_as(3);
+            // Two token blocks: sixteen warps share the chain and packed arithmetic pays.  One
+            // block: eight warps with twice the columns each, where the register pairs it
+            // needs cost more than the instructions it saves.
+            constexpr bool kPacked = NB == 2;
+            uint64_t acc2[kPacked ? CH / 2 : 1];  // chain values, columns (2i, 2i + 1) paired
+#pragma unroll
+            for (int i = 0; i < (kPacked ? CH / 2 : 1); ++i)
+                acc2[i] = 0ull;
             for (int g = 0; g < G; ++g) {
                 const int b = g % kAcc, use = g / kAcc;
                 const float a_s = a0;
+                const uint64_t as2 = pack2(a0, a0);
                 a0 = a1;
                 a1 = a2;
                 a2 = a3;
@@ -532,14 +630,27 @@ gemm_w4a8_tc_kernel(const GemmArgs a) {
                             if (b0 + c < CH) {
                                 const float4 w4 =
                                     *reinterpret_cast<const float4*>(wsf + g * RP + b0 + c);
-                                acc[b0 + c + 0] = __fmaf_rn(int_to_float_exact((int)r[c + 0]),
-                                                            __fmul_rn(w4.x, a_s), acc[b0 + c + 0]);
-                                acc[b0 + c + 1] = __fmaf_rn(int_to_float_exact((int)r[c + 1]),
-                                                            __fmul_rn(w4.y, a_s), acc[b0 + c + 1]);
-                                acc[b0 + c + 2] = __fmaf_rn(int_to_float_exact((int)r[c + 2]),
-                                                            __fmul_rn(w4.z, a_s), acc[b0 + c + 2]);
-                                acc[b0 + c + 3] = __fmaf_rn(int_to_float_exact((int)r[c + 3]),
-                                                            __fmul_rn(w4.w, a_s), acc[b0 + c + 3]);
+                                if constexpr (kPacked) {
+                                    acc2[(b0 + c) / 2] =
+                                        fma2(ints_to_float2_exact(r[c], r[c + 1]),
+                                             mul2(pack2(w4.x, w4.y), as2), acc2[(b0 + c) / 2]);
+                                    acc2[(b0 + c) / 2 + 1] = fma2(
+                                        ints_to_float2_exact(r[c + 2], r[c + 3]),
+                                        mul2(pack2(w4.z, w4.w), as2), acc2[(b0 + c) / 2 + 1]);
+                                } else {
+                                    acc[b0 + c + 0] =
+                                        __fmaf_rn(int_to_float_exact((int)r[c + 0]),
+                                                  __fmul_rn(w4.x, a_s), acc[b0 + c + 0]);
+                                    acc[b0 + c + 1] =
+                                        __fmaf_rn(int_to_float_exact((int)r[c + 1]),
+                                                  __fmul_rn(w4.y, a_s), acc[b0 + c + 1]);
+                                    acc[b0 + c + 2] =
+                                        __fmaf_rn(int_to_float_exact((int)r[c + 2]),
+                                                  __fmul_rn(w4.z, a_s), acc[b0 + c + 2]);
+                                    acc[b0 + c + 3] =
+                                        __fmaf_rn(int_to_float_exact((int)r[c + 3]),
+                                                  __fmul_rn(w4.w, a_s), acc[b0 + c + 3]);
+                                }
                             }
                         }
                     }
@@ -548,6 +659,11 @@ gemm_w4a8_tc_kernel(const GemmArgs a) {
                 __syncwarp();
                 if (lane == 0)
                     mbar_arrive(&acc_free[b]);
+            }
+            if constexpr (kPacked) {
+#pragma unroll
+                for (int i = 0; i < CH / 2; ++i)
+                    unpack2(acc2[i], acc[2 * i], acc[2 * i + 1]);
             }
         }
         // Output: a thread holds one token's CH columns, which lie CH*4 bytes apart from the

@@ -213,3 +213,44 @@ def test_fused_qkv_step_equals_the_separate_operators(ctx, tokens, past, heads, 
         assert kc2.cpu().numpy().tobytes() == kc1.cpu().numpy().tobytes()
         assert vc2.cpu().numpy().tobytes() == vc1.cpu().numpy().tobytes()
         assert out2.cpu().numpy().tobytes() == out1.cpu().numpy().tobytes()
+
+
+@pytest.mark.parametrize("tokens,past,heads,kv_heads,dim", [(33, 0, 8, 2, 128),
+                                                            (256, 0, 32, 8, 128),
+                                                            (40, 100, 4, 4, 64),
+                                                            (17, 5, 6, 2, 256),
+                                                            (64, 300, 32, 4, 128)])
+def test_tile_attention_equals_the_row_kernel(ctx, tokens, past, heads, kv_heads, dim):
+    """A run of tokens takes the tile kernel (a block per kv head and tile of query tokens);
+    it must leave the same bits as the one-row kernel, and agree with the oracle."""
+    import os
+    import torch
+    os.environ["B2W4_ATTN"] = "row"
+    try:
+        ctx_row = pkg.capi.Context(0)
+    finally:
+        del os.environ["B2W4_ATTN"]
+    capacity = past + tokens + 3
+    rng = np.random.default_rng(tokens + dim)
+    q = rng.normal(0, 1, (tokens, heads, dim)).astype(np.float32)
+    k_all = rng.normal(0, 1, (past + tokens, kv_heads, dim)).astype(np.float32)
+    v_all = rng.normal(0, 1, (past + tokens, kv_heads, dim)).astype(np.float32)
+    kc = np.zeros((kv_heads, capacity, dim), dtype=np.float32)
+    vc = np.zeros((kv_heads, capacity, dim), dtype=np.float32)
+    kc[:, :past + tokens] = k_all.transpose(1, 0, 2)
+    vc[:, :past + tokens] = v_all.transpose(1, 0, 2)
+    kcd, vcd, qd = _dev(kc), _dev(vc), _dev(q)
+    scale = dim ** -0.5
+    outs = []
+    for c, past_dev in ((ctx_row, None), (ctx, None),
+                        (ctx, torch.full((1,), past, dtype=torch.int32, device="cuda"))):
+        out = torch.zeros((tokens, heads, dim), dtype=torch.float32, device="cuda")
+        c.attention(qd, None, None, kcd, vcd, out, tokens, heads, kv_heads, dim,
+                    past if past_dev is None else 0, capacity, scale, past_dev)
+        c.sync()
+        outs.append(out.cpu().numpy())
+    ctx_row.close()
+    assert outs[1].tobytes() == outs[0].tobytes()
+    assert outs[2].tobytes() == outs[0].tobytes()
+    want = ol.causal_attention(q, k_all, v_all, heads, kv_heads, past, scale)
+    assert rel_l2(outs[1], want) < 1e-5
