@@ -569,23 +569,21 @@ def json_only_stdout():
     return os.fdopen(keep, "w")
 
 
-def dense_decoder(torch, pkg, ctx, args):
-    """Benchmark configuration 3 end to end on one GPU: the Qwen3-4B-shaped dense decoder (36
-    layers, hidden 2560, 32 q / 8 kv heads of 128, SwiGLU intermediate 9728, vocabulary
-    151936; synthetic W4G128 weights), a 256-token random prompt and 64 greedy steps, every
-    operator a libb200w4 kernel (palm-infra_b200/decoder.py).  The reference's protocol
-    (examples/cli_common.cpp:418-436): prefill_tps = 256 / prefill seconds, decode_tps = 64 /
-    decode seconds; wall clock around synchronised regions, the greedy token read back every
-    step as a sampler would."""
+def decoder_leg(torch, pkg, ctx, cfg, config_text, rules):
+    """A whole decoder end to end on one GPU (palm-infra_b200/decoder.py: every operator a
+    libb200w4 kernel; synthetic W4G128 weights), a 256-token random prompt and 64 greedy steps.
+    The reference's protocol (examples/cli_common.cpp:418-436): prefill_tps = 256 / prefill
+    seconds, decode_tps = 64 / decode seconds; wall clock around synchronised regions, the
+    greedy token read back every step as a sampler would."""
     dec = pkg.decoder
-    cfg = dec.DecoderConfig.qwen3_4b()
-    weights = dec.synthetic_weights(cfg, seed=SEED_W, distinct_layers=1)
     prompt = np.random.default_rng(11).integers(0, cfg.vocab, 256).tolist()
-    out = {"config": "36 layers, hidden 2560, 32/8 heads x 128, intermediate 9728, vocab 151936",
+    out = {"config": config_text,
            "decode_launch": "one captured CUDA graph per step (position and tokens on the "
                             "device), the token read back by the host after every step"}
-    for name, rule in (("reference_rule", pkg.capi.ACT_G32), ("per128_prefill", pkg.capi.ACT_G128)):
+    for name, rule in rules:
+        weights = dec.synthetic_weights(cfg, seed=SEED_W, distinct_layers=1, lazy=True)
         model = dec.DenseDecoder(ctx, cfg, weights, capacity=384, multi_row_rule=rule)
+        del weights
         model.generate(prompt, 3)  # warm every kernel and buffer
         model.generate(prompt, 3, replay=True)
         times = []
@@ -619,9 +617,24 @@ def dense_decoder(torch, pkg, ctx, args):
                      "decode_ms_per_token": dc * 1e3 / 64,
                      "decode_tps_no_host_read": 64 / dq, "decode_tps_eager_launches": 64 / de,
                      "multi_row_rule": "per 32 values (the reference's)" if rule == 32 else
-                                       "per 128 values (tensor-core path)"}
+                                       "per 128 values"}
         model.free()
     return out
+
+
+def dense_decoder(torch, pkg, ctx, args):
+    """Benchmark configuration 3: the Qwen3-4B-shaped dense decoder."""
+    return decoder_leg(torch, pkg, ctx, pkg.decoder.DecoderConfig.qwen3_4b(),
+                       "36 layers, hidden 2560, 32/8 heads x 128, intermediate 9728, vocab 151936",
+                       (("reference_rule", pkg.capi.ACT_G32), ("per128_prefill", pkg.capi.ACT_G128)))
+
+
+def moe_decoder(torch, pkg, ctx, args):
+    """Benchmark configuration 4: the Qwen3-30B-A3B-shaped decoder (16 GB of W4G128 weights;
+    --moe-decoder, not part of the default run)."""
+    return decoder_leg(torch, pkg, ctx, pkg.decoder.DecoderConfig.qwen3_30b_a3b(),
+                       "48 layers, hidden 2048, 32/4 heads x 128, 128 experts x 768 top-8, "
+                       "vocab 151936", (("reference_rule", pkg.capi.ACT_G32),))
 
 
 def run_ours(args):
@@ -1080,6 +1093,8 @@ def run_ours(args):
         line["gpu_reference"] = gpu_reference(torch, pkg, args, value,
                                               sweep["m256"]["us_per_matmul"])
         line["dense_decoder_4b"] = dense_decoder(torch, pkg, ctx, args)
+        if args.moe_decoder:
+            line["moe_decoder_30b_a3b"] = moe_decoder(torch, pkg, ctx, args)
 
         # ---- CPU baseline: the reference's own kernel on this box's host cores ----------
         probe, kind, cores, isa = cpu_gemv_seconds(pkg, 1, 16, 8)
@@ -1134,6 +1149,9 @@ def main():
     ap.add_argument("--per-launch", action="store_true",
                     help="time the one-launch-per-GEMV kernel as the headline instead of the "
                          "persistent list kernel (profiling)")
+    ap.add_argument("--moe-decoder", action="store_true",
+                    help="also run the 30B-A3B-shaped mixture-of-experts decoder end to end "
+                         "(uploads 16 GB of synthetic weights; single GPU)")
     ap.add_argument("--headline-only", action="store_true",
                     help="skip the e2e, sweep and CPU-baseline legs (profiling)")
     args = ap.parse_args()

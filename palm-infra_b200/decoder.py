@@ -1,8 +1,10 @@
-"""A Qwen3-shaped dense decoder driven through the C ABI: embedding rows, per layer RMSNorm ->
+"""A Qwen3-shaped decoder (dense, or with a routed mixture of experts as the feed-forward
+block) driven through the C ABI: embedding rows, per layer RMSNorm ->
 fused qkv matmul -> per-head Q/K RMSNorm -> rotary embedding -> KV append + causal attention ->
-o matmul -> residual add + RMSNorm -> gate_up matmul -> SwiGLU -> down matmul -> residual add
-(+ next RMSNorm), final norm, lm_head with the greedy token picked on the device.  The layer
-structure is the reference's graph builder's (models/qwen3.py:171-345); every operator is a
+o matmul -> residual add + RMSNorm -> gate_up matmul -> SwiGLU -> down matmul (or the MOE
+operator in their place) -> residual add (+ next RMSNorm), final norm, lm_head with the greedy
+token picked on the device.  The layer structure is the reference's graph builder's
+(models/qwen3.py:171-345; the mixture-of-experts block: models/qwen3_moe.py); every operator is a
 libb200w4 kernel, nothing runs on the host between the first embedding row and the token.
 
 This is the host-side mirror of what the reference's engine does per step for benchmark
@@ -19,10 +21,13 @@ from . import capi, synth
 
 class DecoderConfig:
     def __init__(self, layers, hidden, heads, kv_heads, head_dim, intermediate, vocab,
-                 rope_theta=1e6, eps=1e-6):
+                 rope_theta=1e6, eps=1e-6, experts=0, top_k=0):
+        """experts > 0: every layer's feed-forward block is the routed mixture of experts
+        (softmax top-k router, `experts` SwiGLU experts of width `intermediate`)."""
         self.layers, self.hidden, self.heads, self.kv_heads = layers, hidden, heads, kv_heads
         self.head_dim, self.intermediate, self.vocab = head_dim, intermediate, vocab
         self.rope_theta, self.eps = rope_theta, eps
+        self.experts, self.top_k = experts, top_k
         self.q_dim, self.kv_dim = heads * head_dim, kv_heads * head_dim
 
     @staticmethod
@@ -30,6 +35,12 @@ class DecoderConfig:
         """Benchmark configuration 3: 36 layers, hidden 2560, 32 q / 8 kv heads of 128,
         SwiGLU intermediate 9728, vocabulary 151936, rope theta 1e6."""
         return DecoderConfig(36, 2560, 32, 8, 128, 9728, 151936)
+
+    @staticmethod
+    def qwen3_30b_a3b():
+        """Benchmark configuration 4: 48 layers, hidden 2048, 32 q / 4 kv heads of 128, 128
+        experts of width 768 with 8 routed per token, vocabulary 151936."""
+        return DecoderConfig(48, 2048, 32, 4, 128, 768, 151936, experts=128, top_k=8)
 
 
 def rope_tables(positions, rope_dim, theta):
@@ -44,27 +55,37 @@ def rope_tables(positions, rope_dim, theta):
     return np.cos(ang).astype(np.float32), np.sin(ang).astype(np.float32)
 
 
-def synthetic_weights(cfg, seed=20261125, distinct_layers=None):
-    """Host-side synthetic model: BG128 blocks for every matmul weight, fp16 embedding rows,
-    fp32 norm weights.  distinct_layers < cfg.layers generates that many layers and gives the
-    others the same blocks rotated by whole blocks (a different weight per layer at a fraction
-    of the generation time)."""
+def synthetic_weights(cfg, seed=20261125, distinct_layers=None, lazy=False):
+    """Host-side synthetic model: BG128 blocks for every matmul weight, fp16 embedding rows and
+    router rows, fp32 norm weights.  distinct_layers < cfg.layers generates that many layers
+    and gives the others the same blocks rotated by whole blocks (a different weight per layer
+    at a fraction of the generation time).  lazy: "layers" is a generator, so that a model of
+    tens of gigabytes is uploaded layer by layer without ever being whole in host memory."""
     d = distinct_layers or cfg.layers
+    # mixture of experts: the aggregates hold expert e's rows at [e * rows, (e + 1) * rows)
+    per = max(1, cfg.experts)
     shapes = {"qkv": (cfg.q_dim + 2 * cfg.kv_dim, cfg.hidden), "o": (cfg.hidden, cfg.q_dim),
-              "gate_up": (2 * cfg.intermediate, cfg.hidden), "down": (cfg.hidden, cfg.intermediate)}
-    base = [{k: synth.bg128_weight(seed, 1000 + 10 * l + j, n, kk)
-             for j, (k, (n, kk)) in enumerate(shapes.items())} for l in range(d)]
-    layers = []
-    for l in range(cfg.layers):
+              "gate_up": (per * 2 * cfg.intermediate, cfg.hidden),
+              "down": (per * cfg.hidden, cfg.intermediate)}
+    base = {}
+
+    def layer(l):
+        if l % d not in base:
+            base[l % d] = {k: synth.bg128_weight(seed, 1000 + 10 * (l % d) + j, n, kk)
+                           for j, (k, (n, kk)) in enumerate(shapes.items())}
         src = base[l % d]
         w = {k: (v if l < d else np.roll(v, 544 * (l // d))) for k, v in src.items()}
         rng = np.random.default_rng(seed + 7 * l)
         for name, n in (("ln1", cfg.hidden), ("ln2", cfg.hidden), ("q_norm", cfg.head_dim),
                         ("k_norm", cfg.head_dim)):
             w[name] = (1.0 + 0.05 * rng.standard_normal(n)).astype(np.float32)
-        layers.append(w)
+        if cfg.experts:
+            w["router"] = synth.router_weight(seed, 2000 + l, cfg.experts, cfg.hidden)
+        return w
+
+    layers = (layer(l) for l in range(cfg.layers))
     rng = np.random.default_rng(seed + 99)
-    return {"shapes": shapes, "layers": layers,
+    return {"shapes": shapes, "layers": layers if lazy else list(layers),
             "final_norm": (1.0 + 0.05 * rng.standard_normal(cfg.hidden)).astype(np.float32),
             "embed": _embedding(seed, cfg),
             "lm_head": synth.bg128_weight(seed, 901, cfg.vocab, cfg.hidden)}
@@ -95,6 +116,7 @@ class DenseDecoder:
             self.layers.append({
                 **{k: ctx.upload_weight(w[k], *sh[k]) for k in sh},
                 **{k: dev(w[k]) for k in ("ln1", "ln2", "q_norm", "k_norm")},
+                **({"router": dev(w["router"].view(np.int16))} if cfg.experts else {}),
                 "k_cache": torch.zeros((cfg.kv_heads, capacity, cfg.head_dim), device="cuda"),
                 "v_cache": torch.zeros((cfg.kv_heads, capacity, cfg.head_dim), device="cuda")})
         self.final_norm = dev(weights["final_norm"])
@@ -132,7 +154,9 @@ class DenseDecoder:
         qkv = self._b("qkv", T, cfg.q_dim + 2 * cfg.kv_dim)
         q, k, v = self._b("q", T, cfg.q_dim), self._b("k", T, cfg.kv_dim), self._b("v", T, cfg.kv_dim)
         attn, o = self._b("attn", T, cfg.q_dim), self._b("o", T, H)
-        gu, act = self._b("gu", T, 2 * cfg.intermediate), self._b("act", T, cfg.intermediate)
+        gu = act = None
+        if not cfg.experts:
+            gu, act = self._b("gu", T, 2 * cfg.intermediate), self._b("act", T, cfg.intermediate)
         dn = self._b("dn", T, H)
         c.embed_rows(self.embed, ids_dev, x)
         c.rms_norm(x, self.layers[0]["ln1"], cfg.eps, h)
@@ -157,9 +181,13 @@ class DenseDecoder:
                             cfg.kv_heads, D, self.past, self.capacity, D ** -0.5, pos_dev)
             c.matmul(L["o"], attn, o, rule=rule)
             c.add_rms_norm(x, o, L["ln2"], cfg.eps, h)       # x += o; h = norm(x)
-            c.matmul(L["gate_up"], h, gu, rule=rule)
-            c.swiglu(gu, act)
-            c.matmul(L["down"], act, dn, rule=rule)
+            if cfg.experts:  # router, selection, expert matmuls and combine: one operator
+                c.moe_forward(h, L["router"], cfg.top_k, cfg.intermediate, L["gate_up"],
+                              L["down"], dn)
+            else:
+                c.matmul(L["gate_up"], h, gu, rule=rule)
+                c.swiglu(gu, act)
+                c.matmul(L["down"], act, dn, rule=rule)
             nxt = self.layers[li + 1]["ln1"] if li + 1 < len(self.layers) else self.final_norm
             c.add_rms_norm(x, dn, nxt, cfg.eps, h)           # x += dn; h = next norm(x)
         if on_device_position:  # history[past] = the token that went in; past += 1

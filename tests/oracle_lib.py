@@ -370,8 +370,9 @@ def causal_attention(q, k_all, v_all, heads, kv_heads, past, scale, which=None):
 
 
 def dense_decoder_tokens(cfg, weights, prompt, steps, multi_row_rule=ACT_G32):
-    """Greedy tokens of the Qwen3-shaped dense decoder (the layer structure of the reference's
-    graph builder, models/qwen3.py:171-345) computed entirely from the oracle's pieces on the
+    """Greedy tokens of the Qwen3-shaped decoder, dense or with the routed mixture of experts
+    as its feed-forward block (the layer structure of the reference's graph builders,
+    models/qwen3.py:171-345, models/qwen3_moe.py), computed entirely from the oracle's pieces on the
     CPU: the W4A8 matmul (per 128 values for one row, `multi_row_rule` for several), RMSNorm,
     per-head Q/K norm, rotary embedding with host-computed tables, causal attention over all
     keys so far, SwiGLU, residual adds.  Returns (tokens, margins): margin = top-1 minus top-2
@@ -405,8 +406,13 @@ def dense_decoder_tokens(cfg, weights, prompt, steps, multi_row_rule=ACT_G32):
                                     D ** -0.5).reshape(T, cfg.q_dim)
             o = matmul_w4(L["o"], *sh["o"], attn, rule=rule)
             x, h = add_rms_norm(x, o, L["ln2"], cfg.eps)
-            act = swiglu(matmul_w4(L["gate_up"], *sh["gate_up"], h, rule=rule))
-            dn = matmul_w4(L["down"], *sh["down"], act, rule=rule)
+            if cfg.experts:  # the MOE operator under the reference's rule: an expert that
+                # holds several rows quantises per 32 values, a lone row per 128
+                dn = moe_forward(h, L["router"], cfg.top_k, cfg.intermediate, L["gate_up"],
+                                 L["down"], rule=ACT_G32)[0]
+            else:
+                act = swiglu(matmul_w4(L["gate_up"], *sh["gate_up"], h, rule=rule))
+                dn = matmul_w4(L["down"], *sh["down"], act, rule=rule)
             nxt = weights["layers"][li + 1]["ln1"] if li + 1 < cfg.layers else weights["final_norm"]
             x, h = add_rms_norm(x, dn, nxt, cfg.eps)
         past += T
