@@ -637,6 +637,14 @@ def moe_decoder(torch, pkg, ctx, args):
                        "vocab 151936", (("reference_rule", pkg.capi.ACT_G32),))
 
 
+def moe_decoder_235b(torch, pkg, ctx, args):
+    """Benchmark configuration 5: the Qwen3-235B-A22B-shaped decoder on ONE GPU (121 GB of
+    W4G128 weights in 180 GB of HBM; --moe-decoder-235b, minutes of weight generation)."""
+    return decoder_leg(torch, pkg, ctx, pkg.decoder.DecoderConfig.qwen3_235b_a22b(),
+                       "94 layers, hidden 4096, 64/4 heads x 128, 128 experts x 1536 top-8, "
+                       "vocab 151936", (("reference_rule", pkg.capi.ACT_G32),))
+
+
 def run_ours(args):
     out = json_only_stdout()
     import torch
@@ -900,9 +908,9 @@ def run_ours(args):
         nccl_ms = None
     else:
         l0 = ctx.launches
-        make_step(args.rows, graph=False)()
+        make_step(args.rows, rule=args.act_rule, graph=False)()
         launches_per_step = ctx.launches - l0
-        step = make_step(args.rows)
+        step = make_step(args.rows, rule=args.act_rule)
         with ClockSampler(local) as clocks:
             ms = time_steps(torch, step, args.steps, args.warmup, barrier)
         ms = max_over_ranks(ms)
@@ -1095,6 +1103,8 @@ def run_ours(args):
         line["dense_decoder_4b"] = dense_decoder(torch, pkg, ctx, args)
         if args.moe_decoder:
             line["moe_decoder_30b_a3b"] = moe_decoder(torch, pkg, ctx, args)
+        if args.moe_decoder_235b:
+            line["moe_decoder_235b_a22b"] = moe_decoder_235b(torch, pkg, ctx, args)
 
         # ---- CPU baseline: the reference's own kernel on this box's host cores ----------
         probe, kind, cores, isa = cpu_gemv_seconds(pkg, 1, 16, 8)
@@ -1144,6 +1154,9 @@ def main():
     ap.add_argument("--rows", type=int, default=1,
                     help="activation rows of the timed matmul (1 = the headline GEMV; other "
                          "values are for profiling the batched kernels)")
+    ap.add_argument("--act-rule", type=int, default=128, choices=[128, 32],
+                    help="activation rule of the --rows matmul (32 = the reference's rule for "
+                         "several rows; profiling)")
     ap.add_argument("--moe-only", action="store_true",
                     help="run only the MoE layer leg of the sweep (single GPU)")
     ap.add_argument("--per-launch", action="store_true",
@@ -1152,6 +1165,9 @@ def main():
     ap.add_argument("--moe-decoder", action="store_true",
                     help="also run the 30B-A3B-shaped mixture-of-experts decoder end to end "
                          "(uploads 16 GB of synthetic weights; single GPU)")
+    ap.add_argument("--moe-decoder-235b", action="store_true",
+                    help="also run the 235B-A22B-shaped decoder end to end on one GPU (121 GB "
+                         "of synthetic weights, several minutes)")
     ap.add_argument("--headline-only", action="store_true",
                     help="skip the e2e, sweep and CPU-baseline legs (profiling)")
     args = ap.parse_args()

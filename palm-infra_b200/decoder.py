@@ -42,6 +42,13 @@ class DecoderConfig:
         experts of width 768 with 8 routed per token, vocabulary 151936."""
         return DecoderConfig(48, 2048, 32, 4, 128, 768, 151936, experts=128, top_k=8)
 
+    @staticmethod
+    def qwen3_235b_a22b():
+        """Benchmark configuration 5: 94 layers, hidden 4096, 64 q / 4 kv heads of 128, 128
+        experts of width 1536 with 8 routed per token, vocabulary 151936: 121 GB of W4G128
+        weights, which one GPU's 180 GB holds."""
+        return DecoderConfig(94, 4096, 64, 4, 128, 1536, 151936, experts=128, top_k=8)
+
 
 def rope_tables(positions, rope_dim, theta):
     """cos / sin [len(positions), rope_dim // 2] as the reference fills them on the host
