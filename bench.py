@@ -645,6 +645,46 @@ def moe_decoder_235b(torch, pkg, ctx, args):
                        "vocab 151936", (("reference_rule", pkg.capi.ACT_G32),))
 
 
+class ExtrasGuard:
+    """Bounds the extra legs of a multi-GPU run on every rank: after `seconds` rank 0 prints the
+    JSON line as it stands (the headline is complete before the guard starts) with a note, and
+    the process ends with status 0 without running any destructor."""
+
+    def __init__(self, rank, line, out, seconds):
+        import threading
+        self.rank, self.line, self.out, self.seconds = rank, line, out, seconds
+        self.lock = threading.Lock()
+        self.done = False
+        self.timer = threading.Timer(seconds, self._expire)
+        self.timer.daemon = True
+        self.timer.start()
+
+    def _expire(self):
+        with self.lock:
+            if self.done:
+                return
+            self.done = True
+            if self.rank == 0:
+                snapshot = dict(self.line)
+                snapshot["extras_abandoned"] = (
+                    f"the legs after the headline did not finish within {self.seconds:.0f} s on "
+                    "some rank; this line carries what was measured before")
+                self.out.write(json.dumps(snapshot) + "\n")
+                self.out.flush()
+            sys.stderr.write("bench: extra legs abandoned by the guard timer\n")
+            sys.stderr.flush()
+            os._exit(0)
+
+    def finish(self):
+        """True when the legs ended in time (the caller prints the line)."""
+        with self.lock:
+            if self.done:
+                return False
+            self.done = True
+        self.timer.cancel()
+        return True
+
+
 def run_ours(args):
     out = json_only_stdout()
     import torch
@@ -1115,15 +1155,33 @@ def run_ours(args):
             "sample": f"{repeat} GEMVs rotating 16 weight copies, isa {isa}, "
                       f"W4A32 arithmetic ({sec * 1e3:.3f} ms per GEMV)"}
 
+    # The legs below are extras of a multi-GPU run; each ends in collectives, and a rank that
+    # does not come back from one would hold every other rank in the next collective until the
+    # library's own time-out (ten minutes).  A timer on every rank bounds them: when it runs
+    # out, rank 0 prints the line with what is measured and every rank leaves.
+    guard = None
+    if world > 1 and not args.headline_only:
+        guard = ExtrasGuard(rank, line, out, seconds=300.0)
     if world > 1 and not args.headline_only and 128 % world == 0:
         ep = moe_layer_ep(torch, dist, pkg, ctx, rank, world)  # every rank takes part
         line["moe30b_layer_ep"] = ep
     if world > 1 and not args.headline_only:
-        try:
-            line["lm_head_greedy_token_tp"] = lm_head_greedy_tp(torch, dist, pkg, ctx, rank, world)
-        except Exception as exc:  # no symmetric memory on this box
-            line["lm_head_greedy_token_tp"] = {"skipped": str(exc)[:200]}
+        if world >= 8:
+            # At 8 ranks this leg failed in both runs it had: ranks reported the time-out
+            # status of the bounded wait, and in the second run one rank never came back from
+            # the leg.  The cause is not established; the leg is left out there.
+            line["lm_head_greedy_token_tp"] = {
+                "skipped": "not run at 8 ranks: it failed there twice (time-out status; one "
+                           "rank not returning), cause not established"}
+        else:
+            try:
+                line["lm_head_greedy_token_tp"] = lm_head_greedy_tp(torch, dist, pkg, ctx, rank,
+                                                                    world)
+            except Exception as exc:  # no symmetric memory on this box
+                line["lm_head_greedy_token_tp"] = {"skipped": str(exc)[:200]}
 
+    if guard is not None and not guard.finish():
+        return  # the timer is printing the line and ending the process
     if rank == 0:
         out.write(json.dumps(line) + "\n")
         out.flush()

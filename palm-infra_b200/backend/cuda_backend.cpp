@@ -3,9 +3,11 @@
 // reference tree; the engine constructs the backend by that name, engine/model_loader.cpp:
 // 1085, and the reference's tests drive it directly).
 //
-// What runs on the GPU here is the W4G128 path and nothing else:
+// What runs on the GPU here is the W4G128 path and the operators around it in a decoder layer:
 //   OpType::MATMUL with an INT4 BG128 weight   -> b2w4_matmul / b2w4_matmul_host
 //   OpType::MOE, Qwen3-MoE configuration       -> b2w4_moe_forward
+//   OpType::RMS_NORM, ADD_RMS_NORM, SWIGLU, ADD, MUL on resident fp32 rows
+//                                              -> b2w4_rms_norm ... b2w4_elementwise
 //   lm_head GEMV                               -> b2w4_matmul_host / b2w4_matmul
 // Storage (device pool, persistent tensors with host mirrors, boundary uploads, transfers)
 // and the zero-copy view ops are implemented natively because the executor needs them to
@@ -47,6 +49,34 @@ T* device_ptr(const Tensor& t) {
     if (!t.device_data)
         return nullptr;
     return reinterpret_cast<T*>(static_cast<uint8_t*>(t.device_data) + t.device_offset);
+}
+
+// An fp32 tensor read as rows that sit on the device: `width` adjacent values (dimension 0),
+// rows `ld` floats apart.  Two shapes qualify: a matrix [width, rows] with any row stride, and
+// a densely packed tensor of more dimensions, whose outer dimensions flatten into rows.
+struct DeviceRows {
+    float* p = nullptr;
+    int width = 0, rows = 0, ld = 0;
+};
+bool rows_on_device(const Tensor* t, DeviceRows* r) {
+    if (!t || t->prec != Precision::FP32 || t->shape[0] <= 0 ||
+        t->stride[0] != static_cast<int64_t>(sizeof(float)))
+        return false;
+    r->p = device_ptr<float>(*t);
+    r->width = static_cast<int>(t->shape[0]);
+    if (!r->p)
+        return false;
+    if (t->shape[2] == 1 && t->shape[3] == 1) {
+        r->rows = static_cast<int>(t->shape[1]);
+        r->ld = r->rows > 1 ? static_cast<int>(t->stride[1] / sizeof(float)) : r->width;
+        return r->rows > 0 && r->ld >= r->width;
+    }
+    for (int d = 1; d < 4; ++d)
+        if (t->shape[d] > 1 && t->stride[d] != t->stride[d - 1] * t->shape[d - 1])
+            return false;
+    r->rows = static_cast<int>(t->nelements() / t->shape[0]);
+    r->ld = r->width;
+    return r->rows > 0;
 }
 
 bool is_moe_qwen3(const GraphNode& node, const std::vector<const Tensor*>& in) {
@@ -708,6 +738,43 @@ void CudaBackend::dispatch(const GraphNode& node, const std::vector<const Tensor
                               static_cast<int>(output->stride[1] / sizeof(float)), nullptr,
                               nullptr, nullptr),
                           "b2w4_moe_forward"))
+                native();
+            return;
+        }
+    }
+
+    // ---- the operators between a decoder layer's matmuls, on fp32 rows that are resident ---
+    // (anything else about them -- other precisions, host tensors, broadcasting -- goes to the
+    // bridge below)
+    {
+        DeviceRows a, b, w, o;
+        const float eps = graph_params::get_f32(node.params, 0, 1e-6f);
+        int rc = 1;  // 1: not one of these
+        if (node.op_type == OpType::RMS_NORM && inputs.size() >= 2 && rows_on_device(in0, &a) &&
+            rows_on_device(inputs[1], &w) && rows_on_device(output, &o) &&
+            w.width == a.width && w.rows == 1 && o.width == a.width && o.rows == a.rows)
+            rc = b2w4_rms_norm(impl_->ctx, a.p, a.ld, a.rows, a.width, w.p, eps, o.p, o.ld);
+        else if (node.op_type == OpType::ADD_RMS_NORM && inputs.size() >= 3 &&
+                 rows_on_device(in0, &a) && rows_on_device(inputs[1], &b) &&
+                 rows_on_device(inputs[2], &w) && rows_on_device(output, &o) &&
+                 b.width == a.width && b.rows == a.rows && w.width == a.width && w.rows == 1 &&
+                 o.width == a.width && o.rows == a.rows)
+            rc = b2w4_add_rms_norm(impl_->ctx, a.p, a.ld, b.p, b.ld, a.rows, a.width, w.p, eps,
+                                   o.p, o.ld);
+        else if (node.op_type == OpType::SWIGLU && rows_on_device(in0, &a) &&
+                 rows_on_device(output, &o) && a.width == 2 * o.width && a.rows == o.rows)
+            rc = b2w4_swiglu(impl_->ctx, a.p, a.ld, a.rows, o.width, o.p, o.ld);
+        else if ((node.op_type == OpType::ADD || node.op_type == OpType::MUL) &&
+                 inputs.size() >= 2 && rows_on_device(in0, &a) &&
+                 rows_on_device(inputs[1], &b) && rows_on_device(output, &o) &&
+                 a.ld == a.width && b.ld == b.width && o.ld == o.width &&
+                 b.width == a.width && b.rows == a.rows && o.width == a.width &&
+                 o.rows == a.rows)
+            rc = b2w4_elementwise(impl_->ctx, a.p, b.p, o.p,
+                                  static_cast<size_t>(a.width) * a.rows,
+                                  node.op_type == OpType::MUL);
+        if (rc != 1) {
+            if (impl_->b2(rc, "decoder-layer operator"))
                 native();
             return;
         }
