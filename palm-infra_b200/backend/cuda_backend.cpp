@@ -8,6 +8,7 @@
 //   OpType::MOE, Qwen3-MoE configuration       -> b2w4_moe_forward
 //   OpType::RMS_NORM, ADD_RMS_NORM, SWIGLU, ADD, MUL on resident fp32 rows
 //                                              -> b2w4_rms_norm ... b2w4_elementwise
+//                                                 (with MOLLM_B200_NATIVE_OPS=1; else bridged)
 //   lm_head GEMV                               -> b2w4_matmul_host / b2w4_matmul
 // Storage (device pool, persistent tensors with host mirrors, boundary uploads, transfers)
 // and the zero-copy view ops are implemented natively because the executor needs them to
@@ -168,6 +169,7 @@ struct CudaBackend::Impl {
     size_t lm_out_cap = 0;
     std::unordered_map<uint32_t, uint64_t> native_ops, fallback_ops;
     int multi_row_rule = B2W4_ACT_G32;
+    bool native_layer_ops = false;  // MOLLM_B200_NATIVE_OPS=1
 
     bool cuda(cudaError_t e, const char* what) {
         if (e == cudaSuccess)
@@ -331,6 +333,8 @@ CudaBackend::CudaBackend() : impl_(std::make_unique<Impl>()) {
     const char* rule = std::getenv("MOLLM_B200_MULTI_ROW_RULE");
     if (rule && std::atoi(rule) == 128)
         impl_->multi_row_rule = B2W4_ACT_G128;
+    const char* layer_ops = std::getenv("MOLLM_B200_NATIVE_OPS");
+    impl_->native_layer_ops = layer_ops && std::atoi(layer_ops) == 1;
 }
 
 CudaBackend::~CudaBackend() = default;
@@ -745,8 +749,9 @@ void CudaBackend::dispatch(const GraphNode& node, const std::vector<const Tensor
 
     // ---- the operators between a decoder layer's matmuls, on fp32 rows that are resident ---
     // (anything else about them -- other precisions, host tensors, broadcasting -- goes to the
-    // bridge below)
-    {
+    // bridge below).  Behind MOLLM_B200_NATIVE_OPS=1: this dispatch has been compiled against
+    // the reference's headers but not yet run against the reference's backend test on a GPU.
+    if (impl_->native_layer_ops) {
         DeviceRows a, b, w, o;
         const float eps = graph_params::get_f32(node.params, 0, 1e-6f);
         int rc = 1;  // 1: not one of these
