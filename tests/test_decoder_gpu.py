@@ -15,18 +15,21 @@ pkg = load_package()
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("layers,hidden,heads,kv_heads,head_dim,inter,vocab,prompt_len,steps",
-                         [(2, 256, 4, 2, 64, 512, 1000, 12, 64),   # 64 greedy steps
-                          (3, 512, 8, 2, 128, 1024, 2048, 33, 16),
+# Seeds are chosen on the CPU (the oracle decoder alone) for a comfortable smallest top-1 margin
+# over the run: 5e-2 for the 64-step case.
+@pytest.mark.parametrize("layers,hidden,heads,kv_heads,head_dim,inter,vocab,prompt_len,steps,"
+                         "seed",
+                         [(2, 256, 4, 2, 64, 512, 1000, 12, 64, 11),   # 64 greedy steps
+                          (3, 512, 8, 2, 128, 1024, 2048, 33, 16, 20261128),
                           # benchmark configuration 3's widths (hidden 2560, 32 / 8 heads of 128,
                           # intermediate 9728, vocabulary 151936) at four layers: what the CPU
                           # decoder finishes in about a minute
-                          (4, 2560, 32, 8, 128, 9728, 151936, 8, 6)])
+                          (4, 2560, 32, 8, 128, 9728, 151936, 8, 6, 20261129)])
 def test_greedy_tokens_identical_to_the_cpu_decoder(layers, hidden, heads, kv_heads, head_dim,
-                                                   inter, vocab, prompt_len, steps):
+                                                   inter, vocab, prompt_len, steps, seed):
     dec = pkg.decoder
     cfg = dec.DecoderConfig(layers, hidden, heads, kv_heads, head_dim, inter, vocab)
-    weights = dec.synthetic_weights(cfg, seed=20261125 + layers)
+    weights = dec.synthetic_weights(cfg, seed=seed)
     prompt = np.random.default_rng(11).integers(0, vocab, prompt_len).tolist()
     ol.set_exp_mode(True)
     try:
@@ -46,25 +49,25 @@ def test_greedy_tokens_identical_to_the_cpu_decoder(layers, hidden, heads, kv_he
     assert got == want, (got, want, margins)
     assert replayed == want, (replayed, want)
     assert unfused == want, (unfused, want)
-    assert min(margins) > 1e-4  # identity is not an accident of a near-tie
+    assert min(margins) > 1e-2  # identity is not an accident of a near-tie
 
 
 @pytest.mark.parametrize("layers,hidden,heads,kv_heads,head_dim,inter,vocab,experts,top_k,"
-                         "prompt_len,steps",
-                         [(2, 256, 4, 2, 64, 128, 1000, 8, 2, 12, 64),   # 64 greedy steps
+                         "prompt_len,steps,seed",
+                         [(2, 256, 4, 2, 64, 128, 1000, 8, 2, 12, 64, 4),   # 64 greedy steps
                           # benchmark configuration 4's widths (hidden 2048, 32 / 4 heads of 128,
                           # 128 experts of width 768, 8 per token) at two layers
-                          (2, 2048, 32, 4, 128, 768, 4096, 128, 8, 20, 6)])
+                          (2, 2048, 32, 4, 128, 768, 4096, 128, 8, 20, 6, 77 + 128)])
 def test_mixture_of_experts_decoder_tokens_identical(layers, hidden, heads, kv_heads, head_dim,
                                                     inter, vocab, experts, top_k, prompt_len,
-                                                    steps):
+                                                    steps, seed):
     """The same identity with the MOE operator as the feed-forward block (router, selection,
     expert matmuls under the reference's per-expert activation rule, ordered combine): prompt
     rows give experts several rows each, decode steps one."""
     dec = pkg.decoder
     cfg = dec.DecoderConfig(layers, hidden, heads, kv_heads, head_dim, inter, vocab,
                             experts=experts, top_k=top_k)
-    weights = dec.synthetic_weights(cfg, seed=77 + experts)
+    weights = dec.synthetic_weights(cfg, seed=seed)
     prompt = np.random.default_rng(5).integers(0, vocab, prompt_len).tolist()
     ol.set_exp_mode(True)
     try:
@@ -80,4 +83,4 @@ def test_mixture_of_experts_decoder_tokens_identical(layers, hidden, heads, kv_h
     print(f"tokens {got}\nminimum top-1 margin {min(margins):.3e}")
     assert got == want, (got, want, margins)
     assert replayed == want, (replayed, want)
-    assert min(margins) > 1e-4
+    assert min(margins) > 1e-2
