@@ -19,6 +19,9 @@
 //   kernel_elementwise (SWIGLU)   kernels/elementwise.cpp:529-...
 //   kernel_rope                   kernels/rope.cpp:155-195
 //   sdpa_x86_avx512_head          kernels/attention_x86_avx512.cpp:47-109
+//   LLMEngine::load / prefill / decode / prefill_hidden / run_lmhead_raw
+//                                 engine/engine.h:170-330 (the whole CPU engine on a .mollm
+//                                 package, as tests/test_tiny_cpu_inference.cpp drives it)
 #include "kernels/attention_x86.h"
 #include "kernels/elementwise.h"
 #include "kernels/matmul.h"
@@ -29,6 +32,7 @@
 #include "kernels/moe_routing.h"
 #include "kernels/quant_layouts.h"
 #include "kernels/threading.h"
+#include "engine/engine.h"
 #include "engine/sampler.h"
 
 #include <chrono>
@@ -255,3 +259,46 @@ void ref_sdpa_head(const float* query, const float* key, const float* value, flo
 }
 
 }  // extern "C"
+
+
+// The reference's engine on a .mollm package, CPU device, greedy sampling: the first token
+// after the prompt and steps - 1 more go to tokens_out; last_logits_out (vocab floats, may be
+// null) receives the logits of the prompt's last position.  Returns 0, or a negative code.
+extern "C" int ref_engine_generate(const char* package_path, const int* prompt, int n_prompt,
+                                   int steps, int n_ctx, int threads, int* tokens_out,
+                                   float* last_logits_out, int vocab) {
+    if (!package_path || !prompt || n_prompt <= 0 || steps <= 0 || !tokens_out)
+        return -1;
+    LLMEngine engine;
+    EngineConfig config;
+    config.package_path = package_path;
+    config.device = Device::CPU;
+    config.n_ctx = n_ctx;
+    config.num_threads = threads;
+    config.weight_loading = WeightLoadingMode::RESIDENT;
+    config.sampling.temperature = 0.0f;
+    if (!engine.load(config))
+        return -2;
+    const std::vector<int> ids(prompt, prompt + n_prompt);
+    if (last_logits_out) {
+        Tensor hidden = engine.prefill_hidden(ids);
+        if (!hidden.data)
+            return -3;
+        const std::vector<float> logits = engine.run_lmhead_raw(hidden, n_prompt);
+        if (static_cast<int>(logits.size()) != vocab)
+            return -4;
+        std::memcpy(last_logits_out, logits.data(), sizeof(float) * vocab);
+        engine.reset();
+    }
+    int token = engine.prefill(ids);
+    if (token < 0)
+        return -5;
+    tokens_out[0] = token;
+    for (int i = 1; i < steps; ++i) {
+        token = engine.decode(token);
+        if (token < 0)
+            return -6;
+        tokens_out[i] = token;
+    }
+    return 0;
+}

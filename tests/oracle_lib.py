@@ -369,14 +369,19 @@ def causal_attention(q, k_all, v_all, heads, kv_heads, past, scale, which=None):
     return out
 
 
-def dense_decoder_tokens(cfg, weights, prompt, steps, multi_row_rule=ACT_G32):
+def dense_decoder_tokens(cfg, weights, prompt, steps, multi_row_rule=ACT_G32, every_rule=None,
+                         first_logits=None):
     """Greedy tokens of the Qwen3-shaped decoder, dense or with the routed mixture of experts
     as its feed-forward block (the layer structure of the reference's graph builders,
     models/qwen3.py:171-345, models/qwen3_moe.py), computed entirely from the oracle's pieces on the
     CPU: the W4A8 matmul (per 128 values for one row, `multi_row_rule` for several), RMSNorm,
     per-head Q/K norm, rotary embedding with host-computed tables, causal attention over all
     keys so far, SwiGLU, residual adds.  Returns (tokens, margins): margin = top-1 minus top-2
-    logit of each step, the quantity that says how fragile the token identity is."""
+    logit of each step, the quantity that says how fragile the token identity is.
+    every_rule: one activation rule for every matmul, whatever its row count (ACT_F64 = the
+    exact product of fp32 activations with the dequantised weight, the arithmetic of the
+    reference's x86 build up to summation order).  first_logits: a list that receives the
+    logits of the prompt's last position."""
     from __graft_entry__ import load_package
     dec = load_package().decoder
     sh = weights["shapes"]
@@ -390,6 +395,8 @@ def dense_decoder_tokens(cfg, weights, prompt, steps, multi_row_rule=ACT_G32):
         nonlocal past
         T = len(ids)
         rule = ACT_G128 if T == 1 else multi_row_rule
+        if every_rule is not None:
+            rule = every_rule
         cos, sin = dec.rope_tables(range(past, past + T), D, cfg.rope_theta)
         x = embed[np.asarray(ids)]
         h = rms_norm(x, weights["layers"][0]["ln1"], cfg.eps)
@@ -416,7 +423,10 @@ def dense_decoder_tokens(cfg, weights, prompt, steps, multi_row_rule=ACT_G32):
             nxt = weights["layers"][li + 1]["ln1"] if li + 1 < cfg.layers else weights["final_norm"]
             x, h = add_rms_norm(x, dn, nxt, cfg.eps)
         past += T
-        logits = matmul_w4(weights["lm_head"], cfg.vocab, H, h[T - 1:T])[0]
+        logits = matmul_w4(weights["lm_head"], cfg.vocab, H, h[T - 1:T],
+                           rule=ACT_G128 if every_rule is None else every_rule)[0]
+        if first_logits is not None and not first_logits:
+            first_logits.append(logits.copy())
         top = np.sort(logits)[-2:]
         return argmax_token(logits), float(top[1] - top[0])
 

@@ -1,0 +1,82 @@
+"""The decoder against the REFERENCE'S OWN ENGINE.  tests/golden/tiny_qwen3_w4g128.mollm is a
+two-layer Qwen3 package written by the reference's converter (models/converter.py, W4G128
+through tools/quantize_weight.cpp) and tests/golden/tiny_qwen3_reference.npz holds what the
+reference's CPU engine (LLMEngine::prefill / decode, greedy) answers on it; both come from
+tests/golden/make_decoder_golden.py.
+
+  * the package reader (palm-infra_b200/package.py) finds every weight the decoder needs;
+  * the CPU decoder of the tests, with the exact product of fp32 activations and dequantised
+    weights in place of W4A8 (the arithmetic of the reference's x86 build), reproduces the
+    engine's logits to 1e-5 and all 32 greedy tokens: the decoder's structure -- fused qkv,
+    per-head norms, rotary convention, cache and attention, SwiGLU, residuals, final norm,
+    lm_head -- is the reference's;
+  * with W4A8 (the arithmetic of the GPU path and of the reference's ARM build) the logits sit
+    within the activation-quantisation distance of the engine's and the tokens are the same
+    (the fixture's seed was chosen for margins above that distance);
+  * (gpu) the device decoder gives the engine's tokens too, eager and replayed.
+"""
+import os
+
+import numpy as np
+import pytest
+
+import oracle_lib as ol
+from golden_util import rel_l2
+from __graft_entry__ import load_package
+
+pkg = load_package()
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+@pytest.fixture(scope="module")
+def fixture():
+    package = pkg.package.read_package(os.path.join(GOLDEN, "tiny_qwen3_w4g128.mollm"))
+    cfg, weights = pkg.package.qwen3_decoder_weights(package)
+    ref = np.load(os.path.join(GOLDEN, "tiny_qwen3_reference.npz"))
+    return package, cfg, weights, ref["prompt"].tolist(), ref["tokens"].tolist(), ref["logits"]
+
+
+def test_package_reader_finds_the_decoder(fixture):
+    package, cfg, weights, *_ = fixture
+    assert package.metadata["architecture"] == "qwen3"
+    assert package.metadata["quantization"] == "w4g128"
+    assert (cfg.layers, cfg.hidden, cfg.heads, cfg.kv_heads, cfg.head_dim) == (2, 256, 4, 2, 64)
+    assert cfg.intermediate == 512 and cfg.vocab == 512 and cfg.rope_theta == 1e6
+    assert weights["embed"].shape == (512, 256) and weights["embed"].dtype == np.float16
+    assert weights["lm_head"].size == ol.bg128_bytes(512, 256)
+    for layer in weights["layers"]:
+        for key, (n, k) in weights["shapes"].items():
+            assert layer[key].size == ol.bg128_bytes(n, k)
+    with pytest.raises(pkg.package.PackageError):
+        package.weight("no_such_weight.weights")
+
+
+def test_exact_arithmetic_reproduces_the_reference_engine(fixture):
+    _, cfg, weights, prompt, tokens, logits = fixture
+    first = []
+    got, _ = ol.dense_decoder_tokens(cfg, weights, prompt, len(tokens), every_rule=ol.ACT_F64,
+                                     first_logits=first)
+    assert rel_l2(first[0], logits) < 1e-5
+    assert got == tokens
+
+
+def test_w4a8_tokens_are_the_reference_engines(fixture):
+    _, cfg, weights, prompt, tokens, logits = fixture
+    first = []
+    got, margins = ol.dense_decoder_tokens(cfg, weights, prompt, len(tokens), first_logits=first)
+    assert rel_l2(first[0], logits) < 3e-2  # W4A8 against W4A32: the activation quantisation
+    assert got == tokens
+    assert min(margins) > 1e-2
+
+
+@pytest.mark.gpu
+def test_device_decoder_gives_the_reference_engines_tokens(fixture):
+    _, cfg, weights, prompt, tokens, _ = fixture
+    ctx = pkg.capi.Context(0)
+    model = pkg.decoder.DenseDecoder(ctx, cfg, weights, capacity=len(prompt) + len(tokens) + 8)
+    eager = model.generate(prompt, len(tokens))
+    replayed = model.generate(prompt, len(tokens), replay=True)
+    model.free()
+    ctx.close()
+    assert eager == tokens
+    assert replayed == tokens
