@@ -1,5 +1,6 @@
 """Reader for the reference's single-file model package (`.mollm`), as far as a Qwen3-shaped
-dense decoder with W4G128 weights needs it: the package header and its JSON section
+decoder (dense, or with the routed mixture of experts in every layer) with W4G128 weights
+needs it: the package header and its JSON section
 (written by models/transpile.py:1937 `save_package`, read by engine/package.cpp:216-279), the
 weight files inside the weights region (88-byte header + payload, models/transpile.py:1460-1475;
 INT4 tensors are canonical BG128 blocks with embedded scales, :1778-1830) and the key/value
@@ -112,28 +113,41 @@ def read_package(path):
 
 
 def qwen3_decoder_weights(package):
-    """(DecoderConfig, weights) of a dense Qwen3 package with W4G128 matmul weights.  Names as
-    the reference's converter writes them (models/qwen3.py:171-345, models/transpile.py
-    export_weights): fused qkv and gate_up projections, fp16 embedding rows, fp32 norms."""
+    """(DecoderConfig, weights) of a Qwen3 package with W4G128 matmul weights, dense
+    (architecture "qwen3") or with softmax-routed experts in every layer ("qwen3-moe", no shared
+    expert, no dense head layers).  Names as the reference's converters write them
+    (models/qwen3.py:171-345, models/qwen3_moe.py:337-520): fused qkv and gate_up projections,
+    expert aggregates [E * 2I, H] and [E * H, I] with expert e's rows together, fp16 embedding
+    and router rows, fp32 norms."""
     from .decoder import DecoderConfig
     m = package.metadata
-    if m.get("architecture") != "qwen3":
-        raise PackageError(f"architecture {m.get('architecture')!r}: only dense qwen3 is read")
+    arch = m.get("architecture")
+    if arch not in ("qwen3", "qwen3-moe"):
+        raise PackageError(f"architecture {arch!r}: only qwen3 and qwen3-moe are read")
     layers, hidden = int(m["num_layers"]), int(m["hidden_size"])
     heads, kv_heads, head_dim = int(m["num_heads"]), int(m["num_kv_heads"]), int(m["head_dim"])
     vocab = int(m["vocab_size"])
-    gate_up = package.weight("model_layers_0_mlp_gate_up_proj_weight.weights")
-    inter = gate_up.shape[0] // 2
+    experts = top_k = 0
+    if arch == "qwen3-moe":
+        experts, top_k = int(m["num_experts"]), int(m["num_experts_per_tok"])
+        if int(m.get("first_k_dense_replace", 0)) or int(m.get("n_shared_experts", 0)):
+            raise PackageError("dense head layers and shared experts are not read")
+        inter = int(m["moe_intermediate_size"])
+    else:
+        inter = package.weight("model_layers_0_mlp_gate_up_proj_weight.weights").shape[0] // 2
     theta = float(package.graph_metadata.get("rope_theta", 1e6))
     rope_dim = int(package.graph_metadata.get("rope_dim", head_dim))
     if rope_dim != head_dim:
         raise PackageError(f"rope over {rope_dim} of {head_dim} features is not supported here")
     cfg = DecoderConfig(layers, hidden, heads, kv_heads, head_dim, inter, vocab, rope_theta=theta,
-                        eps=float(package.graph_metadata.get("rms_norm_eps", 1e-6)))
+                        eps=float(package.graph_metadata.get("rms_norm_eps", 1e-6)),
+                        experts=experts, top_k=top_k)
+    per = max(1, experts)
     shapes = {"qkv": (cfg.q_dim + 2 * cfg.kv_dim, hidden), "o": (hidden, cfg.q_dim),
-              "gate_up": (2 * inter, hidden), "down": (hidden, inter)}
+              "gate_up": (per * 2 * inter, hidden), "down": (per * hidden, inter)}
     names = {"qkv": "self_attn_qkv_proj_weight", "o": "self_attn_o_proj_weight",
-             "gate_up": "mlp_gate_up_proj_weight", "down": "mlp_down_proj_weight",
+             "gate_up": "mlp_experts_gate_up_proj" if experts else "mlp_gate_up_proj_weight",
+             "down": "mlp_experts_down_proj" if experts else "mlp_down_proj_weight",
              "ln1": "input_layernorm_weight", "ln2": "post_attention_layernorm_weight",
              "q_norm": "self_attn_q_norm_weight", "k_norm": "self_attn_k_norm_weight"}
     out_layers = []
@@ -147,6 +161,11 @@ def qwen3_decoder_weights(package):
                 w[key] = pw.bg128_blocks()
             else:
                 w[key] = pw.fp32()
+        if experts:
+            router = package.weight(f"model_layers_{l}_mlp_gate_weight.weights").fp16()
+            if router.shape != (experts, hidden):
+                raise PackageError(f"layer {l}: router shape {router.shape}")
+            w["router"] = router
         out_layers.append(w)
     lm_head = package.weight("lm_head.weights")
     if lm_head.shape != (vocab, hidden):

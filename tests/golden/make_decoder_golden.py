@@ -1,15 +1,18 @@
 #!/usr/bin/env python3
-"""Generates the decoder fixture: a tiny Qwen3 model package made by the REFERENCE's own
-converter, and what the REFERENCE's own CPU engine answers on it.
+"""Generates the decoder fixtures: tiny Qwen3 model packages (one dense, one with routed
+experts) made by the REFERENCE's own converter, and what the REFERENCE's own CPU engine answers
+on them.
 
-    python tests/golden/make_decoder_golden.py [seed]
+    python tests/golden/make_decoder_golden.py [dense seed] [mixture-of-experts seed]
 
 Needs the reference tree (REF_ROOT, default /root/reference) and `make -C oracle ref reftools`;
 it is run where the reference is available, and its outputs are committed:
 
-    tests/golden/tiny_qwen3_w4g128.mollm        the package (about 1 MB)
+    tests/golden/tiny_qwen3_w4g128.mollm        the dense package (about 1 MB)
     tests/golden/tiny_qwen3_reference.npz       prompt, the engine's greedy tokens, the
                                                 logits of the prompt's last position
+    tests/golden/tiny_qwen3_moe_w4g128.mollm, tiny_qwen3_moe_reference.npz
+                                                the same for 8 experts of width 128, 2 per token
 
 Steps, all with reference code: a Hugging-Face-style directory with seeded random weights
 (config.json + model.safetensors, the fixture recipe of tests/run_tiny_qwen3_cpu_e2e.py scaled
@@ -40,6 +43,7 @@ REF_ROOT = Path(os.environ.get("REF_ROOT", "/root/reference"))
 REF_DIR = ROOT / "oracle" / "_ref"
 
 LAYERS, HIDDEN, HEADS, KV_HEADS, HEAD_DIM, INTER, VOCAB = 2, 256, 4, 2, 64, 512, 512
+EXPERTS, TOP_K, MOE_INTER = 8, 2, 128
 PROMPT_LEN, STEPS = 12, 32
 
 
@@ -57,7 +61,7 @@ def write_safetensors(path, tensors):
     Path(path).write_bytes(struct.pack("<Q", len(encoded)) + encoded + b"".join(parts))
 
 
-def build_model_dir(model_dir, seed):
+def build_model_dir(model_dir, seed, experts=0):
     rng = np.random.default_rng(seed)
 
     def matrix(rows, cols, std=0.05):
@@ -70,6 +74,10 @@ def build_model_dir(model_dir, seed):
               "rms_norm_eps": 1e-6, "rope_theta": 1000000.0, "num_attention_heads": HEADS,
               "num_key_value_heads": KV_HEADS, "head_dim": HEAD_DIM,
               "intermediate_size": INTER, "vocab_size": VOCAB}
+    if experts:  # the fields models/qwen3_moe.py reads (softmax routing, weights renormalised)
+        config.update({"model_type": "qwen3_moe", "moe_intermediate_size": MOE_INTER,
+                       "num_experts": experts, "num_experts_per_tok": TOP_K,
+                       "norm_topk_prob": True, "decoder_sparse_step": 1, "mlp_only_layers": []})
     (model_dir / "config.json").write_text(json.dumps(config), encoding="utf-8")
     tensors = {"model.embed_tokens.weight": matrix(VOCAB, HIDDEN, 0.5),
                "lm_head.weight": matrix(VOCAB, HIDDEN), "model.norm.weight": norm(HIDDEN)}
@@ -83,10 +91,19 @@ def build_model_dir(model_dir, seed):
             f"{p}.self_attn.v_proj.weight": matrix(KV_HEADS * HEAD_DIM, HIDDEN),
             f"{p}.self_attn.q_norm.weight": norm(HEAD_DIM),
             f"{p}.self_attn.k_norm.weight": norm(HEAD_DIM),
-            f"{p}.self_attn.o_proj.weight": matrix(HIDDEN, HEADS * HEAD_DIM),
-            f"{p}.mlp.gate_proj.weight": matrix(INTER, HIDDEN),
-            f"{p}.mlp.up_proj.weight": matrix(INTER, HIDDEN),
-            f"{p}.mlp.down_proj.weight": matrix(HIDDEN, INTER)})
+            f"{p}.self_attn.o_proj.weight": matrix(HIDDEN, HEADS * HEAD_DIM)})
+        if experts:
+            tensors[f"{p}.mlp.gate.weight"] = matrix(experts, HIDDEN, 0.5)
+            for e in range(experts):
+                tensors.update({
+                    f"{p}.mlp.experts.{e}.gate_proj.weight": matrix(MOE_INTER, HIDDEN),
+                    f"{p}.mlp.experts.{e}.up_proj.weight": matrix(MOE_INTER, HIDDEN),
+                    f"{p}.mlp.experts.{e}.down_proj.weight": matrix(HIDDEN, MOE_INTER)})
+        else:
+            tensors.update({
+                f"{p}.mlp.gate_proj.weight": matrix(INTER, HIDDEN),
+                f"{p}.mlp.up_proj.weight": matrix(INTER, HIDDEN),
+                f"{p}.mlp.down_proj.weight": matrix(HIDDEN, INTER)})
     write_safetensors(model_dir / "model.safetensors", tensors)
 
 
@@ -111,26 +128,34 @@ def reference_engine(package, prompt, steps):
     return tokens, logits
 
 
-def main():
-    seed = int(sys.argv[1]) if len(sys.argv) > 1 else 24
+def make(seed, experts, stem):
     tmp = Path(tempfile.mkdtemp(prefix="decoder_golden_"))
     try:
         model_dir = tmp / "model"
         model_dir.mkdir()
-        build_model_dir(model_dir, seed)
+        build_model_dir(model_dir, seed, experts)
         package = tmp / "tiny.mollm"
         convert(model_dir, package)
         prompt = np.random.default_rng(seed + 1).integers(0, VOCAB, PROMPT_LEN).astype(np.int32)
         tokens, logits = reference_engine(package, prompt, STEPS)
         top = np.sort(logits)[-2:]
-        print(f"seed {seed}: reference tokens {tokens.tolist()}")
+        print(f"{stem}, seed {seed}: reference tokens {tokens.tolist()}")
         print(f"top-1 margin at the prompt's end {top[1] - top[0]:.4f}, "
               f"logit scale {np.abs(logits).max():.3f}")
-        shutil.copyfile(package, HERE / "tiny_qwen3_w4g128.mollm")
-        np.savez(HERE / "tiny_qwen3_reference.npz", prompt=prompt, tokens=tokens, logits=logits,
+        shutil.copyfile(package, HERE / f"{stem}_w4g128.mollm")
+        np.savez(HERE / f"{stem}_reference.npz", prompt=prompt, tokens=tokens, logits=logits,
                  seed=np.int64(seed))
     finally:
         shutil.rmtree(tmp, ignore_errors=True)
+
+
+def main():
+    dense_seed = int(sys.argv[1]) if len(sys.argv) > 1 else 24
+    moe_seed = int(sys.argv[2]) if len(sys.argv) > 2 else 34
+    if dense_seed >= 0:
+        make(dense_seed, 0, "tiny_qwen3")
+    if moe_seed >= 0:
+        make(moe_seed, EXPERTS, "tiny_qwen3_moe")
 
 
 if __name__ == "__main__":

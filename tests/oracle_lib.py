@@ -416,7 +416,7 @@ def dense_decoder_tokens(cfg, weights, prompt, steps, multi_row_rule=ACT_G32, ev
             if cfg.experts:  # the MOE operator under the reference's rule: an expert that
                 # holds several rows quantises per 32 values, a lone row per 128
                 dn = moe_forward(h, L["router"], cfg.top_k, cfg.intermediate, L["gate_up"],
-                                 L["down"], rule=ACT_G32)[0]
+                                 L["down"], rule=ACT_G32 if every_rule is None else every_rule)[0]
             else:
                 act = swiglu(matmul_w4(L["gate_up"], *sh["gate_up"], h, rule=rule))
                 dn = matmul_w4(L["down"], *sh["down"], act, rule=rule)

@@ -1,7 +1,8 @@
-"""The decoder against the REFERENCE'S OWN ENGINE.  tests/golden/tiny_qwen3_w4g128.mollm is a
-two-layer Qwen3 package written by the reference's converter (models/converter.py, W4G128
-through tools/quantize_weight.cpp) and tests/golden/tiny_qwen3_reference.npz holds what the
-reference's CPU engine (LLMEngine::prefill / decode, greedy) answers on it; both come from
+"""The decoder against the REFERENCE'S OWN ENGINE.  tests/golden/tiny_qwen3_w4g128.mollm and
+tiny_qwen3_moe_w4g128.mollm are two-layer Qwen3 packages (dense; 8 routed experts, 2 per token)
+written by the reference's converter (models/converter.py, W4G128 through
+tools/quantize_weight.cpp) and the *_reference.npz files hold what the reference's CPU engine
+(LLMEngine::prefill / decode, greedy) answers on them; all come from
 tests/golden/make_decoder_golden.py.
 
   * the package reader (palm-infra_b200/package.py) finds every weight the decoder needs;
@@ -28,20 +29,29 @@ pkg = load_package()
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 
 
-@pytest.fixture(scope="module")
-def fixture():
-    package = pkg.package.read_package(os.path.join(GOLDEN, "tiny_qwen3_w4g128.mollm"))
+def load_fixture(stem):
+    package = pkg.package.read_package(os.path.join(GOLDEN, stem + "_w4g128.mollm"))
     cfg, weights = pkg.package.qwen3_decoder_weights(package)
-    ref = np.load(os.path.join(GOLDEN, "tiny_qwen3_reference.npz"))
+    ref = np.load(os.path.join(GOLDEN, stem + "_reference.npz"))
     return package, cfg, weights, ref["prompt"].tolist(), ref["tokens"].tolist(), ref["logits"]
+
+
+@pytest.fixture(scope="module", params=["tiny_qwen3", "tiny_qwen3_moe"])
+def fixture(request):
+    return load_fixture(request.param)
 
 
 def test_package_reader_finds_the_decoder(fixture):
     package, cfg, weights, *_ = fixture
-    assert package.metadata["architecture"] == "qwen3"
+    assert package.metadata["architecture"] in ("qwen3", "qwen3-moe")
     assert package.metadata["quantization"] == "w4g128"
     assert (cfg.layers, cfg.hidden, cfg.heads, cfg.kv_heads, cfg.head_dim) == (2, 256, 4, 2, 64)
-    assert cfg.intermediate == 512 and cfg.vocab == 512 and cfg.rope_theta == 1e6
+    assert cfg.vocab == 512 and cfg.rope_theta == 1e6
+    if cfg.experts:
+        assert (cfg.experts, cfg.top_k, cfg.intermediate) == (8, 2, 128)
+        assert all(layer["router"].shape == (8, 256) for layer in weights["layers"])
+    else:
+        assert cfg.intermediate == 512
     assert weights["embed"].shape == (512, 256) and weights["embed"].dtype == np.float16
     assert weights["lm_head"].size == ol.bg128_bytes(512, 256)
     for layer in weights["layers"]:
@@ -63,7 +73,12 @@ def test_exact_arithmetic_reproduces_the_reference_engine(fixture):
 def test_w4a8_tokens_are_the_reference_engines(fixture):
     _, cfg, weights, prompt, tokens, logits = fixture
     first = []
-    got, margins = ol.dense_decoder_tokens(cfg, weights, prompt, len(tokens), first_logits=first)
+    ol.set_exp_mode(True)  # exp as the device takes it; the tokens do not depend on it here
+    try:
+        got, margins = ol.dense_decoder_tokens(cfg, weights, prompt, len(tokens),
+                                               first_logits=first)
+    finally:
+        ol.set_exp_mode(False)
     assert rel_l2(first[0], logits) < 3e-2  # W4A8 against W4A32: the activation quantisation
     assert got == tokens
     assert min(margins) > 1e-2
