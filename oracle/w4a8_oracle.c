@@ -191,6 +191,14 @@ void orc_group_sums_g128(const uint8_t* blocks, int n, int k, const int8_t* qa,
  *     acc = fma(float(dot128), fp32(bscale * ascale[g]), acc), g ascending.
  * ORC_ACT_G32: kernels/matmul_w4.cpp:785-901 (dot-product variant) -- per
  *     32-block qb, acc = fma(float(dot32), fp32(bscale[g] * ascale[m][qb]), acc).
+ * ORC_ACT_G32_I8MM: the same per-32 quantisation as the reference computes it on ARM CPUs
+ *     that have the int8 matrix instructions (kernels/matmul_w4.cpp:1018-1030, 1160-1167 ->
+ *     kernels/matmul_w4_i8mm.cpp:129-207): per group, the four blocks are first summed with
+ *     their activation scales, t = fma(float(dot32_b), ascale[m][b], t) for b = 0..3 from
+ *     t = 0 (:100-121, the scvtf #4 undoes the factor 16 of the left-aligned nibbles), then
+ *     acc = fma(t, bscale[g], acc) (:172-179) -- another association of the same products,
+ *     so the two ARM paths agree to fp32 rounding, not bit for bit.  The GPU kernels
+ *     implement ORC_ACT_G32 (the dot-product path, which every ARMv8.2 CPU runs).
  * ORC_ACT_F64: exact dequantised product, the yardstick the reference's x86
  *     W4A32 kernels (kernels/matmul_x86_avx512.cpp:112-213) approximate.      */
 
@@ -206,7 +214,7 @@ int orc_matmul_w4(const uint8_t* blocks, int n, int k, const float* x, int m,
     if (k <= 0 || k % 128 != 0 || n <= 0 || m <= 0)
         return -1;
     if (act_rule != ORC_ACT_G128 && act_rule != ORC_ACT_G32 &&
-        act_rule != ORC_ACT_F64)
+        act_rule != ORC_ACT_G32_I8MM && act_rule != ORC_ACT_F64)
         return -2;
     int groups = k / 128;
     int qblocks = k / 32;
@@ -242,6 +250,23 @@ int orc_matmul_w4(const uint8_t* blocks, int n, int k, const float* x, int m,
                         group_sums[((size_t)r * n + row) * qblocks + qb] = d;
                     float sc = ws[(size_t)row * groups + qb / 4] * as[qb];
                     acc = fmaf((float)d, sc, acc);
+                }
+                yr[row] = acc;
+            }
+        } else if (act_rule == ORC_ACT_G32_I8MM) {
+            orc_quantize_a_g32(xr, 1, k, k, qa, as);
+            for (int row = 0; row < n; ++row) {
+                float acc = 0.f;
+                for (int g = 0; g < groups; ++g) {
+                    float t = 0.f;
+                    for (int b = 0; b < 4; ++b) {
+                        int qb = g * 4 + b;
+                        int32_t d = dot_i8(wq + (size_t)row * k + qb * 32, qa + qb * 32, 32);
+                        if (group_sums)
+                            group_sums[((size_t)r * n + row) * qblocks + qb] = d;
+                        t = fmaf((float)d, as[qb], t);
+                    }
+                    acc = fmaf(t, ws[(size_t)row * groups + g], acc);
                 }
                 yr[row] = acc;
             }

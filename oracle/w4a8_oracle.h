@@ -34,6 +34,8 @@ enum { ORC_BG128_BLOCK_BYTES = 544 };
 enum {
     ORC_ACT_G128 = 128, /* one scale per 128 values (reference M==1 rule)   */
     ORC_ACT_G32 = 32,   /* one scale per 32 values  (reference M>1 rule)    */
+    ORC_ACT_G32_I8MM = 33, /* the same rule as ARM CPUs with int8 matrix
+                              instructions associate it (matmul only)        */
     ORC_ACT_F64 = 0     /* no activation quantisation: exact fp64 product   */
 };
 

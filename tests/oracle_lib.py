@@ -13,6 +13,7 @@ ORACLE_SO = os.path.join(ORACLE_DIR, "liboracle_w4a8.so")
 REF_SO = os.path.join(ORACLE_DIR, "_ref", "libref_shim.so")
 
 ACT_G128, ACT_G32, ACT_F64 = 128, 32, 0
+ACT_G32_I8MM = 33  # the per-32 rule as ARM's int8-matrix kernels associate it (oracle only)
 BLOCK_BYTES = 544
 
 

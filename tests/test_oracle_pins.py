@@ -81,6 +81,34 @@ def test_group_sums_are_plain_integer_dots():
         assert acc.tobytes() == y[r].tobytes()
 
 
+def test_int8_matrix_association_of_the_per32_rule():
+    """The reference has two ARM kernels for several rows: the dot-product one (ACT_G32, what
+    the GPU implements) and, on CPUs with int8 matrix instructions, one that first sums a
+    group's four blocks with their activation scales and then applies the weight scale
+    (kernels/matmul_w4_i8mm.cpp:100-121, 172-179).  Same integer sums, same scales, another
+    association: restated independently here with numpy (a double product plus addend rounded
+    once is the fma), equal to the first rule within fp32 rounding and not bit for bit."""
+    c = case("synth_m5_k512_n72")
+    n, k = 72, 512
+    y32, sums = ol.matmul_w4(c["blocks"], n, k, c["a"], rule=ol.ACT_G32, want_sums=True)
+    y_mm, sums_mm = ol.matmul_w4(c["blocks"], n, k, c["a"], rule=ol.ACT_G32_I8MM, want_sums=True)
+    assert (sums == sums_mm).all()
+    q, s = ol.bg128_decode(c["blocks"], n, k)
+    for r in range(c["a"].shape[0]):
+        sa = ol.quantize_g32(c["a"][r:r + 1])[1][0]
+        acc = np.zeros(n, dtype=np.float32)
+        for g in range(k // 128):
+            t = np.zeros(n, dtype=np.float32)
+            for b in range(4):
+                d = sums[r][:, g * 4 + b].astype(np.float32).astype(np.float64)
+                t = (d * np.float64(sa[g * 4 + b]) + t.astype(np.float64)).astype(np.float32)
+            acc = (t.astype(np.float64) * s[:, g].astype(np.float64)
+                   + acc.astype(np.float64)).astype(np.float32)
+        assert acc.tobytes() == y_mm[r].tobytes()
+    assert rel_l2(y_mm, y32) < 1e-6
+    assert y_mm.tobytes() != y32.tobytes()
+
+
 def test_fused_activation_range():
     c = case("synth_m5_k512_n72")
     y = ol.matmul_w4(c["blocks"], 72, 512, c["a"], rule=ol.ACT_F64)
