@@ -645,6 +645,48 @@ def moe_decoder_235b(torch, pkg, ctx, args):
                        "vocab 151936", (("reference_rule", pkg.capi.ACT_G32),))
 
 
+def tp_decoder_leg(torch, dist, pkg, ctx, rank, world):
+    """Benchmark configuration 3 over `world` GPUs (--tp-decoder; opt-in: the tensor-parallel
+    driver is verified on CPU ranks only so far): 256-token prompt, 64 greedy steps, one
+    launch per operator, NCCL all-gathers between the row-split matmuls.  Wall clock around
+    synchronised regions, max over ranks."""
+    dec = pkg.decoder
+    cfg = dec.DecoderConfig.qwen3_4b()
+    weights = dec.synthetic_weights(cfg, seed=SEED_W, distinct_layers=1)
+    prompt = np.random.default_rng(11).integers(0, cfg.vocab, 256).tolist()
+    model = dec.TensorParallelDecoder(ctx, cfg, weights, capacity=384, rank=rank, world=world)
+    del weights
+    model.generate(prompt, 3)
+    times = []
+    for _ in range(3):
+        model.reset()
+        torch.cuda.synchronize()
+        dist.barrier()
+        t0 = time.perf_counter()
+        model.prefill(prompt)
+        ctx.sync()
+        torch.cuda.synchronize()
+        t1 = time.perf_counter()
+        for _ in range(64):
+            model.decode_step()
+        ctx.sync()
+        torch.cuda.synchronize()
+        t2 = time.perf_counter()
+        times.append((t1 - t0, t2 - t1))
+    pf = statistics.median(t[0] for t in times)
+    dc = statistics.median(t[1] for t in times)
+    both = torch.tensor([pf, dc], device="cuda", dtype=torch.float64)
+    dist.all_reduce(both, op=dist.ReduceOp.MAX)
+    pf, dc = float(both[0].item()), float(both[1].item())
+    token = int(model.token.item())
+    model.free()
+    return {"config": "36 layers, hidden 2560, 32/8 heads x 128, intermediate 9728, vocab 151936",
+            "parallelism": f"tp{world}: row-split matmuls, attention on the rank's heads, four "
+                           "NCCL all-gathers per layer",
+            "prefill_tps": 256 / pf, "decode_tps": 64 / dc, "prefill_ms": pf * 1e3,
+            "decode_ms_per_token": dc * 1e3 / 64, "last_token": token}
+
+
 class ExtrasGuard:
     """Bounds the extra legs of a multi-GPU run on every rank: after `seconds` rank 0 prints the
     JSON line as it stands (the headline is complete before the guard starts) with a note, and
@@ -1180,6 +1222,12 @@ def run_ours(args):
             except Exception as exc:  # no symmetric memory on this box
                 line["lm_head_greedy_token_tp"] = {"skipped": str(exc)[:200]}
 
+    if world > 1 and args.tp_decoder and not args.headline_only:
+        try:
+            line["dense_decoder_4b_tp"] = tp_decoder_leg(torch, dist, pkg, ctx, rank, world)
+        except Exception as exc:
+            line["dense_decoder_4b_tp"] = {"error": str(exc)[:300]}
+
     if guard is not None and not guard.finish():
         return  # the timer is printing the line and ending the process
     if rank == 0:
@@ -1223,6 +1271,9 @@ def main():
     ap.add_argument("--moe-decoder", action="store_true",
                     help="also run the 30B-A3B-shaped mixture-of-experts decoder end to end "
                          "(uploads 16 GB of synthetic weights; single GPU)")
+    ap.add_argument("--tp-decoder", action="store_true",
+                    help="multi-GPU runs: also run the 4B-shaped dense decoder tensor-parallel "
+                         "over the ranks (opt-in)")
     ap.add_argument("--moe-decoder-235b", action="store_true",
                     help="also run the 235B-A22B-shaped decoder end to end on one GPU (121 GB "
                          "of synthetic weights, several minutes)")

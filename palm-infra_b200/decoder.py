@@ -110,31 +110,36 @@ def _embedding(seed, cfg, distinct_rows=8192):
 
 
 class DenseDecoder:
-    def __init__(self, ctx, cfg, weights, capacity, multi_row_rule=capi.ACT_G32, fused_qkv=None):
+    def __init__(self, ctx, cfg, weights, capacity, multi_row_rule=capi.ACT_G32, fused_qkv=None,
+                 device="cuda"):
+        """device: where torch keeps the tensors the operators work on ("cuda" with the C ABI
+        context; the multi-rank tests run the same driver on "cpu" with a context made of the
+        CPU oracle)."""
         import torch
         self.torch, self.ctx, self.cfg, self.capacity = torch, ctx, cfg, capacity
+        self.device = device
         self.multi_row_rule = multi_row_rule
         can_fuse = cfg.head_dim % 64 == 0 and cfg.head_dim <= 256
         self.fused_qkv = can_fuse if fused_qkv is None else (fused_qkv and can_fuse)
         sh = weights["shapes"]
-        dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+        dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(device)
         self.layers = []
         for w in weights["layers"]:
             self.layers.append({
                 **{k: ctx.upload_weight(w[k], *sh[k]) for k in sh},
                 **{k: dev(w[k]) for k in ("ln1", "ln2", "q_norm", "k_norm")},
                 **({"router": dev(w["router"].view(np.int16))} if cfg.experts else {}),
-                "k_cache": torch.zeros((cfg.kv_heads, capacity, cfg.head_dim), device="cuda"),
-                "v_cache": torch.zeros((cfg.kv_heads, capacity, cfg.head_dim), device="cuda")})
+                "k_cache": torch.zeros((cfg.kv_heads, capacity, cfg.head_dim), device=device),
+                "v_cache": torch.zeros((cfg.kv_heads, capacity, cfg.head_dim), device=device)})
         self.final_norm = dev(weights["final_norm"])
         self.embed = dev(weights["embed"].view(np.int16))
         self.lm_head = ctx.upload_weight(weights["lm_head"], cfg.vocab, cfg.hidden)
         cos, sin = rope_tables(range(capacity), cfg.head_dim, cfg.rope_theta)
         self.cos, self.sin = dev(cos), dev(sin)  # rows = positions
         self.past = 0
-        self.token = torch.zeros((1,), dtype=torch.int32, device="cuda")
-        self.past_dev = torch.zeros((1,), dtype=torch.int32, device="cuda")
-        self.history = torch.zeros((capacity,), dtype=torch.int32, device="cuda")
+        self.token = torch.zeros((1,), dtype=torch.int32, device=device)
+        self.past_dev = torch.zeros((1,), dtype=torch.int32, device=device)
+        self.history = torch.zeros((capacity,), dtype=torch.int32, device=device)
         self.step_graph = None
         self._buf = {}
 
@@ -142,7 +147,7 @@ class DenseDecoder:
         key = (name, rows, cols)
         if key not in self._buf:
             self._buf[key] = self.torch.empty((rows, cols), dtype=self.torch.float32,
-                                              device="cuda")
+                                              device=self.device)
         return self._buf[key]
 
     def reset(self):
@@ -204,7 +209,7 @@ class DenseDecoder:
             self.past += T
 
     def prefill(self, ids):
-        ids_dev = self.torch.from_numpy(np.asarray(ids, dtype=np.int32)).cuda()
+        ids_dev = self.torch.from_numpy(np.asarray(ids, dtype=np.int32)).to(self.device)
         self.forward(ids_dev, len(ids))
         self.past_dev.fill_(self.past)
 
@@ -267,3 +272,104 @@ class DenseDecoder:
             for k in ("qkv", "o", "gate_up", "down"):
                 L[k].free()
         self.lm_head.free()
+
+
+class TensorParallelDecoder(DenseDecoder):
+    """The dense decoder over `world` ranks (one process per GPU, torch.distributed): every
+    matmul is split by output rows (shard.decoder_layer_shard), attention runs on the rank's
+    own heads with a cache of their own, and the pieces are put together again by four
+    all-gathers per layer -- after attention, o, SwiGLU and down -- so that every rank holds
+    the full residual stream and the result is the one-GPU result bit for bit (row-split
+    matmuls are exact; norms and residual adds run replicated).  The lm_head is split by rows
+    too: every rank picks the best of its rows on the device and the (value, index) pairs are
+    gathered; the largest value wins, the lowest index among equals, as on one GPU.
+
+    Not run on GPUs yet: the class is exercised by world-size-2 gloo ranks on the CPU with the
+    oracle standing in for the device operators (tests/test_tp_decoder_cpu.py), where its
+    tokens are those of the one-rank decoder."""
+
+    def __init__(self, ctx, cfg, weights, capacity, rank, world, group=None,
+                 multi_row_rule=capi.ACT_G32, device="cuda"):
+        import torch
+        import torch.distributed as dist
+        from . import shard
+        if cfg.vocab % (8 * world):
+            raise ValueError(f"vocabulary {cfg.vocab} does not split into 8-row tiles over "
+                             f"{world} ranks")
+        self.dist, self.group, self.rank, self.world = dist, group, rank, world
+        self.full = cfg
+        local = DecoderConfig(cfg.layers, cfg.hidden, cfg.heads // world, cfg.kv_heads // world,
+                              cfg.head_dim, cfg.intermediate // world, cfg.vocab // world,
+                              rope_theta=cfg.rope_theta, eps=cfg.eps)
+        sharded, local_shapes = [], None
+        for layer in weights["layers"]:
+            w, local_shapes = shard.decoder_layer_shard(cfg, weights["shapes"], layer, rank, world)
+            sharded.append(w)
+        v_lo, v_hi = shard.row_range(cfg.vocab, rank, world)
+        local_weights = {"shapes": local_shapes, "layers": sharded,
+                         "final_norm": weights["final_norm"], "embed": weights["embed"],
+                         "lm_head": shard.rows_of(weights["lm_head"], cfg.hidden, v_lo, v_hi)}
+        # the base class sees a decoder with this rank's heads, intermediate slice and
+        # vocabulary slice; the o and down shapes (rows H / P, full K) come from local_shapes
+        super().__init__(ctx, local, local_weights, capacity, multi_row_rule=multi_row_rule,
+                         device=device)
+        self.vocab_offset = v_lo
+        self.best = torch.zeros((2,), dtype=torch.float32, device=device)  # value, index
+        self.logits = torch.zeros((1, local.vocab), dtype=torch.float32, device=device)
+        self.local_token = torch.zeros((1,), dtype=torch.int32, device=device)
+
+    def _gather_columns(self, local, name):
+        """[T, n] per rank -> [T, world * n] on every rank, rank r's columns at r * n."""
+        torch, T, n = self.torch, local.shape[0], local.shape[1]
+        parts = self._b(name + "_parts", self.world * T, n).view(self.world, T, n)
+        self.dist.all_gather([parts[p] for p in range(self.world)], local.contiguous(),
+                             group=self.group)
+        full = self._b(name + "_full", T, self.world * n)
+        full.view(T, self.world, n).copy_(parts.permute(1, 0, 2))
+        return full
+
+    def forward(self, ids_dev, tokens, on_device_position=False):
+        c, cfg, full = self.ctx, self.cfg, self.full
+        T, H, D = tokens, full.hidden, full.head_dim
+        rule = capi.ACT_G128 if T == 1 else self.multi_row_rule
+        pos_dev = self.past_dev if on_device_position else None
+        x, h = self._b("x", T, H), self._b("h", T, H)
+        qkv = self._b("qkv", T, cfg.q_dim + 2 * cfg.kv_dim)
+        q, attn_l = self._b("q", T, cfg.q_dim), self._b("attn", T, cfg.q_dim)
+        o_l, dn_l = self._b("o", T, H // self.world), self._b("dn", T, H // self.world)
+        gu, act_l = self._b("gu", T, 2 * cfg.intermediate), self._b("act", T, cfg.intermediate)
+        c.embed_rows(self.embed, ids_dev, x)
+        c.rms_norm(x, self.layers[0]["ln1"], full.eps, h)
+        for li, L in enumerate(self.layers):
+            c.matmul(L["qkv"], h, qkv, rule=rule)
+            c.qkv_prepare(qkv, T, cfg.heads, cfg.kv_heads, D, L["q_norm"], L["k_norm"], full.eps,
+                          self.cos, self.sin, self.past, q, L["k_cache"], L["v_cache"],
+                          self.capacity, pos_dev)
+            c.attention(q, None, None, L["k_cache"], L["v_cache"], attn_l, T, cfg.heads,
+                        cfg.kv_heads, D, self.past, self.capacity, D ** -0.5, pos_dev)
+            attn = self._gather_columns(attn_l, "attn")        # [T, all heads * D]
+            c.matmul(L["o"], attn, o_l, rule=rule)
+            o = self._gather_columns(o_l, "o")                 # [T, H]
+            c.add_rms_norm(x, o, L["ln2"], full.eps, h)
+            c.matmul(L["gate_up"], h, gu, rule=rule)
+            c.swiglu(gu, act_l)
+            act = self._gather_columns(act_l, "act")           # [T, I]
+            c.matmul(L["down"], act, dn_l, rule=rule)
+            dn = self._gather_columns(dn_l, "dn")
+            nxt = self.layers[li + 1]["ln1"] if li + 1 < len(self.layers) else self.final_norm
+            c.add_rms_norm(x, dn, nxt, full.eps, h)
+        if on_device_position:
+            c.advance(self.past_dev, T, ids_dev, self.history)
+        # the rank's best row (first maximum, as on one GPU) and its logit, then the best of all
+        c.matmul_argmax(self.lm_head, h[T - 1:T], self.local_token, y=self.logits)
+        torch = self.torch
+        index = self.local_token.to(torch.int64)
+        self.best[0] = self.logits[0].gather(0, index)[0]
+        self.best[1] = (index[0] + self.vocab_offset).to(torch.float32)  # exact below 2^24
+        pairs = self._b("best_parts", self.world, 2)
+        self.dist.all_gather([pairs[p] for p in range(self.world)], self.best, group=self.group)
+        top = pairs[:, 0].max()
+        winners = torch.where(pairs[:, 0] == top, pairs[:, 1], torch.full_like(pairs[:, 1], 3e7))
+        self.token.copy_(winners.min().to(torch.int32).reshape(1))
+        if not on_device_position:
+            self.past += T

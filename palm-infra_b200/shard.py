@@ -23,6 +23,55 @@ def shard_blocks(blocks, n, k, rank, world):
     return blocks[(lo // 8) * tile_bytes:(hi // 8) * tile_bytes], hi - lo, lo
 
 
+def rows_of(blocks, k, lo, hi):
+    """The BG128 blocks of rows [lo, hi) (multiples of 8) of a weight with K columns."""
+    if lo % 8 or hi % 8:
+        raise ValueError(f"rows [{lo}, {hi}) do not fall on 8-row tiles")
+    tile_bytes = (k // 128) * BLOCK_BYTES
+    return blocks[(lo // 8) * tile_bytes:(hi // 8) * tile_bytes]
+
+
+def decoder_layer_shard(cfg, shapes, layer, rank, world):
+    """Rank `rank`'s share of one dense decoder layer, every matmul split by output rows:
+      qkv      the rank's query heads, then its key heads, then its value heads (so the fused
+               projection of the shard is the fused projection of a model with heads / world
+               heads), attention then runs on those heads alone with a cache of their own;
+      o, down  rows [r * H / P, (r + 1) * H / P) over the full input;
+      gate_up  the rank's slice of the gate rows, then the same slice of the up rows (SwiGLU of
+               the shard's output is the rank's slice of the activation).
+    Inputs of o and down are the concatenation of the ranks' outputs in rank order, which is
+    head order and intermediate-feature order.  Norm weights are replicated.  Returns
+    (layer weights, shapes)."""
+    import numpy as np
+    if cfg.experts:
+        raise ValueError("routed experts shard by expert (expert_range), not by rows")
+    if cfg.heads % world or cfg.kv_heads % world:
+        raise ValueError(f"{cfg.heads} / {cfg.kv_heads} heads do not split over {world} ranks")
+    D, H, I = cfg.head_dim, cfg.hidden, cfg.intermediate
+    q_l, kv_l = cfg.q_dim // world, cfg.kv_dim // world
+    i_lo, i_hi = row_range(I, rank, world)
+    h_lo, h_hi = row_range(H, rank, world)
+    if D % 8:
+        raise ValueError("head_dim must be a multiple of 8")
+    qkv = layer["qkv"]
+    parts = [rows_of(qkv, H, rank * q_l, (rank + 1) * q_l),
+             rows_of(qkv, H, cfg.q_dim + rank * kv_l, cfg.q_dim + (rank + 1) * kv_l),
+             rows_of(qkv, H, cfg.q_dim + cfg.kv_dim + rank * kv_l,
+                     cfg.q_dim + cfg.kv_dim + (rank + 1) * kv_l)]
+    out = {"qkv": np.concatenate(parts),
+           "o": rows_of(layer["o"], cfg.q_dim, h_lo, h_hi),
+           "gate_up": np.concatenate([rows_of(layer["gate_up"], H, i_lo, i_hi),
+                                      rows_of(layer["gate_up"], H, I + i_lo, I + i_hi)]),
+           "down": rows_of(layer["down"], I, h_lo, h_hi)}
+    for key in ("ln1", "ln2", "q_norm", "k_norm"):
+        out[key] = layer[key]
+    local_shapes = {"qkv": (q_l + 2 * kv_l, H), "o": (H // world, cfg.q_dim),
+                    "gate_up": (2 * (I // world), H), "down": (H // world, I)}
+    assert all(out[k].size == (n // 8) * (kk // 128) * BLOCK_BYTES
+               for k, (n, kk) in local_shapes.items()), shapes
+    return out, local_shapes
+
+
 def expert_range(num_experts, rank, world):
     """Expert-parallel placement: contiguous blocks of E/P experts per rank."""
     if num_experts % world:
