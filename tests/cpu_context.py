@@ -90,6 +90,13 @@ class OracleContext:
                                   kv_heads, past, scale)
         out.copy_(torch.from_numpy(got.reshape(tokens, heads * dim)))
 
+    def moe_forward(self, hidden, router_fp16_as_int16, top_k, intermediate, gate_up, down, out,
+                    **_):
+        router = _np(router_fp16_as_int16).view(np.float16)
+        got = ol.moe_forward(_np(hidden), router, top_k, intermediate, gate_up.blocks,
+                             down.blocks, rule=ol.ACT_G32)[0]  # the reference's per-expert rule
+        out.copy_(torch.from_numpy(got))
+
     def advance(self, counter, by=1, token=None, history=None):
         at = int(counter[0])
         if token is not None and history is not None and 0 <= at < history.numel():

@@ -84,6 +84,20 @@ def test_w4a8_tokens_are_the_reference_engines(fixture):
     assert min(margins) > 1e-2
 
 
+def test_decoder_driver_gives_the_reference_engines_tokens_on_the_cpu(fixture):
+    """palm-infra_b200/decoder.py itself -- the operator sequence, buffers and cache handling
+    that run on the GPU -- with the oracle standing in for the device operators."""
+    from cpu_context import OracleContext
+    _, cfg, weights, prompt, tokens, _ = fixture
+    model = pkg.decoder.DenseDecoder(OracleContext(), cfg, weights,
+                                     capacity=len(prompt) + len(tokens) + 8, device="cpu")
+    ol.set_exp_mode(True)
+    try:
+        assert model.generate(prompt, len(tokens)) == tokens
+    finally:
+        ol.set_exp_mode(False)
+
+
 @pytest.mark.gpu
 def test_device_decoder_gives_the_reference_engines_tokens(fixture):
     _, cfg, weights, prompt, tokens, _ = fixture

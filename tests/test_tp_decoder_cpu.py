@@ -39,6 +39,15 @@ def test_one_rank_driver_equals_the_straight_line_decoder():
     assert model.generate(prompt, STEPS) == want
 
 
+def test_one_rank_driver_with_routed_experts():
+    cfg = dec.DecoderConfig(2, 256, 4, 2, 64, 128, 512, experts=8, top_k=2)
+    weights = dec.synthetic_weights(cfg, seed=4)
+    prompt = np.random.default_rng(5).integers(0, 512, 12).tolist()
+    want, _ = ol.dense_decoder_tokens(cfg, weights, prompt, 8)
+    model = dec.DenseDecoder(OracleContext(), cfg, weights, capacity=32, device="cpu")
+    assert model.generate(prompt, 8) == want
+
+
 def test_layer_shards_reassemble():
     cfg, weights, _ = _model()
     layer, shapes = weights["layers"][0], weights["shapes"]
