@@ -275,14 +275,17 @@ class DenseDecoder:
 
 
 class TensorParallelDecoder(DenseDecoder):
-    """The dense decoder over `world` ranks (one process per GPU, torch.distributed): every
+    """The decoder over `world` ranks (one process per GPU, torch.distributed): every
     matmul is split by output rows (shard.decoder_layer_shard), attention runs on the rank's
     own heads with a cache of their own, and the pieces are put together again by four
     all-gathers per layer -- after attention, o, SwiGLU and down -- so that every rank holds
     the full residual stream and the result is the one-GPU result bit for bit (row-split
-    matmuls are exact; norms and residual adds run replicated).  The lm_head is split by rows
-    too: every rank picks the best of its rows on the device and the (value, index) pairs are
-    gathered; the largest value wins, the lowest index among equals, as on one GPU.
+    matmuls are exact; norms and residual adds run replicated).  A routed mixture of experts
+    is split by expert instead (expert_parallel.ExpertParallelMoE: the rank's experts' route
+    outputs, one all-reduce of the route buffer, the ordered combine on every rank).  The
+    lm_head is split by rows too: every rank picks the best of its rows on the device and the
+    (value, index) pairs are gathered; the largest value wins, the lowest index among equals,
+    as on one GPU.
 
     Not run on GPUs yet: the class is exercised by world-size-2 gloo ranks on the CPU with the
     oracle standing in for the device operators (tests/test_tp_decoder_cpu.py), where its
@@ -298,9 +301,14 @@ class TensorParallelDecoder(DenseDecoder):
                              f"{world} ranks")
         self.dist, self.group, self.rank, self.world = dist, group, rank, world
         self.full = cfg
+        # what the base class sets up: this rank's heads, its slice of the intermediate
+        # features (or its experts) and its slice of the vocabulary
         local = DecoderConfig(cfg.layers, cfg.hidden, cfg.heads // world, cfg.kv_heads // world,
-                              cfg.head_dim, cfg.intermediate // world, cfg.vocab // world,
-                              rope_theta=cfg.rope_theta, eps=cfg.eps)
+                              cfg.head_dim,
+                              cfg.intermediate if cfg.experts else cfg.intermediate // world,
+                              cfg.vocab // world, rope_theta=cfg.rope_theta, eps=cfg.eps,
+                              experts=cfg.experts // world if cfg.experts else 0,
+                              top_k=cfg.top_k)
         sharded, local_shapes = [], None
         for layer in weights["layers"]:
             w, local_shapes = shard.decoder_layer_shard(cfg, weights["shapes"], layer, rank, world)
@@ -309,10 +317,17 @@ class TensorParallelDecoder(DenseDecoder):
         local_weights = {"shapes": local_shapes, "layers": sharded,
                          "final_norm": weights["final_norm"], "embed": weights["embed"],
                          "lm_head": shard.rows_of(weights["lm_head"], cfg.hidden, v_lo, v_hi)}
-        # the base class sees a decoder with this rank's heads, intermediate slice and
-        # vocabulary slice; the o and down shapes (rows H / P, full K) come from local_shapes
         super().__init__(ctx, local, local_weights, capacity, multi_row_rule=multi_row_rule,
                          device=device)
+        self.moe = []
+        if cfg.experts:
+            from .expert_parallel import DeviceEngine, ExpertParallelMoE
+            e_lo, e_hi = shard.expert_range(cfg.experts, rank, world)
+            reduce_sum = lambda t: dist.all_reduce(t, group=group)
+            for L in self.layers:
+                engine = DeviceEngine(ctx, L["router"], L["gate_up"], L["down"], cfg.top_k,
+                                      cfg.intermediate, e_lo, e_hi - e_lo)
+                self.moe.append(ExpertParallelMoE(engine, reduce_sum))
         self.vocab_offset = v_lo
         self.best = torch.zeros((2,), dtype=torch.float32, device=device)  # value, index
         self.logits = torch.zeros((1, local.vocab), dtype=torch.float32, device=device)
@@ -337,7 +352,10 @@ class TensorParallelDecoder(DenseDecoder):
         qkv = self._b("qkv", T, cfg.q_dim + 2 * cfg.kv_dim)
         q, attn_l = self._b("q", T, cfg.q_dim), self._b("attn", T, cfg.q_dim)
         o_l, dn_l = self._b("o", T, H // self.world), self._b("dn", T, H // self.world)
-        gu, act_l = self._b("gu", T, 2 * cfg.intermediate), self._b("act", T, cfg.intermediate)
+        gu = act_l = None
+        if not full.experts:
+            gu = self._b("gu", T, 2 * cfg.intermediate)
+            act_l = self._b("act", T, cfg.intermediate)
         c.embed_rows(self.embed, ids_dev, x)
         c.rms_norm(x, self.layers[0]["ln1"], full.eps, h)
         for li, L in enumerate(self.layers):
@@ -351,11 +369,14 @@ class TensorParallelDecoder(DenseDecoder):
             c.matmul(L["o"], attn, o_l, rule=rule)
             o = self._gather_columns(o_l, "o")                 # [T, H]
             c.add_rms_norm(x, o, L["ln2"], full.eps, h)
-            c.matmul(L["gate_up"], h, gu, rule=rule)
-            c.swiglu(gu, act_l)
-            act = self._gather_columns(act_l, "act")           # [T, I]
-            c.matmul(L["down"], act, dn_l, rule=rule)
-            dn = self._gather_columns(dn_l, "dn")
+            if full.experts:  # the rank's experts, all-reduce of the route rows, combine
+                dn = self.moe[li].forward(h, self._b("moe_out", T, H))
+            else:
+                c.matmul(L["gate_up"], h, gu, rule=rule)
+                c.swiglu(gu, act_l)
+                act = self._gather_columns(act_l, "act")       # [T, I]
+                c.matmul(L["down"], act, dn_l, rule=rule)
+                dn = self._gather_columns(dn_l, "dn")
             nxt = self.layers[li + 1]["ln1"] if li + 1 < len(self.layers) else self.final_norm
             c.add_rms_norm(x, dn, nxt, full.eps, h)
         if on_device_position:

@@ -32,7 +32,7 @@ def rows_of(blocks, k, lo, hi):
 
 
 def decoder_layer_shard(cfg, shapes, layer, rank, world):
-    """Rank `rank`'s share of one dense decoder layer, every matmul split by output rows:
+    """Rank `rank`'s share of one decoder layer, every matmul split by output rows:
       qkv      the rank's query heads, then its key heads, then its value heads (so the fused
                projection of the shard is the fused projection of a model with heads / world
                heads), attention then runs on those heads alone with a cache of their own;
@@ -40,16 +40,15 @@ def decoder_layer_shard(cfg, shapes, layer, rank, world):
       gate_up  the rank's slice of the gate rows, then the same slice of the up rows (SwiGLU of
                the shard's output is the rank's slice of the activation).
     Inputs of o and down are the concatenation of the ranks' outputs in rank order, which is
-    head order and intermediate-feature order.  Norm weights are replicated.  Returns
-    (layer weights, shapes)."""
+    head order and intermediate-feature order.  Norm weights are replicated.  With routed
+    experts the feed-forward block is split by expert instead (expert_range): the rank keeps
+    its experts' rows of both aggregates and the whole router.  Returns (layer weights,
+    shapes)."""
     import numpy as np
-    if cfg.experts:
-        raise ValueError("routed experts shard by expert (expert_range), not by rows")
     if cfg.heads % world or cfg.kv_heads % world:
         raise ValueError(f"{cfg.heads} / {cfg.kv_heads} heads do not split over {world} ranks")
     D, H, I = cfg.head_dim, cfg.hidden, cfg.intermediate
     q_l, kv_l = cfg.q_dim // world, cfg.kv_dim // world
-    i_lo, i_hi = row_range(I, rank, world)
     h_lo, h_hi = row_range(H, rank, world)
     if D % 8:
         raise ValueError("head_dim must be a multiple of 8")
@@ -58,15 +57,23 @@ def decoder_layer_shard(cfg, shapes, layer, rank, world):
              rows_of(qkv, H, cfg.q_dim + rank * kv_l, cfg.q_dim + (rank + 1) * kv_l),
              rows_of(qkv, H, cfg.q_dim + cfg.kv_dim + rank * kv_l,
                      cfg.q_dim + cfg.kv_dim + (rank + 1) * kv_l)]
-    out = {"qkv": np.concatenate(parts),
-           "o": rows_of(layer["o"], cfg.q_dim, h_lo, h_hi),
-           "gate_up": np.concatenate([rows_of(layer["gate_up"], H, i_lo, i_hi),
-                                      rows_of(layer["gate_up"], H, I + i_lo, I + i_hi)]),
-           "down": rows_of(layer["down"], I, h_lo, h_hi)}
+    out = {"qkv": np.concatenate(parts), "o": rows_of(layer["o"], cfg.q_dim, h_lo, h_hi)}
+    local_shapes = {"qkv": (q_l + 2 * kv_l, H), "o": (H // world, cfg.q_dim)}
+    if cfg.experts:
+        e_lo, e_hi = expert_range(cfg.experts, rank, world)
+        out["gate_up"] = rows_of(layer["gate_up"], H, e_lo * 2 * I, e_hi * 2 * I)
+        out["down"] = rows_of(layer["down"], I, e_lo * H, e_hi * H)
+        out["router"] = layer["router"]
+        local_shapes.update({"gate_up": ((e_hi - e_lo) * 2 * I, H),
+                             "down": ((e_hi - e_lo) * H, I)})
+    else:
+        i_lo, i_hi = row_range(I, rank, world)
+        out["gate_up"] = np.concatenate([rows_of(layer["gate_up"], H, i_lo, i_hi),
+                                         rows_of(layer["gate_up"], H, I + i_lo, I + i_hi)])
+        out["down"] = rows_of(layer["down"], I, h_lo, h_hi)
+        local_shapes.update({"gate_up": (2 * (I // world), H), "down": (H // world, I)})
     for key in ("ln1", "ln2", "q_norm", "k_norm"):
         out[key] = layer[key]
-    local_shapes = {"qkv": (q_l + 2 * kv_l, H), "o": (H // world, cfg.q_dim),
-                    "gate_up": (2 * (I // world), H), "down": (H // world, I)}
     assert all(out[k].size == (n // 8) * (kk // 128) * BLOCK_BYTES
                for k, (n, kk) in local_shapes.items()), shapes
     return out, local_shapes

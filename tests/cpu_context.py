@@ -97,6 +97,23 @@ class OracleContext:
                              down.blocks, rule=ol.ACT_G32)[0]  # the reference's per-expert rule
         out.copy_(torch.from_numpy(got))
 
+    def moe_expert_outputs(self, hidden, router_fp16_as_int16, top_k, intermediate,
+                           gate_up_local, down_local, expert_begin, expert_count, route_out,
+                           indices, weights):
+        x = _np(hidden)
+        logits = ol.router_logits(x, _np(router_fp16_as_int16).view(np.float16))
+        idx, w = ol.select_routes(logits, top_k)
+        # the local aggregates are indexed from the first expert this rank holds
+        routes = ol.expert_route_outputs(x, idx - expert_begin, intermediate,
+                                         gate_up_local.blocks, down_local.blocks, expert_count,
+                                         rule=ol.ACT_G32)
+        route_out.copy_(torch.from_numpy(routes))
+        indices.copy_(torch.from_numpy(idx))
+        weights.copy_(torch.from_numpy(w))
+
+    def moe_combine(self, route_out, top_k, indices, weights, out):
+        out.copy_(torch.from_numpy(ol.moe_combine(_np(route_out), _np(indices), _np(weights))))
+
     def advance(self, counter, by=1, token=None, history=None):
         at = int(counter[0])
         if token is not None and history is not None and 0 <= at < history.numel():

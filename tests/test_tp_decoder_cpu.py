@@ -24,8 +24,9 @@ LAYERS, HIDDEN, HEADS, KV_HEADS, HEAD_DIM, INTER, VOCAB = 2, 256, 4, 4, 64, 256,
 PROMPT_LEN, STEPS, SEED = 9, 10, 31
 
 
-def _model():
-    cfg = dec.DecoderConfig(LAYERS, HIDDEN, HEADS, KV_HEADS, HEAD_DIM, INTER, VOCAB)
+def _model(experts=0):
+    cfg = dec.DecoderConfig(LAYERS, HIDDEN, HEADS, KV_HEADS, HEAD_DIM, 128 if experts else INTER,
+                            VOCAB, experts=experts, top_k=2 if experts else 0)
     weights = dec.synthetic_weights(cfg, seed=SEED)
     prompt = np.random.default_rng(SEED).integers(0, VOCAB, PROMPT_LEN).tolist()
     return cfg, weights, prompt
@@ -70,11 +71,11 @@ def test_layer_shards_reassemble():
         pkg.shard.decoder_layer_shard(cfg, shapes, layer, 0, 3)
 
 
-def _worker(rank, world, port, out_dir):
+def _worker(rank, world, port, out_dir, experts):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
-    cfg, weights, prompt = _model()
+    cfg, weights, prompt = _model(experts)
     model = dec.TensorParallelDecoder(OracleContext(), cfg, weights,
                                       capacity=PROMPT_LEN + STEPS + 4, rank=rank, world=world,
                                       device="cpu")
@@ -84,12 +85,14 @@ def _worker(rank, world, port, out_dir):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world", [2, 4])
-def test_tensor_parallel_driver_gives_the_one_rank_tokens(tmp_path, world):
-    cfg, weights, prompt = _model()
+@pytest.mark.parametrize("world,experts", [(2, 0), (4, 0), (2, 8), (4, 8)])
+def test_tensor_parallel_driver_gives_the_one_rank_tokens(tmp_path, world, experts):
+    """experts > 0: attention split by heads, the feed-forward block split by expert with one
+    all-reduce of the route rows."""
+    cfg, weights, prompt = _model(experts)
     want, margins = ol.dense_decoder_tokens(cfg, weights, prompt, STEPS)
-    port = 29500 + (os.getpid() + 7 * world) % 2000
-    mp.spawn(_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
+    port = 29500 + (os.getpid() + 7 * world + experts) % 2000
+    mp.spawn(_worker, args=(world, port, str(tmp_path), experts), nprocs=world, join=True)
     for rank in range(world):
         with open(tmp_path / f"tokens_{rank}.json") as f:
             assert json.load(f) == want, (rank, margins)
