@@ -411,6 +411,11 @@ int b2w4_advance(b2w4_ctx* ctx, int* counter_dev, int by, const int32_t* token_d
                  int32_t* history_dev, int history_len);
 int b2w4_copy_rows(b2w4_ctx* ctx, const float* src_dev, int ld_src, float* dst_dev, int ld_dst,
                    int rows, int cols);
+/* Host function (no device, no context): cos / sin tables [positions][rope_dim / 2] for
+ * b2w4_rope / b2w4_qkv_prepare, filled as the reference's engine fills them
+ * (engine/input_prep.cpp:18-31), in fp32 through the host libm's float functions. */
+int b2w4_rope_tables(float* cos_host, float* sin_host, int positions, int first_position,
+                     int rope_dim, float theta);
 int b2w4_embed_rows(b2w4_ctx* ctx, const void* table_fp16_dev, const int32_t* ids_dev, int rows,
                     int dim, float* out_dev, int ldo);
 

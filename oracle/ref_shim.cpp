@@ -34,6 +34,9 @@
 #include "kernels/threading.h"
 #include "engine/engine.h"
 #include "engine/sampler.h"
+#include "kernels/cpu_platform.h"
+
+#include <dlfcn.h>
 
 #include <chrono>
 #include <cstdint>
@@ -302,3 +305,41 @@ extern "C" int ref_engine_generate(const char* package_path, const int* prompt, 
     }
     return 0;
 }
+
+
+// ---------------------------------------------------------------------------------------
+// The reference's CPU engine with W4A8 matmuls.  On x86 the engine's INT4 matmuls go through
+// the provider seam mollm::cpu::matmul_int4_packed (kernels/cpu_platform.h:75-79, x86
+// definition kernels/cpu_platform_x86.cpp:128-270: fp32 activations times dequantised
+// weights).  The definition below sits in front of the reference library's in symbol
+// lookup: switched off it forwards to the reference's own; switched on it answers BG128
+// matmuls with the oracle's W4A8 arithmetic under the reference's rule per row count (one
+// row: per 128 values, kernels/matmul_w4.cpp:1058-1075; several: per 32, :1125-1154), which is
+// what the reference's ARM build computes.  Everything else of a run -- graph executor,
+// norms, rotary embedding, attention, MoE control flow, sampler -- stays the reference's code.
+extern "C" int orc_matmul_w4(const uint8_t* blocks, int n, int k, const float* x, int m, int lda,
+                             float* y, int ldc, int act_rule, int32_t* group_sums);
+
+namespace {
+int g_w4a8_provider = 0;
+using ProviderFn = bool (*)(const Tensor&, const Tensor&, Tensor&, int, int, ThreadPool*);
+}  // namespace
+
+extern "C" void ref_set_w4a8_provider(int on) { g_w4a8_provider = on; }
+
+namespace mollm::cpu {
+bool matmul_int4_packed(const Tensor& A, const Tensor& B, Tensor& C, int lda, int ldc,
+                        ThreadPool* thread_pool) {
+    if (g_w4a8_provider && B.is_q4_g128_packed && B.q4_g128_data && B.group_size == 128 &&
+        A.shape[0] % 128 == 0) {
+        const int m = static_cast<int>(A.shape[1]);
+        const int k = static_cast<int>(A.shape[0]);
+        const int n = static_cast<int>(B.shape[0]);
+        return orc_matmul_w4(static_cast<const uint8_t*>(B.q4_g128_data), n, k, A.ptr<float>(),
+                             m, lda, C.ptr<float>(), ldc, m == 1 ? 128 : 32, nullptr) == 0;
+    }
+    static ProviderFn next = reinterpret_cast<ProviderFn>(dlsym(
+        RTLD_NEXT, "_ZN5mollm3cpu18matmul_int4_packedERK6TensorS3_RS1_iiP10ThreadPool"));
+    return next ? next(A, B, C, lda, ldc, thread_pool) : false;
+}
+}  // namespace mollm::cpu

@@ -687,3 +687,23 @@ void orc_sdpa_head(const float* query, const float* key, const float* value, flo
     }
     free(scores);
 }
+
+
+/* ---------------------------------------------------------- rotary tables --
+ * engine/input_prep.cpp:18-31 (fill_rope_cache): per position and feature pair i,
+ * theta_i = 1 / pow(rope_theta, 2 i / rope_dim), angle = position * theta_i, cos and sin of
+ * the angle -- all float, through the host libm (std::pow / std::cos / std::sin on floats are
+ * powf / cosf / sinf).  cos_out / sin_out: [positions][rope_dim / 2].                        */
+void orc_rope_tables(float* cos_out, float* sin_out, int positions, int first_position,
+                     int rope_dim, float rope_theta) {
+    const int half = rope_dim / 2;
+    for (int n = 0; n < positions; ++n) {
+        const int pos = first_position + n;
+        for (int i = 0; i < half; ++i) {
+            const float theta = 1.0f / powf(rope_theta, 2.0f * i / rope_dim);
+            const float angle = pos * theta;
+            cos_out[(size_t)n * half + i] = cosf(angle);
+            sin_out[(size_t)n * half + i] = sinf(angle);
+        }
+    }
+}

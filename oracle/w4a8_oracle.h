@@ -119,4 +119,8 @@ void orc_sdpa_head(const float* query, const float* key, const float* value, flo
                    int query_tokens, int key_tokens, int key_dim, int value_dim, float scale,
                    const float* mask);
 
+/* Rotary tables as the reference's engine fills them (engine/input_prep.cpp:18-31). */
+void orc_rope_tables(float* cos_out, float* sin_out, int positions, int first_position,
+                     int rope_dim, float rope_theta);
+
 #endif

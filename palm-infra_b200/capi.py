@@ -29,7 +29,7 @@ SYMBOLS = [
     "b2w4_chain_input", "b2w4_chain_output", "b2w4_chain_weight_bytes", "b2w4_chain_set_trace",
     "b2w4_rms_norm", "b2w4_add_rms_norm", "b2w4_swiglu", "b2w4_elementwise", "b2w4_rope",
     "b2w4_attention", "b2w4_embed_rows", "b2w4_copy_rows", "b2w4_advance",
-    "b2w4_qkv_prepare",
+    "b2w4_qkv_prepare", "b2w4_rope_tables",
     "b2w4_kernel_launches",
 ]
 
@@ -128,6 +128,7 @@ def lib():
         L.b2w4_rope.argtypes = [vp, f_p, f_p, i, i, i, f_p, f_p, i, i, vp]
         L.b2w4_attention.argtypes = [vp, f_p, f_p, f_p, f_p, f_p, f_p, i, i, i, i, i, vp, i, fl]
         L.b2w4_advance.argtypes = [vp, vp, i, vp, vp, i]
+        L.b2w4_rope_tables.argtypes = [vp, vp, i, i, i, fl]
         L.b2w4_qkv_prepare.argtypes = [vp, f_p, i, i, i, i, i, f_p, f_p, fl, f_p, f_p, i, vp,
                                        f_p, f_p, f_p, i]
         L.b2w4_embed_rows.argtypes = [vp, vp, vp, i, i, f_p, i]
@@ -141,6 +142,19 @@ def lib():
 def _dptr(t):
     """Device pointer of a torch CUDA tensor (or None)."""
     return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def rope_tables(positions, first_position, rope_dim, theta):
+    """(cos, sin) [positions, rope_dim // 2] on the host, as the reference's engine fills them
+    (b2w4_rope_tables); needs no GPU."""
+    import numpy as np
+    cos = np.zeros((positions, rope_dim // 2), dtype=np.float32)
+    sin = np.zeros_like(cos)
+    rc = lib().b2w4_rope_tables(cos.ctypes.data, sin.ctypes.data, positions, first_position,
+                                rope_dim, theta)
+    if rc != 0:
+        raise B200W4Error(f"b2w4_rope_tables: error {rc}")
+    return cos, sin
 
 
 class Weight:

@@ -2,6 +2,8 @@
 // context and weight lifetime, and dispatch to the kernels' launchers.  No arithmetic here.
 #include "b200w4_internal.cuh"
 
+#include <math.h>
+
 #include <cstdlib>
 #include <cstring>
 #include <new>
@@ -38,6 +40,30 @@ int b2w4_reserve(b2w4_ctx* ctx, int slot, size_t bytes, void** out) {
 extern "C" {
 
 const char* b2w4_version(void) { return "b200w4 0.1 (sm_100a)"; }
+
+// Host function, no device involved: the rotary-embedding tables as the reference's engine
+// fills them (engine/input_prep.cpp:18-31) -- theta_i = 1 / theta^(2i / rope_dim), angle =
+// position * theta_i, cosine and sine of the angle, every step in fp32 through the host
+// libm's float functions, so that on the same host the tables carry the engine's bits
+// (the float cosine and sine of a libm are within an ulp of the exact value, not always equal
+// to it, and differ between implementations).
+int b2w4_rope_tables(float* cos_host, float* sin_host, int positions, int first_position,
+                     int rope_dim, float theta) {
+    if (!cos_host || !sin_host || positions <= 0 || first_position < 0 || rope_dim <= 0 ||
+        (rope_dim & 1) || !(theta > 0.f))
+        return B2W4_E_INVALID;
+    const int half = rope_dim / 2;
+    for (int n = 0; n < positions; ++n) {
+        const int pos = first_position + n;
+        for (int i = 0; i < half; ++i) {
+            const float inv = 1.0f / powf(theta, 2.0f * i / rope_dim);
+            const float angle = pos * inv;
+            cos_host[(size_t)n * half + i] = cosf(angle);
+            sin_host[(size_t)n * half + i] = sinf(angle);
+        }
+    }
+    return B2W4_OK;
+}
 
 int b2w4_ctx_create(int device, b2w4_ctx** out) {
     if (!out)

@@ -53,13 +53,13 @@ class DecoderConfig:
 def rope_tables(positions, rope_dim, theta):
     """cos / sin [len(positions), rope_dim // 2] as the reference fills them on the host
     (engine/input_prep.cpp:18-31): theta_i = 1 / theta^(2i / rope_dim), angle = pos * theta_i,
-    all in fp32."""
-    half = rope_dim // 2
-    i = np.arange(half, dtype=np.float32)
-    inv = (np.float32(1.0) / np.power(np.float32(theta), np.float32(2.0) * i / np.float32(rope_dim))
-           ).astype(np.float32)
-    ang = (np.asarray(positions, dtype=np.float32)[:, None] * inv[None, :]).astype(np.float32)
-    return np.cos(ang).astype(np.float32), np.sin(ang).astype(np.float32)
+    all in fp32 through the host libm's float functions (b2w4_rope_tables: numpy's float
+    cosine and sine differ from a libm's in the last bit for a third of the entries).
+    `positions`: consecutive integers."""
+    positions = list(positions)
+    if positions != list(range(positions[0], positions[0] + len(positions))):
+        raise ValueError("positions must be consecutive")
+    return capi.rope_tables(len(positions), positions[0], rope_dim, theta)
 
 
 def synthetic_weights(cfg, seed=20261125, distinct_layers=None, lazy=False):

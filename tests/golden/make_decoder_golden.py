@@ -9,8 +9,10 @@ Needs the reference tree (REF_ROOT, default /root/reference) and `make -C oracle
 it is run where the reference is available, and its outputs are committed:
 
     tests/golden/tiny_qwen3_w4g128.mollm        the dense package (about 1 MB)
-    tests/golden/tiny_qwen3_reference.npz       prompt, the engine's greedy tokens, the
-                                                logits of the prompt's last position
+    tests/golden/tiny_qwen3_reference.npz       prompt, the engine's greedy tokens and the
+                                                logits of the prompt's last position, as the
+                                                x86 build computes them (W4A32) and with the
+                                                W4A8 matmul at the engine's provider seam
     tests/golden/tiny_qwen3_moe_w4g128.mollm, tiny_qwen3_moe_reference.npz
                                                 the same for 8 experts of width 128, 2 per token
 
@@ -23,7 +25,11 @@ tools/quantize_weight.cpp, built as oracle/_ref/mollm-quantize) -> LLMEngine on 
 The reference's x86 build multiplies fp32 activations with dequantised weights (W4A32); the
 W4A8 decoders of this repository differ from it by the activation quantisation, so the seed is
 chosen for top-1 margins far above that difference (printed below), and the tests compare
-logits with a tolerance and tokens exactly.
+those logits with a tolerance and the tokens exactly.  The second recording runs the same
+engine with its INT4 matmuls answered, at the provider seam the reference documents
+(kernels/cpu_platform.h:75-79), by the oracle's W4A8 arithmetic under the reference's rule per
+row count (oracle/ref_shim.cpp): what the reference's ARM build computes, with every other
+operator the reference's own code.  Against that recording the comparison is bit for bit.
 """
 import ctypes as C
 import json
@@ -115,14 +121,16 @@ def convert(model_dir, package):
                    stdout=subprocess.DEVNULL)
 
 
-def reference_engine(package, prompt, steps):
+def reference_engine(package, prompt, steps, w4a8=False):
     lib = C.CDLL(str(REF_DIR / "libref_shim.so"))
+    lib.ref_set_w4a8_provider(1 if w4a8 else 0)
     ids = np.asarray(prompt, dtype=np.int32)
     tokens = np.zeros(steps, dtype=np.int32)
     logits = np.zeros(VOCAB, dtype=np.float32)
     rc = lib.ref_engine_generate(str(package).encode(), ids.ctypes.data_as(C.c_void_p), len(ids),
                                  steps, 256, 1, tokens.ctypes.data_as(C.c_void_p),
                                  logits.ctypes.data_as(C.c_void_p), VOCAB)
+    lib.ref_set_w4a8_provider(0)
     if rc != 0:
         raise RuntimeError(f"ref_engine_generate returned {rc}")
     return tokens, logits
@@ -138,13 +146,14 @@ def make(seed, experts, stem):
         convert(model_dir, package)
         prompt = np.random.default_rng(seed + 1).integers(0, VOCAB, PROMPT_LEN).astype(np.int32)
         tokens, logits = reference_engine(package, prompt, STEPS)
+        tokens_w4a8, logits_w4a8 = reference_engine(package, prompt, STEPS, w4a8=True)
         top = np.sort(logits)[-2:]
         print(f"{stem}, seed {seed}: reference tokens {tokens.tolist()}")
         print(f"top-1 margin at the prompt's end {top[1] - top[0]:.4f}, "
               f"logit scale {np.abs(logits).max():.3f}")
         shutil.copyfile(package, HERE / f"{stem}_w4g128.mollm")
         np.savez(HERE / f"{stem}_reference.npz", prompt=prompt, tokens=tokens, logits=logits,
-                 seed=np.int64(seed))
+                 tokens_w4a8=tokens_w4a8, logits_w4a8=logits_w4a8, seed=np.int64(seed))
     finally:
         shutil.rmtree(tmp, ignore_errors=True)
 

@@ -59,6 +59,25 @@ def ref():
     return _ref
 
 
+def ref_engine_generate(package_path, prompt, steps, vocab, w4a8=False, n_ctx=256):
+    """The reference's CPU engine (LLMEngine, greedy) on a .mollm package: (tokens, logits of
+    the prompt's last position).  w4a8: its INT4 matmuls are answered at the provider seam by
+    the oracle's W4A8 arithmetic under the reference's rule per row count (what its ARM build
+    computes); everything else stays the reference's code (oracle/ref_shim.cpp)."""
+    lib = ref()
+    lib.ref_set_w4a8_provider(1 if w4a8 else 0)
+    ids = np.asarray(prompt, dtype=np.int32)
+    tokens = np.zeros(steps, dtype=np.int32)
+    logits = np.zeros(vocab, dtype=np.float32)
+    try:
+        rc = lib.ref_engine_generate(str(package_path).encode(), _ptr(ids), len(ids), steps,
+                                     n_ctx, 1, _ptr(tokens), _ptr(logits), vocab)
+    finally:
+        lib.ref_set_w4a8_provider(0)
+    assert rc == 0, rc
+    return tokens.tolist(), logits
+
+
 # ---------------------------------------------------------------- oracle calls
 
 def set_exp_mode(correctly_rounded):
@@ -370,6 +389,15 @@ def causal_attention(q, k_all, v_all, heads, kv_heads, past, scale, which=None):
     return out
 
 
+def rope_tables(positions, first_position, rope_dim, theta):
+    """(cos, sin) [positions, rope_dim // 2] as the reference's engine fills them."""
+    cos = np.zeros((positions, rope_dim // 2), dtype=np.float32)
+    sin = np.zeros_like(cos)
+    oracle().orc_rope_tables(_ptr(cos), _ptr(sin), positions, first_position, rope_dim,
+                             C.c_float(theta))
+    return cos, sin
+
+
 def dense_decoder_tokens(cfg, weights, prompt, steps, multi_row_rule=ACT_G32, every_rule=None,
                          first_logits=None):
     """Greedy tokens of the Qwen3-shaped decoder, dense or with the routed mixture of experts
@@ -398,7 +426,7 @@ def dense_decoder_tokens(cfg, weights, prompt, steps, multi_row_rule=ACT_G32, ev
         rule = ACT_G128 if T == 1 else multi_row_rule
         if every_rule is not None:
             rule = every_rule
-        cos, sin = dec.rope_tables(range(past, past + T), D, cfg.rope_theta)
+        cos, sin = rope_tables(T, past, D, cfg.rope_theta)
         x = embed[np.asarray(ids)]
         h = rms_norm(x, weights["layers"][0]["ln1"], cfg.eps)
         for li, L in enumerate(weights["layers"]):

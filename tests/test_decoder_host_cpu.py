@@ -2,6 +2,7 @@
 shapes, the synthetic model generator (eager and layer-by-layer forms give the same bytes), the
 rotary tables, and the weight bytes a decode token streams."""
 import numpy as np
+import pytest
 
 import oracle_lib as ol
 from __graft_entry__ import load_package
@@ -55,15 +56,26 @@ def test_lazy_layers_are_the_eager_layers():
 
 
 def test_rotary_tables_follow_the_engine():
-    """engine/input_prep.cpp:18-31: theta_i = 1 / theta^(2i / rope_dim) in fp32, angle =
-    position * theta_i, cos / sin of the fp32 angle."""
-    cos, sin = dec.rope_tables([0, 1, 7, 300], 64, 1e6)
-    assert cos.shape == sin.shape == (4, 32) and cos.dtype == np.float32
-    assert (cos[0] == 1).all() and (sin[0] == 0).all()
-    for row, pos in ((1, 1), (2, 7), (3, 300)):
-        for i in (0, 5, 31):
-            inv = np.float32(1.0) / np.float32(np.power(np.float32(1e6),
-                                                        np.float32(2.0 * i) / np.float32(64)))
-            ang = np.float32(np.float32(pos) * inv)
-            assert abs(cos[row, i] - np.cos(ang, dtype=np.float32)) <= 1e-6
-            assert abs(sin[row, i] - np.sin(ang, dtype=np.float32)) <= 1e-6
+    """engine/input_prep.cpp:18-31: theta_i = 1 / theta^(2i / rope_dim), angle = position *
+    theta_i, cos / sin of the angle, in fp32 through the host libm.  The product's host
+    function (b2w4_rope_tables) and the oracle's give the same bits, and those are the libm's
+    own, which numpy's float cosine does not always match."""
+    import ctypes
+    cos, sin = dec.rope_tables(range(5, 305), 64, 1e6)
+    assert cos.shape == sin.shape == (300, 32) and cos.dtype == np.float32
+    o_cos, o_sin = ol.rope_tables(300, 5, 64, 1e6)
+    assert cos.tobytes() == o_cos.tobytes() and sin.tobytes() == o_sin.tobytes()
+    first = dec.rope_tables([0], 64, 1e6)
+    assert (first[0] == 1).all() and (first[1] == 0).all()
+    libm = ctypes.CDLL("libm.so.6")
+    for f in (libm.cosf, libm.sinf):
+        f.restype, f.argtypes = ctypes.c_float, [ctypes.c_float]
+    libm.powf.restype, libm.powf.argtypes = ctypes.c_float, [ctypes.c_float, ctypes.c_float]
+    for row, i in ((0, 0), (1, 6), (17, 15), (299, 31)):
+        inv = np.float32(1.0) / np.float32(libm.powf(1e6, float(np.float32(2.0 * i) /
+                                                                np.float32(64))))
+        angle = float(np.float32(np.float32(5 + row) * inv))
+        assert cos[row, i] == np.float32(libm.cosf(angle))
+        assert sin[row, i] == np.float32(libm.sinf(angle))
+    with pytest.raises(ValueError):
+        dec.rope_tables([0, 2, 3], 64, 1e6)

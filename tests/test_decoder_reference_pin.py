@@ -14,6 +14,14 @@ tests/golden/make_decoder_golden.py.
   * with W4A8 (the arithmetic of the GPU path and of the reference's ARM build) the logits sit
     within the activation-quantisation distance of the engine's and the tokens are the same
     (the fixture's seed was chosen for margins above that distance);
+  * against the engine run with the W4A8 matmul at its provider seam
+    (kernels/cpu_platform.h:75-79; oracle/ref_shim.cpp) -- the reference's graph executor,
+    norms, rotary embedding, attention, MoE control flow and sampler around the restated
+    matmul -- the dense CPU decoder is identical BIT FOR BIT, logits and tokens, on the
+    recorded run and, where the reference library is present, live on prompts of many
+    lengths; with routed experts the logits agree to a few ulp (2e-6) and the tokens exactly:
+    the engine's x86 build takes the router's fp16 matmul and the weighted sum of the expert
+    outputs in another order than its ARM build, which the oracle follows;
   * (gpu) the device decoder gives the engine's tokens too, eager and replayed.
 """
 import os
@@ -30,9 +38,12 @@ GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 
 
 def load_fixture(stem):
-    package = pkg.package.read_package(os.path.join(GOLDEN, stem + "_w4g128.mollm"))
+    path = os.path.join(GOLDEN, stem + "_w4g128.mollm")
+    package = pkg.package.read_package(path)
+    package.path = path
     cfg, weights = pkg.package.qwen3_decoder_weights(package)
     ref = np.load(os.path.join(GOLDEN, stem + "_reference.npz"))
+    package.w4a8 = (ref["tokens_w4a8"].tolist(), ref["logits_w4a8"])
     return package, cfg, weights, ref["prompt"].tolist(), ref["tokens"].tolist(), ref["logits"]
 
 
@@ -84,6 +95,43 @@ def test_w4a8_tokens_are_the_reference_engines(fixture):
     assert min(margins) > 1e-2
 
 
+def test_w4a8_decoder_is_the_engine_with_the_w4a8_provider_bit_for_bit(fixture):
+    package, cfg, weights, prompt, tokens, _ = fixture
+    engine_tokens, engine_logits = package.w4a8
+    first = []
+    got, _ = ol.dense_decoder_tokens(cfg, weights, prompt, len(tokens), first_logits=first)
+    if cfg.experts:
+        assert rel_l2(first[0], engine_logits) < 2e-6
+    else:
+        assert first[0].tobytes() == engine_logits.tobytes()
+    assert got == engine_tokens
+
+
+@pytest.mark.skipif(not ol.have_ref(), reason="the reference library is not built")
+def test_live_engine_with_the_w4a8_provider_on_other_prompts(fixture):
+    """The committed package through the live reference engine, prompts of several lengths
+    (one token: every matmul of the prompt takes the one-row rule)."""
+    package, cfg, weights, *_ = fixture
+    for length in (1, 2, 3, 5, 8, 17, 40):
+        prompt = np.random.default_rng(200 + length).integers(0, cfg.vocab, length).tolist()
+        engine_tokens, engine_logits = ol.ref_engine_generate(package.path, prompt, 6,
+                                                              cfg.vocab, w4a8=True)
+        first = []
+        got, margins = ol.dense_decoder_tokens(cfg, weights, prompt, 6, first_logits=first)
+        if cfg.experts:
+            assert rel_l2(first[0], engine_logits) < 2e-6, length
+        else:
+            assert first[0].tobytes() == engine_logits.tobytes(), length
+        if min(margins) > 1e-4:  # a few ulp cannot turn a token with such a margin
+            assert got == engine_tokens, length
+    # and the unmodified engine still is what the fixture recorded
+    recorded = np.load(os.path.join(GOLDEN, os.path.basename(package.path).replace(
+        "_w4g128.mollm", "_reference.npz")))
+    live, _ = ol.ref_engine_generate(package.path, recorded["prompt"].tolist(),
+                                     len(recorded["tokens"]), cfg.vocab)
+    assert live == recorded["tokens"].tolist()
+
+
 def test_decoder_driver_gives_the_reference_engines_tokens_on_the_cpu(fixture):
     """palm-infra_b200/decoder.py itself -- the operator sequence, buffers and cache handling
     that run on the GPU -- with the oracle standing in for the device operators."""
@@ -107,5 +155,5 @@ def test_device_decoder_gives_the_reference_engines_tokens(fixture):
     replayed = model.generate(prompt, len(tokens), replay=True)
     model.free()
     ctx.close()
-    assert eager == tokens
+    assert eager == tokens == fixture[0].w4a8[0]
     assert replayed == tokens
