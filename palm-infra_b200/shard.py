@@ -23,6 +23,26 @@ def shard_blocks(blocks, n, k, rank, world):
     return blocks[(lo // 8) * tile_bytes:(hi // 8) * tile_bytes], hi - lo, lo
 
 
+def shard_blocks_k(blocks, n, k, rank, world):
+    """The other way to cut a weight: by input features.  Rank r keeps the 128-wide groups
+    [r * G / P, (r + 1) * G / P) of every row, as a BG128 weight [N, K / P] of its own, and
+    multiplies them with its slice of the activation row; the ranks' outputs are partial sums
+    that an all-reduce adds up.  The int32 group sums and the activation scales are the
+    one-GPU ones (groups stay whole), but the fp32 chain of a row is now P chains added in
+    another order, so the result equals the one-GPU result to fp32 rounding, not bit for bit --
+    the price for an exchange of N values instead of a gather before a wide-K matmul (o and
+    down projections).  Returns (blocks [N, K / P], first input feature)."""
+    import numpy as np
+    groups = k // 128
+    if k % 128 or groups % world or n % 8:
+        raise ValueError(f"K={k} must split into whole 128-groups over {world} ranks, N={n} "
+                         "into 8-row tiles")
+    per = groups // world
+    tiles = blocks.reshape(n // 8, groups, BLOCK_BYTES)
+    mine = np.ascontiguousarray(tiles[:, rank * per:(rank + 1) * per]).reshape(-1)
+    return mine, rank * per * 128
+
+
 def rows_of(blocks, k, lo, hi):
     """The BG128 blocks of rows [lo, hi) (multiples of 8) of a weight with K columns."""
     if lo % 8 or hi % 8:

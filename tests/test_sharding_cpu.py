@@ -42,6 +42,43 @@ def test_row_sharded_matmul_world2(tmp_path):
     assert y.tobytes() == ol.matmul_w4(blocks, N, K, x).tobytes()
 
 
+def _k_worker(rank, world, port, out_dir):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    n, k, m = 72, 1024, 3
+    blocks = pkg.synth.bg128_weight(5, 7, n, k)
+    x = pkg.synth.activations(6, 7, m, k)
+    mine, k0 = pkg.shard.shard_blocks_k(blocks, n, k, rank, world)
+    kl = k // world
+    y_local, sums = ol.matmul_w4(mine, n, kl, np.ascontiguousarray(x[:, k0:k0 + kl]),
+                                 want_sums=True)
+    y = torch.from_numpy(y_local.copy())
+    dist.all_reduce(y)  # the partial sums meet
+    parts = [torch.zeros(sums.shape, dtype=torch.int32) for _ in range(world)]
+    dist.all_gather(parts, torch.from_numpy(sums))
+    if rank == 0:
+        np.save(os.path.join(out_dir, "y_k.npy"), y.numpy())
+        np.save(os.path.join(out_dir, "sums_k.npy"), torch.cat(parts, dim=2).numpy())
+    dist.destroy_process_group()
+
+
+def test_input_feature_split_with_all_reduce_world2(tmp_path):
+    """The K-split variant: whole 128-groups per rank, partial outputs all-reduced.  Integer
+    group sums are the unsharded ones exactly; the fp32 result agrees to rounding."""
+    port = 29500 + (os.getpid() + 911) % 2000
+    mp.spawn(_k_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    n, k = 72, 1024
+    blocks = pkg.synth.bg128_weight(5, 7, n, k)
+    x = pkg.synth.activations(6, 7, 3, k)
+    want, want_sums = ol.matmul_w4(blocks, n, k, x, want_sums=True)
+    assert (np.load(tmp_path / "sums_k.npy") == want_sums).all()
+    got = np.load(tmp_path / "y_k.npy")
+    assert np.linalg.norm(got - want) / np.linalg.norm(want) < 1e-6
+    with pytest.raises(ValueError):
+        pkg.shard.shard_blocks_k(blocks, n, k, 0, 3)
+
+
 def test_shard_ranges():
     assert pkg.shard.row_range(9728, 3, 8) == (3648, 4864)
     with pytest.raises(ValueError):
