@@ -170,6 +170,30 @@ int ref_select_moe_routes(const float* logits, int tokens, int num_experts,
     return 0;
 }
 
+// The same with every routing parameter the reference has (score kind, choice bias, expert
+// groups, scaling factor).
+int ref_select_moe_routes_ex(const float* logits, int tokens, int num_experts, int top_k,
+                             int score_func, int normalize_topk, int num_groups,
+                             int topk_groups, float scaling, const float* bias,
+                             int32_t* indices, float* weights) {
+    mollm::detail::MoeRoutingParams p;
+    p.num_experts = num_experts;
+    p.top_k = top_k;
+    p.score_func = score_func;
+    p.normalize_topk = normalize_topk != 0;
+    p.num_groups = num_groups;
+    p.topk_groups = topk_groups;
+    p.scaling_factor = scaling;
+    std::vector<int> idx;
+    std::vector<float> w;
+    if (!mollm::detail::select_moe_routes(logits, tokens, bias, p, idx, w))
+        return -1;
+    for (size_t i = 0; i < idx.size(); ++i)
+        indices[i] = idx[i];
+    std::memcpy(weights, w.data(), w.size() * sizeof(float));
+    return 0;
+}
+
 // Routed MoE op with an fp16 router [E, H], BG128 gate_up [E*2I, H] and BG128
 // down [E*H, I] aggregates, softmax top-k routing and no shared expert (the
 // Qwen3-MoE configuration, models/qwen3_moe.py:782-797 of the reference).

@@ -689,6 +689,129 @@ void orc_sdpa_head(const float* query, const float* key, const float* value, flo
 }
 
 
+/* ------------------------------------------- routing, the other score kinds --
+ * kernels/moe_routing.cpp:25-169 beyond the softmax case: score kind 1 takes the logistic
+ * function of each logit, kind 2 the square root of softplus (:10-22); an optional per-expert
+ * bias is added for the CHOICE only (:72-73); with expert groups, a group is scored by the
+ * sum of its two best choice scores (the best alone if it has one expert), the best
+ * `topk_groups` groups stay -- insertion with strict '>', so the lower group id wins ties --
+ * and the experts of the other groups drop out (:76-122); the top k choice scores are taken
+ * as in the softmax case; the weights are the UNBIASED scores of the chosen experts, divided
+ * by their sum when asked (0 if the sum is not positive), times a scaling factor (:146-156).
+ * Score kind 0 is orc_moe_select_routes_softmax.                                            */
+
+static float score_logistic(float v) { return 1.0f / (1.0f + orc_exp(-v)); }
+
+static float score_sqrt_softplus(float v) {
+    float sp = v > 0.0f ? v + log1pf(orc_exp(-v)) : log1pf(orc_exp(v));
+    return sqrtf(sp);
+}
+
+int orc_moe_select_routes(const float* logits, int tokens, int num_experts, int top_k,
+                          int score_kind, int normalize, int groups, int topk_groups,
+                          float scaling, const float* bias, int32_t* indices, float* weights) {
+    if (score_kind == 0)
+        return orc_moe_select_routes_softmax(logits, tokens, num_experts, top_k, indices,
+                                             weights);
+    if (!logits || tokens <= 0 || num_experts <= 0 || top_k <= 0 || top_k > num_experts ||
+        score_kind < 0 || score_kind > 2)
+        return -1;
+    if (groups < 1)
+        groups = 1;
+    if (topk_groups <= 0 || topk_groups > groups)
+        topk_groups = groups;
+    int per_group = num_experts / groups;
+    float* score = (float*)malloc(sizeof(float) * (size_t)num_experts);
+    float* choice = (float*)malloc(sizeof(float) * (size_t)num_experts);
+    float* kept_score = (float*)malloc(sizeof(float) * (size_t)topk_groups);
+    int* kept_group = (int*)malloc(sizeof(int) * (size_t)topk_groups);
+    for (int t = 0; t < tokens; ++t) {
+        const float* row = logits + (size_t)t * num_experts;
+        int32_t* idx = indices + (size_t)t * top_k;
+        float* w = weights + (size_t)t * top_k;
+        for (int e = 0; e < num_experts; ++e) {
+            score[e] = score_kind == 1 ? score_logistic(row[e]) : score_sqrt_softplus(row[e]);
+            choice[e] = score[e] + (bias ? bias[e] : 0.0f);
+        }
+        if (groups > 1 && per_group > 0 && topk_groups < groups) {
+            for (int j = 0; j < topk_groups; ++j) {
+                kept_score[j] = -INFINITY;
+                kept_group[j] = 0;
+            }
+            for (int g = 0; g < groups; ++g) {
+                int lo = g * per_group;
+                int hi = g == groups - 1 ? num_experts : lo + per_group;
+                float first = -INFINITY, second = -INFINITY;
+                for (int e = lo; e < hi; ++e) {
+                    if (choice[e] > first) {
+                        second = first;
+                        first = choice[e];
+                    } else if (choice[e] > second) {
+                        second = choice[e];
+                    }
+                }
+                float gs = isfinite(second) ? first + second : first;
+                for (int j = 0; j < topk_groups; ++j) {
+                    if (gs > kept_score[j]) {
+                        for (int s = topk_groups - 1; s > j; --s) {
+                            kept_score[s] = kept_score[s - 1];
+                            kept_group[s] = kept_group[s - 1];
+                        }
+                        kept_score[j] = gs;
+                        kept_group[j] = g;
+                        break;
+                    }
+                }
+            }
+            for (int e = 0; e < num_experts; ++e) {
+                int g = e / per_group;
+                if (g > groups - 1)
+                    g = groups - 1;
+                int kept = 0;
+                for (int j = 0; j < topk_groups; ++j)
+                    kept |= kept_group[j] == g;
+                if (!kept)
+                    choice[e] = -INFINITY;
+            }
+        }
+        for (int j = 0; j < top_k; ++j) {
+            idx[j] = 0;
+            w[j] = -INFINITY;
+        }
+        for (int e = 0; e < num_experts; ++e) {
+            float v = choice[e];
+            for (int j = 0; j < top_k; ++j) {
+                if (v > w[j]) {
+                    for (int s = top_k - 1; s > j; --s) {
+                        w[s] = w[s - 1];
+                        idx[s] = idx[s - 1];
+                    }
+                    w[j] = v;
+                    idx[j] = e;
+                    break;
+                }
+            }
+        }
+        float sum = 0.0f;
+        for (int j = 0; j < top_k; ++j) {
+            w[j] = score[idx[j]];
+            sum += w[j];
+        }
+        if (normalize) {
+            float inverse = sum > 0.0f ? 1.0f / sum : 0.0f;
+            for (int j = 0; j < top_k; ++j)
+                w[j] *= inverse;
+        }
+        for (int j = 0; j < top_k; ++j)
+            w[j] *= scaling;
+    }
+    free(score);
+    free(choice);
+    free(kept_score);
+    free(kept_group);
+    return 0;
+}
+
 /* ---------------------------------------------------------- rotary tables --
  * engine/input_prep.cpp:18-31 (fill_rope_cache): per position and feature pair i,
  * theta_i = 1 / pow(rope_theta, 2 i / rope_dim), angle = position * theta_i, cos and sin of

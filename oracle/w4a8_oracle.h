@@ -119,6 +119,13 @@ void orc_sdpa_head(const float* query, const float* key, const float* value, flo
                    int query_tokens, int key_tokens, int key_dim, int value_dim, float scale,
                    const float* mask);
 
+/* Routing with the reference's other score kinds (1 logistic, 2 sqrt(softplus)), optional
+ * choice bias, expert groups, optional normalisation and a scaling factor
+ * (kernels/moe_routing.cpp:25-169); kind 0 forwards to the softmax form above. */
+int orc_moe_select_routes(const float* logits, int tokens, int num_experts, int top_k,
+                          int score_kind, int normalize, int groups, int topk_groups,
+                          float scaling, const float* bias, int32_t* indices, float* weights);
+
 /* Rotary tables as the reference's engine fills them (engine/input_prep.cpp:18-31). */
 void orc_rope_tables(float* cos_out, float* sin_out, int positions, int first_position,
                      int rope_dim, float rope_theta);

@@ -278,6 +278,23 @@ def ref_matmul(blocks, n, k, x, act=0, begin=0, length=-1, threads=1):
     return y
 
 
+def select_routes_ex(logits, top_k, score_kind, normalize=True, groups=1, topk_groups=1,
+                     scaling=1.0, bias=None, which=None):
+    """Routing with every parameter of the reference (kernels/moe_routing.h:8-16); `which` =
+    ref() runs the reference's own select_moe_routes."""
+    logits = np.ascontiguousarray(logits, dtype=np.float32)
+    t, e = logits.shape
+    idx = np.zeros((t, top_k), dtype=np.int32)
+    w = np.zeros((t, top_k), dtype=np.float32)
+    b = None if bias is None else np.ascontiguousarray(bias, dtype=np.float32)
+    fn = (which.ref_select_moe_routes_ex if which is not None
+          else oracle().orc_moe_select_routes)
+    rc = fn(_ptr(logits), t, e, top_k, score_kind, 1 if normalize else 0, groups, topk_groups,
+            C.c_float(scaling), _ptr(b), _ptr(idx), _ptr(w))
+    assert rc == 0, rc
+    return idx, w
+
+
 def ref_select_routes(logits, top_k):
     logits = np.ascontiguousarray(logits, dtype=np.float32)
     t, e = logits.shape

@@ -132,6 +132,29 @@ def test_routing_ties_pick_lowest_expert():
     assert list(c["idx"][0][:3]) == [1, 3, 5]     # three-way tie at 2.0
 
 
+@pytest.mark.skipif(not ol.have_ref(), reason="reference library not built")
+@pytest.mark.parametrize("kind", [0, 1, 2])
+def test_routing_score_kinds_groups_bias_match_reference(kind):
+    """select_moe_routes with the logistic and sqrt-softplus score kinds, a choice bias,
+    expert groups (8 groups, 3 kept), with and without normalisation, a scaling factor, ties
+    and large logits: indices and weights identical to the reference's, bit for bit."""
+    rng = np.random.default_rng(40 + kind)
+    logits = rng.normal(0, 2.5, (37, 64)).astype(np.float32)
+    logits[3, 10:14] = logits[3, 10]        # ties inside a group
+    logits[4] = 0.0                         # every expert equal
+    logits[5, :8] = 60.0                    # exp(-x) underflows / softplus is linear
+    logits[6, :8] = -60.0
+    bias = rng.normal(0, 0.3, 64).astype(np.float32)
+    for normalize in (True, False):
+        for groups, kept in ((1, 1), (8, 3), (8, 8), (4, 1)):
+            for b in (None, bias):
+                got = ol.select_routes_ex(logits, 6, kind, normalize, groups, kept, 2.5, b)
+                want = ol.select_routes_ex(logits, 6, kind, normalize, groups, kept, 2.5, b,
+                                           which=ol.ref())
+                assert (got[0] == want[0]).all(), (kind, normalize, groups, kept)
+                assert got[1].tobytes() == want[1].tobytes(), (kind, normalize, groups, kept)
+
+
 def test_moe_control_flow_matches_reference():
     c = case("moe_small")
     t, h, e, top_k, inter = [int(v) for v in c["meta"]]
