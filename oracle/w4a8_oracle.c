@@ -383,11 +383,53 @@ int orc_moe_select_routes_softmax(const float* logits, int tokens,
  * with an fp16, unquantised router weight.  The reference leaves the fp32
  * summation order to whichever dense kernel the host selects; the oracle
  * accumulates in fp64 and rounds once, the order-free reading of that sum.  */
+/* Two places of the MoE operator are summed in an order that depends on how the reference
+ * was built.  Mode 0 (default, what the GPU follows): router logits as the exact dot product
+ * rounded once, the weighted sum of expert outputs with one fused multiply-add per term (the
+ * ARM build contracts `dst += w * src`, kernels/moe.cpp:1100-1110).  Mode 1, the x86 AVX-512
+ * build as compiled here: router logits through its fp16 dense kernel
+ * (kernels/matmul_x86_avx512.cpp:76-110: two 16-lane fused accumulators over alternate
+ * 16-feature chunks, added lane-wise, a last 16-chunk into the sum, the 16 lanes reduced by
+ * halves, a scalar tail), and `w * src` rounded before the addition (no fused instruction in
+ * that translation unit).  Mode 1 exists so that the whole operator can be compared bit for
+ * bit with the x86 engine.                                                                   */
+static int g_moe_host_build = 0;
+
+void orc_set_moe_host_build(int x86_avx512) { g_moe_host_build = x86_avx512 ? 1 : 0; }
+
+static float router_dot_x86_avx512(const float* a, const uint16_t* b_fp16, int count) {
+    float first[16] = {0}, second[16] = {0}, v[16];
+    int i = 0;
+    for (; i + 31 < count; i += 32)
+        for (int l = 0; l < 16; ++l) {
+            first[l] = fmaf(a[i + l], orc_fp16_to_fp32(b_fp16[i + l]), first[l]);
+            second[l] = fmaf(a[i + 16 + l], orc_fp16_to_fp32(b_fp16[i + 16 + l]), second[l]);
+        }
+    for (int l = 0; l < 16; ++l)
+        v[l] = first[l] + second[l];
+    for (; i + 15 < count; i += 16)
+        for (int l = 0; l < 16; ++l)
+            v[l] = fmaf(a[i + l], orc_fp16_to_fp32(b_fp16[i + l]), v[l]);
+    for (int width = 8; width >= 1; width >>= 1)
+        for (int l = 0; l < width; ++l)
+            v[l] = v[l] + v[l + width];
+    float sum = v[0];
+    for (; i < count; ++i)
+        sum += a[i] * orc_fp16_to_fp32(b_fp16[i]);
+    return sum;
+}
+
 void orc_router_logits(const float* hidden, int tokens, int hidden_size, int ldx,
                        const uint16_t* router_fp16, int num_experts,
                        float* logits) {
     for (int t = 0; t < tokens; ++t)
         for (int e = 0; e < num_experts; ++e) {
+            if (g_moe_host_build) {
+                logits[(size_t)t * num_experts + e] = router_dot_x86_avx512(
+                    hidden + (size_t)t * ldx, router_fp16 + (size_t)e * hidden_size,
+                    hidden_size);
+                continue;
+            }
             double acc = 0.0;
             for (int d = 0; d < hidden_size; ++d)
                 acc += (double)hidden[(size_t)t * ldx + d] *
@@ -485,8 +527,14 @@ int orc_moe_forward(const float* hidden, int tokens, int hidden_size, int ldx,
                 float* dst = out + (size_t)route_tokens[begin + i] * ldo;
                 const float* src = dn + (size_t)i * hidden_size;
                 float w = route_weights[begin + i];
-                for (int d = 0; d < hidden_size; ++d)
-                    dst[d] = fmaf(w, src[d], dst[d]);
+                for (int d = 0; d < hidden_size; ++d) {
+                    if (g_moe_host_build) {
+                        volatile float product = w * src[d]; /* rounded before the addition */
+                        dst[d] = dst[d] + product;
+                    } else {
+                        dst[d] = fmaf(w, src[d], dst[d]);
+                    }
+                }
             }
         }
         free(ex);

@@ -119,6 +119,11 @@ void orc_sdpa_head(const float* query, const float* key, const float* value, flo
                    int query_tokens, int key_tokens, int key_dim, int value_dim, float scale,
                    const float* mask);
 
+/* Which build of the reference the MoE operator's two order-sensitive sums follow: 0 (default)
+ * the ARM reading the GPU implements, 1 the x86 AVX-512 build (for bit-for-bit comparison with
+ * the engine compiled on an x86 host). */
+void orc_set_moe_host_build(int x86_avx512);
+
 /* Routing with the reference's other score kinds (1 logistic, 2 sqrt(softplus)), optional
  * choice bias, expert groups, optional normalisation and a scaling factor
  * (kernels/moe_routing.cpp:25-169); kind 0 forwards to the softmax form above. */

@@ -406,6 +406,12 @@ def causal_attention(q, k_all, v_all, heads, kv_heads, past, scale, which=None):
     return out
 
 
+def set_moe_host_build(x86_avx512):
+    """Which build of the reference the MoE operator's router dot product and weighted output
+    sum follow: False = the ARM reading the GPU implements, True = the x86 AVX-512 build."""
+    oracle().orc_set_moe_host_build(1 if x86_avx512 else 0)
+
+
 def rope_tables(positions, first_position, rope_dim, theta):
     """(cos, sin) [positions, rope_dim // 2] as the reference's engine fills them."""
     cos = np.zeros((positions, rope_dim // 2), dtype=np.float32)

@@ -21,7 +21,9 @@ tests/golden/make_decoder_golden.py.
     recorded run and, where the reference library is present, live on prompts of many
     lengths; with routed experts the logits agree to a few ulp (2e-6) and the tokens exactly:
     the engine's x86 build takes the router's fp16 matmul and the weighted sum of the expert
-    outputs in another order than its ARM build, which the oracle follows;
+    outputs in another order than its ARM build, which the oracle follows by default -- and
+    when the oracle is told to take those two sums the x86 way (ol.set_moe_host_build), that
+    decoder is bit-identical to the engine as well, so these two sums are the whole difference;
   * (gpu) the device decoder gives the engine's tokens too, eager and replayed.
 """
 import os
@@ -102,6 +104,15 @@ def test_w4a8_decoder_is_the_engine_with_the_w4a8_provider_bit_for_bit(fixture):
     got, _ = ol.dense_decoder_tokens(cfg, weights, prompt, len(tokens), first_logits=first)
     if cfg.experts:
         assert rel_l2(first[0], engine_logits) < 2e-6
+        ol.set_moe_host_build(True)  # the fixture was recorded with the x86 build
+        try:
+            again = []
+            got_x86, _ = ol.dense_decoder_tokens(cfg, weights, prompt, len(tokens),
+                                                 first_logits=again)
+        finally:
+            ol.set_moe_host_build(False)
+        assert again[0].tobytes() == engine_logits.tobytes()
+        assert got_x86 == engine_tokens
     else:
         assert first[0].tobytes() == engine_logits.tobytes()
     assert got == engine_tokens
@@ -120,6 +131,15 @@ def test_live_engine_with_the_w4a8_provider_on_other_prompts(fixture):
         got, margins = ol.dense_decoder_tokens(cfg, weights, prompt, 6, first_logits=first)
         if cfg.experts:
             assert rel_l2(first[0], engine_logits) < 2e-6, length
+            ol.set_moe_host_build(True)  # this host's build of the reference is the x86 one
+            try:
+                again = []
+                got_x86, _ = ol.dense_decoder_tokens(cfg, weights, prompt, 6,
+                                                     first_logits=again)
+            finally:
+                ol.set_moe_host_build(False)
+            assert again[0].tobytes() == engine_logits.tobytes(), length
+            assert got_x86 == engine_tokens, length
         else:
             assert first[0].tobytes() == engine_logits.tobytes(), length
         if min(margins) > 1e-4:  # a few ulp cannot turn a token with such a margin
