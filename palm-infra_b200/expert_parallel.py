@@ -116,3 +116,65 @@ class PeerExchangeMoE:
         e.ctx.moe_forward_ep(hidden, e.router, e.top_k, e.intermediate, e.gate_up, e.down,
                              e.expert_begin, e.expert_count, self.group, self.stage_rows, out)
         return out
+
+
+class AllToAllMoE:
+    """The routed MoE with SEQUENCE-sharded activations: rank r holds its own tokens only
+    (contiguous blocks of the sequence, rank order = token order), routes them itself (the
+    router is replicated), sends every routed row to the rank that owns its expert, gets the
+    expert outputs back the same way and combines its tokens' routes.  Two all-to-all
+    exchanges of tokens * top_k rows per layer instead of an all-reduce of the whole route
+    buffer; no rank ever holds another rank's hidden states.
+
+    An expert's owner sees all of that expert's rows of the step, in global token order (rows
+    arrive by source rank, a rank's rows in its own token order), so the reference's
+    per-expert activation rule (per 32 values once an expert holds several rows,
+    kernels/moe.cpp:1055-1058) sees the same counts and the result is the one-device result
+    bit for bit.
+
+    `engine` supplies three pieces: routes(hidden) -> (indices [T, k], weights [T, k]);
+    expert_rows(rows [R, H], experts [R]) -> outputs [R, H] of the local experts (ids relative
+    to the rank's first expert, rows of one expert in the order given); combine(route_out
+    [T * k, H], indices, weights, out).  The CPU tests supply them from the oracle.  On the
+    device, routes and combine exist (b2w4_moe_select_routes after a router matmul,
+    b2w4_moe_combine); expert_rows -- the grouped expert matmuls over an explicit row list --
+    is inside libb200w4 but not exported yet, so this class is host logic verified on CPU
+    ranks only."""
+
+    def __init__(self, engine, dist, rank, world, num_experts, group=None):
+        self.engine, self.dist, self.rank, self.world = engine, dist, rank, world
+        self.num_experts, self.group = num_experts, group
+        if num_experts % world:
+            raise ValueError(f"{num_experts} experts do not split over {world} ranks")
+        self.per_rank = num_experts // world
+
+    def forward(self, hidden, out):
+        import torch
+        dist, world, per = self.dist, self.world, self.per_rank
+        idx, wts = self.engine.routes(hidden)
+        tokens, top_k = idx.shape
+        h = hidden.shape[1]
+        flat = idx.reshape(-1).to(torch.int64)                 # route (t, j) -> expert
+        owner = flat // per
+        order = torch.argsort(owner, stable=True)              # by owner, token order inside
+        send_counts = torch.bincount(owner, minlength=world)
+        recv_counts = torch.zeros_like(send_counts)
+        dist.all_to_all_single(recv_counts, send_counts, group=self.group)
+        send_rows = hidden[order // top_k].contiguous()
+        send_experts = (flat[order] - owner[order] * per).contiguous()
+        n_recv = int(recv_counts.sum())
+        recv_rows = torch.zeros((n_recv, h), dtype=hidden.dtype, device=hidden.device)
+        recv_experts = torch.zeros((n_recv,), dtype=torch.int64, device=hidden.device)
+        ins, outs = send_counts.tolist(), recv_counts.tolist()
+        dist.all_to_all_single(recv_rows, send_rows, output_split_sizes=outs,
+                               input_split_sizes=ins, group=self.group)
+        dist.all_to_all_single(recv_experts, send_experts, output_split_sizes=outs,
+                               input_split_sizes=ins, group=self.group)
+        done = self.engine.expert_rows(recv_rows, recv_experts)
+        back = torch.zeros_like(send_rows)
+        dist.all_to_all_single(back, done.contiguous(), output_split_sizes=ins,
+                               input_split_sizes=outs, group=self.group)
+        route_out = torch.zeros((tokens * top_k, h), dtype=hidden.dtype, device=hidden.device)
+        route_out[order] = back
+        self.engine.combine(route_out, idx, wts, out)
+        return out

@@ -222,3 +222,69 @@ def test_row_sharded_greedy_token(tmp_path, world):
     want = [ol.argmax_token(full[m]) for m in range(M)]
     for rank in range(world):
         assert np.load(tmp_path / f"tok{rank}.npy").tolist() == want
+
+
+# ---- sequence-sharded MoE: rows travel to the experts' owners and back (all-to-all) -------
+class _OracleRowsEngine:
+    """The oracle standing in for the three device pieces AllToAllMoE needs."""
+
+    def __init__(self, router, gu_local, dn_local, local_experts):
+        self.router, self.gu, self.dn, self.cnt = router, gu_local, dn_local, local_experts
+
+    def routes(self, hidden):
+        if hidden.shape[0] == 0:  # a rank without tokens still takes part in the exchanges
+            return (torch.zeros((0, TOPK), dtype=torch.int32),
+                    torch.zeros((0, TOPK), dtype=torch.float32))
+        idx, w = ol.select_routes(ol.router_logits(hidden.numpy(), self.router), TOPK)
+        return torch.from_numpy(idx), torch.from_numpy(w)
+
+    def expert_rows(self, rows, experts):
+        if rows.shape[0] == 0:
+            return rows.clone()
+        # every received row is a one-route token of its expert; the reference's rule sees
+        # how many rows each expert holds
+        idx = experts.to(torch.int32).numpy().reshape(-1, 1)
+        return torch.from_numpy(ol.expert_route_outputs(rows.numpy(), idx, I, self.gu, self.dn,
+                                                        self.cnt, rule=ol.ACT_G32))
+
+    def combine(self, route_out, idx, wts, out):
+        if out.shape[0]:
+            out.copy_(torch.from_numpy(ol.moe_combine(route_out.numpy(), idx.numpy(),
+                                                      wts.numpy())))
+
+
+def _a2a_worker(rank, world, port, out_dir, tokens):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    router, gu, dn, _ = _moe_inputs()
+    x = pkg.synth.activations(9, 40 + tokens, tokens, H)
+    # uneven contiguous token blocks: rank r takes tokens [cut[r], cut[r + 1])
+    cut = [0] + [min(tokens, (r + 1) * tokens // world + (1 if r == 0 else 0))
+                 for r in range(world - 1)] + [tokens]
+    mine = torch.from_numpy(np.ascontiguousarray(x[cut[rank]:cut[rank + 1]]))
+    ep = pkg.expert_parallel
+    gu_l, lo, cnt = ep.shard_expert_blocks(gu, E, 2 * I, H, rank, world)
+    dn_l, _, _ = ep.shard_expert_blocks(dn, E, H, I, rank, world)
+    op = ep.AllToAllMoE(_OracleRowsEngine(router, np.ascontiguousarray(gu_l),
+                                          np.ascontiguousarray(dn_l), cnt),
+                        dist, rank, world, E)
+    out = torch.zeros_like(mine)
+    op.forward(mine, out)
+    np.save(os.path.join(out_dir, f"a2a_{rank}.npy"), out.numpy())
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,tokens", [(2, 5), (4, 11), (2, 1)])
+def test_sequence_sharded_moe_all_to_all(tmp_path, world, tokens):
+    """Tokens split over the ranks, rows sent to the experts' owners and back: the one-device
+    result bit for bit under the reference's per-expert rule (an expert's owner sees all its
+    rows), including a rank with no tokens."""
+    port = 29500 + (os.getpid() + 313 * world + tokens) % 2000
+    mp.spawn(_a2a_worker, args=(world, port, str(tmp_path), tokens), nprocs=world, join=True)
+    router, gu, dn, _ = _moe_inputs()
+    x = pkg.synth.activations(9, 40 + tokens, tokens, H)
+    want = ol.moe_forward(x, router, TOPK, I, gu, dn, rule=ol.ACT_G32)[0]
+    got = np.concatenate([np.load(tmp_path / f"a2a_{r}.npy") for r in range(world)])
+    assert got.shape == want.shape
+    assert got.tobytes() == want.tobytes()
