@@ -365,7 +365,10 @@ size_t b2w4_chain_weight_bytes(const b2w4_chain* chain);
  *                      [tokens][heads][dim] over keys 0 .. past + t, full-row softmax,
  *                      P*V accumulated in ascending key order (dim <= 256; the scores
  *                      of all visible keys are held in shared memory, which bounds
- *                      them near 45,000); past_dev (optional)
+ *                      them near 45,000; runs of eight or more tokens take a tiled
+ *                      form -- one block per kv head and tile of query tokens, keys
+ *                      and values staged once per tile, the same bits -- while a
+ *                      tile's scores fit, about 1,400 keys); past_dev (optional)
  *                      gives `past` from device memory instead
  *                      k_dev and v_dev both NULL: nothing is appended, the cache rows
  *                      past .. past + tokens - 1 are in place already (b2w4_qkv_prepare)
