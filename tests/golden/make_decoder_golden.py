@@ -5,7 +5,7 @@ on them.
 
     python tests/golden/make_decoder_golden.py [dense seed] [mixture-of-experts seed]
 
-Needs the reference tree (REF_ROOT, default /root/reference) and `make -C oracle ref reftools`;
+Needs the reference tree (environment variable REF_ROOT) and `make -C oracle ref reftools`;
 it is run where the reference is available, and its outputs are committed:
 
     tests/golden/tiny_qwen3_w4g128.mollm        the dense package (about 1 MB)
